@@ -1,0 +1,191 @@
+/* brisk_cuda.h - C ABI of the B200 (sm_100a) token-loop backend for brisk-llm.
+ *
+ * The reference has no C layer: its backends are C++ classes behind `brisk::Engine`
+ * (src/engine.h:13-37), built at three call sites next to the Metal one
+ * (src/main.cpp:203-212, :335-344; src/server.cpp:241-249). This header is the
+ * boundary a `CudaSession : Engine` binds to: plain pointers and sizes, status
+ * ints instead of exceptions, no C++ or torch types. Each entry point names the
+ * reference interface it stands in for.
+ *
+ * Threading: one caller thread per session, like an Engine (the reference's server
+ * serialises requests, src/server.cpp:160-205). Nothing here falls back to the CPU:
+ * every call fails with a message when no CUDA device is usable.
+ */
+#ifndef BRISK_CUDA_H
+#define BRISK_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BRISK_CUDA_ABI_VERSION 1u
+
+/* Tensor storage types, numbered as in ggml / the reference's TensorType (src/gguf.h:22-27).
+ * Quantised data is passed exactly as it lies in a GGUF file: row after row of blocks
+ * (block layouts: src/quant.h:26-130). */
+enum brisk_cuda_type {
+    BRISK_TYPE_F32 = 0,
+    BRISK_TYPE_F16 = 1,
+    BRISK_TYPE_Q4_0 = 2,
+    BRISK_TYPE_Q8_0 = 8,
+    BRISK_TYPE_Q4_K = 12,
+    BRISK_TYPE_Q6_K = 14,
+    BRISK_TYPE_TQ2_0 = 35
+};
+
+/* Model families of the configured workloads (subset of brisk::Architecture, src/model.h:20-31). */
+enum brisk_cuda_arch {
+    BRISK_ARCH_QWEN3 = 0,  /* per-head RMS norm on Q and K, SiLU-gated FFN, NeoX RoPE            */
+    BRISK_ARCH_LLAMA = 1,  /* adjacent-pair RoPE, optional per-frequency divisors (rope_freqs)  */
+    BRISK_ARCH_BITNET = 2  /* sub-norms before o_proj and down_proj, squared-ReLU gate, NeoX    */
+};
+
+/* A rows x cols weight matrix, `rows` outputs over `cols` inputs (brisk::Matrix, src/model.h:123-134).
+ * `data` is a HOST pointer that only has to stay valid during brisk_cuda_create(): the library
+ * repacks into its own device layout and keeps no host pointer. */
+typedef struct brisk_cuda_matrix {
+    int32_t type; /* enum brisk_cuda_type */
+    int32_t reserved;
+    uint64_t rows;
+    uint64_t cols;
+    const void* data;
+    uint64_t bytes;
+} brisk_cuda_matrix;
+
+/* One decoder layer (brisk::Model::Layer, src/model.h:143-176). Float vectors are f32 host
+ * pointers; an absent one is NULL. */
+typedef struct brisk_cuda_layer {
+    const float* attn_norm;     /* [hidden]                                   */
+    brisk_cuda_matrix q, k, v;  /* [heads*head_dim | kv*head_dim] x hidden    */
+    const float* q_norm;        /* [head_dim] or NULL (qwen3)                 */
+    const float* k_norm;        /* [head_dim] or NULL                         */
+    const float* attn_sub_norm; /* [heads*head_dim] or NULL (bitnet)          */
+    brisk_cuda_matrix o;        /* hidden x heads*head_dim                    */
+    const float* ffn_norm;      /* [hidden]                                   */
+    brisk_cuda_matrix gate, up; /* ffn x hidden                               */
+    const float* ffn_sub_norm;  /* [ffn] or NULL (bitnet)                     */
+    brisk_cuda_matrix down;     /* hidden x ffn                               */
+} brisk_cuda_layer;
+
+/* POD mirror of the brisk::ModelConfig fields the supported families use (src/model.h:36-62)
+ * plus the bound tensors (brisk::Model, src/model.cpp:326-421). */
+typedef struct brisk_cuda_model {
+    uint32_t abi_version; /* BRISK_CUDA_ABI_VERSION */
+    int32_t arch;         /* enum brisk_cuda_arch   */
+    uint32_t vocab_size;
+    uint32_t hidden;
+    uint32_t layer_count;
+    uint32_t head_count;
+    uint32_t kv_head_count;
+    uint32_t head_dim;
+    uint32_t ffn;
+    uint32_t context_length;
+    float rope_base;
+    float rms_epsilon;
+    int32_t rope_neox;           /* 1: pair (i, i+head_dim/2); 0: pair (2i, 2i+1)          */
+    uint32_t rope_factor_count;  /* 0 or head_dim/2                                        */
+    const float* rope_factors;   /* per-frequency divisors of the angle (src/model.cpp:886) */
+    brisk_cuda_matrix token_embd; /* vocab x hidden                                        */
+    brisk_cuda_matrix output;     /* vocab x hidden; data == NULL: tied to token_embd       */
+    const float* output_norm;     /* [hidden]                                              */
+    const brisk_cuda_layer* layers; /* [layer_count]                                        */
+} brisk_cuda_model;
+
+typedef struct brisk_cuda_options {
+    uint64_t max_context; /* 0: the model's context_length (src/model.cpp:659)              */
+    int32_t device;       /* CUDA ordinal                                                   */
+    int32_t tp_rank;      /* tensor-parallel rank of this process, 0 when tp_size <= 1      */
+    int32_t tp_size;      /* 1: no tensor parallelism                                       */
+    uint32_t flags;       /* BRISK_CUDA_FLAG_*                                              */
+    const void* tp_unique_id; /* 128 bytes from brisk_cuda_tp_unique_id(), same on all ranks */
+} brisk_cuda_options;
+
+#define BRISK_CUDA_FLAG_NO_GRAPH 1u      /* launch decode kernels one by one instead of replaying a CUDA graph */
+#define BRISK_CUDA_FLAG_NO_MEGAKERNEL 2u /* decode through per-operation kernels only                         */
+
+typedef struct brisk_cuda_session brisk_cuda_session;
+
+/* Counters of the most recent eval / generate call, for benchmarks. */
+typedef struct brisk_cuda_stats {
+    double device_ms;        /* CUDA-event time of the call's device work on the session's stream */
+    uint64_t kernel_launches; /* kernels of this library launched (graph nodes count one each)     */
+    uint64_t weight_bytes;    /* bytes of weight planes resident in HBM (all matrices + norms)     */
+    uint64_t kv_bytes;        /* bytes of the f16 K/V cache                                        */
+    uint64_t h2d_bytes;       /* host->device bytes copied by the call                             */
+    uint64_t d2h_bytes;       /* device->host bytes copied by the call                             */
+} brisk_cuda_stats;
+
+/* Number of usable CUDA devices; 0 when there is none or the driver is missing.
+ * (The Metal backend's equivalent is the `gpu` flag check, src/main.cpp:204-212.) */
+int brisk_cuda_device_count(void);
+
+/* Builds a session: uploads and repacks every tensor once, allocates the f16 K/V cache for
+ * min(max_context, context_length) positions and the scratch. Stands in for
+ * `MetalSession(model, file, max_context)` (src/metal/metal_session.h:23) and
+ * `Session(model, threads, max_context)` (src/model.cpp:655-702). Returns NULL and writes a
+ * message into err on failure. */
+brisk_cuda_session* brisk_cuda_create(const brisk_cuda_model* model, const brisk_cuda_options* options, char* err,
+                                      size_t errlen);
+
+/* Engine::~Engine (src/engine.h:15). */
+void brisk_cuda_destroy(brisk_cuda_session* session);
+
+/* Engine::eval (all_logits == 0) and Engine::eval_all (all_logits != 0) (src/engine.h:17-26,
+ * src/model.cpp:704-727). Appends n tokens at the current position. *logits then points at
+ * vocab floats (last token) or n*vocab floats (row i predicts the token after tokens[i]) in
+ * pinned host memory owned by the session, valid until its next call. Errors, raised before any
+ * work like the reference: n == 0 ("no tokens to evaluate"), all_logits with n > 64
+ * ("eval_all takes 1 to 64 tokens"), an id outside [0, vocab) ("token id out of range"),
+ * n > max_context - position ("context length exceeded"). Returns 0 on success. */
+int brisk_cuda_eval(brisk_cuda_session* session, const int32_t* tokens, uint64_t n, int all_logits, const float** logits);
+
+/* Engine::rollback (src/engine.h:29, src/model.cpp:735-751): O(1), only moves the cursor;
+ * position > current position fails with "cannot roll forward". */
+int brisk_cuda_rollback(brisk_cuda_session* session, uint64_t position);
+
+/* Engine::position (src/engine.h:31). */
+uint64_t brisk_cuda_position(const brisk_cuda_session* session);
+
+uint32_t brisk_cuda_vocab_size(const brisk_cuda_session* session);
+uint64_t brisk_cuda_max_context(const brisk_cuda_session* session);
+
+/* Message of the session's most recent failure ("cuda: ..."), which the C++ shim rethrows as
+ * std::runtime_error like the reference backends do (src/model.cpp:18, src/metal/metal_session.mm:27). */
+const char* brisk_cuda_last_error(const brisk_cuda_session* session);
+
+/* The greedy loop of cmd_generate (src/main.cpp:288-299) without its per-token host round trip:
+ * evaluates `first_token`, picks the arg-max on the device (lowest id on ties, as
+ * Sampler::sample does for temperature <= 0, src/sampler.cpp:11-13), feeds it back, `steps` times.
+ * out_tokens[i] is the token chosen after step i; out_logits, if not NULL, receives the
+ * [steps][vocab] logits the choices were made from. The session advances by `steps` positions. */
+int brisk_cuda_generate_greedy(brisk_cuda_session* session, int32_t first_token, uint64_t steps, int32_t* out_tokens,
+                               float* out_logits);
+
+int brisk_cuda_get_stats(const brisk_cuda_session* session, brisk_cuda_stats* out);
+
+/* Test hook, the counterpart of metal_matmul (src/metal/metal_session.h:39-47): out[t*rows + r] =
+ * row r of w (file layout, `type`) times activation row t of x ([n][cols] f32), computed the way
+ * Session::multiply does (src/model.cpp:551-653): activations quantised per row to Q8_0 (Q4_0,
+ * Q8_0) or Q8_K (Q4_K, Q6_K, TQ2_0), integer block dots, f32 scaling; F16/F32 weights use raw f32
+ * activations. All pointers are host pointers. */
+int brisk_cuda_matmul(int32_t type, const void* w, uint64_t rows, uint64_t cols, const float* x, uint64_t n, float* out,
+                      char* err, size_t errlen);
+
+/* Bench hook, the counterpart of metal_matmul_seconds (src/metal/metal_session.h:49-59): uploads
+ * `copies` repacked copies of w (so the working set can exceed L2), runs `iterations` multiplies
+ * rotating over them and returns the mean device seconds per multiply in *seconds. */
+int brisk_cuda_matmul_seconds(int32_t type, const void* w, uint64_t rows, uint64_t cols, uint64_t n, uint32_t copies,
+                              uint32_t iterations, double* seconds, char* err, size_t errlen);
+
+/* Tensor parallelism (no counterpart in the reference, which is single-process): rank 0 calls this
+ * and hands the 128 bytes to every rank's brisk_cuda_options.tp_unique_id. */
+int brisk_cuda_tp_unique_id(void* out128, char* err, size_t errlen);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* BRISK_CUDA_H */
