@@ -1,0 +1,340 @@
+#!/usr/bin/env python
+"""Token-loop benchmark: batch-1 decode tok/s (headline) and prefill tok/s on a seeded synthetic model.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config NAME]
+
+One step = one pass of the workload: roll the sequence back to 0, evaluate the prompt (prefill), then decode
+greedily. `value` is decode tokens/s with everything resident in HBM (on-device greedy loop, CUDA-event time);
+`e2e` is the same metric through the Engine-shaped public call with host buffers: token ids copied in and all
+logits copied out every step, arg-max on the host - the loop brisk-llm's `generate` runs. With N > 1 every rank
+runs an independent replica (batch-1 decode of one sequence has nothing to shard for this configuration).
+`--impl reference` times the reference's own CPU engine on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from brisk_llm_b200 import formats as F, synth  # noqa: E402
+
+METRIC = "decode_tokens_per_s_batch1"
+UNIT = "tok/s"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=5)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--config", default="qwen3-0.6b-q4_0", choices=sorted(synth.PRESETS))
+    p.add_argument("--prompt", type=int, default=0)
+    p.add_argument("--decode", type=int, default=0)
+    p.add_argument("--layers", type=int, default=0, help="override the layer count (debugging; the reported number is then not the configured workload)")
+    p.add_argument("--no-cpu-baseline", action="store_true")
+    return p.parse_args()
+
+
+WORKLOADS = {  # prompt tokens, decode steps, context
+    "qwen3-0.6b-q4_0": (512, 128, 2048),
+    "llama-3.2-1b-q4_k_m": (1024, 256, 4096),
+    "bitnet-2b4t-tq2_0": (512, 256, 4096),
+    "mistral-7b-q4_0": (8192, 512, 8704),
+}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def workload_for(args):
+    spec = synth.PRESETS[args.config]
+    prompt, decode, ctx = WORKLOADS[args.config]
+    prompt = args.prompt or prompt
+    decode = args.decode or decode
+    if args.layers:
+        from dataclasses import replace
+        spec = replace(spec, layers=args.layers)
+    from dataclasses import replace
+    spec = replace(spec, context=ctx)
+    return spec, prompt, decode
+
+
+def describe(spec, prompt, decode, extra=None):
+    cfg = {"workload": f"{spec.name}: {spec.layers} layers, hidden {spec.hidden}, {spec.heads}/{spec.kv_heads} heads x {spec.head_dim}, "
+                       f"ffn {spec.ffn}, vocab {spec.vocab}, {F.NAMES[spec.fmt]}; {prompt}-token random prompt + {decode} greedy decode "
+                       f"steps, batch 1, f16 K/V cache, ctx {spec.context}",
+           "l2": "every token streams all weight planes, larger than the 126 MB L2, so timed iterations do not reuse cached inputs",
+           "weights": "seeded synthetic, f32 N(0,0.02) quantised (no checkpoint available)"}
+    if extra:
+        cfg.update(extra)
+    return cfg
+
+
+# ---- reference / CPU arm ------------------------------------------------------------------------------------------
+
+def cpu_engine(model, spec, threads):
+    """The reference CPU engine (oracle/_ref, built from a reference checkout) when it is present, else the C port."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import helpers as H
+    if H.have_ref():
+        from brisk_llm_b200 import gguf_io
+        path = os.path.join(tempfile.gettempdir(), f"brisk_bench_{spec.name}_{spec.layers}_{os.getpid()}.gguf")
+        gguf_io.write_gguf(model, path)
+        r = H.ref()
+        handle = r.ref_session_create(path.encode(), threads, spec.context)
+        if not handle:
+            raise RuntimeError(r.ref_last_error().decode())
+
+        def run(prompt_ids, steps):
+            r.ref_session_rollback(handle, 0)
+            out = np.empty(steps, np.int32)
+            tp, td = C.c_double(), C.c_double()
+            rc = r.ref_session_generate_greedy(handle, H.iptr(prompt_ids), len(prompt_ids), steps, H.iptr(out), None, C.byref(tp), C.byref(td))
+            if rc != 0:
+                raise RuntimeError(r.ref_last_error().decode())
+            return tp.value, td.value
+
+        def close():
+            r.ref_session_destroy(handle)
+            os.remove(path)
+
+        return "reference", r.ref_kernel_set_name().decode(), run, close
+    os.environ["BRISK_ORACLE_THREADS"] = str(threads)
+    sess = H.OracleSession(model, spec.context)
+
+    def run(prompt_ids, steps):
+        sess.rollback(0)
+        t0 = time.perf_counter()
+        logits = sess.eval(prompt_ids)
+        t1 = time.perf_counter()
+        for _ in range(steps - 1):
+            logits = sess.eval([int(np.argmax(logits))])
+        return t1 - t0, time.perf_counter() - t1
+
+    return "port", "scalar C port", run, sess.close
+
+
+def cpu_sample_sizes(spec):
+    # about 10-30 s of CPU work on a few dozen cores: cost grows with the weight bytes per token
+    scale = max(1.0, spec.layers * (spec.hidden * (spec.q_dim * 2 + spec.kv_dim * 2 + 3 * spec.ffn)) / 4.4e8)
+    return max(8, int(128 / scale)), max(4, int(32 / scale))
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    spec, prompt, decode = workload_for(args)
+    model = synth.generate(spec, seed=0)
+    threads = os.cpu_count() or 1
+    sp, sd = cpu_sample_sizes(spec)
+    kind, kernels, run, close = cpu_engine(model, spec, threads)
+    ids = synth.random_tokens(spec, sp, seed=1)
+    for _ in range(min(args.warmup, 1)):
+        run(ids, sd)
+    tp = td = 0.0
+    for _ in range(args.steps):
+        a, b = run(ids, sd)
+        tp += a
+        td += b
+    close()
+    value = args.steps * (sd - 1) / td if td > 0 else 0.0
+    sample = f"{sp}-token prompt + {sd} greedy steps of the same model per step ({kernels} kernels)"
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": min(args.warmup, 1), "ms_per_step": 1e3 * (tp + td) / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int8 dot products, f32 accumulate", "data": "synthetic",
+            "config": describe(spec, prompt, decode, {"sample": sample}), "prefill_tokens_per_s": args.steps * sp / tp,
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# ---- our arm ------------------------------------------------------------------------------------------------------
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    import torch
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from brisk_llm_b200 import engine
+
+    spec, prompt, decode = workload_for(args)
+    model = synth.generate(spec, seed=0)
+    ids = synth.random_tokens(spec, prompt, seed=1)
+    sess = engine.CudaSession(model, max_context=spec.context, device=local)
+    weight_bytes = model.weight_bytes()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def device_step():
+        sess.rollback(0)
+        logits = sess.eval(ids)
+        st = sess.stats()
+        pre_ms, launches = st["device_ms"], st["kernel_launches"]
+        first = int(np.argmax(logits))
+        sess.generate_greedy(first, decode)
+        st = sess.stats()
+        return pre_ms, st["device_ms"], launches + st["kernel_launches"]
+
+    def e2e_step():
+        sess.rollback(0)
+        h2d = d2h = 0
+        t0 = time.perf_counter()
+        logits = sess.eval(ids)
+        st = sess.stats()
+        h2d, d2h = h2d + st["h2d_bytes"], d2h + st["d2h_bytes"]
+        t1 = time.perf_counter()
+        for _ in range(decode):
+            logits = sess.eval([int(np.argmax(logits))])
+            st = sess.stats()
+            h2d, d2h = h2d + st["h2d_bytes"], d2h + st["d2h_bytes"]
+        t2 = time.perf_counter()
+        return t1 - t0, t2 - t1, h2d, d2h
+
+    for _ in range(max(args.warmup, 3)):
+        device_step()
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    pre_ms = dec_ms = 0.0
+    launches = 0
+    t_wall = time.perf_counter()
+    for _ in range(args.steps):
+        a, b, c = device_step()
+        pre_ms, dec_ms, launches = pre_ms + a, dec_ms + b, launches + c
+    barrier()
+    t_wall = time.perf_counter() - t_wall
+    clocks = sampler.stop()
+
+    e2e_step()
+    barrier()
+    e_pre = e_dec = 0.0
+    h2d = d2h = 0
+    for _ in range(args.steps):
+        a, b, c, d = e2e_step()
+        e_pre, e_dec, h2d, d2h = e_pre + a, e_dec + b, c, d
+    barrier()
+
+    def max_over_ranks(v):
+        if dist is None:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=f"cuda:{local}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    pre_ms, dec_ms, e_pre, e_dec = (max_over_ranks(v) for v in (pre_ms, dec_ms, e_pre, e_dec))
+    if rank == 0:
+        peak, peak_kind = peaks()
+        tokens = args.steps * decode
+        value = world * tokens / (dec_ms * 1e-3)
+        achieved = weight_bytes * tokens / (dec_ms * 1e-3) / 1e9
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+                "ms_per_step": (pre_ms + dec_ms) / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "int8 dot products, f32 accumulate (f16 K/V cache)", "data": "synthetic",
+                "config": describe(spec, prompt, decode, {"parallelism": "replicas only" if world > 1 else "single GPU"}),
+                "prefill_tokens_per_s": world * args.steps * prompt / (pre_ms * 1e-3),
+                "decode_us_per_token": 1e3 * dec_ms / tokens,
+                "wall_s_timed_region": t_wall,
+                "e2e": {"value": world * tokens / e_dec, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                        "prefill_tokens_per_s": world * args.steps * prompt / e_pre},
+                "gpu_launches": launches,
+                "clocks": clocks,
+                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                             "traffic": None, "peak_kind": f"of {peak_kind}", "kernel": "decode step (all kernels of one token)",
+                             "algorithmic_bytes_per_token": weight_bytes}}
+        if world == 1 and not args.no_cpu_baseline:
+            try:
+                threads = os.cpu_count() or 1
+                sp, sd = cpu_sample_sizes(spec)
+                kind, kernels, run, close = cpu_engine(model, spec, threads)
+                tp, td = run(synth.random_tokens(spec, sp, seed=1), sd)
+                close()
+                line["cpu_baseline"] = {"value": (sd - 1) / td, "unit": UNIT, "cores": threads, "kind": kind,
+                                        "sample": f"{sp}-token prompt + {sd} greedy steps of the same model ({kernels} kernels)",
+                                        "prefill_tokens_per_s": sp / tp}
+            except Exception as e:  # the baseline is reported, never required
+                line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": f"failed: {e}"}
+        print(json.dumps(line), flush=True)
+    sess.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,104 @@
+// Host-callable launchers of the token-loop kernels. Everything runs on the stream given;
+// nothing here allocates or synchronises.
+#pragma once
+
+#include "common.cuh"
+
+namespace bk {
+
+// ---- load-time repack (repack.cu) -------------------------------------------------------------
+// Bytes of each plane of a rows x cols matrix of `type` in the device layout (see DevMatrix).
+struct PlaneSizes {
+    size_t qa = 0, qb = 0, qc = 0, sc = 0, d = 0;
+    size_t total() const { return qa + qb + qc + sc + d; }
+};
+PlaneSizes plane_sizes(int type, uint32_t rows, uint32_t cols);
+// Carves the planes of `m` out of `base` (256-byte aligned sub-allocations) and fills m's fields.
+void bind_planes(DevMatrix& m, int type, uint32_t rows, uint32_t cols, uint8_t* base);
+// raw_dev: the matrix in file layout, already in device memory. Writes the planes of `m`.
+void launch_repack(const DevMatrix& m, const uint8_t* raw_dev, cudaStream_t s);
+
+// ---- activations (activations.cu) -------------------------------------------------------------
+struct DevActMut {
+    float* f32 = nullptr;
+    int8_t* q0 = nullptr;
+    float* d0 = nullptr;
+    int32_t* s0 = nullptr;
+    int8_t* qk = nullptr;
+    float* dk = nullptr;
+    int16_t* bs = nullptr;
+    uint32_t cols = 0;
+    DevAct view() const { return DevAct{f32, q0, d0, s0, qk, dk, bs, cols}; }
+};
+// For each of n rows of x[n][ldx]: optional RMS norm (weight != nullptr: y = x * rsqrt(mean(x^2)+eps) * weight;
+// the per-row scale uses `norm_cols` = cols values), then the f32 row (if act.f32), its Q8_0 planes (want0) and
+// its Q8_K planes (wantk). x may alias act.f32.
+void launch_norm_quant(const float* x, uint32_t ldx, const float* weight, float eps, uint32_t n, uint32_t cols,
+                       const DevActMut& act, bool want0, bool wantk, cudaStream_t s);
+
+// ---- streaming multiply: 1..8 token rows against whole weight rows (matvec.cu) ----------------
+enum Epilogue : int {
+    EPI_STORE = 0,     // out[t*ldo + r]  = dot
+    EPI_ADD = 1,       // out[t*ldo + r] += dot            (residual stream)
+    EPI_SILU_MUL = 2,  // pair (gate, up): out = silu(gate) * up
+    EPI_RELU2_MUL = 3  // pair (gate, up): out = max(gate,0)^2 * up
+};
+struct MatTarget {
+    DevMatrix m;
+    float* out = nullptr;
+    uint32_t ldo = 0;
+};
+// All targets share `act` (same cols) and the same type. For the pair epilogues pass exactly {gate, up}; the result
+// goes to targets[0].out. n may exceed 8: the launcher walks token tiles.
+void launch_matvec(const MatTarget* targets, int count, const DevAct& act, uint32_t n, Epilogue epi, cudaStream_t s);
+
+// ---- batched multiply on the int8 tensor path (gemm.cu) ----------------------------------------
+// Same contract as launch_matvec for n >= 16 tokens; returns false when this type/shape has no tensor kernel
+// (the caller then uses launch_matvec).
+bool launch_gemm(const MatTarget* targets, int count, const DevAct& act, uint32_t n, Epilogue epi, cudaStream_t s);
+
+// ---- per-token vector work (misc.cu) -----------------------------------------------------------
+// hidden[t][:] = dequantised row tokens[t] of the embedding matrix (Session::eval_batch's embedding_row).
+void launch_embed(const DevMatrix& embd, const int32_t* tokens_dev, uint32_t n, float* hidden, cudaStream_t s);
+
+struct RopeArgs {
+    float* q;            // [n][heads*dim] in place
+    float* k;            // [n][kv*dim]   (normed + rotated, then stored to the cache)
+    const float* v;      // [n][kv*dim]
+    const float* q_norm; // [dim] or nullptr
+    const float* k_norm;
+    const float* rope;   // [max_context][dim]: cos, sin per pair, indexed by absolute position
+    __half* k_cache;     // [kv][max_context][dim]
+    __half* v_cache;
+    const uint32_t* position; // device scalar: position of token 0 of this batch
+    uint32_t n, heads, kv_heads, dim, max_context;
+    float eps;
+    int neox;
+};
+void launch_qk_norm_rope_store(const RopeArgs& a, cudaStream_t s);
+
+struct AttnArgs {
+    const float* q;        // [n][heads*dim]
+    const __half* k_cache; // [kv][max_context][dim]
+    const __half* v_cache;
+    float* out;            // [n][heads*dim]
+    float* partial;        // scratch: [n][heads][splits][dim + 2]
+    const uint32_t* position;
+    uint32_t n, heads, kv_heads, dim, max_context;
+    uint32_t max_visible;  // host-side upper bound of position + n (sizes the grid)
+    float scale;
+};
+uint32_t attn_split_len();
+size_t attn_partial_floats(uint32_t n, uint32_t heads, uint32_t dim, uint32_t max_context);
+void launch_attention(const AttnArgs& a, cudaStream_t s);
+
+// First maximum of each of n rows of logits[n][vocab] (lowest index on ties) -> out_token[n].
+// If next_token/position are given (single row), also feeds the decode loop: *next_token = argmax, *position += 1,
+// and appends the token to history[*history_len++].
+void launch_argmax(const float* logits, uint32_t vocab, uint32_t n, int32_t* out_token, float* scratch_val,
+                   int32_t* scratch_idx, cudaStream_t s);
+size_t argmax_scratch_elems(uint32_t vocab);
+void launch_advance(int32_t* token_slot, const int32_t* chosen, uint32_t* position, int32_t* history, uint32_t* history_len,
+                    cudaStream_t s);
+
+}  // namespace bk

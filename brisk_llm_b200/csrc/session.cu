@@ -1,0 +1,559 @@
+// The CUDA session behind include/brisk_cuda.h: weights repacked once into HBM, an f16 K/V cache,
+// scratch for one batch, the forward pass of Session::eval_batch (src/model.cpp:867-1212) as a
+// sequence of kernel launches on one stream, and a captured CUDA graph for the single-token step.
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../../include/brisk_cuda.h"
+#include "kernels.h"
+
+namespace bk {
+namespace {
+
+constexpr uint32_t kMaxBatch = 512;   // tokens per prefill pass (the reference: 256 on the CPU, 512 on Metal)
+constexpr uint32_t kMaxScored = 64;   // Engine::kMaxScoredTokens, src/engine.h:32
+
+struct DevBuffer {
+    void* p = nullptr;
+    size_t bytes = 0;
+    DevBuffer() = default;
+    DevBuffer(const DevBuffer&) = delete;
+    DevBuffer& operator=(const DevBuffer&) = delete;
+    ~DevBuffer() { if (p) cudaFree(p); }
+    void alloc(size_t n) {
+        bytes = n;
+        BK_CUDA(cudaMalloc(&p, n ? n : 16));
+    }
+    template <class T> T* as() const { return static_cast<T*>(p); }
+};
+
+struct Layer {
+    DevMatrix q, k, v, o, gate, up, down;
+    const float *attn_norm = nullptr, *q_norm = nullptr, *k_norm = nullptr, *attn_sub_norm = nullptr, *ffn_norm = nullptr, *ffn_sub_norm = nullptr;
+    __half *k_cache = nullptr, *v_cache = nullptr;
+};
+
+bool type_supported(int t) { return t == T_F32 || t == T_F16 || t == T_Q4_0 || t == T_Q8_0 || t == T_Q4_K || t == T_Q6_K || t == T_TQ2_0; }
+
+}  // namespace
+
+struct Session {
+    // configuration
+    uint32_t vocab = 0, hidden = 0, n_layers = 0, heads = 0, kv_heads = 0, head_dim = 0, ffn = 0;
+    uint32_t q_dim = 0, kv_dim = 0;
+    uint64_t max_context = 0;
+    float eps = 0, rope_base = 0;
+    int arch = 0, neox = 1, device = 0;
+    uint32_t flags = 0;
+
+    // weights
+    std::vector<std::unique_ptr<DevBuffer>> weight_buffers;
+    std::vector<Layer> layers;
+    DevMatrix embd, head;
+    const float* output_norm = nullptr;
+    uint64_t weight_bytes = 0, kv_bytes = 0;
+
+    // state and scratch
+    DevBuffer kv, rope, tokens_dev, scalars, hidden_b, q_b, k_b, v_b, attended_b, ffn_b, logits_b, actf, actq0, actd0, acts0, actqk,
+        actdk, actbs, partial, am_val, am_idx, history, logit_history;
+    DevActMut act;
+    float* logits_host = nullptr;     // pinned [64][vocab]
+    int32_t* tokens_host = nullptr;   // pinned [kMaxBatch + 4]
+    uint64_t position = 0;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    cudaGraphExec_t step_graph = nullptr;
+    uint64_t step_graph_nodes = 0;
+    uint64_t launches = 0;  // kernels launched by the current call
+    brisk_cuda_stats stats{};
+    std::string error;
+
+    // device scalars: [0] position (u32), [1] chosen token, [2] history length
+    uint32_t* d_position() const { return scalars.as<uint32_t>(); }
+    int32_t* d_chosen() const { return scalars.as<int32_t>() + 1; }
+    uint32_t* d_history_len() const { return scalars.as<uint32_t>() + 2; }
+
+    ~Session() {
+        if (step_graph) cudaGraphExecDestroy(step_graph);
+        if (ev0) cudaEventDestroy(ev0);
+        if (ev1) cudaEventDestroy(ev1);
+        if (stream) cudaStreamDestroy(stream);
+        if (logits_host) cudaFreeHost(logits_host);
+        if (tokens_host) cudaFreeHost(tokens_host);
+    }
+
+    // ---- load ------------------------------------------------------------------------------------------
+    DevMatrix upload_matrix(const brisk_cuda_matrix& m, const char* what, uint64_t rows, uint64_t cols, DevBuffer& staging) {
+        if (m.data == nullptr) throw CudaError(std::string("cuda: missing tensor ") + what);
+        if (!type_supported(m.type)) throw CudaError(std::string("cuda: tensor ") + what + " has an unsupported type " + std::to_string(m.type));
+        if (m.rows != rows || m.cols != cols) throw CudaError(std::string("cuda: tensor ") + what + " has an unexpected shape");
+        const uint32_t be = block_elems(m.type);
+        if (cols % be != 0 || cols % 32 != 0) throw CudaError(std::string("cuda: tensor ") + what + " row length is not a multiple of its block size");
+        const uint64_t expect = rows * (cols / be) * block_bytes(m.type);
+        if (m.bytes != expect) throw CudaError(std::string("cuda: tensor ") + what + " has unexpected quantised data");
+        auto buf = std::make_unique<DevBuffer>();
+        buf->alloc(plane_sizes(m.type, uint32_t(rows), uint32_t(cols)).total());
+        DevMatrix d;
+        bind_planes(d, m.type, uint32_t(rows), uint32_t(cols), buf->as<uint8_t>());
+        if (staging.bytes < expect) {
+            BK_CUDA(cudaStreamSynchronize(stream));
+            if (staging.p) cudaFree(staging.p);
+            staging.p = nullptr;
+            staging.alloc(expect);
+        }
+        BK_CUDA(cudaStreamSynchronize(stream));  // the previous repack still reads the staging buffer
+        BK_CUDA(cudaMemcpyAsync(staging.p, m.data, expect, cudaMemcpyHostToDevice, stream));
+        launch_repack(d, staging.as<uint8_t>(), stream);
+        weight_bytes += expect;
+        stats.h2d_bytes += expect;
+        weight_buffers.push_back(std::move(buf));
+        return d;
+    }
+
+    const float* upload_vector(const float* v, uint64_t n, const char* what, bool required) {
+        if (v == nullptr) {
+            if (required) throw CudaError(std::string("cuda: missing tensor ") + what);
+            return nullptr;
+        }
+        auto buf = std::make_unique<DevBuffer>();
+        buf->alloc(n * sizeof(float));
+        BK_CUDA(cudaMemcpyAsync(buf->p, v, n * sizeof(float), cudaMemcpyHostToDevice, stream));
+        weight_bytes += n * sizeof(float);
+        const float* out = buf->as<float>();
+        weight_buffers.push_back(std::move(buf));
+        return out;
+    }
+
+    void load(const brisk_cuda_model& m, const brisk_cuda_options& opt) {
+        if (m.abi_version != BRISK_CUDA_ABI_VERSION) throw CudaError("cuda: model description has a different ABI version");
+        if (opt.tp_size > 1) throw CudaError("cuda: tensor parallelism is not available in this build");
+        vocab = m.vocab_size; hidden = m.hidden; n_layers = m.layer_count; heads = m.head_count; kv_heads = m.kv_head_count;
+        head_dim = m.head_dim; ffn = m.ffn; eps = m.rms_epsilon; rope_base = m.rope_base; arch = m.arch; neox = m.rope_neox;
+        flags = opt.flags;
+        if (!vocab || !hidden || !n_layers || !heads || !kv_heads || !ffn || !m.context_length) throw CudaError("cuda: a model dimension is zero");
+        if (heads % kv_heads != 0) throw CudaError("cuda: head_count is not a multiple of head_count_kv");
+        if (heads / kv_heads > 16) throw CudaError("cuda: more than 16 query heads per key/value head is not supported");
+        if (head_dim == 0 || head_dim % 32 != 0 || head_dim > 128) throw CudaError("cuda: head size must be a multiple of 32 up to 128");
+        if (m.rope_factor_count != 0 && m.rope_factor_count != head_dim / 2) throw CudaError("cuda: rope factor count must be head_dim / 2");
+        q_dim = heads * head_dim;
+        kv_dim = kv_heads * head_dim;
+        max_context = opt.max_context == 0 ? m.context_length : std::min<uint64_t>(opt.max_context, m.context_length);
+
+        BK_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+        BK_CUDA(cudaEventCreate(&ev0));
+        BK_CUDA(cudaEventCreate(&ev1));
+
+        DevBuffer staging;
+        embd = upload_matrix(m.token_embd, "token_embd.weight", vocab, hidden, staging);
+        head = m.output.data != nullptr ? upload_matrix(m.output, "output.weight", vocab, hidden, staging) : embd;
+        output_norm = upload_vector(m.output_norm, hidden, "output_norm.weight", true);
+        layers.resize(n_layers);
+        for (uint32_t l = 0; l < n_layers; ++l) {
+            const brisk_cuda_layer& s = m.layers[l];
+            Layer& d = layers[l];
+            d.attn_norm = upload_vector(s.attn_norm, hidden, "attn_norm.weight", true);
+            d.q = upload_matrix(s.q, "attn_q.weight", q_dim, hidden, staging);
+            d.k = upload_matrix(s.k, "attn_k.weight", kv_dim, hidden, staging);
+            d.v = upload_matrix(s.v, "attn_v.weight", kv_dim, hidden, staging);
+            d.q_norm = upload_vector(s.q_norm, head_dim, "attn_q_norm.weight", false);
+            d.k_norm = upload_vector(s.k_norm, head_dim, "attn_k_norm.weight", false);
+            d.attn_sub_norm = upload_vector(s.attn_sub_norm, q_dim, "attn_sub_norm.weight", false);
+            d.o = upload_matrix(s.o, "attn_output.weight", hidden, q_dim, staging);
+            d.ffn_norm = upload_vector(s.ffn_norm, hidden, "ffn_norm.weight", true);
+            d.gate = upload_matrix(s.gate, "ffn_gate.weight", ffn, hidden, staging);
+            d.up = upload_matrix(s.up, "ffn_up.weight", ffn, hidden, staging);
+            if (d.gate.type != d.up.type) throw CudaError("cuda: ffn_gate and ffn_up must share one type");
+            d.ffn_sub_norm = upload_vector(s.ffn_sub_norm, ffn, "ffn_sub_norm.weight", false);
+            d.down = upload_matrix(s.down, "ffn_down.weight", hidden, ffn, staging);
+        }
+        BK_CUDA(cudaStreamSynchronize(stream));
+        if (m.output.data == nullptr) {
+            // A tied head is streamed once per token as the head; the embedding lookup reads one row of it.
+        }
+
+        // K/V cache: per layer [kv head][max_context][head_dim] f16, K then V (src/model.cpp:982-991).
+        const size_t per = size_t(kv_heads) * max_context * head_dim;
+        kv_bytes = size_t(n_layers) * 2 * per * sizeof(__half);
+        kv.alloc(kv_bytes);
+        BK_CUDA(cudaMemsetAsync(kv.p, 0, kv_bytes, stream));
+        for (uint32_t l = 0; l < n_layers; ++l) {
+            layers[l].k_cache = kv.as<__half>() + size_t(l) * 2 * per;
+            layers[l].v_cache = layers[l].k_cache + per;
+        }
+
+        // RoPE table for every position, built like the reference builds it per batch (src/model.cpp:880-892):
+        // theta starts at the position and is multiplied by base^(-2/dim) per pair, in f32, with the host's libm.
+        {
+            std::vector<float> table(size_t(max_context) * head_dim);
+            const float theta_scale = std::pow(rope_base, -2.0f / static_cast<float>(head_dim));
+            for (uint64_t p = 0; p < max_context; ++p) {
+                float theta = static_cast<float>(p) * 1.0f;
+                float* r = table.data() + p * head_dim;
+                for (uint32_t i = 0; i < head_dim / 2; ++i) {
+                    const float angle = m.rope_factor_count != 0 ? theta / m.rope_factors[i] : theta;
+                    r[2 * i] = std::cos(angle) * 1.0f;
+                    r[2 * i + 1] = std::sin(angle) * 1.0f;
+                    theta *= theta_scale;
+                }
+            }
+            rope.alloc(table.size() * sizeof(float));
+            BK_CUDA(cudaMemcpy(rope.p, table.data(), table.size() * sizeof(float), cudaMemcpyHostToDevice));
+        }
+
+        const uint32_t widest = std::max(std::max(hidden, q_dim), ffn);
+        tokens_dev.alloc((kMaxBatch + 4) * sizeof(int32_t));
+        scalars.alloc(64);
+        BK_CUDA(cudaMemsetAsync(scalars.p, 0, 64, stream));
+        hidden_b.alloc(size_t(kMaxBatch) * hidden * 4);
+        q_b.alloc(size_t(kMaxBatch) * q_dim * 4);
+        k_b.alloc(size_t(kMaxBatch) * kv_dim * 4);
+        v_b.alloc(size_t(kMaxBatch) * kv_dim * 4);
+        attended_b.alloc(size_t(kMaxBatch) * q_dim * 4);
+        ffn_b.alloc(size_t(kMaxBatch) * ffn * 4);
+        logits_b.alloc(size_t(kMaxScored) * vocab * 4);
+        actf.alloc(size_t(kMaxBatch) * widest * 4);
+        actq0.alloc(size_t(kMaxBatch) * widest);
+        actd0.alloc(size_t(kMaxBatch) * (widest / 32) * 4);
+        acts0.alloc(size_t(kMaxBatch) * (widest / 32) * 4);
+        actqk.alloc(size_t(kMaxBatch) * widest);
+        actdk.alloc(size_t(kMaxBatch) * (widest / 256 + 1) * 4);
+        actbs.alloc(size_t(kMaxBatch) * (widest / 16) * 2);
+        act.f32 = actf.as<float>(); act.q0 = actq0.as<int8_t>(); act.d0 = actd0.as<float>(); act.s0 = acts0.as<int32_t>();
+        act.qk = actqk.as<int8_t>(); act.dk = actdk.as<float>(); act.bs = actbs.as<int16_t>();
+        const size_t pf = std::max(attn_partial_floats(kMaxBatch, heads, head_dim, uint32_t(max_context)),
+                                   attn_partial_floats(kMaxSmallBatch, heads, head_dim, uint32_t(max_context)));
+        partial.alloc(pf * 4);
+        am_val.alloc(argmax_scratch_elems(vocab) * 4);
+        am_idx.alloc(argmax_scratch_elems(vocab) * 4);
+        history.alloc((max_context + 1) * sizeof(int32_t));
+        BK_CUDA(cudaMallocHost(&logits_host, size_t(kMaxScored) * vocab * sizeof(float)));
+        BK_CUDA(cudaMallocHost(&tokens_host, (kMaxBatch + 4) * sizeof(int32_t)));
+        BK_CUDA(cudaStreamSynchronize(stream));
+        stats.weight_bytes = weight_bytes;
+        stats.kv_bytes = kv_bytes;
+    }
+
+    // ---- forward ---------------------------------------------------------------------------------------
+    struct Needs { bool q0 = false, qk = false, f32 = false; };
+    static void need(Needs& n, int type) {
+        if (type == T_F16 || type == T_F32) n.f32 = true;
+        else if (takes_q8_k(type)) n.qk = true;
+        else n.q0 = true;
+    }
+
+    // RMS norm (weight may be null: no norm) then the quantisations the consuming matrices take.
+    DevAct prepare(const float* x, uint32_t ldx, const float* weight, uint32_t n, uint32_t cols, const Needs& nd) {
+        DevActMut a = act;
+        a.cols = cols;
+        if (!nd.f32) a.f32 = nullptr;
+        launch_norm_quant(x, ldx, weight, eps, n, cols, a, nd.q0, nd.qk, stream);
+        ++launches;
+        a.f32 = act.f32;
+        return a.view();
+    }
+
+    void multiply(std::vector<MatTarget> targets, const DevAct& a, uint32_t n, Epilogue epi) {
+        const bool pair = epi == EPI_SILU_MUL || epi == EPI_RELU2_MUL;
+        if (pair) {
+            if (!(n >= 16 && launch_gemm(targets.data(), int(targets.size()), a, n, epi, stream))) {
+                launch_matvec(targets.data(), int(targets.size()), a, n, epi, stream);
+            }
+            launches += (n + kMaxSmallBatch - 1) / kMaxSmallBatch;
+            return;
+        }
+        // Targets of one type share a launch (q and k in Q4_K, v in Q6_K -> two launches).
+        while (!targets.empty()) {
+            std::vector<MatTarget> same, rest;
+            for (const MatTarget& t : targets) (t.m.type == targets[0].m.type ? same : rest).push_back(t);
+            if (!(n >= 16 && launch_gemm(same.data(), int(same.size()), a, n, epi, stream))) {
+                launch_matvec(same.data(), int(same.size()), a, n, epi, stream);
+                launches += (n + kMaxSmallBatch - 1) / kMaxSmallBatch;
+            } else {
+                ++launches;
+            }
+            targets.swap(rest);
+        }
+    }
+
+    // n tokens already in tokens_dev, their first position in d_position(). max_visible bounds position + n.
+    void forward(uint32_t n, bool all_logits, uint32_t max_visible) {
+        float* hid = hidden_b.as<float>();
+        launch_embed(embd, tokens_dev.as<int32_t>(), n, hid, stream);
+        ++launches;
+        const float attn_scale = 1.0f / std::sqrt(static_cast<float>(head_dim));
+        for (uint32_t l = 0; l < n_layers; ++l) {
+            const Layer& L = layers[l];
+            Needs nd;
+            need(nd, L.q.type); need(nd, L.k.type); need(nd, L.v.type);
+            DevAct a = prepare(hid, hidden, L.attn_norm, n, hidden, nd);
+            multiply({{L.q, q_b.as<float>(), q_dim}, {L.k, k_b.as<float>(), kv_dim}, {L.v, v_b.as<float>(), kv_dim}}, a, n, EPI_STORE);
+
+            RopeArgs r{};
+            r.q = q_b.as<float>(); r.k = k_b.as<float>(); r.v = v_b.as<float>();
+            r.q_norm = L.q_norm; r.k_norm = L.k_norm; r.rope = rope.as<float>();
+            r.k_cache = L.k_cache; r.v_cache = L.v_cache; r.position = d_position();
+            r.n = n; r.heads = heads; r.kv_heads = kv_heads; r.dim = head_dim; r.max_context = uint32_t(max_context);
+            r.eps = eps; r.neox = neox;
+            launch_qk_norm_rope_store(r, stream);
+            ++launches;
+
+            AttnArgs at{};
+            at.q = q_b.as<float>(); at.k_cache = L.k_cache; at.v_cache = L.v_cache; at.out = attended_b.as<float>();
+            at.partial = partial.as<float>(); at.position = d_position();
+            at.n = n; at.heads = heads; at.kv_heads = kv_heads; at.dim = head_dim; at.max_context = uint32_t(max_context);
+            at.max_visible = max_visible; at.scale = attn_scale;
+            launch_attention(at, stream);
+            launches += 2;
+
+            Needs no;
+            need(no, L.o.type);
+            a = prepare(attended_b.as<float>(), q_dim, L.attn_sub_norm, n, q_dim, no);
+            multiply({{L.o, hid, hidden}}, a, n, EPI_ADD);
+
+            Needs nf;
+            need(nf, L.gate.type);
+            a = prepare(hid, hidden, L.ffn_norm, n, hidden, nf);
+            multiply({{L.gate, ffn_b.as<float>(), ffn}, {L.up, nullptr, ffn}}, a, n, arch == BRISK_ARCH_BITNET ? EPI_RELU2_MUL : EPI_SILU_MUL);
+
+            Needs ndn;
+            need(ndn, L.down.type);
+            a = prepare(ffn_b.as<float>(), ffn, L.ffn_sub_norm, n, ffn, ndn);
+            multiply({{L.down, hid, hidden}}, a, n, EPI_ADD);
+        }
+        Needs nh;
+        need(nh, head.type);
+        const uint32_t rows = all_logits ? n : 1;
+        DevAct a = prepare(all_logits ? hid : hid + size_t(n - 1) * hidden, hidden, output_norm, rows, hidden, nh);
+        multiply({{head, logits_b.as<float>(), vocab}}, a, rows, EPI_STORE);
+    }
+
+    void build_step_graph() {
+        if (step_graph != nullptr || (flags & BRISK_CUDA_FLAG_NO_GRAPH)) return;
+        const uint64_t before = launches;
+        cudaGraph_t graph = nullptr;
+        BK_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
+        try {
+            forward(1, false, uint32_t(max_context));
+        } catch (...) {
+            cudaStreamEndCapture(stream, &graph);
+            if (graph) cudaGraphDestroy(graph);
+            throw;
+        }
+        BK_CUDA(cudaStreamEndCapture(stream, &graph));
+        step_graph_nodes = launches - before;
+        launches = before;
+        const cudaError_t e = cudaGraphInstantiate(&step_graph, graph, 0);
+        cudaGraphDestroy(graph);
+        BK_CUDA(e);
+    }
+
+    void step_on_device() {  // one token whose id is tokens_dev[0] at *d_position()
+        if (flags & BRISK_CUDA_FLAG_NO_GRAPH) {
+            forward(1, false, uint32_t(max_context));
+        } else {
+            build_step_graph();
+            BK_CUDA(cudaGraphLaunch(step_graph, stream));
+            launches += step_graph_nodes;
+        }
+    }
+
+    void begin_call() {
+        launches = 0;
+        stats.h2d_bytes = stats.d2h_bytes = 0;
+    }
+    void end_call(float ms) {
+        stats.device_ms = ms;
+        stats.kernel_launches = launches;
+    }
+
+    void check_tokens(const int32_t* tokens, uint64_t n, bool all) {
+        if (all ? (n == 0 || n > kMaxScored) : n == 0) throw CudaError(all ? "cuda: eval_all takes 1 to 64 tokens" : "cuda: no tokens to evaluate");
+        for (uint64_t i = 0; i < n; ++i) {
+            if (tokens[i] < 0 || uint32_t(tokens[i]) >= vocab) throw CudaError("cuda: token id out of range");
+        }
+        if (n > max_context - position) throw CudaError("cuda: context length exceeded");
+    }
+
+    const float* eval(const int32_t* tokens, uint64_t n, bool all) {
+        check_tokens(tokens, n, all);
+        begin_call();
+        BK_CUDA(cudaEventRecord(ev0, stream));
+        for (uint64_t begin = 0; begin < n; begin += kMaxBatch) {
+            const uint32_t cnt = uint32_t(std::min<uint64_t>(kMaxBatch, n - begin));
+            BK_CUDA(cudaStreamSynchronize(stream));  // tokens_host is reused
+            std::memcpy(tokens_host, tokens + begin, cnt * sizeof(int32_t));
+            const uint32_t pos32 = uint32_t(position);
+            std::memcpy(tokens_host + kMaxBatch, &pos32, sizeof(pos32));
+            BK_CUDA(cudaMemcpyAsync(tokens_dev.p, tokens_host, cnt * sizeof(int32_t), cudaMemcpyHostToDevice, stream));
+            BK_CUDA(cudaMemcpyAsync(d_position(), tokens_host + kMaxBatch, sizeof(uint32_t), cudaMemcpyHostToDevice, stream));
+            stats.h2d_bytes += cnt * sizeof(int32_t) + sizeof(uint32_t);
+            const bool last = begin + cnt == n;
+            if (cnt == 1 && !all) step_on_device();
+            else forward(cnt, all, uint32_t(position + cnt));
+            (void)last;
+            position += cnt;
+        }
+        const size_t out_bytes = size_t(all ? n : 1) * vocab * sizeof(float);
+        BK_CUDA(cudaMemcpyAsync(logits_host, logits_b.p, out_bytes, cudaMemcpyDeviceToHost, stream));
+        stats.d2h_bytes += out_bytes;
+        BK_CUDA(cudaEventRecord(ev1, stream));
+        BK_CUDA(cudaStreamSynchronize(stream));
+        float ms = 0;
+        BK_CUDA(cudaEventElapsedTime(&ms, ev0, ev1));
+        end_call(ms);
+        return logits_host;
+    }
+
+    void generate_greedy(int32_t first, uint64_t steps, int32_t* out_tokens, float* out_logits) {
+        if (steps == 0) return;
+        check_tokens(&first, 1, false);
+        if (steps > max_context - position) throw CudaError("cuda: context length exceeded");
+        begin_call();
+        if (out_logits != nullptr && logit_history.bytes < steps * vocab * sizeof(float)) {
+            if (logit_history.p) cudaFree(logit_history.p);
+            logit_history.p = nullptr;
+            logit_history.alloc(steps * vocab * sizeof(float));
+        }
+        const uint32_t pos32 = uint32_t(position);
+        tokens_host[0] = first;
+        std::memcpy(tokens_host + kMaxBatch, &pos32, sizeof(pos32));
+        tokens_host[kMaxBatch + 1] = 0;
+        tokens_host[kMaxBatch + 2] = 0;
+        BK_CUDA(cudaMemcpyAsync(tokens_dev.p, tokens_host, sizeof(int32_t), cudaMemcpyHostToDevice, stream));
+        BK_CUDA(cudaMemcpyAsync(scalars.p, tokens_host + kMaxBatch, 3 * sizeof(uint32_t), cudaMemcpyHostToDevice, stream));
+        stats.h2d_bytes += 4 * sizeof(int32_t);
+        build_step_graph();
+        BK_CUDA(cudaEventRecord(ev0, stream));
+        for (uint64_t i = 0; i < steps; ++i) {
+            step_on_device();
+            if (out_logits != nullptr) {
+                BK_CUDA(cudaMemcpyAsync(logit_history.as<float>() + i * vocab, logits_b.p, size_t(vocab) * sizeof(float), cudaMemcpyDeviceToDevice, stream));
+            }
+            launch_argmax(logits_b.as<float>(), vocab, 1, d_chosen(), am_val.as<float>(), am_idx.as<int32_t>(), stream);
+            launch_advance(tokens_dev.as<int32_t>(), d_chosen(), d_position(), history.as<int32_t>(), d_history_len(), stream);
+            launches += 3;
+        }
+        BK_CUDA(cudaEventRecord(ev1, stream));
+        BK_CUDA(cudaMemcpyAsync(out_tokens, history.p, steps * sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+        stats.d2h_bytes += steps * sizeof(int32_t);
+        if (out_logits != nullptr) {
+            BK_CUDA(cudaMemcpyAsync(out_logits, logit_history.p, steps * vocab * sizeof(float), cudaMemcpyDeviceToHost, stream));
+            stats.d2h_bytes += steps * vocab * sizeof(float);
+        }
+        BK_CUDA(cudaStreamSynchronize(stream));
+        float ms = 0;
+        BK_CUDA(cudaEventElapsedTime(&ms, ev0, ev1));
+        position += steps;
+        end_call(ms);
+    }
+};
+
+}  // namespace bk
+
+// ---- C ABI ------------------------------------------------------------------------------------------
+struct brisk_cuda_session {
+    bk::Session s;
+};
+
+namespace {
+
+void put_error(char* err, size_t errlen, const std::string& what) {
+    if (err != nullptr && errlen > 0) std::snprintf(err, errlen, "%s", what.c_str());
+}
+
+template <class Fn>
+int guarded(brisk_cuda_session* session, Fn&& fn) {
+    try {
+        fn();
+        return 0;
+    } catch (const std::exception& e) {
+        session->s.error = e.what();
+        return -1;
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+int brisk_cuda_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+brisk_cuda_session* brisk_cuda_create(const brisk_cuda_model* model, const brisk_cuda_options* options, char* err, size_t errlen) {
+    if (model == nullptr) {
+        put_error(err, errlen, "cuda: no model description");
+        return nullptr;
+    }
+    brisk_cuda_options opt{};
+    if (options != nullptr) opt = *options;
+    if (opt.tp_size < 1) opt.tp_size = 1;
+    try {
+        if (brisk_cuda_device_count() <= opt.device) throw bk::CudaError("cuda: no usable CUDA device (this backend has no CPU path)");
+        BK_CUDA(cudaSetDevice(opt.device));
+        auto session = std::make_unique<brisk_cuda_session>();
+        session->s.device = opt.device;
+        session->s.load(*model, opt);
+        return session.release();
+    } catch (const std::exception& e) {
+        put_error(err, errlen, e.what());
+        return nullptr;
+    }
+}
+
+void brisk_cuda_destroy(brisk_cuda_session* session) {
+    if (session == nullptr) return;
+    cudaSetDevice(session->s.device);
+    delete session;
+}
+
+int brisk_cuda_eval(brisk_cuda_session* session, const int32_t* tokens, uint64_t n, int all_logits, const float** logits) {
+    return guarded(session, [&] {
+        BK_CUDA(cudaSetDevice(session->s.device));
+        const float* out = session->s.eval(tokens, n, all_logits != 0);
+        if (logits != nullptr) *logits = out;
+    });
+}
+
+int brisk_cuda_rollback(brisk_cuda_session* session, uint64_t position) {
+    return guarded(session, [&] {
+        if (position > session->s.position) throw bk::CudaError("cuda: cannot roll forward");
+        session->s.position = position;  // the cache keeps its storage; later entries are simply overwritten
+    });
+}
+
+uint64_t brisk_cuda_position(const brisk_cuda_session* session) { return session->s.position; }
+uint32_t brisk_cuda_vocab_size(const brisk_cuda_session* session) { return session->s.vocab; }
+uint64_t brisk_cuda_max_context(const brisk_cuda_session* session) { return session->s.max_context; }
+const char* brisk_cuda_last_error(const brisk_cuda_session* session) { return session->s.error.c_str(); }
+
+int brisk_cuda_generate_greedy(brisk_cuda_session* session, int32_t first_token, uint64_t steps, int32_t* out_tokens, float* out_logits) {
+    return guarded(session, [&] {
+        BK_CUDA(cudaSetDevice(session->s.device));
+        session->s.generate_greedy(first_token, steps, out_tokens, out_logits);
+    });
+}
+
+int brisk_cuda_get_stats(const brisk_cuda_session* session, brisk_cuda_stats* out) {
+    if (session == nullptr || out == nullptr) return -1;
+    *out = session->s.stats;
+    return 0;
+}
+
+int brisk_cuda_tp_unique_id(void* out128, char* err, size_t errlen) {
+    (void)out128;
+    put_error(err, errlen, "cuda: tensor parallelism is not available in this build");
+    return -1;
+}
+
+}  // extern "C"

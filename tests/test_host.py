@@ -1,0 +1,95 @@
+"""Host-side pieces that need no GPU: the format encoders, the C ABI library's exported symbols, the build."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+import helpers as H
+from brisk_llm_b200 import abi, formats as F, synth
+
+
+@pytest.mark.parametrize("fmt", (F.Q4_0, F.Q8_0, F.Q4_K, F.Q6_K, F.TQ2_0, F.F16), ids=lambda f: F.NAMES[f])
+def test_encoders_are_valid_and_close(fmt):
+    wb, w = H.random_matrix(fmt, 16, 512, seed=fmt)
+    assert wb.nbytes == 16 * F.row_bytes(fmt, 512)
+    deq = np.empty(16 * 512, np.float32)
+    assert H.oracle().oracle_dequantize(fmt, wb.ctypes.data, H.fptr(deq), deq.size) == 0
+    assert np.array_equal(deq, F.dequantize(fmt, wb, deq.size))
+    step = {F.Q4_0: 0.02 * 4 / 8, F.Q8_0: 0.02 * 4 / 127, F.Q4_K: 0.02 * 8 / 15, F.Q6_K: 0.02 * 4 / 32, F.TQ2_0: 1e-6, F.F16: 1e-4}[fmt]
+    assert np.abs(deq - w.ravel()).max() <= step
+
+
+def test_llama3_rope_factors():
+    f = synth.llama3_rope_factors(64, 5e5, 32.0, 1.0, 4.0, 8192)
+    assert f.shape == (32,) and f[0] == 1.0 and f[-1] == 32.0
+    assert np.all(np.diff(f) >= 0)
+
+
+def test_weight_bytes_of_the_headline_shape():
+    # 28 layers of Q4_0 + tied Q4_0 head + f32 norms (the per-token roofline numerator)
+    s = synth.QWEN3_0_6B
+    per_layer = (s.q_dim + 2 * s.kv_dim) * s.hidden + s.hidden * s.q_dim + 3 * s.ffn * s.hidden
+    total = (s.layers * per_layer + s.vocab * s.hidden) * 18 // 32 + (s.layers * (2 * s.hidden + 2 * s.head_dim) + s.hidden) * 4
+    assert total == 335_503_360
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(H.ROOT, "include", "brisk_cuda.h")).read()
+    declared = set(re.findall(r"\b(brisk_cuda_[a-z_0-9]+)\s*\(", header))
+    assert declared == set(abi.SIGNATURES), declared ^ set(abi.SIGNATURES)
+    if not os.path.exists(abi.LIB_PATH):
+        from brisk_llm_b200 import build
+        build.build()
+    lib = C.CDLL(abi.LIB_PATH)
+    for name in declared:
+        assert hasattr(lib, name), name
+
+
+def test_missing_library_fails_loudly(tmp_path):
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        abi.load_library(str(tmp_path / "nope.so"))
+
+
+def test_struct_sizes_match_the_header():
+    # the C compiler's view of the same structs
+    import subprocess, tempfile, textwrap
+    src = textwrap.dedent('''
+        #include <stdio.h>
+        #include "brisk_cuda.h"
+        int main(void) { printf("%zu %zu %zu %zu %zu\\n", sizeof(brisk_cuda_matrix), sizeof(brisk_cuda_layer), sizeof(brisk_cuda_model),
+                                sizeof(brisk_cuda_options), sizeof(brisk_cuda_stats)); return 0; }''')
+    with tempfile.TemporaryDirectory() as d:
+        c = os.path.join(d, "s.c")
+        open(c, "w").write(src)
+        subprocess.run(["gcc", "-I", os.path.join(H.ROOT, "include"), c, "-o", os.path.join(d, "s")], check=True)
+        got = [int(v) for v in subprocess.run([os.path.join(d, "s")], capture_output=True, text=True, check=True).stdout.split()]
+    assert got == [C.sizeof(abi.Matrix), C.sizeof(abi.Layer), C.sizeof(abi.Model), C.sizeof(abi.Options), C.sizeof(abi.Stats)]
+
+
+def test_lookup_drafter_and_speculator_host_logic():
+    from brisk_llm_b200 import speculative
+    d = speculative.LookupDrafter()
+    assert d.draft(5) == []
+    d.observe([1, 2, 3, 4, 5, 1, 2, 3])
+    assert d.draft(5) == [4, 5, 1, 2, 3] and d.draft(1) == [4]
+    r = speculative.LookupDrafter()
+    r.observe([7, 8, 9, 7, 8, 10, 7, 8])
+    assert r.draft(3) == [10, 7, 8]
+    s1 = speculative.LookupDrafter()
+    s1.observe([5, 6, 1, 5])
+    assert s1.draft(4) == [6, 1, 5]
+    f = speculative.LookupDrafter()
+    f.observe([1, 2, 3])
+    assert f.draft(4) == []
+    # the Speculator over the oracle session settles exactly what the C restatement of the reference loop settles
+    import importlib.util
+    spec_ = importlib.util.spec_from_file_location("make_golden", os.path.join(H.GOLDEN, "make_golden.py"))
+    mg = importlib.util.module_from_spec(spec_)
+    spec_.loader.exec_module(mg)
+    g = np.load(os.path.join(H.GOLDEN, "model_qwen3.npz"))
+    s = H.OracleSession(mg.golden_model("qwen3"))
+    got, stats = speculative.speculate(s, g["speculate_prompt"], 8, 24)
+    assert np.array_equal(got, g["speculate24"])
+    assert [stats["rounds"] + stats["plain"], stats["accepted"]] == list(g["speculate_rounds_accepted"])
