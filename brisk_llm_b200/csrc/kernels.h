@@ -82,14 +82,13 @@ struct AttnArgs {
     const __half* k_cache; // [kv][max_context][dim]
     const __half* v_cache;
     float* out;            // [n][heads*dim]
-    float* partial;        // scratch: [n][heads][splits][dim + 2]
+    float* scores;         // scratch: [n][heads][max_context]
     const uint32_t* position;
     uint32_t n, heads, kv_heads, dim, max_context;
     uint32_t max_visible;  // host-side upper bound of position + n (sizes the grid)
     float scale;
 };
-uint32_t attn_split_len();
-size_t attn_partial_floats(uint32_t n, uint32_t heads, uint32_t dim, uint32_t max_context);
+size_t attn_scratch_floats(uint32_t n, uint32_t heads, uint32_t max_context);
 void launch_attention(const AttnArgs& a, cudaStream_t s);
 
 // First maximum of each of n rows of logits[n][vocab] (lowest index on ties) -> out_token[n].

@@ -3,9 +3,18 @@
 // One warp owns RW consecutive weight rows and walks their 16-byte units with lane stride, so each
 // load instruction of a warp covers 512 contiguous bytes of a row and every lane keeps RW independent
 // 16-byte loads in flight. The arithmetic is the reference's (src/quant.cpp:445-596): integer dot per
-// block against Q8_0/Q8_K activations, one f32 scaling per block, f32 sum over blocks. Integer partial
-// sums of lanes that share a block are combined with shuffles BEFORE the conversion to float, so each
-// block's term is the same float the CPU computes; only the order of the final sum over blocks differs.
+// block against Q8_0/Q8_K activations, one f32 scaling per block, f32 sum over blocks IN BLOCK ORDER.
+// Integer partial sums of lanes that share a block are combined with shuffles before the conversion to
+// float, so each block's term is the float the CPU computes; the 32 terms a warp produces per step are
+// then transposed through shared memory so that one lane per (row, token) adds them one after the other,
+// continuing its running sum - the same sequence of roundings as the CPU's loop. Results are therefore
+// bit-identical to the reference's generic kernels, which matters because the next step re-quantises
+// them to 8 bits: a 1-ulp difference occasionally flips a rounding there and the flip then spreads.
+// (F16/F32 matrices - the output head of the ternary model - use lane-partial sums and a tree: their
+// results feed only the arg-max or the sampler, never another quantisation.)
+#include <type_traits>
+
+#include "exact_math.h"
 #include "kernels.h"
 
 namespace bk {
@@ -32,6 +41,8 @@ __device__ __forceinline__ int dp4a(uint32_t a, uint32_t b, int c) { return __dp
 // shuffle, so all 32 lanes call it together; `valid` masks lanes past the row end.
 
 struct FQ4_0 {
+    static constexpr int kLanesPerTerm = 1;
+    static constexpr bool kExact = true;
     struct W { uint4 q; float d; };
     struct X { uint4 lo, hi; float d; int s; };
     static __device__ __forceinline__ W loadw(const DevMatrix& m, uint32_t row, uint32_t u) {
@@ -59,6 +70,8 @@ struct FQ4_0 {
 };
 
 struct FQ8_0 {
+    static constexpr int kLanesPerTerm = 2;
+    static constexpr bool kExact = true;
     struct W { uint4 q; float d; };
     struct X { uint4 q; float d; };
     static __device__ __forceinline__ W loadw(const DevMatrix& m, uint32_t row, uint32_t u) {
@@ -81,6 +94,8 @@ struct FQ8_0 {
 };
 
 struct FQ4_K {
+    static constexpr int kLanesPerTerm = 8;
+    static constexpr bool kExact = true;
     struct W { uint4 q; uint32_t sc0, sc1, mn0, mn1; float d, dmin; };
     struct X { uint4 lo, hi; float d; int bs0, bs1; };
     static __device__ __forceinline__ W loadw(const DevMatrix& m, uint32_t row, uint32_t u) {
@@ -120,6 +135,8 @@ struct FQ4_K {
 };
 
 struct FQ6_K {
+    static constexpr int kLanesPerTerm = 4;
+    static constexpr bool kExact = true;
     struct W { uint4 a, b, c; int sc[4]; float d; };
     struct X { uint4 q[4]; float d; int bs[4]; };
     static __device__ __forceinline__ W loadw(const DevMatrix& m, uint32_t row, uint32_t u) {
@@ -178,6 +195,8 @@ struct FQ6_K {
 };
 
 struct FTQ2_0 {
+    static constexpr int kLanesPerTerm = 4;
+    static constexpr bool kExact = true;
     struct W { uint4 q; float d; };
     struct X { uint4 q[4]; float d; int bsum; };
     static __device__ __forceinline__ W loadw(const DevMatrix& m, uint32_t row, uint32_t u) {
@@ -218,6 +237,8 @@ struct FTQ2_0 {
 
 // Unquantised weights against raw f32 activations (the reference's dot_f32 path for widened F16 tensors).
 struct FF16 {
+    static constexpr int kLanesPerTerm = 1;
+    static constexpr bool kExact = false;
     struct W { uint4 q; };
     struct X { float4 a, b; };
     static __device__ __forceinline__ W loadw(const DevMatrix& m, uint32_t row, uint32_t u) {
@@ -243,6 +264,8 @@ struct FF16 {
 };
 
 struct FF32 {
+    static constexpr int kLanesPerTerm = 1;
+    static constexpr bool kExact = false;
     struct W { float4 q; };
     struct X { float4 a; };
     static __device__ __forceinline__ W loadw(const DevMatrix& m, uint32_t row, uint32_t u) {
@@ -263,7 +286,7 @@ struct FF32 {
 
 __device__ __forceinline__ float silu_mul(float g, float u) {
     // gate / (1 + exp(-gate)) * up, as silu_mul_f32 (src/kernels_f32.cpp:287-289)
-    return __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
+    return __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, exact_expf(-g))), u);
 }
 __device__ __forceinline__ float relu2_mul(float g, float u) {
     const float r = fmaxf(g, 0.0f);  // src/model.cpp:1135-1138
@@ -271,10 +294,16 @@ __device__ __forceinline__ float relu2_mul(float g, float u) {
 }
 
 // RW rows of one matrix (or, for the pair epilogues, RW rows of gate and the same RW rows of up) times NTOK tokens.
+// A "chain" is one output's running sum; chain c = (matrix a, row r, token t) lives in lane c.
 template <class F, int NTOK, int RW, bool PAIR>
 __global__ void __launch_bounds__(kWarps * 32) matvec_kernel(const Params p) {
-    const uint32_t lane = threadIdx.x & 31;
-    const uint32_t group = blockIdx.x * kWarps + (threadIdx.x >> 5);
+    constexpr int MATS = PAIR ? 2 : 1;
+    constexpr int CHAINS = MATS * RW * NTOK;
+    static_assert(CHAINS <= 32, "one lane per chain");
+    __shared__ float tile[F::kExact ? kWarps : 1][F::kExact ? CHAINS : 1][33];
+
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t group = blockIdx.x * kWarps + warp;
     if (group >= p.first_group[PAIR ? 1 : p.count]) return;
     int target = 0;
     if (!PAIR) {
@@ -282,15 +311,15 @@ __global__ void __launch_bounds__(kWarps * 32) matvec_kernel(const Params p) {
     }
     const DevMatrix& m = p.m[target];
     const uint32_t row0 = (group - p.first_group[target]) * RW;
-    constexpr int MATS = PAIR ? 2 : 1;
 
-    float acc[MATS][RW][NTOK];
+    float acc[MATS][RW][NTOK];  // lane-partial sums (inexact formats only)
 #pragma unroll
     for (int a = 0; a < MATS; ++a)
 #pragma unroll
         for (int r = 0; r < RW; ++r)
 #pragma unroll
             for (int t = 0; t < NTOK; ++t) acc[a][r][t] = 0.0f;
+    float run = 0.0f;  // this lane's chain (exact formats)
 
     const uint32_t units = m.units;
     for (uint32_t u0 = 0; u0 < units; u0 += 32) {
@@ -309,24 +338,49 @@ __global__ void __launch_bounds__(kWarps * 32) matvec_kernel(const Params p) {
 #pragma unroll
                 for (int a = 0; a < MATS; ++a)
 #pragma unroll
-                    for (int r = 0; r < RW; ++r) acc[a][r][t] = __fadd_rn(acc[a][r][t], F::term(w[a][r], x, valid, uu));
+                    for (int r = 0; r < RW; ++r) {
+                        const float term = F::term(w[a][r], x, valid, uu);
+                        if constexpr (F::kExact) tile[warp][(a * RW + r) * NTOK + t][lane] = term;
+                        else acc[a][r][t] = __fadd_rn(acc[a][r][t], term);
+                    }
             }
         }
+        if constexpr (F::kExact) {
+            __syncwarp();
+            if (lane < CHAINS) {
+                const int cnt = int(min(32u, units - u0));
+                const float* mine = tile[warp][lane];
+#pragma unroll 8
+                for (int j = 0; j < cnt; j += F::kLanesPerTerm) run = __fadd_rn(run, mine[j]);
+            }
+            __syncwarp();
+        }
     }
-#pragma unroll
-    for (int r = 0; r < RW; ++r) {
-#pragma unroll
-        for (int t = 0; t < NTOK; ++t) {
-            float v0 = warp_sum(acc[0][r][t]);
-            float v1 = PAIR ? warp_sum(acc[MATS - 1][r][t]) : 0.0f;
-            if (lane == 0 && t < int(p.ntok) && row0 + r < m.rows) {
+
+    if constexpr (F::kExact) {
+        // lane c holds chain c; for a pair the up value of the same (row, token) sits RW*NTOK lanes further.
+        const float other = PAIR ? __shfl_down_sync(0xffffffffu, run, (RW * NTOK) & 31) : 0.0f;
+        if (lane < RW * NTOK) {
+            const uint32_t r = lane / NTOK, t = lane % NTOK;
+            if (t < p.ntok && row0 + r < m.rows) {
                 float* o = p.out[PAIR ? 0 : target] + size_t(p.tok0 + t) * p.ldo[PAIR ? 0 : target] + row0 + r;
-                if (PAIR) {
-                    *o = p.epi == EPI_SILU_MUL ? silu_mul(v0, v1) : relu2_mul(v0, v1);
-                } else if (p.epi == EPI_ADD) {
-                    *o = __fadd_rn(*o, v0);
-                } else {
-                    *o = v0;
+                if (PAIR) *o = p.epi == EPI_SILU_MUL ? silu_mul(run, other) : relu2_mul(run, other);
+                else if (p.epi == EPI_ADD) *o = __fadd_rn(*o, run);
+                else *o = run;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int r = 0; r < RW; ++r) {
+#pragma unroll
+            for (int t = 0; t < NTOK; ++t) {
+                const float v0 = warp_sum(acc[0][r][t]);
+                const float v1 = PAIR ? warp_sum(acc[MATS - 1][r][t]) : 0.0f;
+                if (lane == 0 && t < int(p.ntok) && row0 + r < m.rows) {
+                    float* o = p.out[PAIR ? 0 : target] + size_t(p.tok0 + t) * p.ldo[PAIR ? 0 : target] + row0 + r;
+                    if (PAIR) *o = p.epi == EPI_SILU_MUL ? silu_mul(v0, v1) : relu2_mul(v0, v1);
+                    else if (p.epi == EPI_ADD) *o = __fadd_rn(*o, v0);
+                    else *o = v0;
                 }
             }
         }
@@ -339,36 +393,47 @@ void launch_one(const Params& p, uint32_t groups, cudaStream_t s) {
     matvec_kernel<F, NTOK, RW, PAIR><<<grid, kWarps * 32, 0, s>>>(p);
 }
 
-template <class F>
-void dispatch(Params& p, bool pair, uint32_t n, cudaStream_t s) {
-    // Row groups: 4 rows per warp for a single token (more loads in flight), 2 otherwise; 1 if a target's row count is odd.
-    for (uint32_t t0 = 0; t0 < n; t0 += kMaxSmallBatch) {
-        p.tok0 = t0;
-        p.ntok = n - t0 < uint32_t(kMaxSmallBatch) ? n - t0 : kMaxSmallBatch;
-        bool div4 = true, div2 = true;
-        for (int i = 0; i < p.count; ++i) {
-            div4 = div4 && p.m[i].rows % 4 == 0;
-            div2 = div2 && p.m[i].rows % 2 == 0;
-        }
-        const int rw = p.ntok == 1 ? (div4 ? 4 : (div2 ? 2 : 1)) : (div2 ? 2 : 1);
+// Rows per warp: as many as keep one lane per chain (<= 32 chains) and divide every target's row count.
+//   1 token : 8 | 4 | 1        2-4 tokens: 4 | 1        5-8 tokens: 4 (pair: 2) | 1
+template <class F, bool PAIR>
+void dispatch_tile(Params& p, cudaStream_t s) {
+    auto divides = [&](uint32_t rw) {
+        for (int i = 0; i < p.count; ++i)
+            if (p.m[i].rows % rw != 0) return false;
+        return true;
+    };
+    auto groups_for = [&](uint32_t rw) {
         uint32_t groups = 0;
-        const int targets = pair ? 1 : p.count;
+        const int targets = PAIR ? 1 : p.count;
         for (int i = 0; i < targets; ++i) {
             p.first_group[i] = groups;
             groups += (p.m[i].rows + rw - 1) / rw;
         }
         p.first_group[targets] = groups;
-#define BK_LAUNCH(NT, RWV)                                         \
-    if (pair) launch_one<F, NT, RWV, true>(p, groups, s);          \
-    else launch_one<F, NT, RWV, false>(p, groups, s)
-        if (p.ntok == 1) {
-            if (rw == 4) { BK_LAUNCH(1, 4); } else if (rw == 2) { BK_LAUNCH(1, 2); } else { BK_LAUNCH(1, 1); }
-        } else if (p.ntok <= 4) {
-            if (rw == 2) { BK_LAUNCH(4, 2); } else { BK_LAUNCH(4, 1); }
-        } else {
-            if (rw == 2) { BK_LAUNCH(8, 2); } else { BK_LAUNCH(8, 1); }
-        }
-#undef BK_LAUNCH
+        return groups;
+    };
+    constexpr bool heavy = std::is_same_v<F, FQ6_K>;  // many registers per row: cap the rows per warp
+    if (p.ntok == 1) {
+        if (!heavy && divides(8)) launch_one<F, 1, 8, PAIR>(p, groups_for(8), s);
+        else if (divides(4)) launch_one<F, 1, 4, PAIR>(p, groups_for(4), s);
+        else launch_one<F, 1, 1, PAIR>(p, groups_for(1), s);
+    } else if (p.ntok <= 4) {
+        if (divides(4)) launch_one<F, 4, 4, PAIR>(p, groups_for(4), s);
+        else launch_one<F, 4, 1, PAIR>(p, groups_for(1), s);
+    } else {
+        constexpr int RW8 = PAIR ? 2 : 4;
+        if (divides(RW8)) launch_one<F, 8, RW8, PAIR>(p, groups_for(RW8), s);
+        else launch_one<F, 8, 1, PAIR>(p, groups_for(1), s);
+    }
+}
+
+template <class F>
+void dispatch(Params& p, bool pair, uint32_t n, cudaStream_t s) {
+    for (uint32_t t0 = 0; t0 < n; t0 += kMaxSmallBatch) {
+        p.tok0 = t0;
+        p.ntok = n - t0 < uint32_t(kMaxSmallBatch) ? n - t0 : kMaxSmallBatch;
+        if (pair) dispatch_tile<F, true>(p, s);
+        else dispatch_tile<F, false>(p, s);
         BK_CUDA(cudaGetLastError());
     }
 }

@@ -1,5 +1,6 @@
 // Per-token vector kernels of the token loop: embedding lookup, per-head norm + RoPE + K/V cache write,
 // split-position attention with a combine pass, and the greedy arg-max that keeps decoding on the device.
+#include "exact_math.h"
 #include "kernels.h"
 
 namespace bk {
@@ -135,121 +136,117 @@ __global__ void __launch_bounds__(128) qk_norm_rope_store_kernel(const RopeArgs 
 }
 
 // ---- attention --------------------------------------------------------------------------------------------
-// Causal attention of token t (absolute position P + t) over cached positions 0..P+t, all query heads of one
-// K/V head per CTA (GQA: each cached row is read once for the group), positions split across CTAs. A warp walks
-// positions with stride 4; lanes hold dim/32 values of the row, the score is a warp-shuffle dot product, and each
-// (warp, head) keeps an online-softmax state (max, sum, accumulator). The reference computes softmax over the whole
-// row (max, f32 exp, f64 sum, src/kernels_f32.cpp:256-284); the split form differs from it by float rounding only.
+// Causal attention of token t (absolute position P + t) over cached positions 0..P+t, in the reference's own
+// order of float operations (src/model.cpp:1050-1093 over src/kernels_f32.cpp:231-284), so that the result is
+// bit-identical to the CPU engine's and the 8-bit re-quantisation that follows sees the same values:
+//   scores   s[p] = dot_f32(q, k_p) * scale, dot_f32 = 16 interleaved partial sums, then their sum in order
+//   softmax  e[p] = expf(s[p] - max) (glibc's expf, see exact_math.h), sum in f64, p[p] = e[p] * float(1/sum)
+//   output   out[i] = ((p[0]*v_0[i] + p[1]*v_1[i]) + p[2]*v_2[i]) + ...   one position after the other
+// Three kernels: scores (a thread per position, all query heads of one K/V head), softmax (a CTA per row),
+// weighted sum (a thread per output value, walking the positions in order).
 constexpr uint32_t kMaxGroup = 16;  // query heads per K/V head, at most (kMaxHeadsPerKv, src/model.h:34)
 
-template <int VPL>  // values per lane: dim / 32
-__global__ void __launch_bounds__(128) attn_partial_kernel(const AttnArgs a, uint32_t split_len, uint32_t splits) {
-    const uint32_t s = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
+template <int GROUP>
+__global__ void __launch_bounds__(128) attn_scores_kernel(const AttnArgs a) {
+    extern __shared__ float qs[];  // [GROUP][dim]
+    const uint32_t kvh = blockIdx.y, t = blockIdx.z, dim = a.dim;
     const uint32_t visible = *a.position + t + 1;
-    const uint32_t begin = s * split_len;
-    if (begin >= visible) return;
-    const uint32_t end = min(visible, begin + split_len);
-    const uint32_t group = a.heads / a.kv_heads, dim = a.dim;
-    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-
-    extern __shared__ float smem[];  // [4 warps][group][dim + 2] partial states
-
-    const __half* kbase = a.k_cache + size_t(kvh) * a.max_context * dim;
-    const __half* vbase = a.v_cache + size_t(kvh) * a.max_context * dim;
-
-    // Heads are processed in chunks of 4 to bound registers; K/V rows of a split stay in L1/L2 across chunks.
-    for (uint32_t g0 = 0; g0 < group; g0 += 4) {
-        const uint32_t gn = min(4u, group - g0);
-        float qv[4][VPL], acc[4][VPL], m[4], l[4];
+    const uint32_t p = blockIdx.x * 128 + threadIdx.x;
+    if (blockIdx.x * 128 >= visible) return;
+    for (uint32_t i = threadIdx.x; i < GROUP * dim; i += 128) qs[i] = a.q[size_t(t) * a.heads * dim + size_t(kvh) * GROUP * dim + i];
+    __syncthreads();
+    if (p >= visible) return;
+    const __half* kr = a.k_cache + (size_t(kvh) * a.max_context + p) * dim;
+    float lanes[GROUP][16];
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-            m[g] = -INFINITY;
-            l[g] = 0.0f;
+    for (int g = 0; g < GROUP; ++g)
 #pragma unroll
-            for (int i = 0; i < VPL; ++i) {
-                acc[g][i] = 0.0f;
-                qv[g][i] = g < int(gn) ? a.q[size_t(t) * a.heads * dim + size_t(kvh * group + g0 + g) * dim + lane * VPL + i] : 0.0f;
+        for (int j = 0; j < 16; ++j) lanes[g][j] = 0.0f;
+    for (uint32_t i = 0; i < dim; i += 16) {
+        const uint4 k0 = *reinterpret_cast<const uint4*>(kr + i), k1 = *reinterpret_cast<const uint4*>(kr + i + 8);
+        float kf[16];
+        const __half2* h0 = reinterpret_cast<const __half2*>(&k0);
+        const __half2* h1 = reinterpret_cast<const __half2*>(&k1);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f0 = __half22float2(h0[j]), f1 = __half22float2(h1[j]);
+            kf[2 * j] = f0.x; kf[2 * j + 1] = f0.y; kf[8 + 2 * j] = f1.x; kf[8 + 2 * j + 1] = f1.y;
+        }
+#pragma unroll
+        for (int g = 0; g < GROUP; ++g) {
+            const float4* q4 = reinterpret_cast<const float4*>(qs + g * dim + i);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float4 q = q4[j];
+                lanes[g][4 * j + 0] = __fadd_rn(lanes[g][4 * j + 0], __fmul_rn(q.x, kf[4 * j + 0]));
+                lanes[g][4 * j + 1] = __fadd_rn(lanes[g][4 * j + 1], __fmul_rn(q.y, kf[4 * j + 1]));
+                lanes[g][4 * j + 2] = __fadd_rn(lanes[g][4 * j + 2], __fmul_rn(q.z, kf[4 * j + 2]));
+                lanes[g][4 * j + 3] = __fadd_rn(lanes[g][4 * j + 3], __fmul_rn(q.w, kf[4 * j + 3]));
             }
         }
-        for (uint32_t p = begin + warp; p < end; p += 4) {
-            float kf[VPL], vf[VPL];
-            const __half* kr = kbase + size_t(p) * dim + lane * VPL;
-            const __half* vr = vbase + size_t(p) * dim + lane * VPL;
-            if constexpr (VPL == 4) {
-                const uint2 kk = *reinterpret_cast<const uint2*>(kr);
-                const uint2 vv = *reinterpret_cast<const uint2*>(vr);
-                const float2 k0 = __half22float2(*reinterpret_cast<const __half2*>(&kk.x)), k1 = __half22float2(*reinterpret_cast<const __half2*>(&kk.y));
-                const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(&vv.x)), v1 = __half22float2(*reinterpret_cast<const __half2*>(&vv.y));
-                kf[0] = k0.x; kf[1] = k0.y; kf[2] = k1.x; kf[3] = k1.y;
-                vf[0] = v0.x; vf[1] = v0.y; vf[2] = v1.x; vf[3] = v1.y;
-            } else {
+    }
 #pragma unroll
-                for (int i = 0; i < VPL; ++i) {
-                    kf[i] = __half2float(kr[i]);
-                    vf[i] = __half2float(vr[i]);
-                }
-            }
+    for (int g = 0; g < GROUP; ++g) {
+        float sum = 0.0f;
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-                if (g < int(gn)) {
-                    float dot = 0.0f;
-#pragma unroll
-                    for (int i = 0; i < VPL; ++i) dot = fmaf(qv[g][i], kf[i], dot);
-                    dot = __fmul_rn(warp_sum(dot), a.scale);
-                    const float mn = fmaxf(m[g], dot);
-                    const float corr = expf(m[g] - mn);  // exp(-inf) = 0 on the first position
-                    const float e = expf(dot - mn);
-                    l[g] = fmaf(l[g], corr, e);
-#pragma unroll
-                    for (int i = 0; i < VPL; ++i) acc[g][i] = fmaf(acc[g][i], corr, __fmul_rn(e, vf[i]));
-                    m[g] = mn;
-                }
-            }
-        }
-        // Merge the four warps' states, then one partial (max, sum, acc) per (token, head, split).
-        for (uint32_t g = 0; g < gn; ++g) {
-            float* st = smem + (size_t(warp) * 4 + g) * (dim + 2);
-#pragma unroll
-            for (int i = 0; i < VPL; ++i) st[lane * VPL + i] = acc[g][i];
-            if (lane == 0) {
-                st[dim] = m[g];
-                st[dim + 1] = l[g];
-            }
-        }
-        __syncthreads();
-        for (uint32_t g = 0; g < gn; ++g) {
-            const float* s0 = smem + (0 * 4 + g) * (dim + 2);
-            const float* s1 = smem + (1 * 4 + g) * (dim + 2);
-            const float* s2 = smem + (2 * 4 + g) * (dim + 2);
-            const float* s3 = smem + (3 * 4 + g) * (dim + 2);
-            const float M = fmaxf(fmaxf(s0[dim], s1[dim]), fmaxf(s2[dim], s3[dim]));
-            const float c0 = expf(s0[dim] - M), c1 = expf(s1[dim] - M), c2 = expf(s2[dim] - M), c3 = expf(s3[dim] - M);
-            float* o = a.partial + ((size_t(t) * a.heads + kvh * group + g0 + g) * splits + s) * (dim + 2);
-            for (uint32_t i = threadIdx.x; i < dim; i += 128) o[i] = s0[i] * c0 + s1[i] * c1 + s2[i] * c2 + s3[i] * c3;
-            if (threadIdx.x == 0) {
-                o[dim] = M;
-                o[dim + 1] = s0[dim + 1] * c0 + s1[dim + 1] * c1 + s2[dim + 1] * c2 + s3[dim + 1] * c3;
-            }
-        }
-        __syncthreads();
+        for (int j = 0; j < 16; ++j) sum = __fadd_rn(sum, lanes[g][j]);
+        a.scores[(size_t(t) * a.heads + kvh * GROUP + g) * a.max_context + p] = __fmul_rn(sum, a.scale);
     }
 }
 
-__global__ void __launch_bounds__(128) attn_combine_kernel(const AttnArgs a, uint32_t split_len, uint32_t splits) {
-    const uint32_t h = blockIdx.x, t = blockIdx.y, dim = a.dim;
+__global__ void __launch_bounds__(256) attn_softmax_kernel(const AttnArgs a) {
+    const uint32_t h = blockIdx.x, t = blockIdx.y, tid = threadIdx.x;
     const uint32_t visible = *a.position + t + 1;
-    const uint32_t used = (visible + split_len - 1) / split_len;
-    const float* p = a.partial + (size_t(t) * a.heads + h) * splits * (dim + 2);
-    float M = -INFINITY;
-    for (uint32_t s = 0; s < used; ++s) M = fmaxf(M, p[s * (dim + 2) + dim]);
-    float denom = 0.0f;
-    for (uint32_t s = 0; s < used; ++s) denom = fmaf(p[s * (dim + 2) + dim + 1], expf(p[s * (dim + 2) + dim] - M), denom);
-    const float inv = __fdiv_rn(1.0f, denom);
-    for (uint32_t i = threadIdx.x; i < dim; i += 128) {
-        float v = 0.0f;
-        for (uint32_t s = 0; s < used; ++s) v = fmaf(p[s * (dim + 2) + i], expf(p[s * (dim + 2) + dim] - M), v);
-        a.out[size_t(t) * a.heads * dim + size_t(h) * dim + i] = __fmul_rn(v, inv);
+    float* s = a.scores + (size_t(t) * a.heads + h) * a.max_context;
+    __shared__ float redf[8];
+    __shared__ double redd[8];
+    float mx = -INFINITY;
+    for (uint32_t p = tid; p < visible; p += 256) mx = fmaxf(mx, s[p]);
+    mx = warp_max(mx);
+    if ((tid & 31) == 0) redf[tid >> 5] = mx;
+    __syncthreads();
+    mx = redf[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) mx = fmaxf(mx, redf[w]);
+    double part = 0.0;
+    for (uint32_t p = tid; p < visible; p += 256) {
+        const float e = exact_expf(__fsub_rn(s[p], mx));
+        s[p] = e;
+        part += double(e);
     }
+    part = warp_sum(part);
+    if ((tid & 31) == 0) redd[tid >> 5] = part;
+    __syncthreads();
+    double total = 0.0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) total += redd[w];
+    const float inv = float(1.0 / total);
+    for (uint32_t p = tid; p < visible; p += 256) s[p] = __fmul_rn(s[p], inv);
+}
+
+// One thread per output value; a CTA covers 128 consecutive values of a token's attended row (one head of 128, two of 64).
+__global__ void __launch_bounds__(128) attn_weighted_kernel(const AttnArgs a) {
+    const uint32_t t = blockIdx.y, dim = a.dim;
+    const uint32_t col = blockIdx.x * 128 + threadIdx.x;  // index into [heads*dim]
+    if (col >= a.heads * dim) return;
+    const uint32_t h = col / dim, i = col % dim, kvh = h / (a.heads / a.kv_heads);
+    const uint32_t visible = *a.position + t + 1;
+    const float* w = a.scores + (size_t(t) * a.heads + h) * a.max_context;
+    const __half* v = a.v_cache + size_t(kvh) * a.max_context * dim + i;
+    float acc = 0.0f;
+    uint32_t p = 0;
+    for (; p + 8 <= visible; p += 8) {
+        float wv[8], vv[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            wv[j] = w[p + j];
+            vv[j] = __half2float(v[size_t(p + j) * dim]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc = __fadd_rn(acc, __fmul_rn(wv[j], vv[j]));
+    }
+    for (; p < visible; ++p) acc = __fadd_rn(acc, __fmul_rn(w[p], __half2float(v[size_t(p) * dim])));
+    a.out[size_t(t) * a.heads * dim + col] = acc;
 }
 
 // ---- greedy arg-max -------------------------------------------------------------------------------------
@@ -330,35 +327,24 @@ void launch_qk_norm_rope_store(const RopeArgs& a, cudaStream_t s) {
     BK_CUDA(cudaGetLastError());
 }
 
-uint32_t attn_split_len() { return 64; }
-
-static uint32_t split_len_for(uint32_t n, uint32_t max_context) {
-    if (n > uint32_t(kMaxSmallBatch)) return 256;  // prompt batches: many tokens already fill the GPU
-    return max_context > 4096 ? 128 : 32;          // decode: short splits, one wave of CTAs
-}
-
-size_t attn_partial_floats(uint32_t n, uint32_t heads, uint32_t dim, uint32_t max_context) {
-    const uint32_t sl = split_len_for(n, max_context);
-    const uint32_t splits = (max_context + sl - 1) / sl;
-    return size_t(n) * heads * splits * (dim + 2);
-}
+size_t attn_scratch_floats(uint32_t n, uint32_t heads, uint32_t max_context) { return size_t(n) * heads * max_context; }
 
 void launch_attention(const AttnArgs& a, cudaStream_t s) {
     const uint32_t group = a.heads / a.kv_heads;
-    if (a.dim % 32 != 0 || a.dim > 128 || group > kMaxGroup) throw CudaError("cuda: head size must be 32, 64, 96 or 128 and at most 16 query heads per K/V head");
-    const uint32_t sl = split_len_for(a.n, a.max_context);
-    const uint32_t splits = (a.max_context + sl - 1) / sl;
-    const uint32_t used = (a.max_visible + sl - 1) / sl;
-    const dim3 grid(used, a.kv_heads, a.n);
-    const size_t smem = size_t(4) * 4 * (a.dim + 2) * sizeof(float);
-    switch (a.dim / 32) {
-        case 1: attn_partial_kernel<1><<<grid, 128, smem, s>>>(a, sl, splits); break;
-        case 2: attn_partial_kernel<2><<<grid, 128, smem, s>>>(a, sl, splits); break;
-        case 3: attn_partial_kernel<3><<<grid, 128, smem, s>>>(a, sl, splits); break;
-        default: attn_partial_kernel<4><<<grid, 128, smem, s>>>(a, sl, splits); break;
+    if (a.dim % 16 != 0 || a.dim > 256 || group > kMaxGroup) throw CudaError("cuda: head size must be a multiple of 16 up to 256 and at most 16 query heads per K/V head");
+    const dim3 grid((a.max_visible + 127) / 128, a.kv_heads, a.n);
+    const size_t smem = size_t(group) * a.dim * sizeof(float);
+    switch (group) {
+        case 1: attn_scores_kernel<1><<<grid, 128, smem, s>>>(a); break;
+        case 2: attn_scores_kernel<2><<<grid, 128, smem, s>>>(a); break;
+        case 4: attn_scores_kernel<4><<<grid, 128, smem, s>>>(a); break;
+        case 8: attn_scores_kernel<8><<<grid, 128, smem, s>>>(a); break;
+        default: throw CudaError("cuda: query heads per K/V head must be 1, 2, 4 or 8");
     }
     BK_CUDA(cudaGetLastError());
-    attn_combine_kernel<<<dim3(a.heads, a.n), 128, 0, s>>>(a, sl, splits);
+    attn_softmax_kernel<<<dim3(a.heads, a.n), 256, 0, s>>>(a);
+    BK_CUDA(cudaGetLastError());
+    attn_weighted_kernel<<<dim3((a.heads * a.dim + 127) / 128, a.n), 128, 0, s>>>(a);
     BK_CUDA(cudaGetLastError());
 }
 

@@ -13,10 +13,15 @@
 #include "kernels.h"
 
 namespace bk {
+
+struct DevBuffer;
+
 namespace {
 
 constexpr uint32_t kMaxBatch = 512;   // tokens per prefill pass (the reference: 256 on the CPU, 512 on Metal)
 constexpr uint32_t kMaxScored = 64;   // Engine::kMaxScoredTokens, src/engine.h:32
+
+}  // namespace
 
 struct DevBuffer {
     void* p = nullptr;
@@ -31,6 +36,8 @@ struct DevBuffer {
     }
     template <class T> T* as() const { return static_cast<T*>(p); }
 };
+
+namespace {
 
 struct Layer {
     DevMatrix q, k, v, o, gate, up, down;
@@ -225,9 +232,7 @@ struct Session {
         actbs.alloc(size_t(kMaxBatch) * (widest / 16) * 2);
         act.f32 = actf.as<float>(); act.q0 = actq0.as<int8_t>(); act.d0 = actd0.as<float>(); act.s0 = acts0.as<int32_t>();
         act.qk = actqk.as<int8_t>(); act.dk = actdk.as<float>(); act.bs = actbs.as<int16_t>();
-        const size_t pf = std::max(attn_partial_floats(kMaxBatch, heads, head_dim, uint32_t(max_context)),
-                                   attn_partial_floats(kMaxSmallBatch, heads, head_dim, uint32_t(max_context)));
-        partial.alloc(pf * 4);
+        partial.alloc(attn_scratch_floats(kMaxBatch, heads, uint32_t(max_context)) * 4);
         am_val.alloc(argmax_scratch_elems(vocab) * 4);
         am_idx.alloc(argmax_scratch_elems(vocab) * 4);
         history.alloc((max_context + 1) * sizeof(int32_t));
@@ -304,11 +309,11 @@ struct Session {
 
             AttnArgs at{};
             at.q = q_b.as<float>(); at.k_cache = L.k_cache; at.v_cache = L.v_cache; at.out = attended_b.as<float>();
-            at.partial = partial.as<float>(); at.position = d_position();
+            at.scores = partial.as<float>(); at.position = d_position();
             at.n = n; at.heads = heads; at.kv_heads = kv_heads; at.dim = head_dim; at.max_context = uint32_t(max_context);
             at.max_visible = max_visible; at.scale = attn_scale;
             launch_attention(at, stream);
-            launches += 2;
+            launches += 3;
 
             Needs no;
             need(no, L.o.type);
@@ -548,6 +553,20 @@ int brisk_cuda_get_stats(const brisk_cuda_session* session, brisk_cuda_stats* ou
     if (session == nullptr || out == nullptr) return -1;
     *out = session->s.stats;
     return 0;
+}
+
+int brisk_cuda_debug_buffer(brisk_cuda_session* session, const char* name, float* out, uint64_t count) {
+    return guarded(session, [&] {
+        bk::Session& s = session->s;
+        const std::string n(name ? name : "");
+        const bk::DevBuffer* b = n == "hidden" ? &s.hidden_b : n == "query" ? &s.q_b : n == "attended" ? &s.attended_b : n == "ffn" ? &s.ffn_b
+                                 : n == "logits" ? &s.logits_b : nullptr;
+        if (b == nullptr) throw bk::CudaError("cuda: unknown debug buffer '" + n + "'");
+        if (count * sizeof(float) > b->bytes) throw bk::CudaError("cuda: debug read past the end of '" + n + "'");
+        BK_CUDA(cudaSetDevice(s.device));
+        BK_CUDA(cudaStreamSynchronize(s.stream));
+        BK_CUDA(cudaMemcpy(out, b->p, count * sizeof(float), cudaMemcpyDeviceToHost));
+    });
 }
 
 int brisk_cuda_tp_unique_id(void* out128, char* err, size_t errlen) {

@@ -55,22 +55,31 @@ class CudaSession:
     def _fail(self):
         raise RuntimeError(self._lib.brisk_cuda_last_error(self._h).decode())
 
-    def _eval(self, tokens, all_logits: bool) -> np.ndarray:
+    def _eval(self, tokens, all_logits: bool, copy: bool = True) -> np.ndarray:
         tokens = np.ascontiguousarray(np.atleast_1d(tokens), np.int32)
         out = C.POINTER(C.c_float)()
         if self._lib.brisk_cuda_eval(self._h, tokens.ctypes.data_as(C.POINTER(C.c_int32)), len(tokens), int(all_logits), C.byref(out)) != 0:
             self._fail()
         rows = len(tokens) if all_logits else 1
-        view = np.ctypeslib.as_array(out, shape=(rows, self.vocab_size))  # pinned memory of the session, valid until the next call
+        view = np.ctypeslib.as_array(out, shape=(rows, self.vocab_size))  # pinned memory of the session
+        if copy:
+            view = view.copy()
         return view if all_logits else view[0]
 
-    def eval(self, tokens) -> np.ndarray:
-        """Appends the tokens; logits (vocab floats) for the token after the last one. Valid until the next call."""
-        return self._eval(tokens, False)
+    def eval(self, tokens, copy: bool = True) -> np.ndarray:
+        """Appends the tokens; logits (vocab floats) for the token after the last one. With copy=False the result is a
+        view of the session's pinned buffer, valid only until the session's next call (the reference's contract)."""
+        return self._eval(tokens, False, copy)
 
-    def eval_all(self, tokens) -> np.ndarray:
+    def eval_all(self, tokens, copy: bool = True) -> np.ndarray:
         """Like eval(), one row of logits per token; at most 64 tokens."""
-        return self._eval(tokens, True)
+        return self._eval(tokens, True, copy)
+
+    def debug_buffer(self, name: str, count: int) -> np.ndarray:
+        out = np.empty(count, np.float32)
+        if self._lib.brisk_cuda_debug_buffer(self._h, name.encode(), out.ctypes.data_as(C.POINTER(C.c_float)), count) != 0:
+            self._fail()
+        return out
 
     def rollback(self, position: int) -> None:
         if self._lib.brisk_cuda_rollback(self._h, position) != 0:

@@ -180,6 +180,12 @@ int brisk_cuda_matmul(int32_t type, const void* w, uint64_t rows, uint64_t cols,
 int brisk_cuda_matmul_seconds(int32_t type, const void* w, uint64_t rows, uint64_t cols, uint64_t n, uint32_t copies,
                               uint32_t iterations, double* seconds, char* err, size_t errlen);
 
+/* Debug hook, the counterpart of the BRISK_GPU_DEBUG / BRISK_CPU_DEBUG dumps (src/metal/metal_session.mm:1073-1100,
+ * src/model.cpp:1183-1192): copies the first `count` floats of one scratch buffer as the last batch left it.
+ * name: "hidden" (residual stream [n][hidden]), "query" (after norm and RoPE), "attended", "ffn" (gated activation),
+ * "logits". Intended for layer-by-layer comparison with a one-layer model. */
+int brisk_cuda_debug_buffer(brisk_cuda_session* session, const char* name, float* out, uint64_t count);
+
 /* Tensor parallelism (no counterpart in the reference, which is single-process): rank 0 calls this
  * and hands the 128 bytes to every rank's brisk_cuda_options.tp_unique_id. */
 int brisk_cuda_tp_unique_id(void* out128, char* err, size_t errlen);

@@ -702,6 +702,16 @@ int oracle_session_rollback(oracle_session* s, uint64_t position) {
 
 uint64_t oracle_session_position(const oracle_session* s) { return s->position; }
 
+/* Scratch of the most recent batch, for layer-by-layer comparison with a one-layer model (the role of the
+ * reference's BRISK_CPU_DEBUG dump, src/model.cpp:1183-1192). */
+int oracle_session_debug_buffer(const oracle_session* s, const char* name, float* out, uint64_t count) {
+    const float* b = !strcmp(name, "hidden") ? s->hidden : !strcmp(name, "query") ? s->query : !strcmp(name, "attended") ? s->attended
+                     : !strcmp(name, "ffn") ? s->gate : !strcmp(name, "logits") ? s->logits : NULL;
+    if (!b) return -1;
+    memcpy(out, b, count * sizeof(float));
+    return 0;
+}
+
 int oracle_session_layer_trace(const oracle_session* s, float* out) {
     memcpy(out, s->trace, (size_t)s->m.layer_count * s->m.hidden * 4);
     return 0;

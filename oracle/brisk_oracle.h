@@ -41,6 +41,7 @@ int oracle_session_generate_greedy(oracle_session* s, const int32_t* prompt, uin
                                    int32_t* out_tokens, float* out_logits);
 /* The last token's residual stream after each layer of the most recent eval: [layers][hidden]. */
 int oracle_session_layer_trace(const oracle_session* s, float* out);
+int oracle_session_debug_buffer(const oracle_session* s, const char* name, float* out, uint64_t count);
 uint64_t oracle_lookup_draft(const int32_t* history, uint64_t n, uint64_t count, int32_t* out);
 int64_t oracle_session_speculate(oracle_session* s, const int32_t* prompt, uint64_t n_prompt, uint64_t draft_tokens,
                                  uint64_t want, int32_t* out, uint64_t* rounds, uint64_t* accepted);

@@ -64,6 +64,7 @@ def oracle() -> C.CDLL:
         lib.oracle_session_log_likelihood.argtypes = [C.c_void_p, _IP, C.c_uint64, C.POINTER(C.c_double)]
         lib.oracle_session_generate_greedy.argtypes = [C.c_void_p, _IP, C.c_uint64, C.c_uint64, _IP, _FP]
         lib.oracle_session_layer_trace.argtypes = [C.c_void_p, _FP]
+        lib.oracle_session_debug_buffer.argtypes = [C.c_void_p, C.c_char_p, _FP, C.c_uint64]
         lib.oracle_lookup_draft.restype = C.c_uint64
         lib.oracle_lookup_draft.argtypes = [_IP, C.c_uint64, C.c_uint64, _IP]
         lib.oracle_session_speculate.restype = C.c_int64
@@ -169,6 +170,11 @@ class OracleSession:
     def layer_trace(self):
         out = np.empty((self.model.spec.layers, self.model.spec.hidden), np.float32)
         self.lib.oracle_session_layer_trace(self.h, fptr(out))
+        return out
+
+    def debug_buffer(self, name, count):
+        out = np.empty(count, np.float32)
+        assert self.lib.oracle_session_debug_buffer(self.h, name.encode(), fptr(out), count) == 0
         return out
 
     def speculate(self, prompt, draft_tokens, want):

@@ -1,8 +1,12 @@
 """GPU parity of the whole token loop, through the C ABI (CudaSession), against the CPU oracle and the golden
 vectors taken from the reference engine.
 
-Tolerances are the ones the task states for logits: max-abs-diff 2e-2 and relative L2 1e-3; greedy ids must be
-identical except where the reference's top-2 logit gap is below that tolerance.
+Tolerances written here are the stated ones for logits: max-abs-diff 2e-2 and relative L2 1e-3; greedy ids must be
+identical except where the reference's top-2 logit gap is below that tolerance. On top of that, families whose output
+head is quantised must match BIT FOR BIT: the kernels repeat the CPU engine's float operations in the CPU's order,
+because a single differing ulp ahead of an 8-bit re-quantisation or an f16 cache store can flip a rounding and the
+flip then spreads through the layers (measured: ~1e-2 relative after two layers). The ternary family's F16 head sums
+in a different order, so its logits are held to 1e-5 instead (its residual stream is still bit-identical).
 """
 import importlib.util
 import os
@@ -22,11 +26,15 @@ spec_.loader.exec_module(mg)
 MAX_ABS, REL_L2 = 2e-2, 1e-3
 
 
-def close(got, want):
+def close(got, want, exact=True):
     got, want = np.asarray(got), np.asarray(want)
     assert got.shape == want.shape
     assert np.abs(got - want).max() <= MAX_ABS, np.abs(got - want).max()
     assert H.rel_l2(got, want) <= REL_L2, H.rel_l2(got, want)
+    if exact:
+        assert np.array_equal(got, want), (np.abs(got - want).max(), int((got != want).sum()))
+    else:
+        assert np.abs(got - want).max() <= 1e-5
 
 
 def greedy_agrees(got_ids, want_ids, want_logits):
@@ -46,14 +54,15 @@ def test_golden_from_the_reference(family):
     m = mg.golden_model(family)
     assert mg.model_digest(m).encode() == g["digest"].tobytes()
     toks = g["tokens"]
+    ex = family != "bitnet"
     with engine.CudaSession(m) as s:
-        close(s.eval(toks[:33]), g["prefill33"])
+        close(s.eval(toks[:33]), g["prefill33"], ex)
         for i in range(4):
-            close(s.eval(toks[33 + i:34 + i]), g["decode4"][i])
-        close(s.eval_all(toks[37:46]), g["eval_all9"])
+            close(s.eval(toks[33 + i:34 + i]), g["decode4"][i], ex)
+        close(s.eval_all(toks[37:46]), g["eval_all9"], ex)
         s.rollback(35)
         assert s.position() == 35
-        close(s.eval(toks[46:47]), g["after_rollback35"])
+        close(s.eval(toks[46:47]), g["after_rollback35"], ex)
         s.rollback(0)
         ll = s.log_likelihood(toks)
         assert abs(ll - g["log_likelihood48"][0]) < 5e-3 * 47, (ll, g["log_likelihood48"][0])
@@ -63,7 +72,9 @@ def test_golden_from_the_reference(family):
         s.eval(toks[:19])
         ids, logits = s.generate_greedy(int(toks[19]), 16, want_logits=True)
         n = greedy_agrees(ids, g["greedy16_ids"], g["greedy16_logits"])
-        close(logits[:max(n, 1)], g["greedy16_logits"][:max(n, 1)])
+        close(logits[:max(n, 1)], g["greedy16_logits"][:max(n, 1)], ex)
+        if ex:
+            assert n == 16 and np.array_equal(ids, g["greedy16_ids"])
 
 
 @pytest.mark.parametrize("family,spec", [
@@ -78,22 +89,23 @@ def test_full_width_layers_against_the_oracle(family, spec):
     m = synth.perturb_norms(synth.generate(spec, seed=5))
     toks = synth.random_tokens(spec, 640, seed=6)
     o = H.OracleSession(m)
+    ex = family != "bitnet"
     with engine.CudaSession(m) as s:
-        close(s.eval(toks[:600]), o.eval(toks[:600]))
-        trace_ok = o.layer_trace()
-        assert np.isfinite(trace_ok).all()
+        close(s.eval(toks[:600]), o.eval(toks[:600]), ex)
+        # the residual stream of every prompt token of the last batch, bit for bit (all families)
+        assert np.array_equal(s.debug_buffer("hidden", 88 * spec.hidden), o.debug_buffer("hidden", 88 * spec.hidden))
         for i in range(600, 606):
-            close(s.eval(toks[i:i + 1]), o.eval(toks[i:i + 1]))
-        close(s.eval_all(toks[606:615]), o.eval_all(toks[606:615]))
+            close(s.eval(toks[i:i + 1]), o.eval(toks[i:i + 1]), ex)
+        close(s.eval_all(toks[606:615]), o.eval_all(toks[606:615]), ex)
         s.rollback(603)
         o.rollback(603)
         want_ids, want_logits = o.generate_greedy(toks[615:616], 12)
         got_logits0 = s.eval(toks[615:616])
-        close(got_logits0, want_logits[0])
+        close(got_logits0, want_logits[0], ex)
         s.rollback(603)
         ids, logits = s.generate_greedy(int(toks[615]), 12, want_logits=True)
         n = greedy_agrees(ids, want_ids, want_logits)
-        close(logits[:max(n, 1)], want_logits[:max(n, 1)])
+        close(logits[:max(n, 1)], want_logits[:max(n, 1)], ex)
         assert s.position() == 603 + 12
     o.close()
 
