@@ -1,5 +1,8 @@
 // Per-token vector kernels of the token loop: embedding lookup, per-head norm + RoPE + K/V cache write,
 // split-position attention with a combine pass, and the greedy arg-max that keeps decoding on the device.
+#include <cstdio>
+#include <string>
+
 #include "exact_math.h"
 #include "kernels.h"
 
@@ -249,6 +252,8 @@ __global__ void __launch_bounds__(128) attn_weighted_kernel(const AttnArgs a) {
     a.out[size_t(t) * a.heads * dim + col] = acc;
 }
 
+}  // namespace
+
 // ---- greedy arg-max -------------------------------------------------------------------------------------
 constexpr uint32_t kArgmaxBlocks = 148;
 
@@ -304,6 +309,8 @@ __global__ void __launch_bounds__(256) argmax_stage2(const float* pv, const int3
     }
 }
 
+namespace {
+
 __global__ void advance_kernel(int32_t* token_slot, const int32_t* chosen, uint32_t* position, int32_t* history, uint32_t* history_len) {
     const int32_t tok = *chosen;
     *token_slot = tok;
@@ -357,6 +364,56 @@ void launch_argmax(const float* logits, uint32_t vocab, uint32_t n, int32_t* out
     argmax_stage2<<<n, 256, 0, s>>>(scratch_val, scratch_idx, out_token);
     BK_CUDA(cudaGetLastError());
 }
+
+}  // namespace bk
+
+// ---- arg-max for callers that must not allocate ---------------------------------------------------------
+// The two-stage arg-max keeps one (value, index) pair per CTA and row between its stages. The session allocates that
+// scratch with cudaMalloc; this variant keeps it in the library image instead: every GPU that loads the library carries
+// these 76 KB until the process exits, and in exchange the call touches no allocator at all.
+namespace {
+constexpr uint32_t kStaticArgmaxRows = 64;  // rows one call may reduce (the most logits rows a scoring call returns)
+static __device__ __align__(256) unsigned char g_static_argmax_scratch[kStaticArgmaxRows * bk::kArgmaxBlocks * 8];
+constexpr int kMaxDevices = 64;
+void* g_static_argmax_address[kMaxDevices] = {};  // device address of the array, per device, filled on first use
+}  // namespace
+
+extern "C" int brisk_cuda_argmax_static(const float* logits, uint32_t vocab, uint32_t rows, int32_t* out_tokens, void* stream, char* err,
+                                        size_t errlen) {
+    auto fail = [&](const std::string& what) {
+        if (err != nullptr && errlen > 0) std::snprintf(err, errlen, "%s", what.c_str());
+        return -1;
+    };
+    if (rows == 0) return 0;
+    if (logits == nullptr || out_tokens == nullptr || vocab == 0) return fail("cuda: arg-max needs logits, an output and a non-empty vocabulary");
+    if (rows > kStaticArgmaxRows) {
+        return fail("cuda: the allocation-free arg-max reduces at most " + std::to_string(kStaticArgmaxRows) + " rows per call, got " +
+                    std::to_string(rows));
+    }
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return fail(std::string("cuda: cudaGetDevice failed: ") + cudaGetErrorString(e));
+    if (device < 0 || device >= kMaxDevices) return fail("cuda: device ordinal out of range");
+    if (g_static_argmax_address[device] == nullptr) {
+        // In host code the array's name is only a handle; the kernels need the address it has on the current device.
+        void* address = nullptr;
+        e = cudaGetSymbolAddress(&address, g_static_argmax_scratch);
+        if (e != cudaSuccess || address == nullptr) return fail(std::string("cuda: cudaGetSymbolAddress failed: ") + cudaGetErrorString(e));
+        g_static_argmax_address[device] = address;
+    }
+    unsigned char* base = static_cast<unsigned char*>(g_static_argmax_address[device]);
+    float* partial_value = reinterpret_cast<float*>(base);
+    int32_t* partial_index = reinterpret_cast<int32_t*>(base + size_t(kStaticArgmaxRows) * bk::kArgmaxBlocks * 4);
+    // Stage 1 writes every pair stage 2 reads for these rows, so nothing of the previous call has to be cleared.
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    bk::argmax_stage1<<<dim3(bk::kArgmaxBlocks, rows), 256, 0, s>>>(logits, vocab, partial_value, partial_index);
+    bk::argmax_stage2<<<rows, 256, 0, s>>>(partial_value, partial_index, out_tokens);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(std::string("cuda: arg-max launch failed: ") + cudaGetErrorString(e));
+    return 0;
+}
+
+namespace bk {
 
 void launch_advance(int32_t* token_slot, const int32_t* chosen, uint32_t* position, int32_t* history, uint32_t* history_len,
                     cudaStream_t s) {

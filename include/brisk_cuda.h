@@ -180,6 +180,20 @@ int brisk_cuda_matmul(int32_t type, const void* w, uint64_t rows, uint64_t cols,
 int brisk_cuda_matmul_seconds(int32_t type, const void* w, uint64_t rows, uint64_t cols, uint64_t n, uint32_t copies,
                               uint32_t iterations, double* seconds, char* err, size_t errlen);
 
+/* No counterpart in the reference. Greedy pick (first maximum, lowest id on ties - the rule of brisk_cuda_generate_greedy)
+ * of each of `rows` rows of logits[rows][vocab], for hosts that must not allocate device memory at that point: an
+ * embedder that has handed all of HBM to its own arena (a server that sizes its K/V pool to what cudaMemGetInfo
+ * reports), or one that calls from a latency-critical thread where the implicit device-wide synchronisation of an
+ * allocation is not acceptable. `logits` and `out_tokens` are DEVICE pointers owned by the caller; `stream` is a
+ * cudaStream_t (NULL: the default stream). The scratch between the two reduction stages lives in a fixed 76 KB array
+ * inside the library image, so: at most 64 rows per call (more is refused with a message); the array is shared by
+ * every call on that device and keeps the last call's contents (the first stage overwrites all it uses, nothing needs
+ * clearing); two calls whose kernels overlap on the GPU race on it - keep them on one stream or order them. The first
+ * call on each device looks up the array's device address (with that device current); make that first call before any
+ * stream capture begins. Calls no cudaMalloc/cudaFree and no allocating library routine. */
+int brisk_cuda_argmax_static(const float* logits, uint32_t vocab, uint32_t rows, int32_t* out_tokens, void* stream, char* err,
+                             size_t errlen);
+
 /* Debug hook, the counterpart of the BRISK_GPU_DEBUG / BRISK_CPU_DEBUG dumps (src/metal/metal_session.mm:1073-1100,
  * src/model.cpp:1183-1192): copies the first `count` floats of one scratch buffer as the last batch left it.
  * name: "hidden" (residual stream [n][hidden]), "query" (after norm and RoPE), "attended", "ffn" (gated activation),
