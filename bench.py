@@ -45,6 +45,7 @@ def parse():
     p.add_argument("--decode", type=int, default=0)
     p.add_argument("--layers", type=int, default=0, help="override the layer count (debugging; the reported number is then not the configured workload)")
     p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--profile", action="store_true", help="for ncu launch lists: exactly --warmup warm-up steps, no end-to-end loop, no CPU baseline (the printed number is not a bench value)")
     return p.parse_args()
 
 
@@ -267,7 +268,8 @@ def main():
         t2 = time.perf_counter()
         return t1 - t0, t2 - t1, h2d, d2h
 
-    for _ in range(max(args.warmup, 3)):
+    warmups = args.warmup if args.profile else max(args.warmup, 3)
+    for _ in range(warmups):
         device_step()
     sampler = ClockSampler(local)
     barrier()
@@ -282,14 +284,16 @@ def main():
     t_wall = time.perf_counter() - t_wall
     clocks = sampler.stop()
 
-    e2e_step()
-    barrier()
-    e_pre = e_dec = 0.0
+    e_pre = e_dec = 1e-9
     h2d = d2h = 0
-    for _ in range(args.steps):
-        a, b, c, d = e2e_step()
-        e_pre, e_dec, h2d, d2h = e_pre + a, e_dec + b, c, d
-    barrier()
+    if not args.profile:
+        e2e_step()
+        barrier()
+        e_pre = e_dec = 0.0
+        for _ in range(args.steps):
+            a, b, c, d = e2e_step()
+            e_pre, e_dec, h2d, d2h = e_pre + a, e_dec + b, c, d
+        barrier()
 
     def max_over_ranks(v):
         if dist is None:
@@ -304,7 +308,7 @@ def main():
         tokens = args.steps * decode
         value = world * tokens / (dec_ms * 1e-3)
         achieved = weight_bytes * tokens / (dec_ms * 1e-3) / 1e9
-        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmups,
                 "ms_per_step": (pre_ms + dec_ms) / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": "int8 dot products, f32 accumulate (f16 K/V cache)", "data": "synthetic",
                 "config": describe(spec, prompt, decode, {"parallelism": "replicas only" if world > 1 else "single GPU"}),
@@ -318,7 +322,10 @@ def main():
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                              "traffic": None, "peak_kind": f"of {peak_kind}", "kernel": "decode step (all kernels of one token)",
                              "algorithmic_bytes_per_token": weight_bytes}}
-        if world == 1 and not args.no_cpu_baseline:
+        if args.profile:
+            line["profile_run"] = True
+            line.pop("e2e")
+        if world == 1 and not args.no_cpu_baseline and not args.profile:
             try:
                 threads = os.cpu_count() or 1
                 sp, sd = cpu_sample_sizes(spec)

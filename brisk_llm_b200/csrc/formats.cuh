@@ -1,0 +1,270 @@
+// Per-format unit arithmetic of the streaming multiply, shared by the batched-by-8 kernel (matvec.cu) and the fused
+// single-token kernels (decode.cu). See DevMatrix / DevAct in common.cuh for the layouts these read.
+#pragma once
+
+#include "common.cuh"
+#include "exact_math.h"
+
+namespace bk {
+
+__device__ __forceinline__ int dp4a(uint32_t a, uint32_t b, int c) { return __dp4a(int(a), int(b), c); }
+
+// ---- per-format unit arithmetic -------------------------------------------------------------------------
+// Each format provides: W (a unit's weights in registers), X (the matching activations of one token),
+// loadw / loadx, and term(): the f32 contribution of the unit, already including every scale. term() may
+// shuffle, so all 32 lanes call it together; `valid` masks lanes past the row end.
+
+struct FQ4_0 {
+    static constexpr int kLanesPerTerm = 1;
+    static constexpr bool kExact = true;
+    struct W { uint4 q; float d; };
+    struct X { uint4 lo, hi; float d; int s; };
+    static __device__ __forceinline__ W loadw(const DevMatrix& m, uint32_t row, uint32_t u) {
+        const size_t i = size_t(row) * m.units + u;
+        return {ld_stream(m.qa + i * 16), __half2float(m.d[i])};
+    }
+    static __device__ __forceinline__ X loadx(const DevAct& a, uint32_t t, uint32_t u) {
+        const uint4* p = reinterpret_cast<const uint4*>(a.q0 + size_t(t) * a.cols + u * 32);
+        const size_t b = size_t(t) * (a.cols / 32) + u;
+        return {p[0], p[1], a.d0[b], a.s0[b]};
+    }
+    static __device__ __forceinline__ float term(const W& w, const X& x, bool valid, uint32_t) {
+        int acc = 0;
+        acc = dp4a(w.q.x & 0x0F0F0F0Fu, x.lo.x, acc);
+        acc = dp4a(w.q.y & 0x0F0F0F0Fu, x.lo.y, acc);
+        acc = dp4a(w.q.z & 0x0F0F0F0Fu, x.lo.z, acc);
+        acc = dp4a(w.q.w & 0x0F0F0F0Fu, x.lo.w, acc);
+        acc = dp4a((w.q.x >> 4) & 0x0F0F0F0Fu, x.hi.x, acc);
+        acc = dp4a((w.q.y >> 4) & 0x0F0F0F0Fu, x.hi.y, acc);
+        acc = dp4a((w.q.z >> 4) & 0x0F0F0F0Fu, x.hi.z, acc);
+        acc = dp4a((w.q.w >> 4) & 0x0F0F0F0Fu, x.hi.w, acc);
+        acc -= 8 * x.s;  // sum((q-8)*x) = sum(q*x) - 8*sum(x)
+        return valid ? __fmul_rn(__fmul_rn(float(acc), w.d), x.d) : 0.0f;
+    }
+};
+
+struct FQ8_0 {
+    static constexpr int kLanesPerTerm = 2;
+    static constexpr bool kExact = true;
+    struct W { uint4 q; float d; };
+    struct X { uint4 q; float d; };
+    static __device__ __forceinline__ W loadw(const DevMatrix& m, uint32_t row, uint32_t u) {
+        const size_t i = size_t(row) * m.units + u;
+        return {ld_stream(m.qa + i * 16), __half2float(m.d[size_t(row) * m.blocks + (u >> 1)])};
+    }
+    static __device__ __forceinline__ X loadx(const DevAct& a, uint32_t t, uint32_t u) {
+        return {*reinterpret_cast<const uint4*>(a.q0 + size_t(t) * a.cols + u * 16), a.d0[size_t(t) * (a.cols / 32) + (u >> 1)]};
+    }
+    static __device__ __forceinline__ float term(const W& w, const X& x, bool valid, uint32_t u) {
+        int acc = 0;
+        acc = dp4a(w.q.x, x.q.x, acc);
+        acc = dp4a(w.q.y, x.q.y, acc);
+        acc = dp4a(w.q.z, x.q.z, acc);
+        acc = dp4a(w.q.w, x.q.w, acc);
+        acc = valid ? acc : 0;
+        acc += __shfl_xor_sync(0xffffffffu, acc, 1);  // the block's other half
+        return (valid && (u & 1) == 0) ? __fmul_rn(__fmul_rn(float(acc), w.d), x.d) : 0.0f;
+    }
+};
+
+struct FQ4_K {
+    static constexpr int kLanesPerTerm = 8;
+    static constexpr bool kExact = true;
+    struct W { uint4 q; uint32_t sc0, sc1, mn0, mn1; float d, dmin; };
+    struct X { uint4 lo, hi; float d; int bs0, bs1; };
+    static __device__ __forceinline__ W loadw(const DevMatrix& m, uint32_t row, uint32_t u) {
+        const size_t i = size_t(row) * m.units + u;
+        const size_t blk = size_t(row) * m.blocks + (u >> 3);
+        const uint32_t g = (u & 7) >> 1;
+        const uint8_t* s = m.sc + blk * 16;
+        const __half2 dd = reinterpret_cast<const __half2*>(m.d)[blk];
+        return {ld_stream(m.qa + i * 16), s[2 * g], s[2 * g + 1], s[8 + 2 * g], s[9 + 2 * g], __low2float(dd), __high2float(dd)};
+    }
+    static __device__ __forceinline__ X loadx(const DevAct& a, uint32_t t, uint32_t u) {
+        const uint32_t sb = u >> 3, j = u & 7, g = j >> 1, hf = j & 1;
+        const int8_t* base = a.qk + size_t(t) * a.cols + sb * 256 + g * 64 + hf * 16;
+        const int16_t* bs = a.bs + size_t(t) * (a.cols / 16) + sb * 16 + 4 * g + hf;
+        return {*reinterpret_cast<const uint4*>(base), *reinterpret_cast<const uint4*>(base + 32), a.dk[size_t(t) * (a.cols / 256) + sb], bs[0], bs[2]};
+    }
+    static __device__ __forceinline__ float term(const W& w, const X& x, bool valid, uint32_t u) {
+        int lo = 0, hi = 0;
+        lo = dp4a(w.q.x & 0x0F0F0F0Fu, x.lo.x, lo);
+        lo = dp4a(w.q.y & 0x0F0F0F0Fu, x.lo.y, lo);
+        lo = dp4a(w.q.z & 0x0F0F0F0Fu, x.lo.z, lo);
+        lo = dp4a(w.q.w & 0x0F0F0F0Fu, x.lo.w, lo);
+        hi = dp4a((w.q.x >> 4) & 0x0F0F0F0Fu, x.hi.x, hi);
+        hi = dp4a((w.q.y >> 4) & 0x0F0F0F0Fu, x.hi.y, hi);
+        hi = dp4a((w.q.z >> 4) & 0x0F0F0F0Fu, x.hi.z, hi);
+        hi = dp4a((w.q.w >> 4) & 0x0F0F0F0Fu, x.hi.w, hi);
+        int weighted = valid ? int(w.sc0) * lo + int(w.sc1) * hi : 0;
+        int offsets = valid ? int(w.mn0) * x.bs0 + int(w.mn1) * x.bs1 : 0;
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) {  // the super-block's 8 units sit in 8 neighbouring lanes
+            weighted += __shfl_xor_sync(0xffffffffu, weighted, o);
+            offsets += __shfl_xor_sync(0xffffffffu, offsets, o);
+        }
+        if (!valid || (u & 7) != 0) return 0.0f;
+        return __fmul_rn(x.d, __fsub_rn(__fmul_rn(w.d, float(weighted)), __fmul_rn(w.dmin, float(offsets))));
+    }
+};
+
+struct FQ6_K {
+    static constexpr int kLanesPerTerm = 4;
+    static constexpr bool kExact = true;
+    struct W { uint4 a, b, c; int sc[4]; float d; };
+    struct X { uint4 q[4]; float d; int bs[4]; };
+    static __device__ __forceinline__ W loadw(const DevMatrix& m, uint32_t row, uint32_t u) {
+        const size_t i = size_t(row) * m.units + u;
+        const size_t blk = size_t(row) * m.blocks + (u >> 2);
+        const uint32_t c = u & 3;
+        const int8_t* s = reinterpret_cast<const int8_t*>(m.sc) + blk * 16 + (c >> 1) * 8 + (c & 1);
+        W w;
+        w.a = ld_stream(m.qa + i * 16);
+        w.b = ld_stream(m.qb + i * 16);
+        w.c = ld_stream(m.qc + i * 16);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) w.sc[k] = s[2 * k];
+        w.d = __half2float(m.d[blk]);
+        return w;
+    }
+    static __device__ __forceinline__ X loadx(const DevAct& a, uint32_t t, uint32_t u) {
+        const uint32_t sb = u >> 2, c = u & 3;
+        const int8_t* base = a.qk + size_t(t) * a.cols + sb * 256 + (c >> 1) * 128 + (c & 1) * 16;
+        const int16_t* bs = a.bs + size_t(t) * (a.cols / 16) + sb * 16 + (c >> 1) * 8 + (c & 1);
+        X x;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            x.q[k] = *reinterpret_cast<const uint4*>(base + 32 * k);
+            x.bs[k] = bs[2 * k];
+        }
+        x.d = a.dk[size_t(t) * (a.cols / 256) + sb];
+        return x;
+    }
+    static __device__ __forceinline__ int group(uint4 v, uint4 x) {
+        int acc = 0;
+        acc = dp4a(v.x, x.x, acc);
+        acc = dp4a(v.y, x.y, acc);
+        acc = dp4a(v.z, x.z, acc);
+        acc = dp4a(v.w, x.w, acc);
+        return acc;
+    }
+    static __device__ __forceinline__ uint32_t join(uint32_t low, uint32_t high2) { return low | high2; }
+    static __device__ __forceinline__ float term(const W& w, const X& x, bool valid, uint32_t u) {
+        const uint32_t L = 0x0F0F0F0Fu, H = 0x30303030u;
+        uint4 v0 = make_uint4((w.a.x & L) | ((w.c.x << 4) & H), (w.a.y & L) | ((w.c.y << 4) & H), (w.a.z & L) | ((w.c.z << 4) & H), (w.a.w & L) | ((w.c.w << 4) & H));
+        uint4 v1 = make_uint4((w.b.x & L) | ((w.c.x << 2) & H), (w.b.y & L) | ((w.c.y << 2) & H), (w.b.z & L) | ((w.c.z << 2) & H), (w.b.w & L) | ((w.c.w << 2) & H));
+        uint4 v2 = make_uint4(((w.a.x >> 4) & L) | (w.c.x & H), ((w.a.y >> 4) & L) | (w.c.y & H), ((w.a.z >> 4) & L) | (w.c.z & H), ((w.a.w >> 4) & L) | (w.c.w & H));
+        uint4 v3 = make_uint4(((w.b.x >> 4) & L) | ((w.c.x >> 2) & H), ((w.b.y >> 4) & L) | ((w.c.y >> 2) & H), ((w.b.z >> 4) & L) | ((w.c.z >> 2) & H), ((w.b.w >> 4) & L) | ((w.c.w >> 2) & H));
+        int weighted = 0;
+        weighted += w.sc[0] * (group(v0, x.q[0]) - 32 * x.bs[0]);  // (q - 32) * x summed = q*x - 32*sum(x)
+        weighted += w.sc[1] * (group(v1, x.q[1]) - 32 * x.bs[1]);
+        weighted += w.sc[2] * (group(v2, x.q[2]) - 32 * x.bs[2]);
+        weighted += w.sc[3] * (group(v3, x.q[3]) - 32 * x.bs[3]);
+        weighted = valid ? weighted : 0;
+        weighted += __shfl_xor_sync(0xffffffffu, weighted, 1);
+        weighted += __shfl_xor_sync(0xffffffffu, weighted, 2);
+        if (!valid || (u & 3) != 0) return 0.0f;
+        return __fmul_rn(__fmul_rn(x.d, w.d), float(weighted));
+    }
+};
+
+struct FTQ2_0 {
+    static constexpr int kLanesPerTerm = 4;
+    static constexpr bool kExact = true;
+    struct W { uint4 q; float d; };
+    struct X { uint4 q[4]; float d; int bsum; };
+    static __device__ __forceinline__ W loadw(const DevMatrix& m, uint32_t row, uint32_t u) {
+        const size_t i = size_t(row) * m.units + u;
+        return {ld_stream(m.qa + i * 16), __half2float(m.d[size_t(row) * m.blocks + (u >> 2)])};
+    }
+    static __device__ __forceinline__ X loadx(const DevAct& a, uint32_t t, uint32_t u) {
+        const uint32_t sb = u >> 2, c = u & 3;
+        const int8_t* base = a.qk + size_t(t) * a.cols + sb * 256 + (c >> 1) * 128 + (c & 1) * 16;
+        const int16_t* bs = a.bs + size_t(t) * (a.cols / 16) + sb * 16 + (c >> 1) * 8 + (c & 1);
+        X x;
+        x.bsum = 0;
+#pragma unroll
+        for (int l = 0; l < 4; ++l) {
+            x.q[l] = *reinterpret_cast<const uint4*>(base + 32 * l);
+            x.bsum += bs[2 * l];
+        }
+        x.d = a.dk[size_t(t) * (a.cols / 256) + sb];
+        return x;
+    }
+    static __device__ __forceinline__ float term(const W& w, const X& x, bool valid, uint32_t u) {
+        const uint32_t M = 0x03030303u;
+        int acc = 0;
+#pragma unroll
+        for (int l = 0; l < 4; ++l) {
+            acc = dp4a((w.q.x >> (2 * l)) & M, x.q[l].x, acc);
+            acc = dp4a((w.q.y >> (2 * l)) & M, x.q[l].y, acc);
+            acc = dp4a((w.q.z >> (2 * l)) & M, x.q[l].z, acc);
+            acc = dp4a((w.q.w >> (2 * l)) & M, x.q[l].w, acc);
+        }
+        acc = valid ? acc - x.bsum : 0;  // sum((q-1)*x) = sum(q*x) - sum(x)
+        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+        if (!valid || (u & 3) != 0) return 0.0f;
+        return __fmul_rn(__fmul_rn(x.d, w.d), float(acc));
+    }
+};
+
+// Unquantised weights against raw f32 activations (the reference's dot_f32 path for widened F16 tensors).
+struct FF16 {
+    static constexpr int kLanesPerTerm = 1;
+    static constexpr bool kExact = false;
+    struct W { uint4 q; };
+    struct X { float4 a, b; };
+    static __device__ __forceinline__ W loadw(const DevMatrix& m, uint32_t row, uint32_t u) {
+        return {ld_stream(m.qa + (size_t(row) * m.units + u) * 16)};
+    }
+    static __device__ __forceinline__ X loadx(const DevAct& a, uint32_t t, uint32_t u) {
+        const float4* p = reinterpret_cast<const float4*>(a.f32 + size_t(t) * a.cols + u * 8);
+        return {p[0], p[1]};
+    }
+    static __device__ __forceinline__ float term(const W& w, const X& x, bool valid, uint32_t) {
+        const __half2* h = reinterpret_cast<const __half2*>(&w.q);
+        const float2 f0 = __half22float2(h[0]), f1 = __half22float2(h[1]), f2 = __half22float2(h[2]), f3 = __half22float2(h[3]);
+        float s = __fmul_rn(f0.x, x.a.x);
+        s = fmaf(f0.y, x.a.y, s);
+        s = fmaf(f1.x, x.a.z, s);
+        s = fmaf(f1.y, x.a.w, s);
+        s = fmaf(f2.x, x.b.x, s);
+        s = fmaf(f2.y, x.b.y, s);
+        s = fmaf(f3.x, x.b.z, s);
+        s = fmaf(f3.y, x.b.w, s);
+        return valid ? s : 0.0f;
+    }
+};
+
+struct FF32 {
+    static constexpr int kLanesPerTerm = 1;
+    static constexpr bool kExact = false;
+    struct W { float4 q; };
+    struct X { float4 a; };
+    static __device__ __forceinline__ W loadw(const DevMatrix& m, uint32_t row, uint32_t u) {
+        const uint4 v = ld_stream(m.qa + (size_t(row) * m.units + u) * 16);
+        return {make_float4(__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w))};
+    }
+    static __device__ __forceinline__ X loadx(const DevAct& a, uint32_t t, uint32_t u) {
+        return {*reinterpret_cast<const float4*>(a.f32 + size_t(t) * a.cols + u * 4)};
+    }
+    static __device__ __forceinline__ float term(const W& w, const X& x, bool valid, uint32_t) {
+        float s = __fmul_rn(w.q.x, x.a.x);
+        s = fmaf(w.q.y, x.a.y, s);
+        s = fmaf(w.q.z, x.a.z, s);
+        s = fmaf(w.q.w, x.a.w, s);
+        return valid ? s : 0.0f;
+    }
+};
+
+__device__ __forceinline__ float silu_mul(float g, float u) {
+    // gate / (1 + exp(-gate)) * up, as silu_mul_f32 (src/kernels_f32.cpp:287-289)
+    return __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, exact_expf(-g))), u);
+}
+__device__ __forceinline__ float relu2_mul(float g, float u) {
+    const float r = fmaxf(g, 0.0f);  // src/model.cpp:1135-1138
+    return __fmul_rn(__fmul_rn(r, r), u);
+}
+
+}  // namespace bk

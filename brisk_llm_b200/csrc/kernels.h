@@ -91,13 +91,24 @@ struct AttnArgs {
 size_t attn_scratch_floats(uint32_t n, uint32_t heads, uint32_t max_context);
 void launch_attention(const AttnArgs& a, cudaStream_t s);
 
+// ---- fused single-token step (decode.cu) -------------------------------------------------------------------------
+// One multiply of the decode step: every CTA rebuilds the activation row in shared memory (x, optionally RMS-normed with
+// norm_weight, then quantised the way the targets' type takes it) and multiplies its rows. Launched with programmatic
+// dependent launch: weights are prefetched while the previous kernel drains. `sms` sizes the persistent grid.
+void launch_dec_multiply(const MatTarget* targets, int count, const float* x, const float* norm_weight, float eps, uint32_t cols, Epilogue epi,
+                         uint32_t sms, cudaStream_t s, unsigned long long* trace = nullptr);
+// Attention of the single new token: scores kernel (per-head norm + RoPE of q and the new k, f16 K/V store in its
+// prologue) and softmax + weighted-sum kernel. Takes the same argument structs as the batched kernels (n is 1).
+void launch_dec_attention(const RopeArgs& r, const AttnArgs& at, cudaStream_t s);
+
 // First maximum of each of n rows of logits[n][vocab] (lowest index on ties) -> out_token[n].
 // If next_token/position are given (single row), also feeds the decode loop: *next_token = argmax, *position += 1,
 // and appends the token to history[*history_len++].
 void launch_argmax(const float* logits, uint32_t vocab, uint32_t n, int32_t* out_token, float* scratch_val,
                    int32_t* scratch_idx, cudaStream_t s);
 size_t argmax_scratch_elems(uint32_t vocab);
-void launch_advance(int32_t* token_slot, const int32_t* chosen, uint32_t* position, int32_t* history, uint32_t* history_len,
-                    cudaStream_t s);
+// Arg-max of one row that also feeds the decode loop: *token_slot = choice, *position += 1, history[(*history_len)++] = choice.
+void launch_argmax_advance(const float* logits, uint32_t vocab, int32_t* out_token, float* scratch_val, int32_t* scratch_idx,
+                           int32_t* token_slot, uint32_t* position, int32_t* history, uint32_t* history_len, cudaStream_t s);
 
 }  // namespace bk

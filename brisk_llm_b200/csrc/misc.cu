@@ -2,6 +2,7 @@
 // split-position attention with a combine pass, and the greedy arg-max that keeps decoding on the device.
 #include <cstdio>
 #include <string>
+#include <utility>
 
 #include "exact_math.h"
 #include "kernels.h"
@@ -9,9 +10,28 @@
 namespace bk {
 namespace {
 
+// No-op unless the kernel was launched as a programmatic dependent of its predecessor (the decode step does that).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <class... Params, class... Args>
+void launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    BK_CUDA(cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...));
+}
+
 // ---- embedding: one token row of the embedding matrix, decoded exactly like the reference's dequantize_*
 // (src/quant.cpp:196-307, :565-578; embedding_row, src/model.cpp:27-70), read from the repacked planes. ----
-__global__ void embed_kernel(const DevMatrix m, const int32_t* __restrict__ tokens, float* __restrict__ hidden) {
+__global__ void embed_kernel(const DevMatrix m, const int32_t* tokens, float* __restrict__ hidden) {
+    pdl_wait();
     const uint32_t t = blockIdx.x;
     const uint32_t row = uint32_t(tokens[t]);
     float* out = hidden + size_t(t) * m.cols;
@@ -264,7 +284,8 @@ __device__ __forceinline__ void better(float& v, int32_t& i, float ov, int32_t o
     }
 }
 
-__global__ void __launch_bounds__(256) argmax_stage1(const float* __restrict__ logits, uint32_t vocab, float* pv, int32_t* pi) {
+__global__ void __launch_bounds__(256) argmax_stage1(const float* logits, uint32_t vocab, float* pv, int32_t* pi) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // no-op unless launched as a programmatic dependent
     const uint32_t row = blockIdx.y;
     const float* x = logits + size_t(row) * vocab;
     float v = -INFINITY;
@@ -286,7 +307,9 @@ __global__ void __launch_bounds__(256) argmax_stage1(const float* __restrict__ l
     }
 }
 
-__global__ void __launch_bounds__(256) argmax_stage2(const float* pv, const int32_t* pi, int32_t* out) {
+__global__ void __launch_bounds__(256) argmax_stage2(const float* pv, const int32_t* pi, int32_t* out, int32_t* token_slot, uint32_t* position,
+                                                     int32_t* history, uint32_t* history_len) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t row = blockIdx.x;
     float v = -INFINITY;
     int32_t idx = 0x7fffffff;
@@ -306,26 +329,21 @@ __global__ void __launch_bounds__(256) argmax_stage2(const float* pv, const int3
     if (threadIdx.x == 0) {
         for (int w = 1; w < 8; ++w) better(v, idx, sv[w], si[w]);
         out[row] = idx;
+        if (token_slot != nullptr) {  // feed the decode loop: next input token, next position, history
+            *token_slot = idx;
+            *position += 1;
+            if (history != nullptr) {
+                history[*history_len] = idx;
+                *history_len += 1;
+            }
+        }
     }
 }
 
-namespace {
 
-__global__ void advance_kernel(int32_t* token_slot, const int32_t* chosen, uint32_t* position, int32_t* history, uint32_t* history_len) {
-    const int32_t tok = *chosen;
-    *token_slot = tok;
-    *position += 1;
-    if (history != nullptr) {
-        history[*history_len] = tok;
-        *history_len += 1;
-    }
-}
-
-}  // namespace
 
 void launch_embed(const DevMatrix& embd, const int32_t* tokens_dev, uint32_t n, float* hidden, cudaStream_t s) {
-    embed_kernel<<<n, 128, 0, s>>>(embd, tokens_dev, hidden);
-    BK_CUDA(cudaGetLastError());
+    launch_pdl(embed_kernel, dim3(n), dim3(128), 0, s, embd, tokens_dev, hidden);
 }
 
 void launch_qk_norm_rope_store(const RopeArgs& a, cudaStream_t s) {
@@ -361,8 +379,15 @@ void launch_argmax(const float* logits, uint32_t vocab, uint32_t n, int32_t* out
                    cudaStream_t s) {
     argmax_stage1<<<dim3(kArgmaxBlocks, n), 256, 0, s>>>(logits, vocab, scratch_val, scratch_idx);
     BK_CUDA(cudaGetLastError());
-    argmax_stage2<<<n, 256, 0, s>>>(scratch_val, scratch_idx, out_token);
+    argmax_stage2<<<n, 256, 0, s>>>(scratch_val, scratch_idx, out_token, nullptr, nullptr, nullptr, nullptr);
     BK_CUDA(cudaGetLastError());
+}
+
+void launch_argmax_advance(const float* logits, uint32_t vocab, int32_t* out_token, float* scratch_val, int32_t* scratch_idx,
+                           int32_t* token_slot, uint32_t* position, int32_t* history, uint32_t* history_len, cudaStream_t s) {
+    launch_pdl(argmax_stage1, dim3(kArgmaxBlocks, 1), dim3(256), 0, s, logits, vocab, scratch_val, scratch_idx);
+    launch_pdl(argmax_stage2, dim3(1), dim3(256), 0, s, (const float*)scratch_val, (const int32_t*)scratch_idx, out_token, token_slot, position,
+               history, history_len);
 }
 
 }  // namespace bk
@@ -407,7 +432,7 @@ extern "C" int brisk_cuda_argmax_static(const float* logits, uint32_t vocab, uin
     // Stage 1 writes every pair stage 2 reads for these rows, so nothing of the previous call has to be cleared.
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     bk::argmax_stage1<<<dim3(bk::kArgmaxBlocks, rows), 256, 0, s>>>(logits, vocab, partial_value, partial_index);
-    bk::argmax_stage2<<<rows, 256, 0, s>>>(partial_value, partial_index, out_tokens);
+    bk::argmax_stage2<<<rows, 256, 0, s>>>(partial_value, partial_index, out_tokens, nullptr, nullptr, nullptr, nullptr);
     e = cudaGetLastError();
     if (e != cudaSuccess) return fail(std::string("cuda: arg-max launch failed: ") + cudaGetErrorString(e));
     return 0;
@@ -415,10 +440,5 @@ extern "C" int brisk_cuda_argmax_static(const float* logits, uint32_t vocab, uin
 
 namespace bk {
 
-void launch_advance(int32_t* token_slot, const int32_t* chosen, uint32_t* position, int32_t* history, uint32_t* history_len,
-                    cudaStream_t s) {
-    advance_kernel<<<1, 1, 0, s>>>(token_slot, chosen, position, history, history_len);
-    BK_CUDA(cudaGetLastError());
-}
 
 }  // namespace bk

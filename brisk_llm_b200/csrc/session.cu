@@ -4,6 +4,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <string>
@@ -56,6 +57,7 @@ struct Session {
     uint64_t max_context = 0;
     float eps = 0, rope_base = 0;
     int arch = 0, neox = 1, device = 0;
+    uint32_t sms = 148;
     uint32_t flags = 0;
 
     // weights
@@ -67,7 +69,7 @@ struct Session {
 
     // state and scratch
     DevBuffer kv, rope, tokens_dev, scalars, hidden_b, q_b, k_b, v_b, attended_b, ffn_b, logits_b, actf, actq0, actd0, acts0, actqk,
-        actdk, actbs, partial, am_val, am_idx, history, logit_history;
+        actdk, actbs, partial, am_val, am_idx, history, logit_history, trace;
     DevActMut act;
     float* logits_host = nullptr;     // pinned [64][vocab]
     int32_t* tokens_host = nullptr;   // pinned [kMaxBatch + 4]
@@ -151,6 +153,11 @@ struct Session {
         kv_dim = kv_heads * head_dim;
         max_context = opt.max_context == 0 ? m.context_length : std::min<uint64_t>(opt.max_context, m.context_length);
 
+        {
+            int count = 0;
+            BK_CUDA(cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, opt.device));
+            sms = uint32_t(count);
+        }
         BK_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
         BK_CUDA(cudaEventCreate(&ev0));
         BK_CUDA(cudaEventCreate(&ev1));
@@ -236,6 +243,10 @@ struct Session {
         am_val.alloc(argmax_scratch_elems(vocab) * 4);
         am_idx.alloc(argmax_scratch_elems(vocab) * 4);
         history.alloc((max_context + 1) * sizeof(int32_t));
+        if (std::getenv("BRISK_CUDA_TRACE") != nullptr) {  // per-kernel phase time stamps of the decode multiplies
+            trace.alloc(512 * 8 * sizeof(unsigned long long));
+            BK_CUDA(cudaMemsetAsync(trace.p, 0, trace.bytes, stream));
+        }
         BK_CUDA(cudaMallocHost(&logits_host, size_t(kMaxScored) * vocab * sizeof(float)));
         BK_CUDA(cudaMallocHost(&tokens_host, (kMaxBatch + 4) * sizeof(int32_t)));
         BK_CUDA(cudaStreamSynchronize(stream));
@@ -337,13 +348,56 @@ struct Session {
         multiply({{head, logits_b.as<float>(), vocab}}, a, rows, EPI_STORE);
     }
 
+    // The single-token step through the fused kernels of decode.cu (six per layer).
+    void forward_decode() {
+        float* hid = hidden_b.as<float>();
+        launch_embed(embd, tokens_dev.as<int32_t>(), 1, hid, stream);
+        ++launches;
+        const float attn_scale = 1.0f / std::sqrt(static_cast<float>(head_dim));
+        unsigned long long* tr = trace.p ? trace.as<unsigned long long>() : nullptr;
+        uint32_t slot = 0;
+        auto fused = [&](std::vector<MatTarget> targets, const float* x, const float* w, uint32_t cols, Epilogue epi) {
+            unsigned long long* t = tr ? tr + 8 * (slot++ % 512) : nullptr;
+            if (epi == EPI_SILU_MUL || epi == EPI_RELU2_MUL) {
+                launch_dec_multiply(targets.data(), int(targets.size()), x, w, eps, cols, epi, sms, stream, t);
+                ++launches;
+                return;
+            }
+            while (!targets.empty()) {  // one launch per weight type among the targets
+                std::vector<MatTarget> same, rest;
+                for (const MatTarget& t : targets) (t.m.type == targets[0].m.type ? same : rest).push_back(t);
+                launch_dec_multiply(same.data(), int(same.size()), x, w, eps, cols, epi, sms, stream, t);
+                ++launches;
+                targets.swap(rest);
+            }
+        };
+        for (uint32_t l = 0; l < n_layers; ++l) {
+            const Layer& L = layers[l];
+            fused({{L.q, q_b.as<float>(), q_dim}, {L.k, k_b.as<float>(), kv_dim}, {L.v, v_b.as<float>(), kv_dim}}, hid, L.attn_norm, hidden, EPI_STORE);
+            RopeArgs r{};
+            r.q = q_b.as<float>(); r.k = k_b.as<float>(); r.v = v_b.as<float>();
+            r.q_norm = L.q_norm; r.k_norm = L.k_norm; r.rope = rope.as<float>();
+            r.k_cache = L.k_cache; r.v_cache = L.v_cache; r.position = d_position();
+            r.n = 1; r.heads = heads; r.kv_heads = kv_heads; r.dim = head_dim; r.max_context = uint32_t(max_context);
+            r.eps = eps; r.neox = neox;
+            AttnArgs at{};
+            at.out = attended_b.as<float>(); at.scores = partial.as<float>(); at.scale = attn_scale;
+            launch_dec_attention(r, at, stream);
+            launches += 2;
+            fused({{L.o, hid, hidden}}, attended_b.as<float>(), L.attn_sub_norm, q_dim, EPI_ADD);
+            fused({{L.gate, ffn_b.as<float>(), ffn}, {L.up, nullptr, ffn}}, hid, L.ffn_norm, hidden, arch == BRISK_ARCH_BITNET ? EPI_RELU2_MUL : EPI_SILU_MUL);
+            fused({{L.down, hid, hidden}}, ffn_b.as<float>(), L.ffn_sub_norm, ffn, EPI_ADD);
+        }
+        fused({{head, logits_b.as<float>(), vocab}}, hid, output_norm, hidden, EPI_STORE);
+    }
+
     void build_step_graph() {
         if (step_graph != nullptr || (flags & BRISK_CUDA_FLAG_NO_GRAPH)) return;
         const uint64_t before = launches;
         cudaGraph_t graph = nullptr;
         BK_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
         try {
-            forward(1, false, uint32_t(max_context));
+            forward_decode();
         } catch (...) {
             cudaStreamEndCapture(stream, &graph);
             if (graph) cudaGraphDestroy(graph);
@@ -358,8 +412,10 @@ struct Session {
     }
 
     void step_on_device() {  // one token whose id is tokens_dev[0] at *d_position()
-        if (flags & BRISK_CUDA_FLAG_NO_GRAPH) {
-            forward(1, false, uint32_t(max_context));
+        if (flags & BRISK_CUDA_FLAG_NO_MEGAKERNEL) {
+            forward(1, false, uint32_t(max_context));  // the batched kernels, one token
+        } else if (flags & BRISK_CUDA_FLAG_NO_GRAPH) {
+            forward_decode();
         } else {
             build_step_graph();
             BK_CUDA(cudaGraphLaunch(step_graph, stream));
@@ -439,9 +495,9 @@ struct Session {
             if (out_logits != nullptr) {
                 BK_CUDA(cudaMemcpyAsync(logit_history.as<float>() + i * vocab, logits_b.p, size_t(vocab) * sizeof(float), cudaMemcpyDeviceToDevice, stream));
             }
-            launch_argmax(logits_b.as<float>(), vocab, 1, d_chosen(), am_val.as<float>(), am_idx.as<int32_t>(), stream);
-            launch_advance(tokens_dev.as<int32_t>(), d_chosen(), d_position(), history.as<int32_t>(), d_history_len(), stream);
-            launches += 3;
+            launch_argmax_advance(logits_b.as<float>(), vocab, d_chosen(), am_val.as<float>(), am_idx.as<int32_t>(), tokens_dev.as<int32_t>(),
+                                  d_position(), history.as<int32_t>(), d_history_len(), stream);
+            launches += 2;
         }
         BK_CUDA(cudaEventRecord(ev1, stream));
         BK_CUDA(cudaMemcpyAsync(out_tokens, history.p, steps * sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
@@ -567,6 +623,14 @@ int brisk_cuda_debug_buffer(brisk_cuda_session* session, const char* name, float
         BK_CUDA(cudaStreamSynchronize(s.stream));
         BK_CUDA(cudaMemcpy(out, b->p, count * sizeof(float), cudaMemcpyDeviceToHost));
     });
+}
+
+// Not part of the header: prints the phase stamps gathered with BRISK_CUDA_TRACE=1 (development aid).
+int brisk_cuda_dump_trace(brisk_cuda_session* session, unsigned long long* out, uint64_t count) {
+    bk::Session& s = session->s;
+    if (s.trace.p == nullptr || count * 8 > s.trace.bytes) return -1;
+    cudaStreamSynchronize(s.stream);
+    return cudaMemcpy(out, s.trace.p, count * 8, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -1;
 }
 
 int brisk_cuda_tp_unique_id(void* out128, char* err, size_t errlen) {

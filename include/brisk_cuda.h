@@ -104,7 +104,7 @@ typedef struct brisk_cuda_options {
 } brisk_cuda_options;
 
 #define BRISK_CUDA_FLAG_NO_GRAPH 1u      /* launch decode kernels one by one instead of replaying a CUDA graph */
-#define BRISK_CUDA_FLAG_NO_MEGAKERNEL 2u /* decode through per-operation kernels only                         */
+#define BRISK_CUDA_FLAG_NO_MEGAKERNEL 2u /* single-token steps through the batched kernels instead of the fused ones */
 
 typedef struct brisk_cuda_session brisk_cuda_session;
 
