@@ -56,6 +56,9 @@ void launch_matvec(const MatTarget* targets, int count, const DevAct& act, uint3
 // Same contract as launch_matvec for n >= 16 tokens; returns false when this type/shape has no tensor kernel
 // (the caller then uses launch_matvec).
 bool launch_gemm(const MatTarget* targets, int count, const DevAct& act, uint32_t n, Epilogue epi, cudaStream_t s);
+bool gemm_supports(int type, uint32_t cols);
+// gate[i] = silu(gate[i]) * up[i] (relu2: max(gate[i],0)^2 * up[i]) - the activation after separate gate and up GEMMs.
+void launch_gate_mul(float* gate, const float* up, size_t count, bool relu2, cudaStream_t s);
 
 // ---- per-token vector work (misc.cu) -----------------------------------------------------------
 // hidden[t][:] = dequantised row tokens[t] of the embedding matrix (Session::eval_batch's embedding_row).

@@ -178,7 +178,17 @@ void dispatch(Params& p, bool pair, uint32_t n, cudaStream_t s) {
     }
 }
 
+__global__ void gate_mul_kernel(float* gate, const float* up, size_t count, int relu2) {
+    const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < count) gate[i] = relu2 ? relu2_mul(gate[i], up[i]) : silu_mul(gate[i], up[i]);
+}
+
 }  // namespace
+
+void launch_gate_mul(float* gate, const float* up, size_t count, bool relu2, cudaStream_t s) {
+    gate_mul_kernel<<<unsigned((count + 255) / 256), 256, 0, s>>>(gate, up, count, relu2 ? 1 : 0);
+    BK_CUDA(cudaGetLastError());
+}
 
 void launch_matvec(const MatTarget* targets, int count, const DevAct& act, uint32_t n, Epilogue epi, cudaStream_t s) {
     const bool pair = epi == EPI_SILU_MUL || epi == EPI_RELU2_MUL;

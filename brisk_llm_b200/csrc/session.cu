@@ -68,7 +68,7 @@ struct Session {
     uint64_t weight_bytes = 0, kv_bytes = 0;
 
     // state and scratch
-    DevBuffer kv, rope, tokens_dev, scalars, hidden_b, q_b, k_b, v_b, attended_b, ffn_b, logits_b, actf, actq0, actd0, acts0, actqk,
+    DevBuffer kv, rope, tokens_dev, scalars, hidden_b, q_b, k_b, v_b, attended_b, ffn_b, up_b, logits_b, actf, actq0, actd0, acts0, actqk,
         actdk, actbs, partial, am_val, am_idx, history, logit_history, trace;
     DevActMut act;
     float* logits_host = nullptr;     // pinned [64][vocab]
@@ -229,6 +229,7 @@ struct Session {
         v_b.alloc(size_t(kMaxBatch) * kv_dim * 4);
         attended_b.alloc(size_t(kMaxBatch) * q_dim * 4);
         ffn_b.alloc(size_t(kMaxBatch) * ffn * 4);
+        up_b.alloc(size_t(kMaxBatch) * ffn * 4);
         logits_b.alloc(size_t(kMaxScored) * vocab * 4);
         actf.alloc(size_t(kMaxBatch) * widest * 4);
         actq0.alloc(size_t(kMaxBatch) * widest);
@@ -276,9 +277,16 @@ struct Session {
     void multiply(std::vector<MatTarget> targets, const DevAct& a, uint32_t n, Epilogue epi) {
         const bool pair = epi == EPI_SILU_MUL || epi == EPI_RELU2_MUL;
         if (pair) {
-            if (!(n >= 16 && launch_gemm(targets.data(), int(targets.size()), a, n, epi, stream))) {
-                launch_matvec(targets.data(), int(targets.size()), a, n, epi, stream);
+            if (n >= 16 && gemm_supports(targets[0].m.type, targets[0].m.cols)) {
+                // prompt batches: gate and up as two tensor-core multiplies, then the activation elementwise
+                MatTarget gate{targets[0].m, targets[0].out, targets[0].ldo}, up{targets[1].m, up_b.as<float>(), targets[0].ldo};
+                launch_gemm(&gate, 1, a, n, EPI_STORE, stream);
+                launch_gemm(&up, 1, a, n, EPI_STORE, stream);
+                launch_gate_mul(targets[0].out, up_b.as<float>(), size_t(n) * targets[0].ldo, epi == EPI_RELU2_MUL, stream);
+                launches += 3;
+                return;
             }
+            launch_matvec(targets.data(), int(targets.size()), a, n, epi, stream);
             launches += (n + kMaxSmallBatch - 1) / kMaxSmallBatch;
             return;
         }
@@ -290,7 +298,7 @@ struct Session {
                 launch_matvec(same.data(), int(same.size()), a, n, epi, stream);
                 launches += (n + kMaxSmallBatch - 1) / kMaxSmallBatch;
             } else {
-                ++launches;
+                launches += same.size();
             }
             targets.swap(rest);
         }
