@@ -56,7 +56,7 @@ void launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, c
 }
 
 // ---- multiply ---------------------------------------------------------------------------------------------------
-constexpr int kDecWarps = 8;
+constexpr int kDecWarps = 16;  // the per-CTA prologue (norm + quantise) is shared by more warps, and there are fewer CTAs to repeat it
 
 struct DecMatParams {
     DevMatrix m[3];
@@ -77,17 +77,16 @@ __device__ __forceinline__ void stamp(unsigned long long* trace, int slot) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
         trace[slot] = t;
-        if (slot == 0) trace[6] = (unsigned long long)clock64();
-        if (slot == 5) trace[7] = (unsigned long long)clock64();
+
     }
 }
 
-template <class F, int RW, bool PAIR>
+template <class F, int RW, bool PAIR, int kDepth>
 __global__ void __launch_bounds__(kDecWarps * 32) dec_matvec_kernel(const DecMatParams p) {
     constexpr int MATS = PAIR ? 2 : 1;
     constexpr int CHAINS = MATS * RW;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    __shared__ float tile[F::kExact ? kDecWarps : 1][F::kExact ? CHAINS : 1][33];
+    __shared__ __align__(16) float tile[F::kExact ? kDecWarps : 1][F::kExact ? CHAINS : 1][36];
     __shared__ double red[32];
 
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -118,10 +117,27 @@ __global__ void __launch_bounds__(kDecWarps * 32) dec_matvec_kernel(const DecMat
 
     stamp(p.trace, 0);
     // Weights (and the norm weights) do not depend on the previous kernel: get them in flight before waiting for it.
-    typename F::W wnext[MATS][RW];
+    // A ring of kDepth iterations of weights per lane, refilled in iteration order: kDepth = 1 for the layer matrices
+    // (a warp has one to three iterations), deeper for long walks (the output head, 7B-class layers) so that enough
+    // bytes are in flight per SM to cover HBM latency.
+    typename F::W wq[kDepth][MATS][RW];
     const bool any = first < total_groups;
-    if (any) load_weights(first, 0, wnext);
-    constexpr int kNormPrefetch = 8;  // norm weights held in registers: covers rows up to 2048 values
+    const uint32_t my_groups = any ? (total_groups - first + stride - 1) / stride : 0;
+    const uint32_t my_iters = my_groups * steps;
+    uint32_t agroup = first, astep = 0, issued = 0;  // the next iteration to load
+    auto issue = [&](typename F::W (&slot)[MATS][RW]) {
+        if (issued < my_iters) {
+            load_weights(agroup, astep, slot);
+            ++issued;
+            if (++astep == steps) {
+                astep = 0;
+                agroup += stride;
+            }
+        }
+    };
+#pragma unroll
+    for (int d = 0; d < kDepth; ++d) issue(wq[d]);
+    constexpr int kNormPrefetch = 4;  // norm weights held in registers: covers rows up to 2048 values
     float nw[kNormPrefetch];
     const uint32_t cols = p.cols;
     if (p.weight != nullptr) {
@@ -134,21 +150,57 @@ __global__ void __launch_bounds__(kDecWarps * 32) dec_matvec_kernel(const DecMat
     if (p.pdl == 1) pdl_launch_dependents();
     pdl_wait();
     stamp(p.trace, 1);
+    if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {  // tracing only: latency of one dependent load
+        const float probe = *reinterpret_cast<const volatile float*>(p.x);
+        if (probe == 123456.0f) p.trace[7] = 0;
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        p.trace[6] = t;
+    }
 
     // Prologue: the activation row in shared memory - f32 (normed), then the planes this format multiplies by.
+    // Loads are batched in registers (8 per thread in flight) so that their latencies overlap.
     float* xf = reinterpret_cast<float*>(smem_raw);
-    for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) xf[i] = p.x[i];
-    if (p.weight != nullptr) {
-        __syncthreads();
-        stamp(p.trace, 2);
-        const float scale = cta_rms_scale(xf, cols, p.eps, red);
+    constexpr uint32_t kT = kDecWarps * 32;
+    if (cols <= 8 * kT) {
+        float xv[8];
 #pragma unroll
-        for (int k = 0; k < kNormPrefetch; ++k) {
-            const uint32_t i = threadIdx.x + k * (kDecWarps * 32);
-            if (i < cols) xf[i] = __fmul_rn(__fmul_rn(xf[i], scale), nw[k]);
+        for (int k = 0; k < 8; ++k) {
+            const uint32_t i = threadIdx.x + k * kT;
+            xv[k] = i < cols ? p.x[i] : 0.0f;
         }
-        for (uint32_t i = threadIdx.x + kNormPrefetch * (kDecWarps * 32); i < cols; i += blockDim.x) {
-            xf[i] = __fmul_rn(__fmul_rn(xf[i], scale), p.weight[i]);
+        if (p.weight != nullptr) {
+            double part = 0.0;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) part += double(__fmul_rn(xv[k], xv[k]));  // padding adds exact zeros
+            part = warp_sum(part);
+            if (lane == 0) red[warp] = part;
+            __syncthreads();
+            double total = 0.0;
+#pragma unroll
+            for (int w = 0; w < kDecWarps; ++w) total += red[w];
+            const float mean = float(total / double(cols));
+            const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, p.eps)));
+            stamp(p.trace, 2);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const uint32_t i = threadIdx.x + k * kT;
+                if (i < cols) xf[i] = __fmul_rn(__fmul_rn(xv[k], scale), k < kNormPrefetch ? nw[k] : p.weight[i]);
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const uint32_t i = threadIdx.x + k * kT;
+                if (i < cols) xf[i] = xv[k];
+            }
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < cols; i += kT) xf[i] = p.x[i];
+        if (p.weight != nullptr) {
+            __syncthreads();
+            const float scale = cta_rms_scale(xf, cols, p.eps, red);
+            stamp(p.trace, 2);
+            for (uint32_t i = threadIdx.x; i < cols; i += kT) xf[i] = __fmul_rn(__fmul_rn(xf[i], scale), p.weight[i]);
         }
     }
     __syncthreads();
@@ -182,85 +234,95 @@ __global__ void __launch_bounds__(kDecWarps * 32) dec_matvec_kernel(const DecMat
 #pragma unroll
         for (int r = 0; r < RW; ++r) acc[a][r] = 0.0f;
 
-    uint32_t group = first, step = 0;
     float old = 0.0f;  // the residual value a chain lane adds to (EPI_ADD), fetched while the row is being multiplied
-    while (true) {
-        if (F::kExact && !PAIR && step == 0 && p.epi == EPI_ADD && lane < RW) {
-            int target;
-            uint32_t row0;
-            locate(group, target, row0);
-            if (row0 + lane < p.m[target].rows) old = p.out[target][row0 + lane];
-        }
-        typename F::W w[MATS][RW];
+    uint32_t group = first, step = 0;
+    for (uint32_t it0 = 0; it0 < my_iters; it0 += kDepth) {
 #pragma unroll
-        for (int a = 0; a < MATS; ++a)
+        for (int d = 0; d < kDepth; ++d) {
+            const uint32_t it = it0 + d;
+            if (it >= my_iters) break;
+            if (F::kExact && !PAIR && step == 0 && p.epi == EPI_ADD && lane < RW) {
+                int target;
+                uint32_t row0;
+                locate(group, target, row0);
+                if (row0 + lane < p.m[target].rows) old = p.out[target][row0 + lane];
+            }
+            typename F::W w[MATS][RW];
 #pragma unroll
-            for (int r = 0; r < RW; ++r) w[a][r] = wnext[a][r];
-        // next iteration's weights, one step ahead
-        uint32_t ngroup = group, nstep = step + 1;
-        if (nstep == steps) {
-            nstep = 0;
-            ngroup = group + stride;
-        }
-        const bool more = ngroup < total_groups;
-        if (more) load_weights(ngroup, nstep, wnext);
+            for (int a = 0; a < MATS; ++a)
+#pragma unroll
+                for (int r = 0; r < RW; ++r) w[a][r] = wq[d][a][r];
+            issue(wq[d]);  // refill this slot with the iteration kDepth later
 
-        const uint32_t u = step * 32 + lane;
-        const bool valid = u < units;
-        const uint32_t uu = valid ? u : 0;
-        const typename F::X x = F::loadx(act, 0, uu);
+            const uint32_t u = step * 32 + lane;
+            const bool valid = u < units;
+            const uint32_t uu = valid ? u : 0;
+            const typename F::X x = F::loadx(act, 0, uu);
 #pragma unroll
-        for (int a = 0; a < MATS; ++a)
-#pragma unroll
-            for (int r = 0; r < RW; ++r) {
-                const float term = F::term(w[a][r], x, valid, uu);
-                if constexpr (F::kExact) tile[warp][a * RW + r][lane] = term;
-                else acc[a][r] = __fadd_rn(acc[a][r], term);
-            }
-        if constexpr (F::kExact) {
-            __syncwarp();
-            if (lane < CHAINS) {
-                const int cnt = int(min(32u, units - step * 32));
-                const float* mine = tile[warp][lane];
-#pragma unroll 8
-                for (int j = 0; j < cnt; j += F::kLanesPerTerm) run = __fadd_rn(run, mine[j]);
-            }
-            __syncwarp();
-        }
-        if (step + 1 == steps) {  // the group's rows are complete
-            int target;
-            uint32_t row0;
-            locate(group, target, row0);
-            const DevMatrix& m = p.m[target];
-            float* outp = p.out[PAIR ? 0 : target];
-            if constexpr (F::kExact) {
-                const float other = PAIR ? __shfl_down_sync(0xffffffffu, run, RW) : 0.0f;
-                if (lane < RW && row0 + lane < m.rows) {
-                    float* o = outp + row0 + lane;
-                    if (PAIR) *o = p.epi == EPI_SILU_MUL ? silu_mul(run, other) : relu2_mul(run, other);
-                    else if (p.epi == EPI_ADD) *o = __fadd_rn(old, run);
-                    else *o = run;
-                }
-                run = 0.0f;
-            } else {
+            for (int a = 0; a < MATS; ++a)
 #pragma unroll
                 for (int r = 0; r < RW; ++r) {
-                    const float v0 = warp_sum(acc[0][r]);
-                    const float v1 = PAIR ? warp_sum(acc[MATS - 1][r]) : 0.0f;
-                    if (lane == 0 && row0 + r < m.rows) {
-                        float* o = outp + row0 + r;
-                        if (PAIR) *o = p.epi == EPI_SILU_MUL ? silu_mul(v0, v1) : relu2_mul(v0, v1);
-                        else if (p.epi == EPI_ADD) *o = __fadd_rn(*o, v0);
-                        else *o = v0;
+                    const float term = F::term(w[a][r], x, valid, uu);
+                    if constexpr (F::kExact) tile[warp][a * RW + r][lane] = term;
+                    else acc[a][r] = __fadd_rn(acc[a][r], term);
+                }
+            if constexpr (F::kExact) {
+                __syncwarp();
+                if (lane < CHAINS) {
+                    const int cnt = int(min(32u, units - step * 32));
+                    const float4* mine = reinterpret_cast<const float4*>(tile[warp][lane]);
+                    float v[32];  // all of the step's terms first, then the serial adds
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 q = mine[j];
+                        v[4 * j] = q.x; v[4 * j + 1] = q.y; v[4 * j + 2] = q.z; v[4 * j + 3] = q.w;
                     }
-                    acc[0][r] = 0.0f;
-                    acc[MATS - 1][r] = 0.0f;
+                    if (cnt == 32) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += F::kLanesPerTerm) run = __fadd_rn(run, v[j]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j += F::kLanesPerTerm) run = j < cnt ? __fadd_rn(run, v[j]) : run;
+                    }
+                }
+                __syncwarp();
+            }
+            if (step + 1 == steps) {  // the group's rows are complete
+                int target;
+                uint32_t row0;
+                locate(group, target, row0);
+                const DevMatrix& m = p.m[target];
+                float* outp = p.out[PAIR ? 0 : target];
+                if constexpr (F::kExact) {
+                    const float other = PAIR ? __shfl_down_sync(0xffffffffu, run, RW) : 0.0f;
+                    if (lane < RW && row0 + lane < m.rows) {
+                        float* o = outp + row0 + lane;
+                        if (PAIR) *o = p.epi == EPI_SILU_MUL ? silu_mul(run, other) : relu2_mul(run, other);
+                        else if (p.epi == EPI_ADD) *o = __fadd_rn(old, run);
+                        else *o = run;
+                    }
+                    run = 0.0f;
+                } else {
+#pragma unroll
+                    for (int r = 0; r < RW; ++r) {
+                        const float v0 = warp_sum(acc[0][r]);
+                        const float v1 = PAIR ? warp_sum(acc[MATS - 1][r]) : 0.0f;
+                        if (lane == 0 && row0 + r < m.rows) {
+                            float* o = outp + row0 + r;
+                            if (PAIR) *o = p.epi == EPI_SILU_MUL ? silu_mul(v0, v1) : relu2_mul(v0, v1);
+                            else if (p.epi == EPI_ADD) *o = __fadd_rn(*o, v0);
+                            else *o = v0;
+                        }
+                        acc[0][r] = 0.0f;
+                        acc[MATS - 1][r] = 0.0f;
+                    }
                 }
             }
+            if (++step == steps) {
+                step = 0;
+                group += stride;
+            }
         }
-        if (!more) break;
-        group = ngroup;
-        step = nstep;
     }
     stamp(p.trace, 5);
 }
@@ -275,15 +337,26 @@ void launch_dec_one(DecMatParams& p, uint32_t sms, cudaStream_t s) {
     }
     p.first_group[targets] = groups;
     const uint32_t want = (groups + kDecWarps - 1) / kDecWarps;
-    const uint32_t grid = want < sms * 2 ? want : sms * 2;  // at most two CTAs per SM; warps walk the rest
+    const uint32_t grid = want < sms ? want : sms;  // one CTA per SM at most; warps walk the remaining row groups
     const size_t smem = size_t(p.cols) * 4 + p.cols + (p.cols / 32) * 8 + 64;
-    auto kernel = dec_matvec_kernel<F, RW, PAIR>;
-    static bool raised = false;  // per instantiation
-    if (smem > 40 * 1024 && !raised) {
-        BK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
-        raised = true;
+    const uint32_t iters = ((groups + grid * kDecWarps - 1) / (grid * kDecWarps)) * ((p.m[0].units + 31) / 32);
+    if (iters > 4) {
+        auto kernel = dec_matvec_kernel<F, RW, PAIR, 4>;
+        static bool raised = false;  // per instantiation
+        if (smem > 40 * 1024 && !raised) {
+            BK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+            raised = true;
+        }
+        launch_pdl(kernel, dim3(grid), dim3(kDecWarps * 32), smem, s, p);
+    } else {
+        auto kernel = dec_matvec_kernel<F, RW, PAIR, 1>;
+        static bool raised = false;
+        if (smem > 40 * 1024 && !raised) {
+            BK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+            raised = true;
+        }
+        launch_pdl(kernel, dim3(grid), dim3(kDecWarps * 32), smem, s, p);
     }
-    launch_pdl(kernel, dim3(grid), dim3(kDecWarps * 32), smem, s, p);
 }
 
 template <class F>
@@ -295,8 +368,8 @@ void dispatch_dec(DecMatParams& p, bool pair, uint32_t sms, cudaStream_t s) {
         div4 = div4 && p.m[i].rows % 4 == 0;
         div2 = div2 && p.m[i].rows % 2 == 0;
     }
-    // Rows per warp: the most that still gives every SM about two CTAs of 8 warps.
-    const uint32_t enough = sms * 2 * kDecWarps;
+    // Rows per warp: the most that still gives every SM a full CTA.
+    const uint32_t enough = sms * kDecWarps;
     constexpr bool heavy = std::is_same_v<F, FQ6_K>;
     int rw = 1;
     if (div4 && !heavy && rows / 4 >= enough) rw = 4;
@@ -457,8 +530,8 @@ __global__ void __launch_bounds__(128) dec_attn_scores_kernel(const DecAttnParam
 }
 
 // ---- softmax + weighted sum: one CTA per query head -----------------------------------------------------------------
-constexpr uint32_t kVTile = 32;   // positions of V per stage
-constexpr uint32_t kVStages = 6;  // stages in flight: the serial chain consumes a tile faster than L2 delivers one
+constexpr uint32_t kVTile = 64;   // positions of V per stage
+constexpr uint32_t kVStages = 4;  // stages in flight: the serial chain consumes a tile faster than L2 delivers one
 
 __global__ void __launch_bounds__(256) dec_attn_out_kernel(const DecAttnParams a) {
     extern __shared__ __align__(16) unsigned char raw[];  // probabilities [max_context] | V ring kVStages x [kVTile][dim] f16
@@ -493,12 +566,24 @@ __global__ void __launch_bounds__(256) dec_attn_out_kernel(const DecAttnParams a
     };
     for (uint32_t t = 0; t + 1 < kVStages; ++t) stage(t);
 
-    // softmax (src/kernels_f32.cpp:275-284): max, e = expf(s - max), f64 sum, p = e * float(1/sum)
+    // softmax (src/kernels_f32.cpp:275-284): max, e = expf(s - max), f64 sum, p = e * float(1/sum). Up to 8 scores per
+    // thread stay in registers (contexts up to 2048); longer rows go through shared memory.
+    const bool in_regs = visible <= 8 * 256;
+    float sv[8];
     float mx = -INFINITY;
-    for (uint32_t p = tid; p < visible; p += 256) {
-        const float v = s[p];
-        ps[p] = v;
-        mx = fmaxf(mx, v);
+    if (in_regs) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const uint32_t p = tid + k * 256;
+            sv[k] = p < visible ? s[p] : -INFINITY;
+            mx = fmaxf(mx, sv[k]);
+        }
+    } else {
+        for (uint32_t p = tid; p < visible; p += 256) {
+            const float v = s[p];
+            ps[p] = v;
+            mx = fmaxf(mx, v);
+        }
     }
     mx = warp_max(mx);
     if ((tid & 31) == 0) redf[tid >> 5] = mx;
@@ -507,10 +592,20 @@ __global__ void __launch_bounds__(256) dec_attn_out_kernel(const DecAttnParams a
 #pragma unroll
     for (int w = 1; w < 8; ++w) mx = fmaxf(mx, redf[w]);
     double part = 0.0;
-    for (uint32_t p = tid; p < visible; p += 256) {
-        const float e = exact_expf(__fsub_rn(ps[p], mx));
-        ps[p] = e;
-        part += double(e);
+    if (in_regs) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            if (tid + k * 256 < visible) {
+                sv[k] = exact_expf(__fsub_rn(sv[k], mx));
+                part += double(sv[k]);
+            }
+        }
+    } else {
+        for (uint32_t p = tid; p < visible; p += 256) {
+            const float e = exact_expf(__fsub_rn(ps[p], mx));
+            ps[p] = e;
+            part += double(e);
+        }
     }
     part = warp_sum(part);
     if ((tid & 31) == 0) redd[tid >> 5] = part;
@@ -519,7 +614,15 @@ __global__ void __launch_bounds__(256) dec_attn_out_kernel(const DecAttnParams a
 #pragma unroll
     for (int w = 0; w < 8; ++w) total += redd[w];
     const float inv = float(1.0 / total);
-    for (uint32_t p = tid; p < visible; p += 256) ps[p] = __fmul_rn(ps[p], inv);
+    if (in_regs) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const uint32_t p = tid + k * 256;
+            if (p < visible) ps[p] = __fmul_rn(sv[k], inv);
+        }
+    } else {
+        for (uint32_t p = tid; p < visible; p += 256) ps[p] = __fmul_rn(ps[p], inv);
+    }
 
     // weighted sum (src/kernels_f32.cpp:265-273): out[i] += p[pos] * v[pos][i], position after position.
     float acc = 0.0f;
