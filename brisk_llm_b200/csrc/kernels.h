@@ -104,6 +104,9 @@ void launch_dec_multiply(const MatTarget* targets, int count, const float* x, co
 // prologue) and softmax + weighted-sum kernel. Takes the same argument structs as the batched kernels (n is 1).
 void launch_dec_attention(const RopeArgs& r, const AttnArgs& at, cudaStream_t s);
 
+// Tensor parallel re-layout: gathered[rank][t][rows_l] -> dst[t][rank*rows_l + r] (add: dst += ...), tp ranks.
+void launch_tp_unpack(const float* gathered, float* dst, uint32_t n, uint32_t rows_l, uint32_t tp, bool add, cudaStream_t s);
+
 // First maximum of each of n rows of logits[n][vocab] (lowest index on ties) -> out_token[n].
 // If next_token/position are given (single row), also feeds the decode loop: *next_token = argmax, *position += 1,
 // and appends the token to history[*history_len++].

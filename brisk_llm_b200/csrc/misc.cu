@@ -342,6 +342,25 @@ __global__ void __launch_bounds__(256) argmax_stage2(const float* pv, const int3
 
 
 
+namespace {
+__global__ void tp_unpack_kernel(const float* __restrict__ gathered, float* dst, uint32_t n, uint32_t rows_l, uint32_t tp, int add) {
+    const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    const size_t total = size_t(n) * rows_l * tp;
+    if (i >= total) return;
+    const uint32_t full = rows_l * tp;
+    const uint32_t t = uint32_t(i / full), c = uint32_t(i % full);
+    const uint32_t rank = c / rows_l, r = c % rows_l;
+    const float v = gathered[(size_t(rank) * n + t) * rows_l + r];
+    dst[i] = add ? __fadd_rn(dst[i], v) : v;
+}
+}  // namespace
+
+void launch_tp_unpack(const float* gathered, float* dst, uint32_t n, uint32_t rows_l, uint32_t tp, bool add, cudaStream_t s) {
+    const size_t total = size_t(n) * rows_l * tp;
+    tp_unpack_kernel<<<unsigned((total + 255) / 256), 256, 0, s>>>(gathered, dst, n, rows_l, tp, add ? 1 : 0);
+    BK_CUDA(cudaGetLastError());
+}
+
 void launch_embed(const DevMatrix& embd, const int32_t* tokens_dev, uint32_t n, float* hidden, cudaStream_t s) {
     launch_pdl(embed_kernel, dim3(n), dim3(128), 0, s, embd, tokens_dev, hidden);
 }

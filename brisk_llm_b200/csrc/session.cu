@@ -10,10 +10,52 @@
 #include <string>
 #include <vector>
 
+#include <dlfcn.h>
+
 #include "../../include/brisk_cuda.h"
 #include "kernels.h"
 
 namespace bk {
+
+// NCCL is bound at run time (dlopen), so the library has no link-time dependency on it and, inside a process that
+// already loaded a NCCL (PyTorch's), uses that same copy. Only the five calls below are needed.
+struct NcclId {
+    char internal[128];
+};
+struct Nccl {
+    void* lib = nullptr;
+    int (*GetUniqueId)(NcclId*) = nullptr;
+    int (*CommInitRank)(void**, int, NcclId, int) = nullptr;
+    int (*AllGather)(const void*, void*, size_t, int, void*, cudaStream_t) = nullptr;
+    int (*CommDestroy)(void*) = nullptr;
+    const char* (*GetErrorString)(int) = nullptr;
+
+    static Nccl& get() {
+        static Nccl n = [] {
+            Nccl x;
+            const char* env = std::getenv("BRISK_NCCL_LIB");
+            const char* names[] = {env, "libnccl.so.2", "libnccl.so"};
+            for (const char* name : names) {
+                if (name == nullptr) continue;
+                x.lib = dlopen(name, RTLD_NOW | RTLD_GLOBAL);
+                if (x.lib != nullptr) break;
+            }
+            if (x.lib == nullptr) return x;
+            x.GetUniqueId = reinterpret_cast<int (*)(NcclId*)>(dlsym(x.lib, "ncclGetUniqueId"));
+            x.CommInitRank = reinterpret_cast<int (*)(void**, int, NcclId, int)>(dlsym(x.lib, "ncclCommInitRank"));
+            x.AllGather = reinterpret_cast<int (*)(const void*, void*, size_t, int, void*, cudaStream_t)>(dlsym(x.lib, "ncclAllGather"));
+            x.CommDestroy = reinterpret_cast<int (*)(void*)>(dlsym(x.lib, "ncclCommDestroy"));
+            x.GetErrorString = reinterpret_cast<const char* (*)(int)>(dlsym(x.lib, "ncclGetErrorString"));
+            return x;
+        }();
+        return n;
+    }
+    bool ok() const { return lib && GetUniqueId && CommInitRank && AllGather && CommDestroy && GetErrorString; }
+    void check(int rc, const char* what) const {
+        if (rc != 0) throw CudaError(std::string("cuda: ") + what + " failed: " + (GetErrorString ? GetErrorString(rc) : "nccl error"));
+    }
+};
+constexpr int kNcclFloat = 7;  // ncclFloat32
 
 struct DevBuffer;
 
@@ -54,6 +96,12 @@ struct Session {
     // configuration
     uint32_t vocab = 0, hidden = 0, n_layers = 0, heads = 0, kv_heads = 0, head_dim = 0, ffn = 0;
     uint32_t q_dim = 0, kv_dim = 0;
+    // Tensor parallelism: every matrix is split by OUTPUT rows (whole heads for q/k/v), so each output value is still
+    // one rank's sum over all of its input blocks in order - bit-identical to the unsharded result - and the ranks
+    // exchange activations with all-gathers. *_l are this rank's shares.
+    int tp_size = 1, tp_rank = 0;
+    void* comm = nullptr;
+    uint32_t heads_l = 0, kv_heads_l = 0, q_dim_l = 0, kv_dim_l = 0, ffn_l = 0, hidden_l = 0, vocab_l = 0;
     uint64_t max_context = 0;
     float eps = 0, rope_base = 0;
     int arch = 0, neox = 1, device = 0;
@@ -68,7 +116,7 @@ struct Session {
     uint64_t weight_bytes = 0, kv_bytes = 0;
 
     // state and scratch
-    DevBuffer kv, rope, tokens_dev, scalars, hidden_b, q_b, k_b, v_b, attended_b, ffn_b, up_b, logits_b, actf, actq0, actd0, acts0, actqk,
+    DevBuffer kv, rope, tokens_dev, scalars, hidden_b, q_b, k_b, v_b, attended_b, ffn_b, up_b, logits_b, tp_local, tp_gathered, full_b, actf, actq0, actd0, acts0, actqk,
         actdk, actbs, partial, am_val, am_idx, history, logit_history, trace;
     DevActMut act;
     float* logits_host = nullptr;     // pinned [64][vocab]
@@ -88,6 +136,7 @@ struct Session {
     uint32_t* d_history_len() const { return scalars.as<uint32_t>() + 2; }
 
     ~Session() {
+        if (comm != nullptr && Nccl::get().ok()) Nccl::get().CommDestroy(comm);
         if (step_graph) cudaGraphExecDestroy(step_graph);
         if (ev0) cudaEventDestroy(ev0);
         if (ev1) cudaEventDestroy(ev1);
@@ -97,14 +146,18 @@ struct Session {
     }
 
     // ---- load ------------------------------------------------------------------------------------------
-    DevMatrix upload_matrix(const brisk_cuda_matrix& m, const char* what, uint64_t rows, uint64_t cols, DevBuffer& staging) {
+    // Uploads rows [row0, row0 + rows) of a full_rows x cols tensor (row0 = 0, rows = full_rows: all of it).
+    DevMatrix upload_matrix(const brisk_cuda_matrix& m, const char* what, uint64_t full_rows, uint64_t cols, DevBuffer& staging, uint64_t row0 = 0,
+                            uint64_t rows = 0) {
+        if (rows == 0) rows = full_rows;
         if (m.data == nullptr) throw CudaError(std::string("cuda: missing tensor ") + what);
         if (!type_supported(m.type)) throw CudaError(std::string("cuda: tensor ") + what + " has an unsupported type " + std::to_string(m.type));
-        if (m.rows != rows || m.cols != cols) throw CudaError(std::string("cuda: tensor ") + what + " has an unexpected shape");
+        if (m.rows != full_rows || m.cols != cols) throw CudaError(std::string("cuda: tensor ") + what + " has an unexpected shape");
         const uint32_t be = block_elems(m.type);
         if (cols % be != 0 || cols % 32 != 0) throw CudaError(std::string("cuda: tensor ") + what + " row length is not a multiple of its block size");
-        const uint64_t expect = rows * (cols / be) * block_bytes(m.type);
-        if (m.bytes != expect) throw CudaError(std::string("cuda: tensor ") + what + " has unexpected quantised data");
+        const uint64_t row_bytes = (cols / be) * block_bytes(m.type);
+        if (m.bytes != full_rows * row_bytes) throw CudaError(std::string("cuda: tensor ") + what + " has unexpected quantised data");
+        const uint64_t expect = rows * row_bytes;
         auto buf = std::make_unique<DevBuffer>();
         buf->alloc(plane_sizes(m.type, uint32_t(rows), uint32_t(cols)).total());
         DevMatrix d;
@@ -116,7 +169,7 @@ struct Session {
             staging.alloc(expect);
         }
         BK_CUDA(cudaStreamSynchronize(stream));  // the previous repack still reads the staging buffer
-        BK_CUDA(cudaMemcpyAsync(staging.p, m.data, expect, cudaMemcpyHostToDevice, stream));
+        BK_CUDA(cudaMemcpyAsync(staging.p, static_cast<const uint8_t*>(m.data) + row0 * row_bytes, expect, cudaMemcpyHostToDevice, stream));
         launch_repack(d, staging.as<uint8_t>(), stream);
         weight_bytes += expect;
         stats.h2d_bytes += expect;
@@ -140,7 +193,9 @@ struct Session {
 
     void load(const brisk_cuda_model& m, const brisk_cuda_options& opt) {
         if (m.abi_version != BRISK_CUDA_ABI_VERSION) throw CudaError("cuda: model description has a different ABI version");
-        if (opt.tp_size > 1) throw CudaError("cuda: tensor parallelism is not available in this build");
+        tp_size = opt.tp_size > 1 ? opt.tp_size : 1;
+        tp_rank = tp_size > 1 ? opt.tp_rank : 0;
+        if (tp_rank < 0 || tp_rank >= tp_size) throw CudaError("cuda: tensor-parallel rank out of range");
         vocab = m.vocab_size; hidden = m.hidden; n_layers = m.layer_count; heads = m.head_count; kv_heads = m.kv_head_count;
         head_dim = m.head_dim; ffn = m.ffn; eps = m.rms_epsilon; rope_base = m.rope_base; arch = m.arch; neox = m.rope_neox;
         flags = opt.flags;
@@ -152,6 +207,20 @@ struct Session {
         q_dim = heads * head_dim;
         kv_dim = kv_heads * head_dim;
         max_context = opt.max_context == 0 ? m.context_length : std::min<uint64_t>(opt.max_context, m.context_length);
+        const uint32_t tp = uint32_t(tp_size);
+        if (kv_heads % tp != 0 || ffn % (tp * 32) != 0 || hidden % (tp * 32) != 0 || vocab % tp != 0) {
+            throw CudaError("cuda: the tensor-parallel degree must divide the K/V heads, the vocabulary and (in blocks of 32) the hidden and feed-forward sizes");
+        }
+        heads_l = heads / tp; kv_heads_l = kv_heads / tp; q_dim_l = heads_l * head_dim; kv_dim_l = kv_heads_l * head_dim;
+        ffn_l = ffn / tp; hidden_l = hidden / tp; vocab_l = vocab / tp;
+        if (tp_size > 1) {
+            const Nccl& nccl = Nccl::get();
+            if (!nccl.ok()) throw CudaError("cuda: tensor parallelism needs NCCL (libnccl.so.2 was not found; set BRISK_NCCL_LIB)");
+            if (opt.tp_unique_id == nullptr) throw CudaError("cuda: tensor parallelism needs the id from brisk_cuda_tp_unique_id");
+            NcclId id;
+            std::memcpy(&id, opt.tp_unique_id, sizeof(id));
+            nccl.check(nccl.CommInitRank(&comm, tp_size, id, tp_rank), "ncclCommInitRank");
+        }
 
         {
             int count = 0;
@@ -164,26 +233,28 @@ struct Session {
 
         DevBuffer staging;
         embd = upload_matrix(m.token_embd, "token_embd.weight", vocab, hidden, staging);
-        head = m.output.data != nullptr ? upload_matrix(m.output, "output.weight", vocab, hidden, staging) : embd;
+        const uint64_t r = uint64_t(tp_rank);
+        if (tp_size == 1) head = m.output.data != nullptr ? upload_matrix(m.output, "output.weight", vocab, hidden, staging) : embd;
+        else head = upload_matrix(m.output.data != nullptr ? m.output : m.token_embd, "output.weight", vocab, hidden, staging, r * vocab_l, vocab_l);
         output_norm = upload_vector(m.output_norm, hidden, "output_norm.weight", true);
         layers.resize(n_layers);
         for (uint32_t l = 0; l < n_layers; ++l) {
             const brisk_cuda_layer& s = m.layers[l];
             Layer& d = layers[l];
             d.attn_norm = upload_vector(s.attn_norm, hidden, "attn_norm.weight", true);
-            d.q = upload_matrix(s.q, "attn_q.weight", q_dim, hidden, staging);
-            d.k = upload_matrix(s.k, "attn_k.weight", kv_dim, hidden, staging);
-            d.v = upload_matrix(s.v, "attn_v.weight", kv_dim, hidden, staging);
+            d.q = upload_matrix(s.q, "attn_q.weight", q_dim, hidden, staging, r * q_dim_l, q_dim_l);
+            d.k = upload_matrix(s.k, "attn_k.weight", kv_dim, hidden, staging, r * kv_dim_l, kv_dim_l);
+            d.v = upload_matrix(s.v, "attn_v.weight", kv_dim, hidden, staging, r * kv_dim_l, kv_dim_l);
             d.q_norm = upload_vector(s.q_norm, head_dim, "attn_q_norm.weight", false);
             d.k_norm = upload_vector(s.k_norm, head_dim, "attn_k_norm.weight", false);
             d.attn_sub_norm = upload_vector(s.attn_sub_norm, q_dim, "attn_sub_norm.weight", false);
-            d.o = upload_matrix(s.o, "attn_output.weight", hidden, q_dim, staging);
+            d.o = upload_matrix(s.o, "attn_output.weight", hidden, q_dim, staging, r * hidden_l, hidden_l);
             d.ffn_norm = upload_vector(s.ffn_norm, hidden, "ffn_norm.weight", true);
-            d.gate = upload_matrix(s.gate, "ffn_gate.weight", ffn, hidden, staging);
-            d.up = upload_matrix(s.up, "ffn_up.weight", ffn, hidden, staging);
+            d.gate = upload_matrix(s.gate, "ffn_gate.weight", ffn, hidden, staging, r * ffn_l, ffn_l);
+            d.up = upload_matrix(s.up, "ffn_up.weight", ffn, hidden, staging, r * ffn_l, ffn_l);
             if (d.gate.type != d.up.type) throw CudaError("cuda: ffn_gate and ffn_up must share one type");
             d.ffn_sub_norm = upload_vector(s.ffn_sub_norm, ffn, "ffn_sub_norm.weight", false);
-            d.down = upload_matrix(s.down, "ffn_down.weight", hidden, ffn, staging);
+            d.down = upload_matrix(s.down, "ffn_down.weight", hidden, ffn, staging, r * hidden_l, hidden_l);
         }
         BK_CUDA(cudaStreamSynchronize(stream));
         if (m.output.data == nullptr) {
@@ -191,7 +262,7 @@ struct Session {
         }
 
         // K/V cache: per layer [kv head][max_context][head_dim] f16, K then V (src/model.cpp:982-991).
-        const size_t per = size_t(kv_heads) * max_context * head_dim;
+        const size_t per = size_t(kv_heads_l) * max_context * head_dim;
         kv_bytes = size_t(n_layers) * 2 * per * sizeof(__half);
         kv.alloc(kv_bytes);
         BK_CUDA(cudaMemsetAsync(kv.p, 0, kv_bytes, stream));
@@ -240,7 +311,13 @@ struct Session {
         actbs.alloc(size_t(kMaxBatch) * (widest / 16) * 2);
         act.f32 = actf.as<float>(); act.q0 = actq0.as<int8_t>(); act.d0 = actd0.as<float>(); act.s0 = acts0.as<int32_t>();
         act.qk = actqk.as<int8_t>(); act.dk = actdk.as<float>(); act.bs = actbs.as<int16_t>();
-        partial.alloc(attn_scratch_floats(kMaxBatch, heads, uint32_t(max_context)) * 4);
+        partial.alloc(attn_scratch_floats(kMaxBatch, heads_l, uint32_t(max_context)) * 4);
+        if (tp_size > 1) {
+            const size_t widest_rows = std::max<size_t>(std::max<size_t>(q_dim, ffn), std::max<size_t>(hidden, size_t(vocab) * kMaxScored / kMaxBatch + 1));
+            tp_local.alloc(size_t(kMaxBatch) * widest_rows / tp * 4 + 256);
+            tp_gathered.alloc(size_t(kMaxBatch) * widest_rows * 4 + 256);
+            full_b.alloc(size_t(kMaxBatch) * std::max(q_dim, ffn) * 4);
+        }
         am_val.alloc(argmax_scratch_elems(vocab) * 4);
         am_idx.alloc(argmax_scratch_elems(vocab) * 4);
         history.alloc((max_context + 1) * sizeof(int32_t));
@@ -274,6 +351,8 @@ struct Session {
         return a.view();
     }
 
+    // One multiply of the batched path: targets of one weight type share a launch of the streaming kernel; prompt
+    // batches go to the tensor-core kernel where the type has one.
     void multiply(std::vector<MatTarget> targets, const DevAct& a, uint32_t n, Epilogue epi) {
         const bool pair = epi == EPI_SILU_MUL || epi == EPI_RELU2_MUL;
         if (pair) {
@@ -290,7 +369,6 @@ struct Session {
             launches += (n + kMaxSmallBatch - 1) / kMaxSmallBatch;
             return;
         }
-        // Targets of one type share a launch (q and k in Q4_K, v in Q6_K -> two launches).
         while (!targets.empty()) {
             std::vector<MatTarget> same, rest;
             for (const MatTarget& t : targets) (t.m.type == targets[0].m.type ? same : rest).push_back(t);
@@ -304,100 +382,112 @@ struct Session {
         }
     }
 
-    // n tokens already in tokens_dev, their first position in d_position(). max_visible bounds position + n.
-    void forward(uint32_t n, bool all_logits, uint32_t max_visible) {
+    // Tensor parallel: this rank's [n][rows_l] slice -> every rank's [n][rows_l * tp] (store or add), by an all-gather
+    // into [rank][n][rows_l] and a re-layout kernel. No-op for a single GPU (kernels then write dst directly).
+    void exchange(const float* local, float* dst, uint32_t n, uint32_t rows_l, bool add) {
+        const Nccl& nccl = Nccl::get();
+        nccl.check(nccl.AllGather(local, tp_gathered.p, size_t(n) * rows_l, kNcclFloat, comm, stream), "ncclAllGather");
+        launch_tp_unpack(tp_gathered.as<float>(), dst, n, rows_l, uint32_t(tp_size), add, stream);
+        launches += 2;
+    }
+
+    // The layers of one batch. n tokens are in tokens_dev, their first position in d_position(); max_visible bounds
+    // position + n. single = true takes the fused single-token kernels (n == 1).
+    void run_layers(uint32_t n, bool all_logits, uint32_t max_visible, bool single) {
         float* hid = hidden_b.as<float>();
         launch_embed(embd, tokens_dev.as<int32_t>(), n, hid, stream);
         ++launches;
         const float attn_scale = 1.0f / std::sqrt(static_cast<float>(head_dim));
+        const bool tp = tp_size > 1;
+        unsigned long long* tr = trace.p ? trace.as<unsigned long long>() : nullptr;
+        uint32_t slot = 0;
+
+        // out = W x (optionally RMS-normed, then quantised) for one group of targets sharing the input.
+        auto apply = [&](std::vector<MatTarget> targets, const float* x, uint32_t ldx, const float* w, uint32_t cols, Epilogue epi, uint32_t count = 0) {
+            if (count == 0) count = n;
+            if (single) {
+                unsigned long long* t = tr ? tr + 8 * (slot++ % 512) : nullptr;
+                if (epi == EPI_SILU_MUL || epi == EPI_RELU2_MUL) {
+                    launch_dec_multiply(targets.data(), int(targets.size()), x, w, eps, cols, epi, sms, stream, t);
+                    ++launches;
+                    return;
+                }
+                while (!targets.empty()) {  // one launch per weight type among the targets
+                    std::vector<MatTarget> same, rest;
+                    for (const MatTarget& tg : targets) (tg.m.type == targets[0].m.type ? same : rest).push_back(tg);
+                    launch_dec_multiply(same.data(), int(same.size()), x, w, eps, cols, epi, sms, stream, t);
+                    ++launches;
+                    targets.swap(rest);
+                }
+                return;
+            }
+            Needs nd;
+            for (const MatTarget& tg : targets) need(nd, tg.m.type);
+            const DevAct a = prepare(x, ldx, w, count, cols, nd);
+            multiply(std::move(targets), a, count, epi);
+        };
+
         for (uint32_t l = 0; l < n_layers; ++l) {
             const Layer& L = layers[l];
-            Needs nd;
-            need(nd, L.q.type); need(nd, L.k.type); need(nd, L.v.type);
-            DevAct a = prepare(hid, hidden, L.attn_norm, n, hidden, nd);
-            multiply({{L.q, q_b.as<float>(), q_dim}, {L.k, k_b.as<float>(), kv_dim}, {L.v, v_b.as<float>(), kv_dim}}, a, n, EPI_STORE);
+            apply({{L.q, q_b.as<float>(), q_dim_l}, {L.k, k_b.as<float>(), kv_dim_l}, {L.v, v_b.as<float>(), kv_dim_l}}, hid, hidden, L.attn_norm, hidden,
+                  EPI_STORE);
 
             RopeArgs r{};
             r.q = q_b.as<float>(); r.k = k_b.as<float>(); r.v = v_b.as<float>();
             r.q_norm = L.q_norm; r.k_norm = L.k_norm; r.rope = rope.as<float>();
             r.k_cache = L.k_cache; r.v_cache = L.v_cache; r.position = d_position();
-            r.n = n; r.heads = heads; r.kv_heads = kv_heads; r.dim = head_dim; r.max_context = uint32_t(max_context);
+            r.n = n; r.heads = heads_l; r.kv_heads = kv_heads_l; r.dim = head_dim; r.max_context = uint32_t(max_context);
             r.eps = eps; r.neox = neox;
-            launch_qk_norm_rope_store(r, stream);
-            ++launches;
-
             AttnArgs at{};
             at.q = q_b.as<float>(); at.k_cache = L.k_cache; at.v_cache = L.v_cache; at.out = attended_b.as<float>();
             at.scores = partial.as<float>(); at.position = d_position();
-            at.n = n; at.heads = heads; at.kv_heads = kv_heads; at.dim = head_dim; at.max_context = uint32_t(max_context);
+            at.n = n; at.heads = heads_l; at.kv_heads = kv_heads_l; at.dim = head_dim; at.max_context = uint32_t(max_context);
             at.max_visible = max_visible; at.scale = attn_scale;
-            launch_attention(at, stream);
-            launches += 3;
+            if (single) {
+                launch_dec_attention(r, at, stream);
+                launches += 2;
+            } else {
+                launch_qk_norm_rope_store(r, stream);
+                launch_attention(at, stream);
+                launches += 4;
+            }
 
-            Needs no;
-            need(no, L.o.type);
-            a = prepare(attended_b.as<float>(), q_dim, L.attn_sub_norm, n, q_dim, no);
-            multiply({{L.o, hid, hidden}}, a, n, EPI_ADD);
+            // attention output projection + residual
+            const float* attended = attended_b.as<float>();
+            if (tp) {
+                exchange(attended_b.as<float>(), full_b.as<float>(), n, q_dim_l, false);
+                attended = full_b.as<float>();
+                apply({{L.o, tp_local.as<float>(), hidden_l}}, attended, q_dim, L.attn_sub_norm, q_dim, EPI_STORE);
+                exchange(tp_local.as<float>(), hid, n, hidden_l, true);
+            } else {
+                apply({{L.o, hid, hidden}}, attended, q_dim, L.attn_sub_norm, q_dim, EPI_ADD);
+            }
 
-            Needs nf;
-            need(nf, L.gate.type);
-            a = prepare(hid, hidden, L.ffn_norm, n, hidden, nf);
-            multiply({{L.gate, ffn_b.as<float>(), ffn}, {L.up, nullptr, ffn}}, a, n, arch == BRISK_ARCH_BITNET ? EPI_RELU2_MUL : EPI_SILU_MUL);
-
-            Needs ndn;
-            need(ndn, L.down.type);
-            a = prepare(ffn_b.as<float>(), ffn, L.ffn_sub_norm, n, ffn, ndn);
-            multiply({{L.down, hid, hidden}}, a, n, EPI_ADD);
+            // feed-forward + residual
+            const Epilogue act_epi = arch == BRISK_ARCH_BITNET ? EPI_RELU2_MUL : EPI_SILU_MUL;
+            const float* gated = ffn_b.as<float>();
+            if (tp) {
+                apply({{L.gate, tp_local.as<float>(), ffn_l}, {L.up, nullptr, ffn_l}}, hid, hidden, L.ffn_norm, hidden, act_epi);
+                exchange(tp_local.as<float>(), ffn_b.as<float>(), n, ffn_l, false);
+                apply({{L.down, tp_local.as<float>(), hidden_l}}, gated, ffn, L.ffn_sub_norm, ffn, EPI_STORE);
+                exchange(tp_local.as<float>(), hid, n, hidden_l, true);
+            } else {
+                apply({{L.gate, ffn_b.as<float>(), ffn}, {L.up, nullptr, ffn}}, hid, hidden, L.ffn_norm, hidden, act_epi);
+                apply({{L.down, hid, hidden}}, gated, ffn, L.ffn_sub_norm, ffn, EPI_ADD);
+            }
         }
-        Needs nh;
-        need(nh, head.type);
         const uint32_t rows = all_logits ? n : 1;
-        DevAct a = prepare(all_logits ? hid : hid + size_t(n - 1) * hidden, hidden, output_norm, rows, hidden, nh);
-        multiply({{head, logits_b.as<float>(), vocab}}, a, rows, EPI_STORE);
+        const float* last = all_logits ? hid : hid + size_t(n - 1) * hidden;
+        if (tp) {
+            apply({{head, tp_local.as<float>(), vocab_l}}, last, hidden, output_norm, hidden, EPI_STORE, rows);
+            exchange(tp_local.as<float>(), logits_b.as<float>(), rows, vocab_l, false);
+        } else {
+            apply({{head, logits_b.as<float>(), vocab}}, last, hidden, output_norm, hidden, EPI_STORE, rows);
+        }
     }
 
-    // The single-token step through the fused kernels of decode.cu (six per layer).
-    void forward_decode() {
-        float* hid = hidden_b.as<float>();
-        launch_embed(embd, tokens_dev.as<int32_t>(), 1, hid, stream);
-        ++launches;
-        const float attn_scale = 1.0f / std::sqrt(static_cast<float>(head_dim));
-        unsigned long long* tr = trace.p ? trace.as<unsigned long long>() : nullptr;
-        uint32_t slot = 0;
-        auto fused = [&](std::vector<MatTarget> targets, const float* x, const float* w, uint32_t cols, Epilogue epi) {
-            unsigned long long* t = tr ? tr + 8 * (slot++ % 512) : nullptr;
-            if (epi == EPI_SILU_MUL || epi == EPI_RELU2_MUL) {
-                launch_dec_multiply(targets.data(), int(targets.size()), x, w, eps, cols, epi, sms, stream, t);
-                ++launches;
-                return;
-            }
-            while (!targets.empty()) {  // one launch per weight type among the targets
-                std::vector<MatTarget> same, rest;
-                for (const MatTarget& t : targets) (t.m.type == targets[0].m.type ? same : rest).push_back(t);
-                launch_dec_multiply(same.data(), int(same.size()), x, w, eps, cols, epi, sms, stream, t);
-                ++launches;
-                targets.swap(rest);
-            }
-        };
-        for (uint32_t l = 0; l < n_layers; ++l) {
-            const Layer& L = layers[l];
-            fused({{L.q, q_b.as<float>(), q_dim}, {L.k, k_b.as<float>(), kv_dim}, {L.v, v_b.as<float>(), kv_dim}}, hid, L.attn_norm, hidden, EPI_STORE);
-            RopeArgs r{};
-            r.q = q_b.as<float>(); r.k = k_b.as<float>(); r.v = v_b.as<float>();
-            r.q_norm = L.q_norm; r.k_norm = L.k_norm; r.rope = rope.as<float>();
-            r.k_cache = L.k_cache; r.v_cache = L.v_cache; r.position = d_position();
-            r.n = 1; r.heads = heads; r.kv_heads = kv_heads; r.dim = head_dim; r.max_context = uint32_t(max_context);
-            r.eps = eps; r.neox = neox;
-            AttnArgs at{};
-            at.out = attended_b.as<float>(); at.scores = partial.as<float>(); at.scale = attn_scale;
-            launch_dec_attention(r, at, stream);
-            launches += 2;
-            fused({{L.o, hid, hidden}}, attended_b.as<float>(), L.attn_sub_norm, q_dim, EPI_ADD);
-            fused({{L.gate, ffn_b.as<float>(), ffn}, {L.up, nullptr, ffn}}, hid, L.ffn_norm, hidden, arch == BRISK_ARCH_BITNET ? EPI_RELU2_MUL : EPI_SILU_MUL);
-            fused({{L.down, hid, hidden}}, ffn_b.as<float>(), L.ffn_sub_norm, ffn, EPI_ADD);
-        }
-        fused({{head, logits_b.as<float>(), vocab}}, hid, output_norm, hidden, EPI_STORE);
-    }
+    void forward(uint32_t n, bool all_logits, uint32_t max_visible) { run_layers(n, all_logits, max_visible, false); }
+    void forward_decode() { run_layers(1, false, uint32_t(max_context), true); }
 
     void build_step_graph() {
         if (step_graph != nullptr || (flags & BRISK_CUDA_FLAG_NO_GRAPH)) return;
@@ -642,9 +732,17 @@ int brisk_cuda_dump_trace(brisk_cuda_session* session, unsigned long long* out, 
 }
 
 int brisk_cuda_tp_unique_id(void* out128, char* err, size_t errlen) {
-    (void)out128;
-    put_error(err, errlen, "cuda: tensor parallelism is not available in this build");
-    return -1;
+    try {
+        const bk::Nccl& nccl = bk::Nccl::get();
+        if (!nccl.ok()) throw bk::CudaError("cuda: tensor parallelism needs NCCL (libnccl.so.2 was not found; set BRISK_NCCL_LIB)");
+        bk::NcclId id;
+        nccl.check(nccl.GetUniqueId(&id), "ncclGetUniqueId");
+        std::memcpy(out128, &id, sizeof(id));
+        return 0;
+    } catch (const std::exception& e) {
+        put_error(err, errlen, e.what());
+        return -1;
+    }
 }
 
 }  // extern "C"

@@ -122,6 +122,16 @@ class CudaSession:
         return {k: getattr(st, k) for k, _ in abi.Stats._fields_}
 
 
+def tp_unique_id() -> bytes:
+    """128 bytes identifying one tensor-parallel group; rank 0 makes it and hands it to every rank's CudaSession."""
+    lib = abi.load_library()
+    buf = C.create_string_buffer(128)
+    err = C.create_string_buffer(512)
+    if lib.brisk_cuda_tp_unique_id(buf, err, len(err)) != 0:
+        raise RuntimeError(err.value.decode())
+    return buf.raw
+
+
 def device_count() -> int:
     return abi.load_library().brisk_cuda_device_count()
 

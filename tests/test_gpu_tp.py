@@ -1,0 +1,66 @@
+"""Tensor-parallel token loop on 2 GPUs (skipped with fewer): each rank holds half of every matrix's rows and half of
+the K/V heads; the logits every rank returns must equal the CPU oracle's bit for bit, like the single-GPU path."""
+import os
+import subprocess
+import sys
+import textwrap
+
+import numpy as np
+import pytest
+
+import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+WORKER = textwrap.dedent('''
+    import os, sys
+    sys.path.insert(0, sys.argv[1]); sys.path.insert(0, os.path.join(sys.argv[1], "tests"))
+    import numpy as np
+    import torch, torch.distributed as dist
+    from brisk_llm_b200 import parallel, synth
+    import helpers as H
+    rank, local, world = parallel.env_rank()
+    torch.cuda.set_device(local)
+    dist.init_process_group("gloo")
+    spec = synth.tiny(synth.MISTRAL_7B, layers=2, vocab=1024, hidden=1024, heads=8, kv_heads=4, ffn=2048, context=512)
+    model = synth.perturb_norms(synth.generate(spec, seed=4))
+    toks = synth.random_tokens(spec, 80, seed=5)
+    s = parallel.tensor_parallel_session(model)
+    got = [s.eval(toks[:40]).copy()]
+    for i in range(40, 44):
+        got.append(s.eval(toks[i:i + 1]).copy())
+    got.append(s.eval_all(toks[44:53]).copy())
+    s.rollback(42)
+    ids, logits = s.generate_greedy(int(toks[53]), 6, want_logits=True)
+    s.close()
+    if rank == 0:
+        o = H.OracleSession(model)
+        want = [o.eval(toks[:40])]
+        for i in range(40, 44):
+            want.append(o.eval(toks[i:i + 1]))
+        want.append(o.eval_all(toks[44:53]))
+        o.rollback(42)
+        want_ids, want_logits = o.generate_greedy(toks[53:54], 6)
+        for a, b in zip(got, want):
+            assert np.array_equal(a, b), float(np.abs(a - b).max())
+        assert np.array_equal(ids, want_ids) and np.array_equal(logits, want_logits)
+    np.save(os.path.join(sys.argv[2], f"logits{rank}.npy"), got[-1])
+    dist.barrier()
+    dist.destroy_process_group()
+''')
+
+
+def test_two_rank_tensor_parallel_matches_the_oracle(tmp_path):
+    from brisk_llm_b200 import engine
+    if engine.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    script = tmp_path / "tp_worker.py"
+    script.write_text(WORKER)
+    port = 29700 + os.getpid() % 200
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), str(script), H.ROOT, str(tmp_path)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
+    assert r.returncode == 0, (r.stdout[-1500:], r.stderr[-3000:])
+    a, b = np.load(tmp_path / "logits0.npy"), np.load(tmp_path / "logits1.npy")
+    assert np.array_equal(a, b)  # every rank holds the full, identical logits
