@@ -52,7 +52,7 @@ struct GemmParams {
 };
 
 template <int WBYTES>
-__global__ void __launch_bounds__(GWARPS * 32) gemm_q8_kernel(const GemmParams p) {
+__global__ void __launch_bounds__(GWARPS * 32, 2) gemm_q8_kernel(const GemmParams p) {
     using S = Stage<WBYTES>;
     extern __shared__ __align__(16) unsigned char smem[];
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -193,6 +193,7 @@ static void launch_gemm_one(const MatTarget& tg, const DevAct& act, uint32_t n, 
         static bool raised = false;
         if (!raised) {
             BK_CUDA(cudaFuncSetAttribute(gemm_q8_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+            BK_CUDA(cudaFuncSetAttribute(gemm_q8_kernel<16>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
             raised = true;
         }
         gemm_q8_kernel<16><<<grid, GWARPS * 32, smem, s>>>(p);
@@ -201,6 +202,7 @@ static void launch_gemm_one(const MatTarget& tg, const DevAct& act, uint32_t n, 
         static bool raised = false;
         if (!raised) {
             BK_CUDA(cudaFuncSetAttribute(gemm_q8_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+            BK_CUDA(cudaFuncSetAttribute(gemm_q8_kernel<32>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
             raised = true;
         }
         gemm_q8_kernel<32><<<grid, GWARPS * 32, smem, s>>>(p);

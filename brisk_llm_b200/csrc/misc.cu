@@ -169,51 +169,62 @@ __global__ void __launch_bounds__(128) qk_norm_rope_store_kernel(const RopeArgs 
 // weighted sum (a thread per output value, walking the positions in order).
 constexpr uint32_t kMaxGroup = 16;  // query heads per K/V head, at most (kMaxHeadsPerKv, src/model.h:34)
 
-template <int GROUP>
+constexpr uint32_t kTokTile = 8;  // tokens of a batch that share one pass over the cached K (or V) rows
+
+// grid (position chunks of 128, K/V heads, token tiles). A thread owns one cached position: it reads that K row once
+// and scores it against every (token, query head) of the tile, each score in dot_f32's order.
+template <int GROUP, int DIM>
 __global__ void __launch_bounds__(128) attn_scores_kernel(const AttnArgs a) {
-    extern __shared__ float qs[];  // [GROUP][dim]
-    const uint32_t kvh = blockIdx.y, t = blockIdx.z, dim = a.dim;
-    const uint32_t visible = *a.position + t + 1;
+    extern __shared__ float qs[];  // [kTokTile][GROUP][DIM]
+    const uint32_t kvh = blockIdx.y, t0 = blockIdx.z * kTokTile;
+    const uint32_t tn = min(kTokTile, a.n - t0);
+    const uint32_t base_visible = *a.position + t0 + 1;        // positions the tile's first token sees
+    const uint32_t last_visible = base_visible + tn - 1;       // ... and its last
     const uint32_t p = blockIdx.x * 128 + threadIdx.x;
-    if (blockIdx.x * 128 >= visible) return;
-    for (uint32_t i = threadIdx.x; i < GROUP * dim; i += 128) qs[i] = a.q[size_t(t) * a.heads * dim + size_t(kvh) * GROUP * dim + i];
+    if (blockIdx.x * 128 >= last_visible) return;
+    for (uint32_t i = threadIdx.x; i < tn * GROUP * DIM; i += 128) {
+        const uint32_t j = i / (GROUP * DIM), rest = i % (GROUP * DIM);
+        qs[i] = a.q[size_t(t0 + j) * a.heads * DIM + size_t(kvh) * GROUP * DIM + rest];
+    }
     __syncthreads();
-    if (p >= visible) return;
-    const __half* kr = a.k_cache + (size_t(kvh) * a.max_context + p) * dim;
-    float lanes[GROUP][16];
+    if (p >= last_visible) return;
+    const uint4* kr = reinterpret_cast<const uint4*>(a.k_cache + (size_t(kvh) * a.max_context + p) * DIM);
+    float kf[DIM];
 #pragma unroll
-    for (int g = 0; g < GROUP; ++g)
-#pragma unroll
-        for (int j = 0; j < 16; ++j) lanes[g][j] = 0.0f;
-    for (uint32_t i = 0; i < dim; i += 16) {
-        const uint4 k0 = *reinterpret_cast<const uint4*>(kr + i), k1 = *reinterpret_cast<const uint4*>(kr + i + 8);
-        float kf[16];
-        const __half2* h0 = reinterpret_cast<const __half2*>(&k0);
-        const __half2* h1 = reinterpret_cast<const __half2*>(&k1);
+    for (int i = 0; i < DIM / 8; ++i) {
+        const uint4 raw = kr[i];
+        const __half2* h = reinterpret_cast<const __half2*>(&raw);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const float2 f0 = __half22float2(h0[j]), f1 = __half22float2(h1[j]);
-            kf[2 * j] = f0.x; kf[2 * j + 1] = f0.y; kf[8 + 2 * j] = f1.x; kf[8 + 2 * j + 1] = f1.y;
-        }
-#pragma unroll
-        for (int g = 0; g < GROUP; ++g) {
-            const float4* q4 = reinterpret_cast<const float4*>(qs + g * dim + i);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float4 q = q4[j];
-                lanes[g][4 * j + 0] = __fadd_rn(lanes[g][4 * j + 0], __fmul_rn(q.x, kf[4 * j + 0]));
-                lanes[g][4 * j + 1] = __fadd_rn(lanes[g][4 * j + 1], __fmul_rn(q.y, kf[4 * j + 1]));
-                lanes[g][4 * j + 2] = __fadd_rn(lanes[g][4 * j + 2], __fmul_rn(q.z, kf[4 * j + 2]));
-                lanes[g][4 * j + 3] = __fadd_rn(lanes[g][4 * j + 3], __fmul_rn(q.w, kf[4 * j + 3]));
-            }
+            const float2 f = __half22float2(h[j]);
+            kf[8 * i + 2 * j] = f.x;
+            kf[8 * i + 2 * j + 1] = f.y;
         }
     }
+    for (uint32_t j = 0; j < tn; ++j) {
+        if (p >= base_visible + j) continue;  // token j does not see this position
 #pragma unroll
-    for (int g = 0; g < GROUP; ++g) {
-        float sum = 0.0f;
+        for (int g = 0; g < GROUP; ++g) {
+            const float4* q4 = reinterpret_cast<const float4*>(qs + (j * GROUP + g) * DIM);
+            float lanes[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) sum = __fadd_rn(sum, lanes[g][j]);
-        a.scores[(size_t(t) * a.heads + kvh * GROUP + g) * a.max_context + p] = __fmul_rn(sum, a.scale);
+            for (int l = 0; l < 16; ++l) lanes[l] = 0.0f;
+#pragma unroll
+            for (int i = 0; i < DIM; i += 16) {
+#pragma unroll
+                for (int l = 0; l < 4; ++l) {
+                    const float4 q = q4[i / 4 + l];
+                    lanes[4 * l + 0] = __fadd_rn(lanes[4 * l + 0], __fmul_rn(q.x, kf[i + 4 * l + 0]));
+                    lanes[4 * l + 1] = __fadd_rn(lanes[4 * l + 1], __fmul_rn(q.y, kf[i + 4 * l + 1]));
+                    lanes[4 * l + 2] = __fadd_rn(lanes[4 * l + 2], __fmul_rn(q.z, kf[i + 4 * l + 2]));
+                    lanes[4 * l + 3] = __fadd_rn(lanes[4 * l + 3], __fmul_rn(q.w, kf[i + 4 * l + 3]));
+                }
+            }
+            float sum = 0.0f;
+#pragma unroll
+            for (int l = 0; l < 16; ++l) sum = __fadd_rn(sum, lanes[l]);
+            a.scores[(size_t(t0 + j) * a.heads + kvh * GROUP + g) * a.max_context + p] = __fmul_rn(sum, a.scale);
+        }
     }
 }
 
@@ -247,29 +258,51 @@ __global__ void __launch_bounds__(256) attn_softmax_kernel(const AttnArgs a) {
     for (uint32_t p = tid; p < visible; p += 256) s[p] = __fmul_rn(s[p], inv);
 }
 
-// One thread per output value; a CTA covers 128 consecutive values of a token's attended row (one head of 128, two of 64).
+// grid (heads, token tiles), one thread per value of the head. V rows and the tile's probabilities are staged through
+// shared memory in chunks of 64 positions, so every cached row is read once per kTokTile tokens; each thread keeps one
+// accumulator per token and adds p * v position after position, as weighted_sum_f32 does.
+constexpr uint32_t kWChunk = 64;
+
 __global__ void __launch_bounds__(128) attn_weighted_kernel(const AttnArgs a) {
-    const uint32_t t = blockIdx.y, dim = a.dim;
-    const uint32_t col = blockIdx.x * 128 + threadIdx.x;  // index into [heads*dim]
-    if (col >= a.heads * dim) return;
-    const uint32_t h = col / dim, i = col % dim, kvh = h / (a.heads / a.kv_heads);
-    const uint32_t visible = *a.position + t + 1;
-    const float* w = a.scores + (size_t(t) * a.heads + h) * a.max_context;
-    const __half* v = a.v_cache + size_t(kvh) * a.max_context * dim + i;
-    float acc = 0.0f;
-    uint32_t p = 0;
-    for (; p + 8 <= visible; p += 8) {
-        float wv[8], vv[8];
+    extern __shared__ __align__(16) unsigned char wraw[];  // V chunk [kWChunk][dim] f16 | probabilities [kTokTile][kWChunk] f32
+    const uint32_t h = blockIdx.x, t0 = blockIdx.y * kTokTile, dim = a.dim, tid = threadIdx.x;
+    const uint32_t tn = min(kTokTile, a.n - t0);
+    const uint32_t kvh = h / (a.heads / a.kv_heads);
+    const uint32_t base_visible = *a.position + t0 + 1, last_visible = base_visible + tn - 1;
+    __half* vs = reinterpret_cast<__half*>(wraw);
+    float* ws = reinterpret_cast<float*>(wraw + size_t(kWChunk) * dim * sizeof(__half));
+    const __half* vbase = a.v_cache + size_t(kvh) * a.max_context * dim;
+    float acc[kTokTile];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            wv[j] = w[p + j];
-            vv[j] = __half2float(v[size_t(p + j) * dim]);
+    for (int j = 0; j < int(kTokTile); ++j) acc[j] = 0.0f;
+    for (uint32_t c0 = 0; c0 < last_visible; c0 += kWChunk) {
+        const uint32_t cn = min(kWChunk, last_visible - c0);
+        __syncthreads();  // the previous chunk is fully consumed
+        for (uint32_t i = tid; i < cn * dim / 8; i += 128) {
+            reinterpret_cast<uint4*>(vs)[i] = reinterpret_cast<const uint4*>(vbase + size_t(c0) * dim)[i];
         }
+        for (uint32_t i = tid; i < tn * kWChunk; i += 128) {
+            const uint32_t j = i / kWChunk, pp = c0 + i % kWChunk;
+            ws[i] = pp < base_visible + j ? a.scores[(size_t(t0 + j) * a.heads + h) * a.max_context + pp] : 0.0f;
+        }
+        __syncthreads();
+        if (tid < dim) {
+            for (uint32_t pp = 0; pp < cn; ++pp) {
+                const float v = __half2float(vs[pp * dim + tid]);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc = __fadd_rn(acc, __fmul_rn(wv[j], vv[j]));
+                for (int j = 0; j < int(kTokTile); ++j) {
+                    // a position past token j's causal limit must not touch its sum at all (adding 0*v could turn -0 into +0)
+                    if (c0 + pp < base_visible + j && j < int(tn)) acc[j] = __fadd_rn(acc[j], __fmul_rn(ws[j * kWChunk + pp], v));
+                }
+            }
+        }
     }
-    for (; p < visible; ++p) acc = __fadd_rn(acc, __fmul_rn(w[p], __half2float(v[size_t(p) * dim])));
-    a.out[size_t(t) * a.heads * dim + col] = acc;
+    if (tid < dim) {
+#pragma unroll
+        for (int j = 0; j < int(kTokTile); ++j) {
+            if (j < int(tn)) a.out[size_t(t0 + j) * a.heads * dim + size_t(h) * dim + tid] = acc[j];
+        }
+    }
 }
 
 }  // namespace
@@ -376,19 +409,26 @@ size_t attn_scratch_floats(uint32_t n, uint32_t heads, uint32_t max_context) { r
 void launch_attention(const AttnArgs& a, cudaStream_t s) {
     const uint32_t group = a.heads / a.kv_heads;
     if (a.dim % 16 != 0 || a.dim > 256 || group > kMaxGroup) throw CudaError("cuda: head size must be a multiple of 16 up to 256 and at most 16 query heads per K/V head");
-    const dim3 grid((a.max_visible + 127) / 128, a.kv_heads, a.n);
-    const size_t smem = size_t(group) * a.dim * sizeof(float);
+    const uint32_t tiles = (a.n + kTokTile - 1) / kTokTile;
+    const dim3 grid((a.max_visible + 127) / 128, a.kv_heads, tiles);
+    const size_t smem = size_t(kTokTile) * group * a.dim * sizeof(float);
+#define BK_SCORES(G)                                                                        \
+    if (a.dim == 128) attn_scores_kernel<G, 128><<<grid, 128, smem, s>>>(a);                \
+    else if (a.dim == 64) attn_scores_kernel<G, 64><<<grid, 128, smem, s>>>(a);             \
+    else throw CudaError("cuda: attention takes head sizes 64 and 128")
     switch (group) {
-        case 1: attn_scores_kernel<1><<<grid, 128, smem, s>>>(a); break;
-        case 2: attn_scores_kernel<2><<<grid, 128, smem, s>>>(a); break;
-        case 4: attn_scores_kernel<4><<<grid, 128, smem, s>>>(a); break;
-        case 8: attn_scores_kernel<8><<<grid, 128, smem, s>>>(a); break;
+        case 1: BK_SCORES(1); break;
+        case 2: BK_SCORES(2); break;
+        case 4: BK_SCORES(4); break;
+        case 8: BK_SCORES(8); break;
         default: throw CudaError("cuda: query heads per K/V head must be 1, 2, 4 or 8");
     }
+#undef BK_SCORES
     BK_CUDA(cudaGetLastError());
     attn_softmax_kernel<<<dim3(a.heads, a.n), 256, 0, s>>>(a);
     BK_CUDA(cudaGetLastError());
-    attn_weighted_kernel<<<dim3((a.heads * a.dim + 127) / 128, a.n), 128, 0, s>>>(a);
+    const size_t smem_w = size_t(kWChunk) * a.dim * sizeof(__half) + size_t(kTokTile) * kWChunk * sizeof(float);
+    attn_weighted_kernel<<<dim3(a.heads, tiles), 128, smem_w, s>>>(a);
     BK_CUDA(cudaGetLastError());
 }
 
