@@ -136,8 +136,11 @@ struct Session {
     uint32_t* d_history_len() const { return scalars.as<uint32_t>() + 2; }
 
     ~Session() {
-        if (comm != nullptr && Nccl::get().ok()) Nccl::get().CommDestroy(comm);
+        if (stream) cudaStreamSynchronize(stream);
+        // A graph that captured collectives keeps the communicator busy: release it before the communicator.
         if (step_graph) cudaGraphExecDestroy(step_graph);
+        step_graph = nullptr;
+        if (comm != nullptr && Nccl::get().ok()) Nccl::get().CommDestroy(comm);
         if (ev0) cudaEventDestroy(ev0);
         if (ev1) cudaEventDestroy(ev1);
         if (stream) cudaStreamDestroy(stream);

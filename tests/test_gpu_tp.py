@@ -12,8 +12,12 @@ import helpers as H
 
 pytestmark = pytest.mark.gpu
 
-WORKER = textwrap.dedent('''
-    import os, sys
+WORKER = textwrap.dedent(r'''
+    import os, sys, faulthandler
+    log = open(os.path.join(sys.argv[2], "rank%s.log" % os.environ.get("RANK", "0")), "w")
+    faulthandler.dump_traceback_later(90, exit=True, file=log)   # a stuck rank reports where, then exits
+    def mark(what):
+        log.write(what + "\n"); log.flush()
     sys.path.insert(0, sys.argv[1]); sys.path.insert(0, os.path.join(sys.argv[1], "tests"))
     import numpy as np
     import torch, torch.distributed as dist
@@ -25,13 +29,18 @@ WORKER = textwrap.dedent('''
     spec = synth.tiny(synth.MISTRAL_7B, layers=2, vocab=1024, hidden=1024, heads=8, kv_heads=4, ffn=2048, context=512)
     model = synth.perturb_norms(synth.generate(spec, seed=4))
     toks = synth.random_tokens(spec, 80, seed=5)
+    mark("model ready")
     s = parallel.tensor_parallel_session(model)
+    mark("session ready")
     got = [s.eval(toks[:40]).copy()]
+    mark("prefill done")
     for i in range(40, 44):
         got.append(s.eval(toks[i:i + 1]).copy())
+    mark("single steps done")
     got.append(s.eval_all(toks[44:53]).copy())
     s.rollback(42)
     ids, logits = s.generate_greedy(int(toks[53]), 6, want_logits=True)
+    mark("greedy done")
     s.close()
     if rank == 0:
         o = H.OracleSession(model)
@@ -57,10 +66,20 @@ def test_two_rank_tensor_parallel_matches_the_oracle(tmp_path):
     script = tmp_path / "tp_worker.py"
     script.write_text(WORKER)
     port = 29700 + os.getpid() % 200
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", NCCL_IB_DISABLE="1", NCCL_SOCKET_IFNAME="lo", NCCL_DEBUG="WARN")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
            "--master-port", str(port), str(script), H.ROOT, str(tmp_path)]
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
-    assert r.returncode == 0, (r.stdout[-1500:], r.stderr[-3000:])
+    try:
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=200, env=env)
+    except subprocess.TimeoutExpired as e:
+        logs = {f: open(tmp_path / f).read() for f in os.listdir(tmp_path) if f.endswith(".log")}
+        pytest.fail(f"tensor-parallel workers did not finish: {logs} {str(e.stderr)[-2000:]}")
+    logs = {f: open(tmp_path / f).read() for f in os.listdir(tmp_path) if f.endswith(".log")}
+    if r.returncode != 0:
+        out_dir = os.path.join(H.ROOT, "gpurun_out")
+        os.makedirs(out_dir, exist_ok=True)
+        with open(os.path.join(out_dir, "tp_test_failure.log"), "w") as f:
+            f.write(r.stdout + "\n---- stderr ----\n" + r.stderr + "\n---- rank logs ----\n" + repr(logs))
+    assert r.returncode == 0, (logs, r.stdout[-1500:], r.stderr[-3000:])
     a, b = np.load(tmp_path / "logits0.npy"), np.load(tmp_path / "logits1.npy")
     assert np.array_equal(a, b)  # every rank holds the full, identical logits
