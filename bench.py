@@ -188,7 +188,7 @@ def run_reference_arm(args):
     if rank != 0:
         return
     spec, prompt, decode = workload_for(args)
-    model = synth.generate(spec, seed=0)
+    model = synth.generate(spec, seed=0, share_layers=spec.layers * spec.hidden * spec.ffn > 1e9)
     threads = os.cpu_count() or 1
     sp, sd = cpu_sample_sizes(spec)
     kind, kernels, run, close = cpu_engine(model, spec, threads)
@@ -222,6 +222,9 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    # single node: NCCL's bootstrap must not depend on the container's host name resolving
+    os.environ.setdefault("NCCL_SOCKET_IFNAME", "lo")
+    os.environ.setdefault("NCCL_IB_DISABLE", "1")
     import torch
     dist = None
     if world > 1:
@@ -232,10 +235,17 @@ def main():
     from brisk_llm_b200 import engine
 
     spec, prompt, decode = workload_for(args)
-    model = synth.generate(spec, seed=0)
+    big = spec.layers * spec.hidden * spec.ffn > 1e9  # 7B-class: draw one layer's weights and reuse them (same shapes and distributions)
+    model = synth.generate(spec, seed=0, share_layers=big)
     ids = synth.random_tokens(spec, prompt, seed=1)
-    sess = engine.CudaSession(model, max_context=spec.context, device=local)
+    tensor_parallel = world > 1 and args.config == "mistral-7b-q4_0"
+    if tensor_parallel:
+        from brisk_llm_b200 import parallel
+        sess = parallel.tensor_parallel_session(model, max_context=spec.context)
+    else:
+        sess = engine.CudaSession(model, max_context=spec.context, device=local)
     weight_bytes = model.weight_bytes()
+    jobs = 1 if tensor_parallel else world  # sequences decoded at once by the whole job
 
     def barrier():
         torch.cuda.synchronize()
@@ -306,22 +316,24 @@ def main():
     if rank == 0:
         peak, peak_kind = peaks()
         tokens = args.steps * decode
-        value = world * tokens / (dec_ms * 1e-3)
-        achieved = weight_bytes * tokens / (dec_ms * 1e-3) / 1e9
+        value = jobs * tokens / (dec_ms * 1e-3)
+        achieved = weight_bytes / (world if tensor_parallel else 1) * tokens / (dec_ms * 1e-3) / 1e9  # per GPU
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmups,
-                "ms_per_step": (pre_ms + dec_ms) / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "ms_per_step": (pre_ms + dec_ms) / args.steps, "higher_is_better": True, "scaling": "strong" if tensor_parallel else "weak",
+                "vs_baseline": None,
                 "dtype": "int8 dot products, f32 accumulate (f16 K/V cache)", "data": "synthetic",
-                "config": describe(spec, prompt, decode, {"parallelism": "replicas only" if world > 1 else "single GPU"}),
-                "prefill_tokens_per_s": world * args.steps * prompt / (pre_ms * 1e-3),
+                "config": describe(spec, prompt, decode, {"parallelism": f"tensor parallel x{world} (row-split matrices, all-gathers)" if tensor_parallel
+                                                          else "replicas only" if world > 1 else "single GPU"}),
+                "prefill_tokens_per_s": jobs * args.steps * prompt / (pre_ms * 1e-3),
                 "decode_us_per_token": 1e3 * dec_ms / tokens,
                 "wall_s_timed_region": t_wall,
-                "e2e": {"value": world * tokens / e_dec, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                        "prefill_tokens_per_s": world * args.steps * prompt / e_pre},
+                "e2e": {"value": jobs * tokens / e_dec, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                        "prefill_tokens_per_s": jobs * args.steps * prompt / e_pre},
                 "gpu_launches": launches,
                 "clocks": clocks,
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                              "traffic": None, "peak_kind": f"of {peak_kind}", "kernel": "decode step (all kernels of one token)",
-                             "algorithmic_bytes_per_token": weight_bytes}}
+                             "algorithmic_bytes_per_token": weight_bytes // (world if tensor_parallel else 1)}}
         if args.profile:
             line["profile_run"] = True
             line.pop("e2e")

@@ -67,6 +67,7 @@ SIGNATURES = {
     "brisk_cuda_matmul_seconds": (C.c_int, [C.c_int32, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint32,
                                             C.c_uint32, C.POINTER(C.c_double), C.c_char_p, C.c_size_t]),
     "brisk_cuda_argmax_static": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p, C.c_char_p, C.c_size_t]),
+    "brisk_cuda_profile": (C.c_int, [C.c_void_p, C.c_int, C.c_char_p, C.c_size_t]),
     "brisk_cuda_debug_buffer": (C.c_int, [C.c_void_p, C.c_char_p, _FP, C.c_uint64]),
     "brisk_cuda_tp_unique_id": (C.c_int, [C.c_void_p, C.c_char_p, C.c_size_t]),
 }

@@ -195,12 +195,45 @@ __global__ void __launch_bounds__(kDecWarps * 32) dec_matvec_kernel(const DecMat
             }
         }
     } else {
-        for (uint32_t i = threadIdx.x; i < cols; i += kT) xf[i] = p.x[i];
+        // long rows: the same, eight loads at a time per thread
+        double part = 0.0;
+        for (uint32_t base = 0; base < cols; base += 8 * kT) {
+            float xv[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const uint32_t i = base + threadIdx.x + k * kT;
+                xv[k] = i < cols ? p.x[i] : 0.0f;
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const uint32_t i = base + threadIdx.x + k * kT;
+                if (i < cols) xf[i] = xv[k];
+                part += double(__fmul_rn(xv[k], xv[k]));
+            }
+        }
         if (p.weight != nullptr) {
+            part = warp_sum(part);
+            if (lane == 0) red[warp] = part;
             __syncthreads();
-            const float scale = cta_rms_scale(xf, cols, p.eps, red);
+            double total = 0.0;
+#pragma unroll
+            for (int w = 0; w < kDecWarps; ++w) total += red[w];
+            const float mean = float(total / double(cols));
+            const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, p.eps)));
             stamp(p.trace, 2);
-            for (uint32_t i = threadIdx.x; i < cols; i += kT) xf[i] = __fmul_rn(__fmul_rn(xf[i], scale), p.weight[i]);
+            for (uint32_t base = 0; base < cols; base += 8 * kT) {
+                float wv[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const uint32_t i = base + threadIdx.x + k * kT;
+                    wv[k] = i < cols ? p.weight[i] : 0.0f;
+                }
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const uint32_t i = base + threadIdx.x + k * kT;
+                    if (i < cols) xf[i] = __fmul_rn(__fmul_rn(xf[i], scale), wv[k]);  // same thread wrote xf[i]
+                }
+            }
         }
     }
     __syncthreads();
@@ -339,24 +372,17 @@ void launch_dec_one(DecMatParams& p, uint32_t sms, cudaStream_t s) {
     const uint32_t want = (groups + kDecWarps - 1) / kDecWarps;
     const uint32_t grid = want < sms ? want : sms;  // one CTA per SM at most; warps walk the remaining row groups
     const size_t smem = size_t(p.cols) * 4 + p.cols + (p.cols / 32) * 8 + 64;
+    // Ring depth: as deep as keeps the weights in flight per lane (matrices x rows x depth units of 16 bytes) at 8 or
+    // fewer, so that they stay in registers; one iteration ahead is enough when a warp has only a few iterations.
     const uint32_t iters = ((groups + grid * kDecWarps - 1) / (grid * kDecWarps)) * ((p.m[0].units + 31) / 32);
-    if (iters > 4) {
-        auto kernel = dec_matvec_kernel<F, RW, PAIR, 4>;
-        static bool raised = false;  // per instantiation
-        if (smem > 40 * 1024 && !raised) {
-            BK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
-            raised = true;
-        }
+    constexpr int kRegsPerIter = (PAIR ? 2 : 1) * RW * int(sizeof(typename F::W) / 4);  // registers one iteration's weights take
+    constexpr int kDeep = kRegsPerIter * 4 <= 48 ? 4 : kRegsPerIter * 2 <= 48 ? 2 : 1;
+    auto go = [&](auto kernel) {
+        if (smem > 40 * 1024) BK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
         launch_pdl(kernel, dim3(grid), dim3(kDecWarps * 32), smem, s, p);
-    } else {
-        auto kernel = dec_matvec_kernel<F, RW, PAIR, 1>;
-        static bool raised = false;
-        if (smem > 40 * 1024 && !raised) {
-            BK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
-            raised = true;
-        }
-        launch_pdl(kernel, dim3(grid), dim3(kDecWarps * 32), smem, s, p);
-    }
+    };
+    if (iters > 2 && kDeep > 1) go(dec_matvec_kernel<F, RW, PAIR, kDeep>);
+    else go(dec_matvec_kernel<F, RW, PAIR, 1>);
 }
 
 template <class F>
@@ -368,12 +394,13 @@ void dispatch_dec(DecMatParams& p, bool pair, uint32_t sms, cudaStream_t s) {
         div4 = div4 && p.m[i].rows % 4 == 0;
         div2 = div2 && p.m[i].rows % 2 == 0;
     }
-    // Rows per warp: the most that still gives every SM a full CTA.
-    const uint32_t enough = sms * kDecWarps;
-    constexpr bool heavy = std::is_same_v<F, FQ6_K>;
+    // Rows per warp: more rows per warp share the activation loads and the serial adds (fewer instructions per weight
+    // byte), as long as about half of all warps still get a row group.
+    const uint32_t enough = sms * kDecWarps / 2;
+    constexpr bool heavy = sizeof(typename F::W) > 32;  // K-quants: many registers per row, cap the rows per warp
     int rw = 1;
     if (div4 && !heavy && rows / 4 >= enough) rw = 4;
-    else if (div2 && rows / 2 >= enough) rw = 2;
+    else if (div2 && (!heavy || !pair) && rows / 2 >= enough) rw = 2;
     if (pair) {
         if (rw == 4) launch_dec_one<F, 4, true>(p, sms, s);
         else if (rw == 2) launch_dec_one<F, 2, true>(p, sms, s);

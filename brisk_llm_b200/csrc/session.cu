@@ -127,6 +127,52 @@ struct Session {
     cudaGraphExec_t step_graph = nullptr;
     uint64_t step_graph_nodes = 0;
     uint64_t launches = 0;  // kernels launched by the current call
+    // Per-phase device time, the counterpart of the reference's Session::Profile / BRISK_GPU_PROFILE
+    // (src/model.h:242-245, src/metal/metal_session.mm:711-719). Enabled by brisk_cuda_profile_enable(): every phase is
+    // then bracketed by CUDA events and the single-token step runs without its graph.
+    enum Phase : int { PH_EMBED, PH_QKV, PH_ATTENTION, PH_ATTN_OUT, PH_GATE_UP, PH_DOWN, PH_HEAD, PH_EXCHANGE, PH_SAMPLE, PH_COUNT };
+    bool profiling = false;
+    double phase_ms[PH_COUNT] = {};
+    uint64_t phase_calls[PH_COUNT] = {};
+    std::vector<cudaEvent_t> event_pool;
+    struct Span { int phase; cudaEvent_t a, b; };
+    std::vector<Span> spans;
+    size_t events_used = 0;
+    cudaEvent_t take_event() {
+        if (events_used == event_pool.size()) {
+            cudaEvent_t e;
+            BK_CUDA(cudaEventCreate(&e));
+            event_pool.push_back(e);
+        }
+        return event_pool[events_used++];
+    }
+    struct Scope {
+        Session* s;
+        Span span;
+        Scope(Session* session, int phase) : s(session->profiling ? session : nullptr) {
+            if (s) {
+                span = {phase, s->take_event(), s->take_event()};
+                cudaEventRecord(span.a, s->stream);
+            }
+        }
+        ~Scope() {
+            if (s) {
+                cudaEventRecord(span.b, s->stream);
+                s->spans.push_back(span);
+            }
+        }
+    };
+    void collect_profile() {  // after the stream is idle
+        for (const Span& sp : spans) {
+            float ms = 0;
+            if (cudaEventElapsedTime(&ms, sp.a, sp.b) == cudaSuccess) {
+                phase_ms[sp.phase] += ms;
+                phase_calls[sp.phase] += 1;
+            }
+        }
+        spans.clear();
+        events_used = 0;
+    }
     brisk_cuda_stats stats{};
     std::string error;
 
@@ -141,6 +187,7 @@ struct Session {
         if (step_graph) cudaGraphExecDestroy(step_graph);
         step_graph = nullptr;
         if (comm != nullptr && Nccl::get().ok()) Nccl::get().CommDestroy(comm);
+        for (cudaEvent_t e : event_pool) cudaEventDestroy(e);
         if (ev0) cudaEventDestroy(ev0);
         if (ev1) cudaEventDestroy(ev1);
         if (stream) cudaStreamDestroy(stream);
@@ -388,6 +435,7 @@ struct Session {
     // Tensor parallel: this rank's [n][rows_l] slice -> every rank's [n][rows_l * tp] (store or add), by an all-gather
     // into [rank][n][rows_l] and a re-layout kernel. No-op for a single GPU (kernels then write dst directly).
     void exchange(const float* local, float* dst, uint32_t n, uint32_t rows_l, bool add) {
+        Scope sc(this, PH_EXCHANGE);
         const Nccl& nccl = Nccl::get();
         nccl.check(nccl.AllGather(local, tp_gathered.p, size_t(n) * rows_l, kNcclFloat, comm, stream), "ncclAllGather");
         launch_tp_unpack(tp_gathered.as<float>(), dst, n, rows_l, uint32_t(tp_size), add, stream);
@@ -398,7 +446,10 @@ struct Session {
     // position + n. single = true takes the fused single-token kernels (n == 1).
     void run_layers(uint32_t n, bool all_logits, uint32_t max_visible, bool single) {
         float* hid = hidden_b.as<float>();
-        launch_embed(embd, tokens_dev.as<int32_t>(), n, hid, stream);
+        {
+            Scope sc(this, PH_EMBED);
+            launch_embed(embd, tokens_dev.as<int32_t>(), n, hid, stream);
+        }
         ++launches;
         const float attn_scale = 1.0f / std::sqrt(static_cast<float>(head_dim));
         const bool tp = tp_size > 1;
@@ -432,8 +483,11 @@ struct Session {
 
         for (uint32_t l = 0; l < n_layers; ++l) {
             const Layer& L = layers[l];
-            apply({{L.q, q_b.as<float>(), q_dim_l}, {L.k, k_b.as<float>(), kv_dim_l}, {L.v, v_b.as<float>(), kv_dim_l}}, hid, hidden, L.attn_norm, hidden,
-                  EPI_STORE);
+            {
+                Scope sc(this, PH_QKV);
+                apply({{L.q, q_b.as<float>(), q_dim_l}, {L.k, k_b.as<float>(), kv_dim_l}, {L.v, v_b.as<float>(), kv_dim_l}}, hid, hidden, L.attn_norm,
+                      hidden, EPI_STORE);
+            }
 
             RopeArgs r{};
             r.q = q_b.as<float>(); r.k = k_b.as<float>(); r.v = v_b.as<float>();
@@ -446,13 +500,16 @@ struct Session {
             at.scores = partial.as<float>(); at.position = d_position();
             at.n = n; at.heads = heads_l; at.kv_heads = kv_heads_l; at.dim = head_dim; at.max_context = uint32_t(max_context);
             at.max_visible = max_visible; at.scale = attn_scale;
-            if (single) {
-                launch_dec_attention(r, at, stream);
-                launches += 2;
-            } else {
-                launch_qk_norm_rope_store(r, stream);
-                launch_attention(at, stream);
-                launches += 4;
+            {
+                Scope sc(this, PH_ATTENTION);
+                if (single) {
+                    launch_dec_attention(r, at, stream);
+                    launches += 2;
+                } else {
+                    launch_qk_norm_rope_store(r, stream);
+                    launch_attention(at, stream);
+                    launches += 4;
+                }
             }
 
             // attention output projection + residual
@@ -460,9 +517,13 @@ struct Session {
             if (tp) {
                 exchange(attended_b.as<float>(), full_b.as<float>(), n, q_dim_l, false);
                 attended = full_b.as<float>();
-                apply({{L.o, tp_local.as<float>(), hidden_l}}, attended, q_dim, L.attn_sub_norm, q_dim, EPI_STORE);
+                {
+                    Scope sc(this, PH_ATTN_OUT);
+                    apply({{L.o, tp_local.as<float>(), hidden_l}}, attended, q_dim, L.attn_sub_norm, q_dim, EPI_STORE);
+                }
                 exchange(tp_local.as<float>(), hid, n, hidden_l, true);
             } else {
+                Scope sc(this, PH_ATTN_OUT);
                 apply({{L.o, hid, hidden}}, attended, q_dim, L.attn_sub_norm, q_dim, EPI_ADD);
             }
 
@@ -470,21 +531,35 @@ struct Session {
             const Epilogue act_epi = arch == BRISK_ARCH_BITNET ? EPI_RELU2_MUL : EPI_SILU_MUL;
             const float* gated = ffn_b.as<float>();
             if (tp) {
-                apply({{L.gate, tp_local.as<float>(), ffn_l}, {L.up, nullptr, ffn_l}}, hid, hidden, L.ffn_norm, hidden, act_epi);
+                {
+                    Scope sc(this, PH_GATE_UP);
+                    apply({{L.gate, tp_local.as<float>(), ffn_l}, {L.up, nullptr, ffn_l}}, hid, hidden, L.ffn_norm, hidden, act_epi);
+                }
                 exchange(tp_local.as<float>(), ffn_b.as<float>(), n, ffn_l, false);
-                apply({{L.down, tp_local.as<float>(), hidden_l}}, gated, ffn, L.ffn_sub_norm, ffn, EPI_STORE);
+                {
+                    Scope sc(this, PH_DOWN);
+                    apply({{L.down, tp_local.as<float>(), hidden_l}}, gated, ffn, L.ffn_sub_norm, ffn, EPI_STORE);
+                }
                 exchange(tp_local.as<float>(), hid, n, hidden_l, true);
             } else {
-                apply({{L.gate, ffn_b.as<float>(), ffn}, {L.up, nullptr, ffn}}, hid, hidden, L.ffn_norm, hidden, act_epi);
+                {
+                    Scope sc(this, PH_GATE_UP);
+                    apply({{L.gate, ffn_b.as<float>(), ffn}, {L.up, nullptr, ffn}}, hid, hidden, L.ffn_norm, hidden, act_epi);
+                }
+                Scope sc(this, PH_DOWN);
                 apply({{L.down, hid, hidden}}, gated, ffn, L.ffn_sub_norm, ffn, EPI_ADD);
             }
         }
         const uint32_t rows = all_logits ? n : 1;
         const float* last = all_logits ? hid : hid + size_t(n - 1) * hidden;
         if (tp) {
-            apply({{head, tp_local.as<float>(), vocab_l}}, last, hidden, output_norm, hidden, EPI_STORE, rows);
+            {
+                Scope sc(this, PH_HEAD);
+                apply({{head, tp_local.as<float>(), vocab_l}}, last, hidden, output_norm, hidden, EPI_STORE, rows);
+            }
             exchange(tp_local.as<float>(), logits_b.as<float>(), rows, vocab_l, false);
         } else {
+            Scope sc(this, PH_HEAD);
             apply({{head, logits_b.as<float>(), vocab}}, last, hidden, output_norm, hidden, EPI_STORE, rows);
         }
     }
@@ -515,7 +590,7 @@ struct Session {
     void step_on_device() {  // one token whose id is tokens_dev[0] at *d_position()
         if (flags & BRISK_CUDA_FLAG_NO_MEGAKERNEL) {
             forward(1, false, uint32_t(max_context));  // the batched kernels, one token
-        } else if (flags & BRISK_CUDA_FLAG_NO_GRAPH) {
+        } else if ((flags & BRISK_CUDA_FLAG_NO_GRAPH) || profiling) {
             forward_decode();
         } else {
             build_step_graph();
@@ -529,6 +604,7 @@ struct Session {
         stats.h2d_bytes = stats.d2h_bytes = 0;
     }
     void end_call(float ms) {
+        if (profiling) collect_profile();
         stats.device_ms = ms;
         stats.kernel_launches = launches;
     }
@@ -596,8 +672,11 @@ struct Session {
             if (out_logits != nullptr) {
                 BK_CUDA(cudaMemcpyAsync(logit_history.as<float>() + i * vocab, logits_b.p, size_t(vocab) * sizeof(float), cudaMemcpyDeviceToDevice, stream));
             }
-            launch_argmax_advance(logits_b.as<float>(), vocab, d_chosen(), am_val.as<float>(), am_idx.as<int32_t>(), tokens_dev.as<int32_t>(),
-                                  d_position(), history.as<int32_t>(), d_history_len(), stream);
+            {
+                Scope sc(this, PH_SAMPLE);
+                launch_argmax_advance(logits_b.as<float>(), vocab, d_chosen(), am_val.as<float>(), am_idx.as<int32_t>(), tokens_dev.as<int32_t>(),
+                                      d_position(), history.as<int32_t>(), d_history_len(), stream);
+            }
             launches += 2;
         }
         BK_CUDA(cudaEventRecord(ev1, stream));
@@ -710,6 +789,29 @@ int brisk_cuda_get_stats(const brisk_cuda_session* session, brisk_cuda_stats* ou
     if (session == nullptr || out == nullptr) return -1;
     *out = session->s.stats;
     return 0;
+}
+
+int brisk_cuda_profile(brisk_cuda_session* session, int enable, char* json, size_t len) {
+    return guarded(session, [&] {
+        bk::Session& s = session->s;
+        static const char* names[bk::Session::PH_COUNT] = {"embed", "qkv", "attention", "attn_out", "gate_up", "down", "head", "exchange", "sample"};
+        if (json != nullptr && len > 0) {
+            std::string out = "{";
+            for (int i = 0; i < bk::Session::PH_COUNT; ++i) {
+                char buf[128];
+                std::snprintf(buf, sizeof buf, "%s\"%s\": {\"ms\": %.6f, \"calls\": %llu}", i ? ", " : "", names[i], s.phase_ms[i],
+                              static_cast<unsigned long long>(s.phase_calls[i]));
+                out += buf;
+            }
+            out += "}";
+            std::snprintf(json, len, "%s", out.c_str());
+        }
+        for (int i = 0; i < bk::Session::PH_COUNT; ++i) {
+            s.phase_ms[i] = 0;
+            s.phase_calls[i] = 0;
+        }
+        s.profiling = enable != 0;
+    });
 }
 
 int brisk_cuda_debug_buffer(brisk_cuda_session* session, const char* name, float* out, uint64_t count) {

@@ -75,6 +75,14 @@ class CudaSession:
         """Like eval(), one row of logits per token; at most 64 tokens."""
         return self._eval(tokens, True, copy)
 
+    def profile(self, enable: bool = True) -> dict:
+        """Per-phase device milliseconds accumulated since the previous call (then cleared); switches profiling on/off."""
+        import json
+        buf = C.create_string_buffer(2048)
+        if self._lib.brisk_cuda_profile(self._h, int(enable), buf, len(buf)) != 0:
+            self._fail()
+        return json.loads(buf.value.decode())
+
     def debug_buffer(self, name: str, count: int) -> np.ndarray:
         out = np.empty(count, np.float32)
         if self._lib.brisk_cuda_debug_buffer(self._h, name.encode(), out.ctypes.data_as(C.POINTER(C.c_float)), count) != 0:

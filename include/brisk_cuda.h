@@ -194,6 +194,13 @@ int brisk_cuda_matmul_seconds(int32_t type, const void* w, uint64_t rows, uint64
 int brisk_cuda_argmax_static(const float* logits, uint32_t vocab, uint32_t rows, int32_t* out_tokens, void* stream, char* err,
                              size_t errlen);
 
+/* Per-phase device time, the counterpart of Session::profile() / BRISK_PROFILE (src/model.h:242-245,
+ * src/main.cpp:302-306) and BRISK_GPU_PROFILE (src/metal/metal_session.mm:711-719). Writes the time accumulated since
+ * the previous call as JSON ({"qkv": {"ms": .., "calls": ..}, ...}) into `json` (may be NULL), clears the counters, and
+ * switches profiling on or off. While it is on, every phase is bracketed by CUDA events and the single-token step
+ * runs kernel by kernel instead of as a graph, so totals are slower than an unprofiled run: use it for shares. */
+int brisk_cuda_profile(brisk_cuda_session* session, int enable, char* json, size_t len);
+
 /* Debug hook, the counterpart of the BRISK_GPU_DEBUG / BRISK_CPU_DEBUG dumps (src/metal/metal_session.mm:1073-1100,
  * src/model.cpp:1183-1192): copies the first `count` floats of one scratch buffer as the last batch left it.
  * name: "hidden" (residual stream [n][hidden]), "query" (after norm and RoPE), "attended", "ffn" (gated activation),
