@@ -137,16 +137,7 @@ __global__ void __launch_bounds__(kDecWarps * 32) dec_matvec_kernel(const DecMat
     };
 #pragma unroll
     for (int d = 0; d < kDepth; ++d) issue(wq[d]);
-    constexpr int kNormPrefetch = 4;  // norm weights held in registers: covers rows up to 2048 values
-    float nw[kNormPrefetch];
     const uint32_t cols = p.cols;
-    if (p.weight != nullptr) {
-#pragma unroll
-        for (int k = 0; k < kNormPrefetch; ++k) {
-            const uint32_t i = threadIdx.x + k * (kDecWarps * 32);
-            nw[k] = i < cols ? p.weight[i] : 0.0f;
-        }
-    }
     if (p.pdl == 1) pdl_launch_dependents();
     pdl_wait();
     stamp(p.trace, 1);
@@ -162,76 +153,53 @@ __global__ void __launch_bounds__(kDecWarps * 32) dec_matvec_kernel(const DecMat
     // Loads are batched in registers (8 per thread in flight) so that their latencies overlap.
     float* xf = reinterpret_cast<float*>(smem_raw);
     constexpr uint32_t kT = kDecWarps * 32;
-    if (cols <= 8 * kT) {
-        float xv[8];
+    // x as float4s (row lengths are multiples of 32), up to 8 per thread at a time so the loads overlap
+    const float4* x4 = reinterpret_cast<const float4*>(p.x);
+    float4* xf4 = reinterpret_cast<float4*>(xf);
+    const uint32_t n4 = cols / 4;
+    double part = 0.0;
+    for (uint32_t base = 0; base < n4; base += 8 * kT) {
+        float4 xv[8];
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-            const uint32_t i = threadIdx.x + k * kT;
-            xv[k] = i < cols ? p.x[i] : 0.0f;
+            const uint32_t i = base + threadIdx.x + k * kT;
+            xv[k] = i < n4 ? x4[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         }
-        if (p.weight != nullptr) {
-            double part = 0.0;
 #pragma unroll
-            for (int k = 0; k < 8; ++k) part += double(__fmul_rn(xv[k], xv[k]));  // padding adds exact zeros
-            part = warp_sum(part);
-            if (lane == 0) red[warp] = part;
-            __syncthreads();
-            double total = 0.0;
-#pragma unroll
-            for (int w = 0; w < kDecWarps; ++w) total += red[w];
-            const float mean = float(total / double(cols));
-            const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, p.eps)));
-            stamp(p.trace, 2);
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const uint32_t i = threadIdx.x + k * kT;
-                if (i < cols) xf[i] = __fmul_rn(__fmul_rn(xv[k], scale), k < kNormPrefetch ? nw[k] : p.weight[i]);
-            }
-        } else {
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const uint32_t i = threadIdx.x + k * kT;
-                if (i < cols) xf[i] = xv[k];
-            }
+        for (int k = 0; k < 8; ++k) {
+            const uint32_t i = base + threadIdx.x + k * kT;
+            if (i < n4) xf4[i] = xv[k];
+            part += double(__fmul_rn(xv[k].x, xv[k].x));  // padding adds exact zeros
+            part += double(__fmul_rn(xv[k].y, xv[k].y));
+            part += double(__fmul_rn(xv[k].z, xv[k].z));
+            part += double(__fmul_rn(xv[k].w, xv[k].w));
         }
-    } else {
-        // long rows: the same, eight loads at a time per thread
-        double part = 0.0;
-        for (uint32_t base = 0; base < cols; base += 8 * kT) {
-            float xv[8];
+    }
+    if (p.weight != nullptr) {
+        part = warp_sum(part);
+        if (lane == 0) red[warp] = part;
+        __syncthreads();
+        double total = 0.0;
+#pragma unroll
+        for (int w = 0; w < kDecWarps; ++w) total += red[w];
+        const float mean = float(total / double(cols));
+        const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, p.eps)));
+        stamp(p.trace, 2);
+        const float4* w4 = reinterpret_cast<const float4*>(p.weight);
+        for (uint32_t base = 0; base < n4; base += 8 * kT) {
+            float4 wv[8];
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
                 const uint32_t i = base + threadIdx.x + k * kT;
-                xv[k] = i < cols ? p.x[i] : 0.0f;
+                wv[k] = i < n4 ? w4[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             }
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
                 const uint32_t i = base + threadIdx.x + k * kT;
-                if (i < cols) xf[i] = xv[k];
-                part += double(__fmul_rn(xv[k], xv[k]));
-            }
-        }
-        if (p.weight != nullptr) {
-            part = warp_sum(part);
-            if (lane == 0) red[warp] = part;
-            __syncthreads();
-            double total = 0.0;
-#pragma unroll
-            for (int w = 0; w < kDecWarps; ++w) total += red[w];
-            const float mean = float(total / double(cols));
-            const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, p.eps)));
-            stamp(p.trace, 2);
-            for (uint32_t base = 0; base < cols; base += 8 * kT) {
-                float wv[8];
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    const uint32_t i = base + threadIdx.x + k * kT;
-                    wv[k] = i < cols ? p.weight[i] : 0.0f;
-                }
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    const uint32_t i = base + threadIdx.x + k * kT;
-                    if (i < cols) xf[i] = __fmul_rn(__fmul_rn(xf[i], scale), wv[k]);  // same thread wrote xf[i]
+                if (i < n4) {  // the same thread wrote xf4[i] above
+                    const float4 xx = xf4[i];
+                    xf4[i] = make_float4(__fmul_rn(__fmul_rn(xx.x, scale), wv[k].x), __fmul_rn(__fmul_rn(xx.y, scale), wv[k].y),
+                                         __fmul_rn(__fmul_rn(xx.z, scale), wv[k].z), __fmul_rn(__fmul_rn(xx.w, scale), wv[k].w));
                 }
             }
         }

@@ -38,9 +38,22 @@ struct ActBuffers {
     }
 };
 
-void multiply(const bk::DevMatrix& m, float* out, const bk::DevAct& a, uint32_t n, cudaStream_t s) {
+// The multiply the session would run for n tokens: the fused single-token kernel (which quantises x itself), the
+// streaming kernel for small batches, the tensor-core kernel for prompt batches.
+void multiply(const bk::DevMatrix& m, float* out, const float* x, const bk::DevAct& a, uint32_t n, uint32_t sms, cudaStream_t s) {
     bk::MatTarget t{m, out, m.rows};
-    if (!(n >= 16 && bk::launch_gemm(&t, 1, a, n, bk::EPI_STORE, s))) bk::launch_matvec(&t, 1, a, n, bk::EPI_STORE, s);
+    if (n == 1) {
+        bk::launch_dec_multiply(&t, 1, x, nullptr, 0.0f, m.cols, bk::EPI_STORE, sms, s);
+    } else if (!(n >= 16 && bk::launch_gemm(&t, 1, a, n, bk::EPI_STORE, s))) {
+        bk::launch_matvec(&t, 1, a, n, bk::EPI_STORE, s);
+    }
+}
+
+uint32_t sm_count() {
+    int dev = 0, count = 0;
+    BK_CUDA(cudaGetDevice(&dev));
+    BK_CUDA(cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev));
+    return uint32_t(count);
 }
 
 }  // namespace
@@ -65,7 +78,7 @@ int brisk_cuda_matmul(int32_t type, const void* w, uint64_t rows, uint64_t cols,
         bk::DevActMut a = ab.act;
         if (!f) a.f32 = nullptr;
         bk::launch_norm_quant(xd.as<float>(), uint32_t(cols), nullptr, 0.0f, uint32_t(n), uint32_t(cols), a, !k && !f, k, nullptr);
-        multiply(m, od.as<float>(), ab.act.view(), uint32_t(n), nullptr);
+        multiply(m, od.as<float>(), xd.as<float>(), ab.act.view(), uint32_t(n), sm_count(), nullptr);
         BK_CUDA(cudaMemcpy(out, od.p, n * rows * 4, cudaMemcpyDeviceToHost));
         return 0;
     } catch (const std::exception& e) {
@@ -100,12 +113,13 @@ int brisk_cuda_matmul_seconds(int32_t type, const void* w, uint64_t rows, uint64
         BK_CUDA(cudaMemcpy(xd.p, xh.data(), xh.size() * 4, cudaMemcpyHostToDevice));
         const bool k = bk::takes_q8_k(type), f = type == bk::T_F16 || type == bk::T_F32;
         bk::launch_norm_quant(xd.as<float>(), uint32_t(cols), nullptr, 0.0f, uint32_t(n), uint32_t(cols), ab.act, !k && !f, k, nullptr);
-        for (uint32_t i = 0; i < 3; ++i) multiply(ms[i % copies], od.as<float>(), ab.act.view(), uint32_t(n), nullptr);
+        const uint32_t sms = sm_count();
+        for (uint32_t i = 0; i < 3; ++i) multiply(ms[i % copies], od.as<float>(), xd.as<float>(), ab.act.view(), uint32_t(n), sms, nullptr);
         cudaEvent_t e0, e1;
         BK_CUDA(cudaEventCreate(&e0));
         BK_CUDA(cudaEventCreate(&e1));
         BK_CUDA(cudaEventRecord(e0, nullptr));
-        for (uint32_t i = 0; i < iterations; ++i) multiply(ms[i % copies], od.as<float>(), ab.act.view(), uint32_t(n), nullptr);
+        for (uint32_t i = 0; i < iterations; ++i) multiply(ms[i % copies], od.as<float>(), xd.as<float>(), ab.act.view(), uint32_t(n), sms, nullptr);
         BK_CUDA(cudaEventRecord(e1, nullptr));
         BK_CUDA(cudaEventSynchronize(e1));
         float ms_total = 0;

@@ -30,45 +30,36 @@ __device__ __forceinline__ float cta_rms_scale(const float* x, uint32_t cols, fl
     return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
 }
 
-// row[0..cols) -> q (int8), d (f16-rounded scale widened to f32), s (sum of the block's q). A warp takes four 32-value
-// blocks at a time so that their shuffle reductions overlap (the prologue of the fused decode kernels is latency-bound).
+// row[0..cols) -> q (int8), d (f16-rounded scale widened to f32), s (sum of the block's q). ONE LANE PER BLOCK: each
+// lane reads its 32 values (as eight float4, in an order rotated by the lane so that the quarter-warps hit distinct
+// shared-memory banks), takes the maximum, divides once, converts and packs. No shuffles - on this GPU a warp shuffle
+// issues at a quarter of the ALU rate, and the reduction-per-block form spent most of its time in them - and no
+// redundant divisions. `row` must be 16-byte aligned.
 __device__ __forceinline__ void cta_quantize_q8_0(const float* row, uint32_t cols, int8_t* q, float* d, int32_t* s) {
-    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const uint32_t nb = cols / 32;
-    for (uint32_t b0 = warp * 4; b0 < nb; b0 += warps * 4) {
-        float v[4], amax[4];
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+    uint32_t* q4 = reinterpret_cast<uint32_t*>(q);
+    for (uint32_t b = threadIdx.x; b < nb; b += blockDim.x) {
+        const uint32_t rot = threadIdx.x & 7;
+        float4 v[8];
+        float amax = 0.0f;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            v[k] = b0 + k < nb ? row[(b0 + k) * 32 + lane] : 0.0f;
-            amax[k] = fabsf(v[k]);
+        for (int i = 0; i < 8; ++i) {
+            v[i] = row4[b * 8 + ((i + rot) & 7)];
+            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
         }
+        const float dd = __fdiv_rn(amax, 127.0f);
+        const float inv = dd != 0.0f ? __fdiv_rn(1.0f, dd) : 0.0f;
+        int sum = 0;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-            for (int k = 0; k < 4; ++k) amax[k] = fmaxf(amax[k], __shfl_xor_sync(0xffffffffu, amax[k], o));
-        int qi[4], sum[4];
-        float dd[4];
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            dd[k] = __fdiv_rn(amax[k], 127.0f);
-            const float inv = dd[k] != 0.0f ? __fdiv_rn(1.0f, dd[k]) : 0.0f;
-            qi[k] = __float2int_rn(__fmul_rn(v[k], inv));
-            sum[k] = qi[k];
+        for (int i = 0; i < 8; ++i) {
+            const int q0 = __float2int_rn(__fmul_rn(v[i].x, inv)), q1 = __float2int_rn(__fmul_rn(v[i].y, inv));
+            const int q2 = __float2int_rn(__fmul_rn(v[i].z, inv)), q3 = __float2int_rn(__fmul_rn(v[i].w, inv));
+            sum += q0 + q1 + q2 + q3;
+            q4[b * 8 + ((i + rot) & 7)] = uint32_t(q0 & 0xFF) | (uint32_t(q1 & 0xFF) << 8) | (uint32_t(q2 & 0xFF) << 16) | (uint32_t(q3 & 0xFF) << 24);
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-            for (int k = 0; k < 4; ++k) sum[k] += __shfl_xor_sync(0xffffffffu, sum[k], o);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            if (b0 + k < nb) {
-                q[(b0 + k) * 32 + lane] = int8_t(qi[k]);
-                if (lane == 0) {
-                    d[b0 + k] = __half2float(__float2half_rn(dd[k]));
-                    s[b0 + k] = sum[k];
-                }
-            }
-        }
+        d[b] = __half2float(__float2half_rn(dd));
+        s[b] = sum;
     }
 }
 
