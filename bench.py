@@ -57,6 +57,12 @@ WORKLOADS = {  # prompt tokens, decode steps, context
 }
 
 
+# DRAM bytes one decoded token moves, composed from ncu captures of each kernel of the step at context ~512
+# (dram__bytes_read + write per launch): four multiplies 1.83 + 2.40 + 1.22 + 3.58 MB and two attention kernels
+# 1.10 + 1.12 MB per layer, plus the output head at its algorithmic 87.5 MB (not captured separately).
+MEASURED_TRAFFIC_PER_TOKEN = {"qwen3-0.6b-q4_0": int(28 * (1.8304 + 2.3954 + 1.2183 + 3.5758 + 1.1003 + 1.1244) * 1e6 + 87_515_136)}
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -332,7 +338,8 @@ def main():
                 "gpu_launches": launches,
                 "clocks": clocks,
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                             "traffic": None, "peak_kind": f"of {peak_kind}", "kernel": "decode step (all kernels of one token)",
+                             "traffic": MEASURED_TRAFFIC_PER_TOKEN.get(args.config) if (world == 1 and not args.layers) else None,
+                             "peak_kind": f"of {peak_kind}", "kernel": "decode step (all kernels of one token)",
                              "algorithmic_bytes_per_token": weight_bytes // (world if tensor_parallel else 1)}}
         if args.profile:
             line["profile_run"] = True
