@@ -182,7 +182,10 @@ __global__ void __launch_bounds__(GWARPS * 32, 2) gemm_q8_kernel(const GemmParam
 
 }  // namespace
 
-bool gemm_supports(int type, uint32_t cols) { return (type == T_Q4_0 || type == T_Q8_0) && cols % (32 * KB) == 0; }
+bool gemm_k_supports(int type);  // gemm_k.cu: the 256-value super-block formats
+void launch_gemm_k(const MatTarget& tg, const DevAct& act, uint32_t n, Epilogue epi, cudaStream_t s);
+
+bool gemm_supports(int type, uint32_t cols) { return ((type == T_Q4_0 || type == T_Q8_0) && cols % (32 * KB) == 0) || gemm_k_supports(type); }
 
 // out = weights x activations for one target (EPI_STORE / EPI_ADD).
 static void launch_gemm_one(const MatTarget& tg, const DevAct& act, uint32_t n, Epilogue epi, cudaStream_t s) {
@@ -215,7 +218,10 @@ bool launch_gemm(const MatTarget* targets, int count, const DevAct& act, uint32_
     for (int i = 0; i < count; ++i) {
         if (!gemm_supports(targets[i].m.type, targets[i].m.cols)) return false;
     }
-    for (int i = 0; i < count; ++i) launch_gemm_one(targets[i], act, n, epi, s);
+    for (int i = 0; i < count; ++i) {
+        if (gemm_k_supports(targets[i].m.type)) launch_gemm_k(targets[i], act, n, epi, s);
+        else launch_gemm_one(targets[i], act, n, epi, s);
+    }
     return true;
 }
 
