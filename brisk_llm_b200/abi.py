@@ -50,9 +50,14 @@ class Stats(C.Structure):
                 ("kv_bytes", C.c_uint64), ("h2d_bytes", C.c_uint64), ("d2h_bytes", C.c_uint64)]
 
 
+class Memory(C.Structure):
+    _fields_ = [("weights", C.c_uint64), ("cache", C.c_uint64), ("scratch", C.c_uint64)]
+
+
 # Every symbol include/brisk_cuda.h declares, with its ctypes signature.
 SIGNATURES = {
     "brisk_cuda_device_count": (C.c_int, []),
+    "brisk_cuda_estimate_memory": (C.c_int, [C.POINTER(Model), C.POINTER(Options), C.POINTER(Memory)]),
     "brisk_cuda_create": (C.c_void_p, [C.POINTER(Model), C.POINTER(Options), C.c_char_p, C.c_size_t]),
     "brisk_cuda_destroy": (None, [C.c_void_p]),
     "brisk_cuda_eval": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_uint64, C.c_int, C.POINTER(_FP)]),

@@ -88,6 +88,41 @@ struct Layer {
     __half *k_cache = nullptr, *v_cache = nullptr;
 };
 
+std::string gb(uint64_t bytes) {
+    char buf[32];
+    std::snprintf(buf, sizeof buf, "%.2f GB", double(bytes) / 1e9);
+    return buf;
+}
+
+// Mirrors the allocations of Session::load for a description and options (tensor-parallel share included).
+brisk_cuda_memory estimate(const brisk_cuda_model& m, const brisk_cuda_options& opt) {
+    brisk_cuda_memory e{};
+    const uint64_t tp = opt.tp_size > 1 ? uint64_t(opt.tp_size) : 1;
+    const uint64_t hidden = m.hidden, ffn = m.ffn, vocab = m.vocab_size, dim = m.head_dim;
+    const uint64_t q_dim = uint64_t(m.head_count) * dim, kv_dim = uint64_t(m.kv_head_count) * dim;
+    const uint64_t ctx = opt.max_context == 0 ? m.context_length : std::min<uint64_t>(opt.max_context, m.context_length);
+    auto planes = [](int type, uint64_t rows, uint64_t cols) { return uint64_t(plane_sizes(type, uint32_t(rows), uint32_t(cols)).total()); };
+    e.weights += planes(m.token_embd.type, vocab, hidden);
+    if (m.output.data != nullptr || tp > 1) e.weights += planes(m.output.data != nullptr ? m.output.type : m.token_embd.type, vocab / tp, hidden);
+    e.weights += hidden * 4;
+    for (uint32_t l = 0; l < m.layer_count; ++l) {
+        const brisk_cuda_layer& L = m.layers[l];
+        e.weights += planes(L.q.type, q_dim / tp, hidden) + planes(L.k.type, kv_dim / tp, hidden) + planes(L.v.type, kv_dim / tp, hidden);
+        e.weights += planes(L.o.type, hidden / tp, q_dim) + planes(L.gate.type, ffn / tp, hidden) + planes(L.up.type, ffn / tp, hidden);
+        e.weights += planes(L.down.type, hidden / tp, ffn);
+        e.weights += (2 * hidden + (L.q_norm ? dim : 0) + (L.k_norm ? dim : 0) + (L.attn_sub_norm ? q_dim : 0) + (L.ffn_sub_norm ? ffn : 0)) * 4;
+    }
+    e.cache = uint64_t(m.layer_count) * 2 * (kv_dim / tp) * ctx * 2;
+    const uint64_t widest = std::max(std::max(hidden, q_dim), ffn), batch = kMaxBatch;
+    e.scratch += batch * (hidden + q_dim / tp + 2 * kv_dim / tp + q_dim / tp + 2 * ffn) * 4;  // residual, q, k, v, attended, gated, up
+    e.scratch += batch * widest * (4 + 1 + 1) + batch * (widest / 32) * 8 + batch * (widest / 16) * 2 + batch * (widest / 256 + 1) * 4;  // activation planes
+    e.scratch += batch * (uint64_t(m.head_count) / tp) * ctx * 4;  // attention scores of one batch
+    e.scratch += uint64_t(kMaxScored) * vocab * 4;                 // logits
+    e.scratch += ctx * dim * 4 + (ctx + 1) * 4;                    // RoPE table, token history
+    if (tp > 1) e.scratch += batch * std::max<uint64_t>(widest, vocab * kMaxScored / batch + 1) * 4 * 2 + batch * std::max(q_dim, ffn) * 4;
+    return e;
+}
+
 bool type_supported(int t) { return t == T_F32 || t == T_F16 || t == T_Q4_0 || t == T_Q8_0 || t == T_Q4_K || t == T_Q6_K || t == T_TQ2_0; }
 
 }  // namespace
@@ -276,6 +311,24 @@ struct Session {
             int count = 0;
             BK_CUDA(cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, opt.device));
             sms = uint32_t(count);
+        }
+        if (std::getenv("BRISK_NO_MEMORY_CHECK") == nullptr) {  // refuse up front what cannot fit (src/memory.cpp:114-135)
+            const brisk_cuda_memory need_bytes = estimate(m, opt);
+            size_t free_bytes = 0, total_bytes = 0;
+            BK_CUDA(cudaMemGetInfo(&free_bytes, &total_bytes));
+            if (const char* fake = std::getenv("BRISK_CUDA_ASSUME_FREE_BYTES")) free_bytes = std::strtoull(fake, nullptr, 10);  // tests
+            const uint64_t total = need_bytes.weights + need_bytes.cache + need_bytes.scratch, margin = uint64_t(256) << 20;
+            if (total + margin > free_bytes) {
+                const uint64_t shortfall = total + margin - free_bytes;
+                std::string hint = "a smaller file or quantisation";
+                if (shortfall <= need_bytes.cache * 7 / 8 + need_bytes.scratch / 2 && max_context > 512) {
+                    hint = "a shorter context (this estimate is for " + std::to_string(max_context) + " tokens and the cache is " + gb(need_bytes.cache) +
+                           "), or " + hint;
+                }
+                throw CudaError("cuda: the model needs about " + gb(total) + " of device memory (" + gb(need_bytes.weights) + " weights, " +
+                                gb(need_bytes.cache) + " cache, " + gb(need_bytes.scratch) + " scratch) but " + gb(free_bytes) +
+                                " is free. Try " + hint + ", or set BRISK_NO_MEMORY_CHECK=1 to proceed regardless.");
+            }
         }
         BK_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
         BK_CUDA(cudaEventCreate(&ev0));
@@ -788,6 +841,14 @@ int brisk_cuda_generate_greedy(brisk_cuda_session* session, int32_t first_token,
 int brisk_cuda_get_stats(const brisk_cuda_session* session, brisk_cuda_stats* out) {
     if (session == nullptr || out == nullptr) return -1;
     *out = session->s.stats;
+    return 0;
+}
+
+int brisk_cuda_estimate_memory(const brisk_cuda_model* model, const brisk_cuda_options* options, brisk_cuda_memory* out) {
+    if (model == nullptr || out == nullptr || model->layers == nullptr) return -1;
+    brisk_cuda_options opt{};
+    if (options != nullptr) opt = *options;
+    *out = bk::estimate(*model, opt);
     return 0;
 }
 

@@ -140,6 +140,17 @@ def tp_unique_id() -> bytes:
     return buf.raw
 
 
+def estimate_memory(host_model, max_context: int = 0, tp_size: int = 1) -> dict:
+    """Device bytes a session would hold (weights / cache / scratch), without touching a GPU."""
+    lib = abi.load_library()
+    opts = abi.Options()
+    opts.max_context, opts.tp_size = max_context, tp_size
+    mem = abi.Memory()
+    if lib.brisk_cuda_estimate_memory(C.byref(host_model.c_model), C.byref(opts), C.byref(mem)) != 0:
+        raise RuntimeError("cuda: memory estimate failed")
+    return {"weights": mem.weights, "cache": mem.cache, "scratch": mem.scratch, "total": mem.weights + mem.cache + mem.scratch}
+
+
 def device_count() -> int:
     return abi.load_library().brisk_cuda_device_count()
 

@@ -118,6 +118,20 @@ typedef struct brisk_cuda_stats {
     uint64_t d2h_bytes;       /* device->host bytes copied by the call                             */
 } brisk_cuda_stats;
 
+/* Device memory a session will hold, before anything is allocated - the device-side analogue of estimate_memory /
+ * MemoryEstimate (src/memory.h:13-24, src/memory.cpp:46-96). */
+typedef struct brisk_cuda_memory {
+    uint64_t weights; /* repacked weight planes and norm vectors of this rank            */
+    uint64_t cache;   /* f16 K/V cache for the session's context                         */
+    uint64_t scratch; /* one batch of activations, attention scores, logits, RoPE table  */
+} brisk_cuda_memory;
+
+/* Fills `out` for the session brisk_cuda_create(model, options) would build. Needs no GPU. brisk_cuda_create runs the
+ * same estimate against the device's free memory and refuses, with the breakdown and a hint (a shorter context when the
+ * cache is what does not fit), instead of running out of memory half-way - check_memory's behaviour
+ * (src/memory.cpp:114-135); BRISK_NO_MEMORY_CHECK=1 skips the check, as in the reference. */
+int brisk_cuda_estimate_memory(const brisk_cuda_model* model, const brisk_cuda_options* options, brisk_cuda_memory* out);
+
 /* Number of usable CUDA devices; 0 when there is none or the driver is missing.
  * (The Metal backend's equivalent is the `gpu` flag check, src/main.cpp:204-212.) */
 int brisk_cuda_device_count(void);

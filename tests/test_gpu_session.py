@@ -185,3 +185,19 @@ def test_speculative_verify_on_the_gpu_matches_the_oracle():
         got, stats = speculative.speculate(s, prompt, 8, 24)
     first_diff = next((i for i, (a, b) in enumerate(zip(got, want)) if a != b), len(want))
     assert first_diff >= 20, (list(got), list(want))
+
+
+def test_memory_preflight_refuses_what_cannot_fit(monkeypatch):
+    """brisk_cuda_create checks its estimate against the device's free memory, like check_memory does for host RAM
+    (src/memory.cpp:114-135); the free figure is overridden here so that nothing actually runs out of memory."""
+    spec = synth.tiny(synth.QWEN3_0_6B, layers=2, vocab=1024, context=8192)
+    m = synth.generate(spec, seed=2)
+    need = engine.estimate_memory(m)
+    monkeypatch.setenv("BRISK_CUDA_ASSUME_FREE_BYTES", str(need["total"] - need["cache"] // 2))
+    with pytest.raises(RuntimeError, match="of device memory .* weights, .* cache, .* scratch.* is free. Try a shorter context"):
+        engine.CudaSession(m)
+    with engine.CudaSession(m, max_context=512) as s:  # the hint works
+        assert s.max_context == 512
+    monkeypatch.setenv("BRISK_NO_MEMORY_CHECK", "1")
+    with engine.CudaSession(m) as s:
+        assert s.max_context == 8192

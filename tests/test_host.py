@@ -93,3 +93,17 @@ def test_lookup_drafter_and_speculator_host_logic():
     got, stats = speculative.speculate(s, g["speculate_prompt"], 8, 24)
     assert np.array_equal(got, g["speculate24"])
     assert [stats["rounds"] + stats["plain"], stats["accepted"]] == list(g["speculate_rounds_accepted"])
+
+
+def test_device_memory_estimate_needs_no_gpu():
+    from brisk_llm_b200 import engine
+    spec = synth.tiny(synth.QWEN3_0_6B, layers=2, vocab=1024, context=512)
+    m = synth.generate(spec, seed=0)
+    e = engine.estimate_memory(m)
+    assert e["cache"] == 2 * 2 * spec.kv_dim * 512 * 2  # layers x (K, V) x kv_dim x context x f16
+    file_bytes = sum(d.nbytes for n, (f, s, d) in m.tensors.items())
+    assert file_bytes <= e["weights"] <= 1.1 * file_bytes + 64 * 256  # planes hold the file's bytes plus alignment padding
+    half = engine.estimate_memory(m, max_context=256)
+    assert half["cache"] * 2 == e["cache"] and half["scratch"] < e["scratch"]
+    tp2 = engine.estimate_memory(m, tp_size=2)
+    assert tp2["cache"] * 2 == e["cache"] and tp2["weights"] < e["weights"]
