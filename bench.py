@@ -341,6 +341,7 @@ def main():
                              "traffic": MEASURED_TRAFFIC_PER_TOKEN.get(args.config) if (world == 1 and not args.layers) else None,
                              "peak_kind": f"of {peak_kind}", "kernel": "decode step (all kernels of one token)",
                              "algorithmic_bytes_per_token": weight_bytes // (world if tensor_parallel else 1)}}
+        line["config"]["single_token_path"] = sess.step_path()
         if args.profile:
             line["profile_run"] = True
             line.pop("e2e")

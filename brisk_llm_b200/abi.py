@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(PKG_DIR, "libbrisk_cuda.so")
 
 ARCH_QWEN3, ARCH_LLAMA, ARCH_BITNET = 0, 1, 2
 ARCH_BY_NAME = {"qwen3": ARCH_QWEN3, "llama": ARCH_LLAMA, "bitnet": ARCH_BITNET, "bitnet-b1.58": ARCH_BITNET}
-FLAG_NO_GRAPH, FLAG_NO_MEGAKERNEL = 1, 2
+FLAG_NO_GRAPH, FLAG_NO_MEGAKERNEL, FLAG_NO_PERSISTENT = 1, 2, 4
 
 
 class Matrix(C.Structure):
@@ -47,7 +47,8 @@ class Options(C.Structure):
 
 class Stats(C.Structure):
     _fields_ = [("device_ms", C.c_double), ("kernel_launches", C.c_uint64), ("weight_bytes", C.c_uint64),
-                ("kv_bytes", C.c_uint64), ("h2d_bytes", C.c_uint64), ("d2h_bytes", C.c_uint64)]
+                ("kv_bytes", C.c_uint64), ("h2d_bytes", C.c_uint64), ("d2h_bytes", C.c_uint64),
+                ("persistent_steps", C.c_uint64)]
 
 
 class Memory(C.Structure):
@@ -57,6 +58,7 @@ class Memory(C.Structure):
 # Every symbol include/brisk_cuda.h declares, with its ctypes signature.
 SIGNATURES = {
     "brisk_cuda_device_count": (C.c_int, []),
+    "brisk_cuda_step_path": (C.c_int, [C.c_void_p, C.c_char_p, C.c_size_t]),
     "brisk_cuda_estimate_memory": (C.c_int, [C.POINTER(Model), C.POINTER(Options), C.POINTER(Memory)]),
     "brisk_cuda_create": (C.c_void_p, [C.POINTER(Model), C.POINTER(Options), C.c_char_p, C.c_size_t]),
     "brisk_cuda_destroy": (None, [C.c_void_p]),

@@ -1,0 +1,511 @@
+// Device-side bodies of the single-token step, shared by the one-kernel-per-operation path (decode.cu) and the
+// persistent whole-step kernel (step.cu). A body is handed a "gate": gate.wait() returns once the results of the
+// previous operation are visible (griddepcontrol.wait in the first path, a grid-wide barrier in the second); loads
+// that do not depend on the previous operation - the first weight units, cached K rows, V tiles - are issued before
+// it. Values produced by an earlier operation of the same step are read with L2 loads (__ldcg), never through L1:
+// inside the persistent kernel another SM wrote them during the same launch.
+//
+// All arithmetic is the reference's, in the reference's order (see formats.cuh, rowops.cuh, exact_math.h), so either
+// path stays bit-identical to the CPU engine.
+#pragma once
+
+#include <type_traits>
+
+#include "formats.cuh"
+#include "kernels.h"
+#include "rowops.cuh"
+
+namespace bk {
+
+constexpr int kDecWarps = 16;  // warps per CTA of every single-token kernel; the per-CTA prologue (norm + quantise) is shared by all of them
+
+// ---- multiply ---------------------------------------------------------------------------------------------------
+struct DecMatParams {
+    DevMatrix m[3];
+    float* out[3];
+    uint32_t first_group[4];
+    int count;
+    int epi;
+    const float* x;       // [cols] f32 input of the step (residual stream, attended row, gated activation)
+    const float* weight;  // RMS-norm weight or nullptr (no norm)
+    float eps;
+    uint32_t cols;
+    unsigned long long* trace;  // optional: 8 time stamps (ns) written by thread 0 of CTA 0, for BRISK_CUDA_TRACE
+    int pdl;
+};
+
+// Row groups of `rw` rows: fills first_group for the targets (one entry for a gate/up pair) and returns the total.
+inline uint32_t dec_assign_groups(DecMatParams& p, int rw, bool pair) {
+    uint32_t groups = 0;
+    const int targets = pair ? 1 : p.count;
+    for (int i = 0; i < targets; ++i) {
+        p.first_group[i] = groups;
+        groups += (p.m[i].rows + rw - 1) / rw;
+    }
+    p.first_group[targets] = groups;
+    return groups;
+}
+
+// Bytes of shared memory the multiply body takes for the activation row: f32 values, then the quantised planes.
+inline size_t dec_act_smem(uint32_t cols) { return size_t(cols) * 4 + cols + (cols / 32) * 8 + 64; }
+// Floats of the per-warp transpose tile for CHAINS row chains.
+constexpr size_t dec_tile_floats(int chains) { return size_t(kDecWarps) * chains * 36; }
+
+#ifdef __CUDACC__
+
+__device__ __forceinline__ void dec_stamp(unsigned long long* trace, uint32_t cta, int slot) {
+    if (trace != nullptr && cta == 0 && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        trace[slot] = t;
+    }
+}
+
+// One fused multiply by CTA `cta` of `nctas` (kDecWarps warps each): the CTA rebuilds the activation row in shared
+// memory (x, optionally RMS-normed, then quantised the way F takes it) and its warps walk row groups of RW rows.
+//   act_smem: dec_act_smem(cols) bytes, 16-byte aligned;  tile: dec_tile_floats(CHAINS) floats (exact formats);
+//   red: 32 doubles.
+// Ends with every thread past its last shared-memory access except the epilogue stores; callers that reuse the shared
+// memory must put a barrier after it.
+template <class F, int RW, bool PAIR, int kDepth, class Gate>
+__device__ __forceinline__ void dec_multiply_body(const DecMatParams& p, const uint32_t cta, const uint32_t nctas, unsigned char* act_smem, float* tile,
+                                                  double* red, Gate&& gate) {
+    constexpr int MATS = PAIR ? 2 : 1;
+    constexpr int CHAINS = MATS * RW;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t total_groups = p.first_group[PAIR ? 1 : p.count];
+    const uint32_t stride = nctas * kDecWarps;
+    const uint32_t first = cta * kDecWarps + warp;
+
+    auto locate = [&](uint32_t group, int& target, uint32_t& row0) {
+        target = 0;
+        if (!PAIR) {
+            while (target + 1 < p.count && group >= p.first_group[target + 1]) ++target;
+        }
+        row0 = (group - p.first_group[target]) * RW;
+    };
+    const uint32_t units = p.m[0].units;  // all targets share cols and type
+    const uint32_t steps = (units + 31) / 32;
+    auto load_weights = [&](uint32_t group, uint32_t step, typename F::W (&w)[MATS][RW]) {
+        int target;
+        uint32_t row0;
+        locate(group, target, row0);
+        const uint32_t u = step * 32 + lane;
+        const uint32_t uu = u < units ? u : 0;
+#pragma unroll
+        for (int a = 0; a < MATS; ++a)
+#pragma unroll
+            for (int r = 0; r < RW; ++r) w[a][r] = F::loadw(p.m[PAIR ? a : target], min(row0 + r, p.m[target].rows - 1), uu);
+    };
+
+    dec_stamp(p.trace, cta, 0);
+    // Weights (and the norm weights) do not depend on the previous operation: get them in flight before waiting for
+    // it. A ring of kDepth iterations of weights per lane, refilled in iteration order: kDepth = 1 for the layer
+    // matrices of small models (a warp has one to three iterations), deeper for long walks (the output head, 7B-class
+    // layers) so that enough bytes are in flight per SM to cover HBM latency.
+    typename F::W wq[kDepth][MATS][RW];
+    const bool any = first < total_groups;
+    const uint32_t my_groups = any ? (total_groups - first + stride - 1) / stride : 0;
+    const uint32_t my_iters = my_groups * steps;
+    uint32_t agroup = first, astep = 0, issued = 0;  // the next iteration to load
+    auto issue = [&](typename F::W (&slot)[MATS][RW]) {
+        if (issued < my_iters) {
+            load_weights(agroup, astep, slot);
+            ++issued;
+            if (++astep == steps) {
+                astep = 0;
+                agroup += stride;
+            }
+        }
+    };
+#pragma unroll
+    for (int d = 0; d < kDepth; ++d) issue(wq[d]);
+    const uint32_t cols = p.cols;
+    gate.wait();
+    dec_stamp(p.trace, cta, 1);
+    if (p.trace != nullptr && cta == 0 && threadIdx.x == 0) {  // tracing only: latency of one dependent load
+        const float probe = *reinterpret_cast<const volatile float*>(p.x);
+        if (probe == 123456.0f) p.trace[7] = 0;
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        p.trace[6] = t;
+    }
+
+    // Prologue: the activation row in shared memory - f32 (normed), then the planes this format multiplies by.
+    // x as float4s (row lengths are multiples of 32), up to 8 per thread in flight so that their latencies overlap.
+    float* xf = reinterpret_cast<float*>(act_smem);
+    constexpr uint32_t kT = kDecWarps * 32;
+    const float4* x4 = reinterpret_cast<const float4*>(p.x);
+    float4* xf4 = reinterpret_cast<float4*>(xf);
+    const uint32_t n4 = cols / 4;
+    double part = 0.0;
+    for (uint32_t base = 0; base < n4; base += 8 * kT) {
+        float4 xv[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const uint32_t i = base + threadIdx.x + k * kT;
+            xv[k] = i < n4 ? __ldcg(x4 + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const uint32_t i = base + threadIdx.x + k * kT;
+            if (i < n4) xf4[i] = xv[k];
+            part += double(__fmul_rn(xv[k].x, xv[k].x));  // padding adds exact zeros
+            part += double(__fmul_rn(xv[k].y, xv[k].y));
+            part += double(__fmul_rn(xv[k].z, xv[k].z));
+            part += double(__fmul_rn(xv[k].w, xv[k].w));
+        }
+    }
+    if (p.weight != nullptr) {
+        part = warp_sum(part);
+        if (lane == 0) red[warp] = part;
+        __syncthreads();
+        double total = 0.0;
+#pragma unroll
+        for (int w = 0; w < kDecWarps; ++w) total += red[w];
+        const float mean = float(total / double(cols));
+        const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, p.eps)));
+        dec_stamp(p.trace, cta, 2);
+        const float4* w4 = reinterpret_cast<const float4*>(p.weight);
+        for (uint32_t base = 0; base < n4; base += 8 * kT) {
+            float4 wv[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const uint32_t i = base + threadIdx.x + k * kT;
+                wv[k] = i < n4 ? w4[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const uint32_t i = base + threadIdx.x + k * kT;
+                if (i < n4) {  // the same thread wrote xf4[i] above
+                    const float4 xx = xf4[i];
+                    xf4[i] = make_float4(__fmul_rn(__fmul_rn(xx.x, scale), wv[k].x), __fmul_rn(__fmul_rn(xx.y, scale), wv[k].y),
+                                         __fmul_rn(__fmul_rn(xx.z, scale), wv[k].z), __fmul_rn(__fmul_rn(xx.w, scale), wv[k].w));
+                }
+            }
+        }
+    }
+    __syncthreads();
+    dec_stamp(p.trace, cta, 3);
+    DevAct act{};
+    act.cols = cols;
+    act.f32 = xf;
+    unsigned char* planes = act_smem + size_t(cols) * 4;
+    if constexpr (std::is_same_v<F, FQ4_0> || std::is_same_v<F, FQ8_0>) {
+        int8_t* q = reinterpret_cast<int8_t*>(planes);
+        float* d = reinterpret_cast<float*>(planes + cols);
+        int32_t* s = reinterpret_cast<int32_t*>(planes + cols + (cols / 32) * 4);
+        cta_quantize_q8_0(xf, cols, q, d, s);
+        act.q0 = q; act.d0 = d; act.s0 = s;
+    } else if constexpr (F::kExact) {
+        int8_t* q = reinterpret_cast<int8_t*>(planes);
+        float* d = reinterpret_cast<float*>(planes + cols);
+        int16_t* bs = reinterpret_cast<int16_t*>(planes + cols + ((cols / 256 + 3) / 4) * 16);
+        cta_quantize_q8_k(xf, cols, q, d, bs);
+        act.qk = q; act.dk = d; act.bs = bs;
+    }
+    __syncthreads();
+    gate.prologue_done();
+    dec_stamp(p.trace, cta, 4);
+    if (!any) return;
+
+    float run = 0.0f;
+    float acc[MATS][RW];
+#pragma unroll
+    for (int a = 0; a < MATS; ++a)
+#pragma unroll
+        for (int r = 0; r < RW; ++r) acc[a][r] = 0.0f;
+
+    float old = 0.0f;  // the residual value a chain lane adds to (EPI_ADD), fetched while the row is being multiplied
+    uint32_t group = first, step = 0;
+    for (uint32_t it0 = 0; it0 < my_iters; it0 += kDepth) {
+#pragma unroll
+        for (int d = 0; d < kDepth; ++d) {
+            const uint32_t it = it0 + d;
+            if (it >= my_iters) break;
+            if (F::kExact && !PAIR && step == 0 && p.epi == EPI_ADD && lane < RW) {
+                int target;
+                uint32_t row0;
+                locate(group, target, row0);
+                if (row0 + lane < p.m[target].rows) old = __ldcg(p.out[target] + row0 + lane);
+            }
+            typename F::W w[MATS][RW];
+#pragma unroll
+            for (int a = 0; a < MATS; ++a)
+#pragma unroll
+                for (int r = 0; r < RW; ++r) w[a][r] = wq[d][a][r];
+            issue(wq[d]);  // refill this slot with the iteration kDepth later
+
+            const uint32_t u = step * 32 + lane;
+            const bool valid = u < units;
+            const uint32_t uu = valid ? u : 0;
+            const typename F::X x = F::loadx(act, 0, uu);
+#pragma unroll
+            for (int a = 0; a < MATS; ++a)
+#pragma unroll
+                for (int r = 0; r < RW; ++r) {
+                    const float term = F::term(w[a][r], x, valid, uu);
+                    if constexpr (F::kExact) tile[(warp * CHAINS + a * RW + r) * 36 + lane] = term;
+                    else acc[a][r] = __fadd_rn(acc[a][r], term);
+                }
+            if constexpr (F::kExact) {
+                __syncwarp();
+                if (lane < CHAINS) {
+                    const int cnt = int(min(32u, units - step * 32));
+                    const float4* mine = reinterpret_cast<const float4*>(tile + (warp * CHAINS + lane) * 36);
+                    float v[32];  // all of the step's terms first, then the serial adds
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 q = mine[j];
+                        v[4 * j] = q.x; v[4 * j + 1] = q.y; v[4 * j + 2] = q.z; v[4 * j + 3] = q.w;
+                    }
+                    if (cnt == 32) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += F::kLanesPerTerm) run = __fadd_rn(run, v[j]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j += F::kLanesPerTerm) run = j < cnt ? __fadd_rn(run, v[j]) : run;
+                    }
+                }
+                __syncwarp();
+            }
+            if (step + 1 == steps) {  // the group's rows are complete
+                int target;
+                uint32_t row0;
+                locate(group, target, row0);
+                const DevMatrix& m = p.m[target];
+                float* outp = p.out[PAIR ? 0 : target];
+                if constexpr (F::kExact) {
+                    const float other = PAIR ? __shfl_down_sync(0xffffffffu, run, RW) : 0.0f;
+                    if (lane < RW && row0 + lane < m.rows) {
+                        float* o = outp + row0 + lane;
+                        if (PAIR) *o = p.epi == EPI_SILU_MUL ? silu_mul(run, other) : relu2_mul(run, other);
+                        else if (p.epi == EPI_ADD) *o = __fadd_rn(old, run);
+                        else *o = run;
+                    }
+                    run = 0.0f;
+                } else {
+#pragma unroll
+                    for (int r = 0; r < RW; ++r) {
+                        const float v0 = warp_sum(acc[0][r]);
+                        const float v1 = PAIR ? warp_sum(acc[MATS - 1][r]) : 0.0f;
+                        if (lane == 0 && row0 + r < m.rows) {
+                            float* o = outp + row0 + r;
+                            if (PAIR) *o = p.epi == EPI_SILU_MUL ? silu_mul(v0, v1) : relu2_mul(v0, v1);
+                            else if (p.epi == EPI_ADD) *o = __fadd_rn(__ldcg(o), v0);
+                            else *o = v0;
+                        }
+                        acc[0][r] = 0.0f;
+                        acc[MATS - 1][r] = 0.0f;
+                    }
+                }
+            }
+            if (++step == steps) {
+                step = 0;
+                group += stride;
+            }
+        }
+    }
+    dec_stamp(p.trace, cta, 5);
+}
+
+// ---- attention ---------------------------------------------------------------------------------------------------
+struct DecAttnParams {
+    const float* q;       // [heads*dim] raw projections of this token
+    const float* k;       // [kv*dim]
+    const float* v;       // [kv*dim]
+    const float* q_norm;  // [dim] or nullptr
+    const float* k_norm;
+    const float* rope;    // [max_context][dim]
+    __half* k_cache;      // [kv][max_context][dim]
+    __half* v_cache;
+    float* scores;        // [heads][max_context]
+    float* out;           // [heads*dim]
+    const uint32_t* position;
+    uint32_t heads, kv_heads, dim, max_context;
+    float eps, scale;
+    int neox;
+    int pdl;
+};
+
+// Per-head RMS norm (optional) + RoPE of one head by ONE WARP, as src/model.cpp:1031-1042. Lane l holds VPL = dim/32
+// values chosen so that both members of every rotation pair sit in the same lane: elements l + 32k for the NeoX
+// pairing (i, i + dim/2), elements VPL*l + k for the adjacent pairing (2i, 2i+1). No block-level barrier is needed.
+// `src` is read with L2 loads (it was produced by the previous operation of the step).
+template <int VPL, bool NEOX>
+__device__ __forceinline__ void warp_norm_rope_head_impl(const float* src, const float* norm, const float* rope, float eps, float* dst) {
+    constexpr uint32_t dim = VPL * 32;
+    const uint32_t lane = threadIdx.x & 31;
+    float v[VPL];
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) v[k] = __ldcg(src + (NEOX ? lane + 32 * k : VPL * lane + k));
+    if (norm != nullptr) {
+        double part = 0.0;
+#pragma unroll
+        for (int k = 0; k < VPL; ++k) part += double(__fmul_rn(v[k], v[k]));
+        part = warp_sum(part);
+        const float mean = float(part / double(dim));
+        const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+#pragma unroll
+        for (int k = 0; k < VPL; ++k) v[k] = __fmul_rn(__fmul_rn(v[k], scale), norm[NEOX ? lane + 32 * k : VPL * lane + k]);
+    }
+#pragma unroll
+    for (int k = 0; k < VPL / 2; ++k) {
+        // pair (a, b): NeoX -> registers k and k + VPL/2 (elements i, i + dim/2); adjacent -> registers 2k, 2k+1 (elements 2i, 2i+1)
+        const int ra = NEOX ? k : 2 * k, rb = NEOX ? k + VPL / 2 : 2 * k + 1;
+        const uint32_t ia = NEOX ? lane + 32 * ra : VPL * lane + ra, ib = NEOX ? lane + 32 * rb : VPL * lane + rb;
+        const uint32_t pair = NEOX ? ia : ia / 2;  // index of the (cos, sin) entry
+        const float c = rope[2 * pair], sn = rope[2 * pair + 1];
+        const float x0 = v[ra], x1 = v[rb];
+        dst[ia] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, sn));
+        dst[ib] = __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, c));
+    }
+}
+
+template <int VPL>
+__device__ __forceinline__ void warp_norm_rope_head(const float* src, const float* norm, const float* rope, float eps, int neox, float* dst) {
+    if (neox) warp_norm_rope_head_impl<VPL, true>(src, norm, rope, eps, dst);
+    else warp_norm_rope_head_impl<VPL, false>(src, norm, rope, eps, dst);
+}
+
+// The new position's K and V rows of K/V head `kvh`: k (already normed and rotated, in `knew`) is rounded to f16,
+// stored, and read back into `knew` so that the position's own score uses the cache's value; v is rounded and stored.
+// One warp; call after the warp's warp_norm_rope_head into knew and a __syncwarp().
+__device__ __forceinline__ void warp_store_new_kv(const DecAttnParams& a, uint32_t kvh, uint32_t pos, float* knew) {
+    const size_t base = (size_t(kvh) * a.max_context + pos) * a.dim;
+    for (uint32_t i = threadIdx.x & 31; i < a.dim; i += 32) {
+        const __half kh = __float2half_rn(knew[i]);
+        a.k_cache[base + i] = kh;
+        knew[i] = __half2float(kh);
+        a.v_cache[base + i] = __float2half_rn(__ldcg(a.v + size_t(kvh) * a.dim + i));
+    }
+}
+
+// ---- softmax + weighted sum of one query head by one CTA of NT threads -------------------------------------------
+constexpr uint32_t kVTile = 64;   // positions of V per stage
+constexpr uint32_t kVStages = 4;  // stages in flight: the serial chain consumes a tile faster than L2 delivers one
+
+inline size_t dec_attn_out_smem(uint32_t max_context, uint32_t dim) {
+    return ((size_t(max_context) * 4 + 15) & ~size_t(15)) + size_t(kVStages) * kVTile * dim * sizeof(__half);
+}
+
+// raw: dec_attn_out_smem() bytes (probabilities [max_context] | V ring kVStages x [kVTile][dim] f16);
+// redf / redd: NT/32 floats / doubles. V tiles that hold only earlier positions are requested before gate.wait();
+// the last tile holds the position written by this step and is requested after it.
+template <int NT, class Gate>
+__device__ __forceinline__ void dec_attn_out_body(const DecAttnParams& a, const uint32_t h, unsigned char* raw, float* redf, double* redd, Gate&& gate) {
+    constexpr int kWarps = NT / 32;
+    const uint32_t tid = threadIdx.x, dim = a.dim;
+    const uint32_t visible = *a.position + 1;
+    const uint32_t kvh = h / (a.heads / a.kv_heads);
+    float* ps = reinterpret_cast<float*>(raw);
+    __half* vt = reinterpret_cast<__half*>(raw + ((size_t(a.max_context) * 4 + 15) & ~size_t(15)));
+    const float* s = a.scores + size_t(h) * a.max_context;
+    const __half* vbase = a.v_cache + size_t(kvh) * a.max_context * dim;
+
+    // V tiles stream through a ring of shared-memory stages with cp.async (L2 -> shared, not through L1).
+    const uint32_t tiles = (visible + kVTile - 1) / kVTile;
+    const uint32_t chunks_per_tile = kVTile * dim / 8;  // 16-byte chunks
+    auto stage = [&](uint32_t tile_index) {
+        if (tile_index < tiles) {
+            __half* dst = vt + size_t(tile_index % kVStages) * kVTile * dim;
+            const __half* src = vbase + size_t(tile_index) * kVTile * dim;
+            const uint32_t rows = min(kVTile, visible - tile_index * kVTile);
+            for (uint32_t c = tid; c < chunks_per_tile; c += NT) {
+                if (c * 8 < rows * dim) {
+                    const uint32_t sm_addr = uint32_t(__cvta_generic_to_shared(dst + c * 8));
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sm_addr), "l"(src + c * 8) : "memory");
+                }
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");  // one group per tile index, empty past the end
+    };
+    uint32_t staged = 0;
+    while (staged + 1 < kVStages && staged + 1 < tiles) stage(staged++);  // tiles before the last one
+    gate.wait();
+    while (staged + 1 < kVStages) stage(staged++);
+
+    // softmax (src/kernels_f32.cpp:275-284): max, e = expf(s - max), f64 sum, p = e * float(1/sum). Up to 8 scores per
+    // thread stay in registers; longer rows go through shared memory.
+    const bool in_regs = visible <= 8 * NT;
+    float sv[8];
+    float mx = -INFINITY;
+    if (in_regs) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const uint32_t p = tid + k * NT;
+            sv[k] = p < visible ? __ldcg(s + p) : -INFINITY;
+            mx = fmaxf(mx, sv[k]);
+        }
+    } else {
+        for (uint32_t p = tid; p < visible; p += NT) {
+            const float v = __ldcg(s + p);
+            ps[p] = v;
+            mx = fmaxf(mx, v);
+        }
+    }
+    mx = warp_max(mx);
+    if ((tid & 31) == 0) redf[tid >> 5] = mx;
+    __syncthreads();
+    mx = redf[0];
+#pragma unroll
+    for (int w = 1; w < kWarps; ++w) mx = fmaxf(mx, redf[w]);
+    double part = 0.0;
+    if (in_regs) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            if (tid + k * NT < visible) {
+                sv[k] = exact_expf(__fsub_rn(sv[k], mx));
+                part += double(sv[k]);
+            }
+        }
+    } else {
+        for (uint32_t p = tid; p < visible; p += NT) {
+            const float e = exact_expf(__fsub_rn(ps[p], mx));
+            ps[p] = e;
+            part += double(e);
+        }
+    }
+    part = warp_sum(part);
+    if ((tid & 31) == 0) redd[tid >> 5] = part;
+    __syncthreads();
+    double total = 0.0;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) total += redd[w];
+    const float inv = float(1.0 / total);
+    if (in_regs) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const uint32_t p = tid + k * NT;
+            if (p < visible) ps[p] = __fmul_rn(sv[k], inv);
+        }
+    } else {
+        for (uint32_t p = tid; p < visible; p += NT) ps[p] = __fmul_rn(ps[p], inv);
+    }
+
+    // weighted sum (src/kernels_f32.cpp:265-273): out[i] += p[pos] * v[pos][i], position after position.
+    float acc = 0.0f;
+    for (uint32_t t = 0; t < tiles; ++t) {
+        stage(t + kVStages - 1);  // refills the stage consumed in the previous iteration
+        asm volatile("cp.async.wait_group %0;" ::"n"(kVStages - 1) : "memory");
+        __syncthreads();  // tile t has landed for every thread (and ps is complete on the first pass)
+        if (tid < dim) {
+            const __half* tv = vt + size_t(t % kVStages) * kVTile * dim + tid;
+            const uint32_t rows = min(kVTile, visible - t * kVTile);
+            const float* pw = ps + t * kVTile;
+            if (rows == kVTile) {
+#pragma unroll
+                for (uint32_t j = 0; j < kVTile; ++j) acc = __fadd_rn(acc, __fmul_rn(pw[j], __half2float(tv[j * dim])));
+            } else {
+                for (uint32_t j = 0; j < rows; ++j) acc = __fadd_rn(acc, __fmul_rn(pw[j], __half2float(tv[j * dim])));
+            }
+        }
+        __syncthreads();  // everyone is done with tile t before its stage is refilled
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");  // only empty groups remain
+    if (tid < dim) a.out[size_t(h) * dim + tid] = acc;
+}
+
+#endif  // __CUDACC__
+
+}  // namespace bk

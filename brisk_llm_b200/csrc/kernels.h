@@ -2,6 +2,9 @@
 // nothing here allocates or synchronises.
 #pragma once
 
+#include <string>
+#include <vector>
+
 #include "common.cuh"
 
 namespace bk {
@@ -103,6 +106,58 @@ void launch_dec_multiply(const MatTarget* targets, int count, const float* x, co
 // Attention of the single new token: scores kernel (per-head norm + RoPE of q and the new k, f16 K/V store in its
 // prologue) and softmax + weighted-sum kernel. Takes the same argument structs as the batched kernels (n is 1).
 void launch_dec_attention(const RopeArgs& r, const AttnArgs& at, cudaStream_t s);
+
+// ---- the single-token step of all layers as one persistent kernel (step.cu) -------------------------------------
+struct StepLayerArgs {
+    DevMatrix q, k, v, o, gate, up, down;
+    const float* attn_norm = nullptr;
+    const float* q_norm = nullptr;
+    const float* k_norm = nullptr;
+    const float* attn_sub_norm = nullptr;
+    const float* ffn_norm = nullptr;
+    const float* ffn_sub_norm = nullptr;
+    __half* k_cache = nullptr;
+    __half* v_cache = nullptr;
+};
+struct StepShared {  // the step's activation vectors and the model constants every layer shares
+    float* hidden = nullptr;    // [hidden_size] residual stream, in and out
+    float* q = nullptr;         // [heads*dim]
+    float* k = nullptr;         // [kv_heads*dim]
+    float* v = nullptr;
+    float* attended = nullptr;  // [heads*dim]
+    float* gated = nullptr;     // [ffn_size]
+    float* scores = nullptr;    // [heads][max_context]
+    const float* rope = nullptr;
+    const uint32_t* position = nullptr;
+    uint32_t hidden_size = 0, ffn_size = 0, heads = 0, kv_heads = 0, dim = 0, max_context = 0;
+    float eps = 0.0f, scale = 0.0f;
+    int neox = 0;
+    int act_epi = EPI_SILU_MUL;
+};
+// Built once per session (the weights and buffers are fixed); launch() runs layers 0..n-1 of one token whose embedding
+// is in `hidden` and whose position is in *position. build() returns false, with the reason, when the model is outside
+// what the persistent kernel covers (mixed weight types in the layers, F16/F32 layer matrices, head sizes other than 64
+// and 128, a context too long for its shared memory) - the caller then keeps the one-kernel-per-operation path.
+// Every barrier wait inside the kernel is bounded; a wait that ran out sets the word at error_word() (device memory),
+// which the caller copies back with the step's results and checks, then rearm()s.
+class StepPlan {
+public:
+    StepPlan();
+    ~StepPlan();
+    StepPlan(const StepPlan&) = delete;
+    StepPlan& operator=(const StepPlan&) = delete;
+    bool build(const std::vector<StepLayerArgs>& layers, const StepShared& shared, uint32_t sms, cudaStream_t s, std::string& why_not);
+    bool ready() const { return impl_ != nullptr; }
+    void launch(cudaStream_t s) const;
+    const unsigned int* error_word() const;
+    void rearm(cudaStream_t s);
+    const std::string& description() const { return description_; }
+
+private:
+    struct Impl;
+    Impl* impl_ = nullptr;
+    std::string description_;
+};
 
 // Tensor parallel re-layout: gathered[rank][t][rows_l] -> dst[t][rank*rows_l + r] (add: dst += ...), tp ranks.
 void launch_tp_unpack(const float* gathered, float* dst, uint32_t n, uint32_t rows_l, uint32_t tp, bool add, cudaStream_t s);

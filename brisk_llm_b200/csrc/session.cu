@@ -161,6 +161,12 @@ struct Session {
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     cudaGraphExec_t step_graph = nullptr;
     uint64_t step_graph_nodes = 0;
+    // The persistent all-layer kernel of the single-token step (step.cu), when the model is within what it covers.
+    StepPlan step_plan;
+    bool step_enabled = false;
+    std::string step_note;                 // how it was configured, or why it is not used
+    unsigned int* step_error_host = nullptr;  // pinned copy of the kernel's barrier-timeout word
+    uint64_t persistent_steps = 0;
     uint64_t launches = 0;  // kernels launched by the current call
     // Per-phase device time, the counterpart of the reference's Session::Profile / BRISK_GPU_PROFILE
     // (src/model.h:242-245, src/metal/metal_session.mm:711-719). Enabled by brisk_cuda_profile_enable(): every phase is
@@ -228,6 +234,7 @@ struct Session {
         if (stream) cudaStreamDestroy(stream);
         if (logits_host) cudaFreeHost(logits_host);
         if (tokens_host) cudaFreeHost(tokens_host);
+        if (step_error_host) cudaFreeHost(step_error_host);
     }
 
     // ---- load ------------------------------------------------------------------------------------------
@@ -430,9 +437,40 @@ struct Session {
         }
         BK_CUDA(cudaMallocHost(&logits_host, size_t(kMaxScored) * vocab * sizeof(float)));
         BK_CUDA(cudaMallocHost(&tokens_host, (kMaxBatch + 4) * sizeof(int32_t)));
+        BK_CUDA(cudaMallocHost(&step_error_host, sizeof(unsigned int)));
+        *step_error_host = 0;
         BK_CUDA(cudaStreamSynchronize(stream));
+        plan_step();
         stats.weight_bytes = weight_bytes;
         stats.kv_bytes = kv_bytes;
+    }
+
+    void plan_step() {
+        const char* env = std::getenv("BRISK_CUDA_STEP");
+        if (tp_size > 1) step_note = "off: tensor parallel steps exchange activations between the operations";
+        else if (flags & (BRISK_CUDA_FLAG_NO_MEGAKERNEL | BRISK_CUDA_FLAG_NO_PERSISTENT)) step_note = "off: disabled by the session's flags";
+        else if (env != nullptr && std::atoi(env) == 0) step_note = "off: BRISK_CUDA_STEP=0";
+        else if (trace.p != nullptr) step_note = "off: tracing the per-operation kernels";
+        if (!step_note.empty()) return;
+        std::vector<StepLayerArgs> args(n_layers);
+        for (uint32_t l = 0; l < n_layers; ++l) {
+            const Layer& L = layers[l];
+            StepLayerArgs& a = args[l];
+            a.q = L.q; a.k = L.k; a.v = L.v; a.o = L.o; a.gate = L.gate; a.up = L.up; a.down = L.down;
+            a.attn_norm = L.attn_norm; a.q_norm = L.q_norm; a.k_norm = L.k_norm; a.attn_sub_norm = L.attn_sub_norm;
+            a.ffn_norm = L.ffn_norm; a.ffn_sub_norm = L.ffn_sub_norm; a.k_cache = L.k_cache; a.v_cache = L.v_cache;
+        }
+        StepShared sh;
+        sh.hidden = hidden_b.as<float>(); sh.q = q_b.as<float>(); sh.k = k_b.as<float>(); sh.v = v_b.as<float>();
+        sh.attended = attended_b.as<float>(); sh.gated = ffn_b.as<float>(); sh.scores = partial.as<float>();
+        sh.rope = rope.as<float>(); sh.position = d_position();
+        sh.hidden_size = hidden; sh.ffn_size = ffn; sh.heads = heads; sh.kv_heads = kv_heads; sh.dim = head_dim;
+        sh.max_context = uint32_t(max_context);
+        sh.eps = eps; sh.scale = 1.0f / std::sqrt(static_cast<float>(head_dim)); sh.neox = neox;
+        sh.act_epi = arch == BRISK_ARCH_BITNET ? EPI_RELU2_MUL : EPI_SILU_MUL;
+        std::string why;
+        step_enabled = step_plan.build(args, sh, sms, stream, why);
+        step_note = step_enabled ? "on: " + step_plan.description() : "off: " + why;
     }
 
     // ---- forward ---------------------------------------------------------------------------------------
@@ -618,10 +656,45 @@ struct Session {
     }
 
     void forward(uint32_t n, bool all_logits, uint32_t max_visible) { run_layers(n, all_logits, max_visible, false); }
-    void forward_decode() { run_layers(1, false, uint32_t(max_context), true); }
+    bool step_active() const { return step_enabled && !profiling; }
+    void forward_decode() {
+        if (!step_active()) {
+            run_layers(1, false, uint32_t(max_context), true);
+            return;
+        }
+        // embedding | all layers in one persistent kernel | output head
+        launch_embed(embd, tokens_dev.as<int32_t>(), 1, hidden_b.as<float>(), stream);
+        step_plan.launch(stream);
+        MatTarget target{head, logits_b.as<float>(), vocab};
+        launch_dec_multiply(&target, 1, hidden_b.as<float>(), output_norm, eps, hidden, EPI_STORE, sms, stream, nullptr);
+        launches += 3;
+        ++persistent_steps;
+    }
+    // After the call's final synchronisation: did a barrier wait of the persistent kernel run out?
+    void queue_step_check() {
+        if (step_enabled) BK_CUDA(cudaMemcpyAsync(step_error_host, step_plan.error_word(), sizeof(unsigned int), cudaMemcpyDeviceToHost, stream));
+    }
+    void finish_step_check() {
+        if (step_enabled && *step_error_host != 0) {
+            *step_error_host = 0;
+            step_plan.rearm(stream);
+            step_enabled = false;  // later steps take the per-operation kernels
+            step_note = "off: a grid barrier timed out";
+            throw CudaError("cuda: a grid barrier of the single-token kernel timed out; the results of this call are invalid");
+        }
+    }
+
+    // Three launches per token gain little from a graph; BRISK_CUDA_STEP_GRAPH=1 captures them all the same.
+    static bool step_in_graph() {
+        static const bool on = [] {
+            const char* env = std::getenv("BRISK_CUDA_STEP_GRAPH");
+            return env != nullptr && std::atoi(env) != 0;
+        }();
+        return on;
+    }
 
     void build_step_graph() {
-        if (step_graph != nullptr || (flags & BRISK_CUDA_FLAG_NO_GRAPH)) return;
+        if (step_graph != nullptr || (flags & BRISK_CUDA_FLAG_NO_GRAPH) || (step_active() && !step_in_graph())) return;
         const uint64_t before = launches;
         cudaGraph_t graph = nullptr;
         BK_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
@@ -643,7 +716,7 @@ struct Session {
     void step_on_device() {  // one token whose id is tokens_dev[0] at *d_position()
         if (flags & BRISK_CUDA_FLAG_NO_MEGAKERNEL) {
             forward(1, false, uint32_t(max_context));  // the batched kernels, one token
-        } else if ((flags & BRISK_CUDA_FLAG_NO_GRAPH) || profiling) {
+        } else if ((flags & BRISK_CUDA_FLAG_NO_GRAPH) || profiling || (step_active() && !step_in_graph())) {
             forward_decode();
         } else {
             build_step_graph();
@@ -654,12 +727,14 @@ struct Session {
 
     void begin_call() {
         launches = 0;
+        persistent_steps = 0;
         stats.h2d_bytes = stats.d2h_bytes = 0;
     }
     void end_call(float ms) {
         if (profiling) collect_profile();
         stats.device_ms = ms;
         stats.kernel_launches = launches;
+        stats.persistent_steps = persistent_steps;
     }
 
     void check_tokens(const int32_t* tokens, uint64_t n, bool all) {
@@ -693,10 +768,12 @@ struct Session {
         BK_CUDA(cudaMemcpyAsync(logits_host, logits_b.p, out_bytes, cudaMemcpyDeviceToHost, stream));
         stats.d2h_bytes += out_bytes;
         BK_CUDA(cudaEventRecord(ev1, stream));
+        queue_step_check();
         BK_CUDA(cudaStreamSynchronize(stream));
         float ms = 0;
         BK_CUDA(cudaEventElapsedTime(&ms, ev0, ev1));
         end_call(ms);
+        finish_step_check();
         return logits_host;
     }
 
@@ -739,11 +816,13 @@ struct Session {
             BK_CUDA(cudaMemcpyAsync(out_logits, logit_history.p, steps * vocab * sizeof(float), cudaMemcpyDeviceToHost, stream));
             stats.d2h_bytes += steps * vocab * sizeof(float);
         }
+        queue_step_check();
         BK_CUDA(cudaStreamSynchronize(stream));
         float ms = 0;
         BK_CUDA(cudaEventElapsedTime(&ms, ev0, ev1));
         position += steps;
         end_call(ms);
+        finish_step_check();
     }
 };
 
@@ -873,6 +952,12 @@ int brisk_cuda_profile(brisk_cuda_session* session, int enable, char* json, size
         }
         s.profiling = enable != 0;
     });
+}
+
+int brisk_cuda_step_path(brisk_cuda_session* session, char* text, size_t len) {
+    if (session == nullptr || text == nullptr || len == 0) return -1;
+    std::snprintf(text, len, "persistent step kernel %s", session->s.step_note.c_str());
+    return 0;
 }
 
 int brisk_cuda_debug_buffer(brisk_cuda_session* session, const char* name, float* out, uint64_t count) {

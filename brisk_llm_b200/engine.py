@@ -124,6 +124,13 @@ class CudaSession:
             self._fail()
         return (toks, logits) if want_logits else toks
 
+    def step_path(self) -> str:
+        """How single-token steps run: 'persistent step kernel on: ...' or '... off: <reason>'."""
+        buf = C.create_string_buffer(256)
+        if self._lib.brisk_cuda_step_path(self._h, buf, len(buf)) != 0:
+            self._fail()
+        return buf.value.decode()
+
     def stats(self) -> dict:
         st = abi.Stats()
         self._lib.brisk_cuda_get_stats(self._h, C.byref(st))

@@ -105,6 +105,8 @@ typedef struct brisk_cuda_options {
 
 #define BRISK_CUDA_FLAG_NO_GRAPH 1u      /* launch decode kernels one by one instead of replaying a CUDA graph */
 #define BRISK_CUDA_FLAG_NO_MEGAKERNEL 2u /* single-token steps through the batched kernels instead of the fused ones */
+#define BRISK_CUDA_FLAG_NO_PERSISTENT 4u /* single-token steps as one fused kernel per operation (replayed as a CUDA graph)
+                                            instead of one persistent kernel for all layers */
 
 typedef struct brisk_cuda_session brisk_cuda_session;
 
@@ -116,6 +118,7 @@ typedef struct brisk_cuda_stats {
     uint64_t kv_bytes;        /* bytes of the f16 K/V cache                                        */
     uint64_t h2d_bytes;       /* host->device bytes copied by the call                             */
     uint64_t d2h_bytes;       /* device->host bytes copied by the call                             */
+    uint64_t persistent_steps; /* single-token steps of the call that ran as the persistent all-layer kernel */
 } brisk_cuda_stats;
 
 /* Device memory a session will hold, before anything is allocated - the device-side analogue of estimate_memory /
@@ -207,6 +210,11 @@ int brisk_cuda_matmul_seconds(int32_t type, const void* w, uint64_t rows, uint64
  * stream capture begins. Calls no cudaMalloc/cudaFree and no allocating library routine. */
 int brisk_cuda_argmax_static(const float* logits, uint32_t vocab, uint32_t rows, int32_t* out_tokens, void* stream, char* err,
                              size_t errlen);
+
+/* How single-token steps run in this session, as text: "persistent step kernel on: <configuration>" or
+ * "persistent step kernel off: <reason>" (tensor parallel, flags, a model outside what the kernel covers, a barrier
+ * that timed out earlier). No reference counterpart; benchmarks record it next to their numbers. */
+int brisk_cuda_step_path(brisk_cuda_session* session, char* text, size_t len);
 
 /* Per-phase device time, the counterpart of Session::profile() / BRISK_PROFILE (src/model.h:242-245,
  * src/main.cpp:302-306) and BRISK_GPU_PROFILE (src/metal/metal_session.mm:711-719). Writes the time accumulated since

@@ -201,3 +201,47 @@ def test_memory_preflight_refuses_what_cannot_fit(monkeypatch):
     monkeypatch.setenv("BRISK_NO_MEMORY_CHECK", "1")
     with engine.CudaSession(m) as s:
         assert s.max_context == 8192
+
+
+@pytest.mark.parametrize("family,spec", [
+    ("qwen3", synth.tiny(synth.QWEN3_0_6B, layers=3, vocab=1024, context=2048)),
+    ("llama", synth.tiny(synth.LLAMA_3_2_1B, layers=2, vocab=1024, context=1024)),
+    ("bitnet", synth.tiny(synth.BITNET_2B, layers=2, vocab=1024, context=1024)),
+    ("mistral", synth.tiny(synth.MISTRAL_7B, layers=2, vocab=1024, context=1024)),
+])
+def test_the_three_single_token_paths_agree_bit_for_bit(family, spec):
+    """A single-token step can run as one persistent kernel for all layers (the default where the model allows it), as
+    one fused kernel per operation, or through the batched kernels. All three repeat the same float operations in the
+    same order: their logits must be identical bits, at several context lengths (one that crosses the 512-position
+    chunk of the scores phase and the 64-position V tiles included)."""
+    from brisk_llm_b200 import abi
+    m = synth.perturb_norms(synth.generate(spec, seed=11))
+    toks = synth.random_tokens(spec, 700, seed=12)
+    results = {}
+    for name, flags in (("persistent", 0), ("per_operation", abi.FLAG_NO_PERSISTENT), ("batched", abi.FLAG_NO_MEGAKERNEL)):
+        with engine.CudaSession(m, flags=flags) as s:
+            assert ("kernel on" in s.step_path()) == (name == "persistent"), s.step_path()
+            out = []
+            at = 0
+            for prompt in (1, 62, 448, 130):  # decode at positions 1.., 63.., 511.. (crossing 512) and 641..
+                if prompt > 1:
+                    s.eval(toks[at:at + prompt - 1])
+                    at += prompt - 1
+                for _ in range(3):
+                    out.append(s.eval(toks[at:at + 1]))
+                    st = s.stats()
+                    assert st["persistent_steps"] == (1 if name == "persistent" else 0)
+                    at += 1
+            ids, logits = s.generate_greedy(int(toks[at]), 5, want_logits=True)
+            assert s.stats()["persistent_steps"] == (5 if name == "persistent" else 0)
+            out.append(logits)
+            out.append(np.asarray(ids, np.float32))
+            results[name] = out
+    for other in ("per_operation", "batched"):
+        # the ternary family's F16 head sums lane partials; the batched head kernel may group them differently
+        exact = family != "bitnet" or other == "per_operation"
+        for a, b in zip(results["persistent"], results[other]):
+            if exact:
+                assert np.array_equal(a, b), (other, float(np.abs(a - b).max()))
+            else:
+                assert np.abs(a - b).max() <= 1e-5, (other, float(np.abs(a - b).max()))
