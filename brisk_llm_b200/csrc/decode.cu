@@ -212,7 +212,7 @@ __global__ void __launch_bounds__(256) dec_attn_out_kernel(const DecAttnParams a
     extern __shared__ __align__(16) unsigned char raw[];
     __shared__ float redf[8];
     __shared__ double redd[8];
-    dec_attn_out_body<256>(a, blockIdx.x, raw, redf, redd, PdlGateEarly{a.pdl});
+    dec_attn_out_body<256>(a, blockIdx.x, blockIdx.y, raw, redf, redd, PdlGateEarly{a.pdl});
 }
 
 }  // namespace
@@ -250,7 +250,7 @@ void launch_dec_multiply(const MatTarget* targets, int count, const float* x, co
     }
 }
 
-void launch_dec_attention(const RopeArgs& r, const AttnArgs& at, cudaStream_t s) {
+void launch_dec_attention(const RopeArgs& r, const AttnArgs& at, uint32_t sms, cudaStream_t s) {
     DecAttnParams a{};
     a.q = r.q; a.k = r.k; a.v = r.v; a.q_norm = r.q_norm; a.k_norm = r.k_norm; a.rope = r.rope;
     a.k_cache = r.k_cache; a.v_cache = r.v_cache; a.scores = at.scores; a.out = at.out; a.position = r.position;
@@ -273,14 +273,15 @@ void launch_dec_attention(const RopeArgs& r, const AttnArgs& at, cudaStream_t s)
         default: throw CudaError("cuda: query heads per K/V head must be 1, 2, 4 or 8");
     }
 #undef BK_SCORES
-    const size_t smem2 = dec_attn_out_smem(a.max_context, a.dim);
+    a.slice_width = dec_attn_slice_width(a.heads, a.dim, sms);
+    const size_t smem2 = dec_attn_out_smem(a.max_context, a.slice_width);
     static bool raised = false;
     if (smem2 > 40 * 1024 && !raised) {
         BK_CUDA(cudaFuncSetAttribute(dec_attn_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         raised = true;
     }
     if (smem2 > 200 * 1024) throw CudaError("cuda: context too long for the single-token attention kernel");
-    launch_pdl(dec_attn_out_kernel, dim3(a.heads), dim3(256), smem2, s, a);
+    launch_pdl(dec_attn_out_kernel, dim3(a.heads, a.dim / a.slice_width), dim3(256), smem2, s, a);
 }
 
 }  // namespace bk

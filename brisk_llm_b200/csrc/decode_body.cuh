@@ -61,15 +61,66 @@ __device__ __forceinline__ void dec_stamp(unsigned long long* trace, uint32_t ct
     }
 }
 
+// ---- how a body exchanges vectors with the operations before and after it --------------------------------------
+// PlainIo: ordinary f32 vectors; the caller's gate (a kernel boundary, a grid barrier) orders producer and consumer.
+// TaggedIo: every element is an 8-byte pair {value bits, tag} written with ONE 8-byte store and read with 8- or
+// 16-byte loads that bypass L1. A consumer knows the tag its producer writes (unique per token, layer and operation)
+// and simply re-reads until every pair it needs carries that tag - value and tag arrive together, so no fence, no
+// counter and no barrier is needed between operations: a CTA starts an operation the moment ITS inputs are complete.
+// Safety of reuse: a buffer is overwritten only by an operation that has validated results which (transitively) could
+// only be produced after every reader of the buffer's previous contents had finished reading; CTAs with no rows in
+// an operation therefore must not read its input (they skip the prologue). Every poll loop is bounded: when it runs
+// out the CTA sets *error and goes on with whatever it has read, so the kernel always ends.
+struct PlainIo {
+    static constexpr bool kTagged = false;
+};
+struct TaggedIo {
+    static constexpr bool kTagged = true;
+    uint32_t tag_x;     // tag of the input vector
+    uint32_t tag_old;   // EPI_ADD: tag of the residual values being added to
+    uint32_t tag_out;   // tag this operation writes
+    unsigned int* error;
+    float* plain_out;   // optional: also store the results as ordinary floats (the step's final residual stream)
+};
+constexpr uint32_t kPollLimit = 1u << 20;  // re-reads of one batch before giving up (a fraction of a second)
+
+__device__ __forceinline__ uint4 ld_pairs2(const void* p) {  // two {value, tag} pairs, from L2
+    uint4 v;
+    asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint2 ld_pair(const void* p) {
+    uint2 v;
+    asm volatile("ld.relaxed.gpu.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_pair(void* p, float value, uint32_t tag) {
+    asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(__float_as_uint(value)), "r"(tag) : "memory");
+}
+__device__ __forceinline__ void poll_failed(unsigned int* error) { atomicExch(error, 1u); }
+// One tagged value; bounded.
+__device__ __forceinline__ float poll_pair(const void* p, uint32_t tag, unsigned int* error) {
+    uint2 v = ld_pair(p);
+    for (uint32_t spin = 0; v.y != tag; ++spin) {
+        if (spin == kPollLimit) {
+            poll_failed(error);
+            break;
+        }
+        v = ld_pair(p);
+    }
+    return __uint_as_float(v.x);
+}
+
 // One fused multiply by CTA `cta` of `nctas` (kDecWarps warps each): the CTA rebuilds the activation row in shared
 // memory (x, optionally RMS-normed, then quantised the way F takes it) and its warps walk row groups of RW rows.
 //   act_smem: dec_act_smem(cols) bytes, 16-byte aligned;  tile: dec_tile_floats(CHAINS) floats (exact formats);
 //   red: 32 doubles.
 // Ends with every thread past its last shared-memory access except the epilogue stores; callers that reuse the shared
 // memory must put a barrier after it.
-template <class F, int RW, bool PAIR, int kDepth, class Gate>
+template <class F, int RW, bool PAIR, int kDepth, class Gate, class Io = PlainIo>
 __device__ __forceinline__ void dec_multiply_body(const DecMatParams& p, const uint32_t cta, const uint32_t nctas, unsigned char* act_smem, float* tile,
-                                                  double* red, Gate&& gate) {
+                                                  double* red, Gate&& gate, const Io& io = Io{}) {
+    static_assert(!Io::kTagged || F::kExact, "tagged exchange is implemented for the exact (quantised) formats");
     constexpr int MATS = PAIR ? 2 : 1;
     constexpr int CHAINS = MATS * RW;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -98,6 +149,7 @@ __device__ __forceinline__ void dec_multiply_body(const DecMatParams& p, const u
             for (int r = 0; r < RW; ++r) w[a][r] = F::loadw(p.m[PAIR ? a : target], min(row0 + r, p.m[target].rows - 1), uu);
     };
 
+    if (cta * kDecWarps >= total_groups) return;  // no rows for this CTA: it must not touch the input either (see TaggedIo)
     dec_stamp(p.trace, cta, 0);
     // Weights (and the norm weights) do not depend on the previous operation: get them in flight before waiting for
     // it. A ring of kDepth iterations of weights per lane, refilled in iteration order: kDepth = 1 for the layer
@@ -121,6 +173,15 @@ __device__ __forceinline__ void dec_multiply_body(const DecMatParams& p, const u
 #pragma unroll
     for (int d = 0; d < kDepth; ++d) issue(wq[d]);
     const uint32_t cols = p.cols;
+    constexpr uint32_t kT = kDecWarps * 32;
+    const uint32_t n4 = cols / 4;
+    const float4* w4 = reinterpret_cast<const float4*>(p.weight);
+    float4 wpre[2];  // the norm weights of this thread's first two float4s (rows up to 4096 values): no dependence on the previous operation either
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const uint32_t i = threadIdx.x + k * kT;
+        wpre[k] = (p.weight != nullptr && i < n4) ? w4[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
     gate.wait();
     dec_stamp(p.trace, cta, 1);
     if (p.trace != nullptr && cta == 0 && threadIdx.x == 0) {  // tracing only: latency of one dependent load
@@ -134,17 +195,48 @@ __device__ __forceinline__ void dec_multiply_body(const DecMatParams& p, const u
     // Prologue: the activation row in shared memory - f32 (normed), then the planes this format multiplies by.
     // x as float4s (row lengths are multiples of 32), up to 8 per thread in flight so that their latencies overlap.
     float* xf = reinterpret_cast<float*>(act_smem);
-    constexpr uint32_t kT = kDecWarps * 32;
     const float4* x4 = reinterpret_cast<const float4*>(p.x);
     float4* xf4 = reinterpret_cast<float4*>(xf);
-    const uint32_t n4 = cols / 4;
     double part = 0.0;
     for (uint32_t base = 0; base < n4; base += 8 * kT) {
         float4 xv[8];
+        if constexpr (Io::kTagged) {
+            // float4 i = pairs 4i..4i+3 = two 16-byte loads; re-read the ones whose tags are not all there yet
+            const uint4* xp = reinterpret_cast<const uint4*>(p.x);
+            uint32_t pending = 0;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const uint32_t i = base + threadIdx.x + k * kT;
-            xv[k] = i < n4 ? __ldcg(x4 + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            for (int k = 0; k < 8; ++k) {
+                xv[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (base + threadIdx.x + k * kT < n4) pending |= 1u << k;
+            }
+            for (uint32_t spin = 0; pending != 0; ++spin) {
+                if (spin == kPollLimit) {
+                    poll_failed(io.error);
+                    break;
+                }
+                uint4 a[8], b[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    if (pending & (1u << k)) {
+                        const uint32_t i = base + threadIdx.x + k * kT;
+                        a[k] = ld_pairs2(xp + 2 * i);
+                        b[k] = ld_pairs2(xp + 2 * i + 1);
+                    }
+                }
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    if ((pending & (1u << k)) && a[k].y == io.tag_x && a[k].w == io.tag_x && b[k].y == io.tag_x && b[k].w == io.tag_x) {
+                        xv[k] = make_float4(__uint_as_float(a[k].x), __uint_as_float(a[k].z), __uint_as_float(b[k].x), __uint_as_float(b[k].z));
+                        pending &= ~(1u << k);
+                    }
+                }
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const uint32_t i = base + threadIdx.x + k * kT;
+                xv[k] = i < n4 ? __ldcg(x4 + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
         }
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
@@ -163,16 +255,19 @@ __device__ __forceinline__ void dec_multiply_body(const DecMatParams& p, const u
         double total = 0.0;
 #pragma unroll
         for (int w = 0; w < kDecWarps; ++w) total += red[w];
-        const float mean = float(total / double(cols));
+        // total / cols; a power-of-two length divides exactly by multiplying with its reciprocal (no f64 division)
+        const bool pow2 = (cols & (cols - 1)) == 0;
+        const double recip = __longlong_as_double((long long)(1023 - (31 - __clz(int(cols)))) << 52);
+        const float mean = float(pow2 ? total * recip : total / double(cols));
         const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, p.eps)));
         dec_stamp(p.trace, cta, 2);
-        const float4* w4 = reinterpret_cast<const float4*>(p.weight);
         for (uint32_t base = 0; base < n4; base += 8 * kT) {
             float4 wv[8];
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
                 const uint32_t i = base + threadIdx.x + k * kT;
-                wv[k] = i < n4 ? w4[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (k < 2 && base == 0) wv[k] = wpre[k];
+                else wv[k] = i < n4 ? w4[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             }
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
@@ -227,7 +322,10 @@ __device__ __forceinline__ void dec_multiply_body(const DecMatParams& p, const u
                 int target;
                 uint32_t row0;
                 locate(group, target, row0);
-                if (row0 + lane < p.m[target].rows) old = __ldcg(p.out[target] + row0 + lane);
+                if (row0 + lane < p.m[target].rows) {
+                    if constexpr (Io::kTagged) old = poll_pair(reinterpret_cast<const uint2*>(p.out[target]) + row0 + lane, io.tag_old, io.error);
+                    else old = __ldcg(p.out[target] + row0 + lane);
+                }
             }
             typename F::W w[MATS][RW];
 #pragma unroll
@@ -278,10 +376,16 @@ __device__ __forceinline__ void dec_multiply_body(const DecMatParams& p, const u
                 if constexpr (F::kExact) {
                     const float other = PAIR ? __shfl_down_sync(0xffffffffu, run, RW) : 0.0f;
                     if (lane < RW && row0 + lane < m.rows) {
-                        float* o = outp + row0 + lane;
-                        if (PAIR) *o = p.epi == EPI_SILU_MUL ? silu_mul(run, other) : relu2_mul(run, other);
-                        else if (p.epi == EPI_ADD) *o = __fadd_rn(old, run);
-                        else *o = run;
+                        float result;
+                        if (PAIR) result = p.epi == EPI_SILU_MUL ? silu_mul(run, other) : relu2_mul(run, other);
+                        else if (p.epi == EPI_ADD) result = __fadd_rn(old, run);
+                        else result = run;
+                        if constexpr (Io::kTagged) {
+                            st_pair(reinterpret_cast<uint2*>(outp) + row0 + lane, result, io.tag_out);
+                            if (io.plain_out != nullptr) io.plain_out[row0 + lane] = result;
+                        } else {
+                            outp[row0 + lane] = result;
+                        }
                     }
                     run = 0.0f;
                 } else {
@@ -326,6 +430,8 @@ struct DecAttnParams {
     float eps, scale;
     int neox;
     int pdl;
+    uint32_t slice_width;  // columns of V one CTA of the weighted sum takes (see dec_attn_slice_width)
+    unsigned long long* trace;  // optional development aid: time stamps (ns) of CTA 0 - 8 words for the scores, 8 for the weighted sum
 };
 
 // Per-head RMS norm (optional) + RoPE of one head by ONE WARP, as src/model.cpp:1031-1042. Lane l holds VPL = dim/32
@@ -333,12 +439,16 @@ struct DecAttnParams {
 // pairing (i, i + dim/2), elements VPL*l + k for the adjacent pairing (2i, 2i+1). No block-level barrier is needed.
 // `src` is read with L2 loads (it was produced by the previous operation of the step).
 template <int VPL, bool NEOX>
-__device__ __forceinline__ void warp_norm_rope_head_impl(const float* src, const float* norm, const float* rope, float eps, float* dst) {
-    constexpr uint32_t dim = VPL * 32;
+__device__ __forceinline__ void warp_head_load(const float* src, float (&v)[VPL]) {
     const uint32_t lane = threadIdx.x & 31;
-    float v[VPL];
 #pragma unroll
     for (int k = 0; k < VPL; ++k) v[k] = __ldcg(src + (NEOX ? lane + 32 * k : VPL * lane + k));
+}
+
+template <int VPL, bool NEOX>
+__device__ __forceinline__ void warp_head_norm_rope(float (&v)[VPL], const float* norm, const float* rope, float eps, float* dst) {
+    constexpr uint32_t dim = VPL * 32;
+    const uint32_t lane = threadIdx.x & 31;
     if (norm != nullptr) {
         double part = 0.0;
 #pragma unroll
@@ -362,6 +472,13 @@ __device__ __forceinline__ void warp_norm_rope_head_impl(const float* src, const
     }
 }
 
+template <int VPL, bool NEOX>
+__device__ __forceinline__ void warp_norm_rope_head_impl(const float* src, const float* norm, const float* rope, float eps, float* dst) {
+    float v[VPL];
+    warp_head_load<VPL, NEOX>(src, v);
+    warp_head_norm_rope<VPL, NEOX>(v, norm, rope, eps, dst);
+}
+
 template <int VPL>
 __device__ __forceinline__ void warp_norm_rope_head(const float* src, const float* norm, const float* rope, float eps, int neox, float* dst) {
     if (neox) warp_norm_rope_head_impl<VPL, true>(src, norm, rope, eps, dst);
@@ -381,48 +498,74 @@ __device__ __forceinline__ void warp_store_new_kv(const DecAttnParams& a, uint32
     }
 }
 
-// ---- softmax + weighted sum of one query head by one CTA of NT threads -------------------------------------------
+// ---- softmax + weighted sum: one CTA of NT threads per (query head, slice of the head's dimensions) --------------
+// The weighted sum is a serial chain per output dimension (position after position, as the CPU engine adds), so a head
+// cannot be split by positions - but it can be split by dimensions: each CTA recomputes the head's softmax (cheap) and
+// streams only its `slice_width` columns of V. More CTAs then pull V through more SMs' memory pipes at once, which is
+// what bounds this latency-bound phase.
 constexpr uint32_t kVTile = 64;   // positions of V per stage
-constexpr uint32_t kVStages = 4;  // stages in flight: the serial chain consumes a tile faster than L2 delivers one
+constexpr uint32_t kVStages = 8;  // stages in flight: contexts up to 512 positions are requested in one go
 
-inline size_t dec_attn_out_smem(uint32_t max_context, uint32_t dim) {
-    return ((size_t(max_context) * 4 + 15) & ~size_t(15)) + size_t(kVStages) * kVTile * dim * sizeof(__half);
+// The narrowest slice (16, 32, 64 ... columns) that still gives every (head, slice) task its own CTA.
+inline uint32_t dec_attn_slice_width(uint32_t heads, uint32_t dim, uint32_t ctas) {
+    uint32_t width = 16;
+    while (width < dim && heads * (dim / width) > ctas) width *= 2;
+    return width;
+}
+inline size_t dec_attn_out_smem(uint32_t max_context, uint32_t slice_width) {
+    return ((size_t(max_context) * 4 + 15) & ~size_t(15)) + size_t(kVStages) * kVTile * slice_width * sizeof(__half);
 }
 
-// raw: dec_attn_out_smem() bytes (probabilities [max_context] | V ring kVStages x [kVTile][dim] f16);
+// raw: dec_attn_out_smem() bytes (probabilities [max_context] | V ring kVStages x [kVTile][slice_width] f16);
 // redf / redd: NT/32 floats / doubles. V tiles that hold only earlier positions are requested before gate.wait();
 // the last tile holds the position written by this step and is requested after it.
-template <int NT, class Gate>
-__device__ __forceinline__ void dec_attn_out_body(const DecAttnParams& a, const uint32_t h, unsigned char* raw, float* redf, double* redd, Gate&& gate) {
+// With TaggedAttnIo the scores, the token's own V row (taken from the tagged v vector and rounded to f16 here, since
+// the cache row written earlier in the same launch is not ordered against anything this CTA can observe) and the
+// output are tagged pairs.
+struct TaggedAttnIo {
+    static constexpr bool kTagged = true;
+    uint32_t tag_scores, tag_v, tag_out;
+    unsigned int* error;
+};
+
+template <int NT, class Gate, class Io = PlainIo>
+__device__ __forceinline__ void dec_attn_out_body(const DecAttnParams& a, const uint32_t h, const uint32_t slice, unsigned char* raw, float* redf,
+                                                  double* redd, Gate&& gate, const Io& io = Io{}) {
     constexpr int kWarps = NT / 32;
-    const uint32_t tid = threadIdx.x, dim = a.dim;
+    const uint32_t tid = threadIdx.x, dim = a.dim, width = a.slice_width;
     const uint32_t visible = *a.position + 1;
     const uint32_t kvh = h / (a.heads / a.kv_heads);
     float* ps = reinterpret_cast<float*>(raw);
     __half* vt = reinterpret_cast<__half*>(raw + ((size_t(a.max_context) * 4 + 15) & ~size_t(15)));
     const float* s = a.scores + size_t(h) * a.max_context;
-    const __half* vbase = a.v_cache + size_t(kvh) * a.max_context * dim;
+    const __half* vbase = a.v_cache + size_t(kvh) * a.max_context * dim + slice * width;
 
     // V tiles stream through a ring of shared-memory stages with cp.async (L2 -> shared, not through L1).
     const uint32_t tiles = (visible + kVTile - 1) / kVTile;
-    const uint32_t chunks_per_tile = kVTile * dim / 8;  // 16-byte chunks
+    const uint32_t per_row = width / 8;                  // 16-byte chunks of one position's slice
+    const uint32_t chunks_per_tile = kVTile * per_row;
+    const uint32_t in_cache = Io::kTagged ? visible - 1 : visible;  // positions whose V row is read from the cache
     auto stage = [&](uint32_t tile_index) {
-        if (tile_index < tiles) {
-            __half* dst = vt + size_t(tile_index % kVStages) * kVTile * dim;
+        if (tile_index * kVTile < in_cache) {
+            __half* dst = vt + size_t(tile_index % kVStages) * kVTile * width;
             const __half* src = vbase + size_t(tile_index) * kVTile * dim;
-            const uint32_t rows = min(kVTile, visible - tile_index * kVTile);
+            const uint32_t rows = min(kVTile, in_cache - tile_index * kVTile);
             for (uint32_t c = tid; c < chunks_per_tile; c += NT) {
-                if (c * 8 < rows * dim) {
-                    const uint32_t sm_addr = uint32_t(__cvta_generic_to_shared(dst + c * 8));
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sm_addr), "l"(src + c * 8) : "memory");
+                const uint32_t row = c / per_row, col = (c % per_row) * 8;
+                if (row < rows) {
+                    const uint32_t sm_addr = uint32_t(__cvta_generic_to_shared(dst + row * width + col));
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sm_addr), "l"(src + size_t(row) * dim + col) : "memory");
                 }
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");  // one group per tile index, empty past the end
     };
+    unsigned long long* trace = (a.trace != nullptr && h == 0 && slice == 0) ? a.trace + 8 : nullptr;
+    dec_stamp(trace, 0, 0);
     uint32_t staged = 0;
     while (staged + 1 < kVStages && staged + 1 < tiles) stage(staged++);  // tiles before the last one
     gate.wait();
+    dec_stamp(trace, 0, 1);
     while (staged + 1 < kVStages) stage(staged++);
 
     // softmax (src/kernels_f32.cpp:275-284): max, e = expf(s - max), f64 sum, p = e * float(1/sum). Up to 8 scores per
@@ -434,12 +577,15 @@ __device__ __forceinline__ void dec_attn_out_body(const DecAttnParams& a, const 
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
             const uint32_t p = tid + k * NT;
-            sv[k] = p < visible ? __ldcg(s + p) : -INFINITY;
+            if constexpr (Io::kTagged) sv[k] = p < visible ? poll_pair(reinterpret_cast<const uint2*>(a.scores) + size_t(h) * a.max_context + p, io.tag_scores, io.error) : -INFINITY;
+            else sv[k] = p < visible ? __ldcg(s + p) : -INFINITY;
             mx = fmaxf(mx, sv[k]);
         }
     } else {
         for (uint32_t p = tid; p < visible; p += NT) {
-            const float v = __ldcg(s + p);
+            float v;
+            if constexpr (Io::kTagged) v = poll_pair(reinterpret_cast<const uint2*>(a.scores) + size_t(h) * a.max_context + p, io.tag_scores, io.error);
+            else v = __ldcg(s + p);
             ps[p] = v;
             mx = fmaxf(mx, v);
         }
@@ -450,6 +596,7 @@ __device__ __forceinline__ void dec_attn_out_body(const DecAttnParams& a, const 
     mx = redf[0];
 #pragma unroll
     for (int w = 1; w < kWarps; ++w) mx = fmaxf(mx, redf[w]);
+    dec_stamp(trace, 0, 2);
     double part = 0.0;
     if (in_regs) {
 #pragma unroll
@@ -466,6 +613,7 @@ __device__ __forceinline__ void dec_attn_out_body(const DecAttnParams& a, const 
             part += double(e);
         }
     }
+    dec_stamp(trace, 0, 3);
     part = warp_sum(part);
     if ((tid & 31) == 0) redd[tid >> 5] = part;
     __syncthreads();
@@ -473,6 +621,7 @@ __device__ __forceinline__ void dec_attn_out_body(const DecAttnParams& a, const 
 #pragma unroll
     for (int w = 0; w < kWarps; ++w) total += redd[w];
     const float inv = float(1.0 / total);
+    dec_stamp(trace, 0, 4);
     if (in_regs) {
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
@@ -489,21 +638,31 @@ __device__ __forceinline__ void dec_attn_out_body(const DecAttnParams& a, const 
         stage(t + kVStages - 1);  // refills the stage consumed in the previous iteration
         asm volatile("cp.async.wait_group %0;" ::"n"(kVStages - 1) : "memory");
         __syncthreads();  // tile t has landed for every thread (and ps is complete on the first pass)
-        if (tid < dim) {
-            const __half* tv = vt + size_t(t % kVStages) * kVTile * dim + tid;
+        if constexpr (Io::kTagged) {
+            if (t + 1 == tiles && tid < width) {  // the token's own row: column tid is read back by this same thread below
+                const float v = poll_pair(reinterpret_cast<const uint2*>(a.v) + size_t(kvh) * dim + slice * width + tid, io.tag_v, io.error);
+                vt[size_t(t % kVStages) * kVTile * width + ((visible - 1) % kVTile) * width + tid] = __float2half_rn(v);
+            }
+        }
+        if (tid < width) {
+            const __half* tv = vt + size_t(t % kVStages) * kVTile * width + tid;
             const uint32_t rows = min(kVTile, visible - t * kVTile);
             const float* pw = ps + t * kVTile;
             if (rows == kVTile) {
 #pragma unroll
-                for (uint32_t j = 0; j < kVTile; ++j) acc = __fadd_rn(acc, __fmul_rn(pw[j], __half2float(tv[j * dim])));
+                for (uint32_t j = 0; j < kVTile; ++j) acc = __fadd_rn(acc, __fmul_rn(pw[j], __half2float(tv[j * width])));
             } else {
-                for (uint32_t j = 0; j < rows; ++j) acc = __fadd_rn(acc, __fmul_rn(pw[j], __half2float(tv[j * dim])));
+                for (uint32_t j = 0; j < rows; ++j) acc = __fadd_rn(acc, __fmul_rn(pw[j], __half2float(tv[j * width])));
             }
         }
         __syncthreads();  // everyone is done with tile t before its stage is refilled
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");  // only empty groups remain
-    if (tid < dim) a.out[size_t(h) * dim + tid] = acc;
+    dec_stamp(trace, 0, 5);
+    if (tid < width) {
+        if constexpr (Io::kTagged) st_pair(reinterpret_cast<uint2*>(a.out) + size_t(h) * dim + slice * width + tid, acc, io.tag_out);
+        else a.out[size_t(h) * dim + slice * width + tid] = acc;
+    }
 }
 
 #endif  // __CUDACC__

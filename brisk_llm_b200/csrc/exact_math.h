@@ -37,7 +37,9 @@ namespace bk {
 
 static const uint64_t kExp2TableHost[32] = {BK_EXP2_TABLE};
 #if defined(__CUDACC__)
-static __constant__ uint64_t kExp2TableDev[32] = {BK_EXP2_TABLE};
+// In global memory, read through the read-only cache: lanes of a warp look up different entries, which constant
+// memory would serve one address at a time.
+static __device__ const uint64_t kExp2TableDev[32] = {BK_EXP2_TABLE};
 #endif
 
 BK_HD float exact_expf(float x) {
@@ -54,7 +56,7 @@ BK_HD float exact_expf(float x) {
     const uint64_t ki = uint64_t(__double_as_longlong(kd));
     kd = __dsub_rn(kd, shift);
     const double r = __dsub_rn(z, kd);
-    const double s = __longlong_as_double((long long)(kExp2TableDev[ki & 31] + (ki << 47)));
+    const double s = __longlong_as_double((long long)(__ldg(&kExp2TableDev[ki & 31]) + (ki << 47)));
     const double p = __dadd_rn(__dmul_rn(c0, r), c1);
     const double r2 = __dmul_rn(r, r);
     double y = __dadd_rn(__dmul_rn(c2, r), 1.0);

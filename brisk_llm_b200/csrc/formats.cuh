@@ -12,16 +12,18 @@ __device__ __forceinline__ int dp4a(uint32_t a, uint32_t b, int c) { return __dp
 // ---- per-format unit arithmetic -------------------------------------------------------------------------
 // Each format provides: W (a unit's weights in registers), X (the matching activations of one token),
 // loadw / loadx, and term(): the f32 contribution of the unit, already including every scale. term() may
-// shuffle, so all 32 lanes call it together; `valid` masks lanes past the row end.
+// shuffle, so all 32 lanes call it together; `valid` masks lanes past the row end. loadw() only loads - scales stay
+// f16 in W and are widened in term() - so that a kernel can issue a unit's loads long before it uses them without an
+// arithmetic instruction on a loaded value stalling the warp in between.
 
 struct FQ4_0 {
     static constexpr int kLanesPerTerm = 1;
     static constexpr bool kExact = true;
-    struct W { uint4 q; float d; };
+    struct W { uint4 q; __half d; };
     struct X { uint4 lo, hi; float d; int s; };
     static __device__ __forceinline__ W loadw(const DevMatrix& m, uint32_t row, uint32_t u) {
         const size_t i = size_t(row) * m.units + u;
-        return {ld_stream(m.qa + i * 16), __half2float(m.d[i])};
+        return {ld_stream(m.qa + i * 16), m.d[i]};
     }
     static __device__ __forceinline__ X loadx(const DevAct& a, uint32_t t, uint32_t u) {
         const uint4* p = reinterpret_cast<const uint4*>(a.q0 + size_t(t) * a.cols + u * 32);
@@ -39,18 +41,18 @@ struct FQ4_0 {
         acc = dp4a((w.q.z >> 4) & 0x0F0F0F0Fu, x.hi.z, acc);
         acc = dp4a((w.q.w >> 4) & 0x0F0F0F0Fu, x.hi.w, acc);
         acc -= 8 * x.s;  // sum((q-8)*x) = sum(q*x) - 8*sum(x)
-        return valid ? __fmul_rn(__fmul_rn(float(acc), w.d), x.d) : 0.0f;
+        return valid ? __fmul_rn(__fmul_rn(float(acc), __half2float(w.d)), x.d) : 0.0f;
     }
 };
 
 struct FQ8_0 {
     static constexpr int kLanesPerTerm = 2;
     static constexpr bool kExact = true;
-    struct W { uint4 q; float d; };
+    struct W { uint4 q; __half d; };
     struct X { uint4 q; float d; };
     static __device__ __forceinline__ W loadw(const DevMatrix& m, uint32_t row, uint32_t u) {
         const size_t i = size_t(row) * m.units + u;
-        return {ld_stream(m.qa + i * 16), __half2float(m.d[size_t(row) * m.blocks + (u >> 1)])};
+        return {ld_stream(m.qa + i * 16), m.d[size_t(row) * m.blocks + (u >> 1)]};
     }
     static __device__ __forceinline__ X loadx(const DevAct& a, uint32_t t, uint32_t u) {
         return {*reinterpret_cast<const uint4*>(a.q0 + size_t(t) * a.cols + u * 16), a.d0[size_t(t) * (a.cols / 32) + (u >> 1)]};
@@ -63,14 +65,14 @@ struct FQ8_0 {
         acc = dp4a(w.q.w, x.q.w, acc);
         acc = valid ? acc : 0;
         acc += __shfl_xor_sync(0xffffffffu, acc, 1);  // the block's other half
-        return (valid && (u & 1) == 0) ? __fmul_rn(__fmul_rn(float(acc), w.d), x.d) : 0.0f;
+        return (valid && (u & 1) == 0) ? __fmul_rn(__fmul_rn(float(acc), __half2float(w.d)), x.d) : 0.0f;
     }
 };
 
 struct FQ4_K {
     static constexpr int kLanesPerTerm = 8;
     static constexpr bool kExact = true;
-    struct W { uint4 q; uint32_t sc0, sc1, mn0, mn1; float d, dmin; };
+    struct W { uint4 q; uint32_t sc0, sc1, mn0, mn1; __half2 dd; };
     struct X { uint4 lo, hi; float d; int bs0, bs1; };
     static __device__ __forceinline__ W loadw(const DevMatrix& m, uint32_t row, uint32_t u) {
         const size_t i = size_t(row) * m.units + u;
@@ -78,7 +80,7 @@ struct FQ4_K {
         const uint32_t g = (u & 7) >> 1;
         const uint8_t* s = m.sc + blk * 16;
         const __half2 dd = reinterpret_cast<const __half2*>(m.d)[blk];
-        return {ld_stream(m.qa + i * 16), s[2 * g], s[2 * g + 1], s[8 + 2 * g], s[9 + 2 * g], __low2float(dd), __high2float(dd)};
+        return {ld_stream(m.qa + i * 16), s[2 * g], s[2 * g + 1], s[8 + 2 * g], s[9 + 2 * g], dd};
     }
     static __device__ __forceinline__ X loadx(const DevAct& a, uint32_t t, uint32_t u) {
         const uint32_t sb = u >> 3, j = u & 7, g = j >> 1, hf = j & 1;
@@ -104,14 +106,14 @@ struct FQ4_K {
             offsets += __shfl_xor_sync(0xffffffffu, offsets, o);
         }
         if (!valid || (u & 7) != 0) return 0.0f;
-        return __fmul_rn(x.d, __fsub_rn(__fmul_rn(w.d, float(weighted)), __fmul_rn(w.dmin, float(offsets))));
+        return __fmul_rn(x.d, __fsub_rn(__fmul_rn(__low2float(w.dd), float(weighted)), __fmul_rn(__high2float(w.dd), float(offsets))));
     }
 };
 
 struct FQ6_K {
     static constexpr int kLanesPerTerm = 4;
     static constexpr bool kExact = true;
-    struct W { uint4 a, b, c; int sc[4]; float d; };
+    struct W { uint4 a, b, c; int sc[4]; __half d; };
     struct X { uint4 q[4]; float d; int bs[4]; };
     static __device__ __forceinline__ W loadw(const DevMatrix& m, uint32_t row, uint32_t u) {
         const size_t i = size_t(row) * m.units + u;
@@ -124,7 +126,7 @@ struct FQ6_K {
         w.c = ld_stream(m.qc + i * 16);
 #pragma unroll
         for (int k = 0; k < 4; ++k) w.sc[k] = s[2 * k];
-        w.d = __half2float(m.d[blk]);
+        w.d = m.d[blk];
         return w;
     }
     static __device__ __forceinline__ X loadx(const DevAct& a, uint32_t t, uint32_t u) {
@@ -164,18 +166,18 @@ struct FQ6_K {
         weighted += __shfl_xor_sync(0xffffffffu, weighted, 1);
         weighted += __shfl_xor_sync(0xffffffffu, weighted, 2);
         if (!valid || (u & 3) != 0) return 0.0f;
-        return __fmul_rn(__fmul_rn(x.d, w.d), float(weighted));
+        return __fmul_rn(__fmul_rn(x.d, __half2float(w.d)), float(weighted));
     }
 };
 
 struct FTQ2_0 {
     static constexpr int kLanesPerTerm = 4;
     static constexpr bool kExact = true;
-    struct W { uint4 q; float d; };
+    struct W { uint4 q; __half d; };
     struct X { uint4 q[4]; float d; int bsum; };
     static __device__ __forceinline__ W loadw(const DevMatrix& m, uint32_t row, uint32_t u) {
         const size_t i = size_t(row) * m.units + u;
-        return {ld_stream(m.qa + i * 16), __half2float(m.d[size_t(row) * m.blocks + (u >> 2)])};
+        return {ld_stream(m.qa + i * 16), m.d[size_t(row) * m.blocks + (u >> 2)]};
     }
     static __device__ __forceinline__ X loadx(const DevAct& a, uint32_t t, uint32_t u) {
         const uint32_t sb = u >> 2, c = u & 3;
@@ -205,7 +207,7 @@ struct FTQ2_0 {
         acc += __shfl_xor_sync(0xffffffffu, acc, 1);
         acc += __shfl_xor_sync(0xffffffffu, acc, 2);
         if (!valid || (u & 3) != 0) return 0.0f;
-        return __fmul_rn(__fmul_rn(x.d, w.d), float(acc));
+        return __fmul_rn(__fmul_rn(x.d, __half2float(w.d)), float(acc));
     }
 };
 

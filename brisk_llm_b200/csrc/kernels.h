@@ -105,7 +105,7 @@ void launch_dec_multiply(const MatTarget* targets, int count, const float* x, co
                          uint32_t sms, cudaStream_t s, unsigned long long* trace = nullptr);
 // Attention of the single new token: scores kernel (per-head norm + RoPE of q and the new k, f16 K/V store in its
 // prologue) and softmax + weighted-sum kernel. Takes the same argument structs as the batched kernels (n is 1).
-void launch_dec_attention(const RopeArgs& r, const AttnArgs& at, cudaStream_t s);
+void launch_dec_attention(const RopeArgs& r, const AttnArgs& at, uint32_t sms, cudaStream_t s);
 
 // ---- the single-token step of all layers as one persistent kernel (step.cu) -------------------------------------
 struct StepLayerArgs {
@@ -133,6 +133,7 @@ struct StepShared {  // the step's activation vectors and the model constants ev
     float eps = 0.0f, scale = 0.0f;
     int neox = 0;
     int act_epi = EPI_SILU_MUL;
+    unsigned long long* body_trace = nullptr;  // development aid: 4 x 8 words for the stamps inside one layer's multiplies
 };
 // Built once per session (the weights and buffers are fixed); launch() runs layers 0..n-1 of one token whose embedding
 // is in `hidden` and whose position is in *position. build() returns false, with the reason, when the model is outside
@@ -150,6 +151,8 @@ public:
     bool ready() const { return impl_ != nullptr; }
     void launch(cudaStream_t s) const;
     const unsigned int* error_word() const;
+    // Development aid: 4 words per phase (6 per layer) written by CTA 0 - entry, barrier passed, finished (ns), polls.
+    void set_trace(unsigned long long* words);
     void rearm(cudaStream_t s);
     const std::string& description() const { return description_; }
 

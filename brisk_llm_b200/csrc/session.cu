@@ -468,9 +468,16 @@ struct Session {
         sh.max_context = uint32_t(max_context);
         sh.eps = eps; sh.scale = 1.0f / std::sqrt(static_cast<float>(head_dim)); sh.neox = neox;
         sh.act_epi = arch == BRISK_ARCH_BITNET ? EPI_RELU2_MUL : EPI_SILU_MUL;
+        const bool tracing = std::getenv("BRISK_CUDA_STEP_TRACE") != nullptr;
+        if (tracing) {  // per-phase stamps of every layer, then the stamps inside one layer's multiplies
+            trace.alloc((size_t(n_layers) * 6 * 4 + 48) * sizeof(unsigned long long));
+            BK_CUDA(cudaMemset(trace.p, 0, trace.bytes));
+            sh.body_trace = trace.as<unsigned long long>() + size_t(n_layers) * 6 * 4;
+        }
         std::string why;
         step_enabled = step_plan.build(args, sh, sms, stream, why);
         step_note = step_enabled ? "on: " + step_plan.description() : "off: " + why;
+        if (step_enabled && tracing) step_plan.set_trace(trace.as<unsigned long long>());
     }
 
     // ---- forward ---------------------------------------------------------------------------------------
@@ -594,7 +601,7 @@ struct Session {
             {
                 Scope sc(this, PH_ATTENTION);
                 if (single) {
-                    launch_dec_attention(r, at, stream);
+                    launch_dec_attention(r, at, sms, stream);
                     launches += 2;
                 } else {
                     launch_qk_norm_rope_store(r, stream);

@@ -16,8 +16,9 @@
 // Barrier: a monotonic arrival counter; barrier k opens when it reaches k x CTAs. Every CTA arrives once per phase and
 // waits once per barrier, also when it has no work in a phase (otherwise its early arrivals would open a later barrier
 // too soon). The last CTA to leave the kernel zeroes the counter for the next launch. Every wait is bounded: after
-// kSpinLimit polls (about a second) the CTA sets the error word, stops waiting at this and every later barrier, and
-// the kernel runs to its end with meaningless results; the host checks the word after the launch and raises. The launch
+// kSpinLimit polls (about a second) the CTA sets the error word and adds a huge constant to the counter, which opens
+// this and every later barrier for all CTAs; the kernel runs to its end with meaningless results, and the host checks
+// the word after the launch and raises. The launch
 // is cooperative, so the CTAs are co-resident or the launch itself fails.
 #include <algorithm>
 #include <cstdio>
@@ -29,22 +30,31 @@
 
 namespace bk {
 
-struct StepLayerDesc {
+struct alignas(16) StepLayerDesc {
     DecMatParams qkv, o, gate_up, down;
     DecAttnParams attn;
 };
+static_assert(sizeof(StepLayerDesc) % 16 == 0, "copied in 16-byte pieces");
 
 namespace {
 
 constexpr uint32_t kStepThreads = kDecWarps * 32;
 constexpr uint32_t kSpinLimit = 1u << 21;
+constexpr unsigned int kOpenAll = 1u << 30;  // far above any arrival count of one launch
 
 struct StepParams {
     const StepLayerDesc* layers;
     uint32_t n_layers;
     unsigned int* sync;   // [0] arrivals, [1] exits, [2] error
     uint32_t tile_offset; // bytes from the start of dynamic shared memory to the transpose tile (after the widest activation row)
+    unsigned long long* trace;  // optional (BRISK_CUDA_STEP_TRACE): per phase, CTA 0's time of entry, of passing the barrier, of finishing, and its polls
 };
+
+__device__ __forceinline__ unsigned long long now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 __device__ __forceinline__ unsigned int ld_acquire(const unsigned int* p) {
     unsigned int v;
@@ -60,94 +70,156 @@ struct GridGate {
     unsigned int target;  // arrivals that open the next barrier
     unsigned int nctas;
     bool waited;          // this phase's barrier has been passed (or the phase needs none)
+    unsigned long long* trace;  // CTA 0 only, else nullptr: four words per phase
+    int* open_flag;       // shared memory: the result of enter()'s single poll
 
+    // Start of a phase: ONE poll before the phase requests anything. An acquire load does not complete while the
+    // thread's earlier loads are in flight, so a poll issued after the weight prefetch would wait for the prefetch; a
+    // CTA that finds its barrier open already (the usual case for the CTAs that arrive last) skips the wait entirely
+    // and its prefetch overlaps the activation prologue instead.
+    __device__ __forceinline__ void enter() {
+        if (waited) return;
+        if (threadIdx.x == 0) *open_flag = int(ld_acquire(sync) - target) >= 0 ? 1 : 0;
+        __syncthreads();
+        if (*open_flag != 0) {
+            waited = true;
+            if (trace != nullptr && threadIdx.x == 0) {
+                trace[1] = now_ns();
+                trace[3] = 0;
+            }
+        }
+    }
+
+    // Thread 0 polls with acquire loads; the barrier that follows orders every other thread of the CTA behind it.
     __device__ __forceinline__ void wait() {
         if (waited) return;
         waited = true;
         if (threadIdx.x == 0) {
-            const volatile unsigned int* error = sync + 2;
-            if (*error == 0) {
-                unsigned int spins = 0;
-                while (int(ld_acquire(sync) - target) < 0) {
-                    if (++spins > kSpinLimit || ((spins & 255u) == 0 && *error != 0)) {
-                        atomicExch(sync + 2, 1u);
-                        break;
-                    }
-                    if (spins > 16) __nanosleep(64);
+            unsigned int spins = 0;
+            while (int(ld_acquire(sync) - target) < 0) {
+                if (++spins > kSpinLimit) {  // give up: flag it and open this and every later barrier for every CTA
+                    atomicExch(sync + 2, 1u);
+                    atomicAdd(sync, kOpenAll);
+                    break;
                 }
             }
-            __threadfence();
+            if (trace != nullptr) {
+                trace[1] = now_ns();
+                trace[3] = spins;
+            }
         }
         __syncthreads();
     }
     __device__ __forceinline__ void prologue_done() {}
     // End of a phase: make sure this phase's barrier was passed, publish the phase's results, arm the next barrier.
+    // The release reduction of thread 0, after the CTA barrier, publishes the stores of all of the CTA's threads.
     __device__ __forceinline__ void arrive() {
+        if (trace != nullptr && threadIdx.x == 0) trace[2] = now_ns();
         wait();
         __syncthreads();  // every thread's stores of this phase are issued
         if (threadIdx.x == 0) {
-            __threadfence();
             red_release_add(sync, 1u);
+            if (trace != nullptr) {
+                trace += 4;
+                trace[0] = now_ns();
+            }
         }
         target += nctas;
         waited = false;
     }
 };
 
-// Scores of the new token against every visible position: tasks of (K/V head, 512 positions), one position per thread,
-// the query heads of the group one after another against the thread's K row. The row waits in shared memory (each
-// thread copies its own 2*dim bytes with cp.async, requested before the barrier; rows are padded by 16 bytes so that the
-// 16-byte reads of a quarter warp fall into distinct banks) - held in registers it would not fit the 128 registers a
-// 512-thread CTA has per thread. The task that covers the token's own position norms, rotates and stores the new K and
-// V rows. sm: (group + 1) * dim floats, then 512 padded K rows.
-__host__ __device__ inline size_t step_scores_smem(uint32_t group, uint32_t dim) {
-    return size_t(group + 1) * dim * sizeof(float) + size_t(kStepThreads) * (dim * 2 + 16);
+// Scores of the new token against every visible position, as WARP tasks of (K/V head, 32 positions) dealt round-robin
+// over the CTAs (a 600-position context of 8 K/V heads gives 152 tasks: one warp on every SM), so that the K rows come
+// in over every SM's memory pipe at once. A warp needs no CTA barrier: it copies its 32 K rows into its own slice of
+// shared memory with cp.async (requested BEFORE the grid barrier; rows padded by 16 bytes so that the 16-byte reads of
+// a quarter warp fall into distinct banks), norms and rotates the group's query heads into the same slice, and each
+// lane then owns one position. The task that covers the token's own position also norms, rotates and stores the new
+// K and V rows. Arithmetic and order per (head, position) are those of the per-operation scores kernel.
+constexpr uint32_t kMaxGroup = 8;
+__host__ __device__ inline size_t step_scores_warp_smem(uint32_t group, uint32_t dim) {
+    return size_t(group + 1) * dim * sizeof(float) + size_t(32) * (dim * 2 + 16);
 }
 
+template <int VPL, bool NEOX>
 __device__ __forceinline__ void step_scores(const DecAttnParams& a, const uint32_t cta, const uint32_t nctas, unsigned char* sm, GridGate& gate) {
-    const uint32_t dim = a.dim, group = a.heads / a.kv_heads;
+    constexpr uint32_t dim = VPL * 32;
+    const uint32_t group = a.heads / a.kv_heads;
     const uint32_t pos = *a.position, visible = pos + 1;
-    const uint32_t chunks = (visible + kStepThreads - 1) / kStepThreads;
+    const uint32_t chunks = (visible + 31) / 32;
     const uint32_t tasks = a.kv_heads * chunks;
-    const uint32_t warp = threadIdx.x >> 5;
-    float* qs = reinterpret_cast<float*>(sm);
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    unsigned char* mine = sm + size_t(warp) * step_scores_warp_smem(group, dim);
+    float* qs = reinterpret_cast<float*>(mine);
     float* knew = qs + group * dim;
-    const uint4* krow = reinterpret_cast<const uint4*>(sm + size_t(group + 1) * dim * sizeof(float) + size_t(threadIdx.x) * (dim * 2 + 16));
+    const uint4* krow = reinterpret_cast<const uint4*>(mine + size_t(group + 1) * dim * sizeof(float) + size_t(lane) * (dim * 2 + 16));
     const float* rope = a.rope + size_t(pos) * dim;
-    for (uint32_t task = cta; task < tasks; task += nctas) {
-        const uint32_t kvh = task / chunks, begin = (task % chunks) * kStepThreads;
-        const uint32_t p = begin + threadIdx.x;
-        const bool cached = p < visible && p != pos;
-        if (cached) {
+
+    auto request_row = [&](uint32_t task) {  // this lane's cached K row of the task, if it has one
+        const uint32_t kvh = task / chunks, p = (task % chunks) * 32 + lane;
+        if (p < visible && p != pos) {
             const __half* kr = a.k_cache + (size_t(kvh) * a.max_context + p) * dim;
             const uint32_t dst = uint32_t(__cvta_generic_to_shared(krow));
+#pragma unroll
             for (uint32_t i = 0; i < dim / 8; ++i) {
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + i * 16), "l"(kr + i * 8) : "memory");
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
-        gate.wait();
-        const bool owns_new = pos >= begin && pos < begin + kStepThreads;
-        for (uint32_t t = warp; t < group + 1u; t += kDecWarps) {
-            if (t < group) {
-                const float* src = a.q + size_t(kvh * group + t) * dim;
-                if (dim == 128) warp_norm_rope_head<4>(src, a.q_norm, rope, a.eps, a.neox, qs + t * dim);
-                else warp_norm_rope_head<2>(src, a.q_norm, rope, a.eps, a.neox, qs + t * dim);
-            } else if (owns_new) {
-                const float* src = a.k + size_t(kvh) * dim;
-                if (dim == 128) warp_norm_rope_head<4>(src, a.k_norm, rope, a.eps, a.neox, knew);
-                else warp_norm_rope_head<2>(src, a.k_norm, rope, a.eps, a.neox, knew);
-                __syncwarp();
-                warp_store_new_kv(a, kvh, pos, knew);
+    };
+    const uint32_t first = cta + warp * nctas, stride = nctas * kDecWarps;
+    dec_stamp(a.trace, cta, 0);
+    if (first < tasks) request_row(first);
+    gate.wait();
+    dec_stamp(a.trace, cta, 1);
+    for (uint32_t task = first; task < tasks; task += stride) {
+        if (task != first) request_row(task);
+        const uint32_t kvh = task / chunks, begin = (task % chunks) * 32;
+        const uint32_t p = begin + lane;
+        const bool cached = p < visible && p != pos;
+        // the group's raw query heads (contiguous in q) and, for the task that owns the token's position, the raw new
+        // K row: into the slice through L2, then norm + RoPE in place (a lane rewrites exactly the elements it read)
+        {
+            const float* qsrc = a.q + size_t(kvh) * group * dim;
+            const uint32_t qdst = uint32_t(__cvta_generic_to_shared(qs));
+            for (uint32_t i = lane; i < group * dim / 4; i += 32) {
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(qdst + i * 16), "l"(qsrc + i * 4) : "memory");
             }
         }
-        asm volatile("cp.async.wait_group 0;" ::: "memory");  // this thread's own row
-        __syncthreads();
+        const bool owner = pos >= begin && pos < begin + 32;
+        if (owner) {
+            const float* ksrc = a.k + size_t(kvh) * dim;
+            const uint32_t kdst = uint32_t(__cvta_generic_to_shared(knew));
+            for (uint32_t i = lane; i < dim / 4; i += 32) {
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kdst + i * 16), "l"(ksrc + i * 4) : "memory");
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");  // the raw heads, and this lane's K row requested earlier
+        __syncwarp();
+        dec_stamp(a.trace, cta, 2);
+        if (owner) {
+            float kv[VPL];
+#pragma unroll
+            for (int k = 0; k < VPL; ++k) kv[k] = knew[NEOX ? lane + 32 * k : VPL * lane + k];
+            warp_head_norm_rope<VPL, NEOX>(kv, a.k_norm, rope, a.eps, knew);
+            __syncwarp();
+            warp_store_new_kv(a, kvh, pos, knew);
+        }
+        for (uint32_t g = 0; g < group; ++g) {
+            float v[VPL];
+#pragma unroll
+            for (int k = 0; k < VPL; ++k) v[k] = qs[g * dim + (NEOX ? lane + 32 * k : VPL * lane + k)];
+            warp_head_norm_rope<VPL, NEOX>(v, a.q_norm, rope, a.eps, qs + g * dim);
+        }
+        __syncwarp();
+        dec_stamp(a.trace, cta, 3);
         if (p < visible) {
             for (uint32_t g = 0; g < group; ++g) {
                 float lanes[16];
 #pragma unroll
                 for (int j = 0; j < 16; ++j) lanes[j] = 0.0f;
+#pragma unroll
                 for (uint32_t i = 0; i < dim; i += 16) {
                     float kf[16];
                     if (!cached) {
@@ -179,7 +251,8 @@ __device__ __forceinline__ void step_scores(const DecAttnParams& a, const uint32
                 a.scores[size_t(kvh * group + g) * a.max_context + p] = __fmul_rn(sum, a.scale);
             }
         }
-        __syncthreads();  // qs / knew and the K rows are rewritten by the CTA's next task
+        __syncwarp();  // the slice is rewritten by the warp's next task
+        dec_stamp(a.trace, cta, 4);
     }
 }
 
@@ -193,31 +266,68 @@ __global__ void __launch_bounds__(kStepThreads, 1) step_kernel(const StepParams 
     constexpr int kWordsPerUnit = int(sizeof(typename F::W) / 4);
     float* tile = reinterpret_cast<float*>(smem + P.tile_offset);
     const uint32_t cta = blockIdx.x, nctas = gridDim.x;
-    GridGate gate{P.sync, 0u, nctas, true};  // the first phase reads what earlier kernels wrote: no barrier
+    // The layer's descriptor (pointers, shapes, row-group tables) is read many times on the way to the first weight
+    // load of a phase; from global memory those dependent reads cost more than a microsecond per phase. Each layer's
+    // descriptor is therefore copied into shared memory while the previous layer runs.
+    __shared__ StepLayerDesc desc[2];
+    constexpr uint32_t kDescPieces = sizeof(StepLayerDesc) / 16;
+    auto fetch_desc = [&](uint32_t layer) {
+        if (threadIdx.x < kDescPieces) {
+            const uint32_t dst = uint32_t(__cvta_generic_to_shared(reinterpret_cast<unsigned char*>(&desc[layer & 1]) + threadIdx.x * 16));
+            const unsigned char* src = reinterpret_cast<const unsigned char*>(P.layers + layer) + threadIdx.x * 16;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    static_assert(kDescPieces <= kStepThreads, "one piece per thread");
+    fetch_desc(0);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    __shared__ int open_flag;
+    GridGate gate{P.sync, 0u, nctas, true, cta == 0 ? P.trace : nullptr, &open_flag};  // the first phase reads what earlier kernels wrote: no barrier
+    if (gate.trace != nullptr && threadIdx.x == 0) gate.trace[0] = now_ns();
 
     for (uint32_t l = 0; l < P.n_layers; ++l) {
-        const StepLayerDesc& L = P.layers[l];
+        const StepLayerDesc& L = desc[l & 1];
+        if (l + 1 < P.n_layers) fetch_desc(l + 1);  // the other buffer's layer finished behind the barrier of its last arrive
+        gate.enter();
         dec_multiply_body<F, RWA, false, ring_depth(RWA * kWordsPerUnit, DEEP)>(L.qkv, cta, nctas, smem, tile, red, gate);
         gate.arrive();
 
-        step_scores(L.attn, cta, nctas, smem, gate);
-        gate.arrive();
-
-        for (uint32_t h = cta; h < L.attn.heads; h += nctas) {
-            dec_attn_out_body<kStepThreads>(L.attn, h, smem, redf, red, gate);
-            __syncthreads();  // the shared-memory row of probabilities is rewritten for the CTA's next head
+        gate.enter();
+        if (L.attn.dim == 128) {
+            if (L.attn.neox) step_scores<4, true>(L.attn, cta, nctas, smem, gate);
+            else step_scores<4, false>(L.attn, cta, nctas, smem, gate);
+        } else {
+            if (L.attn.neox) step_scores<2, true>(L.attn, cta, nctas, smem, gate);
+            else step_scores<2, false>(L.attn, cta, nctas, smem, gate);
         }
         gate.arrive();
 
+        gate.enter();
+        {
+            const uint32_t slices = L.attn.dim / L.attn.slice_width;
+            for (uint32_t task = cta; task < L.attn.heads * slices; task += nctas) {
+                dec_attn_out_body<kStepThreads>(L.attn, task / slices, task % slices, smem, redf, red, gate);
+                __syncthreads();  // the shared-memory row of probabilities is rewritten for the CTA's next task
+            }
+        }
+        gate.arrive();
+
+        gate.enter();
         dec_multiply_body<F, RWO, false, ring_depth(RWO * kWordsPerUnit, DEEP)>(L.o, cta, nctas, smem, tile, red, gate);
         gate.arrive();
 
+        gate.enter();
         dec_multiply_body<F, RWG, true, ring_depth(2 * RWG * kWordsPerUnit, DEEP)>(L.gate_up, cta, nctas, smem, tile, red, gate);
         gate.arrive();
 
+        gate.enter();
         dec_multiply_body<F, RWD, false, ring_depth(RWD * kWordsPerUnit, DEEP)>(L.down, cta, nctas, smem, tile, red, gate);
+        asm volatile("cp.async.wait_group 0;" ::: "memory");  // the next layer's descriptor (long since landed); arrive's barrier publishes it
         if (l + 1 < P.n_layers) gate.arrive();
     }
+    if (gate.trace != nullptr && threadIdx.x == 0) gate.trace[2] = now_ns();
 
     // Leave: the last CTA out re-arms the counters for the next launch (every CTA is past all of its waits by then).
     __syncthreads();
@@ -292,6 +402,7 @@ struct StepPlan::Impl {
     unsigned int* sync_dev = nullptr;
     uint32_t n_layers = 0, grid = 0, tile_offset = 0;
     size_t smem = 0;
+    unsigned long long* trace = nullptr;
 };
 
 StepPlan::StepPlan() = default;
@@ -328,7 +439,7 @@ bool StepPlan::build(const std::vector<StepLayerArgs>& layers, const StepShared&
         return false;
     }
     const uint32_t group = sh.heads / sh.kv_heads;
-    if (group > 8) {
+    if (group > kMaxGroup) {
         why_not = "more than 8 query heads per K/V head";
         return false;
     }
@@ -356,6 +467,15 @@ bool StepPlan::build(const std::vector<StepLayerArgs>& layers, const StepShared&
         a.k_cache = L.k_cache; a.v_cache = L.v_cache; a.scores = sh.scores; a.out = sh.attended; a.position = sh.position;
         a.heads = sh.heads; a.kv_heads = sh.kv_heads; a.dim = sh.dim; a.max_context = sh.max_context;
         a.eps = sh.eps; a.scale = sh.scale; a.neox = sh.neox; a.pdl = 0;
+        a.slice_width = dec_attn_slice_width(sh.heads, sh.dim, sms);
+    }
+    if (sh.body_trace != nullptr) {
+        StepLayerDesc& d = descs[std::min<size_t>(5, descs.size() - 1)];
+        d.qkv.trace = sh.body_trace;
+        d.o.trace = sh.body_trace + 8;
+        d.gate_up.trace = sh.body_trace + 16;
+        d.down.trace = sh.body_trace + 24;
+        d.attn.trace = sh.body_trace + 32;
     }
     // One variant for all layers: the rows per warp every layer can take.
     int want[4] = {4, 4, 4, 4};
@@ -385,7 +505,7 @@ bool StepPlan::build(const std::vector<StepLayerArgs>& layers, const StepShared&
     const uint32_t widest = std::max(std::max(sh.hidden_size, sh.heads * sh.dim), sh.ffn_size);
     const size_t act = (dec_act_smem(widest) + 15) & ~size_t(15);
     const size_t multiply = act + dec_tile_floats(8) * sizeof(float);
-    const size_t attention = std::max(dec_attn_out_smem(sh.max_context, sh.dim), step_scores_smem(group, sh.dim));
+    const size_t attention = std::max(dec_attn_out_smem(sh.max_context, dec_attn_slice_width(sh.heads, sh.dim, sms)), size_t(kDecWarps) * step_scores_warp_smem(group, sh.dim));
     const size_t smem = std::max(multiply, attention);
     int dev = 0, limit = 0, coop = 0;
     BK_CUDA(cudaGetDevice(&dev));
@@ -430,6 +550,7 @@ void StepPlan::launch(cudaStream_t s) const {
     P.n_layers = impl_->n_layers;
     P.sync = impl_->sync_dev;
     P.tile_offset = impl_->tile_offset;
+    P.trace = impl_->trace;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(impl_->grid);
     cfg.blockDim = dim3(kStepThreads);
@@ -442,6 +563,8 @@ void StepPlan::launch(cudaStream_t s) const {
     cfg.numAttrs = 1;
     BK_CUDA(cudaLaunchKernelEx(&cfg, impl_->kernel, P));
 }
+
+void StepPlan::set_trace(unsigned long long* words) { impl_->trace = words; }
 
 const unsigned int* StepPlan::error_word() const { return impl_->sync_dev + 2; }
 

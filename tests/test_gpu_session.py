@@ -220,7 +220,9 @@ def test_the_three_single_token_paths_agree_bit_for_bit(family, spec):
     results = {}
     for name, flags in (("persistent", 0), ("per_operation", abi.FLAG_NO_PERSISTENT), ("batched", abi.FLAG_NO_MEGAKERNEL)):
         with engine.CudaSession(m, flags=flags) as s:
-            assert ("kernel on" in s.step_path()) == (name == "persistent"), s.step_path()
+            uniform = len({f for n, (f, sh, d) in m.tensors.items() if n.startswith("blk.") and not n.endswith("norm.weight")}) == 1
+            persistent = name == "persistent" and uniform  # mixed weight types in the layers keep the per-operation kernels
+            assert ("kernel on" in s.step_path()) == persistent, s.step_path()
             out = []
             at = 0
             for prompt in (1, 62, 448, 130):  # decode at positions 1.., 63.., 511.. (crossing 512) and 641..
@@ -230,10 +232,10 @@ def test_the_three_single_token_paths_agree_bit_for_bit(family, spec):
                 for _ in range(3):
                     out.append(s.eval(toks[at:at + 1]))
                     st = s.stats()
-                    assert st["persistent_steps"] == (1 if name == "persistent" else 0)
+                    assert st["persistent_steps"] == (1 if persistent else 0)
                     at += 1
             ids, logits = s.generate_greedy(int(toks[at]), 5, want_logits=True)
-            assert s.stats()["persistent_steps"] == (5 if name == "persistent" else 0)
+            assert s.stats()["persistent_steps"] == (5 if persistent else 0)
             out.append(logits)
             out.append(np.asarray(ids, np.float32))
             results[name] = out
