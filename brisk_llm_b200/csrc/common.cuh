@@ -15,7 +15,7 @@
 namespace bk {
 
 // ggml tensor-type ids (same numbering as include/brisk_cuda.h).
-enum : int { T_F32 = 0, T_F16 = 1, T_Q4_0 = 2, T_Q8_0 = 8, T_Q4_K = 12, T_Q6_K = 14, T_TQ2_0 = 35 };
+enum : int { T_F32 = 0, T_F16 = 1, T_Q4_0 = 2, T_Q4_1 = 3, T_Q5_0 = 6, T_Q8_0 = 8, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14, T_BF16 = 30, T_TQ2_0 = 35 };
 
 constexpr int kMaxSmallBatch = 8;  // tokens one pass of the streaming (matvec-family) kernels covers
 
@@ -37,14 +37,18 @@ inline void check(cudaError_t e, const char* what, const char* file, int line) {
 // so a warp reading consecutive units of a row issues fully coalesced 16-byte loads.
 //
 //   Q4_0   unit = one 32-value block: qa[16 B] (file nibble order); d: f16 per block
+//   Q4_1   as Q4_0;                                                 d: half2 (d, m) per block
+//   Q5_0   as Q4_0; qb: the block's 32 fifth bits (one u32);        d: f16 per block
 //   Q8_0   unit = half a block (16 int8);                           d: f16 per block (unit/2)
 //   Q4_K   unit = 16 bytes of qs: 16 low-nibble values of sub-block 2g and 16 high-nibble values of
 //          sub-block 2g+1 (g = (unit%8)/2, half (unit%2) of each); sc: 16 B per super-block =
 //          8 unpacked 6-bit scales then 8 mins; d: half2 (d, dmin) per super-block
+//   Q5_K   as Q4_K; qb: one u32 per unit - bits 0..15 the fifth bits of the unit's 16 low-nibble values,
+//          bits 16..31 those of its 16 high-nibble values
 //   Q6_K   unit = 64 values: qa/qb = the two 16-byte runs of low nibbles, qc = 16 bytes of high bit
 //          pairs; 4 units per super-block; sc: 16 int8 per super-block; d: f16 per super-block
 //   TQ2_0  unit = 16 bytes = 4 runs of 16 ternary values; 4 units per super-block; d: f16 per super-block
-//   F16 / F32: qa = the row-major values, no other plane
+//   F16 / F32: qa = the row-major values, no other plane (BF16 files are widened to F32 at upload)
 struct DevMatrix {
     int type = T_F32;
     uint32_t rows = 0, cols = 0;
@@ -75,13 +79,19 @@ struct DevAct {
     uint32_t cols = 0;
 };
 
-inline bool takes_q8_k(int type) { return type == T_Q4_K || type == T_Q6_K || type == T_TQ2_0; }
-inline uint32_t block_elems(int type) { return type == T_Q4_0 || type == T_Q8_0 ? 32u : (type == T_F32 || type == T_F16 ? 1u : 256u); }
+inline bool takes_q8_k(int type) { return type == T_Q4_K || type == T_Q5_K || type == T_Q6_K || type == T_TQ2_0; }
+inline uint32_t block_elems(int type) {
+    return type == T_Q4_0 || type == T_Q4_1 || type == T_Q5_0 || type == T_Q8_0 ? 32u : (type == T_F32 || type == T_F16 || type == T_BF16 ? 1u : 256u);
+}
 inline uint32_t block_bytes(int type) {
     switch (type) {
         case T_F32: return 4;
         case T_F16: return 2;
+        case T_BF16: return 2;
         case T_Q4_0: return 18;
+        case T_Q4_1: return 20;
+        case T_Q5_0: return 22;
+        case T_Q5_K: return 176;
         case T_Q8_0: return 34;
         case T_Q4_K: return 144;
         case T_Q6_K: return 210;

@@ -77,8 +77,7 @@ __global__ void __launch_bounds__(kDecWarps * 32) dec_matvec_kernel(const DecMat
 template <class F, int RW, bool PAIR>
 void launch_dec_one(DecMatParams& p, uint32_t sms, cudaStream_t s) {
     const uint32_t groups = dec_assign_groups(p, RW, PAIR);
-    const uint32_t want = (groups + kDecWarps - 1) / kDecWarps;
-    const uint32_t grid = want < sms ? want : sms;  // one CTA per SM at most; warps walk the remaining row groups
+    const uint32_t grid = groups < sms ? groups : sms;  // one CTA per SM; row groups go round-robin over CTAs, then warps
     const size_t smem = dec_act_smem(p.cols);
     // Ring depth: as deep as keeps the weights in flight per lane (matrices x rows x depth units of 16 bytes) at 8 or
     // fewer, so that they stay in registers; one iteration ahead is enough when a warp has only a few iterations.
@@ -240,7 +239,10 @@ void launch_dec_multiply(const MatTarget* targets, int count, const float* x, co
     if (pair && targets[0].m.rows != targets[1].m.rows) throw CudaError("cuda: gate and up must have the same rows");
     switch (targets[0].m.type) {
         case T_Q4_0: dispatch_dec<FQ4_0>(p, pair, sms, s); break;
+        case T_Q4_1: dispatch_dec<FQ4_1>(p, pair, sms, s); break;
+        case T_Q5_0: dispatch_dec<FQ5_0>(p, pair, sms, s); break;
         case T_Q8_0: dispatch_dec<FQ8_0>(p, pair, sms, s); break;
+        case T_Q5_K: dispatch_dec<FQ5_K>(p, pair, sms, s); break;
         case T_Q4_K: dispatch_dec<FQ4_K>(p, pair, sms, s); break;
         case T_Q6_K: dispatch_dec<FQ6_K>(p, pair, sms, s); break;
         case T_TQ2_0: dispatch_dec<FTQ2_0>(p, pair, sms, s); break;

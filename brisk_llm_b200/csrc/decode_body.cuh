@@ -125,8 +125,10 @@ __device__ __forceinline__ void dec_multiply_body(const DecMatParams& p, const u
     constexpr int CHAINS = MATS * RW;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t total_groups = p.first_group[PAIR ? 1 : p.count];
+    // Row groups are dealt round-robin over the CTAs first, then over a CTA's warps: a matrix with fewer groups than
+    // the grid has warps still streams through every SM's memory pipe.
     const uint32_t stride = nctas * kDecWarps;
-    const uint32_t first = cta * kDecWarps + warp;
+    const uint32_t first = warp * nctas + cta;
 
     auto locate = [&](uint32_t group, int& target, uint32_t& row0) {
         target = 0;
@@ -149,7 +151,7 @@ __device__ __forceinline__ void dec_multiply_body(const DecMatParams& p, const u
             for (int r = 0; r < RW; ++r) w[a][r] = F::loadw(p.m[PAIR ? a : target], min(row0 + r, p.m[target].rows - 1), uu);
     };
 
-    if (cta * kDecWarps >= total_groups) return;  // no rows for this CTA: it must not touch the input either (see TaggedIo)
+    if (cta >= total_groups) return;  // no rows for this CTA: it must not touch the input either (see TaggedIo)
     dec_stamp(p.trace, cta, 0);
     // Weights (and the norm weights) do not depend on the previous operation: get them in flight before waiting for
     // it. A ring of kDepth iterations of weights per lane, refilled in iteration order: kDepth = 1 for the layer
@@ -198,48 +200,47 @@ __device__ __forceinline__ void dec_multiply_body(const DecMatParams& p, const u
     const float4* x4 = reinterpret_cast<const float4*>(p.x);
     float4* xf4 = reinterpret_cast<float4*>(xf);
     double part = 0.0;
-    for (uint32_t base = 0; base < n4; base += 8 * kT) {
-        float4 xv[8];
+    constexpr int kBatch = Io::kTagged ? 4 : 8;  // float4s per thread in flight (the tagged form holds twice the registers per float4)
+    // K = how many float4s per thread this batch really has (1, 2, 4 or 8): a 1024-value row is one float4 for half of
+    // the threads, and a fixed 8-way unrolled, predicated form would have every warp issue eight times the code.
+    auto load_batch = [&](uint32_t base, auto kc) {
+        constexpr int K = decltype(kc)::value;
+        float4 xv[K];
         if constexpr (Io::kTagged) {
-            // float4 i = pairs 4i..4i+3 = two 16-byte loads; re-read the ones whose tags are not all there yet
+            // float4 i = pairs 4i..4i+3 = two 16-byte loads; the whole batch is re-read until every tag is there
             const uint4* xp = reinterpret_cast<const uint4*>(p.x);
-            uint32_t pending = 0;
+            uint4 a[K], b[K];
+            for (uint32_t spin = 0;; ++spin) {
+                bool complete = true;
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                xv[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                if (base + threadIdx.x + k * kT < n4) pending |= 1u << k;
-            }
-            for (uint32_t spin = 0; pending != 0; ++spin) {
+                for (int k = 0; k < K; ++k) {
+                    const uint32_t i = base + threadIdx.x + k * kT;
+                    if (i < n4) {
+                        a[k] = ld_pairs2(xp + 2 * i);
+                        b[k] = ld_pairs2(xp + 2 * i + 1);
+                    } else {
+                        a[k] = b[k] = make_uint4(0u, io.tag_x, 0u, io.tag_x);
+                    }
+                }
+#pragma unroll
+                for (int k = 0; k < K; ++k) complete = complete && a[k].y == io.tag_x && a[k].w == io.tag_x && b[k].y == io.tag_x && b[k].w == io.tag_x;
+                if (complete) break;
                 if (spin == kPollLimit) {
                     poll_failed(io.error);
                     break;
                 }
-                uint4 a[8], b[8];
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    if (pending & (1u << k)) {
-                        const uint32_t i = base + threadIdx.x + k * kT;
-                        a[k] = ld_pairs2(xp + 2 * i);
-                        b[k] = ld_pairs2(xp + 2 * i + 1);
-                    }
-                }
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    if ((pending & (1u << k)) && a[k].y == io.tag_x && a[k].w == io.tag_x && b[k].y == io.tag_x && b[k].w == io.tag_x) {
-                        xv[k] = make_float4(__uint_as_float(a[k].x), __uint_as_float(a[k].z), __uint_as_float(b[k].x), __uint_as_float(b[k].z));
-                        pending &= ~(1u << k);
-                    }
-                }
             }
+#pragma unroll
+            for (int k = 0; k < K; ++k) xv[k] = make_float4(__uint_as_float(a[k].x), __uint_as_float(a[k].z), __uint_as_float(b[k].x), __uint_as_float(b[k].z));
         } else {
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
+            for (int k = 0; k < K; ++k) {
                 const uint32_t i = base + threadIdx.x + k * kT;
                 xv[k] = i < n4 ? __ldcg(x4 + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             }
         }
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
+        for (int k = 0; k < K; ++k) {
             const uint32_t i = base + threadIdx.x + k * kT;
             if (i < n4) xf4[i] = xv[k];
             part += double(__fmul_rn(xv[k].x, xv[k].x));  // padding adds exact zeros
@@ -247,6 +248,13 @@ __device__ __forceinline__ void dec_multiply_body(const DecMatParams& p, const u
             part += double(__fmul_rn(xv[k].z, xv[k].z));
             part += double(__fmul_rn(xv[k].w, xv[k].w));
         }
+    };
+    for (uint32_t base = 0; base < n4; base += kBatch * kT) {
+        const uint32_t left = n4 - base;
+        if (left <= kT) load_batch(base, std::integral_constant<int, 1>{});
+        else if (left <= 2 * kT) load_batch(base, std::integral_constant<int, 2>{});
+        else if (left <= 4 * kT || kBatch == 4) load_batch(base, std::integral_constant<int, 4>{});
+        else load_batch(base, std::integral_constant<int, kBatch>{});
     }
     if (p.weight != nullptr) {
         part = warp_sum(part);
@@ -261,16 +269,17 @@ __device__ __forceinline__ void dec_multiply_body(const DecMatParams& p, const u
         const float mean = float(pow2 ? total * recip : total / double(cols));
         const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, p.eps)));
         dec_stamp(p.trace, cta, 2);
-        for (uint32_t base = 0; base < n4; base += 8 * kT) {
-            float4 wv[8];
+        auto scale_batch = [&](uint32_t base, auto kc) {
+            constexpr int K = decltype(kc)::value;
+            float4 wv[K];
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
+            for (int k = 0; k < K; ++k) {
                 const uint32_t i = base + threadIdx.x + k * kT;
                 if (k < 2 && base == 0) wv[k] = wpre[k];
                 else wv[k] = i < n4 ? w4[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             }
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
+            for (int k = 0; k < K; ++k) {
                 const uint32_t i = base + threadIdx.x + k * kT;
                 if (i < n4) {  // the same thread wrote xf4[i] above
                     const float4 xx = xf4[i];
@@ -278,6 +287,12 @@ __device__ __forceinline__ void dec_multiply_body(const DecMatParams& p, const u
                                          __fmul_rn(__fmul_rn(xx.z, scale), wv[k].z), __fmul_rn(__fmul_rn(xx.w, scale), wv[k].w));
                 }
             }
+        };
+        for (uint32_t base = 0; base < n4; base += 8 * kT) {
+            const uint32_t left = n4 - base;
+            if (left <= kT) scale_batch(base, std::integral_constant<int, 1>{});
+            else if (left <= 2 * kT) scale_batch(base, std::integral_constant<int, 2>{});
+            else scale_batch(base, std::integral_constant<int, 8>{});
         }
     }
     __syncthreads();
@@ -286,7 +301,7 @@ __device__ __forceinline__ void dec_multiply_body(const DecMatParams& p, const u
     act.cols = cols;
     act.f32 = xf;
     unsigned char* planes = act_smem + size_t(cols) * 4;
-    if constexpr (std::is_same_v<F, FQ4_0> || std::is_same_v<F, FQ8_0>) {
+    if constexpr (std::is_same_v<F, FQ4_0> || std::is_same_v<F, FQ4_1> || std::is_same_v<F, FQ5_0> || std::is_same_v<F, FQ8_0>) {
         int8_t* q = reinterpret_cast<int8_t*>(planes);
         float* d = reinterpret_cast<float*>(planes + cols);
         int32_t* s = reinterpret_cast<int32_t*>(planes + cols + (cols / 32) * 4);
@@ -501,24 +516,19 @@ __device__ __forceinline__ void warp_store_new_kv(const DecAttnParams& a, uint32
 // ---- softmax + weighted sum: one CTA of NT threads per (query head, slice of the head's dimensions) --------------
 // The weighted sum is a serial chain per output dimension (position after position, as the CPU engine adds), so a head
 // cannot be split by positions - but it can be split by dimensions: each CTA recomputes the head's softmax (cheap) and
-// streams only its `slice_width` columns of V. More CTAs then pull V through more SMs' memory pipes at once, which is
-// what bounds this latency-bound phase.
+// streams only its `slice_width` (16 or 32) columns of V. More CTAs then pull V through more SMs' memory pipes at
+// once, which is what bounds this latency-bound phase. Inside the CTA all warps share the softmax; the chain itself is
+// one warp's work, so that warp alone also feeds its V ring (cp.async groups are per thread: with producer = consumer
+// the tile loop needs no CTA barrier, only warp barriers).
 constexpr uint32_t kVTile = 64;   // positions of V per stage
 constexpr uint32_t kVStages = 8;  // stages in flight: contexts up to 512 positions are requested in one go
 
-// The narrowest slice (16, 32, 64 ... columns) that still gives every (head, slice) task its own CTA.
-inline uint32_t dec_attn_slice_width(uint32_t heads, uint32_t dim, uint32_t ctas) {
-    uint32_t width = 16;
-    while (width < dim && heads * (dim / width) > ctas) width *= 2;
-    return width;
-}
+// The narrowest slice (16, then 32 columns) that still gives every (head, slice) task its own CTA.
+inline uint32_t dec_attn_slice_width(uint32_t heads, uint32_t dim, uint32_t ctas) { return heads * (dim / 16) > ctas ? 32u : 16u; }
 inline size_t dec_attn_out_smem(uint32_t max_context, uint32_t slice_width) {
     return ((size_t(max_context) * 4 + 15) & ~size_t(15)) + size_t(kVStages) * kVTile * slice_width * sizeof(__half);
 }
 
-// raw: dec_attn_out_smem() bytes (probabilities [max_context] | V ring kVStages x [kVTile][slice_width] f16);
-// redf / redd: NT/32 floats / doubles. V tiles that hold only earlier positions are requested before gate.wait();
-// the last tile holds the position written by this step and is requested after it.
 // With TaggedAttnIo the scores, the token's own V row (taken from the tagged v vector and rounded to f16 here, since
 // the cache row written earlier in the same launch is not ordered against anything this CTA can observe) and the
 // output are tagged pairs.
@@ -528,11 +538,14 @@ struct TaggedAttnIo {
     unsigned int* error;
 };
 
+// raw: dec_attn_out_smem() bytes (probabilities [max_context] | V ring kVStages x [kVTile][slice_width] f16);
+// redf / redd: NT/32 floats / doubles. V tiles that hold only earlier positions are requested before gate.wait();
+// the last tile holds the position written by this step and is requested after it.
 template <int NT, class Gate, class Io = PlainIo>
 __device__ __forceinline__ void dec_attn_out_body(const DecAttnParams& a, const uint32_t h, const uint32_t slice, unsigned char* raw, float* redf,
                                                   double* redd, Gate&& gate, const Io& io = Io{}) {
     constexpr int kWarps = NT / 32;
-    const uint32_t tid = threadIdx.x, dim = a.dim, width = a.slice_width;
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, dim = a.dim, width = a.slice_width;
     const uint32_t visible = *a.position + 1;
     const uint32_t kvh = h / (a.heads / a.kv_heads);
     float* ps = reinterpret_cast<float*>(raw);
@@ -540,7 +553,7 @@ __device__ __forceinline__ void dec_attn_out_body(const DecAttnParams& a, const 
     const float* s = a.scores + size_t(h) * a.max_context;
     const __half* vbase = a.v_cache + size_t(kvh) * a.max_context * dim + slice * width;
 
-    // V tiles stream through a ring of shared-memory stages with cp.async (L2 -> shared, not through L1).
+    // V tiles stream through a ring of shared-memory stages with cp.async (L2 -> shared, not through L1); warp 0 only.
     const uint32_t tiles = (visible + kVTile - 1) / kVTile;
     const uint32_t per_row = width / 8;                  // 16-byte chunks of one position's slice
     const uint32_t chunks_per_tile = kVTile * per_row;
@@ -550,7 +563,7 @@ __device__ __forceinline__ void dec_attn_out_body(const DecAttnParams& a, const 
             __half* dst = vt + size_t(tile_index % kVStages) * kVTile * width;
             const __half* src = vbase + size_t(tile_index) * kVTile * dim;
             const uint32_t rows = min(kVTile, in_cache - tile_index * kVTile);
-            for (uint32_t c = tid; c < chunks_per_tile; c += NT) {
+            for (uint32_t c = lane; c < chunks_per_tile; c += 32) {
                 const uint32_t row = c / per_row, col = (c % per_row) * 8;
                 if (row < rows) {
                     const uint32_t sm_addr = uint32_t(__cvta_generic_to_shared(dst + row * width + col));
@@ -563,105 +576,104 @@ __device__ __forceinline__ void dec_attn_out_body(const DecAttnParams& a, const 
     unsigned long long* trace = (a.trace != nullptr && h == 0 && slice == 0) ? a.trace + 8 : nullptr;
     dec_stamp(trace, 0, 0);
     uint32_t staged = 0;
-    while (staged + 1 < kVStages && staged + 1 < tiles) stage(staged++);  // tiles before the last one
+    if (warp == 0) {
+        while (staged + 1 < kVStages && staged + 1 < tiles) stage(staged++);  // tiles before the last one
+    }
     gate.wait();
     dec_stamp(trace, 0, 1);
-    while (staged + 1 < kVStages) stage(staged++);
+    if (warp == 0) {
+        while (staged + 1 < kVStages) stage(staged++);
+    }
 
-    // softmax (src/kernels_f32.cpp:275-284): max, e = expf(s - max), f64 sum, p = e * float(1/sum). Up to 8 scores per
-    // thread stay in registers; longer rows go through shared memory.
-    const bool in_regs = visible <= 8 * NT;
-    float sv[8];
+    // softmax (src/kernels_f32.cpp:275-284): max, e = expf(s - max), f64 sum, p = e * float(1/sum). The row lives in
+    // shared memory; the loops have run-time trip counts (one or two rounds at short contexts) - an unrolled,
+    // predicated form issues its exp code eight times whether or not a thread has a score.
     float mx = -INFINITY;
-    if (in_regs) {
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const uint32_t p = tid + k * NT;
-            if constexpr (Io::kTagged) sv[k] = p < visible ? poll_pair(reinterpret_cast<const uint2*>(a.scores) + size_t(h) * a.max_context + p, io.tag_scores, io.error) : -INFINITY;
-            else sv[k] = p < visible ? __ldcg(s + p) : -INFINITY;
-            mx = fmaxf(mx, sv[k]);
-        }
-    } else {
-        for (uint32_t p = tid; p < visible; p += NT) {
-            float v;
-            if constexpr (Io::kTagged) v = poll_pair(reinterpret_cast<const uint2*>(a.scores) + size_t(h) * a.max_context + p, io.tag_scores, io.error);
-            else v = __ldcg(s + p);
-            ps[p] = v;
-            mx = fmaxf(mx, v);
-        }
+    for (uint32_t p = tid; p < visible; p += NT) {
+        float v;
+        if constexpr (Io::kTagged) v = poll_pair(reinterpret_cast<const uint2*>(a.scores) + size_t(h) * a.max_context + p, io.tag_scores, io.error);
+        else v = __ldcg(s + p);
+        ps[p] = v;
+        mx = fmaxf(mx, v);
     }
     mx = warp_max(mx);
-    if ((tid & 31) == 0) redf[tid >> 5] = mx;
+    if (lane == 0) redf[warp] = mx;
     __syncthreads();
     mx = redf[0];
 #pragma unroll
     for (int w = 1; w < kWarps; ++w) mx = fmaxf(mx, redf[w]);
     dec_stamp(trace, 0, 2);
     double part = 0.0;
-    if (in_regs) {
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            if (tid + k * NT < visible) {
-                sv[k] = exact_expf(__fsub_rn(sv[k], mx));
-                part += double(sv[k]);
-            }
-        }
-    } else {
-        for (uint32_t p = tid; p < visible; p += NT) {
-            const float e = exact_expf(__fsub_rn(ps[p], mx));
-            ps[p] = e;
-            part += double(e);
-        }
+    for (uint32_t p = tid; p < visible; p += NT) {
+        const float e = exact_expf(__fsub_rn(ps[p], mx));
+        ps[p] = e;
+        part += double(e);
     }
     dec_stamp(trace, 0, 3);
     part = warp_sum(part);
-    if ((tid & 31) == 0) redd[tid >> 5] = part;
+    if (lane == 0) redd[warp] = part;
     __syncthreads();
     double total = 0.0;
 #pragma unroll
     for (int w = 0; w < kWarps; ++w) total += redd[w];
     const float inv = float(1.0 / total);
     dec_stamp(trace, 0, 4);
-    if (in_regs) {
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const uint32_t p = tid + k * NT;
-            if (p < visible) ps[p] = __fmul_rn(sv[k], inv);
-        }
-    } else {
-        for (uint32_t p = tid; p < visible; p += NT) ps[p] = __fmul_rn(ps[p], inv);
-    }
+    for (uint32_t p = tid; p < visible; p += NT) ps[p] = __fmul_rn(ps[p], inv);
+    __syncthreads();  // the probabilities are complete for warp 0
+    if (warp != 0) return;
 
-    // weighted sum (src/kernels_f32.cpp:265-273): out[i] += p[pos] * v[pos][i], position after position.
+    // weighted sum (src/kernels_f32.cpp:265-273): out[i] += p[pos] * v[pos][i], position after position. Lane c owns
+    // column c of the slice. Batches of 16 positions: a batch's 16 products are formed (independent loads, conversions
+    // and multiplies) while the previous batch's 16 adds - the serial chain - are still in flight.
+    const uint32_t col = lane < width ? lane : 0;
     float acc = 0.0f;
     for (uint32_t t = 0; t < tiles; ++t) {
         stage(t + kVStages - 1);  // refills the stage consumed in the previous iteration
         asm volatile("cp.async.wait_group %0;" ::"n"(kVStages - 1) : "memory");
-        __syncthreads();  // tile t has landed for every thread (and ps is complete on the first pass)
+        __syncwarp();  // tile t has landed for every lane
+        __half* tile_v = vt + size_t(t % kVStages) * kVTile * width;
         if constexpr (Io::kTagged) {
-            if (t + 1 == tiles && tid < width) {  // the token's own row: column tid is read back by this same thread below
-                const float v = poll_pair(reinterpret_cast<const uint2*>(a.v) + size_t(kvh) * dim + slice * width + tid, io.tag_v, io.error);
-                vt[size_t(t % kVStages) * kVTile * width + ((visible - 1) % kVTile) * width + tid] = __float2half_rn(v);
+            if (t + 1 == tiles && lane < width) {  // the token's own row: column `lane` is read back by this same lane below
+                const float v = poll_pair(reinterpret_cast<const uint2*>(a.v) + size_t(kvh) * dim + slice * width + lane, io.tag_v, io.error);
+                tile_v[((visible - 1) % kVTile) * width + lane] = __float2half_rn(v);
             }
         }
-        if (tid < width) {
-            const __half* tv = vt + size_t(t % kVStages) * kVTile * width + tid;
-            const uint32_t rows = min(kVTile, visible - t * kVTile);
-            const float* pw = ps + t * kVTile;
-            if (rows == kVTile) {
+        const __half* tv = tile_v + col;
+        const uint32_t rows = min(kVTile, visible - t * kVTile);
+        const float* pw = ps + t * kVTile;
+        auto products = [&](uint32_t j, float (&prod)[16]) {
 #pragma unroll
-                for (uint32_t j = 0; j < kVTile; ++j) acc = __fadd_rn(acc, __fmul_rn(pw[j], __half2float(tv[j * width])));
-            } else {
-                for (uint32_t j = 0; j < rows; ++j) acc = __fadd_rn(acc, __fmul_rn(pw[j], __half2float(tv[j * width])));
+            for (int q = 0; q < 4; ++q) {
+                const float4 pv = *reinterpret_cast<const float4*>(pw + j + 4 * q);
+                prod[4 * q + 0] = __fmul_rn(pv.x, __half2float(tv[(j + 4 * q + 0) * width]));
+                prod[4 * q + 1] = __fmul_rn(pv.y, __half2float(tv[(j + 4 * q + 1) * width]));
+                prod[4 * q + 2] = __fmul_rn(pv.z, __half2float(tv[(j + 4 * q + 2) * width]));
+                prod[4 * q + 3] = __fmul_rn(pv.w, __half2float(tv[(j + 4 * q + 3) * width]));
             }
+        };
+        uint32_t j = 0;
+        if (rows >= 16) {
+            float cur[16], nxt[16];
+            products(0, cur);
+            for (; j + 32 <= rows; j += 16) {
+                products(j + 16, nxt);
+#pragma unroll
+                for (int q = 0; q < 16; ++q) acc = __fadd_rn(acc, cur[q]);
+#pragma unroll
+                for (int q = 0; q < 16; ++q) cur[q] = nxt[q];
+            }
+#pragma unroll
+            for (int q = 0; q < 16; ++q) acc = __fadd_rn(acc, cur[q]);
+            j += 16;
         }
-        __syncthreads();  // everyone is done with tile t before its stage is refilled
+        for (; j < rows; ++j) acc = __fadd_rn(acc, __fmul_rn(pw[j], __half2float(tv[j * width])));
+        __syncwarp();  // every lane is done with tile t before its stage is refilled
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");  // only empty groups remain
     dec_stamp(trace, 0, 5);
-    if (tid < width) {
-        if constexpr (Io::kTagged) st_pair(reinterpret_cast<uint2*>(a.out) + size_t(h) * dim + slice * width + tid, acc, io.tag_out);
-        else a.out[size_t(h) * dim + slice * width + tid] = acc;
+    if (lane < width) {
+        if constexpr (Io::kTagged) st_pair(reinterpret_cast<uint2*>(a.out) + size_t(h) * dim + slice * width + lane, acc, io.tag_out);
+        else a.out[size_t(h) * dim + slice * width + lane] = acc;
     }
 }
 

@@ -45,6 +45,62 @@ struct FQ4_0 {
     }
 };
 
+// Spreads the low four bits of n into bit 4 of four bytes: the fifth bits of four 5-bit quants, ready to OR onto nibbles.
+__device__ __forceinline__ uint32_t fifth_bits(uint32_t n) { return (((n & 0xFu) * 0x00204081u) & 0x01010101u) << 4; }
+
+// weight = q * d + m (src/quant.cpp:484-498): the offset meets the activation block's sum, scaled by the activation scale first.
+struct FQ4_1 {
+    static constexpr int kLanesPerTerm = 1;
+    static constexpr bool kExact = true;
+    struct W { uint4 q; __half2 dm; };
+    using X = FQ4_0::X;
+    static __device__ __forceinline__ W loadw(const DevMatrix& m, uint32_t row, uint32_t u) {
+        const size_t i = size_t(row) * m.units + u;
+        return {ld_stream(m.qa + i * 16), reinterpret_cast<const __half2*>(m.d)[i]};
+    }
+    static __device__ __forceinline__ X loadx(const DevAct& a, uint32_t t, uint32_t u) { return FQ4_0::loadx(a, t, u); }
+    static __device__ __forceinline__ float term(const W& w, const X& x, bool valid, uint32_t) {
+        int acc = 0;
+        acc = dp4a(w.q.x & 0x0F0F0F0Fu, x.lo.x, acc);
+        acc = dp4a(w.q.y & 0x0F0F0F0Fu, x.lo.y, acc);
+        acc = dp4a(w.q.z & 0x0F0F0F0Fu, x.lo.z, acc);
+        acc = dp4a(w.q.w & 0x0F0F0F0Fu, x.lo.w, acc);
+        acc = dp4a((w.q.x >> 4) & 0x0F0F0F0Fu, x.hi.x, acc);
+        acc = dp4a((w.q.y >> 4) & 0x0F0F0F0Fu, x.hi.y, acc);
+        acc = dp4a((w.q.z >> 4) & 0x0F0F0F0Fu, x.hi.z, acc);
+        acc = dp4a((w.q.w >> 4) & 0x0F0F0F0Fu, x.hi.w, acc);
+        const float scaled = __fmul_rn(__fmul_rn(float(acc), __low2float(w.dm)), x.d);
+        const float offset = __fmul_rn(__high2float(w.dm), __fmul_rn(x.d, float(x.s)));
+        return valid ? __fadd_rn(scaled, offset) : 0.0f;
+    }
+};
+
+// weight = (q - 16) * d with 5-bit q (src/quant.cpp:458-472): bit i of qh is the fifth bit of value i.
+struct FQ5_0 {
+    static constexpr int kLanesPerTerm = 1;
+    static constexpr bool kExact = true;
+    struct W { uint4 q; uint32_t qh; __half d; };
+    using X = FQ4_0::X;
+    static __device__ __forceinline__ W loadw(const DevMatrix& m, uint32_t row, uint32_t u) {
+        const size_t i = size_t(row) * m.units + u;
+        return {ld_stream(m.qa + i * 16), reinterpret_cast<const uint32_t*>(m.qb)[i], m.d[i]};
+    }
+    static __device__ __forceinline__ X loadx(const DevAct& a, uint32_t t, uint32_t u) { return FQ4_0::loadx(a, t, u); }
+    static __device__ __forceinline__ float term(const W& w, const X& x, bool valid, uint32_t) {
+        int acc = 0;
+        acc = dp4a((w.q.x & 0x0F0F0F0Fu) | fifth_bits(w.qh), x.lo.x, acc);
+        acc = dp4a((w.q.y & 0x0F0F0F0Fu) | fifth_bits(w.qh >> 4), x.lo.y, acc);
+        acc = dp4a((w.q.z & 0x0F0F0F0Fu) | fifth_bits(w.qh >> 8), x.lo.z, acc);
+        acc = dp4a((w.q.w & 0x0F0F0F0Fu) | fifth_bits(w.qh >> 12), x.lo.w, acc);
+        acc = dp4a(((w.q.x >> 4) & 0x0F0F0F0Fu) | fifth_bits(w.qh >> 16), x.hi.x, acc);
+        acc = dp4a(((w.q.y >> 4) & 0x0F0F0F0Fu) | fifth_bits(w.qh >> 20), x.hi.y, acc);
+        acc = dp4a(((w.q.z >> 4) & 0x0F0F0F0Fu) | fifth_bits(w.qh >> 24), x.hi.z, acc);
+        acc = dp4a(((w.q.w >> 4) & 0x0F0F0F0Fu) | fifth_bits(w.qh >> 28), x.hi.w, acc);
+        acc -= 16 * x.s;  // sum((q-16)*x) = sum(q*x) - 16*sum(x)
+        return valid ? __fmul_rn(__fmul_rn(float(acc), __half2float(w.d)), x.d) : 0.0f;
+    }
+};
+
 struct FQ8_0 {
     static constexpr int kLanesPerTerm = 2;
     static constexpr bool kExact = true;
@@ -102,6 +158,43 @@ struct FQ4_K {
         int offsets = valid ? int(w.mn0) * x.bs0 + int(w.mn1) * x.bs1 : 0;
 #pragma unroll
         for (int o = 1; o < 8; o <<= 1) {  // the super-block's 8 units sit in 8 neighbouring lanes
+            weighted += __shfl_xor_sync(0xffffffffu, weighted, o);
+            offsets += __shfl_xor_sync(0xffffffffu, offsets, o);
+        }
+        if (!valid || (u & 7) != 0) return 0.0f;
+        return __fmul_rn(x.d, __fsub_rn(__fmul_rn(__low2float(w.dd), float(weighted)), __fmul_rn(__high2float(w.dd), float(offsets))));
+    }
+};
+
+// Q4_K's arithmetic with a fifth bit per weight (src/quant.cpp:523-547).
+struct FQ5_K {
+    static constexpr int kLanesPerTerm = 8;
+    static constexpr bool kExact = true;
+    struct W { uint4 q; uint32_t qh, sc0, sc1, mn0, mn1; __half2 dd; };
+    using X = FQ4_K::X;
+    static __device__ __forceinline__ W loadw(const DevMatrix& m, uint32_t row, uint32_t u) {
+        const size_t i = size_t(row) * m.units + u;
+        const size_t blk = size_t(row) * m.blocks + (u >> 3);
+        const uint32_t g = (u & 7) >> 1;
+        const uint8_t* s = m.sc + blk * 16;
+        const __half2 dd = reinterpret_cast<const __half2*>(m.d)[blk];
+        return {ld_stream(m.qa + i * 16), reinterpret_cast<const uint32_t*>(m.qb)[i], s[2 * g], s[2 * g + 1], s[8 + 2 * g], s[9 + 2 * g], dd};
+    }
+    static __device__ __forceinline__ X loadx(const DevAct& a, uint32_t t, uint32_t u) { return FQ4_K::loadx(a, t, u); }
+    static __device__ __forceinline__ float term(const W& w, const X& x, bool valid, uint32_t u) {
+        int lo = 0, hi = 0;
+        lo = dp4a((w.q.x & 0x0F0F0F0Fu) | fifth_bits(w.qh), x.lo.x, lo);
+        lo = dp4a((w.q.y & 0x0F0F0F0Fu) | fifth_bits(w.qh >> 4), x.lo.y, lo);
+        lo = dp4a((w.q.z & 0x0F0F0F0Fu) | fifth_bits(w.qh >> 8), x.lo.z, lo);
+        lo = dp4a((w.q.w & 0x0F0F0F0Fu) | fifth_bits(w.qh >> 12), x.lo.w, lo);
+        hi = dp4a(((w.q.x >> 4) & 0x0F0F0F0Fu) | fifth_bits(w.qh >> 16), x.hi.x, hi);
+        hi = dp4a(((w.q.y >> 4) & 0x0F0F0F0Fu) | fifth_bits(w.qh >> 20), x.hi.y, hi);
+        hi = dp4a(((w.q.z >> 4) & 0x0F0F0F0Fu) | fifth_bits(w.qh >> 24), x.hi.z, hi);
+        hi = dp4a(((w.q.w >> 4) & 0x0F0F0F0Fu) | fifth_bits(w.qh >> 28), x.hi.w, hi);
+        int weighted = valid ? int(w.sc0) * lo + int(w.sc1) * hi : 0;
+        int offsets = valid ? int(w.mn0) * x.bs0 + int(w.mn1) * x.bs1 : 0;
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) {
             weighted += __shfl_xor_sync(0xffffffffu, weighted, o);
             offsets += __shfl_xor_sync(0xffffffffu, offsets, o);
         }

@@ -67,14 +67,16 @@ int brisk_cuda_matmul(int32_t type, const void* w, uint64_t rows, uint64_t cols,
         validate(type, rows, cols);
         if (n == 0) return 0;
         const size_t raw_bytes = rows * (cols / bk::block_elems(type)) * bk::block_bytes(type);
-        Buf raw(raw_bytes), planes(bk::plane_sizes(type, uint32_t(rows), uint32_t(cols)).total()), xd(n * cols * 4), od(n * rows * 4);
+        const int dev_type = type == bk::T_BF16 ? int(bk::T_F32) : type;  // BF16 is widened on upload
+        Buf raw(raw_bytes), planes(bk::plane_sizes(dev_type, uint32_t(rows), uint32_t(cols)).total()), xd(n * cols * 4), od(n * rows * 4);
         ActBuffers ab(n, cols);
         bk::DevMatrix m;
-        bk::bind_planes(m, type, uint32_t(rows), uint32_t(cols), planes.as<uint8_t>());
+        bk::bind_planes(m, dev_type, uint32_t(rows), uint32_t(cols), planes.as<uint8_t>());
         BK_CUDA(cudaMemcpy(raw.p, w, raw_bytes, cudaMemcpyHostToDevice));
         BK_CUDA(cudaMemcpy(xd.p, x, n * cols * 4, cudaMemcpyHostToDevice));
-        bk::launch_repack(m, raw.as<uint8_t>(), nullptr);
-        const bool k = bk::takes_q8_k(type), f = type == bk::T_F16 || type == bk::T_F32;
+        if (type == bk::T_BF16) bk::launch_widen_bf16(m, raw.as<uint8_t>(), nullptr);
+        else bk::launch_repack(m, raw.as<uint8_t>(), nullptr);
+        const bool k = bk::takes_q8_k(type), f = type == bk::T_F16 || type == bk::T_F32 || type == bk::T_BF16;
         bk::DevActMut a = ab.act;
         if (!f) a.f32 = nullptr;
         bk::launch_norm_quant(xd.as<float>(), uint32_t(cols), nullptr, 0.0f, uint32_t(n), uint32_t(cols), a, !k && !f, k, nullptr);

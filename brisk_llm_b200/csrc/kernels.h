@@ -20,6 +20,9 @@ PlaneSizes plane_sizes(int type, uint32_t rows, uint32_t cols);
 void bind_planes(DevMatrix& m, int type, uint32_t rows, uint32_t cols, uint8_t* base);
 // raw_dev: the matrix in file layout, already in device memory. Writes the planes of `m`.
 void launch_repack(const DevMatrix& m, const uint8_t* raw_dev, cudaStream_t s);
+// raw_dev: rows x cols bfloat16 values; m: an F32 matrix of the same shape. The reference widens BF16 (and F16)
+// tensors to f32 when it loads them (src/model.cpp:439-449).
+void launch_widen_bf16(const DevMatrix& m, const uint8_t* raw_dev, cudaStream_t s);
 
 // ---- activations (activations.cu) -------------------------------------------------------------
 struct DevActMut {
@@ -149,7 +152,7 @@ public:
     StepPlan& operator=(const StepPlan&) = delete;
     bool build(const std::vector<StepLayerArgs>& layers, const StepShared& shared, uint32_t sms, cudaStream_t s, std::string& why_not);
     bool ready() const { return impl_ != nullptr; }
-    void launch(cudaStream_t s) const;
+    void launch(cudaStream_t s);
     const unsigned int* error_word() const;
     // Development aid: 4 words per phase (6 per layer) written by CTA 0 - entry, barrier passed, finished (ns), polls.
     void set_trace(unsigned long long* words);

@@ -208,7 +208,10 @@ void launch_matvec(const MatTarget* targets, int count, const DevAct& act, uint3
     if (pair && targets[0].m.rows != targets[1].m.rows) throw CudaError("cuda: gate and up must have the same rows");
     switch (targets[0].m.type) {
         case T_Q4_0: dispatch<FQ4_0>(p, pair, n, s); break;
+        case T_Q4_1: dispatch<FQ4_1>(p, pair, n, s); break;
+        case T_Q5_0: dispatch<FQ5_0>(p, pair, n, s); break;
         case T_Q8_0: dispatch<FQ8_0>(p, pair, n, s); break;
+        case T_Q5_K: dispatch<FQ5_K>(p, pair, n, s); break;
         case T_Q4_K: dispatch<FQ4_K>(p, pair, n, s); break;
         case T_Q6_K: dispatch<FQ6_K>(p, pair, n, s); break;
         case T_TQ2_0: dispatch<FTQ2_0>(p, pair, n, s); break;

@@ -53,6 +53,25 @@ __global__ void embed_kernel(const DevMatrix m, const int32_t* tokens, float* __
                 }
                 break;
             }
+            case T_Q4_1: {  // dequantize_q4_1, src/quant.cpp:207-217
+                const float d = __half2float(m.d[2 * i]), mm = __half2float(m.d[2 * i + 1]);
+                for (int k = 0; k < 16; ++k) {
+                    out[u * 32 + k] = __fadd_rn(__fmul_rn(float(qa[k] & 0xF), d), mm);
+                    out[u * 32 + 16 + k] = __fadd_rn(__fmul_rn(float(qa[k] >> 4), d), mm);
+                }
+                break;
+            }
+            case T_Q5_0: {  // dequantize_q5_0, src/quant.cpp:219-232
+                const float d = __half2float(m.d[i]);
+                const uint32_t qh = reinterpret_cast<const uint32_t*>(m.qb)[i];
+                for (int k = 0; k < 16; ++k) {
+                    const int lo = int(qa[k] & 0xF) | int(((qh >> k) & 1) << 4);
+                    const int hi = int(qa[k] >> 4) | int(((qh >> (k + 16)) & 1) << 4);
+                    out[u * 32 + k] = __fmul_rn(float(lo - 16), d);
+                    out[u * 32 + 16 + k] = __fmul_rn(float(hi - 16), d);
+                }
+                break;
+            }
             case T_Q8_0: {
                 const float d = __half2float(m.d[size_t(row) * m.blocks + (u >> 1)]);
                 for (int k = 0; k < 16; ++k) out[u * 16 + k] = __fmul_rn(float(reinterpret_cast<const int8_t*>(qa)[k]), d);
@@ -69,6 +88,21 @@ __global__ void embed_kernel(const DevMatrix m, const int32_t* tokens, float* __
                 for (int k = 0; k < 16; ++k) {
                     y[k] = __fsub_rn(__fmul_rn(d1, float(qa[k] & 0xF)), m1);
                     y[32 + k] = __fsub_rn(__fmul_rn(d2, float(qa[k] >> 4)), m2);
+                }
+                break;
+            }
+            case T_Q5_K: {  // dequantize_q5_k, src/quant.cpp:263-283
+                const uint32_t sb = u >> 3, j = u & 7, g = j >> 1, hf = j & 1;
+                const size_t blk = size_t(row) * m.blocks + sb;
+                const uint8_t* s = m.sc + blk * 16;
+                const uint32_t qh = reinterpret_cast<const uint32_t*>(m.qb)[i];
+                const float d = __half2float(m.d[2 * blk]), dmin = __half2float(m.d[2 * blk + 1]);
+                const float d1 = __fmul_rn(d, float(s[2 * g])), m1 = __fmul_rn(dmin, float(s[8 + 2 * g]));
+                const float d2 = __fmul_rn(d, float(s[2 * g + 1])), m2 = __fmul_rn(dmin, float(s[9 + 2 * g]));
+                float* y = out + sb * 256 + g * 64 + hf * 16;
+                for (int k = 0; k < 16; ++k) {
+                    y[k] = __fsub_rn(__fmul_rn(d1, float(int(qa[k] & 0xF) | int(((qh >> k) & 1) << 4))), m1);
+                    y[32 + k] = __fsub_rn(__fmul_rn(d2, float(int(qa[k] >> 4) | int(((qh >> (16 + k)) & 1) << 4))), m2);
                 }
                 break;
             }

@@ -17,7 +17,10 @@ PlaneSizes plane_sizes(int type, uint32_t rows, uint32_t cols) {
         case T_F32: p.qa = r * cols * 4; break;
         case T_F16: p.qa = r * cols * 2; break;
         case T_Q4_0: p.qa = r * (cols / 32) * 16; p.d = r * (cols / 32) * 2; break;
+        case T_Q4_1: p.qa = r * (cols / 32) * 16; p.d = r * (cols / 32) * 4; break;
+        case T_Q5_0: p.qa = r * (cols / 32) * 16; p.qb = r * (cols / 32) * 4; p.d = r * (cols / 32) * 2; break;
         case T_Q8_0: p.qa = r * (cols / 32) * 32; p.d = r * (cols / 32) * 2; break;
+        case T_Q5_K: p.qa = r * (cols / 256) * 128; p.qb = r * (cols / 256) * 32; p.sc = r * (cols / 256) * 16; p.d = r * (cols / 256) * 4; break;
         case T_Q4_K: p.qa = r * (cols / 256) * 128; p.sc = r * (cols / 256) * 16; p.d = r * (cols / 256) * 4; break;
         case T_Q6_K:
             p.qa = p.qb = p.qc = r * (cols / 256) * 64;
@@ -38,9 +41,9 @@ void bind_planes(DevMatrix& m, int type, uint32_t rows, uint32_t cols, uint8_t* 
     m.cols = cols;
     m.bytes = p.total();
     switch (type) {
-        case T_Q4_0: m.units = cols / 32; m.blocks = cols / 32; break;
+        case T_Q4_0: case T_Q4_1: case T_Q5_0: m.units = cols / 32; m.blocks = cols / 32; break;
         case T_Q8_0: m.units = cols / 16; m.blocks = cols / 32; break;
-        case T_Q4_K: m.units = cols / 32; m.blocks = cols / 256; break;
+        case T_Q4_K: case T_Q5_K: m.units = cols / 32; m.blocks = cols / 256; break;
         case T_Q6_K: m.units = cols / 64; m.blocks = cols / 256; break;
         case T_TQ2_0: m.units = cols / 64; m.blocks = cols / 256; break;
         case T_F16: m.units = cols / 8; m.blocks = 0; break;
@@ -79,6 +82,20 @@ __global__ void repack_kernel(int type, size_t total_units, const uint8_t* __res
             copy16(qa + i * 16, b + 2);
             break;
         }
+        case T_Q4_1: {
+            const uint8_t* b = raw + i * 20;
+            d[2 * i] = load_u16(b);
+            d[2 * i + 1] = load_u16(b + 2);
+            copy16(qa + i * 16, b + 4);
+            break;
+        }
+        case T_Q5_0: {
+            const uint8_t* b = raw + i * 22;
+            d[i] = load_u16(b);
+            reinterpret_cast<uint32_t*>(qb)[i] = uint32_t(b[2]) | (uint32_t(b[3]) << 8) | (uint32_t(b[4]) << 16) | (uint32_t(b[5]) << 24);
+            copy16(qa + i * 16, b + 6);
+            break;
+        }
         case T_Q8_0: {
             const size_t blk = i >> 1, half = i & 1;
             const uint8_t* b = raw + blk * 34;
@@ -94,6 +111,31 @@ __global__ void repack_kernel(int type, size_t total_units, const uint8_t* __res
                 d[2 * blk] = load_u16(b);
                 d[2 * blk + 1] = load_u16(b + 2);
                 const uint8_t* s = b + 4;  // 12 bytes of packed 6-bit scales and mins (src/quant.h:256-264)
+                uint8_t* o = sc + blk * 16;
+                for (int k = 0; k < 4; ++k) {
+                    o[k] = s[k] & 63;
+                    o[8 + k] = s[k + 4] & 63;
+                    o[4 + k] = uint8_t((s[k + 8] & 0xF) | ((s[k] >> 6) << 4));
+                    o[12 + k] = uint8_t((s[k + 8] >> 4) | ((s[k + 4] >> 6) << 4));
+                }
+            }
+            break;
+        }
+        case T_Q5_K: {
+            const size_t blk = i >> 3, j = i & 7, g = j >> 1, hf = j & 1;
+            const uint8_t* b = raw + blk * 176;
+            copy16(qa + i * 16, b + 48 + j * 16);
+            const uint8_t* qh = b + 16 + hf * 16;  // bit sb of qh[e] is the fifth bit of value e of sub-block sb (src/quant.h:101-110)
+            uint32_t bits = 0;
+            for (int k = 0; k < 16; ++k) {
+                bits |= uint32_t((qh[k] >> (2 * g)) & 1) << k;
+                bits |= uint32_t((qh[k] >> (2 * g + 1)) & 1) << (16 + k);
+            }
+            reinterpret_cast<uint32_t*>(qb)[i] = bits;
+            if (j == 0) {
+                d[2 * blk] = load_u16(b);
+                d[2 * blk + 1] = load_u16(b + 2);
+                const uint8_t* s = b + 4;
                 uint8_t* o = sc + blk * 16;
                 for (int k = 0; k < 4; ++k) {
                     o[k] = s[k] & 63;
@@ -127,7 +169,19 @@ __global__ void repack_kernel(int type, size_t total_units, const uint8_t* __res
     }
 }
 
+__global__ void widen_bf16_kernel(size_t count, const uint16_t* __restrict__ raw, float* out) {
+    const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < count) out[i] = __uint_as_float(uint32_t(raw[i]) << 16);  // bfloat_to_float, src/model.cpp:20-25
+}
+
 }  // namespace
+
+void launch_widen_bf16(const DevMatrix& m, const uint8_t* raw_dev, cudaStream_t s) {
+    const size_t count = size_t(m.rows) * m.cols;
+    widen_bf16_kernel<<<unsigned((count + 255) / 256), 256, 0, s>>>(count, reinterpret_cast<const uint16_t*>(raw_dev),
+                                                                    reinterpret_cast<float*>(const_cast<uint8_t*>(m.qa)));
+    BK_CUDA(cudaGetLastError());
+}
 
 void launch_repack(const DevMatrix& m, const uint8_t* raw_dev, cudaStream_t s) {
     if (m.type == T_F32 || m.type == T_F16) {

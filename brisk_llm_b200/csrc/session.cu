@@ -101,7 +101,7 @@ brisk_cuda_memory estimate(const brisk_cuda_model& m, const brisk_cuda_options& 
     const uint64_t hidden = m.hidden, ffn = m.ffn, vocab = m.vocab_size, dim = m.head_dim;
     const uint64_t q_dim = uint64_t(m.head_count) * dim, kv_dim = uint64_t(m.kv_head_count) * dim;
     const uint64_t ctx = opt.max_context == 0 ? m.context_length : std::min<uint64_t>(opt.max_context, m.context_length);
-    auto planes = [](int type, uint64_t rows, uint64_t cols) { return uint64_t(plane_sizes(type, uint32_t(rows), uint32_t(cols)).total()); };
+    auto planes = [](int type, uint64_t rows, uint64_t cols) { return uint64_t(plane_sizes(type == T_BF16 ? int(T_F32) : type, uint32_t(rows), uint32_t(cols)).total()); };
     e.weights += planes(m.token_embd.type, vocab, hidden);
     if (m.output.data != nullptr || tp > 1) e.weights += planes(m.output.data != nullptr ? m.output.type : m.token_embd.type, vocab / tp, hidden);
     e.weights += hidden * 4;
@@ -123,7 +123,10 @@ brisk_cuda_memory estimate(const brisk_cuda_model& m, const brisk_cuda_options& 
     return e;
 }
 
-bool type_supported(int t) { return t == T_F32 || t == T_F16 || t == T_Q4_0 || t == T_Q8_0 || t == T_Q4_K || t == T_Q6_K || t == T_TQ2_0; }
+bool type_supported(int t) {
+    return t == T_F32 || t == T_F16 || t == T_BF16 || t == T_Q4_0 || t == T_Q4_1 || t == T_Q5_0 || t == T_Q8_0 || t == T_Q4_K || t == T_Q5_K || t == T_Q6_K ||
+           t == T_TQ2_0;
+}
 
 }  // namespace
 
@@ -250,10 +253,11 @@ struct Session {
         const uint64_t row_bytes = (cols / be) * block_bytes(m.type);
         if (m.bytes != full_rows * row_bytes) throw CudaError(std::string("cuda: tensor ") + what + " has unexpected quantised data");
         const uint64_t expect = rows * row_bytes;
+        const int dev_type = m.type == T_BF16 ? int(T_F32) : m.type;  // BF16 is widened on upload, like the reference's load (src/model.cpp:439-449)
         auto buf = std::make_unique<DevBuffer>();
-        buf->alloc(plane_sizes(m.type, uint32_t(rows), uint32_t(cols)).total());
+        buf->alloc(plane_sizes(dev_type, uint32_t(rows), uint32_t(cols)).total());
         DevMatrix d;
-        bind_planes(d, m.type, uint32_t(rows), uint32_t(cols), buf->as<uint8_t>());
+        bind_planes(d, dev_type, uint32_t(rows), uint32_t(cols), buf->as<uint8_t>());
         if (staging.bytes < expect) {
             BK_CUDA(cudaStreamSynchronize(stream));
             if (staging.p) cudaFree(staging.p);
@@ -262,7 +266,8 @@ struct Session {
         }
         BK_CUDA(cudaStreamSynchronize(stream));  // the previous repack still reads the staging buffer
         BK_CUDA(cudaMemcpyAsync(staging.p, static_cast<const uint8_t*>(m.data) + row0 * row_bytes, expect, cudaMemcpyHostToDevice, stream));
-        launch_repack(d, staging.as<uint8_t>(), stream);
+        if (m.type == T_BF16) launch_widen_bf16(d, staging.as<uint8_t>(), stream);
+        else launch_repack(d, staging.as<uint8_t>(), stream);
         weight_bytes += expect;
         stats.h2d_bytes += expect;
         weight_buffers.push_back(std::move(buf));

@@ -24,6 +24,7 @@
 #include <cstdio>
 #include <cstring>
 #include <initializer_list>
+#include <memory>
 #include <utility>
 
 #include "decode_body.cuh"
@@ -48,7 +49,50 @@ struct StepParams {
     unsigned int* sync;   // [0] arrivals, [1] exits, [2] error
     uint32_t tile_offset; // bytes from the start of dynamic shared memory to the transpose tile (after the widest activation row)
     unsigned long long* trace;  // optional (BRISK_CUDA_STEP_TRACE): per phase, CTA 0's time of entry, of passing the barrier, of finishing, and its polls
+    // tagged exchange (see TaggedIo): the tags of this launch start above tag_base; the residual stream comes in and
+    // goes out as ordinary floats in plain_hidden and lives in between as tagged pairs in tagged_hidden
+    uint32_t tag_base;
+    float* plain_hidden;
+    uint2* tagged_hidden;
+    uint32_t hidden_size;
 };
+
+struct NoGate {  // tagged exchange: nothing to wait for, the data itself says when it is there
+    __device__ __forceinline__ void wait() {}
+    __device__ __forceinline__ void prologue_done() {}
+};
+
+// `count` tagged values (a multiple of 2) from src into shared memory at dst, by one warp; bounded re-reads.
+__device__ __forceinline__ void warp_fetch_tagged(const uint2* src, float* dst, uint32_t count, uint32_t tag, unsigned int* error) {
+    const uint32_t lane = threadIdx.x & 31;
+    const uint4* src2 = reinterpret_cast<const uint4*>(src);
+    for (uint32_t base = 0; base < count / 2; base += 32 * 4) {
+        uint4 v[4];
+        for (uint32_t spin = 0;; ++spin) {
+            bool complete = true;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const uint32_t i = base + lane + 32 * k;
+                v[k] = i < count / 2 ? ld_pairs2(src2 + i) : make_uint4(0u, tag, 0u, tag);
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) complete = complete && v[k].y == tag && v[k].w == tag;
+            if (complete) break;
+            if (spin == kPollLimit) {
+                poll_failed(error);
+                break;
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t i = base + lane + 32 * k;
+            if (i < count / 2) {
+                dst[2 * i] = __uint_as_float(v[k].x);
+                dst[2 * i + 1] = __uint_as_float(v[k].z);
+            }
+        }
+    }
+}
 
 __device__ __forceinline__ unsigned long long now_ns() {
     unsigned long long t;
@@ -129,9 +173,9 @@ struct GridGate {
     }
 };
 
-// Scores of the new token against every visible position, as WARP tasks of (K/V head, 32 positions) dealt round-robin
-// over the CTAs (a 600-position context of 8 K/V heads gives 152 tasks: one warp on every SM), so that the K rows come
-// in over every SM's memory pipe at once. A warp needs no CTA barrier: it copies its 32 K rows into its own slice of
+// Scores of the new token against every visible position, as WARP tasks of (query head, 32 positions) dealt round-robin
+// over the CTAs (a 600-position context of 16 heads gives 304 tasks: two or three warps on every SM), so that the K
+// rows come in over every SM's memory pipe at once (the heads of a group read the same rows; the second read hits L2). A warp needs no CTA barrier: it copies its 32 K rows into its own slice of
 // shared memory with cp.async (requested BEFORE the grid barrier; rows padded by 16 bytes so that the 16-byte reads of
 // a quarter warp fall into distinct banks), norms and rotates the group's query heads into the same slice, and each
 // lane then owns one position. The task that covers the token's own position also norms, rotates and stores the new
@@ -141,22 +185,27 @@ __host__ __device__ inline size_t step_scores_warp_smem(uint32_t group, uint32_t
     return size_t(group + 1) * dim * sizeof(float) + size_t(32) * (dim * 2 + 16);
 }
 
-template <int VPL, bool NEOX>
-__device__ __forceinline__ void step_scores(const DecAttnParams& a, const uint32_t cta, const uint32_t nctas, unsigned char* sm, GridGate& gate) {
+struct ScoreTags {
+    uint32_t in, out;  // tag of q/k/v, tag of the scores
+    unsigned int* error;
+};
+
+template <int VPL, bool NEOX, bool TAGGED, class Gate>
+__device__ __forceinline__ void step_scores(const DecAttnParams& a, const uint32_t cta, const uint32_t nctas, unsigned char* sm, Gate& gate, const ScoreTags& tags) {
     constexpr uint32_t dim = VPL * 32;
     const uint32_t group = a.heads / a.kv_heads;
     const uint32_t pos = *a.position, visible = pos + 1;
     const uint32_t chunks = (visible + 31) / 32;
-    const uint32_t tasks = a.kv_heads * chunks;
+    const uint32_t tasks = a.heads * chunks;  // (query head, 32 positions)
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     unsigned char* mine = sm + size_t(warp) * step_scores_warp_smem(group, dim);
     float* qs = reinterpret_cast<float*>(mine);
-    float* knew = qs + group * dim;
+    float* knew = qs + dim;
     const uint4* krow = reinterpret_cast<const uint4*>(mine + size_t(group + 1) * dim * sizeof(float) + size_t(lane) * (dim * 2 + 16));
     const float* rope = a.rope + size_t(pos) * dim;
 
     auto request_row = [&](uint32_t task) {  // this lane's cached K row of the task, if it has one
-        const uint32_t kvh = task / chunks, p = (task % chunks) * 32 + lane;
+        const uint32_t kvh = (task / chunks) / group, p = (task % chunks) * 32 + lane;
         if (p < visible && p != pos) {
             const __half* kr = a.k_cache + (size_t(kvh) * a.max_context + p) * dim;
             const uint32_t dst = uint32_t(__cvta_generic_to_shared(krow));
@@ -169,29 +218,42 @@ __device__ __forceinline__ void step_scores(const DecAttnParams& a, const uint32
     };
     const uint32_t first = cta + warp * nctas, stride = nctas * kDecWarps;
     dec_stamp(a.trace, cta, 0);
-    if (first < tasks) request_row(first);
+    if (first < tasks) {
+        request_row(first);
+        // The RoPE row of this position and the per-head norm weights do not depend on the projections either: pull
+        // their cache lines in now, so that the loads behind the poll hit L1.
+        if (lane * 32 < dim) {
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(rope + lane * 32));
+            if (a.q_norm != nullptr) asm volatile("prefetch.global.L1 [%0];" ::"l"(a.q_norm + lane * 32));
+            if (a.k_norm != nullptr) asm volatile("prefetch.global.L1 [%0];" ::"l"(a.k_norm + lane * 32));
+        }
+    }
     gate.wait();
     dec_stamp(a.trace, cta, 1);
     for (uint32_t task = first; task < tasks; task += stride) {
         if (task != first) request_row(task);
-        const uint32_t kvh = task / chunks, begin = (task % chunks) * 32;
+        const uint32_t head = task / chunks, kvh = head / group, begin = (task % chunks) * 32;
         const uint32_t p = begin + lane;
         const bool cached = p < visible && p != pos;
-        // the group's raw query heads (contiguous in q) and, for the task that owns the token's position, the raw new
-        // K row: into the slice through L2, then norm + RoPE in place (a lane rewrites exactly the elements it read)
-        {
-            const float* qsrc = a.q + size_t(kvh) * group * dim;
+        // The raw query head and, for the tasks that cover the token's own position, the raw new K row: into the slice
+        // through L2, then norm + RoPE in place (a lane rewrites exactly the elements it read). Every head of the group
+        // prepares the new K row for its own score; the group's first head also stores it (and V) to the cache.
+        const bool owner = pos >= begin && pos < begin + 32;
+        if constexpr (TAGGED) {
+            warp_fetch_tagged(reinterpret_cast<const uint2*>(a.q) + size_t(head) * dim, qs, dim, tags.in, tags.error);
+            if (owner) warp_fetch_tagged(reinterpret_cast<const uint2*>(a.k) + size_t(kvh) * dim, knew, dim, tags.in, tags.error);
+        } else {
+            const float* qsrc = a.q + size_t(head) * dim;
             const uint32_t qdst = uint32_t(__cvta_generic_to_shared(qs));
-            for (uint32_t i = lane; i < group * dim / 4; i += 32) {
+            for (uint32_t i = lane; i < dim / 4; i += 32) {
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(qdst + i * 16), "l"(qsrc + i * 4) : "memory");
             }
-        }
-        const bool owner = pos >= begin && pos < begin + 32;
-        if (owner) {
-            const float* ksrc = a.k + size_t(kvh) * dim;
-            const uint32_t kdst = uint32_t(__cvta_generic_to_shared(knew));
-            for (uint32_t i = lane; i < dim / 4; i += 32) {
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kdst + i * 16), "l"(ksrc + i * 4) : "memory");
+            if (owner) {
+                const float* ksrc = a.k + size_t(kvh) * dim;
+                const uint32_t kdst = uint32_t(__cvta_generic_to_shared(knew));
+                for (uint32_t i = lane; i < dim / 4; i += 32) {
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kdst + i * 16), "l"(ksrc + i * 4) : "memory");
+                }
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
@@ -204,52 +266,64 @@ __device__ __forceinline__ void step_scores(const DecAttnParams& a, const uint32
             for (int k = 0; k < VPL; ++k) kv[k] = knew[NEOX ? lane + 32 * k : VPL * lane + k];
             warp_head_norm_rope<VPL, NEOX>(kv, a.k_norm, rope, a.eps, knew);
             __syncwarp();
-            warp_store_new_kv(a, kvh, pos, knew);
+            const bool stores = head % group == 0;
+            const size_t row = (size_t(kvh) * a.max_context + pos) * dim;
+            for (uint32_t i = lane; i < dim; i += 32) {  // as warp_store_new_kv
+                const __half kh = __float2half_rn(knew[i]);
+                knew[i] = __half2float(kh);  // the score of the own position uses the cache's f16 value
+                if (stores) {
+                    a.k_cache[row + i] = kh;
+                    float v;
+                    if constexpr (TAGGED) v = poll_pair(reinterpret_cast<const uint2*>(a.v) + size_t(kvh) * dim + i, tags.in, tags.error);
+                    else v = __ldcg(a.v + size_t(kvh) * dim + i);
+                    a.v_cache[row + i] = __float2half_rn(v);
+                }
+            }
         }
-        for (uint32_t g = 0; g < group; ++g) {
+        {
             float v[VPL];
 #pragma unroll
-            for (int k = 0; k < VPL; ++k) v[k] = qs[g * dim + (NEOX ? lane + 32 * k : VPL * lane + k)];
-            warp_head_norm_rope<VPL, NEOX>(v, a.q_norm, rope, a.eps, qs + g * dim);
+            for (int k = 0; k < VPL; ++k) v[k] = qs[NEOX ? lane + 32 * k : VPL * lane + k];
+            warp_head_norm_rope<VPL, NEOX>(v, a.q_norm, rope, a.eps, qs);
         }
         __syncwarp();
         dec_stamp(a.trace, cta, 3);
         if (p < visible) {
-            for (uint32_t g = 0; g < group; ++g) {
-                float lanes[16];
+            float lanes[16];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) lanes[j] = 0.0f;
+            for (int j = 0; j < 16; ++j) lanes[j] = 0.0f;
 #pragma unroll
-                for (uint32_t i = 0; i < dim; i += 16) {
-                    float kf[16];
-                    if (!cached) {
+            for (uint32_t i = 0; i < dim; i += 16) {
+                float kf[16];
+                if (!cached) {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) kf[j] = knew[i + j];
-                    } else {
-                        const uint4 r0 = krow[i / 8], r1 = krow[i / 8 + 1];
-                        const __half2* h0 = reinterpret_cast<const __half2*>(&r0);
-                        const __half2* h1 = reinterpret_cast<const __half2*>(&r1);
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const float2 f0 = __half22float2(h0[j]), f1 = __half22float2(h1[j]);
-                            kf[2 * j] = f0.x; kf[2 * j + 1] = f0.y; kf[8 + 2 * j] = f1.x; kf[8 + 2 * j + 1] = f1.y;
-                        }
-                    }
-                    const float4* q4 = reinterpret_cast<const float4*>(qs + g * dim + i);
+                    for (int j = 0; j < 16; ++j) kf[j] = knew[i + j];
+                } else {
+                    const uint4 r0 = krow[i / 8], r1 = krow[i / 8 + 1];
+                    const __half2* h0 = reinterpret_cast<const __half2*>(&r0);
+                    const __half2* h1 = reinterpret_cast<const __half2*>(&r1);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const float4 q = q4[j];
-                        lanes[4 * j + 0] = __fadd_rn(lanes[4 * j + 0], __fmul_rn(q.x, kf[4 * j + 0]));
-                        lanes[4 * j + 1] = __fadd_rn(lanes[4 * j + 1], __fmul_rn(q.y, kf[4 * j + 1]));
-                        lanes[4 * j + 2] = __fadd_rn(lanes[4 * j + 2], __fmul_rn(q.z, kf[4 * j + 2]));
-                        lanes[4 * j + 3] = __fadd_rn(lanes[4 * j + 3], __fmul_rn(q.w, kf[4 * j + 3]));
+                        const float2 f0 = __half22float2(h0[j]), f1 = __half22float2(h1[j]);
+                        kf[2 * j] = f0.x; kf[2 * j + 1] = f0.y; kf[8 + 2 * j] = f1.x; kf[8 + 2 * j + 1] = f1.y;
                     }
                 }
-                float sum = 0.0f;
+                const float4* q4 = reinterpret_cast<const float4*>(qs + i);
 #pragma unroll
-                for (int j = 0; j < 16; ++j) sum = __fadd_rn(sum, lanes[j]);
-                a.scores[size_t(kvh * group + g) * a.max_context + p] = __fmul_rn(sum, a.scale);
+                for (int j = 0; j < 4; ++j) {
+                    const float4 q = q4[j];
+                    lanes[4 * j + 0] = __fadd_rn(lanes[4 * j + 0], __fmul_rn(q.x, kf[4 * j + 0]));
+                    lanes[4 * j + 1] = __fadd_rn(lanes[4 * j + 1], __fmul_rn(q.y, kf[4 * j + 1]));
+                    lanes[4 * j + 2] = __fadd_rn(lanes[4 * j + 2], __fmul_rn(q.z, kf[4 * j + 2]));
+                    lanes[4 * j + 3] = __fadd_rn(lanes[4 * j + 3], __fmul_rn(q.w, kf[4 * j + 3]));
+                }
             }
+            float sum = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) sum = __fadd_rn(sum, lanes[j]);
+            const size_t at = size_t(head) * a.max_context + p;
+            if constexpr (TAGGED) st_pair(reinterpret_cast<uint2*>(a.scores) + at, __fmul_rn(sum, a.scale), tags.out);
+            else a.scores[at] = __fmul_rn(sum, a.scale);
         }
         __syncwarp();  // the slice is rewritten by the warp's next task
         dec_stamp(a.trace, cta, 4);
@@ -258,7 +332,7 @@ __device__ __forceinline__ void step_scores(const DecAttnParams& a, const uint32
 
 constexpr int ring_depth(int regs_per_iter, bool deep) { return !deep ? 1 : regs_per_iter * 4 <= 48 ? 4 : regs_per_iter * 2 <= 48 ? 2 : 1; }
 
-template <class F, int RWA, int RWO, int RWG, int RWD, bool DEEP>
+template <class F, int RWA, int RWO, int RWG, int RWD, bool DEEP, bool TAGGED>
 __global__ void __launch_bounds__(kStepThreads, 1) step_kernel(const StepParams P) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ double red[32];
@@ -283,61 +357,133 @@ __global__ void __launch_bounds__(kStepThreads, 1) step_kernel(const StepParams 
     fetch_desc(0);
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
-    __shared__ int open_flag;
-    GridGate gate{P.sync, 0u, nctas, true, cta == 0 ? P.trace : nullptr, &open_flag};  // the first phase reads what earlier kernels wrote: no barrier
-    if (gate.trace != nullptr && threadIdx.x == 0) gate.trace[0] = now_ns();
-
-    for (uint32_t l = 0; l < P.n_layers; ++l) {
-        const StepLayerDesc& L = desc[l & 1];
-        if (l + 1 < P.n_layers) fetch_desc(l + 1);  // the other buffer's layer finished behind the barrier of its last arrive
-        gate.enter();
-        dec_multiply_body<F, RWA, false, ring_depth(RWA * kWordsPerUnit, DEEP)>(L.qkv, cta, nctas, smem, tile, red, gate);
-        gate.arrive();
-
-        gate.enter();
-        if (L.attn.dim == 128) {
-            if (L.attn.neox) step_scores<4, true>(L.attn, cta, nctas, smem, gate);
-            else step_scores<4, false>(L.attn, cta, nctas, smem, gate);
-        } else {
-            if (L.attn.neox) step_scores<2, true>(L.attn, cta, nctas, smem, gate);
-            else step_scores<2, false>(L.attn, cta, nctas, smem, gate);
-        }
-        gate.arrive();
-
-        gate.enter();
-        {
-            const uint32_t slices = L.attn.dim / L.attn.slice_width;
-            for (uint32_t task = cta; task < L.attn.heads * slices; task += nctas) {
-                dec_attn_out_body<kStepThreads>(L.attn, task / slices, task % slices, smem, redf, red, gate);
-                __syncthreads();  // the shared-memory row of probabilities is rewritten for the CTA's next task
+    if constexpr (TAGGED) {
+        // ---- tagged exchange: no barriers, every operation polls its own inputs --------------------------------
+        unsigned int* error = P.sync + 2;
+        unsigned long long* trace = cta == 0 ? P.trace : nullptr;
+        auto enter = [&] {
+            if (trace != nullptr && threadIdx.x == 0) trace[0] = trace[1] = now_ns();
+        };
+        auto leave = [&] {
+            __syncthreads();  // shared memory (activation row, tiles, descriptor buffers) changes hands between operations
+            if (trace != nullptr && threadIdx.x == 0) {
+                trace[2] = now_ns();
+                trace += 4;
             }
+        };
+        NoGate gate;
+        const uint32_t tag_in = P.tag_base + 1;
+        if (cta == 0) {  // the token's embedding row arrives as ordinary floats: hand it to every CTA as tagged pairs
+            for (uint32_t i = threadIdx.x; i < P.hidden_size; i += kStepThreads) st_pair(P.tagged_hidden + i, __ldcg(P.plain_hidden + i), tag_in);
         }
-        gate.arrive();
+        for (uint32_t l = 0; l < P.n_layers; ++l) {
+            const StepLayerDesc& L = desc[l & 1];
+            if (l + 1 < P.n_layers) fetch_desc(l + 1);
+            const uint32_t t0 = P.tag_base + 2 + l * 6;  // tags of this layer's six operations: t0 .. t0 + 5
+            const uint32_t tag_residual = l == 0 ? tag_in : t0 - 1;  // the previous layer's down projection
+            const bool last = l + 1 == P.n_layers;
 
-        gate.enter();
-        dec_multiply_body<F, RWO, false, ring_depth(RWO * kWordsPerUnit, DEEP)>(L.o, cta, nctas, smem, tile, red, gate);
-        gate.arrive();
+            enter();
+            dec_multiply_body<F, RWA, false, ring_depth(RWA * kWordsPerUnit, DEEP)>(L.qkv, cta, nctas, smem, tile, red, gate,
+                                                                                    TaggedIo{tag_residual, 0u, t0, error, nullptr});
+            leave();
 
-        gate.enter();
-        dec_multiply_body<F, RWG, true, ring_depth(2 * RWG * kWordsPerUnit, DEEP)>(L.gate_up, cta, nctas, smem, tile, red, gate);
-        gate.arrive();
+            enter();
+            {
+                const ScoreTags tags{t0, t0 + 1, error};
+                if (L.attn.dim == 128) {
+                    if (L.attn.neox) step_scores<4, true, true>(L.attn, cta, nctas, smem, gate, tags);
+                    else step_scores<4, false, true>(L.attn, cta, nctas, smem, gate, tags);
+                } else {
+                    if (L.attn.neox) step_scores<2, true, true>(L.attn, cta, nctas, smem, gate, tags);
+                    else step_scores<2, false, true>(L.attn, cta, nctas, smem, gate, tags);
+                }
+            }
+            leave();
 
-        gate.enter();
-        dec_multiply_body<F, RWD, false, ring_depth(RWD * kWordsPerUnit, DEEP)>(L.down, cta, nctas, smem, tile, red, gate);
-        asm volatile("cp.async.wait_group 0;" ::: "memory");  // the next layer's descriptor (long since landed); arrive's barrier publishes it
-        if (l + 1 < P.n_layers) gate.arrive();
-    }
-    if (gate.trace != nullptr && threadIdx.x == 0) gate.trace[2] = now_ns();
+            enter();
+            {
+                const uint32_t slices = L.attn.dim / L.attn.slice_width;
+                for (uint32_t task = cta; task < L.attn.heads * slices; task += nctas) {
+                    dec_attn_out_body<kStepThreads>(L.attn, task / slices, task % slices, smem, redf, red, gate, TaggedAttnIo{t0 + 1, t0, t0 + 2, error});
+                    __syncthreads();
+                }
+            }
+            leave();
 
-    // Leave: the last CTA out re-arms the counters for the next launch (every CTA is past all of its waits by then).
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence();
-        const unsigned int before = atomicAdd(P.sync + 1, 1u);
-        if (before + 1 == nctas) {
-            P.sync[0] = 0;
-            P.sync[1] = 0;
+            enter();
+            dec_multiply_body<F, RWO, false, ring_depth(RWO * kWordsPerUnit, DEEP)>(L.o, cta, nctas, smem, tile, red, gate,
+                                                                                    TaggedIo{t0 + 2, tag_residual, t0 + 3, error, nullptr});
+            leave();
+
+            enter();
+            dec_multiply_body<F, RWG, true, ring_depth(2 * RWG * kWordsPerUnit, DEEP)>(L.gate_up, cta, nctas, smem, tile, red, gate,
+                                                                                       TaggedIo{t0 + 3, 0u, t0 + 4, error, nullptr});
+            leave();
+
+            enter();
+            dec_multiply_body<F, RWD, false, ring_depth(RWD * kWordsPerUnit, DEEP)>(L.down, cta, nctas, smem, tile, red, gate,
+                                                                                    TaggedIo{t0 + 4, t0 + 3, t0 + 5, error, last ? P.plain_hidden : nullptr});
+            asm volatile("cp.async.wait_group 0;" ::: "memory");  // the next layer's descriptor
+            leave();
+        }
+    } else {
+        __shared__ int open_flag;
+        GridGate gate{P.sync, 0u, nctas, true, cta == 0 ? P.trace : nullptr, &open_flag};  // the first phase reads what earlier kernels wrote: no barrier
+        if (gate.trace != nullptr && threadIdx.x == 0) gate.trace[0] = now_ns();
+
+        for (uint32_t l = 0; l < P.n_layers; ++l) {
+            const StepLayerDesc& L = desc[l & 1];
+            if (l + 1 < P.n_layers) fetch_desc(l + 1);  // the other buffer's layer finished behind the barrier of its last arrive
+            gate.enter();
+            dec_multiply_body<F, RWA, false, ring_depth(RWA * kWordsPerUnit, DEEP)>(L.qkv, cta, nctas, smem, tile, red, gate);
+            gate.arrive();
+
+            gate.enter();
+            if (L.attn.dim == 128) {
+                if (L.attn.neox) step_scores<4, true, false>(L.attn, cta, nctas, smem, gate, ScoreTags{});
+                else step_scores<4, false, false>(L.attn, cta, nctas, smem, gate, ScoreTags{});
+            } else {
+                if (L.attn.neox) step_scores<2, true, false>(L.attn, cta, nctas, smem, gate, ScoreTags{});
+                else step_scores<2, false, false>(L.attn, cta, nctas, smem, gate, ScoreTags{});
+            }
+            gate.arrive();
+
+            gate.enter();
+            {
+                const uint32_t slices = L.attn.dim / L.attn.slice_width;
+                for (uint32_t task = cta; task < L.attn.heads * slices; task += nctas) {
+                    dec_attn_out_body<kStepThreads>(L.attn, task / slices, task % slices, smem, redf, red, gate);
+                    __syncthreads();  // the shared-memory row of probabilities is rewritten for the CTA's next task
+                }
+            }
+            gate.arrive();
+
+            gate.enter();
+            dec_multiply_body<F, RWO, false, ring_depth(RWO * kWordsPerUnit, DEEP)>(L.o, cta, nctas, smem, tile, red, gate);
+            gate.arrive();
+
+            gate.enter();
+            dec_multiply_body<F, RWG, true, ring_depth(2 * RWG * kWordsPerUnit, DEEP)>(L.gate_up, cta, nctas, smem, tile, red, gate);
+            gate.arrive();
+
+            gate.enter();
+            dec_multiply_body<F, RWD, false, ring_depth(RWD * kWordsPerUnit, DEEP)>(L.down, cta, nctas, smem, tile, red, gate);
+            asm volatile("cp.async.wait_group 0;" ::: "memory");  // the next layer's descriptor (long since landed); arrive's barrier publishes it
+            if (l + 1 < P.n_layers) gate.arrive();
+        }
+        if (gate.trace != nullptr && threadIdx.x == 0) gate.trace[2] = now_ns();
+
+        // Leave: the last CTA out re-arms the counters for the next launch (every CTA is past all of its waits by then).
+        __syncthreads();
+        if (threadIdx.x == 0) {
             __threadfence();
+            const unsigned int before = atomicAdd(P.sync + 1, 1u);
+            if (before + 1 == nctas) {
+                P.sync[0] = 0;
+                P.sync[1] = 0;
+                __threadfence();
+            }
         }
     }
 }
@@ -346,22 +492,22 @@ using StepKernel = void (*)(StepParams);
 
 struct Variant {
     int rw[4];  // rows per warp of the q/k/v, output, gate/up and down multiplies
-    StepKernel kernel;
+    StepKernel tagged, barrier;
 };
 
 template <class F>
 const Variant* variants(int& count) {
     constexpr bool heavy = sizeof(typename F::W) > 32;  // K-quants hold many registers per row
     if constexpr (heavy) {
-        static const Variant v[] = {{{2, 2, 1, 2}, step_kernel<F, 2, 2, 1, 2, true>},
-                                    {{2, 1, 1, 1}, step_kernel<F, 2, 1, 1, 1, false>},
-                                    {{1, 1, 1, 1}, step_kernel<F, 1, 1, 1, 1, false>}};
+        static const Variant v[] = {{{2, 2, 1, 2}, step_kernel<F, 2, 2, 1, 2, true, true>, step_kernel<F, 2, 2, 1, 2, true, false>},
+                                    {{2, 1, 1, 1}, step_kernel<F, 2, 1, 1, 1, false, true>, step_kernel<F, 2, 1, 1, 1, false, false>},
+                                    {{1, 1, 1, 1}, step_kernel<F, 1, 1, 1, 1, false, true>, step_kernel<F, 1, 1, 1, 1, false, false>}};
         count = 3;
         return v;
     } else {
-        static const Variant v[] = {{{4, 2, 4, 2}, step_kernel<F, 4, 2, 4, 2, true>},
-                                    {{2, 1, 2, 1}, step_kernel<F, 2, 1, 2, 1, false>},
-                                    {{1, 1, 1, 1}, step_kernel<F, 1, 1, 1, 1, false>}};
+        static const Variant v[] = {{{4, 2, 4, 2}, step_kernel<F, 4, 2, 4, 2, true, true>, step_kernel<F, 4, 2, 4, 2, true, false>},
+                                    {{2, 1, 2, 1}, step_kernel<F, 2, 1, 2, 1, false, true>, step_kernel<F, 2, 1, 2, 1, false, false>},
+                                    {{1, 1, 1, 1}, step_kernel<F, 1, 1, 1, 1, false, true>, step_kernel<F, 1, 1, 1, 1, false, false>}};
         count = 3;
         return v;
     }
@@ -398,8 +544,16 @@ int wanted_rows_per_warp(const DecMatParams& p, bool pair, uint32_t sms) {
 
 struct StepPlan::Impl {
     StepKernel kernel = nullptr;
+    bool tagged = true;
     StepLayerDesc* layers_dev = nullptr;
     unsigned int* sync_dev = nullptr;
+    uint2* pairs_dev = nullptr;  // tagged exchange: hidden | q | k | v | scores | attended | gated, as {value, tag} pairs
+    size_t pairs = 0;
+    uint2* tagged_hidden = nullptr;
+    float* plain_hidden = nullptr;
+    uint32_t hidden_size = 0;
+    uint32_t epoch = 0;          // launches so far; tags of a launch start above epoch * tags_per_launch
+    uint32_t tags_per_launch = 0;
     uint32_t n_layers = 0, grid = 0, tile_offset = 0;
     size_t smem = 0;
     unsigned long long* trace = nullptr;
@@ -410,11 +564,13 @@ StepPlan::~StepPlan() {
     if (impl_ != nullptr) {
         if (impl_->layers_dev) cudaFree(impl_->layers_dev);
         if (impl_->sync_dev) cudaFree(impl_->sync_dev);
+        if (impl_->pairs_dev) cudaFree(impl_->pairs_dev);
         delete impl_;
     }
 }
 
-bool StepPlan::build(const std::vector<StepLayerArgs>& layers, const StepShared& sh, uint32_t sms, cudaStream_t s, std::string& why_not) {
+bool StepPlan::build(const std::vector<StepLayerArgs>& layers, const StepShared& shared, uint32_t sms, cudaStream_t s, std::string& why_not) {
+    StepShared sh = shared;
     if (layers.empty()) {
         why_not = "no layers";
         return false;
@@ -442,6 +598,38 @@ bool StepPlan::build(const std::vector<StepLayerArgs>& layers, const StepShared&
     if (group > kMaxGroup) {
         why_not = "more than 8 query heads per K/V head";
         return false;
+    }
+
+    // BRISK_CUDA_STEP_SYNC=barrier keeps ordinary vectors and grid barriers between the operations (for comparison);
+    // the default is the tagged exchange.
+    const char* mode = std::getenv("BRISK_CUDA_STEP_SYNC");
+    const bool tagged = !(mode != nullptr && std::strcmp(mode, "barrier") == 0);
+    struct Freer {
+        void operator()(void* p) const { cudaFree(p); }
+    };
+    std::unique_ptr<void, Freer> pairs_guard;
+    uint2* pairs_dev = nullptr;
+    const size_t q_dim = size_t(sh.heads) * sh.dim, kv_dim = size_t(sh.kv_heads) * sh.dim;
+    const size_t pairs = sh.hidden_size + q_dim + 2 * kv_dim + size_t(sh.heads) * sh.max_context + q_dim + sh.ffn_size;
+    uint2* tagged_hidden = nullptr;
+    if (tagged) {
+        BK_CUDA(cudaMalloc(&pairs_dev, pairs * sizeof(uint2)));
+        pairs_guard.reset(pairs_dev);
+        BK_CUDA(cudaMemsetAsync(pairs_dev, 0, pairs * sizeof(uint2), s));  // tag 0 is never expected
+        uint2* at = pairs_dev;
+        auto take = [&](size_t n) {
+            float* p = reinterpret_cast<float*>(at);
+            at += n;
+            return p;
+        };
+        tagged_hidden = at;
+        sh.hidden = take(sh.hidden_size);
+        sh.q = take(q_dim);
+        sh.k = take(kv_dim);
+        sh.v = take(kv_dim);
+        sh.scores = take(size_t(sh.heads) * sh.max_context);
+        sh.attended = take(q_dim);
+        sh.gated = take(sh.ffn_size);
     }
 
     std::vector<StepLayerDesc> descs(layers.size());
@@ -519,16 +707,24 @@ bool StepPlan::build(const std::vector<StepLayerArgs>& layers, const StepShared&
         why_not = "the context is too long for the persistent kernel's shared memory";
         return false;
     }
-    BK_CUDA(cudaFuncSetAttribute(pick->kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    const StepKernel kernel = tagged ? pick->tagged : pick->barrier;
+    BK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
     int per_sm = 0;
-    BK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, pick->kernel, int(kStepThreads), smem));
+    BK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, int(kStepThreads), smem));
     if (per_sm < 1) {
         why_not = "the persistent kernel does not fit an SM";
         return false;
     }
 
     impl_ = new Impl();
-    impl_->kernel = pick->kernel;
+    impl_->kernel = kernel;
+    impl_->tagged = tagged;
+    impl_->pairs_dev = static_cast<uint2*>(pairs_guard.release());
+    impl_->pairs = pairs;
+    impl_->tagged_hidden = tagged_hidden;
+    impl_->plain_hidden = shared.hidden;
+    impl_->hidden_size = shared.hidden_size;
+    impl_->tags_per_launch = uint32_t(descs.size()) * 6 + 2;
     impl_->n_layers = uint32_t(descs.size());
     impl_->grid = sms;
     impl_->tile_offset = uint32_t(act);
@@ -539,18 +735,31 @@ bool StepPlan::build(const std::vector<StepLayerArgs>& layers, const StepShared&
     BK_CUDA(cudaMemsetAsync(impl_->sync_dev, 0, 64, s));
     BK_CUDA(cudaStreamSynchronize(s));  // descs goes out of scope
     char text[96];
-    std::snprintf(text, sizeof text, "rows per warp %d/%d/%d/%d, %u CTAs, %zu KB shared", pick->rw[0], pick->rw[1], pick->rw[2], pick->rw[3], sms, smem / 1024);
+    std::snprintf(text, sizeof text, "%s, rows per warp %d/%d/%d/%d, %u CTAs, %zu KB shared", tagged ? "tagged exchange" : "grid barriers", pick->rw[0],
+                  pick->rw[1], pick->rw[2], pick->rw[3], sms, smem / 1024);
     description_ = text;
     return true;
 }
 
-void StepPlan::launch(cudaStream_t s) const {
+void StepPlan::launch(cudaStream_t s) {
     StepParams P{};
     P.layers = impl_->layers_dev;
     P.n_layers = impl_->n_layers;
     P.sync = impl_->sync_dev;
     P.tile_offset = impl_->tile_offset;
     P.trace = impl_->trace;
+    if (impl_->tagged) {
+        // Tags must never repeat while old pairs are still in the buffers: when the 32-bit range runs out, wipe them.
+        if (uint64_t(impl_->epoch + 2) * impl_->tags_per_launch >= (uint64_t(1) << 32)) {
+            BK_CUDA(cudaMemsetAsync(impl_->pairs_dev, 0, impl_->pairs * sizeof(uint2), s));
+            impl_->epoch = 0;
+        }
+        ++impl_->epoch;
+        P.tag_base = impl_->epoch * impl_->tags_per_launch;
+        P.plain_hidden = impl_->plain_hidden;
+        P.tagged_hidden = impl_->tagged_hidden;
+        P.hidden_size = impl_->hidden_size;
+    }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(impl_->grid);
     cfg.blockDim = dim3(kStepThreads);

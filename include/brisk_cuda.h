@@ -30,9 +30,13 @@ enum brisk_cuda_type {
     BRISK_TYPE_F32 = 0,
     BRISK_TYPE_F16 = 1,
     BRISK_TYPE_Q4_0 = 2,
+    BRISK_TYPE_Q4_1 = 3,
+    BRISK_TYPE_Q5_0 = 6,
     BRISK_TYPE_Q8_0 = 8,
     BRISK_TYPE_Q4_K = 12,
+    BRISK_TYPE_Q5_K = 13,
     BRISK_TYPE_Q6_K = 14,
+    BRISK_TYPE_BF16 = 30, /* matrices only; widened to f32 on upload, as the reference widens it on load (src/model.cpp:439-449) */
     BRISK_TYPE_TQ2_0 = 35
 };
 

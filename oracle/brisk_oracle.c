@@ -104,7 +104,10 @@ uint16_t oracle_float_to_half(float f) {
 /* ---- block layouts (src/quant.h:26-130, :199-204), packed exactly as in a GGUF file ---- */
 #pragma pack(push, 1)
 typedef struct { uint16_t d; uint8_t qs[16]; } q4_0_t;                               /* 18 B  */
+typedef struct { uint16_t d, m; uint8_t qs[16]; } q4_1_t;                            /* 20 B  */
+typedef struct { uint16_t d; uint8_t qh[4]; uint8_t qs[16]; } q5_0_t;                /* 22 B  */
 typedef struct { uint16_t d; int8_t qs[32]; } q8_0_t;                                /* 34 B  */
+typedef struct { uint16_t d, dmin; uint8_t scales[12]; uint8_t qh[32]; uint8_t qs[128]; } q5_k_t; /* 176 B */
 typedef struct { uint16_t d, dmin; uint8_t scales[12]; uint8_t qs[128]; } q4_k_t;    /* 144 B */
 typedef struct { uint8_t ql[128]; uint8_t qh[64]; int8_t scales[16]; uint16_t d; } q6_k_t; /* 210 B */
 typedef struct { uint8_t qs[64]; uint16_t d; } tq2_0_t;                              /* 66 B  */
@@ -113,16 +116,19 @@ typedef struct { float d; int8_t qs[256]; int16_t bsums[16]; } q8_k_t;          
 
 static size_t type_block_elems(int32_t t) {
     switch (t) {
-        case BRISK_TYPE_Q4_0: case BRISK_TYPE_Q8_0: return QK;
-        case BRISK_TYPE_Q4_K: case BRISK_TYPE_Q6_K: case BRISK_TYPE_TQ2_0: return QKK;
+        case BRISK_TYPE_Q4_0: case BRISK_TYPE_Q4_1: case BRISK_TYPE_Q5_0: case BRISK_TYPE_Q8_0: return QK;
+        case BRISK_TYPE_Q4_K: case BRISK_TYPE_Q5_K: case BRISK_TYPE_Q6_K: case BRISK_TYPE_TQ2_0: return QKK;
         default: return 1;
     }
 }
 static size_t type_block_bytes(int32_t t) {
     switch (t) {
         case BRISK_TYPE_F32: return 4;
-        case BRISK_TYPE_F16: return 2;
+        case BRISK_TYPE_F16: case BRISK_TYPE_BF16: return 2;
         case BRISK_TYPE_Q4_0: return 18;
+        case BRISK_TYPE_Q4_1: return 20;
+        case BRISK_TYPE_Q5_0: return 22;
+        case BRISK_TYPE_Q5_K: return 176;
         case BRISK_TYPE_Q8_0: return 34;
         case BRISK_TYPE_Q4_K: return 144;
         case BRISK_TYPE_Q6_K: return 210;
@@ -130,7 +136,15 @@ static size_t type_block_bytes(int32_t t) {
         default: return 0;
     }
 }
-static int type_takes_q8_k(int32_t t) { return t == BRISK_TYPE_Q4_K || t == BRISK_TYPE_Q6_K || t == BRISK_TYPE_TQ2_0; }
+static int type_takes_q8_k(int32_t t) { return t == BRISK_TYPE_Q4_K || t == BRISK_TYPE_Q5_K || t == BRISK_TYPE_Q6_K || t == BRISK_TYPE_TQ2_0; }
+static int type_is_float(int32_t t) { return t == BRISK_TYPE_F32 || t == BRISK_TYPE_F16 || t == BRISK_TYPE_BF16; }
+/* src/model.cpp:20-25 */
+static float bfloat_to_float(uint16_t b) {
+    const uint32_t bits = (uint32_t)b << 16;
+    float out;
+    memcpy(&out, &bits, sizeof out);
+    return out;
+}
 
 /* ---- activation quantisers ---- */
 
@@ -205,7 +219,7 @@ static void q6_k_unpack(const q6_k_t* b, int8_t* q) {
     }
 }
 
-/* dequantize_q4_0 :196, _q8_0 :234, _q4_k :241, _q6_k :299, _tq2_0 :565 (src/quant.cpp). */
+/* dequantize_q4_0 :196, _q4_1 :207, _q5_0 :219, _q8_0 :234, _q4_k :241, _q5_k :263, _q6_k :299, _tq2_0 :565 (src/quant.cpp). */
 int oracle_dequantize(int32_t type, const void* blocks, float* out, uint64_t count) {
     switch (type) {
         case BRISK_TYPE_F32: memcpy(out, blocks, count * 4); return 0;
@@ -223,11 +237,61 @@ int oracle_dequantize(int32_t type, const void* blocks, float* out, uint64_t cou
             }
             return 0;
         }
+        case BRISK_TYPE_BF16:
+            for (uint64_t i = 0; i < count; ++i) out[i] = bfloat_to_float(((const uint16_t*)blocks)[i]);
+            return 0;
+        case BRISK_TYPE_Q4_1: {
+            const q4_1_t* w = (const q4_1_t*)blocks;
+            for (uint64_t b = 0; b < count / QK; ++b) {
+                const float d = oracle_half_to_float(w[b].d), m = oracle_half_to_float(w[b].m);
+                for (int i = 0; i < 16; ++i) {
+                    out[b * QK + i] = (float)(w[b].qs[i] & 0xF) * d + m;
+                    out[b * QK + i + 16] = (float)(w[b].qs[i] >> 4) * d + m;
+                }
+            }
+            return 0;
+        }
+        case BRISK_TYPE_Q5_0: {
+            const q5_0_t* w = (const q5_0_t*)blocks;
+            for (uint64_t b = 0; b < count / QK; ++b) {
+                const float d = oracle_half_to_float(w[b].d);
+                uint32_t qh;
+                memcpy(&qh, w[b].qh, 4);
+                for (int i = 0; i < 16; ++i) {
+                    const int lo = (w[b].qs[i] & 0xF) | (int)(((qh >> i) & 1) << 4);
+                    const int hi = (w[b].qs[i] >> 4) | (int)(((qh >> (i + 16)) & 1) << 4);
+                    out[b * QK + i] = (float)(lo - 16) * d;
+                    out[b * QK + i + 16] = (float)(hi - 16) * d;
+                }
+            }
+            return 0;
+        }
         case BRISK_TYPE_Q8_0: {
             const q8_0_t* w = (const q8_0_t*)blocks;
             for (uint64_t b = 0; b < count / QK; ++b) {
                 const float d = oracle_half_to_float(w[b].d);
                 for (int i = 0; i < QK; ++i) out[b * QK + i] = (float)w[b].qs[i] * d;
+            }
+            return 0;
+        }
+        case BRISK_TYPE_Q5_K: {
+            const q5_k_t* w = (const q5_k_t*)blocks;
+            for (uint64_t b = 0; b < count / QKK; ++b) {
+                const float d = oracle_half_to_float(w[b].d), dmin = oracle_half_to_float(w[b].dmin);
+                float* y = out + b * QKK;
+                for (int chunk = 0; chunk < 4; ++chunk) {
+                    uint8_t sc, mn;
+                    q4_k_scale_min(w[b].scales, 2 * chunk, &sc, &mn);
+                    const float d1 = d * sc, m1 = dmin * mn;
+                    q4_k_scale_min(w[b].scales, 2 * chunk + 1, &sc, &mn);
+                    const float d2 = d * sc, m2 = dmin * mn;
+                    const uint8_t* q = w[b].qs + chunk * 32;
+                    const uint8_t lo_bit = (uint8_t)(1u << (2 * chunk)), hi_bit = (uint8_t)(lo_bit << 1);
+                    for (int i = 0; i < 32; ++i) {
+                        y[chunk * 64 + i] = d1 * (float)((q[i] & 0xF) | ((w[b].qh[i] & lo_bit) ? 16 : 0)) - m1;
+                        y[chunk * 64 + 32 + i] = d2 * (float)((q[i] >> 4) | ((w[b].qh[i] & hi_bit) ? 16 : 0)) - m2;
+                    }
+                }
             }
             return 0;
         }
@@ -288,6 +352,63 @@ static float dot_q4_0(const q4_0_t* w, const q8_0_t* x, size_t blocks) {
             acc += ((w[b].qs[i] >> 4) - 8) * x[b].qs[i + 16];
         }
         sum += (float)acc * oracle_half_to_float(w[b].d) * oracle_half_to_float(x[b].d);
+    }
+    return sum;
+}
+
+/* src/quant.cpp:458-472 */
+static float dot_q5_0(const q5_0_t* w, const q8_0_t* x, size_t blocks) {
+    float sum = 0.0f;
+    for (size_t b = 0; b < blocks; ++b) {
+        uint32_t qh;
+        memcpy(&qh, w[b].qh, 4);
+        int32_t acc = 0;
+        for (int i = 0; i < 16; ++i) {
+            const int lo = ((w[b].qs[i] & 0xF) | (int)(((qh >> i) & 1) << 4)) - 16;
+            const int hi = ((w[b].qs[i] >> 4) | (int)(((qh >> (i + 16)) & 1) << 4)) - 16;
+            acc += lo * x[b].qs[i] + hi * x[b].qs[i + 16];
+        }
+        sum += (float)acc * oracle_half_to_float(w[b].d) * oracle_half_to_float(x[b].d);
+    }
+    return sum;
+}
+
+/* src/quant.cpp:484-498: the offset m multiplies the activation block's sum, scaled by the activation scale first. */
+static float dot_q4_1(const q4_1_t* w, const q8_0_t* x, size_t blocks) {
+    float sum = 0.0f;
+    for (size_t b = 0; b < blocks; ++b) {
+        int32_t acc = 0, xsum = 0;
+        for (int i = 0; i < 16; ++i) {
+            acc += (w[b].qs[i] & 0xF) * x[b].qs[i];
+            acc += (w[b].qs[i] >> 4) * x[b].qs[i + 16];
+            xsum += x[b].qs[i] + x[b].qs[i + 16];
+        }
+        const float dx = oracle_half_to_float(x[b].d);
+        sum += (float)acc * oracle_half_to_float(w[b].d) * dx + oracle_half_to_float(w[b].m) * (dx * (float)xsum);
+    }
+    return sum;
+}
+
+/* src/quant.cpp:523-547: Q4_K's arithmetic with the fifth bit of every weight taken from qh. */
+static float dot_q5_k(const q5_k_t* w, const q8_k_t* x, size_t blocks) {
+    float sum = 0.0f;
+    for (size_t b = 0; b < blocks; ++b) {
+        int32_t weighted = 0, offsets = 0;
+        for (int sb = 0; sb < 8; ++sb) {
+            uint8_t sc, mn;
+            q4_k_scale_min(w[b].scales, sb, &sc, &mn);
+            const uint8_t* q = w[b].qs + (sb / 2) * 32;
+            const uint8_t bit = (uint8_t)(1u << sb);
+            const int8_t* xq = x[b].qs + sb * 32;
+            int32_t dot = 0;
+            for (int i = 0; i < 32; ++i) {
+                const int v = ((sb & 1) ? (q[i] >> 4) : (q[i] & 0xF)) | ((w[b].qh[i] & bit) ? 16 : 0);
+                dot += v * xq[i];
+            }
+            weighted += sc * dot;
+            offsets += mn * (x[b].bsums[2 * sb] + x[b].bsums[2 * sb + 1]);
+        }
+        sum += x[b].d * (oracle_half_to_float(w[b].d) * (float)weighted - oracle_half_to_float(w[b].dmin) * (float)offsets);
     }
     return sum;
 }
@@ -371,7 +492,10 @@ static float dot_f32(const float* a, const float* b, size_t n) {
 static float dot_row(int32_t type, const uint8_t* row, const void* xq, size_t blocks) {
     switch (type) {
         case BRISK_TYPE_Q4_0: return dot_q4_0((const q4_0_t*)row, (const q8_0_t*)xq, blocks);
+        case BRISK_TYPE_Q4_1: return dot_q4_1((const q4_1_t*)row, (const q8_0_t*)xq, blocks);
+        case BRISK_TYPE_Q5_0: return dot_q5_0((const q5_0_t*)row, (const q8_0_t*)xq, blocks);
         case BRISK_TYPE_Q8_0: return dot_q8_0((const q8_0_t*)row, (const q8_0_t*)xq, blocks);
+        case BRISK_TYPE_Q5_K: return dot_q5_k((const q5_k_t*)row, (const q8_k_t*)xq, blocks);
         case BRISK_TYPE_Q4_K: return dot_q4_k((const q4_k_t*)row, (const q8_k_t*)xq, blocks);
         case BRISK_TYPE_Q6_K: return dot_q6_k((const q6_k_t*)row, (const q8_k_t*)xq, blocks);
         default: return dot_tq2_0((const tq2_0_t*)row, (const q8_k_t*)xq, blocks);
@@ -401,7 +525,7 @@ static void mm_rows_float(void* p, int64_t r0, int64_t r1) {
             wr = (const float*)j->w + (size_t)r * j->cols;
         } else {
             const uint16_t* h = (const uint16_t*)j->w + (size_t)r * j->cols;
-            for (size_t i = 0; i < j->cols; ++i) wide[i] = oracle_half_to_float(h[i]);
+            for (size_t i = 0; i < j->cols; ++i) wide[i] = j->type == BRISK_TYPE_BF16 ? bfloat_to_float(h[i]) : oracle_half_to_float(h[i]);
             wr = wide;
         }
         for (uint64_t t = 0; t < j->n; ++t) j->out[t * j->rows + r] = dot_f32(wr, j->x + t * j->cols, j->cols);
@@ -419,7 +543,7 @@ static void mm_rows_quant(void* p, int64_t r0, int64_t r1) {
 
 int oracle_matmul(int32_t type, const void* w, uint64_t rows, uint64_t cols, const float* x, uint64_t n, float* out) {
     mm_job j = {type, w, rows, cols, n, x, NULL, 0, 0, 0, out};
-    if (type == BRISK_TYPE_F32 || type == BRISK_TYPE_F16) {
+    if (type_is_float(type)) {
         parallel_for((int64_t)rows, mm_rows_float, &j);
         return 0;
     }

@@ -35,7 +35,10 @@ thread_local std::string g_error;
 bool to_format(int ggml_type, brisk::WeightFormat& out) {
     switch (ggml_type) {
         case 2: out = brisk::WeightFormat::Q4_0; return true;
+        case 3: out = brisk::WeightFormat::Q4_1; return true;
+        case 6: out = brisk::WeightFormat::Q5_0; return true;
         case 8: out = brisk::WeightFormat::Q8_0; return true;
+        case 13: out = brisk::WeightFormat::Q5_K; return true;
         case 12: out = brisk::WeightFormat::Q4_K; return true;
         case 14: out = brisk::WeightFormat::Q6_K; return true;
         case 35: out = brisk::WeightFormat::TQ2_0; return true;
@@ -82,6 +85,9 @@ int ref_dequantize(int ggml_type, const void* blocks, float* out, std::uint64_t 
     if (!to_format(ggml_type, f)) return -1;
     switch (f) {
         case brisk::WeightFormat::Q4_0: brisk::dequantize_q4_0(static_cast<const brisk::BlockQ4_0*>(blocks), out, count); break;
+        case brisk::WeightFormat::Q4_1: brisk::dequantize_q4_1(static_cast<const brisk::BlockQ4_1*>(blocks), out, count); break;
+        case brisk::WeightFormat::Q5_0: brisk::dequantize_q5_0(static_cast<const brisk::BlockQ5_0*>(blocks), out, count); break;
+        case brisk::WeightFormat::Q5_K: brisk::dequantize_q5_k(static_cast<const brisk::BlockQ5_K*>(blocks), out, count); break;
         case brisk::WeightFormat::Q8_0: brisk::dequantize_q8_0(static_cast<const brisk::BlockQ8_0*>(blocks), out, count); break;
         case brisk::WeightFormat::Q4_K: brisk::dequantize_q4_k(static_cast<const brisk::BlockQ4_K*>(blocks), out, count); break;
         case brisk::WeightFormat::Q6_K: brisk::dequantize_q6_k(static_cast<const brisk::BlockQ6_K*>(blocks), out, count); break;

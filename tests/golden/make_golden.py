@@ -27,6 +27,7 @@ FAMILIES = {
     "mistral": synth.tiny(synth.MISTRAL_7B, hidden=256, heads=4, kv_heads=2, ffn=512, vocab=256),
 }
 FORMATS = (F.Q4_0, F.Q8_0, F.Q4_K, F.Q6_K, F.TQ2_0)
+MORE_FORMATS = (F.Q4_1, F.Q5_0, F.Q5_K)  # formats the reference reads but the benchmark configurations do not use; in primitives_more.npz
 
 
 def golden_model(family):
@@ -51,6 +52,27 @@ def primitive_inputs():
     return x
 
 
+def format_vectors(r, formats, out):
+    """Per format: a seeded matrix, the reference's dequantisation of it, and its products with 1 and 7 activation rows."""
+    xs = primitive_inputs().reshape(7, 1024)
+    for fmt in formats:
+        wb, _ = H.random_matrix(fmt, 37, 1024, seed=100 + fmt)
+        deq = np.empty(37 * 1024, np.float32)
+        assert r.ref_dequantize(fmt, wb.ctypes.data, H.fptr(deq), deq.size) == 0
+        mv = np.empty((1, 37), np.float32)
+        mm = np.empty((7, 37), np.float32)
+        assert r.ref_matmul(fmt, wb.ctypes.data, 37, 1024, H.fptr(xs[:1].copy()), 1, H.fptr(mv)) == 0
+        assert r.ref_matmul(fmt, wb.ctypes.data, 37, 1024, H.fptr(xs), 7, H.fptr(mm)) == 0
+        n = F.NAMES[fmt]
+        out[f"w_{n}"], out[f"deq_{n}"], out[f"matvec_{n}"], out[f"matmul_{n}"] = wb, deq, mv, mm
+
+
+def more_formats():
+    out = {}
+    format_vectors(H.ref(), MORE_FORMATS, out)
+    np.savez_compressed(os.path.join(HERE, "primitives_more.npz"), **out)
+
+
 def main():
     r = H.ref()
     out = {}
@@ -72,18 +94,9 @@ def main():
     kq = np.zeros(34, np.uint8)
     r.ref_quantize_q8_0(H.fptr(ka), kq.ctypes.data, 32)
     out["q8_0_known_answer"] = kq
-    xs = x.reshape(7, 1024)
-    for fmt in FORMATS:
-        wb, _ = H.random_matrix(fmt, 37, 1024, seed=100 + fmt)
-        deq = np.empty(37 * 1024, np.float32)
-        r.ref_dequantize(fmt, wb.ctypes.data, H.fptr(deq), deq.size)
-        mv = np.empty((1, 37), np.float32)
-        mm = np.empty((7, 37), np.float32)
-        r.ref_matmul(fmt, wb.ctypes.data, 37, 1024, H.fptr(xs[:1].copy()), 1, H.fptr(mv))
-        r.ref_matmul(fmt, wb.ctypes.data, 37, 1024, H.fptr(xs), 7, H.fptr(mm))
-        n = F.NAMES[fmt]
-        out[f"w_{n}"], out[f"deq_{n}"], out[f"matvec_{n}"], out[f"matmul_{n}"] = wb, deq, mv, mm
+    format_vectors(r, FORMATS, out)
     np.savez_compressed(os.path.join(HERE, "primitives.npz"), **out)
+    more_formats()
 
     for family, spec in FAMILIES.items():
         m = golden_model(family)
@@ -133,4 +146,7 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    if "--more-formats-only" in sys.argv:
+        more_formats()
+    else:
+        main()

@@ -12,7 +12,7 @@ import helpers as H
 from brisk_llm_b200 import engine, formats as F
 
 pytestmark = pytest.mark.gpu
-FORMATS = (F.Q4_0, F.Q8_0, F.Q4_K, F.Q6_K, F.TQ2_0)
+FORMATS = (F.Q4_0, F.Q4_1, F.Q5_0, F.Q8_0, F.Q4_K, F.Q5_K, F.Q6_K, F.TQ2_0)
 
 
 def check(fmt, rows, cols, n, seed=0, scale=1.0):
@@ -62,7 +62,7 @@ def test_zero_and_extreme_activations(fmt):
     assert np.all(got[0] == 0.0)
 
 
-@pytest.mark.parametrize("fmt", (F.F16, F.F32), ids=lambda f: F.NAMES[f])
+@pytest.mark.parametrize("fmt", (F.F16, F.BF16, F.F32), ids=lambda f: F.NAMES[f])
 def test_float_head(fmt):
     rng = np.random.default_rng(3)
     w = (rng.standard_normal((77, 2560)) * 0.02).astype(np.float16)

@@ -10,14 +10,15 @@ import helpers as H
 from brisk_llm_b200 import abi, formats as F, synth
 
 
-@pytest.mark.parametrize("fmt", (F.Q4_0, F.Q8_0, F.Q4_K, F.Q6_K, F.TQ2_0, F.F16), ids=lambda f: F.NAMES[f])
+@pytest.mark.parametrize("fmt", (F.Q4_0, F.Q4_1, F.Q5_0, F.Q8_0, F.Q4_K, F.Q5_K, F.Q6_K, F.TQ2_0, F.F16, F.BF16), ids=lambda f: F.NAMES[f])
 def test_encoders_are_valid_and_close(fmt):
     wb, w = H.random_matrix(fmt, 16, 512, seed=fmt)
     assert wb.nbytes == 16 * F.row_bytes(fmt, 512)
     deq = np.empty(16 * 512, np.float32)
     assert H.oracle().oracle_dequantize(fmt, wb.ctypes.data, H.fptr(deq), deq.size) == 0
     assert np.array_equal(deq, F.dequantize(fmt, wb, deq.size))
-    step = {F.Q4_0: 0.02 * 4 / 8, F.Q8_0: 0.02 * 4 / 127, F.Q4_K: 0.02 * 8 / 15, F.Q6_K: 0.02 * 4 / 32, F.TQ2_0: 1e-6, F.F16: 1e-4}[fmt]
+    step = {F.Q4_0: 0.02 * 4 / 8, F.Q8_0: 0.02 * 4 / 127, F.Q4_K: 0.02 * 8 / 15, F.Q6_K: 0.02 * 4 / 32, F.TQ2_0: 1e-6, F.F16: 1e-4,
+            F.Q4_1: 0.02 * 8 / 15, F.Q5_0: 0.02 * 4 / 16, F.Q5_K: 0.02 * 8 / 31, F.BF16: 1e-3}[fmt]
     assert np.abs(deq - w.ravel()).max() <= step
 
 

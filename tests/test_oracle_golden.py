@@ -16,7 +16,8 @@ spec = importlib.util.spec_from_file_location("make_golden", os.path.join(H.GOLD
 mg = importlib.util.module_from_spec(spec)
 spec.loader.exec_module(mg)
 
-PRIM = np.load(os.path.join(H.GOLDEN, "primitives.npz"))
+PRIM = dict(np.load(os.path.join(H.GOLDEN, "primitives.npz")))
+PRIM.update(np.load(os.path.join(H.GOLDEN, "primitives_more.npz")))
 
 
 def test_half_conversions():
@@ -60,7 +61,7 @@ def test_activation_quantisers_bytes():
     assert np.array_equal(qk, PRIM["q8_k_bytes"])
 
 
-@pytest.mark.parametrize("fmt", mg.FORMATS, ids=lambda f: F.NAMES[f])
+@pytest.mark.parametrize("fmt", mg.FORMATS + mg.MORE_FORMATS, ids=lambda f: F.NAMES[f])
 def test_dequantize_and_multiply(fmt):
     o = H.oracle()
     n = F.NAMES[fmt]

@@ -17,7 +17,7 @@ def test_reference_runs_generic_kernels():
     assert H.ref().ref_kernel_set_name() in (b"generic", b"neon", b"dotprod", b"i8mm")
 
 
-@pytest.mark.parametrize("fmt", (F.Q4_0, F.Q8_0, F.Q4_K, F.Q6_K, F.TQ2_0), ids=lambda f: F.NAMES[f])
+@pytest.mark.parametrize("fmt", (F.Q4_0, F.Q4_1, F.Q5_0, F.Q8_0, F.Q4_K, F.Q5_K, F.Q6_K, F.TQ2_0), ids=lambda f: F.NAMES[f])
 @pytest.mark.parametrize("rows,cols,n", [(36, 1024, 1), (37, 1024, 7), (48, 2048, 3), (5, 256, 2)])
 def test_multiply_bit_exact(fmt, rows, cols, n):
     r = H.ref()
@@ -45,6 +45,9 @@ def test_f16_head_bit_exact():
     ("llama", synth.tiny(synth.LLAMA_3_2_1B, hidden=512, heads=8, kv_heads=2, ffn=1024, context=512)),
     ("bitnet", synth.tiny(synth.BITNET_2B, hidden=512, heads=4, kv_heads=1, ffn=768, context=512)),
     ("mistral", synth.tiny(synth.MISTRAL_7B, hidden=256, heads=4, kv_heads=2, ffn=512, layers=3, context=512)),
+    # the formats the reference reads beyond the benchmark configurations, mixed the way stock downloads mix them
+    ("mixed", synth.tiny(synth.QWEN3_0_6B, hidden=256, heads=4, kv_heads=2, ffn=512, context=512, tied=False, fmt=F.Q5_K,
+                         fmt_overrides={"v": F.Q4_1, "down": F.Q5_0, "embd": F.Q4_1, "output": F.BF16})),
 ])
 def test_session_bit_exact(family, spec):
     r = H.ref()
