@@ -8,7 +8,7 @@ from __future__ import annotations
 import ctypes as C
 import os
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG_DIR, "libbrisk_cuda.so")
 
@@ -28,7 +28,7 @@ _FP = C.POINTER(C.c_float)
 class Layer(C.Structure):
     _fields_ = [("attn_norm", _FP), ("q", Matrix), ("k", Matrix), ("v", Matrix), ("q_norm", _FP), ("k_norm", _FP),
                 ("attn_sub_norm", _FP), ("o", Matrix), ("ffn_norm", _FP), ("gate", Matrix), ("up", Matrix),
-                ("ffn_sub_norm", _FP), ("down", Matrix)]
+                ("ffn_sub_norm", _FP), ("down", Matrix), ("q_bias", _FP), ("k_bias", _FP), ("v_bias", _FP)]
 
 
 class Model(C.Structure):

@@ -147,9 +147,10 @@ __global__ void __launch_bounds__(128) dec_attn_scores_kernel(const DecAttnParam
     const bool owns_new = pos >= begin && pos < begin + 128;  // this CTA's chunk holds the token's own position
     for (uint32_t task = warp; task < GROUP + 1u; task += 4) {
         if (task < GROUP) {
-            warp_norm_rope_head<DIM / 32>(a.q + size_t(kvh * GROUP + task) * dim, a.q_norm, rope, a.eps, a.neox, qs + task * dim);
+            warp_norm_rope_head<DIM / 32>(a.q + size_t(kvh * GROUP + task) * dim, a.q_bias ? a.q_bias + size_t(kvh * GROUP + task) * dim : nullptr, a.q_norm, rope, a.eps,
+                                          a.neox, qs + task * dim);
         } else if (owns_new) {
-            warp_norm_rope_head<DIM / 32>(a.k + size_t(kvh) * dim, a.k_norm, rope, a.eps, a.neox, knew);
+            warp_norm_rope_head<DIM / 32>(a.k + size_t(kvh) * dim, a.k_bias ? a.k_bias + size_t(kvh) * dim : nullptr, a.k_norm, rope, a.eps, a.neox, knew);
             __syncwarp();
             warp_store_new_kv(a, kvh, pos, knew);
         }
@@ -255,6 +256,7 @@ void launch_dec_multiply(const MatTarget* targets, int count, const float* x, co
 void launch_dec_attention(const RopeArgs& r, const AttnArgs& at, uint32_t sms, cudaStream_t s) {
     DecAttnParams a{};
     a.q = r.q; a.k = r.k; a.v = r.v; a.q_norm = r.q_norm; a.k_norm = r.k_norm; a.rope = r.rope;
+    a.q_bias = r.q_bias; a.k_bias = r.k_bias; a.v_bias = r.v_bias;
     a.k_cache = r.k_cache; a.v_cache = r.v_cache; a.scores = at.scores; a.out = at.out; a.position = r.position;
     a.heads = r.heads; a.kv_heads = r.kv_heads; a.dim = r.dim; a.max_context = r.max_context;
     a.eps = r.eps; a.scale = at.scale; a.neox = r.neox;

@@ -435,6 +435,9 @@ struct DecAttnParams {
     const float* v;       // [kv*dim]
     const float* q_norm;  // [dim] or nullptr
     const float* k_norm;
+    const float* q_bias;  // [heads*dim] / [kv*dim] / [kv*dim] projection biases added before norm and RoPE, or nullptr
+    const float* k_bias;
+    const float* v_bias;
     const float* rope;    // [max_context][dim]
     __half* k_cache;      // [kv][max_context][dim]
     __half* v_cache;
@@ -454,10 +457,14 @@ struct DecAttnParams {
 // pairing (i, i + dim/2), elements VPL*l + k for the adjacent pairing (2i, 2i+1). No block-level barrier is needed.
 // `src` is read with L2 loads (it was produced by the previous operation of the step).
 template <int VPL, bool NEOX>
-__device__ __forceinline__ void warp_head_load(const float* src, float (&v)[VPL]) {
+__device__ __forceinline__ void warp_head_load(const float* src, const float* bias, float (&v)[VPL]) {
     const uint32_t lane = threadIdx.x & 31;
 #pragma unroll
-    for (int k = 0; k < VPL; ++k) v[k] = __ldcg(src + (NEOX ? lane + 32 * k : VPL * lane + k));
+    for (int k = 0; k < VPL; ++k) {
+        const uint32_t i = NEOX ? lane + 32 * k : VPL * lane + k;
+        v[k] = __ldcg(src + i);
+        if (bias != nullptr) v[k] = __fadd_rn(v[k], bias[i]);  // add_bias, src/model.cpp:1026-1030
+    }
 }
 
 template <int VPL, bool NEOX>
@@ -488,16 +495,16 @@ __device__ __forceinline__ void warp_head_norm_rope(float (&v)[VPL], const float
 }
 
 template <int VPL, bool NEOX>
-__device__ __forceinline__ void warp_norm_rope_head_impl(const float* src, const float* norm, const float* rope, float eps, float* dst) {
+__device__ __forceinline__ void warp_norm_rope_head_impl(const float* src, const float* bias, const float* norm, const float* rope, float eps, float* dst) {
     float v[VPL];
-    warp_head_load<VPL, NEOX>(src, v);
+    warp_head_load<VPL, NEOX>(src, bias, v);
     warp_head_norm_rope<VPL, NEOX>(v, norm, rope, eps, dst);
 }
 
 template <int VPL>
-__device__ __forceinline__ void warp_norm_rope_head(const float* src, const float* norm, const float* rope, float eps, int neox, float* dst) {
-    if (neox) warp_norm_rope_head_impl<VPL, true>(src, norm, rope, eps, dst);
-    else warp_norm_rope_head_impl<VPL, false>(src, norm, rope, eps, dst);
+__device__ __forceinline__ void warp_norm_rope_head(const float* src, const float* bias, const float* norm, const float* rope, float eps, int neox, float* dst) {
+    if (neox) warp_norm_rope_head_impl<VPL, true>(src, bias, norm, rope, eps, dst);
+    else warp_norm_rope_head_impl<VPL, false>(src, bias, norm, rope, eps, dst);
 }
 
 // The new position's K and V rows of K/V head `kvh`: k (already normed and rotated, in `knew`) is rounded to f16,
@@ -509,7 +516,9 @@ __device__ __forceinline__ void warp_store_new_kv(const DecAttnParams& a, uint32
         const __half kh = __float2half_rn(knew[i]);
         a.k_cache[base + i] = kh;
         knew[i] = __half2float(kh);
-        a.v_cache[base + i] = __float2half_rn(__ldcg(a.v + size_t(kvh) * a.dim + i));
+        float v = __ldcg(a.v + size_t(kvh) * a.dim + i);
+        if (a.v_bias != nullptr) v = __fadd_rn(v, a.v_bias[size_t(kvh) * a.dim + i]);
+        a.v_cache[base + i] = __float2half_rn(v);
     }
 }
 
@@ -553,37 +562,37 @@ __device__ __forceinline__ void dec_attn_out_body(const DecAttnParams& a, const 
     const float* s = a.scores + size_t(h) * a.max_context;
     const __half* vbase = a.v_cache + size_t(kvh) * a.max_context * dim + slice * width;
 
-    // V tiles stream through a ring of shared-memory stages with cp.async (L2 -> shared, not through L1); warp 0 only.
+    // V: the first kVStages tiles (all of V at contexts up to 512) are requested by every thread of the CTA at once,
+    // before anything else - cp.async, L2 -> shared, not through L1 - so that their latency hides behind the wait for
+    // the scores and the softmax. Longer contexts continue through the same stages as a ring that warp 0 refills.
     const uint32_t tiles = (visible + kVTile - 1) / kVTile;
-    const uint32_t per_row = width / 8;                  // 16-byte chunks of one position's slice
-    const uint32_t chunks_per_tile = kVTile * per_row;
+    const uint32_t row_shift = width == 16 ? 1 : 2;       // 16-byte chunks of one position's slice: 2 or 4
+    const uint32_t chunks_per_tile = kVTile << row_shift;
     const uint32_t in_cache = Io::kTagged ? visible - 1 : visible;  // positions whose V row is read from the cache
-    auto stage = [&](uint32_t tile_index) {
+    auto stage = [&](uint32_t tile_index, uint32_t first, uint32_t step) {  // by threads first, first + step, ...
         if (tile_index * kVTile < in_cache) {
             __half* dst = vt + size_t(tile_index % kVStages) * kVTile * width;
             const __half* src = vbase + size_t(tile_index) * kVTile * dim;
             const uint32_t rows = min(kVTile, in_cache - tile_index * kVTile);
-            for (uint32_t c = lane; c < chunks_per_tile; c += 32) {
-                const uint32_t row = c / per_row, col = (c % per_row) * 8;
+            for (uint32_t c = first; c < chunks_per_tile; c += step) {
+                const uint32_t row = c >> row_shift, col = (c & ((1u << row_shift) - 1)) * 8;
                 if (row < rows) {
                     const uint32_t sm_addr = uint32_t(__cvta_generic_to_shared(dst + row * width + col));
                     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sm_addr), "l"(src + size_t(row) * dim + col) : "memory");
                 }
             }
         }
-        asm volatile("cp.async.commit_group;" ::: "memory");  // one group per tile index, empty past the end
     };
     unsigned long long* trace = (a.trace != nullptr && h == 0 && slice == 0) ? a.trace + 8 : nullptr;
     dec_stamp(trace, 0, 0);
-    uint32_t staged = 0;
-    if (warp == 0) {
-        while (staged + 1 < kVStages && staged + 1 < tiles) stage(staged++);  // tiles before the last one
-    }
+    const uint32_t bulk = min(tiles, kVStages);
+    // The position written by this step sits in the last tile: without tags that tile waits for the gate.
+    const uint32_t early = Io::kTagged ? bulk : min(bulk, tiles - 1);
+    for (uint32_t t = 0; t < early; ++t) stage(t, tid, NT);
     gate.wait();
     dec_stamp(trace, 0, 1);
-    if (warp == 0) {
-        while (staged + 1 < kVStages) stage(staged++);
-    }
+    for (uint32_t t = early; t < bulk; ++t) stage(t, tid, NT);
+    asm volatile("cp.async.commit_group;" ::: "memory");
 
     // softmax (src/kernels_f32.cpp:275-284): max, e = expf(s - max), f64 sum, p = e * float(1/sum). The row lives in
     // shared memory; the loops have run-time trip counts (one or two rounds at short contexts) - an unrolled,
@@ -619,7 +628,8 @@ __device__ __forceinline__ void dec_attn_out_body(const DecAttnParams& a, const 
     const float inv = float(1.0 / total);
     dec_stamp(trace, 0, 4);
     for (uint32_t p = tid; p < visible; p += NT) ps[p] = __fmul_rn(ps[p], inv);
-    __syncthreads();  // the probabilities are complete for warp 0
+    asm volatile("cp.async.wait_group 0;" ::: "memory");  // this thread's share of the first tiles
+    __syncthreads();  // the probabilities and the first kVStages tiles are complete for warp 0
     if (warp != 0) return;
 
     // weighted sum (src/kernels_f32.cpp:265-273): out[i] += p[pos] * v[pos][i], position after position. Lane c owns
@@ -628,13 +638,15 @@ __device__ __forceinline__ void dec_attn_out_body(const DecAttnParams& a, const 
     const uint32_t col = lane < width ? lane : 0;
     float acc = 0.0f;
     for (uint32_t t = 0; t < tiles; ++t) {
-        stage(t + kVStages - 1);  // refills the stage consumed in the previous iteration
-        asm volatile("cp.async.wait_group %0;" ::"n"(kVStages - 1) : "memory");
-        __syncwarp();  // tile t has landed for every lane
+        if (t >= kVStages) {  // a tile warp 0 requested itself, kVStages iterations ago: one group per iteration since
+            asm volatile("cp.async.wait_group %0;" ::"n"(kVStages - 1) : "memory");
+            __syncwarp();
+        }
         __half* tile_v = vt + size_t(t % kVStages) * kVTile * width;
         if constexpr (Io::kTagged) {
             if (t + 1 == tiles && lane < width) {  // the token's own row: column `lane` is read back by this same lane below
-                const float v = poll_pair(reinterpret_cast<const uint2*>(a.v) + size_t(kvh) * dim + slice * width + lane, io.tag_v, io.error);
+                float v = poll_pair(reinterpret_cast<const uint2*>(a.v) + size_t(kvh) * dim + slice * width + lane, io.tag_v, io.error);
+                if (a.v_bias != nullptr) v = __fadd_rn(v, a.v_bias[size_t(kvh) * dim + slice * width + lane]);
                 tile_v[((visible - 1) % kVTile) * width + lane] = __float2half_rn(v);
             }
         }
@@ -667,7 +679,9 @@ __device__ __forceinline__ void dec_attn_out_body(const DecAttnParams& a, const 
             j += 16;
         }
         for (; j < rows; ++j) acc = __fadd_rn(acc, __fmul_rn(pw[j], __half2float(tv[j * width])));
-        __syncwarp();  // every lane is done with tile t before its stage is refilled
+        __syncwarp();  // every lane is done with tile t: its stage takes the tile kVStages further on
+        stage(t + kVStages, lane, 32);
+        asm volatile("cp.async.commit_group;" ::: "memory");
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");  // only empty groups remain
     dec_stamp(trace, 0, 5);

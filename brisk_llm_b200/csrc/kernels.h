@@ -76,6 +76,9 @@ struct RopeArgs {
     const float* v;      // [n][kv*dim]
     const float* q_norm; // [dim] or nullptr
     const float* k_norm;
+    const float* q_bias = nullptr;  // [heads*dim] / [kv*dim] projection biases, or nullptr (all three or none)
+    const float* k_bias = nullptr;
+    const float* v_bias = nullptr;
     const float* rope;   // [max_context][dim]: cos, sin per pair, indexed by absolute position
     __half* k_cache;     // [kv][max_context][dim]
     __half* v_cache;
@@ -119,6 +122,9 @@ struct StepLayerArgs {
     const float* attn_sub_norm = nullptr;
     const float* ffn_norm = nullptr;
     const float* ffn_sub_norm = nullptr;
+    const float* q_bias = nullptr;
+    const float* k_bias = nullptr;
+    const float* v_bias = nullptr;
     __half* k_cache = nullptr;
     __half* v_cache = nullptr;
 };

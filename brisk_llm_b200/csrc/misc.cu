@@ -150,7 +150,13 @@ __global__ void __launch_bounds__(128) qk_norm_rope_store_kernel(const RopeArgs 
     const float* norm = is_q ? a.q_norm : a.k_norm;
     const uint32_t pos = *a.position + t;
 
-    for (uint32_t i = tid; i < dim; i += 128) head[i] = src[i];
+    const float* bias = is_q ? a.q_bias : a.k_bias;  // add_bias before norm and RoPE (src/model.cpp:1026-1030)
+    if (bias != nullptr) {
+        bias += size_t(is_q ? h : kvh) * dim;
+        for (uint32_t i = tid; i < dim; i += 128) head[i] = __fadd_rn(src[i], bias[i]);
+    } else {
+        for (uint32_t i = tid; i < dim; i += 128) head[i] = src[i];
+    }
     __syncthreads();
     if (norm != nullptr) {
         double part = 0.0;
@@ -189,7 +195,12 @@ __global__ void __launch_bounds__(128) qk_norm_rope_store_kernel(const RopeArgs 
         a.k_cache[base + i1] = __float2half_rn(out1);
     }
     const float* v = a.v + size_t(t) * a.kv_heads * dim + size_t(kvh) * dim;
-    for (uint32_t i = tid; i < dim; i += 128) a.v_cache[base + i] = __float2half_rn(v[i]);
+    if (a.v_bias != nullptr) {
+        const float* vb = a.v_bias + size_t(kvh) * dim;
+        for (uint32_t i = tid; i < dim; i += 128) a.v_cache[base + i] = __float2half_rn(__fadd_rn(v[i], vb[i]));
+    } else {
+        for (uint32_t i = tid; i < dim; i += 128) a.v_cache[base + i] = __float2half_rn(v[i]);
+    }
 }
 
 // ---- attention --------------------------------------------------------------------------------------------

@@ -85,6 +85,7 @@ namespace {
 struct Layer {
     DevMatrix q, k, v, o, gate, up, down;
     const float *attn_norm = nullptr, *q_norm = nullptr, *k_norm = nullptr, *attn_sub_norm = nullptr, *ffn_norm = nullptr, *ffn_sub_norm = nullptr;
+    const float *q_bias = nullptr, *k_bias = nullptr, *v_bias = nullptr;  // this rank's rows
     __half *k_cache = nullptr, *v_cache = nullptr;
 };
 
@@ -110,7 +111,8 @@ brisk_cuda_memory estimate(const brisk_cuda_model& m, const brisk_cuda_options& 
         e.weights += planes(L.q.type, q_dim / tp, hidden) + planes(L.k.type, kv_dim / tp, hidden) + planes(L.v.type, kv_dim / tp, hidden);
         e.weights += planes(L.o.type, hidden / tp, q_dim) + planes(L.gate.type, ffn / tp, hidden) + planes(L.up.type, ffn / tp, hidden);
         e.weights += planes(L.down.type, hidden / tp, ffn);
-        e.weights += (2 * hidden + (L.q_norm ? dim : 0) + (L.k_norm ? dim : 0) + (L.attn_sub_norm ? q_dim : 0) + (L.ffn_sub_norm ? ffn : 0)) * 4;
+        e.weights += (2 * hidden + (L.q_norm ? dim : 0) + (L.k_norm ? dim : 0) + (L.attn_sub_norm ? q_dim : 0) + (L.ffn_sub_norm ? ffn : 0) +
+                      (L.q_bias ? (q_dim + 2 * kv_dim) / tp : 0)) * 4;
     }
     e.cache = uint64_t(m.layer_count) * 2 * (kv_dim / tp) * ctx * 2;
     const uint64_t widest = std::max(std::max(hidden, q_dim), ffn), batch = kMaxBatch;
@@ -362,6 +364,12 @@ struct Session {
             d.v = upload_matrix(s.v, "attn_v.weight", kv_dim, hidden, staging, r * kv_dim_l, kv_dim_l);
             d.q_norm = upload_vector(s.q_norm, head_dim, "attn_q_norm.weight", false);
             d.k_norm = upload_vector(s.k_norm, head_dim, "attn_k_norm.weight", false);
+            if ((s.q_bias != nullptr) != (s.k_bias != nullptr) || (s.q_bias != nullptr) != (s.v_bias != nullptr)) {
+                throw CudaError("cuda: attn_q.bias, attn_k.bias and attn_v.bias come all three or not at all");
+            }
+            d.q_bias = upload_vector(s.q_bias ? s.q_bias + r * q_dim_l : nullptr, q_dim_l, "attn_q.bias", false);
+            d.k_bias = upload_vector(s.k_bias ? s.k_bias + r * kv_dim_l : nullptr, kv_dim_l, "attn_k.bias", false);
+            d.v_bias = upload_vector(s.v_bias ? s.v_bias + r * kv_dim_l : nullptr, kv_dim_l, "attn_v.bias", false);
             d.attn_sub_norm = upload_vector(s.attn_sub_norm, q_dim, "attn_sub_norm.weight", false);
             d.o = upload_matrix(s.o, "attn_output.weight", hidden, q_dim, staging, r * hidden_l, hidden_l);
             d.ffn_norm = upload_vector(s.ffn_norm, hidden, "ffn_norm.weight", true);
@@ -464,6 +472,7 @@ struct Session {
             a.q = L.q; a.k = L.k; a.v = L.v; a.o = L.o; a.gate = L.gate; a.up = L.up; a.down = L.down;
             a.attn_norm = L.attn_norm; a.q_norm = L.q_norm; a.k_norm = L.k_norm; a.attn_sub_norm = L.attn_sub_norm;
             a.ffn_norm = L.ffn_norm; a.ffn_sub_norm = L.ffn_sub_norm; a.k_cache = L.k_cache; a.v_cache = L.v_cache;
+            a.q_bias = L.q_bias; a.k_bias = L.k_bias; a.v_bias = L.v_bias;
         }
         StepShared sh;
         sh.hidden = hidden_b.as<float>(); sh.q = q_b.as<float>(); sh.k = k_b.as<float>(); sh.v = v_b.as<float>();
@@ -595,6 +604,7 @@ struct Session {
             RopeArgs r{};
             r.q = q_b.as<float>(); r.k = k_b.as<float>(); r.v = v_b.as<float>();
             r.q_norm = L.q_norm; r.k_norm = L.k_norm; r.rope = rope.as<float>();
+            r.q_bias = L.q_bias; r.k_bias = L.k_bias; r.v_bias = L.v_bias;
             r.k_cache = L.k_cache; r.v_cache = L.v_cache; r.position = d_position();
             r.n = n; r.heads = heads_l; r.kv_heads = kv_heads_l; r.dim = head_dim; r.max_context = uint32_t(max_context);
             r.eps = eps; r.neox = neox;

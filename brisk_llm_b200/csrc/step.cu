@@ -263,7 +263,11 @@ __device__ __forceinline__ void step_scores(const DecAttnParams& a, const uint32
         if (owner) {
             float kv[VPL];
 #pragma unroll
-            for (int k = 0; k < VPL; ++k) kv[k] = knew[NEOX ? lane + 32 * k : VPL * lane + k];
+            for (int k = 0; k < VPL; ++k) {
+                const uint32_t i = NEOX ? lane + 32 * k : VPL * lane + k;
+                kv[k] = knew[i];
+                if (a.k_bias != nullptr) kv[k] = __fadd_rn(kv[k], a.k_bias[size_t(kvh) * dim + i]);  // add_bias, src/model.cpp:1026-1030
+            }
             warp_head_norm_rope<VPL, NEOX>(kv, a.k_norm, rope, a.eps, knew);
             __syncwarp();
             const bool stores = head % group == 0;
@@ -276,6 +280,7 @@ __device__ __forceinline__ void step_scores(const DecAttnParams& a, const uint32
                     float v;
                     if constexpr (TAGGED) v = poll_pair(reinterpret_cast<const uint2*>(a.v) + size_t(kvh) * dim + i, tags.in, tags.error);
                     else v = __ldcg(a.v + size_t(kvh) * dim + i);
+                    if (a.v_bias != nullptr) v = __fadd_rn(v, a.v_bias[size_t(kvh) * dim + i]);
                     a.v_cache[row + i] = __float2half_rn(v);
                 }
             }
@@ -283,7 +288,11 @@ __device__ __forceinline__ void step_scores(const DecAttnParams& a, const uint32
         {
             float v[VPL];
 #pragma unroll
-            for (int k = 0; k < VPL; ++k) v[k] = qs[NEOX ? lane + 32 * k : VPL * lane + k];
+            for (int k = 0; k < VPL; ++k) {
+                const uint32_t i = NEOX ? lane + 32 * k : VPL * lane + k;
+                v[k] = qs[i];
+                if (a.q_bias != nullptr) v[k] = __fadd_rn(v[k], a.q_bias[size_t(head) * dim + i]);
+            }
             warp_head_norm_rope<VPL, NEOX>(v, a.q_norm, rope, a.eps, qs);
         }
         __syncwarp();
@@ -652,6 +661,7 @@ bool StepPlan::build(const std::vector<StepLayerArgs>& layers, const StepShared&
         fill(d.down, {{&L.down, sh.hidden}}, sh.gated, L.ffn_sub_norm, sh.ffn_size, EPI_ADD);
         DecAttnParams& a = d.attn;
         a.q = sh.q; a.k = sh.k; a.v = sh.v; a.q_norm = L.q_norm; a.k_norm = L.k_norm; a.rope = sh.rope;
+        a.q_bias = L.q_bias; a.k_bias = L.k_bias; a.v_bias = L.v_bias;
         a.k_cache = L.k_cache; a.v_cache = L.v_cache; a.scores = sh.scores; a.out = sh.attended; a.position = sh.position;
         a.heads = sh.heads; a.kv_heads = sh.kv_heads; a.dim = sh.dim; a.max_context = sh.max_context;
         a.eps = sh.eps; a.scale = sh.scale; a.neox = sh.neox; a.pdl = 0;

@@ -44,6 +44,9 @@ public:
             d.v = describe(s.value, file, p + "attn_v.weight");
             d.q_norm = s.query_norm.empty() ? nullptr : s.query_norm.data();
             d.k_norm = s.key_norm.empty() ? nullptr : s.key_norm.data();
+            d.q_bias = s.query_bias.empty() ? nullptr : s.query_bias.data();
+            d.k_bias = s.key_bias.empty() ? nullptr : s.key_bias.data();
+            d.v_bias = s.value_bias.empty() ? nullptr : s.value_bias.data();
             d.attn_sub_norm = s.attention_sub_norm.empty() ? nullptr : s.attention_sub_norm.data();
             d.o = describe(s.attention_output, file, p + "attn_output.weight");
             d.ffn_norm = s.feed_forward_norm.data();
@@ -121,8 +124,11 @@ private:
         }
         switch (m.format) {
             case WeightFormat::Q4_0: out.type = BRISK_TYPE_Q4_0; break;
+            case WeightFormat::Q4_1: out.type = BRISK_TYPE_Q4_1; break;
+            case WeightFormat::Q5_0: out.type = BRISK_TYPE_Q5_0; break;
             case WeightFormat::Q8_0: out.type = BRISK_TYPE_Q8_0; break;
             case WeightFormat::Q4_K: out.type = BRISK_TYPE_Q4_K; break;
+            case WeightFormat::Q5_K: out.type = BRISK_TYPE_Q5_K; break;
             case WeightFormat::Q6_K: out.type = BRISK_TYPE_Q6_K; break;
             case WeightFormat::TQ2_0: out.type = BRISK_TYPE_TQ2_0; break;
             default: throw std::runtime_error("cuda: tensor '" + std::string(name) + "' has a format the CUDA backend does not read (build the Model with repack = false)");

@@ -36,6 +36,7 @@ class ModelSpec:
     fmt_overrides: dict = field(default_factory=dict)  # role -> format, roles: q k v o gate up down embd output
     llama3_rope: tuple | None = None  # (factor, low_freq_factor, high_freq_factor, original_context)
     std: float = 0.02
+    qkv_bias: bool = False  # Qwen2-style projection biases (src/model.cpp:411-416)
 
     def fmt_of(self, role: str) -> int:
         return self.fmt_overrides.get(role, self.fmt)
@@ -126,6 +127,7 @@ class HostModel:
             L.gate, L.up = self._mat(p + "ffn_gate.weight"), self._mat(p + "ffn_up.weight")
             L.ffn_sub_norm = self._vec(p + "ffn_sub_norm.weight")
             L.down = self._mat(p + "ffn_down.weight")
+            L.q_bias, L.k_bias, L.v_bias = self._vec(p + "attn_q.bias"), self._vec(p + "attn_k.bias"), self._vec(p + "attn_v.bias")
         m = abi.Model()
         m.abi_version = abi.ABI_VERSION
         m.arch = abi.ARCH_BY_NAME[s.arch]
@@ -191,6 +193,9 @@ def generate(spec: ModelSpec, seed: int = 0, share_layers: bool = False) -> Host
         matrix(p + "attn_q.weight", "q", spec.q_dim, spec.hidden)
         matrix(p + "attn_k.weight", "k", spec.kv_dim, spec.hidden)
         matrix(p + "attn_v.weight", "v", spec.kv_dim, spec.hidden)
+        if spec.qkv_bias:
+            for nm, size in (("attn_q.bias", spec.q_dim), ("attn_k.bias", spec.kv_dim), ("attn_v.bias", spec.kv_dim)):
+                t[p + nm] = (F.F32, (1, size), (rng.standard_normal(size) * 0.05).astype(np.float32))
         if spec.arch == "qwen3":
             ones(p + "attn_q_norm.weight", spec.head_dim)
             ones(p + "attn_k_norm.weight", spec.head_dim)
@@ -215,7 +220,7 @@ def perturb_norms(model: HostModel, seed: int = 1) -> HostModel:
     rng = np.random.default_rng(seed)
     t = dict(model.tensors)
     for name, (fmt, shape, data) in model.tensors.items():
-        if data.dtype == np.float32 and fmt == F.F32 and shape[0] == 1:
+        if data.dtype == np.float32 and fmt == F.F32 and shape[0] == 1 and name.endswith("norm.weight"):
             t[name] = (fmt, shape, (1.0 + 0.1 * rng.standard_normal(shape[1])).astype(np.float32))
     return HostModel(model.spec, t, model.rope_factors)
 

@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define BRISK_CUDA_ABI_VERSION 1u
+#define BRISK_CUDA_ABI_VERSION 2u
 
 /* Tensor storage types, numbered as in ggml / the reference's TensorType (src/gguf.h:22-27).
  * Quantised data is passed exactly as it lies in a GGUF file: row after row of blocks
@@ -72,6 +72,11 @@ typedef struct brisk_cuda_layer {
     brisk_cuda_matrix gate, up; /* ffn x hidden                               */
     const float* ffn_sub_norm;  /* [ffn] or NULL (bitnet)                     */
     brisk_cuda_matrix down;     /* hidden x ffn                               */
+    /* Projection biases (Qwen2-style files, src/model.cpp:411-416): all three or none. Added to the q/k/v
+     * projections before the per-head norm and RoPE (src/model.cpp:1026-1030). */
+    const float* q_bias;        /* [heads*head_dim] or NULL                   */
+    const float* k_bias;        /* [kv*head_dim] or NULL                      */
+    const float* v_bias;        /* [kv*head_dim] or NULL                      */
 } brisk_cuda_layer;
 
 /* POD mirror of the brisk::ModelConfig fields the supported families use (src/model.h:36-62)

@@ -723,6 +723,11 @@ static void eval_batch(oracle_session* s, const int32_t* tokens, size_t n, int a
         mm(&L->v, s->normed, n, s->newv);
         for (size_t t = 0; t < n; ++t) { /* :1022-1046 */
             const float* rope = s->rope + t * D;
+            if (L->q_bias) { /* add_bias, :1026-1030 (src/model.cpp:117-119) */
+                for (size_t i = 0; i < Q; ++i) s->query[t * Q + i] += L->q_bias[i];
+                for (size_t i = 0; i < KV; ++i) s->newk[t * KV + i] += L->k_bias[i];
+                for (size_t i = 0; i < KV; ++i) s->newv[t * KV + i] += L->v_bias[i];
+            }
             for (size_t h = 0; h < c->head_count; ++h) {
                 float* q = s->query + t * Q + h * D;
                 if (L->q_norm) rms_norm(q, L->q_norm, eps, q, D);

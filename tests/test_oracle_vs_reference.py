@@ -45,6 +45,8 @@ def test_f16_head_bit_exact():
     ("llama", synth.tiny(synth.LLAMA_3_2_1B, hidden=512, heads=8, kv_heads=2, ffn=1024, context=512)),
     ("bitnet", synth.tiny(synth.BITNET_2B, hidden=512, heads=4, kv_heads=1, ffn=768, context=512)),
     ("mistral", synth.tiny(synth.MISTRAL_7B, hidden=256, heads=4, kv_heads=2, ffn=512, layers=3, context=512)),
+    # Qwen2-style projection biases on a llama-shaped model (src/model.cpp:411-416, :1026-1030)
+    ("biased", synth.tiny(synth.MISTRAL_7B, hidden=256, heads=4, kv_heads=2, ffn=512, context=512, qkv_bias=True, fmt=F.Q8_0)),
     # the formats the reference reads beyond the benchmark configurations, mixed the way stock downloads mix them
     ("mixed", synth.tiny(synth.QWEN3_0_6B, hidden=256, heads=4, kv_heads=2, ffn=512, context=512, tied=False, fmt=F.Q5_K,
                          fmt_overrides={"v": F.Q4_1, "down": F.Q5_0, "embd": F.Q4_1, "output": F.BF16})),
