@@ -278,7 +278,9 @@ def main():
         h2d, d2h = h2d + st["h2d_bytes"], d2h + st["d2h_bytes"]
         t1 = time.perf_counter()
         for _ in range(decode):
-            logits = sess.eval([int(np.argmax(logits))])
+            # the logits are read where the session leaves them (pinned host memory, valid until the next call -
+            # the span Engine::eval returns), as the reference's sampler reads them
+            logits = sess.eval([int(np.argmax(logits))], copy=False)
             st = sess.stats()
             h2d, d2h = h2d + st["h2d_bytes"], d2h + st["d2h_bytes"]
         t2 = time.perf_counter()

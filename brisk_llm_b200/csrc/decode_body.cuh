@@ -525,17 +525,21 @@ __device__ __forceinline__ void warp_store_new_kv(const DecAttnParams& a, uint32
 // ---- softmax + weighted sum: one CTA of NT threads per (query head, slice of the head's dimensions) --------------
 // The weighted sum is a serial chain per output dimension (position after position, as the CPU engine adds), so a head
 // cannot be split by positions - but it can be split by dimensions: each CTA recomputes the head's softmax (cheap) and
-// streams only its `slice_width` (16 or 32) columns of V. More CTAs then pull V through more SMs' memory pipes at
-// once, which is what bounds this latency-bound phase. Inside the CTA all warps share the softmax; the chain itself is
-// one warp's work, so that warp alone also feeds its V ring (cp.async groups are per thread: with producer = consumer
-// the tile loop needs no CTA barrier, only warp barriers).
-constexpr uint32_t kVTile = 64;   // positions of V per stage
-constexpr uint32_t kVStages = 8;  // stages in flight: contexts up to 512 positions are requested in one go
+// streams only its `slice_width` (16 or 32) columns of V, so that V comes in through many SMs' memory pipes at once.
+// Inside the CTA the work is arranged around the one thing that cannot be parallelised, the chain of f32 adds:
+//   all threads   softmax of the head's scores into shared memory
+//   all threads   per chunk of 512 positions: products p[pos] * v[pos][c] (independent) into shared memory, transposed
+//   one warp      lane c adds column c's products in position order: one 16-byte shared load and four dependent adds
+//                 per four positions - about the latency of the adds themselves
+// while the chain of one chunk runs, the other threads already request the next chunk's V.
+constexpr uint32_t kVChunk = 512;                 // positions per chunk
+constexpr uint32_t kProdStride = kVChunk + 4;     // floats per column of the product buffer (+4: columns fall into different banks)
 
 // The narrowest slice (16, then 32 columns) that still gives every (head, slice) task its own CTA.
 inline uint32_t dec_attn_slice_width(uint32_t heads, uint32_t dim, uint32_t ctas) { return heads * (dim / 16) > ctas ? 32u : 16u; }
+// probabilities [max_context] f32 | V chunk [kVChunk][width] f16 | products [width][kProdStride] f32
 inline size_t dec_attn_out_smem(uint32_t max_context, uint32_t slice_width) {
-    return ((size_t(max_context) * 4 + 15) & ~size_t(15)) + size_t(kVStages) * kVTile * slice_width * sizeof(__half);
+    return ((size_t(max_context) * 4 + 15) & ~size_t(15)) + size_t(kVChunk) * slice_width * sizeof(__half) + size_t(slice_width) * kProdStride * sizeof(float);
 }
 
 // With TaggedAttnIo the scores, the token's own V row (taken from the tagged v vector and rounded to f16 here, since
@@ -547,51 +551,40 @@ struct TaggedAttnIo {
     unsigned int* error;
 };
 
-// raw: dec_attn_out_smem() bytes (probabilities [max_context] | V ring kVStages x [kVTile][slice_width] f16);
-// redf / redd: NT/32 floats / doubles. V tiles that hold only earlier positions are requested before gate.wait();
-// the last tile holds the position written by this step and is requested after it.
+// raw: dec_attn_out_smem() bytes; redf / redd: NT/32 floats / doubles. V rows of earlier positions are requested
+// before gate.wait(); the row of the position written by this step only after it (or, tagged, taken from the v vector).
 template <int NT, class Gate, class Io = PlainIo>
 __device__ __forceinline__ void dec_attn_out_body(const DecAttnParams& a, const uint32_t h, const uint32_t slice, unsigned char* raw, float* redf,
                                                   double* redd, Gate&& gate, const Io& io = Io{}) {
     constexpr int kWarps = NT / 32;
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, dim = a.dim, width = a.slice_width;
-    const uint32_t visible = *a.position + 1;
+    const uint32_t visible = *a.position + 1, pos = visible - 1;
     const uint32_t kvh = h / (a.heads / a.kv_heads);
     float* ps = reinterpret_cast<float*>(raw);
     __half* vt = reinterpret_cast<__half*>(raw + ((size_t(a.max_context) * 4 + 15) & ~size_t(15)));
+    float* prod = reinterpret_cast<float*>(vt + size_t(kVChunk) * width);
     const float* s = a.scores + size_t(h) * a.max_context;
     const __half* vbase = a.v_cache + size_t(kvh) * a.max_context * dim + slice * width;
 
-    // V: the first kVStages tiles (all of V at contexts up to 512) are requested by every thread of the CTA at once,
-    // before anything else - cp.async, L2 -> shared, not through L1 - so that their latency hides behind the wait for
-    // the scores and the softmax. Longer contexts continue through the same stages as a ring that warp 0 refills.
-    const uint32_t tiles = (visible + kVTile - 1) / kVTile;
-    const uint32_t row_shift = width == 16 ? 1 : 2;       // 16-byte chunks of one position's slice: 2 or 4
-    const uint32_t chunks_per_tile = kVTile << row_shift;
-    const uint32_t in_cache = Io::kTagged ? visible - 1 : visible;  // positions whose V row is read from the cache
-    auto stage = [&](uint32_t tile_index, uint32_t first, uint32_t step) {  // by threads first, first + step, ...
-        if (tile_index * kVTile < in_cache) {
-            __half* dst = vt + size_t(tile_index % kVStages) * kVTile * width;
-            const __half* src = vbase + size_t(tile_index) * kVTile * dim;
-            const uint32_t rows = min(kVTile, in_cache - tile_index * kVTile);
-            for (uint32_t c = first; c < chunks_per_tile; c += step) {
-                const uint32_t row = c >> row_shift, col = (c & ((1u << row_shift) - 1)) * 8;
-                if (row < rows) {
-                    const uint32_t sm_addr = uint32_t(__cvta_generic_to_shared(dst + row * width + col));
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sm_addr), "l"(src + size_t(row) * dim + col) : "memory");
-                }
-            }
+    const uint32_t row_shift = width == 16 ? 1 : 2;  // 16-byte pieces of one position's slice: 2 or 4
+    // Requests rows [first, last) of V (absolute positions) into the chunk buffer; every thread takes a share.
+    auto request_rows = [&](uint32_t chunk, uint32_t first, uint32_t last) {
+        if (last <= first) return;
+        const uint32_t base = chunk * kVChunk;
+        const uint32_t pieces = (last - first) << row_shift;
+        for (uint32_t c = tid; c < pieces; c += NT) {
+            const uint32_t row = first + (c >> row_shift), col = (c & ((1u << row_shift) - 1)) * 8;
+            const uint32_t sm_addr = uint32_t(__cvta_generic_to_shared(vt + (row - base) * width + col));
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sm_addr), "l"(vbase + size_t(row) * dim + col) : "memory");
         }
     };
     unsigned long long* trace = (a.trace != nullptr && h == 0 && slice == 0) ? a.trace + 8 : nullptr;
     dec_stamp(trace, 0, 0);
-    const uint32_t bulk = min(tiles, kVStages);
-    // The position written by this step sits in the last tile: without tags that tile waits for the gate.
-    const uint32_t early = Io::kTagged ? bulk : min(bulk, tiles - 1);
-    for (uint32_t t = 0; t < early; ++t) stage(t, tid, NT);
+    const uint32_t chunks = (visible + kVChunk - 1) / kVChunk;
+    request_rows(0, 0, min(kVChunk, pos));  // every earlier position of the first chunk
     gate.wait();
     dec_stamp(trace, 0, 1);
-    for (uint32_t t = early; t < bulk; ++t) stage(t, tid, NT);
+    if (!Io::kTagged && pos < kVChunk) request_rows(0, pos, pos + 1);
     asm volatile("cp.async.commit_group;" ::: "memory");
 
     // softmax (src/kernels_f32.cpp:275-284): max, e = expf(s - max), f64 sum, p = e * float(1/sum). The row lives in
@@ -628,64 +621,54 @@ __device__ __forceinline__ void dec_attn_out_body(const DecAttnParams& a, const 
     const float inv = float(1.0 / total);
     dec_stamp(trace, 0, 4);
     for (uint32_t p = tid; p < visible; p += NT) ps[p] = __fmul_rn(ps[p], inv);
-    asm volatile("cp.async.wait_group 0;" ::: "memory");  // this thread's share of the first tiles
-    __syncthreads();  // the probabilities and the first kVStages tiles are complete for warp 0
-    if (warp != 0) return;
 
-    // weighted sum (src/kernels_f32.cpp:265-273): out[i] += p[pos] * v[pos][i], position after position. Lane c owns
-    // column c of the slice. Batches of 16 positions: a batch's 16 products are formed (independent loads, conversions
-    // and multiplies) while the previous batch's 16 adds - the serial chain - are still in flight.
-    const uint32_t col = lane < width ? lane : 0;
+    // weighted sum (src/kernels_f32.cpp:265-273): out[i] += p[pos] * v[pos][i], position after position.
     float acc = 0.0f;
-    for (uint32_t t = 0; t < tiles; ++t) {
-        if (t >= kVStages) {  // a tile warp 0 requested itself, kVStages iterations ago: one group per iteration since
-            asm volatile("cp.async.wait_group %0;" ::"n"(kVStages - 1) : "memory");
-            __syncwarp();
-        }
-        __half* tile_v = vt + size_t(t % kVStages) * kVTile * width;
+    for (uint32_t c = 0; c < chunks; ++c) {
+        const uint32_t base = c * kVChunk, rows = min(kVChunk, visible - base);
         if constexpr (Io::kTagged) {
-            if (t + 1 == tiles && lane < width) {  // the token's own row: column `lane` is read back by this same lane below
-                float v = poll_pair(reinterpret_cast<const uint2*>(a.v) + size_t(kvh) * dim + slice * width + lane, io.tag_v, io.error);
-                if (a.v_bias != nullptr) v = __fadd_rn(v, a.v_bias[size_t(kvh) * dim + slice * width + lane]);
-                tile_v[((visible - 1) % kVTile) * width + lane] = __float2half_rn(v);
+            if (c + 1 == chunks && tid < width) {  // the token's own row, from the tagged v vector
+                float v = poll_pair(reinterpret_cast<const uint2*>(a.v) + size_t(kvh) * dim + slice * width + tid, io.tag_v, io.error);
+                if (a.v_bias != nullptr) v = __fadd_rn(v, a.v_bias[size_t(kvh) * dim + slice * width + tid]);
+                vt[(pos - base) * width + tid] = __float2half_rn(v);
             }
         }
-        const __half* tv = tile_v + col;
-        const uint32_t rows = min(kVTile, visible - t * kVTile);
-        const float* pw = ps + t * kVTile;
-        auto products = [&](uint32_t j, float (&prod)[16]) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const float4 pv = *reinterpret_cast<const float4*>(pw + j + 4 * q);
-                prod[4 * q + 0] = __fmul_rn(pv.x, __half2float(tv[(j + 4 * q + 0) * width]));
-                prod[4 * q + 1] = __fmul_rn(pv.y, __half2float(tv[(j + 4 * q + 1) * width]));
-                prod[4 * q + 2] = __fmul_rn(pv.z, __half2float(tv[(j + 4 * q + 2) * width]));
-                prod[4 * q + 3] = __fmul_rn(pv.w, __half2float(tv[(j + 4 * q + 3) * width]));
-            }
-        };
-        uint32_t j = 0;
-        if (rows >= 16) {
-            float cur[16], nxt[16];
-            products(0, cur);
-            for (; j + 32 <= rows; j += 16) {
-                products(j + 16, nxt);
-#pragma unroll
-                for (int q = 0; q < 16; ++q) acc = __fadd_rn(acc, cur[q]);
-#pragma unroll
-                for (int q = 0; q < 16; ++q) cur[q] = nxt[q];
-            }
-#pragma unroll
-            for (int q = 0; q < 16; ++q) acc = __fadd_rn(acc, cur[q]);
-            j += 16;
+        asm volatile("cp.async.wait_group 0;" ::: "memory");  // this thread's share of the chunk's V
+        __syncthreads();  // V chunk c (and, the first time, the probabilities) complete; the previous chunk's chain is done
+        if (c == 0) dec_stamp(trace, 0, 6);
+        // products, transposed: consecutive threads take consecutive columns of one position
+        for (uint32_t e = tid; e < rows * width; e += NT) {
+            const uint32_t r = e / width, col = e % width;
+            prod[col * kProdStride + r] = __fmul_rn(ps[base + r], __half2float(vt[e]));
         }
-        for (; j < rows; ++j) acc = __fadd_rn(acc, __fmul_rn(pw[j], __half2float(tv[j * width])));
-        __syncwarp();  // every lane is done with tile t: its stage takes the tile kVStages further on
-        stage(t + kVStages, lane, 32);
-        asm volatile("cp.async.commit_group;" ::: "memory");
+        __syncthreads();  // products complete; the V buffer is free again
+        if (c + 1 < chunks) {
+            request_rows(c + 1, base + kVChunk, min(base + 2 * kVChunk, Io::kTagged ? pos : visible));
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+        if (warp == 0 && lane < width) {
+            const float* mine = prod + lane * kProdStride;
+            uint32_t j = 0;
+            if (rows >= 16) {  // the next 16 products are loaded while the current 16 adds - the dependent chain - run
+                float4 n0 = *reinterpret_cast<const float4*>(mine), n1 = *reinterpret_cast<const float4*>(mine + 4);
+                float4 n2 = *reinterpret_cast<const float4*>(mine + 8), n3 = *reinterpret_cast<const float4*>(mine + 12);
+                for (; j + 16 <= rows; j += 16) {
+                    const float4 p0 = n0, p1 = n1, p2 = n2, p3 = n3;
+                    if (j + 32 <= rows) {
+                        n0 = *reinterpret_cast<const float4*>(mine + j + 16); n1 = *reinterpret_cast<const float4*>(mine + j + 20);
+                        n2 = *reinterpret_cast<const float4*>(mine + j + 24); n3 = *reinterpret_cast<const float4*>(mine + j + 28);
+                    }
+                    acc = __fadd_rn(acc, p0.x); acc = __fadd_rn(acc, p0.y); acc = __fadd_rn(acc, p0.z); acc = __fadd_rn(acc, p0.w);
+                    acc = __fadd_rn(acc, p1.x); acc = __fadd_rn(acc, p1.y); acc = __fadd_rn(acc, p1.z); acc = __fadd_rn(acc, p1.w);
+                    acc = __fadd_rn(acc, p2.x); acc = __fadd_rn(acc, p2.y); acc = __fadd_rn(acc, p2.z); acc = __fadd_rn(acc, p2.w);
+                    acc = __fadd_rn(acc, p3.x); acc = __fadd_rn(acc, p3.y); acc = __fadd_rn(acc, p3.z); acc = __fadd_rn(acc, p3.w);
+                }
+            }
+            for (; j < rows; ++j) acc = __fadd_rn(acc, mine[j]);
+        }
     }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");  // only empty groups remain
     dec_stamp(trace, 0, 5);
-    if (lane < width) {
+    if (warp == 0 && lane < width) {
         if constexpr (Io::kTagged) st_pair(reinterpret_cast<uint2*>(a.out) + size_t(h) * dim + slice * width + lane, acc, io.tag_out);
         else a.out[size_t(h) * dim + slice * width + lane] = acc;
     }

@@ -227,7 +227,7 @@ def test_the_three_single_token_paths_agree_bit_for_bit(family, spec):
     results = {}
     for name, flags in (("persistent", 0), ("per_operation", abi.FLAG_NO_PERSISTENT), ("batched", abi.FLAG_NO_MEGAKERNEL)):
         with engine.CudaSession(m, flags=flags) as s:
-            uniform = len({f for n, (f, sh, d) in m.tensors.items() if n.startswith("blk.") and not n.endswith("norm.weight")}) == 1
+            uniform = len({f for n, (f, sh, d) in m.tensors.items() if n.startswith("blk.") and n.endswith(".weight") and not n.endswith("norm.weight")}) == 1
             persistent = name == "persistent" and uniform  # mixed weight types in the layers keep the per-operation kernels
             assert ("kernel on" in s.step_path()) == persistent, s.step_path()
             out = []
