@@ -178,6 +178,7 @@ struct Session {
     // then bracketed by CUDA events and the single-token step runs without its graph.
     enum Phase : int { PH_EMBED, PH_QKV, PH_ATTENTION, PH_ATTN_OUT, PH_GATE_UP, PH_DOWN, PH_HEAD, PH_EXCHANGE, PH_SAMPLE, PH_COUNT };
     bool profiling = false;
+    bool capturing = false;  // a stream capture is recording the step: events recorded now would never run
     double phase_ms[PH_COUNT] = {};
     uint64_t phase_calls[PH_COUNT] = {};
     std::vector<cudaEvent_t> event_pool;
@@ -195,7 +196,7 @@ struct Session {
     struct Scope {
         Session* s;
         Span span;
-        Scope(Session* session, int phase) : s(session->profiling ? session : nullptr) {
+        Scope(Session* session, int phase) : s(session->profiling && !session->capturing ? session : nullptr) {
             if (s) {
                 span = {phase, s->take_event(), s->take_event()};
                 cudaEventRecord(span.a, s->stream);
@@ -214,6 +215,8 @@ struct Session {
             if (cudaEventElapsedTime(&ms, sp.a, sp.b) == cudaSuccess) {
                 phase_ms[sp.phase] += ms;
                 phase_calls[sp.phase] += 1;
+            } else {
+                cudaGetLastError();  // not measured; leave no stale error for the next launch check
             }
         }
         spans.clear();
@@ -720,13 +723,16 @@ struct Session {
         const uint64_t before = launches;
         cudaGraph_t graph = nullptr;
         BK_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
+        capturing = true;
         try {
             forward_decode();
         } catch (...) {
+            capturing = false;
             cudaStreamEndCapture(stream, &graph);
             if (graph) cudaGraphDestroy(graph);
             throw;
         }
+        capturing = false;
         BK_CUDA(cudaStreamEndCapture(stream, &graph));
         step_graph_nodes = launches - before;
         launches = before;

@@ -211,19 +211,19 @@ def test_memory_preflight_refuses_what_cannot_fit(monkeypatch):
 
 @pytest.mark.parametrize("family,spec", [
     ("qwen3", synth.tiny(synth.QWEN3_0_6B, layers=3, vocab=1024, context=2048)),
-    ("llama", synth.tiny(synth.LLAMA_3_2_1B, layers=2, vocab=1024, context=1024)),
-    ("bitnet", synth.tiny(synth.BITNET_2B, layers=2, vocab=1024, context=1024)),
-    ("mistral", synth.tiny(synth.MISTRAL_7B, layers=2, vocab=1024, context=1024)),
-    ("biased", synth.tiny(synth.MISTRAL_7B, layers=2, vocab=1024, context=1024, hidden=1024, heads=8, kv_heads=2, ffn=2048, qkv_bias=True)),
+    ("llama", synth.tiny(synth.LLAMA_3_2_1B, layers=2, vocab=1024, context=2048)),
+    ("bitnet", synth.tiny(synth.BITNET_2B, layers=2, vocab=1024, context=2048)),
+    ("mistral", synth.tiny(synth.MISTRAL_7B, layers=2, vocab=1024, context=2048)),
+    ("biased", synth.tiny(synth.MISTRAL_7B, layers=2, vocab=1024, context=2048, hidden=1024, heads=8, kv_heads=2, ffn=2048, qkv_bias=True)),
 ])
 def test_the_three_single_token_paths_agree_bit_for_bit(family, spec):
     """A single-token step can run as one persistent kernel for all layers (the default where the model allows it), as
     one fused kernel per operation, or through the batched kernels. All three repeat the same float operations in the
     same order: their logits must be identical bits, at several context lengths (one that crosses the 512-position
-    chunk of the scores phase and the 64-position V tiles included)."""
+    chunks of the attention phases included)."""
     from brisk_llm_b200 import abi
     m = synth.perturb_norms(synth.generate(spec, seed=11))
-    toks = synth.random_tokens(spec, 700, seed=12)
+    toks = synth.random_tokens(spec, 1200, seed=12)
     results = {}
     for name, flags in (("persistent", 0), ("per_operation", abi.FLAG_NO_PERSISTENT), ("batched", abi.FLAG_NO_MEGAKERNEL)):
         with engine.CudaSession(m, flags=flags) as s:
@@ -232,7 +232,9 @@ def test_the_three_single_token_paths_agree_bit_for_bit(family, spec):
             assert ("kernel on" in s.step_path()) == persistent, s.step_path()
             out = []
             at = 0
-            for prompt in (1, 62, 448, 130):  # decode at positions 1.., 63.., 511.. (crossing 512) and 641..
+            # decode at positions 1.., 63.., 511.. (crossing 512), 641.. and 1123.. (past the 1024 positions up to which
+            # the persistent kernel runs attention as one operation)
+            for prompt in (1, 62, 448, 130, 480):
                 if prompt > 1:
                     s.eval(toks[at:at + prompt - 1])
                     at += prompt - 1
