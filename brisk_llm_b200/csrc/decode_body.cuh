@@ -638,10 +638,11 @@ __device__ __forceinline__ void dec_attn_out_body(const DecAttnParams& a, const 
         if (c == 0) dec_stamp(trace, 0, 6);
         // products, transposed: consecutive threads take consecutive columns of one position
         for (uint32_t e = tid; e < rows * width; e += NT) {
-            const uint32_t r = e / width, col = e % width;
+            const uint32_t r = e >> (row_shift + 3), col = e & (width - 1);  // width is 16 or 32
             prod[col * kProdStride + r] = __fmul_rn(ps[base + r], __half2float(vt[e]));
         }
         __syncthreads();  // products complete; the V buffer is free again
+        if (c == 0) dec_stamp(trace, 0, 7);
         if (c + 1 < chunks) {
             request_rows(c + 1, base + kVChunk, min(base + 2 * kVChunk, Io::kTagged ? pos : visible));
             asm volatile("cp.async.commit_group;" ::: "memory");

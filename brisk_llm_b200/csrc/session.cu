@@ -465,7 +465,7 @@ struct Session {
         const char* env = std::getenv("BRISK_CUDA_STEP");
         if (tp_size > 1) step_note = "off: tensor parallel steps exchange activations between the operations";
         else if (flags & (BRISK_CUDA_FLAG_NO_MEGAKERNEL | BRISK_CUDA_FLAG_NO_PERSISTENT)) step_note = "off: disabled by the session's flags";
-        else if (env != nullptr && std::atoi(env) == 0) step_note = "off: BRISK_CUDA_STEP=0";
+        else if (env != nullptr && std::strcmp(env, "0") == 0) step_note = "off: BRISK_CUDA_STEP=0";
         else if (trace.p != nullptr) step_note = "off: tracing the per-operation kernels";
         if (!step_note.empty()) return;
         std::vector<StepLayerArgs> args(n_layers);

@@ -603,6 +603,16 @@ bool StepPlan::build(const std::vector<StepLayerArgs>& layers, const StepShared&
         why_not = "head size is not 64 or 128";
         return false;
     }
+    // Measured on B200 (decode tok/s, persistent vs one kernel per operation): 0.6B-class Q4_0 (rows up to 3072 values)
+    // 1282 vs 1135; 2B-class TQ2_0 (up to 6912) 664 vs 698; 7B-class Q4_0 (up to 14336, context 8192) 177 vs 198. Every
+    // CTA re-reads the whole activation row of an operation, as tagged pairs twice the bytes: beyond a few thousand values
+    // that traffic outweighs the saved launches. BRISK_CUDA_STEP=force overrides (tests use it to cover the wide variants).
+    const uint32_t widest_row = std::max(std::max(sh.hidden_size, sh.heads * sh.dim), sh.ffn_size);
+    const char* force = std::getenv("BRISK_CUDA_STEP");
+    if (widest_row > 4096 && !(force != nullptr && std::strcmp(force, "force") == 0)) {
+        why_not = "activation rows wider than 4096 values (the per-operation kernels are faster there)";
+        return false;
+    }
     const uint32_t group = sh.heads / sh.kv_heads;
     if (group > kMaxGroup) {
         why_not = "more than 8 query heads per K/V head";

@@ -216,12 +216,14 @@ def test_memory_preflight_refuses_what_cannot_fit(monkeypatch):
     ("mistral", synth.tiny(synth.MISTRAL_7B, layers=2, vocab=1024, context=2048)),
     ("biased", synth.tiny(synth.MISTRAL_7B, layers=2, vocab=1024, context=2048, hidden=1024, heads=8, kv_heads=2, ffn=2048, qkv_bias=True)),
 ])
-def test_the_three_single_token_paths_agree_bit_for_bit(family, spec):
+def test_the_three_single_token_paths_agree_bit_for_bit(family, spec, monkeypatch):
     """A single-token step can run as one persistent kernel for all layers (the default where the model allows it), as
     one fused kernel per operation, or through the batched kernels. All three repeat the same float operations in the
     same order: their logits must be identical bits, at several context lengths (one that crosses the 512-position
     chunks of the attention phases included)."""
     from brisk_llm_b200 import abi
+    # the persistent kernel is off by default for models with wide rows (slower there); force it, to test its variants
+    monkeypatch.setenv("BRISK_CUDA_STEP", "force")
     m = synth.perturb_norms(synth.generate(spec, seed=11))
     toks = synth.random_tokens(spec, 1200, seed=12)
     results = {}
@@ -256,3 +258,13 @@ def test_the_three_single_token_paths_agree_bit_for_bit(family, spec):
                 assert np.array_equal(a, b), (other, float(np.abs(a - b).max()))
             else:
                 assert np.abs(a - b).max() <= 1e-5, (other, float(np.abs(a - b).max()))
+
+
+def test_default_choice_of_the_single_token_path():
+    """Where the persistent kernel is measured to be slower (rows wider than 4096 values) or does not apply (layer
+    matrices of several types), sessions use one kernel per operation by default; step_path() says which and why."""
+    for spec, expect in ((synth.tiny(synth.QWEN3_0_6B, layers=1, vocab=512), "kernel on: tagged exchange"),
+                         (synth.tiny(synth.MISTRAL_7B, layers=1, vocab=512), "off: activation rows wider than 4096"),
+                         (synth.tiny(synth.LLAMA_3_2_1B, layers=1, vocab=512), "off: ")):
+        with engine.CudaSession(synth.generate(spec, seed=1)) as s:
+            assert expect in s.step_path(), s.step_path()
