@@ -108,3 +108,26 @@ def test_device_memory_estimate_needs_no_gpu():
     assert half["cache"] * 2 == e["cache"] and half["scratch"] < e["scratch"]
     tp2 = engine.estimate_memory(m, tp_size=2)
     assert tp2["cache"] * 2 == e["cache"] and tp2["weights"] < e["weights"]
+
+
+def test_ctypes_mirror_has_the_layout_of_the_c_header(tmp_path):
+    """The Python structs are written by hand; a C compiler says what include/brisk_cuda.h really lays out."""
+    import subprocess
+    names = {"brisk_cuda_matrix": abi.Matrix, "brisk_cuda_layer": abi.Layer, "brisk_cuda_model": abi.Model,
+             "brisk_cuda_options": abi.Options, "brisk_cuda_stats": abi.Stats, "brisk_cuda_memory": abi.Memory}
+    src = tmp_path / "sizes.c"
+    lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "brisk_cuda.h"', 'int main(void) {']
+    for n in names:
+        lines.append(f'    printf("{n} %zu\\n", sizeof({n}));')
+    lines += ['    printf("layer.q_bias %zu\\n", offsetof(brisk_cuda_layer, q_bias));',
+              '    printf("model.layers %zu\\n", offsetof(brisk_cuda_model, layers));',
+              '    printf("abi %u\\n", (unsigned)BRISK_CUDA_ABI_VERSION);', '    return 0;', '}']
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "sizes"
+    subprocess.run(["gcc", "-I", os.path.join(H.ROOT, "include"), str(src), "-o", str(exe)], check=True)
+    out = dict(l.rsplit(" ", 1) for l in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.strip().split("\n"))
+    for n, cls in names.items():
+        assert int(out[n]) == C.sizeof(cls), n
+    assert int(out["layer.q_bias"]) == abi.Layer.q_bias.offset
+    assert int(out["model.layers"]) == abi.Model.layers.offset
+    assert int(out["abi"]) == abi.ABI_VERSION
