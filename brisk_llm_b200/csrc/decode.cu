@@ -82,7 +82,7 @@ void launch_dec_one(DecMatParams& p, uint32_t sms, cudaStream_t s) {
     // Ring depth: as deep as keeps the weights in flight per lane (matrices x rows x depth units of 16 bytes) at 8 or
     // fewer, so that they stay in registers; one iteration ahead is enough when a warp has only a few iterations.
     const uint32_t iters = ((groups + grid * kDecWarps - 1) / (grid * kDecWarps)) * ((p.m[0].units + 31) / 32);
-    constexpr int kRegsPerIter = (PAIR ? 2 : 1) * RW * int(sizeof(typename F::W) / 4);  // registers one iteration's weights take
+    constexpr int kRegsPerIter = (PAIR ? 2 : 1) * RW * F::kRegs;  // registers one iteration's weights take
     constexpr int kDeep = kRegsPerIter * 4 <= 48 ? 4 : kRegsPerIter * 2 <= 48 ? 2 : 1;
     auto go = [&](auto kernel) {
         if (smem > 40 * 1024) BK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));

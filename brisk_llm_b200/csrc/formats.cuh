@@ -17,6 +17,7 @@ __device__ __forceinline__ int dp4a(uint32_t a, uint32_t b, int c) { return __dp
 // arithmetic instruction on a loaded value stalling the warp in between.
 
 struct FQ4_0 {
+    static constexpr int kRegs = 5;  // 32-bit registers one unit of weights occupies (W is padded to 16-byte alignment)
     static constexpr int kLanesPerTerm = 1;
     static constexpr bool kExact = true;
     struct W { uint4 q; __half d; };
@@ -50,6 +51,7 @@ __device__ __forceinline__ uint32_t fifth_bits(uint32_t n) { return (((n & 0xFu)
 
 // weight = q * d + m (src/quant.cpp:484-498): the offset meets the activation block's sum, scaled by the activation scale first.
 struct FQ4_1 {
+    static constexpr int kRegs = 5;  // 32-bit registers one unit of weights occupies (W is padded to 16-byte alignment)
     static constexpr int kLanesPerTerm = 1;
     static constexpr bool kExact = true;
     struct W { uint4 q; __half2 dm; };
@@ -77,6 +79,7 @@ struct FQ4_1 {
 
 // weight = (q - 16) * d with 5-bit q (src/quant.cpp:458-472): bit i of qh is the fifth bit of value i.
 struct FQ5_0 {
+    static constexpr int kRegs = 6;  // 32-bit registers one unit of weights occupies (W is padded to 16-byte alignment)
     static constexpr int kLanesPerTerm = 1;
     static constexpr bool kExact = true;
     struct W { uint4 q; uint32_t qh; __half d; };
@@ -102,6 +105,7 @@ struct FQ5_0 {
 };
 
 struct FQ8_0 {
+    static constexpr int kRegs = 5;  // 32-bit registers one unit of weights occupies (W is padded to 16-byte alignment)
     static constexpr int kLanesPerTerm = 2;
     static constexpr bool kExact = true;
     struct W { uint4 q; __half d; };
@@ -126,6 +130,7 @@ struct FQ8_0 {
 };
 
 struct FQ4_K {
+    static constexpr int kRegs = 9;  // 32-bit registers one unit of weights occupies (W is padded to 16-byte alignment)
     static constexpr int kLanesPerTerm = 8;
     static constexpr bool kExact = true;
     struct W { uint4 q; uint32_t sc0, sc1, mn0, mn1; __half2 dd; };
@@ -168,6 +173,7 @@ struct FQ4_K {
 
 // Q4_K's arithmetic with a fifth bit per weight (src/quant.cpp:523-547).
 struct FQ5_K {
+    static constexpr int kRegs = 10;  // 32-bit registers one unit of weights occupies (W is padded to 16-byte alignment)
     static constexpr int kLanesPerTerm = 8;
     static constexpr bool kExact = true;
     struct W { uint4 q; uint32_t qh, sc0, sc1, mn0, mn1; __half2 dd; };
@@ -204,6 +210,7 @@ struct FQ5_K {
 };
 
 struct FQ6_K {
+    static constexpr int kRegs = 17;  // 32-bit registers one unit of weights occupies (W is padded to 16-byte alignment)
     static constexpr int kLanesPerTerm = 4;
     static constexpr bool kExact = true;
     struct W { uint4 a, b, c; int sc[4]; __half d; };
@@ -264,6 +271,7 @@ struct FQ6_K {
 };
 
 struct FTQ2_0 {
+    static constexpr int kRegs = 5;  // 32-bit registers one unit of weights occupies (W is padded to 16-byte alignment)
     static constexpr int kLanesPerTerm = 4;
     static constexpr bool kExact = true;
     struct W { uint4 q; __half d; };
@@ -306,6 +314,7 @@ struct FTQ2_0 {
 
 // Unquantised weights against raw f32 activations (the reference's dot_f32 path for widened F16 tensors).
 struct FF16 {
+    static constexpr int kRegs = 4;  // 32-bit registers one unit of weights occupies (W is padded to 16-byte alignment)
     static constexpr int kLanesPerTerm = 1;
     static constexpr bool kExact = false;
     struct W { uint4 q; };
@@ -333,6 +342,7 @@ struct FF16 {
 };
 
 struct FF32 {
+    static constexpr int kRegs = 4;  // 32-bit registers one unit of weights occupies (W is padded to 16-byte alignment)
     static constexpr int kLanesPerTerm = 1;
     static constexpr bool kExact = false;
     struct W { float4 q; };

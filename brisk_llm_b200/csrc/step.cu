@@ -346,7 +346,7 @@ __global__ void __launch_bounds__(kStepThreads, 1) step_kernel(const StepParams 
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ double red[32];
     __shared__ float redf[kDecWarps];
-    constexpr int kWordsPerUnit = int(sizeof(typename F::W) / 4);
+    constexpr int kWordsPerUnit = F::kRegs;
     float* tile = reinterpret_cast<float*>(smem + P.tile_offset);
     const uint32_t cta = blockIdx.x, nctas = gridDim.x;
     // The layer's descriptor (pointers, shapes, row-group tables) is read many times on the way to the first weight
