@@ -57,10 +57,10 @@ WORKLOADS = {  # prompt tokens, decode steps, context
 }
 
 
-# DRAM bytes one decoded token moves, composed from ncu captures of each kernel of the step at context ~512
-# (dram__bytes_read + write per launch): four multiplies 1.83 + 2.40 + 1.22 + 3.58 MB and two attention kernels
-# 1.10 + 1.12 MB per layer, plus the output head at its algorithmic 87.5 MB (not captured separately).
-MEASURED_TRAFFIC_PER_TOKEN = {"qwen3-0.6b-q4_0": int(28 * (1.8304 + 2.3954 + 1.2183 + 3.5758 + 1.1003 + 1.1244) * 1e6 + 87_515_136)}
+# DRAM bytes one decoded token moves, from ncu captures of the two kernels that move them at context ~516
+# (dram__bytes_read + write per launch): the persistent step kernel 306.94 + 5.39 MB and the output head
+# 87.56 + 2.85 MB; the embedding and arg-max kernels move well under 1 MB.
+MEASURED_TRAFFIC_PER_TOKEN = {"qwen3-0.6b-q4_0": int((306.94 + 5.39 + 87.56 + 2.85) * 1e6)}
 
 
 def peaks():

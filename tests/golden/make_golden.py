@@ -26,12 +26,20 @@ FAMILIES = {
     "bitnet": synth.tiny(synth.BITNET_2B, hidden=512, heads=4, kv_heads=1, ffn=768, vocab=256),
     "mistral": synth.tiny(synth.MISTRAL_7B, hidden=256, heads=4, kv_heads=2, ffn=512, vocab=256),
 }
+# Beyond the benchmark configurations (written by `--more-families-only`, which leaves the files above untouched):
+# Qwen2-style projection biases, and the remaining weight formats mixed the way stock downloads mix them.
+MORE_FAMILIES = {
+    "biased": synth.tiny(synth.MISTRAL_7B, hidden=256, heads=4, kv_heads=2, ffn=512, vocab=256, qkv_bias=True, fmt=F.Q8_0),
+    "mixed": synth.tiny(synth.QWEN3_0_6B, hidden=256, heads=4, kv_heads=2, ffn=512, vocab=256, tied=False, fmt=F.Q5_K,
+                        fmt_overrides={"v": F.Q4_1, "down": F.Q5_0, "embd": F.Q4_1, "output": F.BF16}),
+}
 FORMATS = (F.Q4_0, F.Q8_0, F.Q4_K, F.Q6_K, F.TQ2_0)
 MORE_FORMATS = (F.Q4_1, F.Q5_0, F.Q5_K)  # formats the reference reads but the benchmark configurations do not use; in primitives_more.npz
 
 
 def golden_model(family):
-    return synth.perturb_norms(synth.generate(FAMILIES[family], seed=11), seed=12)
+    spec = FAMILIES[family] if family in FAMILIES else MORE_FAMILIES[family]
+    return synth.perturb_norms(synth.generate(spec, seed=11), seed=12)
 
 
 def model_digest(model):
@@ -98,7 +106,13 @@ def main():
     np.savez_compressed(os.path.join(HERE, "primitives.npz"), **out)
     more_formats()
 
-    for family, spec in FAMILIES.items():
+    family_vectors(r, FAMILIES)
+    # LookupDrafter known answers (tests/speculative_test.cpp:19-42)
+    print("golden written to", HERE)
+
+
+def family_vectors(r, families):
+    for family, spec in families.items():
         m = golden_model(family)
         path = f"/tmp/golden_{family}.gguf"
         gguf_io.write_gguf(m, path)
@@ -141,12 +155,12 @@ def main():
         os.remove(path)
         np.savez_compressed(os.path.join(HERE, f"model_{family}.npz"), **g)
         print(family, "ok", V)
-    # LookupDrafter known answers (tests/speculative_test.cpp:19-42)
-    print("golden written to", HERE)
 
 
 if __name__ == "__main__":
     if "--more-formats-only" in sys.argv:
         more_formats()
+    elif "--more-families-only" in sys.argv:
+        family_vectors(H.ref(), MORE_FAMILIES)
     else:
         main()

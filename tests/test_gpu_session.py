@@ -48,13 +48,13 @@ def greedy_agrees(got_ids, want_ids, want_logits):
     return len(want_ids)
 
 
-@pytest.mark.parametrize("family", list(mg.FAMILIES))
+@pytest.mark.parametrize("family", list(mg.FAMILIES) + list(mg.MORE_FAMILIES))
 def test_golden_from_the_reference(family):
     g = np.load(os.path.join(H.GOLDEN, f"model_{family}.npz"))
     m = mg.golden_model(family)
     assert mg.model_digest(m).encode() == g["digest"].tobytes()
     toks = g["tokens"]
-    ex = family != "bitnet"
+    ex = family not in ("bitnet", "mixed")  # unquantised heads (F16, BF16) sum in another order
     with engine.CudaSession(m) as s:
         close(s.eval(toks[:33]), g["prefill33"], ex)
         for i in range(4):

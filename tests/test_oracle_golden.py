@@ -81,7 +81,7 @@ def test_dequantize_and_multiply(fmt):
     assert np.all(np.abs(PRIM[f"matmul_{n}"] - ref) <= tol)
 
 
-@pytest.mark.parametrize("family", list(mg.FAMILIES))
+@pytest.mark.parametrize("family", list(mg.FAMILIES) + list(mg.MORE_FAMILIES))
 def test_model_golden(family):
     g = np.load(os.path.join(H.GOLDEN, f"model_{family}.npz"))
     m = mg.golden_model(family)
