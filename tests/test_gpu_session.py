@@ -268,3 +268,25 @@ def test_default_choice_of_the_single_token_path():
                          (synth.tiny(synth.LLAMA_3_2_1B, layers=1, vocab=512), "off: ")):
         with engine.CudaSession(synth.generate(spec, seed=1)) as s:
             assert expect in s.step_path(), s.step_path()
+
+
+@pytest.mark.parametrize("family,spec", [
+    ("qwen3", synth.tiny(synth.QWEN3_0_6B, layers=2, vocab=512, context=2048)),
+    ("mistral", synth.tiny(synth.MISTRAL_7B, layers=1, vocab=512, context=2048)),
+])
+def test_long_prompt_against_the_oracle(family, spec):
+    """A 1300-token prompt: three device batches, the last of which sees more than 1024 positions and takes the
+    16-token tiles of the batched attention; then decode steps at that context."""
+    m = synth.perturb_norms(synth.generate(spec, seed=21))
+    toks = synth.random_tokens(spec, 1310, seed=22)
+    o = H.OracleSession(m)
+    with engine.CudaSession(m) as s:
+        close(s.eval(toks[:1300]), o.eval(toks[:1300]))
+        # the residual stream of the prompt's last 20 tokens, bit for bit: the device's last batch holds 1300 - 2 * 512 = 276
+        # tokens, the oracle's (CPU chunks of 256) the last 1300 - 5 * 256 = 20
+        got = s.debug_buffer("hidden", 276 * spec.hidden).reshape(276, spec.hidden)[256:]
+        assert np.array_equal(got, o.debug_buffer("hidden", 20 * spec.hidden).reshape(20, spec.hidden))
+        for i in range(1300, 1304):
+            close(s.eval(toks[i:i + 1]), o.eval(toks[i:i + 1]))
+        close(s.eval_all(toks[1304:1310]), o.eval_all(toks[1304:1310]))
+    o.close()
