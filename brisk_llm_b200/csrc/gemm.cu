@@ -9,7 +9,8 @@
 // widened in registers (the low nibbles of a 4-byte word are exactly the MMA fragment for k = 4t..4t+3, the high
 // nibbles the fragment for k = 16+4t..), and its -8 offset is folded in as -8 * sum(x) per block.
 //
-// Tiling: CTA = 128 rows x 64 tokens, 8 warps of 32 x 32; weights, activations and their scales are staged through
+// Tiling: CTA = 128 rows x 64 tokens, 8 warps of 32 x 32 - or, for matrices with so few rows that such tiles would leave
+// half of the SMs idle, 64 rows x 64 tokens with warps of 16 x 32; weights, activations and their scales are staged through
 // shared memory with cp.async, two stages of 8 blocks (256 columns). Padding of 16 bytes per row keeps the fragment
 // reads bank-conflict free. The per-block rescale (5 ALU instructions per output and block) bounds the kernel, not the
 // tensor pipe: that is the price of integer-exact semantics.
@@ -18,9 +19,9 @@
 namespace bk {
 namespace {
 
-constexpr int GM = 128, GN = 64, KB = 8, GWARPS = 8;
+constexpr int GN = 64, KB = 8, GWARPS = 8;  // GM, the rows of a CTA tile, is 64 * MI (MI = 16-row MMA tiles per warp)
 
-template <int WBYTES>  // bytes of quants per block and row: 16 (Q4_0) or 32 (Q8_0)
+template <int WBYTES, int GM>  // bytes of quants per block and row: 16 (Q4_0) or 32 (Q8_0); rows of the CTA tile
 struct Stage {
     static constexpr int kARow = KB * WBYTES + 16;
     static constexpr int kBRow = KB * 32 + 16;
@@ -51,14 +52,15 @@ struct GemmParams {
     int epi;  // EPI_STORE or EPI_ADD
 };
 
-template <int WBYTES>
+template <int WBYTES, int MI>
 __global__ void __launch_bounds__(GWARPS * 32, 2) gemm_q8_kernel(const GemmParams p) {
-    using S = Stage<WBYTES>;
+    constexpr int GM = 64 * MI;
+    using S = Stage<WBYTES, GM>;
     extern __shared__ __align__(16) unsigned char smem[];
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t g = lane >> 2, t = lane & 3;
     const uint32_t row_base = blockIdx.x * GM, tok_base = blockIdx.y * GN;
-    const uint32_t wr = (warp & 3) * 32, wt = (warp >> 2) * 32;  // this warp's 32 x 32 corner inside the CTA tile
+    const uint32_t wr = (warp & 3) * (16 * MI), wt = (warp >> 2) * 32;  // this warp's (16 MI) x 32 corner inside the CTA tile
     const uint32_t nb = p.m.blocks;                              // 32-value blocks per row
     const uint32_t chunks = nb / KB;
 
@@ -94,9 +96,9 @@ __global__ void __launch_bounds__(GWARPS * 32, 2) gemm_q8_kernel(const GemmParam
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
-    float acc[2][4][4];
+    float acc[MI][4][4];
 #pragma unroll
-    for (int mi = 0; mi < 2; ++mi)
+    for (int mi = 0; mi < MI; ++mi)
 #pragma unroll
         for (int ni = 0; ni < 4; ++ni)
 #pragma unroll
@@ -119,10 +121,10 @@ __global__ void __launch_bounds__(GWARPS * 32, 2) gemm_q8_kernel(const GemmParam
         const int* bs = reinterpret_cast<const int*>(bq + S::kB + S::kBd);
 #pragma unroll
         for (int b = 0; b < KB; ++b) {
-            uint32_t a[2][4];
-            float dw[2][2];
+            uint32_t a[MI][4];
+            float dw[MI][2];
 #pragma unroll
-            for (int mi = 0; mi < 2; ++mi) {
+            for (int mi = 0; mi < MI; ++mi) {
                 const uint32_t r0 = wr + mi * 16 + g, r1 = r0 + 8;
                 if (WBYTES == 16) {
                     const uint32_t w0 = *reinterpret_cast<const uint32_t*>(aq + r0 * S::kARow + b * 16 + 4 * t);
@@ -149,7 +151,7 @@ __global__ void __launch_bounds__(GWARPS * 32, 2) gemm_q8_kernel(const GemmParam
                 const float dx0 = bd[c0 * KB + b], dx1 = bd[c1 * KB + b];
                 const int off0 = WBYTES == 16 ? 8 * bs[c0 * KB + b] : 0, off1 = WBYTES == 16 ? 8 * bs[c1 * KB + b] : 0;
 #pragma unroll
-                for (int mi = 0; mi < 2; ++mi) {
+                for (int mi = 0; mi < MI; ++mi) {
                     int c[4] = {0, 0, 0, 0};
                     mma_s8(c, a[mi][0], a[mi][1], a[mi][2], a[mi][3], b0, b1);
                     // (row g, col 2t) (row g, col 2t+1) (row g+8, col 2t) (row g+8, col 2t+1)
@@ -164,7 +166,7 @@ __global__ void __launch_bounds__(GWARPS * 32, 2) gemm_q8_kernel(const GemmParam
     }
 
 #pragma unroll
-    for (int mi = 0; mi < 2; ++mi) {
+    for (int mi = 0; mi < MI; ++mi) {
 #pragma unroll
         for (int ni = 0; ni < 4; ++ni) {
 #pragma unroll
@@ -188,29 +190,38 @@ void launch_gemm_k(const MatTarget& tg, const DevAct& act, uint32_t n, Epilogue 
 bool gemm_supports(int type, uint32_t cols) { return ((type == T_Q4_0 || type == T_Q8_0) && cols % (32 * KB) == 0) || gemm_k_supports(type); }
 
 // out = weights x activations for one target (EPI_STORE / EPI_ADD).
-static void launch_gemm_one(const MatTarget& tg, const DevAct& act, uint32_t n, Epilogue epi, cudaStream_t s) {
-    GemmParams p{tg.m, act, tg.out, tg.ldo, n, int(epi)};
-    const dim3 grid((tg.m.rows + GM - 1) / GM, (n + GN - 1) / GN);
-    if (tg.m.type == T_Q4_0) {
-        constexpr size_t smem = 2 * Stage<16>::kBytes;
-        static bool raised = false;
-        if (!raised) {
-            BK_CUDA(cudaFuncSetAttribute(gemm_q8_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-            BK_CUDA(cudaFuncSetAttribute(gemm_q8_kernel<16>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
-            raised = true;
-        }
-        gemm_q8_kernel<16><<<grid, GWARPS * 32, smem, s>>>(p);
-    } else {
-        constexpr size_t smem = 2 * Stage<32>::kBytes;
-        static bool raised = false;
-        if (!raised) {
-            BK_CUDA(cudaFuncSetAttribute(gemm_q8_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-            BK_CUDA(cudaFuncSetAttribute(gemm_q8_kernel<32>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
-            raised = true;
-        }
-        gemm_q8_kernel<32><<<grid, GWARPS * 32, smem, s>>>(p);
+template <int WBYTES, int MI>
+static void launch_gemm_tile(const GemmParams& p, cudaStream_t s) {
+    constexpr int GM = 64 * MI;
+    constexpr size_t smem = 2 * Stage<WBYTES, GM>::kBytes;
+    static bool raised = false;
+    if (!raised) {
+        BK_CUDA(cudaFuncSetAttribute(gemm_q8_kernel<WBYTES, MI>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        BK_CUDA(cudaFuncSetAttribute(gemm_q8_kernel<WBYTES, MI>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+        raised = true;
     }
+    const dim3 grid((p.m.rows + GM - 1) / GM, (p.n + GN - 1) / GN);
+    gemm_q8_kernel<WBYTES, MI><<<grid, GWARPS * 32, smem, s>>>(p);
     BK_CUDA(cudaGetLastError());
+}
+
+static void launch_gemm_one(const MatTarget& tg, const DevAct& act, uint32_t n, Epilogue epi, cudaStream_t s) {
+    const GemmParams p{tg.m, act, tg.out, tg.ldo, n, int(epi)};
+    static const int sms = [] {
+        int dev = 0, count = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev);
+        return count;
+    }();
+    // 128-row tiles unless they would leave SMs without a CTA: then 64-row tiles, twice as many CTAs
+    const uint32_t big_tiles = ((tg.m.rows + 127) / 128) * ((n + GN - 1) / GN);
+    const bool small = big_tiles < uint32_t(sms);
+    if (tg.m.type == T_Q4_0) {
+        if (small) launch_gemm_tile<16, 1>(p, s);
+        else launch_gemm_tile<16, 2>(p, s);
+    } else {
+        if (small) launch_gemm_tile<32, 1>(p, s);
+        else launch_gemm_tile<32, 2>(p, s);
+    }
 }
 
 bool launch_gemm(const MatTarget* targets, int count, const DevAct& act, uint32_t n, Epilogue epi, cudaStream_t s) {
