@@ -75,10 +75,10 @@ def test_two_rank_tensor_parallel_matches_the_oracle(tmp_path):
         logs = {f: open(tmp_path / f).read() for f in os.listdir(tmp_path) if f.endswith(".log")}
         pytest.fail(f"tensor-parallel workers did not finish: {logs} {str(e.stderr)[-2000:]}")
     logs = {f: open(tmp_path / f).read() for f in os.listdir(tmp_path) if f.endswith(".log")}
-    if r.returncode != 0:
-        out_dir = os.path.join(H.ROOT, "gpurun_out")
-        os.makedirs(out_dir, exist_ok=True)
-        with open(os.path.join(out_dir, "tp_test_failure.log"), "w") as f:
+    log_dir = os.environ.get("BRISK_TEST_LOG_DIR")
+    if r.returncode != 0 and log_dir:
+        os.makedirs(log_dir, exist_ok=True)
+        with open(os.path.join(log_dir, "tp_test_failure.log"), "w") as f:
             f.write(r.stdout + "\n---- stderr ----\n" + r.stderr + "\n---- rank logs ----\n" + repr(logs))
     assert r.returncode == 0, (logs, r.stdout[-1500:], r.stderr[-3000:])
     a, b = np.load(tmp_path / "logits0.npy"), np.load(tmp_path / "logits1.npy")
