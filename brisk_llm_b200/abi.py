@@ -8,12 +8,12 @@ from __future__ import annotations
 import ctypes as C
 import os
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG_DIR, "libbrisk_cuda.so")
 
-ARCH_QWEN3, ARCH_LLAMA, ARCH_BITNET = 0, 1, 2
-ARCH_BY_NAME = {"qwen3": ARCH_QWEN3, "llama": ARCH_LLAMA, "bitnet": ARCH_BITNET, "bitnet-b1.58": ARCH_BITNET}
+ARCH_QWEN3, ARCH_LLAMA, ARCH_BITNET, ARCH_GEMMA3 = 0, 1, 2, 3
+ARCH_BY_NAME = {"qwen3": ARCH_QWEN3, "llama": ARCH_LLAMA, "bitnet": ARCH_BITNET, "bitnet-b1.58": ARCH_BITNET, "gemma3": ARCH_GEMMA3}
 FLAG_NO_GRAPH, FLAG_NO_MEGAKERNEL, FLAG_NO_PERSISTENT = 1, 2, 4
 
 
@@ -28,7 +28,8 @@ _FP = C.POINTER(C.c_float)
 class Layer(C.Structure):
     _fields_ = [("attn_norm", _FP), ("q", Matrix), ("k", Matrix), ("v", Matrix), ("q_norm", _FP), ("k_norm", _FP),
                 ("attn_sub_norm", _FP), ("o", Matrix), ("ffn_norm", _FP), ("gate", Matrix), ("up", Matrix),
-                ("ffn_sub_norm", _FP), ("down", Matrix), ("q_bias", _FP), ("k_bias", _FP), ("v_bias", _FP)]
+                ("ffn_sub_norm", _FP), ("down", Matrix), ("q_bias", _FP), ("k_bias", _FP), ("v_bias", _FP),
+                ("attn_post_norm", _FP), ("ffn_post_norm", _FP), ("slides", C.c_int32), ("reserved", C.c_int32)]
 
 
 class Model(C.Structure):
@@ -37,7 +38,9 @@ class Model(C.Structure):
                 ("head_dim", C.c_uint32), ("ffn", C.c_uint32), ("context_length", C.c_uint32),
                 ("rope_base", C.c_float), ("rms_epsilon", C.c_float), ("rope_neox", C.c_int32),
                 ("rope_factor_count", C.c_uint32), ("rope_factors", _FP), ("token_embd", Matrix), ("output", Matrix),
-                ("output_norm", _FP), ("layers", C.POINTER(Layer))]
+                ("output_norm", _FP), ("layers", C.POINTER(Layer)),
+                ("rope_scale", C.c_float), ("rope_base_local", C.c_float), ("sliding_window", C.c_uint32),
+                ("embedding_scale", C.c_float), ("final_softcap", C.c_float), ("gelu", C.c_int32)]
 
 
 class Options(C.Structure):

@@ -16,7 +16,7 @@ from .synth import HostModel, ModelSpec
 
 ALIGN = 32
 _U32, _F32, _STR, _U64 = 4, 6, 8, 10
-ARCH_NAME = {"qwen3": "qwen3", "llama": "llama", "bitnet": "bitnet-b1.58"}
+ARCH_NAME = {"qwen3": "qwen3", "llama": "llama", "bitnet": "bitnet-b1.58", "gemma3": "gemma3"}
 
 
 def _s(b: bytes) -> bytes:
@@ -32,6 +32,9 @@ def write_gguf(model: HostModel, path: str) -> None:
           (f"{arch}.attention.key_length", _U32, s.head_dim), (f"{arch}.attention.value_length", _U32, s.head_dim),
           (f"{arch}.feed_forward_length", _U32, s.ffn), (f"{arch}.context_length", _U32, s.context),
           (f"{arch}.rope.freq_base", _F32, s.rope_base), (f"{arch}.attention.layer_norm_rms_epsilon", _F32, s.eps)]
+    if s.arch == "gemma3":  # src/model.cpp:170-175
+        kv += [(f"{arch}.attention.sliding_window", _U32, s.sliding_window), (f"{arch}.rope.freq_base_swa", _F32, s.rope_base_local),
+               (f"{arch}.rope.scaling.factor", _F32, s.rope_scaling_factor), (f"{arch}.final_logit_softcapping", _F32, s.final_softcap)]
     tensors = dict(model.tensors)
     if model.rope_factors is not None:
         tensors["rope_freqs.weight"] = (F.F32, (1, len(model.rope_factors)), model.rope_factors)
@@ -108,9 +111,9 @@ def read_gguf(path: str) -> HostModel:
     align = meta.get("general.alignment", ALIGN)
     base = (r.p + align - 1) // align * align
     arch = meta["general.architecture"]
-    fam = {"qwen3": "qwen3", "llama": "llama", "bitnet": "bitnet", "bitnet-b1.58": "bitnet"}.get(arch)
+    fam = {"qwen3": "qwen3", "llama": "llama", "bitnet": "bitnet", "bitnet-b1.58": "bitnet", "gemma3": "gemma3"}.get(arch)
     if fam is None:
-        raise ValueError(f"gguf: architecture '{arch}' is not one this backend runs (qwen3, llama, bitnet)")
+        raise ValueError(f"gguf: architecture '{arch}' is not one this backend runs (qwen3, llama, bitnet, gemma3)")
     g = lambda k, d=None: meta.get(f"{arch}.{k}", d)
     tensors, rope = {}, None
     for name, dims, typ, off in infos:
@@ -133,4 +136,8 @@ def read_gguf(path: str) -> HostModel:
                      g("attention.key_length", hidden // heads), g("feed_forward_length"), emb[1][0], g("context_length"),
                      g("rope.freq_base"), g("attention.layer_norm_rms_epsilon"), "output.weight" not in tensors,
                      tensors["blk.0.attn_q.weight"][0])
+    if fam == "gemma3":
+        from dataclasses import replace
+        spec = replace(spec, sliding_window=g("attention.sliding_window", 0), rope_base_local=g("rope.freq_base_swa", 10000.0),
+                       rope_scaling_factor=g("rope.scaling.factor", 1.0), final_softcap=g("final_logit_softcapping", 0.0))
     return HostModel(spec, tensors, rope)

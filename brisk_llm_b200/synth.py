@@ -20,7 +20,7 @@ from . import abi, formats as F
 @dataclass(frozen=True)
 class ModelSpec:
     name: str
-    arch: str  # "qwen3" | "llama" | "bitnet"
+    arch: str  # "qwen3" | "llama" | "bitnet" | "gemma3"
     layers: int
     hidden: int
     heads: int
@@ -37,6 +37,15 @@ class ModelSpec:
     llama3_rope: tuple | None = None  # (factor, low_freq_factor, high_freq_factor, original_context)
     std: float = 0.02
     qkv_bias: bool = False  # Qwen2-style projection biases (src/model.cpp:411-416)
+    # Gemma 3 (src/model.cpp:169-176): window of the sliding layers (every layer whose index is not 5 mod 6), their RoPE
+    # base, the file's rope.scaling.factor for the global layers, the soft cap of the logits
+    sliding_window: int = 0
+    rope_base_local: float = 10000.0
+    rope_scaling_factor: float = 1.0
+    final_softcap: float = 0.0
+
+    def layer_slides(self, layer: int) -> bool:
+        return self.arch == "gemma3" and self.sliding_window != 0 and layer % 6 != 5
 
     def fmt_of(self, role: str) -> int:
         return self.fmt_overrides.get(role, self.fmt)
@@ -128,6 +137,8 @@ class HostModel:
             L.ffn_sub_norm = self._vec(p + "ffn_sub_norm.weight")
             L.down = self._mat(p + "ffn_down.weight")
             L.q_bias, L.k_bias, L.v_bias = self._vec(p + "attn_q.bias"), self._vec(p + "attn_k.bias"), self._vec(p + "attn_v.bias")
+            L.attn_post_norm, L.ffn_post_norm = self._vec(p + "post_attention_norm.weight"), self._vec(p + "post_ffw_norm.weight")
+            L.slides = 1 if s.layer_slides(i) else 0
         m = abi.Model()
         m.abi_version = abi.ABI_VERSION
         m.arch = abi.ARCH_BY_NAME[s.arch]
@@ -139,6 +150,11 @@ class HostModel:
         if self.rope_factors is not None:
             m.rope_factor_count = len(self.rope_factors)
             m.rope_factors = self.rope_factors.ctypes.data_as(C.POINTER(C.c_float))
+        if s.arch == "gemma3":
+            m.rope_scale = float(np.float32(1.0) / np.float32(s.rope_scaling_factor))
+            m.rope_base_local, m.sliding_window = s.rope_base_local, s.sliding_window
+            m.embedding_scale = float(np.sqrt(np.float32(s.hidden)))
+            m.final_softcap, m.gelu = s.final_softcap, 1
         m.token_embd = self._mat("token_embd.weight")
         if "output.weight" in self.tensors:
             m.output = self._mat("output.weight")
@@ -196,13 +212,16 @@ def generate(spec: ModelSpec, seed: int = 0, share_layers: bool = False) -> Host
         if spec.qkv_bias:
             for nm, size in (("attn_q.bias", spec.q_dim), ("attn_k.bias", spec.kv_dim), ("attn_v.bias", spec.kv_dim)):
                 t[p + nm] = (F.F32, (1, size), (rng.standard_normal(size) * 0.05).astype(np.float32))
-        if spec.arch == "qwen3":
+        if spec.arch in ("qwen3", "gemma3"):
             ones(p + "attn_q_norm.weight", spec.head_dim)
             ones(p + "attn_k_norm.weight", spec.head_dim)
         if spec.arch == "bitnet":
             ones(p + "attn_sub_norm.weight", spec.q_dim)
             ones(p + "ffn_sub_norm.weight", spec.ffn)
         matrix(p + "attn_output.weight", "o", spec.hidden, spec.q_dim)
+        if spec.arch == "gemma3":
+            ones(p + "post_attention_norm.weight", spec.hidden)
+            ones(p + "post_ffw_norm.weight", spec.hidden)
         ones(p + "ffn_norm.weight", spec.hidden)
         matrix(p + "ffn_gate.weight", "gate", spec.ffn, spec.hidden)
         matrix(p + "ffn_up.weight", "up", spec.ffn, spec.hidden)

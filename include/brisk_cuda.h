@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define BRISK_CUDA_ABI_VERSION 2u
+#define BRISK_CUDA_ABI_VERSION 3u
 
 /* Tensor storage types, numbered as in ggml / the reference's TensorType (src/gguf.h:22-27).
  * Quantised data is passed exactly as it lies in a GGUF file: row after row of blocks
@@ -44,7 +44,10 @@ enum brisk_cuda_type {
 enum brisk_cuda_arch {
     BRISK_ARCH_QWEN3 = 0,  /* per-head RMS norm on Q and K, SiLU-gated FFN, NeoX RoPE            */
     BRISK_ARCH_LLAMA = 1,  /* adjacent-pair RoPE, optional per-frequency divisors (rope_freqs)  */
-    BRISK_ARCH_BITNET = 2  /* sub-norms before o_proj and down_proj, squared-ReLU gate, NeoX    */
+    BRISK_ARCH_BITNET = 2, /* sub-norms before o_proj and down_proj, squared-ReLU gate, NeoX    */
+    BRISK_ARCH_GEMMA3 = 3  /* Q/K norms, norms after attention and the feed-forward, tanh-GELU gate,
+                              scaled embeddings, sliding-window layers with their own RoPE base,
+                              optional soft cap on the logits (src/model.h:24, :63-71)           */
 };
 
 /* A rows x cols weight matrix, `rows` outputs over `cols` inputs (brisk::Matrix, src/model.h:123-134).
@@ -77,6 +80,14 @@ typedef struct brisk_cuda_layer {
     const float* q_bias;        /* [heads*head_dim] or NULL                   */
     const float* k_bias;        /* [kv*head_dim] or NULL                      */
     const float* v_bias;        /* [kv*head_dim] or NULL                      */
+    /* Gemma: RMS norm of a projection's output before it is added to the residual stream
+     * (src/model.h:161-162, src/model.cpp:1116-1119, :1150-1153). NULL: plain residual add. */
+    const float* attn_post_norm; /* [hidden] or NULL                          */
+    const float* ffn_post_norm;  /* [hidden] or NULL                          */
+    /* 1: the layer attends only to the last `sliding_window` positions and rotates with the table of
+     * rope_base_local (ModelConfig::layer_slides, src/model.h:87-90; src/model.cpp:1084-1085). */
+    int32_t slides;
+    int32_t reserved;
 } brisk_cuda_layer;
 
 /* POD mirror of the brisk::ModelConfig fields the supported families use (src/model.h:36-62)
@@ -101,6 +112,14 @@ typedef struct brisk_cuda_model {
     brisk_cuda_matrix output;     /* vocab x hidden; data == NULL: tied to token_embd       */
     const float* output_norm;     /* [hidden]                                              */
     const brisk_cuda_layer* layers; /* [layer_count]                                        */
+    /* Gemma 3 (src/model.cpp:169-176, :286). Zero in every field: none of it applies. */
+    float rope_scale;        /* the position is multiplied by this before the angles are built (1 / rope.scaling.factor,
+                                src/model.cpp:173, :882); 0 means 1                                                 */
+    float rope_base_local;   /* RoPE base of the sliding layers (scale 1, no per-frequency divisors; src/model.cpp:894) */
+    uint32_t sliding_window; /* positions a sliding layer sees; 0: no layer slides                                   */
+    float embedding_scale;   /* embedding rows are multiplied by this (sqrt(hidden), src/model.cpp:899-901); 0 means 1 */
+    float final_softcap;     /* logits = c * tanh(logits / c) when non-zero (src/model.cpp:1206-1209)                */
+    int32_t gelu;            /* 1: gate with tanh-GELU instead of SiLU (src/model.cpp:1139-1140)                     */
 } brisk_cuda_model;
 
 typedef struct brisk_cuda_options {

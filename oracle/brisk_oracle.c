@@ -575,7 +575,7 @@ struct oracle_session {
     uint64_t max_context, position;
     uint16_t** keys;   /* per layer: [kv head][max_context][head_dim] f16 (src/model.cpp:982-991) */
     uint16_t** values;
-    float *hidden, *normed, *query, *newk, *newv, *attended, *projected, *gate, *up, *rope, *logits, *trace;
+    float *hidden, *normed, *query, *newk, *newv, *attended, *projected, *gate, *up, *rope, *rope_local, *logits, *trace;
 };
 
 #define MAXB 256 /* kMaxBatch, src/model.cpp:533 */
@@ -631,6 +631,7 @@ oracle_session* oracle_session_create(const brisk_cuda_model* model, uint64_t ma
     s->gate = (float*)malloc(MAXB * (size_t)model->ffn * 4);
     s->up = (float*)malloc(MAXB * (size_t)model->ffn * 4);
     s->rope = (float*)malloc(MAXB * (size_t)model->head_dim * 4);
+    s->rope_local = (float*)malloc(MAXB * (size_t)model->head_dim * 4);
     s->logits = (float*)malloc(64 * (size_t)model->vocab_size * 4);
     s->trace = (float*)calloc((size_t)model->layer_count * H, 4);
     return s;
@@ -643,7 +644,7 @@ void oracle_session_destroy(oracle_session* s) {
         free(s->values[l]);
     }
     free(s->keys); free(s->values); free(s->hidden); free(s->normed); free(s->query); free(s->newk); free(s->newv);
-    free(s->attended); free(s->projected); free(s->gate); free(s->up); free(s->rope); free(s->logits);
+    free(s->attended); free(s->projected); free(s->gate); free(s->up); free(s->rope); free(s->rope_local); free(s->logits);
     free(s->trace); free(s->layers); free(s);
 }
 
@@ -667,23 +668,25 @@ static void attention_range(void* p, int64_t i0, int64_t i1) {
         const size_t t = (size_t)idx / c->head_count, h = (size_t)idx % c->head_count;
         const size_t visible = s->position + t + 1, kvh = h / group;
         const float* q = s->query + t * Q + h * D;
-        for (size_t pp = 0; pp < visible; ++pp) {
+        /* A sliding layer sees only the last sliding_window positions (src/model.cpp:1084-1085). */
+        const size_t start = s->layers[l].slides && visible > c->sliding_window ? visible - c->sliding_window : 0;
+        for (size_t pp = start; pp < visible; ++pp) {
             const uint16_t* kr = s->keys[l] + (kvh * s->max_context + pp) * D;
             for (size_t i = 0; i < D; ++i) key[i] = oracle_half_to_float(kr[i]);
             sc[pp] = dot_f32(q, key, D) * j->scale;
         }
-        float mx = sc[0];
-        for (size_t pp = 1; pp < visible; ++pp) mx = sc[pp] > mx ? sc[pp] : mx;
+        float mx = sc[start];
+        for (size_t pp = start + 1; pp < visible; ++pp) mx = sc[pp] > mx ? sc[pp] : mx;
         double sum = 0.0;
-        for (size_t pp = 0; pp < visible; ++pp) {
+        for (size_t pp = start; pp < visible; ++pp) {
             sc[pp] = expf(sc[pp] - mx);
             sum += sc[pp];
         }
         const float inv = (float)(1.0 / sum);
-        for (size_t pp = 0; pp < visible; ++pp) sc[pp] *= inv;
+        for (size_t pp = start; pp < visible; ++pp) sc[pp] *= inv;
         float* out = s->attended + t * Q + h * D;
         for (size_t i = 0; i < D; ++i) out[i] = 0.0f;
-        for (size_t pp = 0; pp < visible; ++pp) {
+        for (size_t pp = start; pp < visible; ++pp) {
             const uint16_t* vr = s->values[l] + (kvh * s->max_context + pp) * D;
             const float wgt = sc[pp];
             for (size_t i = 0; i < D; ++i) out[i] += wgt * oracle_half_to_float(vr[i]);
@@ -692,7 +695,7 @@ static void attention_range(void* p, int64_t i0, int64_t i1) {
     free(sc);
 }
 
-/* Session::eval_batch, src/model.cpp:867-1212, for the qwen3 / llama / bitnet layer shapes. */
+/* Session::eval_batch, src/model.cpp:867-1212, for the qwen3 / llama / bitnet / gemma3 layer shapes. */
 static void eval_batch(oracle_session* s, const int32_t* tokens, size_t n, int all_logits) {
     const brisk_cuda_model* c = &s->m;
     const size_t H = c->hidden, D = c->head_dim, Q = (size_t)c->head_count * D, KV = (size_t)c->kv_head_count * D, F = c->ffn;
@@ -702,8 +705,9 @@ static void eval_batch(oracle_session* s, const int32_t* tokens, size_t n, int a
 
     /* cos/sin by repeated multiplication from pos (src/model.cpp:880-892). */
     const float theta_scale = powf(c->rope_base, -2.0f / (float)D);
+    const float rope_scale = c->rope_scale != 0.0f ? c->rope_scale : 1.0f;
     for (size_t t = 0; t < n; ++t) {
-        float theta = (float)(s->position + t) * 1.0f;
+        float theta = (float)(s->position + t) * rope_scale;
         float* rope = s->rope + t * D;
         for (size_t i = 0; i < D / 2; ++i) {
             const float angle = c->rope_factor_count ? theta / c->rope_factors[i] : theta;
@@ -712,7 +716,23 @@ static void eval_batch(oracle_session* s, const int32_t* tokens, size_t n, int a
             theta *= theta_scale;
         }
     }
-    for (size_t t = 0; t < n; ++t) embedding_row(&c->token_embd, (size_t)tokens[t], s->hidden + t * H); /* :896-902 */
+    if (c->sliding_window != 0) { /* the sliding layers' table: their own base, scale 1, no divisors (:894) */
+        const float local_scale = powf(c->rope_base_local, -2.0f / (float)D);
+        for (size_t t = 0; t < n; ++t) {
+            float theta = (float)(s->position + t) * 1.0f;
+            float* rope = s->rope_local + t * D;
+            for (size_t i = 0; i < D / 2; ++i) {
+                rope[2 * i] = cosf(theta) * 1.0f;
+                rope[2 * i + 1] = sinf(theta) * 1.0f;
+                theta *= local_scale;
+            }
+        }
+    }
+    for (size_t t = 0; t < n; ++t) { /* :896-902 */
+        embedding_row(&c->token_embd, (size_t)tokens[t], s->hidden + t * H);
+        if (c->embedding_scale != 0.0f && c->embedding_scale != 1.0f)
+            for (size_t i = 0; i < H; ++i) s->hidden[t * H + i] *= c->embedding_scale;
+    }
 
     const float attn_scale = 1.0f / sqrtf((float)D); /* :978 */
     for (uint32_t l = 0; l < c->layer_count; ++l) {
@@ -722,7 +742,7 @@ static void eval_batch(oracle_session* s, const int32_t* tokens, size_t n, int a
         mm(&L->k, s->normed, n, s->newk);
         mm(&L->v, s->normed, n, s->newv);
         for (size_t t = 0; t < n; ++t) { /* :1022-1046 */
-            const float* rope = s->rope + t * D;
+            const float* rope = (L->slides && c->sliding_window != 0 ? s->rope_local : s->rope) + t * D; /* :1024 */
             if (L->q_bias) { /* add_bias, :1026-1030 (src/model.cpp:117-119) */
                 for (size_t i = 0; i < Q; ++i) s->query[t * Q + i] += L->q_bias[i];
                 for (size_t i = 0; i < KV; ++i) s->newk[t * KV + i] += L->k_bias[i];
@@ -755,7 +775,8 @@ static void eval_batch(oracle_session* s, const int32_t* tokens, size_t n, int a
         mm(&L->o, s->attended, n, s->projected); /* :1109 */
         for (size_t t = 0; t < n; ++t) {          /* :1111-1123 */
             float* h = s->hidden + t * H;
-            const float* p = s->projected + t * H;
+            float* p = s->projected + t * H;
+            if (L->attn_post_norm) rms_norm(p, L->attn_post_norm, eps, p, H); /* Gemma, :1116-1119 */
             for (size_t i = 0; i < H; ++i) h[i] += p[i];
             rms_norm(h, L->ffn_norm, eps, s->normed + t * H, H);
         }
@@ -769,6 +790,11 @@ static void eval_batch(oracle_session* s, const int32_t* tokens, size_t n, int a
                     const float r = fmaxf(g[i], 0.0f);
                     g[i] = r * r * u[i];
                 }
+            } else if (c->gelu) { /* gelu_mul_f32, src/kernels_f32.cpp:291-296 */
+                for (size_t i = 0; i < F; ++i) {
+                    const float x = g[i];
+                    g[i] = 0.5f * x * (1.0f + tanhf(0.7978845608f * (x + 0.044715f * x * x * x))) * u[i];
+                }
             } else {
                 for (size_t i = 0; i < F; ++i) g[i] = g[i] / (1.0f + expf(-g[i])) * u[i]; /* src/kernels_f32.cpp:287-289 */
             }
@@ -777,7 +803,8 @@ static void eval_batch(oracle_session* s, const int32_t* tokens, size_t n, int a
         mm(&L->down, s->gate, n, s->projected); /* :1150 */
         for (size_t t = 0; t < n; ++t) {         /* :1151-1162 */
             float* h = s->hidden + t * H;
-            const float* p = s->projected + t * H;
+            float* p = s->projected + t * H;
+            if (L->ffn_post_norm) rms_norm(p, L->ffn_post_norm, eps, p, H); /* Gemma, :1155-1158 */
             for (size_t i = 0; i < H; ++i) h[i] += p[i];
         }
         memcpy(s->trace + (size_t)l * H, s->hidden + (n - 1) * H, H * 4);
@@ -789,6 +816,10 @@ static void eval_batch(oracle_session* s, const int32_t* tokens, size_t n, int a
     } else { /* :1201-1205 */
         rms_norm(s->hidden + (n - 1) * H, c->output_norm, eps, s->normed, H);
         mm(head, s->normed, 1, s->logits);
+    }
+    if (c->final_softcap != 0.0f) { /* :1206-1209 */
+        const size_t count = (all_logits ? n : 1) * (size_t)c->vocab_size;
+        for (size_t i = 0; i < count; ++i) s->logits[i] = c->final_softcap * tanhf(s->logits[i] / c->final_softcap);
     }
     s->position += n;
 }

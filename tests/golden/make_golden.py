@@ -32,6 +32,9 @@ MORE_FAMILIES = {
     "biased": synth.tiny(synth.MISTRAL_7B, hidden=256, heads=4, kv_heads=2, ffn=512, vocab=256, qkv_bias=True, fmt=F.Q8_0),
     "mixed": synth.tiny(synth.QWEN3_0_6B, hidden=256, heads=4, kv_heads=2, ffn=512, vocab=256, tied=False, fmt=F.Q5_K,
                         fmt_overrides={"v": F.Q4_1, "down": F.Q5_0, "embd": F.Q4_1, "output": F.BF16}),
+    # Gemma 3 layers: six sliding layers (window 16) around one global layer, soft-capped logits
+    "gemma3": synth.tiny(synth.QWEN3_0_6B, arch="gemma3", layers=7, hidden=256, heads=4, kv_heads=2, ffn=512, vocab=256,
+                         sliding_window=16, rope_scaling_factor=8.0, final_softcap=30.0),
 }
 FORMATS = (F.Q4_0, F.Q8_0, F.Q4_K, F.Q6_K, F.TQ2_0)
 MORE_FORMATS = (F.Q4_1, F.Q5_0, F.Q5_K)  # formats the reference reads but the benchmark configurations do not use; in primitives_more.npz
@@ -162,5 +165,8 @@ if __name__ == "__main__":
         more_formats()
     elif "--more-families-only" in sys.argv:
         family_vectors(H.ref(), MORE_FAMILIES)
+    elif "--family" in sys.argv:  # one of MORE_FAMILIES, leaving every other file untouched
+        name = sys.argv[sys.argv.index("--family") + 1]
+        family_vectors(H.ref(), {name: MORE_FAMILIES[name]})
     else:
         main()

@@ -121,6 +121,8 @@ def test_ctypes_mirror_has_the_layout_of_the_c_header(tmp_path):
         lines.append(f'    printf("{n} %zu\\n", sizeof({n}));')
     lines += ['    printf("layer.q_bias %zu\\n", offsetof(brisk_cuda_layer, q_bias));',
               '    printf("model.layers %zu\\n", offsetof(brisk_cuda_model, layers));',
+              '    printf("layer.slides %zu\\n", offsetof(brisk_cuda_layer, slides));',
+              '    printf("model.gelu %zu\\n", offsetof(brisk_cuda_model, gelu));',
               '    printf("abi %u\\n", (unsigned)BRISK_CUDA_ABI_VERSION);', '    return 0;', '}']
     src.write_text("\n".join(lines))
     exe = tmp_path / "sizes"
@@ -130,4 +132,6 @@ def test_ctypes_mirror_has_the_layout_of_the_c_header(tmp_path):
         assert int(out[n]) == C.sizeof(cls), n
     assert int(out["layer.q_bias"]) == abi.Layer.q_bias.offset
     assert int(out["model.layers"]) == abi.Model.layers.offset
+    assert int(out["layer.slides"]) == abi.Layer.slides.offset
+    assert int(out["model.gelu"]) == abi.Model.gelu.offset
     assert int(out["abi"]) == abi.ABI_VERSION

@@ -50,6 +50,10 @@ def test_f16_head_bit_exact():
     # the formats the reference reads beyond the benchmark configurations, mixed the way stock downloads mix them
     ("mixed", synth.tiny(synth.QWEN3_0_6B, hidden=256, heads=4, kv_heads=2, ffn=512, context=512, tied=False, fmt=F.Q5_K,
                          fmt_overrides={"v": F.Q4_1, "down": F.Q5_0, "embd": F.Q4_1, "output": F.BF16})),
+    # Gemma 3: scaled embeddings, post-norms, tanh-GELU, layers 0-4 and 6 slide over 64 positions with their own RoPE base,
+    # layer 5 is global with a scaled position, soft-capped logits (src/model.cpp:169-176, :1084-1085, :1116-1119, :1206-1209)
+    ("gemma3", synth.tiny(synth.QWEN3_0_6B, arch="gemma3", layers=7, hidden=256, heads=4, kv_heads=2, ffn=512, context=512,
+                          sliding_window=64, rope_scaling_factor=8.0, final_softcap=30.0)),
 ])
 def test_session_bit_exact(family, spec):
     r = H.ref()
