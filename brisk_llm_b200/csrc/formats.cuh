@@ -371,5 +371,16 @@ __device__ __forceinline__ float relu2_mul(float g, float u) {
     const float r = fmaxf(g, 0.0f);  // src/model.cpp:1135-1138
     return __fmul_rn(__fmul_rn(r, r), u);
 }
+// tanhf through double precision: the correctly rounded value in all but a vanishing share of inputs. The CPU engine
+// calls the C library's tanhf, which may differ from it in the last bit, so results that pass through a tanh agree with
+// the CPU engine to rounding, not bit for bit.
+__device__ __forceinline__ float tanh_via_double(float z) { return float(tanh(double(z))); }
+__device__ __forceinline__ float gelu_mul(float x, float u) {
+    // 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))) * up in the scalar code's order of operations (gelu_mul_f32,
+    // src/kernels_f32.cpp:291-296)
+    const float cube = __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, x), x), x);
+    const float t = tanh_via_double(__fmul_rn(0.7978845608f, __fadd_rn(x, cube)));
+    return __fmul_rn(__fmul_rn(__fmul_rn(0.5f, x), __fadd_rn(1.0f, t)), u);
+}
 
 }  // namespace bk

@@ -63,8 +63,17 @@ void launch_matvec(const MatTarget* targets, int count, const DevAct& act, uint3
 // (the caller then uses launch_matvec).
 bool launch_gemm(const MatTarget* targets, int count, const DevAct& act, uint32_t n, Epilogue epi, cudaStream_t s);
 bool gemm_supports(int type, uint32_t cols);
-// gate[i] = silu(gate[i]) * up[i] (relu2: max(gate[i],0)^2 * up[i]) - the activation after separate gate and up GEMMs.
-void launch_gate_mul(float* gate, const float* up, size_t count, bool relu2, cudaStream_t s);
+// The activation after separate gate and up multiplies. mode 0: gate[i] = silu(gate[i]) * up[i]; 1: max(gate[i],0)^2 * up[i];
+// 2: tanh-GELU(gate[i]) * up[i] (gelu_mul_f32, src/kernels_f32.cpp:291-296).
+void launch_gate_mul(float* gate, const float* up, size_t count, int mode, cudaStream_t s);
+
+// ---- Gemma layer variants (gemma.cu) ------------------------------------------------------------
+// x[i] *= scale: the embedding scale (src/model.cpp:899-901).
+void launch_scale_rows(float* x, size_t count, float scale, cudaStream_t s);
+// hidden[t][:] += rms_norm(proj[t][:]) * weight, the norm as in src/model.cpp:87-97 (post-norms, :1116-1119, :1155-1158).
+void launch_post_norm_add(const float* proj, const float* weight, float* hidden, uint32_t n, uint32_t cols, float eps, cudaStream_t s);
+// logits[i] = cap * tanh(logits[i] / cap) (src/model.cpp:1206-1209).
+void launch_softcap(float* logits, size_t count, float cap, cudaStream_t s);
 
 // ---- per-token vector work (misc.cu) -----------------------------------------------------------
 // hidden[t][:] = dequantised row tokens[t] of the embedding matrix (Session::eval_batch's embedding_row).
@@ -99,6 +108,7 @@ struct AttnArgs {
     uint32_t n, heads, kv_heads, dim, max_context;
     uint32_t max_visible;  // host-side upper bound of position + n (sizes the grid)
     float scale;
+    uint32_t window = 0;   // sliding-window layer: a token attends to its last `window` positions only (0: to all)
 };
 size_t attn_scratch_floats(uint32_t n, uint32_t heads, uint32_t max_context);
 void launch_attention(const AttnArgs& a, cudaStream_t s);

@@ -237,16 +237,24 @@ __global__ void __launch_bounds__(128) attn_scores_kernel(const AttnArgs a) {
     __syncthreads();
     if (p >= last_visible) return;
     const uint4* kr = reinterpret_cast<const uint4*>(a.k_cache + (size_t(kvh) * a.max_context + p) * DIM);
-    float kf[DIM];
+    // The K row stays in registers: widened to f32 up to 128 values; a 256-wide row is kept as packed halves (128 registers)
+    // and widened sixteen values at a time where it is used.
+    constexpr bool kPacked = DIM > 128;
+    float kf[kPacked ? 1 : DIM];
+    uint4 kraw[kPacked ? DIM / 8 : 1];
 #pragma unroll
     for (int i = 0; i < DIM / 8; ++i) {
         const uint4 raw = kr[i];
-        const __half2* h = reinterpret_cast<const __half2*>(&raw);
+        if constexpr (kPacked) {
+            kraw[i] = raw;
+        } else {
+            const __half2* h = reinterpret_cast<const __half2*>(&raw);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float2 f = __half22float2(h[j]);
-            kf[8 * i + 2 * j] = f.x;
-            kf[8 * i + 2 * j + 1] = f.y;
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(h[j]);
+                kf[8 * i + 2 * j] = f.x;
+                kf[8 * i + 2 * j + 1] = f.y;
+            }
         }
     }
     for (uint32_t j = 0; j < tn; ++j) {
@@ -259,13 +267,30 @@ __global__ void __launch_bounds__(128) attn_scores_kernel(const AttnArgs a) {
             for (int l = 0; l < 16; ++l) lanes[l] = 0.0f;
 #pragma unroll
             for (int i = 0; i < DIM; i += 16) {
+                float kk[16];
+                if constexpr (kPacked) {
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const uint4 raw = kraw[i / 8 + u];
+                        const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+                        for (int x = 0; x < 4; ++x) {
+                            const float2 f = __half22float2(h[x]);
+                            kk[8 * u + 2 * x] = f.x;
+                            kk[8 * u + 2 * x + 1] = f.y;
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int x = 0; x < 16; ++x) kk[x] = kf[i + x];
+                }
 #pragma unroll
                 for (int l = 0; l < 4; ++l) {
                     const float4 q = q4[i / 4 + l];
-                    lanes[4 * l + 0] = __fadd_rn(lanes[4 * l + 0], __fmul_rn(q.x, kf[i + 4 * l + 0]));
-                    lanes[4 * l + 1] = __fadd_rn(lanes[4 * l + 1], __fmul_rn(q.y, kf[i + 4 * l + 1]));
-                    lanes[4 * l + 2] = __fadd_rn(lanes[4 * l + 2], __fmul_rn(q.z, kf[i + 4 * l + 2]));
-                    lanes[4 * l + 3] = __fadd_rn(lanes[4 * l + 3], __fmul_rn(q.w, kf[i + 4 * l + 3]));
+                    lanes[4 * l + 0] = __fadd_rn(lanes[4 * l + 0], __fmul_rn(q.x, kk[4 * l + 0]));
+                    lanes[4 * l + 1] = __fadd_rn(lanes[4 * l + 1], __fmul_rn(q.y, kk[4 * l + 1]));
+                    lanes[4 * l + 2] = __fadd_rn(lanes[4 * l + 2], __fmul_rn(q.z, kk[4 * l + 2]));
+                    lanes[4 * l + 3] = __fadd_rn(lanes[4 * l + 3], __fmul_rn(q.w, kk[4 * l + 3]));
                 }
             }
             float sum = 0.0f;
@@ -279,11 +304,13 @@ __global__ void __launch_bounds__(128) attn_scores_kernel(const AttnArgs a) {
 __global__ void __launch_bounds__(256) attn_softmax_kernel(const AttnArgs a) {
     const uint32_t h = blockIdx.x, t = blockIdx.y, tid = threadIdx.x;
     const uint32_t visible = *a.position + t + 1;
+    // a sliding-window layer normalises over the last `window` positions only (src/model.cpp:1084-1088)
+    const uint32_t start = a.window != 0 && visible > a.window ? visible - a.window : 0;
     float* s = a.scores + (size_t(t) * a.heads + h) * a.max_context;
     __shared__ float redf[8];
     __shared__ double redd[8];
     float mx = -INFINITY;
-    for (uint32_t p = tid; p < visible; p += 256) mx = fmaxf(mx, s[p]);
+    for (uint32_t p = start + tid; p < visible; p += 256) mx = fmaxf(mx, s[p]);
     mx = warp_max(mx);
     if ((tid & 31) == 0) redf[tid >> 5] = mx;
     __syncthreads();
@@ -291,7 +318,7 @@ __global__ void __launch_bounds__(256) attn_softmax_kernel(const AttnArgs a) {
 #pragma unroll
     for (int w = 1; w < 8; ++w) mx = fmaxf(mx, redf[w]);
     double part = 0.0;
-    for (uint32_t p = tid; p < visible; p += 256) {
+    for (uint32_t p = start + tid; p < visible; p += 256) {
         const float e = exact_expf(__fsub_rn(s[p], mx));
         s[p] = e;
         part += double(e);
@@ -303,10 +330,11 @@ __global__ void __launch_bounds__(256) attn_softmax_kernel(const AttnArgs a) {
 #pragma unroll
     for (int w = 0; w < 8; ++w) total += redd[w];
     const float inv = float(1.0 / total);
-    for (uint32_t p = tid; p < visible; p += 256) s[p] = __fmul_rn(s[p], inv);
+    for (uint32_t p = start + tid; p < visible; p += 256) s[p] = __fmul_rn(s[p], inv);
 }
 
-// grid (heads, token tiles), one thread per value of the head. V rows and the tile's probabilities are staged through
+// grid (heads x parts, token tiles), one thread per value of the head; a 256-wide head is summed as two independent
+// 128-wide parts (every output value is its own sum over the positions). V rows and the tile's probabilities are staged through
 // shared memory in chunks of 64 positions, so every cached row is read once per kTokTile tokens; each thread keeps one
 // accumulator per token and adds p * v position after position, as weighted_sum_f32 does.
 constexpr uint32_t kWChunk = 64;
@@ -314,29 +342,39 @@ constexpr uint32_t kWChunk = 64;
 template <uint32_t kTokTile>
 __global__ void __launch_bounds__(128) attn_weighted_kernel(const AttnArgs a) {
     extern __shared__ __align__(16) unsigned char wraw[];  // V chunk [kWChunk][dim] f16 | probabilities [kTokTile][kWChunk] f32
-    const uint32_t h = blockIdx.x, t0 = blockIdx.y * kTokTile, dim = a.dim, tid = threadIdx.x;
+    const uint32_t parts = (a.dim + 127) / 128, dim = a.dim / parts;  // dim: the 64 or 128 values this CTA sums
+    const uint32_t h = blockIdx.x / parts, doff = blockIdx.x % parts * dim, t0 = blockIdx.y * kTokTile, tid = threadIdx.x;
+    const uint32_t row_shift = dim == 128 ? 4 : 3;  // 16-byte pieces per staged row: dim / 8
     const uint32_t tn = min(kTokTile, a.n - t0);
     const uint32_t kvh = h / (a.heads / a.kv_heads);
     const uint32_t base_visible = *a.position + t0 + 1, last_visible = base_visible + tn - 1;
     __half* vs = reinterpret_cast<__half*>(wraw);
     float* ws = reinterpret_cast<float*>(wraw + size_t(kWChunk) * dim * sizeof(__half));
-    const __half* vbase = a.v_cache + size_t(kvh) * a.max_context * dim;
+    const __half* vbase = a.v_cache + size_t(kvh) * a.max_context * a.dim + doff;
     float acc[kTokTile];
 #pragma unroll
     for (int j = 0; j < int(kTokTile); ++j) acc[j] = 0.0f;
-    for (uint32_t c0 = 0; c0 < last_visible; c0 += kWChunk) {
+    // Sliding-window layer: token j sums positions [start_j, visible_j) with start_j = max(0, visible_j - window), in order
+    // (src/model.cpp:1085-1091). Chunks below the first token's start are skipped; chunks at or above the last token's start
+    // are seen in full by every token of the tile.
+    const uint32_t win = a.window;
+    const uint32_t start_first = win != 0 && base_visible > win ? base_visible - win : 0;
+    const uint32_t start_last = win != 0 && last_visible > win ? last_visible - win : 0;
+    for (uint32_t c0 = start_first / kWChunk * kWChunk; c0 < last_visible; c0 += kWChunk) {
         const uint32_t cn = min(kWChunk, last_visible - c0);
         __syncthreads();  // the previous chunk is fully consumed
         for (uint32_t i = tid; i < cn * dim / 8; i += 128) {
-            reinterpret_cast<uint4*>(vs)[i] = reinterpret_cast<const uint4*>(vbase + size_t(c0) * dim)[i];
+            const uint32_t row = i >> row_shift, piece = i & ((1u << row_shift) - 1);
+            reinterpret_cast<uint4*>(vs)[i] = *reinterpret_cast<const uint4*>(vbase + size_t(c0 + row) * a.dim + piece * 8);
         }
         for (uint32_t i = tid; i < tn * kWChunk; i += 128) {
             const uint32_t j = i / kWChunk, pp = c0 + i % kWChunk;
-            ws[i] = pp < base_visible + j ? a.scores[(size_t(t0 + j) * a.heads + h) * a.max_context + pp] : 0.0f;
+            const uint32_t vis = base_visible + j, st = win != 0 && vis > win ? vis - win : 0;
+            ws[i] = pp < vis && pp >= st ? a.scores[(size_t(t0 + j) * a.heads + h) * a.max_context + pp] : 0.0f;
         }
         __syncthreads();
         if (tid < dim) {
-            if (c0 + cn <= base_visible && tn == kTokTile && cn % 4 == 0) {
+            if (c0 + cn <= base_visible && c0 >= start_last && tn == kTokTile && cn % 4 == 0) {
                 // Every token of the tile sees the whole chunk (all chunks but the last one or two): no causal tests, and the
                 // probabilities of four positions come in one 16-byte read per token. Per token the products are still added
                 // in position order.
@@ -358,7 +396,8 @@ __global__ void __launch_bounds__(128) attn_weighted_kernel(const AttnArgs a) {
 #pragma unroll
                     for (int j = 0; j < int(kTokTile); ++j) {
                         // a position past token j's causal limit must not touch its sum at all (adding 0*v could turn -0 into +0)
-                        if (c0 + pp < base_visible + j && j < int(tn)) acc[j] = __fadd_rn(acc[j], __fmul_rn(ws[j * kWChunk + pp], v));
+                        const uint32_t vis = base_visible + j, st = win != 0 && vis > win ? vis - win : 0;
+                        if (c0 + pp < vis && c0 + pp >= st && j < int(tn)) acc[j] = __fadd_rn(acc[j], __fmul_rn(ws[j * kWChunk + pp], v));
                     }
                 }
             }
@@ -367,7 +406,7 @@ __global__ void __launch_bounds__(128) attn_weighted_kernel(const AttnArgs a) {
     if (tid < dim) {
 #pragma unroll
         for (int j = 0; j < int(kTokTile); ++j) {
-            if (j < int(tn)) a.out[size_t(t0 + j) * a.heads * dim + size_t(h) * dim + tid] = acc[j];
+            if (j < int(tn)) a.out[size_t(t0 + j) * a.heads * a.dim + size_t(h) * a.dim + doff + tid] = acc[j];
         }
     }
 }
@@ -475,7 +514,7 @@ size_t attn_scratch_floats(uint32_t n, uint32_t heads, uint32_t max_context) { r
 
 void launch_attention(const AttnArgs& a, cudaStream_t s) {
     const uint32_t group = a.heads / a.kv_heads;
-    if (a.dim % 16 != 0 || a.dim > 256 || group > kMaxGroup) throw CudaError("cuda: head size must be a multiple of 16 up to 256 and at most 16 query heads per K/V head");
+    if ((a.dim != 64 && a.dim != 128 && a.dim != 256) || group > kMaxGroup) throw CudaError("cuda: attention takes head sizes 64, 128 and 256 and at most 16 query heads per K/V head");
     const uint32_t tile = a.max_visible > kLongContext ? 16u : 8u;
     const uint32_t tiles = (a.n + tile - 1) / tile;
     const dim3 grid((a.max_visible + 127) / 128, a.kv_heads, tiles);
@@ -493,7 +532,8 @@ void launch_attention(const AttnArgs& a, cudaStream_t s) {
         if (tile == 16) BK_SCORES_T(G, 64, 16);                                 \
         else BK_SCORES_T(G, 64, 8);                                             \
     } else {                                                                    \
-        throw CudaError("cuda: attention takes head sizes 64 and 128");         \
+        if (tile == 16) BK_SCORES_T(G, 256, 16);                                \
+        else BK_SCORES_T(G, 256, 8);                                            \
     }
     switch (group) {
         case 1: BK_SCORES(1); break;
@@ -507,9 +547,10 @@ void launch_attention(const AttnArgs& a, cudaStream_t s) {
     BK_CUDA(cudaGetLastError());
     attn_softmax_kernel<<<dim3(a.heads, a.n), 256, 0, s>>>(a);
     BK_CUDA(cudaGetLastError());
-    const size_t smem_w = size_t(kWChunk) * a.dim * sizeof(__half) + size_t(tile) * kWChunk * sizeof(float);
-    if (tile == 16) attn_weighted_kernel<16><<<dim3(a.heads, tiles), 128, smem_w, s>>>(a);
-    else attn_weighted_kernel<8><<<dim3(a.heads, tiles), 128, smem_w, s>>>(a);
+    const uint32_t parts = (a.dim + 127) / 128;
+    const size_t smem_w = size_t(kWChunk) * (a.dim / parts) * sizeof(__half) + size_t(tile) * kWChunk * sizeof(float);
+    if (tile == 16) attn_weighted_kernel<16><<<dim3(a.heads * parts, tiles), 128, smem_w, s>>>(a);
+    else attn_weighted_kernel<8><<<dim3(a.heads * parts, tiles), 128, smem_w, s>>>(a);
     BK_CUDA(cudaGetLastError());
 }
 

@@ -86,6 +86,8 @@ struct Layer {
     DevMatrix q, k, v, o, gate, up, down;
     const float *attn_norm = nullptr, *q_norm = nullptr, *k_norm = nullptr, *attn_sub_norm = nullptr, *ffn_norm = nullptr, *ffn_sub_norm = nullptr;
     const float *q_bias = nullptr, *k_bias = nullptr, *v_bias = nullptr;  // this rank's rows
+    const float *attn_post_norm = nullptr, *ffn_post_norm = nullptr;      // Gemma: norm of a projection before the residual add
+    bool slides = false;                                                  // Gemma: sliding-window layer with the local RoPE table
     __half *k_cache = nullptr, *v_cache = nullptr;
 };
 
@@ -112,7 +114,7 @@ brisk_cuda_memory estimate(const brisk_cuda_model& m, const brisk_cuda_options& 
         e.weights += planes(L.o.type, hidden / tp, q_dim) + planes(L.gate.type, ffn / tp, hidden) + planes(L.up.type, ffn / tp, hidden);
         e.weights += planes(L.down.type, hidden / tp, ffn);
         e.weights += (2 * hidden + (L.q_norm ? dim : 0) + (L.k_norm ? dim : 0) + (L.attn_sub_norm ? q_dim : 0) + (L.ffn_sub_norm ? ffn : 0) +
-                      (L.q_bias ? (q_dim + 2 * kv_dim) / tp : 0)) * 4;
+                      (L.q_bias ? (q_dim + 2 * kv_dim) / tp : 0) + (L.attn_post_norm ? hidden : 0) + (L.ffn_post_norm ? hidden : 0)) * 4;
     }
     e.cache = uint64_t(m.layer_count) * 2 * (kv_dim / tp) * ctx * 2;
     const uint64_t widest = std::max(std::max(hidden, q_dim), ffn), batch = kMaxBatch;
@@ -121,6 +123,8 @@ brisk_cuda_memory estimate(const brisk_cuda_model& m, const brisk_cuda_options& 
     e.scratch += batch * (uint64_t(m.head_count) / tp) * ctx * 4;  // attention scores of one batch
     e.scratch += uint64_t(kMaxScored) * vocab * 4;                 // logits
     e.scratch += ctx * dim * 4 + (ctx + 1) * 4;                    // RoPE table, token history
+    if (m.sliding_window != 0) e.scratch += ctx * dim * 4;          // the sliding layers' RoPE table
+    if (m.layer_count != 0 && (m.layers[0].attn_post_norm || m.layers[0].ffn_post_norm)) e.scratch += batch * hidden * 4;  // projection before its norm
     if (tp > 1) e.scratch += batch * std::max<uint64_t>(widest, vocab * kMaxScored / batch + 1) * 4 * 2 + batch * std::max(q_dim, ffn) * 4;
     return e;
 }
@@ -144,6 +148,11 @@ struct Session {
     uint32_t heads_l = 0, kv_heads_l = 0, q_dim_l = 0, kv_dim_l = 0, ffn_l = 0, hidden_l = 0, vocab_l = 0;
     uint64_t max_context = 0;
     float eps = 0, rope_base = 0;
+    // Gemma 3 (src/model.cpp:169-176, :286): scaled embeddings, tanh-GELU gate, sliding window, soft cap of the logits.
+    // Such a model runs every step, single tokens too, through the batched kernels plus the few kernels of gemma.cu.
+    float embedding_scale = 1.0f, final_softcap = 0.0f;
+    uint32_t sliding_window = 0;
+    bool gelu = false, variant_layers = false;
     int arch = 0, neox = 1, device = 0;
     uint32_t sms = 148;
     uint32_t flags = 0;
@@ -156,7 +165,7 @@ struct Session {
     uint64_t weight_bytes = 0, kv_bytes = 0;
 
     // state and scratch
-    DevBuffer kv, rope, tokens_dev, scalars, hidden_b, q_b, k_b, v_b, attended_b, ffn_b, up_b, logits_b, tp_local, tp_gathered, full_b, actf, actq0, actd0, acts0, actqk,
+    DevBuffer kv, rope, rope_local, proj_b, tokens_dev, scalars, hidden_b, q_b, k_b, v_b, attended_b, ffn_b, up_b, logits_b, tp_local, tp_gathered, full_b, actf, actq0, actd0, acts0, actqk,
         actdk, actbs, partial, am_val, am_idx, history, logit_history, trace;
     DevActMut act;
     float* logits_host = nullptr;     // pinned [64][vocab]
@@ -301,10 +310,18 @@ struct Session {
         vocab = m.vocab_size; hidden = m.hidden; n_layers = m.layer_count; heads = m.head_count; kv_heads = m.kv_head_count;
         head_dim = m.head_dim; ffn = m.ffn; eps = m.rms_epsilon; rope_base = m.rope_base; arch = m.arch; neox = m.rope_neox;
         flags = opt.flags;
+        if (arch != BRISK_ARCH_QWEN3 && arch != BRISK_ARCH_LLAMA && arch != BRISK_ARCH_BITNET && arch != BRISK_ARCH_GEMMA3) {
+            throw CudaError("cuda: unknown architecture id in the model description");
+        }
+        embedding_scale = m.embedding_scale != 0.0f ? m.embedding_scale : 1.0f;
+        final_softcap = m.final_softcap;
+        sliding_window = m.sliding_window;
+        gelu = m.gelu != 0;
+        if (gelu && arch == BRISK_ARCH_BITNET) throw CudaError("cuda: the squared-ReLU gate and the GELU gate exclude each other");
         if (!vocab || !hidden || !n_layers || !heads || !kv_heads || !ffn || !m.context_length) throw CudaError("cuda: a model dimension is zero");
         if (heads % kv_heads != 0) throw CudaError("cuda: head_count is not a multiple of head_count_kv");
         if (heads / kv_heads > 16) throw CudaError("cuda: more than 16 query heads per key/value head is not supported");
-        if (head_dim == 0 || head_dim % 32 != 0 || head_dim > 128) throw CudaError("cuda: head size must be a multiple of 32 up to 128");
+        if (head_dim != 64 && head_dim != 128 && head_dim != 256) throw CudaError("cuda: head size must be 64, 128 or 256");
         if (m.rope_factor_count != 0 && m.rope_factor_count != head_dim / 2) throw CudaError("cuda: rope factor count must be head_dim / 2");
         q_dim = heads * head_dim;
         kv_dim = kv_heads * head_dim;
@@ -381,7 +398,13 @@ struct Session {
             if (d.gate.type != d.up.type) throw CudaError("cuda: ffn_gate and ffn_up must share one type");
             d.ffn_sub_norm = upload_vector(s.ffn_sub_norm, ffn, "ffn_sub_norm.weight", false);
             d.down = upload_matrix(s.down, "ffn_down.weight", hidden, ffn, staging, r * hidden_l, hidden_l);
+            d.attn_post_norm = upload_vector(s.attn_post_norm, hidden, "post_attention_norm.weight", false);
+            d.ffn_post_norm = upload_vector(s.ffn_post_norm, hidden, "post_ffw_norm.weight", false);
+            d.slides = s.slides != 0 && sliding_window != 0;
+            if (d.attn_post_norm || d.ffn_post_norm || d.slides) variant_layers = true;
         }
+        if (gelu || embedding_scale != 1.0f || final_softcap != 0.0f) variant_layers = true;
+        if (head_dim > 128) variant_layers = true;  // the fused single-token kernels take heads of 64 and 128
         BK_CUDA(cudaStreamSynchronize(stream));
         if (m.output.data == nullptr) {
             // A tied head is streamed once per token as the head; the embedding lookup reads one row of it.
@@ -399,22 +422,25 @@ struct Session {
 
         // RoPE table for every position, built like the reference builds it per batch (src/model.cpp:880-892):
         // theta starts at the position and is multiplied by base^(-2/dim) per pair, in f32, with the host's libm.
-        {
+        auto build_rope = [&](DevBuffer& dst, float base, float scale, bool factors) {
             std::vector<float> table(size_t(max_context) * head_dim);
-            const float theta_scale = std::pow(rope_base, -2.0f / static_cast<float>(head_dim));
+            const float theta_scale = std::pow(base, -2.0f / static_cast<float>(head_dim));
             for (uint64_t p = 0; p < max_context; ++p) {
-                float theta = static_cast<float>(p) * 1.0f;
+                float theta = static_cast<float>(p) * scale;
                 float* r = table.data() + p * head_dim;
                 for (uint32_t i = 0; i < head_dim / 2; ++i) {
-                    const float angle = m.rope_factor_count != 0 ? theta / m.rope_factors[i] : theta;
+                    const float angle = factors && m.rope_factor_count != 0 ? theta / m.rope_factors[i] : theta;
                     r[2 * i] = std::cos(angle) * 1.0f;
                     r[2 * i + 1] = std::sin(angle) * 1.0f;
                     theta *= theta_scale;
                 }
             }
-            rope.alloc(table.size() * sizeof(float));
-            BK_CUDA(cudaMemcpy(rope.p, table.data(), table.size() * sizeof(float), cudaMemcpyHostToDevice));
-        }
+            dst.alloc(table.size() * sizeof(float));
+            BK_CUDA(cudaMemcpy(dst.p, table.data(), table.size() * sizeof(float), cudaMemcpyHostToDevice));
+        };
+        build_rope(rope, rope_base, m.rope_scale != 0.0f ? m.rope_scale : 1.0f, true);
+        // The sliding layers rotate with their own base, an unscaled position and no per-frequency divisors (src/model.cpp:894).
+        if (sliding_window != 0) build_rope(rope_local, m.rope_base_local, 1.0f, false);
 
         const uint32_t widest = std::max(std::max(hidden, q_dim), ffn);
         tokens_dev.alloc((kMaxBatch + 4) * sizeof(int32_t));
@@ -428,6 +454,7 @@ struct Session {
         ffn_b.alloc(size_t(kMaxBatch) * ffn * 4);
         up_b.alloc(size_t(kMaxBatch) * ffn * 4);
         logits_b.alloc(size_t(kMaxScored) * vocab * 4);
+        if (variant_layers) proj_b.alloc(size_t(kMaxBatch) * hidden * 4);
         actf.alloc(size_t(kMaxBatch) * widest * 4);
         actq0.alloc(size_t(kMaxBatch) * widest);
         actd0.alloc(size_t(kMaxBatch) * (widest / 32) * 4);
@@ -464,6 +491,7 @@ struct Session {
     void plan_step() {
         const char* env = std::getenv("BRISK_CUDA_STEP");
         if (tp_size > 1) step_note = "off: tensor parallel steps exchange activations between the operations";
+        else if (variant_layers) step_note = "off: Gemma layer variants (post-norms, GELU, sliding window) and 256-wide heads run through the batched kernels";
         else if (flags & (BRISK_CUDA_FLAG_NO_MEGAKERNEL | BRISK_CUDA_FLAG_NO_PERSISTENT)) step_note = "off: disabled by the session's flags";
         else if (env != nullptr && std::strcmp(env, "0") == 0) step_note = "off: BRISK_CUDA_STEP=0";
         else if (trace.p != nullptr) step_note = "off: tracing the per-operation kernels";
@@ -561,9 +589,14 @@ struct Session {
     // position + n. single = true takes the fused single-token kernels (n == 1).
     void run_layers(uint32_t n, bool all_logits, uint32_t max_visible, bool single) {
         float* hid = hidden_b.as<float>();
+        if (variant_layers) single = false;
         {
             Scope sc(this, PH_EMBED);
             launch_embed(embd, tokens_dev.as<int32_t>(), n, hid, stream);
+            if (embedding_scale != 1.0f) {  // src/model.cpp:899-901
+                launch_scale_rows(hid, size_t(n) * hidden, embedding_scale, stream);
+                ++launches;
+            }
         }
         ++launches;
         const float attn_scale = 1.0f / std::sqrt(static_cast<float>(head_dim));
@@ -606,7 +639,7 @@ struct Session {
 
             RopeArgs r{};
             r.q = q_b.as<float>(); r.k = k_b.as<float>(); r.v = v_b.as<float>();
-            r.q_norm = L.q_norm; r.k_norm = L.k_norm; r.rope = rope.as<float>();
+            r.q_norm = L.q_norm; r.k_norm = L.k_norm; r.rope = L.slides ? rope_local.as<float>() : rope.as<float>();
             r.q_bias = L.q_bias; r.k_bias = L.k_bias; r.v_bias = L.v_bias;
             r.k_cache = L.k_cache; r.v_cache = L.v_cache; r.position = d_position();
             r.n = n; r.heads = heads_l; r.kv_heads = kv_heads_l; r.dim = head_dim; r.max_context = uint32_t(max_context);
@@ -615,7 +648,7 @@ struct Session {
             at.q = q_b.as<float>(); at.k_cache = L.k_cache; at.v_cache = L.v_cache; at.out = attended_b.as<float>();
             at.scores = partial.as<float>(); at.position = d_position();
             at.n = n; at.heads = heads_l; at.kv_heads = kv_heads_l; at.dim = head_dim; at.max_context = uint32_t(max_context);
-            at.max_visible = max_visible; at.scale = attn_scale;
+            at.max_visible = max_visible; at.scale = attn_scale; at.window = L.slides ? sliding_window : 0;
             {
                 Scope sc(this, PH_ATTENTION);
                 if (single) {
@@ -629,6 +662,12 @@ struct Session {
             }
 
             // attention output projection + residual
+            // A projection's output joins the residual stream directly, or (Gemma) after an RMS norm of its own
+            // (src/model.cpp:1116-1119, :1155-1158): then it is stored whole first.
+            auto post_norm_add = [&](const float* weight) {
+                launch_post_norm_add(proj_b.as<float>(), weight, hid, n, hidden, eps, stream);
+                ++launches;
+            };
             const float* attended = attended_b.as<float>();
             if (tp) {
                 exchange(attended_b.as<float>(), full_b.as<float>(), n, q_dim_l, false);
@@ -637,33 +676,51 @@ struct Session {
                     Scope sc(this, PH_ATTN_OUT);
                     apply({{L.o, tp_local.as<float>(), hidden_l}}, attended, q_dim, L.attn_sub_norm, q_dim, EPI_STORE);
                 }
-                exchange(tp_local.as<float>(), hid, n, hidden_l, true);
+                exchange(tp_local.as<float>(), L.attn_post_norm ? proj_b.as<float>() : hid, n, hidden_l, L.attn_post_norm == nullptr);
+                if (L.attn_post_norm) post_norm_add(L.attn_post_norm);
             } else {
                 Scope sc(this, PH_ATTN_OUT);
-                apply({{L.o, hid, hidden}}, attended, q_dim, L.attn_sub_norm, q_dim, EPI_ADD);
+                if (L.attn_post_norm) {
+                    apply({{L.o, proj_b.as<float>(), hidden}}, attended, q_dim, L.attn_sub_norm, q_dim, EPI_STORE);
+                    post_norm_add(L.attn_post_norm);
+                } else {
+                    apply({{L.o, hid, hidden}}, attended, q_dim, L.attn_sub_norm, q_dim, EPI_ADD);
+                }
             }
 
             // feed-forward + residual
             const Epilogue act_epi = arch == BRISK_ARCH_BITNET ? EPI_RELU2_MUL : EPI_SILU_MUL;
             const float* gated = ffn_b.as<float>();
-            if (tp) {
-                {
-                    Scope sc(this, PH_GATE_UP);
-                    apply({{L.gate, tp_local.as<float>(), ffn_l}, {L.up, nullptr, ffn_l}}, hid, hidden, L.ffn_norm, hidden, act_epi);
+            // gate and up into `dst` (row length ld): fused with the activation, or (GELU) two plain multiplies and an
+            // elementwise kernel (gelu_mul_f32, src/kernels_f32.cpp:291-296).
+            auto gate_up = [&](float* dst, uint32_t ld) {
+                Scope sc(this, PH_GATE_UP);
+                if (gelu) {
+                    apply({{L.gate, dst, ld}, {L.up, up_b.as<float>(), ld}}, hid, hidden, L.ffn_norm, hidden, EPI_STORE);
+                    launch_gate_mul(dst, up_b.as<float>(), size_t(n) * ld, 2, stream);
+                    ++launches;
+                } else {
+                    apply({{L.gate, dst, ld}, {L.up, nullptr, ld}}, hid, hidden, L.ffn_norm, hidden, act_epi);
                 }
+            };
+            if (tp) {
+                gate_up(tp_local.as<float>(), ffn_l);
                 exchange(tp_local.as<float>(), ffn_b.as<float>(), n, ffn_l, false);
                 {
                     Scope sc(this, PH_DOWN);
                     apply({{L.down, tp_local.as<float>(), hidden_l}}, gated, ffn, L.ffn_sub_norm, ffn, EPI_STORE);
                 }
-                exchange(tp_local.as<float>(), hid, n, hidden_l, true);
+                exchange(tp_local.as<float>(), L.ffn_post_norm ? proj_b.as<float>() : hid, n, hidden_l, L.ffn_post_norm == nullptr);
+                if (L.ffn_post_norm) post_norm_add(L.ffn_post_norm);
             } else {
-                {
-                    Scope sc(this, PH_GATE_UP);
-                    apply({{L.gate, ffn_b.as<float>(), ffn}, {L.up, nullptr, ffn}}, hid, hidden, L.ffn_norm, hidden, act_epi);
-                }
+                gate_up(ffn_b.as<float>(), ffn);
                 Scope sc(this, PH_DOWN);
-                apply({{L.down, hid, hidden}}, gated, ffn, L.ffn_sub_norm, ffn, EPI_ADD);
+                if (L.ffn_post_norm) {
+                    apply({{L.down, proj_b.as<float>(), hidden}}, gated, ffn, L.ffn_sub_norm, ffn, EPI_STORE);
+                    post_norm_add(L.ffn_post_norm);
+                } else {
+                    apply({{L.down, hid, hidden}}, gated, ffn, L.ffn_sub_norm, ffn, EPI_ADD);
+                }
             }
         }
         const uint32_t rows = all_logits ? n : 1;
@@ -677,6 +734,10 @@ struct Session {
         } else {
             Scope sc(this, PH_HEAD);
             apply({{head, logits_b.as<float>(), vocab}}, last, hidden, output_norm, hidden, EPI_STORE, rows);
+        }
+        if (final_softcap != 0.0f) {  // src/model.cpp:1206-1209
+            launch_softcap(logits_b.as<float>(), size_t(rows) * vocab, final_softcap, stream);
+            ++launches;
         }
     }
 

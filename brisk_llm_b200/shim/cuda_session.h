@@ -31,7 +31,8 @@ public:
             case Architecture::Qwen3: arch = BRISK_ARCH_QWEN3; break;
             case Architecture::Llama: arch = BRISK_ARCH_LLAMA; break;
             case Architecture::BitNet: arch = BRISK_ARCH_BITNET; break;
-            default: throw std::runtime_error("cuda: this architecture is not supported by the CUDA backend (qwen3, llama, bitnet are)");
+            case Architecture::Gemma3: arch = BRISK_ARCH_GEMMA3; break;
+            default: throw std::runtime_error("cuda: this architecture is not supported by the CUDA backend (qwen3, llama, bitnet, gemma3 are)");
         }
         std::vector<brisk_cuda_layer> layers(c.layer_count);
         for (std::size_t i = 0; i < layers.size(); ++i) {
@@ -54,6 +55,9 @@ public:
             d.up = describe(s.up, file, p + "ffn_up.weight");
             d.ffn_sub_norm = s.feed_forward_sub_norm.empty() ? nullptr : s.feed_forward_sub_norm.data();
             d.down = describe(s.down, file, p + "ffn_down.weight");
+            d.attn_post_norm = s.attention_post_norm.empty() ? nullptr : s.attention_post_norm.data();
+            d.ffn_post_norm = s.feed_forward_post_norm.empty() ? nullptr : s.feed_forward_post_norm.data();
+            d.slides = c.layer_slides(static_cast<std::uint32_t>(i)) ? 1 : 0;
         }
         brisk_cuda_model d{};
         d.abi_version = BRISK_CUDA_ABI_VERSION;
@@ -75,6 +79,12 @@ public:
         if (file.tensor("output.weight") != nullptr) d.output = describe(model.output_projection(), file, "output.weight");
         d.output_norm = model.output_norm().data();
         d.layers = layers.data();
+        d.rope_scale = c.rope_scale;
+        d.rope_base_local = c.rope_base_local;
+        d.sliding_window = c.sliding_window;
+        d.embedding_scale = c.embedding_scale;
+        d.final_softcap = c.final_softcap;
+        d.gelu = c.gelu ? 1 : 0;
         brisk_cuda_options opt{};
         opt.max_context = max_context;
         opt.device = device;

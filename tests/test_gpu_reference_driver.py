@@ -19,6 +19,8 @@ DRIVER = os.path.join(H.ORACLE_DIR, "_ref", "ref_driver")
     ("qwen3", synth.tiny(synth.QWEN3_0_6B, layers=3, vocab=1024, hidden=512, heads=8, kv_heads=4, ffn=1024)),
     ("llama", synth.tiny(synth.LLAMA_3_2_1B, layers=2, vocab=1024, hidden=512, heads=8, kv_heads=2, ffn=1024)),
     ("bitnet", synth.tiny(synth.BITNET_2B, layers=2, vocab=1024, hidden=512, heads=4, kv_heads=1, ffn=768)),
+    ("gemma3", synth.tiny(synth.QWEN3_0_6B, arch="gemma3", layers=7, vocab=1024, hidden=512, heads=8, kv_heads=4, ffn=1024,
+                          sliding_window=16, rope_scaling_factor=8.0, final_softcap=30.0)),
 ])
 def test_reference_callers_over_cuda_session(family, spec, tmp_path):
     if not os.path.exists(DRIVER):
@@ -31,7 +33,7 @@ def test_reference_callers_over_cuda_session(family, spec, tmp_path):
     first, second = (json.loads(line) for line in r.stdout.strip().splitlines())
     assert first["greedy_equal"] and first["speculated_equal"]
     assert first["prefill_logits_max_abs_diff"] <= 2e-2
-    if family != "bitnet":
+    if family not in ("bitnet", "gemma3"):  # an F16 head sums in another order; Gemma's tanh may differ in the last bit
         assert first["prefill_logits_bit_equal"]
         assert first["log_likelihood_cpu"] == first["log_likelihood_cuda"]
     else:

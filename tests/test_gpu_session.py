@@ -31,10 +31,19 @@ def close(got, want, exact=True):
     assert got.shape == want.shape
     assert np.abs(got - want).max() <= MAX_ABS, np.abs(got - want).max()
     assert H.rel_l2(got, want) <= REL_L2, H.rel_l2(got, want)
+    if exact is None:  # only the stated tolerance (results that pass through a tanh, see exactness())
+        return
     if exact:
         assert np.array_equal(got, want), (np.abs(got - want).max(), int((got != want).sum()))
     else:
         assert np.abs(got - want).max() <= 1e-5
+
+
+def exactness(family):
+    """True: bit for bit. False: unquantised heads (F16, BF16) sum in another order, 1e-5. None: Gemma's GELU and soft cap
+    go through tanh - the CPU engine calls the C library's tanhf, the device rounds a double-precision tanh, the two can
+    differ in the last bit and the 8-bit re-quantisation that follows can amplify that - so the stated tolerance applies."""
+    return None if family == "gemma3" else family not in ("bitnet", "mixed")
 
 
 def greedy_agrees(got_ids, want_ids, want_logits):
@@ -54,7 +63,7 @@ def test_golden_from_the_reference(family):
     m = mg.golden_model(family)
     assert mg.model_digest(m).encode() == g["digest"].tobytes()
     toks = g["tokens"]
-    ex = family not in ("bitnet", "mixed")  # unquantised heads (F16, BF16) sum in another order
+    ex = exactness(family)
     with engine.CudaSession(m) as s:
         close(s.eval(toks[:33]), g["prefill33"], ex)
         for i in range(4):
@@ -77,6 +86,50 @@ def test_golden_from_the_reference(family):
             assert n == 16 and np.array_equal(ids, g["greedy16_ids"])
 
 
+@pytest.mark.parametrize("context,prompt", [(1024, 600), (2048, 1300)])
+def test_heads_of_256_values(context, prompt):
+    """Gemma 3's head geometry (256-wide heads, one K/V head for four query heads) on an otherwise Qwen3-shaped layer, so that
+    everything stays bit for bit: 8-token tiles below 1024 positions, 16-token tiles past them, then single tokens."""
+    spec = synth.tiny(synth.QWEN3_0_6B, layers=2, vocab=512, context=context, heads=4, kv_heads=1, head_dim=256)
+    m = synth.perturb_norms(synth.generate(spec, seed=51))
+    toks = synth.random_tokens(spec, prompt + 8, seed=52)
+    o = H.OracleSession(m)
+    with engine.CudaSession(m) as s:
+        assert "256-wide heads" in s.step_path()
+        close(s.eval(toks[:prompt]), o.eval(toks[:prompt]))
+        for i in range(prompt, prompt + 3):
+            close(s.eval(toks[i:i + 1]), o.eval(toks[i:i + 1]))
+        close(s.eval_all(toks[prompt + 3:prompt + 8]), o.eval_all(toks[prompt + 3:prompt + 8]))
+        s.rollback(prompt)
+        o.rollback(prompt)
+        want_ids, want_logits = o.generate_greedy(toks[prompt:prompt + 1], 6)
+        ids, logits = s.generate_greedy(int(toks[prompt]), 6, want_logits=True)
+        assert np.array_equal(ids, want_ids) and np.array_equal(logits, want_logits)
+    o.close()
+
+
+def test_sliding_window_layers_are_bit_exact_without_a_tanh():
+    """The sliding window, the local RoPE table and the embedding scale involve no tanh, so their kernels must reproduce
+    the CPU engine bit for bit: the attended values of a one-layer Gemma-3-shaped model (its only layer slides), read
+    before anything has passed through the GELU."""
+    spec = synth.tiny(synth.QWEN3_0_6B, arch="gemma3", layers=1, vocab=512, context=2048, sliding_window=300)
+    m = synth.perturb_norms(synth.generate(spec, seed=41))
+    toks = synth.random_tokens(spec, 1300, seed=42)
+    o = H.OracleSession(m)
+    with engine.CudaSession(m) as s:
+        # three device batches; the last (276 tokens) takes the 16-token tiles, every token's window starts mid-chunk
+        s.eval(toks[:1300])
+        o.eval(toks[:1300])
+        q = spec.q_dim
+        got = s.debug_buffer("attended", 276 * q).reshape(276, q)[256:]
+        assert np.array_equal(got, o.debug_buffer("attended", 20 * q).reshape(20, q))
+        for i in range(1300, 1303):  # single tokens through the same kernels
+            s.eval(toks[i:i + 1])
+            o.eval(toks[i:i + 1])
+            assert np.array_equal(s.debug_buffer("attended", q), o.debug_buffer("attended", q))
+    o.close()
+
+
 @pytest.mark.parametrize("family,spec", [
     ("qwen3", synth.tiny(synth.QWEN3_0_6B, layers=4, vocab=2048, context=1024)),
     ("llama", synth.tiny(synth.LLAMA_3_2_1B, layers=3, vocab=1024, context=1024)),
@@ -87,6 +140,10 @@ def test_golden_from_the_reference(family):
     # the formats beyond the benchmark configurations (Q5_K, Q4_1, Q5_0, a BF16 head), mixed as stock downloads mix them
     ("mixed", synth.tiny(synth.QWEN3_0_6B, layers=2, vocab=1024, context=1024, tied=False, fmt=formats.Q5_K,
                          fmt_overrides={"v": formats.Q4_1, "down": formats.Q5_0, "embd": formats.Q4_1, "output": formats.BF16})),
+    # Gemma 3 layer variants: six layers sliding over 128 positions around one global layer with a scaled position,
+    # post-norms, tanh-GELU, scaled embeddings, soft-capped logits
+    ("gemma3", synth.tiny(synth.QWEN3_0_6B, arch="gemma3", layers=7, vocab=1024, context=1024, sliding_window=128,
+                          rope_scaling_factor=8.0, final_softcap=30.0)),
 ])
 def test_full_width_layers_against_the_oracle(family, spec):
     """The real layer widths of each configuration (few layers, small vocabulary), a 600-token prompt processed in
@@ -94,11 +151,15 @@ def test_full_width_layers_against_the_oracle(family, spec):
     m = synth.perturb_norms(synth.generate(spec, seed=5))
     toks = synth.random_tokens(spec, 640, seed=6)
     o = H.OracleSession(m)
-    ex = family not in ("bitnet", "mixed")  # unquantised heads (F16, BF16) sum in another order
+    ex = exactness(family)
     with engine.CudaSession(m) as s:
         close(s.eval(toks[:600]), o.eval(toks[:600]), ex)
-        # the residual stream of every prompt token of the last batch, bit for bit (all families)
-        assert np.array_equal(s.debug_buffer("hidden", 88 * spec.hidden), o.debug_buffer("hidden", 88 * spec.hidden))
+        # the residual stream of every prompt token of the last batch, bit for bit (all families without a tanh)
+        got_hidden, want_hidden = s.debug_buffer("hidden", 88 * spec.hidden), o.debug_buffer("hidden", 88 * spec.hidden)
+        if ex is None:
+            assert H.rel_l2(got_hidden, want_hidden) <= REL_L2
+        else:
+            assert np.array_equal(got_hidden, want_hidden)
         for i in range(600, 606):
             close(s.eval(toks[i:i + 1]), o.eval(toks[i:i + 1]), ex)
         close(s.eval_all(toks[606:615]), o.eval_all(toks[606:615]), ex)
