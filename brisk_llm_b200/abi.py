@@ -13,7 +13,8 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG_DIR, "libbrisk_cuda.so")
 
 ARCH_QWEN3, ARCH_LLAMA, ARCH_BITNET, ARCH_GEMMA3 = 0, 1, 2, 3
-ARCH_BY_NAME = {"qwen3": ARCH_QWEN3, "llama": ARCH_LLAMA, "bitnet": ARCH_BITNET, "bitnet-b1.58": ARCH_BITNET, "gemma3": ARCH_GEMMA3}
+ARCH_BY_NAME = {"qwen3": ARCH_QWEN3, "llama": ARCH_LLAMA, "bitnet": ARCH_BITNET, "bitnet-b1.58": ARCH_BITNET, "gemma3": ARCH_GEMMA3,
+                "smollm3": ARCH_LLAMA}  # llama-shaped; its layers without RoPE are flagged per layer
 FLAG_NO_GRAPH, FLAG_NO_MEGAKERNEL, FLAG_NO_PERSISTENT = 1, 2, 4
 
 
@@ -29,7 +30,7 @@ class Layer(C.Structure):
     _fields_ = [("attn_norm", _FP), ("q", Matrix), ("k", Matrix), ("v", Matrix), ("q_norm", _FP), ("k_norm", _FP),
                 ("attn_sub_norm", _FP), ("o", Matrix), ("ffn_norm", _FP), ("gate", Matrix), ("up", Matrix),
                 ("ffn_sub_norm", _FP), ("down", Matrix), ("q_bias", _FP), ("k_bias", _FP), ("v_bias", _FP),
-                ("attn_post_norm", _FP), ("ffn_post_norm", _FP), ("slides", C.c_int32), ("reserved", C.c_int32)]
+                ("attn_post_norm", _FP), ("ffn_post_norm", _FP), ("slides", C.c_int32), ("no_rope", C.c_int32)]
 
 
 class Model(C.Structure):

@@ -371,15 +371,32 @@ __device__ __forceinline__ float relu2_mul(float g, float u) {
     const float r = fmaxf(g, 0.0f);  // src/model.cpp:1135-1138
     return __fmul_rn(__fmul_rn(r, r), u);
 }
-// tanhf through double precision: the correctly rounded value in all but a vanishing share of inputs. The CPU engine
-// calls the C library's tanhf, which may differ from it in the last bit, so results that pass through a tanh agree with
-// the CPU engine to rounding, not bit for bit.
-__device__ __forceinline__ float tanh_via_double(float z) { return float(tanh(double(z))); }
-__device__ __forceinline__ float gelu_mul(float x, float u) {
+// tanhf as the host's C library computes it. The CPU engine calls that library's tanhf (std::tanh on a float), whose
+// result is not always the correctly rounded one (glibc 2.39: 2.8 % of all inputs differ by one or two units in the last
+// place), and an activation that differs in its last bit can become a different 8-bit integer in the next multiply. So
+// the device computes base(|z|) = float(tanh(double(|z|))) and adds a correction from a table with one 4-bit entry per
+// float in [2^-25, 22): entry = (library's bits - base's bits) + 8, filled at session creation from the device's own base
+// values and the host library's results (build_tanh_table, gemma.cu). Below 2^-25 both round to z, from 22 on both to 1.
+// Without a table (nullptr) the result is base itself: correct to rounding, not bit for bit with the CPU engine.
+constexpr uint32_t kTanhTableLo = 0x33000000u;  // bits of 2^-25f
+constexpr uint32_t kTanhTableHi = 0x41b00000u;  // bits of 22.0f
+__device__ __forceinline__ float tanh_base(float az) { return float(tanh(double(az))); }
+__device__ __forceinline__ float tanh_like_host(float z, const uint8_t* __restrict__ table) {
+    const float az = fabsf(z);
+    uint32_t bits = __float_as_uint(tanh_base(az));
+    const uint32_t in = __float_as_uint(az);
+    if (table != nullptr && in >= kTanhTableLo && in < kTanhTableHi) {
+        const uint32_t i = in - kTanhTableLo;
+        const int nibble = (__ldg(table + (i >> 1)) >> ((i & 1) * 4)) & 0xF;
+        bits = uint32_t(int(bits) + nibble - 8);
+    }
+    return copysignf(__uint_as_float(bits), z);
+}
+__device__ __forceinline__ float gelu_mul(float x, float u, const uint8_t* __restrict__ tanh_table) {
     // 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))) * up in the scalar code's order of operations (gelu_mul_f32,
     // src/kernels_f32.cpp:291-296)
     const float cube = __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, x), x), x);
-    const float t = tanh_via_double(__fmul_rn(0.7978845608f, __fadd_rn(x, cube)));
+    const float t = tanh_like_host(__fmul_rn(0.7978845608f, __fadd_rn(x, cube)), tanh_table);
     return __fmul_rn(__fmul_rn(__fmul_rn(0.5f, x), __fadd_rn(1.0f, t)), u);
 }
 

@@ -1,6 +1,15 @@
 // The few extra kernels of the Gemma 3 layer variants (brisk-llm src/model.h:24): the embedding scale, the RMS norm a
-// projection's output gets before it joins the residual stream, and the soft cap of the logits. The tanh-GELU gate is
-// gelu_mul() in formats.cuh, applied by launch_gate_mul; the sliding window is a parameter of the attention kernels.
+// projection's output gets before it joins the residual stream, the soft cap of the logits, and the table that lets the
+// device's tanh reproduce the host C library's tanhf. The tanh-GELU gate is gelu_mul() in formats.cuh, applied by
+// launch_gate_mul; the sliding window is a parameter of the attention kernels.
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <vector>
+
 #include "common.cuh"
 #include "formats.cuh"
 #include "kernels.h"
@@ -26,9 +35,15 @@ __global__ void __launch_bounds__(256) post_norm_add_kernel(const float* __restr
     }
 }
 
-__global__ void __launch_bounds__(256) softcap_kernel(float* logits, size_t count, float cap) {
+__global__ void __launch_bounds__(256) softcap_kernel(float* logits, size_t count, float cap, const uint8_t* tanh_table) {
     const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (i < count) logits[i] = __fmul_rn(cap, tanh_via_double(__fdiv_rn(logits[i], cap)));
+    if (i < count) logits[i] = __fmul_rn(cap, tanh_like_host(__fdiv_rn(logits[i], cap), tanh_table));
+}
+
+// out[i] = the device's base tanh of the float whose bits are first + i.
+__global__ void __launch_bounds__(256) tanh_base_kernel(uint32_t first, uint32_t count, float* out) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count) out[i] = tanh_base(__uint_as_float(first + i));
 }
 
 }  // namespace
@@ -43,9 +58,68 @@ void launch_post_norm_add(const float* proj, const float* weight, float* hidden,
     BK_CUDA(cudaGetLastError());
 }
 
-void launch_softcap(float* logits, size_t count, float cap, cudaStream_t s) {
-    softcap_kernel<<<unsigned((count + 255) / 256), 256, 0, s>>>(logits, count, cap);
+void launch_softcap(float* logits, size_t count, float cap, const uint8_t* tanh_table, cudaStream_t s) {
+    softcap_kernel<<<unsigned((count + 255) / 256), 256, 0, s>>>(logits, count, cap, tanh_table);
     BK_CUDA(cudaGetLastError());
+}
+
+size_t tanh_table_bytes() { return size_t(kTanhTableHi - kTanhTableLo) / 2; }
+
+void build_tanh_table(uint8_t* table, unsigned threads, cudaStream_t s) {
+    constexpr uint32_t kChunk = 1u << 24;  // floats per round trip (64 MB of base values)
+    const uint32_t total = kTanhTableHi - kTanhTableLo;
+    threads = std::max(1u, std::min(threads, 32u));
+    float* base_dev = nullptr;
+    BK_CUDA(cudaMalloc(&base_dev, size_t(kChunk) * sizeof(float)));
+    std::vector<float> base(kChunk);
+    std::vector<uint8_t> packed(tanh_table_bytes());
+    std::string failure;
+    std::mutex failure_lock;
+    for (uint32_t c0 = 0; c0 < total; c0 += kChunk) {
+        const uint32_t n = std::min(kChunk, total - c0);  // even: kChunk and total are
+        tanh_base_kernel<<<(n + 255) / 256, 256, 0, s>>>(kTanhTableLo + c0, n, base_dev);
+        cudaError_t e = cudaGetLastError();
+        if (e == cudaSuccess) e = cudaMemcpyAsync(base.data(), base_dev, size_t(n) * sizeof(float), cudaMemcpyDeviceToHost, s);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+        if (e != cudaSuccess) {
+            cudaFree(base_dev);
+            throw CudaError(std::string("cuda: ") + cudaGetErrorString(e) + " (tanh table)");
+        }
+        auto work = [&](uint32_t lo, uint32_t hi) {  // [lo, hi) of this chunk, lo and hi even
+            for (uint32_t i = lo; i < hi; i += 2) {
+                uint8_t byte = 0;
+                for (uint32_t k = 0; k < 2; ++k) {
+                    const uint32_t in = kTanhTableLo + c0 + i + k;
+                    float x, want;
+                    std::memcpy(&x, &in, sizeof x);
+                    want = ::tanhf(x);  // the C library's tanhf: what std::tanh on a float calls in the CPU engine
+                    int32_t wb, bb;
+                    std::memcpy(&wb, &want, sizeof wb);
+                    std::memcpy(&bb, &base[i + k], sizeof bb);
+                    const int64_t delta = int64_t(wb) - int64_t(bb);
+                    if (delta < -8 || delta > 7) {
+                        std::lock_guard<std::mutex> g(failure_lock);
+                        failure = "cuda: the host library's tanhf and the device's differ by more than 8 units in the last place";
+                        return;
+                    }
+                    byte |= uint8_t(delta + 8) << (4 * k);
+                }
+                packed[(size_t(c0) + i) / 2] = byte;
+            }
+        };
+        std::vector<std::thread> pool;
+        const uint32_t per = ((n / 2 + threads - 1) / threads) * 2;
+        for (uint32_t t = 0; t < threads; ++t) {
+            const uint32_t lo = std::min(n, t * per), hi = std::min(n, lo + per);
+            if (lo < hi) pool.emplace_back(work, lo, hi);
+        }
+        for (std::thread& t : pool) t.join();
+        if (!failure.empty()) break;
+    }
+    cudaFree(base_dev);
+    if (!failure.empty()) throw CudaError(failure);
+    BK_CUDA(cudaMemcpyAsync(table, packed.data(), packed.size(), cudaMemcpyHostToDevice, s));
+    BK_CUDA(cudaStreamSynchronize(s));
 }
 
 }  // namespace bk

@@ -64,8 +64,9 @@ void launch_matvec(const MatTarget* targets, int count, const DevAct& act, uint3
 bool launch_gemm(const MatTarget* targets, int count, const DevAct& act, uint32_t n, Epilogue epi, cudaStream_t s);
 bool gemm_supports(int type, uint32_t cols);
 // The activation after separate gate and up multiplies. mode 0: gate[i] = silu(gate[i]) * up[i]; 1: max(gate[i],0)^2 * up[i];
-// 2: tanh-GELU(gate[i]) * up[i] (gelu_mul_f32, src/kernels_f32.cpp:291-296).
-void launch_gate_mul(float* gate, const float* up, size_t count, int mode, cudaStream_t s);
+// 2: tanh-GELU(gate[i]) * up[i] (gelu_mul_f32, src/kernels_f32.cpp:291-296), its tanh corrected by tanh_table (see
+// build_tanh_table) when one is given.
+void launch_gate_mul(float* gate, const float* up, size_t count, int mode, cudaStream_t s, const uint8_t* tanh_table = nullptr);
 
 // ---- Gemma layer variants (gemma.cu) ------------------------------------------------------------
 // x[i] *= scale: the embedding scale (src/model.cpp:899-901).
@@ -73,7 +74,13 @@ void launch_scale_rows(float* x, size_t count, float scale, cudaStream_t s);
 // hidden[t][:] += rms_norm(proj[t][:]) * weight, the norm as in src/model.cpp:87-97 (post-norms, :1116-1119, :1155-1158).
 void launch_post_norm_add(const float* proj, const float* weight, float* hidden, uint32_t n, uint32_t cols, float eps, cudaStream_t s);
 // logits[i] = cap * tanh(logits[i] / cap) (src/model.cpp:1206-1209).
-void launch_softcap(float* logits, size_t count, float cap, cudaStream_t s);
+void launch_softcap(float* logits, size_t count, float cap, const uint8_t* tanh_table, cudaStream_t s);
+// The table that makes the device's tanh return the bits of the host C library's tanhf (tanh_like_host, formats.cuh):
+// one 4-bit correction per float in [2^-25, 22), tanh_table_bytes() in all. The device evaluates its own base function for
+// every such float, the host evaluates its library's tanhf for the same inputs on `threads` threads, and the differences
+// are uploaded to `table` (device memory of tanh_table_bytes()). Called once per session of a model that uses a tanh.
+size_t tanh_table_bytes();
+void build_tanh_table(uint8_t* table, unsigned threads, cudaStream_t s);
 
 // ---- per-token vector work (misc.cu) -----------------------------------------------------------
 // hidden[t][:] = dequantised row tokens[t] of the embedding matrix (Session::eval_batch's embedding_row).

@@ -178,15 +178,15 @@ void dispatch(Params& p, bool pair, uint32_t n, cudaStream_t s) {
     }
 }
 
-__global__ void gate_mul_kernel(float* gate, const float* up, size_t count, int mode) {
+__global__ void gate_mul_kernel(float* gate, const float* up, size_t count, int mode, const uint8_t* tanh_table) {
     const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (i < count) gate[i] = mode == 2 ? gelu_mul(gate[i], up[i]) : mode == 1 ? relu2_mul(gate[i], up[i]) : silu_mul(gate[i], up[i]);
+    if (i < count) gate[i] = mode == 2 ? gelu_mul(gate[i], up[i], tanh_table) : mode == 1 ? relu2_mul(gate[i], up[i]) : silu_mul(gate[i], up[i]);
 }
 
 }  // namespace
 
-void launch_gate_mul(float* gate, const float* up, size_t count, int mode, cudaStream_t s) {
-    gate_mul_kernel<<<unsigned((count + 255) / 256), 256, 0, s>>>(gate, up, count, mode);
+void launch_gate_mul(float* gate, const float* up, size_t count, int mode, cudaStream_t s, const uint8_t* tanh_table) {
+    gate_mul_kernel<<<unsigned((count + 255) / 256), 256, 0, s>>>(gate, up, count, mode, tanh_table);
     BK_CUDA(cudaGetLastError());
 }
 

@@ -8,6 +8,7 @@
 #include <cstring>
 #include <memory>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include <dlfcn.h>
@@ -88,6 +89,7 @@ struct Layer {
     const float *q_bias = nullptr, *k_bias = nullptr, *v_bias = nullptr;  // this rank's rows
     const float *attn_post_norm = nullptr, *ffn_post_norm = nullptr;      // Gemma: norm of a projection before the residual add
     bool slides = false;                                                  // Gemma: sliding-window layer with the local RoPE table
+    bool no_rope = false;                                                 // SmolLM3: the layer attends without rotation
     __half *k_cache = nullptr, *v_cache = nullptr;
 };
 
@@ -124,6 +126,13 @@ brisk_cuda_memory estimate(const brisk_cuda_model& m, const brisk_cuda_options& 
     e.scratch += uint64_t(kMaxScored) * vocab * 4;                 // logits
     e.scratch += ctx * dim * 4 + (ctx + 1) * 4;                    // RoPE table, token history
     if (m.sliding_window != 0) e.scratch += ctx * dim * 4;          // the sliding layers' RoPE table
+    if (m.gelu != 0 || m.final_softcap != 0.0f) e.scratch += tanh_table_bytes();  // corrections of the device's tanh
+    for (uint32_t l = 0; l < m.layer_count; ++l) {
+        if (m.layers[l].no_rope) {
+            e.scratch += ctx * dim * 4;  // the identity table of layers without rotation
+            break;
+        }
+    }
     if (m.layer_count != 0 && (m.layers[0].attn_post_norm || m.layers[0].ffn_post_norm)) e.scratch += batch * hidden * 4;  // projection before its norm
     if (tp > 1) e.scratch += batch * std::max<uint64_t>(widest, vocab * kMaxScored / batch + 1) * 4 * 2 + batch * std::max(q_dim, ffn) * 4;
     return e;
@@ -153,6 +162,7 @@ struct Session {
     float embedding_scale = 1.0f, final_softcap = 0.0f;
     uint32_t sliding_window = 0;
     bool gelu = false, variant_layers = false;
+    bool unrotated_layers = false;  // SmolLM3: some layers attend without RoPE (src/model.h:97-110)
     int arch = 0, neox = 1, device = 0;
     uint32_t sms = 148;
     uint32_t flags = 0;
@@ -165,7 +175,7 @@ struct Session {
     uint64_t weight_bytes = 0, kv_bytes = 0;
 
     // state and scratch
-    DevBuffer kv, rope, rope_local, proj_b, tokens_dev, scalars, hidden_b, q_b, k_b, v_b, attended_b, ffn_b, up_b, logits_b, tp_local, tp_gathered, full_b, actf, actq0, actd0, acts0, actqk,
+    DevBuffer kv, rope, rope_local, rope_none, proj_b, tanh_table, tokens_dev, scalars, hidden_b, q_b, k_b, v_b, attended_b, ffn_b, up_b, logits_b, tp_local, tp_gathered, full_b, actf, actq0, actd0, acts0, actqk,
         actdk, actbs, partial, am_val, am_idx, history, logit_history, trace;
     DevActMut act;
     float* logits_host = nullptr;     // pinned [64][vocab]
@@ -401,6 +411,8 @@ struct Session {
             d.attn_post_norm = upload_vector(s.attn_post_norm, hidden, "post_attention_norm.weight", false);
             d.ffn_post_norm = upload_vector(s.ffn_post_norm, hidden, "post_ffw_norm.weight", false);
             d.slides = s.slides != 0 && sliding_window != 0;
+            d.no_rope = s.no_rope != 0;
+            if (d.no_rope) unrotated_layers = true;
             if (d.attn_post_norm || d.ffn_post_norm || d.slides) variant_layers = true;
         }
         if (gelu || embedding_scale != 1.0f || final_softcap != 0.0f) variant_layers = true;
@@ -441,6 +453,17 @@ struct Session {
         build_rope(rope, rope_base, m.rope_scale != 0.0f ? m.rope_scale : 1.0f, true);
         // The sliding layers rotate with their own base, an unscaled position and no per-frequency divisors (src/model.cpp:894).
         if (sliding_window != 0) build_rope(rope_local, m.rope_base_local, 1.0f, false);
+        // A layer without rotation (the reference rotates zero pairs there, src/model.cpp:1024) runs the same kernels over
+        // a table of cos = 1, sin = 0: x0 * 1 - x1 * 0 and x0 * 0 + x1 * 1 return x0 and x1 themselves.
+        if (unrotated_layers) {
+            std::vector<float> table(size_t(max_context) * head_dim);
+            for (size_t i = 0; i < table.size(); i += 2) {
+                table[i] = 1.0f;
+                table[i + 1] = 0.0f;
+            }
+            rope_none.alloc(table.size() * sizeof(float));
+            BK_CUDA(cudaMemcpy(rope_none.p, table.data(), table.size() * sizeof(float), cudaMemcpyHostToDevice));
+        }
 
         const uint32_t widest = std::max(std::max(hidden, q_dim), ffn);
         tokens_dev.alloc((kMaxBatch + 4) * sizeof(int32_t));
@@ -455,6 +478,15 @@ struct Session {
         up_b.alloc(size_t(kMaxBatch) * ffn * 4);
         logits_b.alloc(size_t(kMaxScored) * vocab * 4);
         if (variant_layers) proj_b.alloc(size_t(kMaxBatch) * hidden * 4);
+        if (gelu || final_softcap != 0.0f) {
+            // The CPU engine's GELU and soft cap call the C library's tanhf; the table makes the device return the same bits
+            // (tanh_like_host, formats.cuh). BRISK_CUDA_TANH_TABLE=0 skips it: results then agree to rounding only.
+            const char* env = std::getenv("BRISK_CUDA_TANH_TABLE");
+            if (env == nullptr || std::strcmp(env, "0") != 0) {
+                tanh_table.alloc(tanh_table_bytes());
+                build_tanh_table(tanh_table.as<uint8_t>(), std::thread::hardware_concurrency(), stream);
+            }
+        }
         actf.alloc(size_t(kMaxBatch) * widest * 4);
         actq0.alloc(size_t(kMaxBatch) * widest);
         actd0.alloc(size_t(kMaxBatch) * (widest / 32) * 4);
@@ -491,6 +523,7 @@ struct Session {
     void plan_step() {
         const char* env = std::getenv("BRISK_CUDA_STEP");
         if (tp_size > 1) step_note = "off: tensor parallel steps exchange activations between the operations";
+        else if (unrotated_layers) step_note = "off: layers without RoPE take the per-operation kernels (the persistent kernel rotates every layer with one table)";
         else if (variant_layers) step_note = "off: Gemma layer variants (post-norms, GELU, sliding window) and 256-wide heads run through the batched kernels";
         else if (flags & (BRISK_CUDA_FLAG_NO_MEGAKERNEL | BRISK_CUDA_FLAG_NO_PERSISTENT)) step_note = "off: disabled by the session's flags";
         else if (env != nullptr && std::strcmp(env, "0") == 0) step_note = "off: BRISK_CUDA_STEP=0";
@@ -639,7 +672,7 @@ struct Session {
 
             RopeArgs r{};
             r.q = q_b.as<float>(); r.k = k_b.as<float>(); r.v = v_b.as<float>();
-            r.q_norm = L.q_norm; r.k_norm = L.k_norm; r.rope = L.slides ? rope_local.as<float>() : rope.as<float>();
+            r.q_norm = L.q_norm; r.k_norm = L.k_norm; r.rope = L.no_rope ? rope_none.as<float>() : L.slides ? rope_local.as<float>() : rope.as<float>();
             r.q_bias = L.q_bias; r.k_bias = L.k_bias; r.v_bias = L.v_bias;
             r.k_cache = L.k_cache; r.v_cache = L.v_cache; r.position = d_position();
             r.n = n; r.heads = heads_l; r.kv_heads = kv_heads_l; r.dim = head_dim; r.max_context = uint32_t(max_context);
@@ -697,7 +730,7 @@ struct Session {
                 Scope sc(this, PH_GATE_UP);
                 if (gelu) {
                     apply({{L.gate, dst, ld}, {L.up, up_b.as<float>(), ld}}, hid, hidden, L.ffn_norm, hidden, EPI_STORE);
-                    launch_gate_mul(dst, up_b.as<float>(), size_t(n) * ld, 2, stream);
+                    launch_gate_mul(dst, up_b.as<float>(), size_t(n) * ld, 2, stream, tanh_table.as<uint8_t>());
                     ++launches;
                 } else {
                     apply({{L.gate, dst, ld}, {L.up, nullptr, ld}}, hid, hidden, L.ffn_norm, hidden, act_epi);
@@ -736,7 +769,7 @@ struct Session {
             apply({{head, logits_b.as<float>(), vocab}}, last, hidden, output_norm, hidden, EPI_STORE, rows);
         }
         if (final_softcap != 0.0f) {  // src/model.cpp:1206-1209
-            launch_softcap(logits_b.as<float>(), size_t(rows) * vocab, final_softcap, stream);
+            launch_softcap(logits_b.as<float>(), size_t(rows) * vocab, final_softcap, tanh_table.as<uint8_t>(), stream);
             ++launches;
         }
     }

@@ -16,7 +16,7 @@ from .synth import HostModel, ModelSpec
 
 ALIGN = 32
 _U32, _F32, _STR, _U64 = 4, 6, 8, 10
-ARCH_NAME = {"qwen3": "qwen3", "llama": "llama", "bitnet": "bitnet-b1.58", "gemma3": "gemma3"}
+ARCH_NAME = {"qwen3": "qwen3", "llama": "llama", "bitnet": "bitnet-b1.58", "gemma3": "gemma3", "smollm3": "smollm3"}
 
 
 def _s(b: bytes) -> bytes:
@@ -111,9 +111,9 @@ def read_gguf(path: str) -> HostModel:
     align = meta.get("general.alignment", ALIGN)
     base = (r.p + align - 1) // align * align
     arch = meta["general.architecture"]
-    fam = {"qwen3": "qwen3", "llama": "llama", "bitnet": "bitnet", "bitnet-b1.58": "bitnet", "gemma3": "gemma3"}.get(arch)
+    fam = {"qwen3": "qwen3", "llama": "llama", "bitnet": "bitnet", "bitnet-b1.58": "bitnet", "gemma3": "gemma3", "smollm3": "smollm3"}.get(arch)
     if fam is None:
-        raise ValueError(f"gguf: architecture '{arch}' is not one this backend runs (qwen3, llama, bitnet, gemma3)")
+        raise ValueError(f"gguf: architecture '{arch}' is not one this backend runs (qwen3, llama, bitnet, gemma3, smollm3)")
     g = lambda k, d=None: meta.get(f"{arch}.{k}", d)
     tensors, rope = {}, None
     for name, dims, typ, off in infos:

@@ -32,7 +32,8 @@ public:
             case Architecture::Llama: arch = BRISK_ARCH_LLAMA; break;
             case Architecture::BitNet: arch = BRISK_ARCH_BITNET; break;
             case Architecture::Gemma3: arch = BRISK_ARCH_GEMMA3; break;
-            default: throw std::runtime_error("cuda: this architecture is not supported by the CUDA backend (qwen3, llama, bitnet, gemma3 are)");
+            case Architecture::SmolLM3: arch = BRISK_ARCH_LLAMA; break;  // llama-shaped; its layers without RoPE are flagged below
+            default: throw std::runtime_error("cuda: this architecture is not supported by the CUDA backend (qwen3, llama, bitnet, gemma3, smollm3 are)");
         }
         std::vector<brisk_cuda_layer> layers(c.layer_count);
         for (std::size_t i = 0; i < layers.size(); ++i) {
@@ -58,6 +59,7 @@ public:
             d.attn_post_norm = s.attention_post_norm.empty() ? nullptr : s.attention_post_norm.data();
             d.ffn_post_norm = s.feed_forward_post_norm.empty() ? nullptr : s.feed_forward_post_norm.data();
             d.slides = c.layer_slides(static_cast<std::uint32_t>(i)) ? 1 : 0;
+            d.no_rope = c.layer_has_rope(i) ? 0 : 1;
         }
         brisk_cuda_model d{};
         d.abi_version = BRISK_CUDA_ABI_VERSION;

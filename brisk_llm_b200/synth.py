@@ -20,7 +20,7 @@ from . import abi, formats as F
 @dataclass(frozen=True)
 class ModelSpec:
     name: str
-    arch: str  # "qwen3" | "llama" | "bitnet" | "gemma3"
+    arch: str  # "qwen3" | "llama" | "bitnet" | "gemma3" | "smollm3"
     layers: int
     hidden: int
     heads: int
@@ -43,6 +43,10 @@ class ModelSpec:
     rope_base_local: float = 10000.0
     rope_scaling_factor: float = 1.0
     final_softcap: float = 0.0
+
+    def layer_has_rope(self, layer: int) -> bool:
+        """SmolLM3: every fourth layer attends without positional rotation (src/model.cpp:168, src/model.h:97-110)."""
+        return self.arch != "smollm3" or (layer + 1) % 4 != 0
 
     def layer_slides(self, layer: int) -> bool:
         return self.arch == "gemma3" and self.sliding_window != 0 and layer % 6 != 5
@@ -139,6 +143,7 @@ class HostModel:
             L.q_bias, L.k_bias, L.v_bias = self._vec(p + "attn_q.bias"), self._vec(p + "attn_k.bias"), self._vec(p + "attn_v.bias")
             L.attn_post_norm, L.ffn_post_norm = self._vec(p + "post_attention_norm.weight"), self._vec(p + "post_ffw_norm.weight")
             L.slides = 1 if s.layer_slides(i) else 0
+            L.no_rope = 0 if s.layer_has_rope(i) else 1
         m = abi.Model()
         m.abi_version = abi.ABI_VERSION
         m.arch = abi.ARCH_BY_NAME[s.arch]
@@ -146,7 +151,7 @@ class HostModel:
         m.head_count, m.kv_head_count, m.head_dim, m.ffn = s.heads, s.kv_heads, s.head_dim, s.ffn
         m.context_length = s.context
         m.rope_base, m.rms_epsilon = s.rope_base, s.eps
-        m.rope_neox = 0 if s.arch == "llama" else 1  # brisk-llm src/model.cpp:167
+        m.rope_neox = 0 if s.arch in ("llama", "smollm3") else 1  # brisk-llm src/model.cpp:167
         if self.rope_factors is not None:
             m.rope_factor_count = len(self.rope_factors)
             m.rope_factors = self.rope_factors.ctypes.data_as(C.POINTER(C.c_float))

@@ -87,7 +87,9 @@ typedef struct brisk_cuda_layer {
     /* 1: the layer attends only to the last `sliding_window` positions and rotates with the table of
      * rope_base_local (ModelConfig::layer_slides, src/model.h:87-90; src/model.cpp:1084-1085). */
     int32_t slides;
-    int32_t reserved;
+    /* 1: the layer attends without positional rotation (SmolLM3's every fourth layer, ModelConfig::layer_has_rope,
+     * src/model.h:97-110; src/model.cpp:1024). */
+    int32_t no_rope;
 } brisk_cuda_layer;
 
 /* POD mirror of the brisk::ModelConfig fields the supported families use (src/model.h:36-62)

@@ -751,13 +751,13 @@ static void eval_batch(oracle_session* s, const int32_t* tokens, size_t n, int a
             for (size_t h = 0; h < c->head_count; ++h) {
                 float* q = s->query + t * Q + h * D;
                 if (L->q_norm) rms_norm(q, L->q_norm, eps, q, D);
-                apply_rope(q, rope, D, c->rope_neox);
+                if (!L->no_rope) apply_rope(q, rope, D, c->rope_neox); /* rope_dim 0 on SmolLM3's NoPE layers, :1024 */
             }
             for (size_t h = 0; h < c->kv_head_count; ++h) {
                 float* k = s->newk + t * KV + h * D;
                 float* v = s->newv + t * KV + h * D;
                 if (L->k_norm) rms_norm(k, L->k_norm, eps, k, D);
-                apply_rope(k, rope, D, c->rope_neox);
+                if (!L->no_rope) apply_rope(k, rope, D, c->rope_neox);
                 uint16_t* kc = s->keys[l] + (h * s->max_context + s->position + t) * D;
                 uint16_t* vc = s->values[l] + (h * s->max_context + s->position + t) * D;
                 for (size_t i = 0; i < D; ++i) {

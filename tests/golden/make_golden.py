@@ -32,6 +32,8 @@ MORE_FAMILIES = {
     "biased": synth.tiny(synth.MISTRAL_7B, hidden=256, heads=4, kv_heads=2, ffn=512, vocab=256, qkv_bias=True, fmt=F.Q8_0),
     "mixed": synth.tiny(synth.QWEN3_0_6B, hidden=256, heads=4, kv_heads=2, ffn=512, vocab=256, tied=False, fmt=F.Q5_K,
                         fmt_overrides={"v": F.Q4_1, "down": F.Q5_0, "embd": F.Q4_1, "output": F.BF16}),
+    # SmolLM3: llama-shaped, the fourth layer attends without RoPE
+    "smollm3": synth.tiny(synth.LLAMA_3_2_1B, arch="smollm3", layers=4, hidden=256, heads=8, kv_heads=2, ffn=512, vocab=256),
     # Gemma 3 layers: six sliding layers (window 16) around one global layer, soft-capped logits
     "gemma3": synth.tiny(synth.QWEN3_0_6B, arch="gemma3", layers=7, hidden=256, heads=4, kv_heads=2, ffn=512, vocab=256,
                          sliding_window=16, rope_scaling_factor=8.0, final_softcap=30.0),

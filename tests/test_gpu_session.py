@@ -31,7 +31,7 @@ def close(got, want, exact=True):
     assert got.shape == want.shape
     assert np.abs(got - want).max() <= MAX_ABS, np.abs(got - want).max()
     assert H.rel_l2(got, want) <= REL_L2, H.rel_l2(got, want)
-    if exact is None:  # only the stated tolerance (results that pass through a tanh, see exactness())
+    if exact is None:  # only the stated tolerance
         return
     if exact:
         assert np.array_equal(got, want), (np.abs(got - want).max(), int((got != want).sum()))
@@ -40,10 +40,9 @@ def close(got, want, exact=True):
 
 
 def exactness(family):
-    """True: bit for bit. False: unquantised heads (F16, BF16) sum in another order, 1e-5. None: Gemma's GELU and soft cap
-    go through tanh - the CPU engine calls the C library's tanhf, the device rounds a double-precision tanh, the two can
-    differ in the last bit and the 8-bit re-quantisation that follows can amplify that - so the stated tolerance applies."""
-    return None if family == "gemma3" else family not in ("bitnet", "mixed")
+    """True: bit for bit - Gemma 3 included: its GELU and soft cap go through the C library's tanhf on the CPU, which the
+    device reproduces with its correction table. False: unquantised heads (F16, BF16) sum in another order, 1e-5."""
+    return family not in ("bitnet", "mixed")
 
 
 def greedy_agrees(got_ids, want_ids, want_logits):
@@ -114,7 +113,7 @@ def test_sliding_window_layers_are_bit_exact_without_a_tanh():
     before anything has passed through the GELU."""
     spec = synth.tiny(synth.QWEN3_0_6B, arch="gemma3", layers=1, vocab=512, context=2048, sliding_window=300)
     m = synth.perturb_norms(synth.generate(spec, seed=41))
-    toks = synth.random_tokens(spec, 1300, seed=42)
+    toks = synth.random_tokens(spec, 1310, seed=42)
     o = H.OracleSession(m)
     with engine.CudaSession(m) as s:
         # three device batches; the last (276 tokens) takes the 16-token tiles, every token's window starts mid-chunk
@@ -140,6 +139,8 @@ def test_sliding_window_layers_are_bit_exact_without_a_tanh():
     # the formats beyond the benchmark configurations (Q5_K, Q4_1, Q5_0, a BF16 head), mixed as stock downloads mix them
     ("mixed", synth.tiny(synth.QWEN3_0_6B, layers=2, vocab=1024, context=1024, tied=False, fmt=formats.Q5_K,
                          fmt_overrides={"v": formats.Q4_1, "down": formats.Q5_0, "embd": formats.Q4_1, "output": formats.BF16})),
+    # SmolLM3: llama-shaped, every fourth layer attends without RoPE
+    ("smollm3", synth.tiny(synth.LLAMA_3_2_1B, arch="smollm3", layers=4, vocab=1024, context=1024)),
     # Gemma 3 layer variants: six layers sliding over 128 positions around one global layer with a scaled position,
     # post-norms, tanh-GELU, scaled embeddings, soft-capped logits
     ("gemma3", synth.tiny(synth.QWEN3_0_6B, arch="gemma3", layers=7, vocab=1024, context=1024, sliding_window=128,

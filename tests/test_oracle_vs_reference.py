@@ -54,6 +54,8 @@ def test_f16_head_bit_exact():
     # layer 5 is global with a scaled position, soft-capped logits (src/model.cpp:169-176, :1084-1085, :1116-1119, :1206-1209)
     ("gemma3", synth.tiny(synth.QWEN3_0_6B, arch="gemma3", layers=7, hidden=256, heads=4, kv_heads=2, ffn=512, context=512,
                           sliding_window=64, rope_scaling_factor=8.0, final_softcap=30.0)),
+    # SmolLM3: llama-shaped, the fourth layer attends without RoPE (src/model.cpp:168, :1024)
+    ("smollm3", synth.tiny(synth.LLAMA_3_2_1B, arch="smollm3", layers=5, hidden=512, heads=8, kv_heads=2, ffn=1024, context=512)),
     # Gemma 3's head geometry: 256-wide heads, one K/V head for four query heads
     ("wide-heads", synth.tiny(synth.QWEN3_0_6B, hidden=256, heads=4, kv_heads=1, head_dim=256, ffn=512, context=512)),
 ])
