@@ -54,6 +54,7 @@ WORKLOADS = {  # prompt tokens, decode steps, context
     "llama-3.2-1b-q4_k_m": (1024, 256, 4096),
     "bitnet-2b4t-tq2_0": (512, 256, 4096),
     "mistral-7b-q4_0": (8192, 512, 8704),
+    "gemma3-1b-q4_0": (1024, 256, 4096),  # not a benchmark configuration: the Gemma 3 layer variants at a real model's shape
 }
 
 

@@ -538,9 +538,13 @@ void launch_attention(const AttnArgs& a, cudaStream_t s) {
     switch (group) {
         case 1: BK_SCORES(1); break;
         case 2: BK_SCORES(2); break;
+        case 3: BK_SCORES(3); break;
         case 4: BK_SCORES(4); break;
+        case 5: BK_SCORES(5); break;
+        case 6: BK_SCORES(6); break;
+        case 7: BK_SCORES(7); break;
         case 8: BK_SCORES(8); break;
-        default: throw CudaError("cuda: query heads per K/V head must be 1, 2, 4 or 8");
+        default: throw CudaError("cuda: query heads per K/V head must be 1 to 8");
     }
 #undef BK_SCORES
 #undef BK_SCORES_T

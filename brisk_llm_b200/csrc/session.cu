@@ -330,7 +330,7 @@ struct Session {
         if (gelu && arch == BRISK_ARCH_BITNET) throw CudaError("cuda: the squared-ReLU gate and the GELU gate exclude each other");
         if (!vocab || !hidden || !n_layers || !heads || !kv_heads || !ffn || !m.context_length) throw CudaError("cuda: a model dimension is zero");
         if (heads % kv_heads != 0) throw CudaError("cuda: head_count is not a multiple of head_count_kv");
-        if (heads / kv_heads > 16) throw CudaError("cuda: more than 16 query heads per key/value head is not supported");
+        if (heads / kv_heads > 8) throw CudaError("cuda: more than 8 query heads per key/value head is not supported");
         if (head_dim != 64 && head_dim != 128 && head_dim != 256) throw CudaError("cuda: head size must be 64, 128 or 256");
         if (m.rope_factor_count != 0 && m.rope_factor_count != head_dim / 2) throw CudaError("cuda: rope factor count must be head_dim / 2");
         q_dim = heads * head_dim;

@@ -70,7 +70,10 @@ LLAMA_3_2_1B = ModelSpec("llama-3.2-1b-q4_k_m", "llama", 16, 2048, 32, 8, 64, 81
 BITNET_2B = ModelSpec("bitnet-2b4t-tq2_0", "bitnet", 30, 2560, 20, 5, 128, 6912, 128256, 4096, 5e5, 1e-5, True, F.TQ2_0,
                       {"embd": F.F16})
 MISTRAL_7B = ModelSpec("mistral-7b-q4_0", "llama", 32, 4096, 32, 8, 128, 14336, 32768, 8704, 1e6, 1e-5, False, F.Q4_0)
-PRESETS = {s.name: s for s in (QWEN3_0_6B, LLAMA_3_2_1B, BITNET_2B, MISTRAL_7B)}
+# Beyond the benchmark configurations: the shape of Gemma-3-1B (256-wide heads, five sliding layers per global one).
+GEMMA3_1B = ModelSpec("gemma3-1b-q4_0", "gemma3", 26, 1152, 4, 1, 256, 6912, 262144, 4096, 1e6, 1e-6, True, F.Q4_0,
+                      sliding_window=512, rope_base_local=10000.0, rope_scaling_factor=1.0, final_softcap=0.0)
+PRESETS = {s.name: s for s in (QWEN3_0_6B, LLAMA_3_2_1B, BITNET_2B, MISTRAL_7B, GEMMA3_1B)}
 
 
 def tiny(spec: ModelSpec, layers=2, vocab=512, context=256, **kw) -> ModelSpec:

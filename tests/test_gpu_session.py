@@ -139,6 +139,11 @@ def test_sliding_window_layers_are_bit_exact_without_a_tanh():
     # the formats beyond the benchmark configurations (Q5_K, Q4_1, Q5_0, a BF16 head), mixed as stock downloads mix them
     ("mixed", synth.tiny(synth.QWEN3_0_6B, layers=2, vocab=1024, context=1024, tied=False, fmt=formats.Q5_K,
                          fmt_overrides={"v": formats.Q4_1, "down": formats.Q5_0, "embd": formats.Q4_1, "output": formats.BF16})),
+    # 5 and 6 query heads per K/V head (Qwen2.5-14B, Qwen2.5-1.5B)
+    ("group5", synth.tiny(synth.QWEN3_0_6B, layers=2, vocab=1024, context=1024, hidden=640, heads=5, kv_heads=1, ffn=1280)),
+    ("group6", synth.tiny(synth.MISTRAL_7B, layers=2, vocab=1024, context=1024, hidden=768, heads=12, kv_heads=2, head_dim=64, ffn=1536, qkv_bias=True)),
+    ("group3", synth.tiny(synth.QWEN3_0_6B, layers=2, vocab=1024, context=1024, hidden=768, heads=6, kv_heads=2, ffn=1536)),
+    ("group7", synth.tiny(synth.MISTRAL_7B, layers=2, vocab=1024, context=1024, hidden=896, heads=14, kv_heads=2, head_dim=64, ffn=1792, qkv_bias=True)),
     # SmolLM3: llama-shaped, every fourth layer attends without RoPE
     ("smollm3", synth.tiny(synth.LLAMA_3_2_1B, arch="smollm3", layers=4, vocab=1024, context=1024)),
     # Gemma 3 layer variants: six layers sliding over 128 positions around one global layer with a scaled position,
@@ -277,6 +282,9 @@ def test_memory_preflight_refuses_what_cannot_fit(monkeypatch):
     ("bitnet", synth.tiny(synth.BITNET_2B, layers=2, vocab=1024, context=2048)),
     ("mistral", synth.tiny(synth.MISTRAL_7B, layers=2, vocab=1024, context=2048)),
     ("biased", synth.tiny(synth.MISTRAL_7B, layers=2, vocab=1024, context=2048, hidden=1024, heads=8, kv_heads=2, ffn=2048, qkv_bias=True)),
+    # query heads per K/V head that are not powers of two: 3 (Llama-3.2-3B, Phi-4-mini) and 7 (Qwen2.5-7B, with its biases)
+    ("group3", synth.tiny(synth.QWEN3_0_6B, layers=2, vocab=1024, context=2048, hidden=768, heads=6, kv_heads=2, ffn=1536)),
+    ("group7", synth.tiny(synth.MISTRAL_7B, layers=2, vocab=1024, context=2048, hidden=896, heads=14, kv_heads=2, head_dim=64, ffn=1792, qkv_bias=True)),
 ])
 def test_the_three_single_token_paths_agree_bit_for_bit(family, spec, monkeypatch):
     """A single-token step can run as one persistent kernel for all layers (the default where the model allows it), as
