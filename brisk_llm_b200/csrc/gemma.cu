@@ -68,31 +68,47 @@ size_t tanh_table_bytes() { return size_t(kTanhTableHi - kTanhTableLo) / 2; }
 void build_tanh_table(uint8_t* table, unsigned threads, cudaStream_t s) {
     constexpr uint32_t kChunk = 1u << 24;  // floats per round trip (64 MB of base values)
     const uint32_t total = kTanhTableHi - kTanhTableLo;
-    threads = std::max(1u, std::min(threads, 32u));
-    float* base_dev = nullptr;
-    BK_CUDA(cudaMalloc(&base_dev, size_t(kChunk) * sizeof(float)));
-    std::vector<float> base(kChunk);
+    threads = std::max(1u, std::min(threads, 64u));
+    // Two device buffers and two pinned host buffers: the device evaluates and copies chunk i + 1 while the host threads
+    // work on chunk i.
+    struct Buffers {
+        float* dev[2] = {nullptr, nullptr};
+        float* host[2] = {nullptr, nullptr};
+        ~Buffers() {
+            for (int i = 0; i < 2; ++i) {
+                if (dev[i]) cudaFree(dev[i]);
+                if (host[i]) cudaFreeHost(host[i]);
+            }
+        }
+    } buf;
+    for (int i = 0; i < 2; ++i) {
+        BK_CUDA(cudaMalloc(&buf.dev[i], size_t(kChunk) * sizeof(float)));
+        BK_CUDA(cudaMallocHost(&buf.host[i], size_t(kChunk) * sizeof(float)));
+    }
     std::vector<uint8_t> packed(tanh_table_bytes());
     std::string failure;
     std::mutex failure_lock;
-    for (uint32_t c0 = 0; c0 < total; c0 += kChunk) {
+    auto request = [&](uint32_t c0, int slot) {
+        const uint32_t n = std::min(kChunk, total - c0);
+        tanh_base_kernel<<<(n + 255) / 256, 256, 0, s>>>(kTanhTableLo + c0, n, buf.dev[slot]);
+        BK_CUDA(cudaGetLastError());
+        BK_CUDA(cudaMemcpyAsync(buf.host[slot], buf.dev[slot], size_t(n) * sizeof(float), cudaMemcpyDeviceToHost, s));
+    };
+    request(0, 0);
+    int slot = 0;
+    for (uint32_t c0 = 0; c0 < total; c0 += kChunk, slot ^= 1) {
         const uint32_t n = std::min(kChunk, total - c0);  // even: kChunk and total are
-        tanh_base_kernel<<<(n + 255) / 256, 256, 0, s>>>(kTanhTableLo + c0, n, base_dev);
-        cudaError_t e = cudaGetLastError();
-        if (e == cudaSuccess) e = cudaMemcpyAsync(base.data(), base_dev, size_t(n) * sizeof(float), cudaMemcpyDeviceToHost, s);
-        if (e == cudaSuccess) e = cudaStreamSynchronize(s);
-        if (e != cudaSuccess) {
-            cudaFree(base_dev);
-            throw CudaError(std::string("cuda: ") + cudaGetErrorString(e) + " (tanh table)");
-        }
-        auto work = [&](uint32_t lo, uint32_t hi) {  // [lo, hi) of this chunk, lo and hi even
+        BK_CUDA(cudaStreamSynchronize(s));                 // chunk c0 is in buf.host[slot]
+        if (c0 + kChunk < total) request(c0 + kChunk, slot ^ 1);
+        const float* base = buf.host[slot];
+        auto work = [&, base, c0](uint32_t lo, uint32_t hi) {  // [lo, hi) of this chunk, lo and hi even
             for (uint32_t i = lo; i < hi; i += 2) {
                 uint8_t byte = 0;
                 for (uint32_t k = 0; k < 2; ++k) {
                     const uint32_t in = kTanhTableLo + c0 + i + k;
-                    float x, want;
+                    float x;
                     std::memcpy(&x, &in, sizeof x);
-                    want = ::tanhf(x);  // the C library's tanhf: what std::tanh on a float calls in the CPU engine
+                    const float want = ::tanhf(x);  // the C library's tanhf: what std::tanh on a float calls in the CPU engine
                     int32_t wb, bb;
                     std::memcpy(&wb, &want, sizeof wb);
                     std::memcpy(&bb, &base[i + k], sizeof bb);
@@ -116,7 +132,7 @@ void build_tanh_table(uint8_t* table, unsigned threads, cudaStream_t s) {
         for (std::thread& t : pool) t.join();
         if (!failure.empty()) break;
     }
-    cudaFree(base_dev);
+    BK_CUDA(cudaStreamSynchronize(s));
     if (!failure.empty()) throw CudaError(failure);
     BK_CUDA(cudaMemcpyAsync(table, packed.data(), packed.size(), cudaMemcpyHostToDevice, s));
     BK_CUDA(cudaStreamSynchronize(s));

@@ -552,6 +552,12 @@ void launch_attention(const AttnArgs& a, cudaStream_t s) {
     attn_softmax_kernel<<<dim3(a.heads, a.n), 256, 0, s>>>(a);
     BK_CUDA(cudaGetLastError());
     const uint32_t parts = (a.dim + 127) / 128;
+    if (a.n == 1) {  // a single token (models that take these kernels for their decode steps too): no tile to share V rows with
+        const size_t smem_1 = size_t(kWChunk) * (a.dim / parts) * sizeof(__half) + size_t(kWChunk) * sizeof(float);
+        attn_weighted_kernel<1><<<dim3(a.heads * parts, 1), 128, smem_1, s>>>(a);
+        BK_CUDA(cudaGetLastError());
+        return;
+    }
     const size_t smem_w = size_t(kWChunk) * (a.dim / parts) * sizeof(__half) + size_t(tile) * kWChunk * sizeof(float);
     if (tile == 16) attn_weighted_kernel<16><<<dim3(a.heads * parts, tiles), 128, smem_w, s>>>(a);
     else attn_weighted_kernel<8><<<dim3(a.heads * parts, tiles), 128, smem_w, s>>>(a);

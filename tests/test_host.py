@@ -110,6 +110,20 @@ def test_device_memory_estimate_needs_no_gpu():
     assert tp2["cache"] * 2 == e["cache"] and tp2["weights"] < e["weights"]
 
 
+def test_memory_estimate_counts_the_gemma_tables():
+    """A model whose GELU or soft cap needs the tanh correction table (one 4-bit entry per float of [2^-25, 22)) and a
+    second RoPE table for its sliding layers is estimated with them."""
+    from brisk_llm_b200 import engine
+    plain = synth.tiny(synth.QWEN3_0_6B, layers=2, vocab=1024, context=512)
+    gemma = synth.tiny(synth.QWEN3_0_6B, arch="gemma3", layers=2, vocab=1024, context=512, sliding_window=64)
+    a, b = engine.estimate_memory(synth.generate(plain, seed=0)), engine.estimate_memory(synth.generate(gemma, seed=0))
+    table = (0x41B00000 - 0x33000000) // 2
+    rope_local = 512 * plain.head_dim * 4
+    staged_projection = 512 * plain.hidden * 4
+    assert b["scratch"] - a["scratch"] == table + rope_local + staged_projection
+    assert b["weights"] - a["weights"] == 2 * 2 * plain.hidden * 4  # two post-norm vectors per layer
+
+
 def test_ctypes_mirror_has_the_layout_of_the_c_header(tmp_path):
     """The Python structs are written by hand; a C compiler says what include/brisk_cuda.h really lays out."""
     import subprocess
