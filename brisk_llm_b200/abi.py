@@ -8,13 +8,15 @@ from __future__ import annotations
 import ctypes as C
 import os
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG_DIR, "libbrisk_cuda.so")
 
 ARCH_QWEN3, ARCH_LLAMA, ARCH_BITNET, ARCH_GEMMA3 = 0, 1, 2, 3
 ARCH_BY_NAME = {"qwen3": ARCH_QWEN3, "llama": ARCH_LLAMA, "bitnet": ARCH_BITNET, "bitnet-b1.58": ARCH_BITNET, "gemma3": ARCH_GEMMA3,
-                "smollm3": ARCH_LLAMA}  # llama-shaped; its layers without RoPE are flagged per layer
+                "smollm3": ARCH_LLAMA,
+                "qwen2": ARCH_QWEN3,
+                "phi3": ARCH_QWEN3}  # Phi-3/4-mini: NeoX rotation of the first rope_dim values, no Q/K norms  # Qwen2/2.5: the Qwen3 layer without Q/K norms, with q/k/v biases  # llama-shaped; its layers without RoPE are flagged per layer
 FLAG_NO_GRAPH, FLAG_NO_MEGAKERNEL, FLAG_NO_PERSISTENT = 1, 2, 4
 
 
@@ -41,7 +43,8 @@ class Model(C.Structure):
                 ("rope_factor_count", C.c_uint32), ("rope_factors", _FP), ("token_embd", Matrix), ("output", Matrix),
                 ("output_norm", _FP), ("layers", C.POINTER(Layer)),
                 ("rope_scale", C.c_float), ("rope_base_local", C.c_float), ("sliding_window", C.c_uint32),
-                ("embedding_scale", C.c_float), ("final_softcap", C.c_float), ("gelu", C.c_int32)]
+                ("embedding_scale", C.c_float), ("final_softcap", C.c_float), ("gelu", C.c_int32),
+                ("rope_dim", C.c_uint32), ("rope_attn_factor", C.c_float)]
 
 
 class Options(C.Structure):

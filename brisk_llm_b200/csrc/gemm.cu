@@ -33,6 +33,11 @@ struct Stage {
     static constexpr int kBytes = kA + kAd + kB + kBd + kBs;
 };
 
+__device__ __forceinline__ void cp_async8(void* smem, const void* gmem) {
+    const uint32_t a = uint32_t(__cvta_generic_to_shared(smem));
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(a), "l"(gmem) : "memory");
+}
+
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     const uint32_t a = uint32_t(__cvta_generic_to_shared(smem));
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(a), "l"(gmem) : "memory");
@@ -62,26 +67,40 @@ __global__ void __launch_bounds__(GWARPS * 32, 2) gemm_q8_kernel(const GemmParam
     const uint32_t row_base = blockIdx.x * GM, tok_base = blockIdx.y * GN;
     const uint32_t wr = (warp & 3) * (16 * MI), wt = (warp >> 2) * 32;  // this warp's (16 MI) x 32 corner inside the CTA tile
     const uint32_t nb = p.m.blocks;                              // 32-value blocks per row
-    const uint32_t chunks = nb / KB;
+    // Rows are walked in chunks of KB blocks. A row whose block count is a multiple of 4 but not of 8 (1152 or 896 values)
+    // ends in a chunk of 4 blocks: its other 4 are neither loaded nor multiplied, so every output is still the sum over
+    // its own blocks in order.
+    const uint32_t chunks = (nb + KB - 1) / KB;
+    const bool aligned8 = nb % KB == 0;  // else the f16 scale rows start on 8-byte, not 16-byte, boundaries
 
     auto stage_ptr = [&](int s) { return smem + size_t(s) * S::kBytes; };
     auto load_stage = [&](int s, uint32_t chunk) {
         unsigned char* base = stage_ptr(s);
         const uint32_t b0 = chunk * KB;
+        const uint32_t valid = min(uint32_t(KB), nb - b0);  // blocks of this chunk that exist: KB, or 4 in a short last chunk
         // weights: GM rows x KB*WBYTES bytes, 16-byte pieces
         constexpr int kPiecesA = KB * WBYTES / 16;
         for (uint32_t i = tid; i < GM * kPiecesA; i += GWARPS * 32) {
             const uint32_t r = i / kPiecesA, piece = i % kPiecesA;
+            if (piece * 16 >= valid * WBYTES) continue;
             const uint32_t row = min(row_base + r, p.m.rows - 1);
             cp_async16(base + r * S::kARow + piece * 16, p.m.qa + (size_t(row) * nb + b0) * WBYTES + piece * 16);
         }
         for (uint32_t r = tid; r < GM; r += GWARPS * 32) {
             const uint32_t row = min(row_base + r, p.m.rows - 1);
-            cp_async16(base + S::kA + r * KB * 2, p.m.d + size_t(row) * nb + b0);
+            const __half* src = p.m.d + size_t(row) * nb + b0;
+            unsigned char* dst = base + S::kA + r * KB * 2;
+            if (aligned8) {
+                cp_async16(dst, src);
+            } else {
+                cp_async8(dst, src);
+                if (valid > 4) cp_async8(dst + 8, src + 4);
+            }
         }
         unsigned char* bq = base + S::kA + S::kAd;
         for (uint32_t i = tid; i < GN * (KB * 2); i += GWARPS * 32) {
             const uint32_t r = i / (KB * 2), piece = i % (KB * 2);
+            if (piece >= valid * 2) continue;
             const uint32_t tok = min(tok_base + r, p.n - 1);
             cp_async16(bq + r * S::kBRow + piece * 16, p.act.q0 + size_t(tok) * p.act.cols + b0 * 32 + piece * 16);
         }
@@ -89,6 +108,7 @@ __global__ void __launch_bounds__(GWARPS * 32, 2) gemm_q8_kernel(const GemmParam
         unsigned char* bs = bd + S::kBd;
         for (uint32_t i = tid; i < GN * 2; i += GWARPS * 32) {
             const uint32_t r = i >> 1, piece = i & 1;
+            if (piece * 4 >= valid) continue;
             const uint32_t tok = min(tok_base + r, p.n - 1);
             cp_async16(bd + r * KB * 4 + piece * 16, p.act.d0 + size_t(tok) * nb + b0 + piece * 4);
             cp_async16(bs + r * KB * 4 + piece * 16, p.act.s0 + size_t(tok) * nb + b0 + piece * 4);
@@ -119,8 +139,10 @@ __global__ void __launch_bounds__(GWARPS * 32, 2) gemm_q8_kernel(const GemmParam
         const unsigned char* bq = base + S::kA + S::kAd;
         const float* bd = reinterpret_cast<const float*>(bq + S::kB);
         const int* bs = reinterpret_cast<const int*>(bq + S::kB + S::kBd);
+        const int valid = int(min(uint32_t(KB), nb - chunk * KB));
 #pragma unroll
         for (int b = 0; b < KB; ++b) {
+            if (b >= 4 && valid <= 4) continue;  // the short last chunk of a row of 8k + 4 blocks
             uint32_t a[MI][4];
             float dw[MI][2];
 #pragma unroll
@@ -187,7 +209,8 @@ __global__ void __launch_bounds__(GWARPS * 32, 2) gemm_q8_kernel(const GemmParam
 bool gemm_k_supports(int type);  // gemm_k.cu: the 256-value super-block formats
 void launch_gemm_k(const MatTarget& tg, const DevAct& act, uint32_t n, Epilogue epi, cudaStream_t s);
 
-bool gemm_supports(int type, uint32_t cols) { return ((type == T_Q4_0 || type == T_Q8_0) && cols % (32 * KB) == 0) || gemm_k_supports(type); }
+// Q4_0 / Q8_0 rows of a multiple of 4 blocks (128 values): whole chunks of 8 blocks plus, at most, one chunk of 4.
+bool gemm_supports(int type, uint32_t cols) { return ((type == T_Q4_0 || type == T_Q8_0) && cols % 128 == 0) || gemm_k_supports(type); }
 
 // out = weights x activations for one target (EPI_STORE / EPI_ADD).
 template <int WBYTES, int MI>

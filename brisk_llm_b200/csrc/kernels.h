@@ -92,6 +92,7 @@ struct RopeArgs {
     const float* v;      // [n][kv*dim]
     const float* q_norm; // [dim] or nullptr
     const float* k_norm;
+    uint32_t rope_dim = 0;          // leading values of a head that rotate (Phi's partial rotary); 0: all of them
     const float* q_bias = nullptr;  // [heads*dim] / [kv*dim] projection biases, or nullptr (all three or none)
     const float* k_bias = nullptr;
     const float* v_bias = nullptr;

@@ -143,7 +143,9 @@ __global__ void embed_kernel(const DevMatrix m, const int32_t* tokens, float* __
 __global__ void __launch_bounds__(128) qk_norm_rope_store_kernel(const RopeArgs a) {
     __shared__ float head[512];
     __shared__ double red[4];
-    const uint32_t t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, dim = a.dim, half = dim / 2;
+    // `half` pairs rotate: all dim / 2 of them, or (partial rotary, src/model.cpp:104-115, :1024) only the pairs within the
+    // first rope_dim values - NeoX pairs (i, i + rope_dim / 2) - while the rest of the head passes through.
+    const uint32_t t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, dim = a.dim, half = (a.rope_dim != 0 ? a.rope_dim : dim) / 2;
     const bool is_q = h < a.heads;
     const uint32_t kvh = is_q ? 0 : h - a.heads;
     float* src = is_q ? a.q + size_t(t) * a.heads * dim + size_t(h) * dim : a.k + size_t(t) * a.kv_heads * dim + size_t(kvh) * dim;
@@ -187,6 +189,7 @@ __global__ void __launch_bounds__(128) qk_norm_rope_store_kernel(const RopeArgs 
             src[i0] = out0;
             src[i1] = out1;
         }
+        for (uint32_t i = 2 * half + tid; i < dim; i += 128) src[i] = head[i];  // unrotated tail (biased / normed values)
         return;
     }
     const size_t base = (size_t(kvh) * a.max_context + pos) * dim;
@@ -194,6 +197,7 @@ __global__ void __launch_bounds__(128) qk_norm_rope_store_kernel(const RopeArgs 
         a.k_cache[base + i0] = __float2half_rn(out0);
         a.k_cache[base + i1] = __float2half_rn(out1);
     }
+    for (uint32_t i = 2 * half + tid; i < dim; i += 128) a.k_cache[base + i] = __float2half_rn(head[i]);
     const float* v = a.v + size_t(t) * a.kv_heads * dim + size_t(kvh) * dim;
     if (a.v_bias != nullptr) {
         const float* vb = a.v_bias + size_t(kvh) * dim;

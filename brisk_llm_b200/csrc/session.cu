@@ -162,6 +162,7 @@ struct Session {
     float embedding_scale = 1.0f, final_softcap = 0.0f;
     uint32_t sliding_window = 0;
     bool gelu = false, variant_layers = false;
+    uint32_t rope_dim = 0;  // values of a head that rotate (Phi's partial rotary, src/model.cpp:178, :1024); head_dim: all
     bool unrotated_layers = false;  // SmolLM3: some layers attend without RoPE (src/model.h:97-110)
     int arch = 0, neox = 1, device = 0;
     uint32_t sms = 148;
@@ -332,7 +333,10 @@ struct Session {
         if (heads % kv_heads != 0) throw CudaError("cuda: head_count is not a multiple of head_count_kv");
         if (heads / kv_heads > 8) throw CudaError("cuda: more than 8 query heads per key/value head is not supported");
         if (head_dim != 64 && head_dim != 128 && head_dim != 256) throw CudaError("cuda: head size must be 64, 128 or 256");
-        if (m.rope_factor_count != 0 && m.rope_factor_count != head_dim / 2) throw CudaError("cuda: rope factor count must be head_dim / 2");
+        rope_dim = m.rope_dim != 0 ? m.rope_dim : head_dim;
+        if (rope_dim > head_dim || rope_dim % 2 != 0) throw CudaError("cuda: the rotated width must be even and at most the head size");
+        if (rope_dim != head_dim && !m.rope_neox) throw CudaError("cuda: partial rotary is built for the NeoX pairing");
+        if (m.rope_factor_count != 0 && m.rope_factor_count != rope_dim / 2) throw CudaError("cuda: rope factor count must be half the rotated width");
         q_dim = heads * head_dim;
         kv_dim = kv_heads * head_dim;
         max_context = opt.max_context == 0 ? m.context_length : std::min<uint64_t>(opt.max_context, m.context_length);
@@ -417,6 +421,7 @@ struct Session {
         }
         if (gelu || embedding_scale != 1.0f || final_softcap != 0.0f) variant_layers = true;
         if (head_dim > 128) variant_layers = true;  // the fused single-token kernels take heads of 64 and 128
+        if (rope_dim != head_dim) variant_layers = true;  // ... and rotate whole heads
         BK_CUDA(cudaStreamSynchronize(stream));
         if (m.output.data == nullptr) {
             // A tied head is streamed once per token as the head; the embedding lookup reads one row of it.
@@ -434,25 +439,28 @@ struct Session {
 
         // RoPE table for every position, built like the reference builds it per batch (src/model.cpp:880-892):
         // theta starts at the position and is multiplied by base^(-2/dim) per pair, in f32, with the host's libm.
-        auto build_rope = [&](DevBuffer& dst, float base, float scale, bool factors) {
+        // `width` values of a head rotate; the angles are built for that width (src/model.cpp:880-893). Rows keep the stride
+        // head_dim. cos and sin carry rope_attn_factor (:887-888).
+        const float attn_factor = m.rope_attn_factor != 0.0f ? m.rope_attn_factor : 1.0f;
+        auto build_rope = [&](DevBuffer& dst, float base, float scale, bool factors, uint32_t width) {
             std::vector<float> table(size_t(max_context) * head_dim);
-            const float theta_scale = std::pow(base, -2.0f / static_cast<float>(head_dim));
+            const float theta_scale = std::pow(base, -2.0f / static_cast<float>(width));
             for (uint64_t p = 0; p < max_context; ++p) {
                 float theta = static_cast<float>(p) * scale;
                 float* r = table.data() + p * head_dim;
-                for (uint32_t i = 0; i < head_dim / 2; ++i) {
+                for (uint32_t i = 0; i < width / 2; ++i) {
                     const float angle = factors && m.rope_factor_count != 0 ? theta / m.rope_factors[i] : theta;
-                    r[2 * i] = std::cos(angle) * 1.0f;
-                    r[2 * i + 1] = std::sin(angle) * 1.0f;
+                    r[2 * i] = std::cos(angle) * attn_factor;
+                    r[2 * i + 1] = std::sin(angle) * attn_factor;
                     theta *= theta_scale;
                 }
             }
             dst.alloc(table.size() * sizeof(float));
             BK_CUDA(cudaMemcpy(dst.p, table.data(), table.size() * sizeof(float), cudaMemcpyHostToDevice));
         };
-        build_rope(rope, rope_base, m.rope_scale != 0.0f ? m.rope_scale : 1.0f, true);
+        build_rope(rope, rope_base, m.rope_scale != 0.0f ? m.rope_scale : 1.0f, true, rope_dim);
         // The sliding layers rotate with their own base, an unscaled position and no per-frequency divisors (src/model.cpp:894).
-        if (sliding_window != 0) build_rope(rope_local, m.rope_base_local, 1.0f, false);
+        if (sliding_window != 0) build_rope(rope_local, m.rope_base_local, 1.0f, false, head_dim);
         // A layer without rotation (the reference rotates zero pairs there, src/model.cpp:1024) runs the same kernels over
         // a table of cos = 1, sin = 0: x0 * 1 - x1 * 0 and x0 * 0 + x1 * 1 return x0 and x1 themselves.
         if (unrotated_layers) {
@@ -524,7 +532,7 @@ struct Session {
         const char* env = std::getenv("BRISK_CUDA_STEP");
         if (tp_size > 1) step_note = "off: tensor parallel steps exchange activations between the operations";
         else if (unrotated_layers) step_note = "off: layers without RoPE take the per-operation kernels (the persistent kernel rotates every layer with one table)";
-        else if (variant_layers) step_note = "off: Gemma layer variants (post-norms, GELU, sliding window) and 256-wide heads run through the batched kernels";
+        else if (variant_layers) step_note = "off: Gemma layer variants (post-norms, GELU, sliding window), 256-wide heads and partial rotary run through the batched kernels";
         else if (flags & (BRISK_CUDA_FLAG_NO_MEGAKERNEL | BRISK_CUDA_FLAG_NO_PERSISTENT)) step_note = "off: disabled by the session's flags";
         else if (env != nullptr && std::strcmp(env, "0") == 0) step_note = "off: BRISK_CUDA_STEP=0";
         else if (trace.p != nullptr) step_note = "off: tracing the per-operation kernels";
@@ -677,6 +685,7 @@ struct Session {
             r.k_cache = L.k_cache; r.v_cache = L.v_cache; r.position = d_position();
             r.n = n; r.heads = heads_l; r.kv_heads = kv_heads_l; r.dim = head_dim; r.max_context = uint32_t(max_context);
             r.eps = eps; r.neox = neox;
+            r.rope_dim = (L.slides || L.no_rope) ? 0 : rope_dim;  // those tables span the whole head
             AttnArgs at{};
             at.q = q_b.as<float>(); at.k_cache = L.k_cache; at.v_cache = L.v_cache; at.out = attended_b.as<float>();
             at.scores = partial.as<float>(); at.position = d_position();

@@ -16,7 +16,7 @@ from .synth import HostModel, ModelSpec
 
 ALIGN = 32
 _U32, _F32, _STR, _U64 = 4, 6, 8, 10
-ARCH_NAME = {"qwen3": "qwen3", "llama": "llama", "bitnet": "bitnet-b1.58", "gemma3": "gemma3", "smollm3": "smollm3"}
+ARCH_NAME = {"qwen3": "qwen3", "llama": "llama", "bitnet": "bitnet-b1.58", "gemma3": "gemma3", "smollm3": "smollm3", "qwen2": "qwen2", "phi3": "phi3"}
 
 
 def _s(b: bytes) -> bytes:
@@ -36,7 +36,24 @@ def write_gguf(model: HostModel, path: str) -> None:
         kv += [(f"{arch}.attention.sliding_window", _U32, s.sliding_window), (f"{arch}.rope.freq_base_swa", _F32, s.rope_base_local),
                (f"{arch}.rope.scaling.factor", _F32, s.rope_scaling_factor), (f"{arch}.final_logit_softcapping", _F32, s.final_softcap)]
     tensors = dict(model.tensors)
-    if model.rope_factors is not None:
+    if s.arch == "phi3":  # src/model.cpp:177-188; Q, K, V rows in one tensor, gate and up rows in another (:370-382)
+        kv += [(f"{arch}.rope.dimension_count", _U32, s.rope_dim or s.head_dim), (f"{arch}.rope.scaling.attn_factor", _F32, s.rope_attn_factor),
+               (f"{arch}.rope.scaling.original_context_length", _U32, s.rope_original_context)]
+        fused = {}
+        for name, entry in tensors.items():
+            if name.endswith(("attn_k.weight", "attn_v.weight", "ffn_gate.weight")):
+                continue
+            if name.endswith("attn_q.weight") or name.endswith("ffn_up.weight"):
+                p = name[:name.rindex(".weight")].rsplit(".", 1)[0] + "."
+                parts = ["attn_q.weight", "attn_k.weight", "attn_v.weight"] if name.endswith("attn_q.weight") else ["ffn_gate.weight", "ffn_up.weight"]
+                group = [tensors[p + q] for q in parts]
+                assert len({g[0] for g in group}) == 1, "fused tensors need one type"
+                fused[p + ("attn_qkv.weight" if len(parts) == 3 else "ffn_up.weight")] = (
+                    group[0][0], (sum(g[1][0] for g in group), group[0][1][1]), np.concatenate([np.ascontiguousarray(g[2]).reshape(-1) for g in group]))
+            else:
+                fused[name] = entry
+        tensors = fused
+    if model.rope_factors is not None and s.arch != "phi3":
         tensors["rope_freqs.weight"] = (F.F32, (1, len(model.rope_factors)), model.rope_factors)
     head = bytearray(b"GGUF" + struct.pack("<IQQ", 3, len(tensors), len(kv)))
     for key, typ, val in kv:
@@ -111,9 +128,9 @@ def read_gguf(path: str) -> HostModel:
     align = meta.get("general.alignment", ALIGN)
     base = (r.p + align - 1) // align * align
     arch = meta["general.architecture"]
-    fam = {"qwen3": "qwen3", "llama": "llama", "bitnet": "bitnet", "bitnet-b1.58": "bitnet", "gemma3": "gemma3", "smollm3": "smollm3"}.get(arch)
+    fam = {"qwen3": "qwen3", "llama": "llama", "bitnet": "bitnet", "bitnet-b1.58": "bitnet", "gemma3": "gemma3", "smollm3": "smollm3", "qwen2": "qwen2"}.get(arch)
     if fam is None:
-        raise ValueError(f"gguf: architecture '{arch}' is not one this backend runs (qwen3, llama, bitnet, gemma3, smollm3)")
+        raise ValueError(f"gguf: architecture '{arch}' is not one this backend runs (qwen3, qwen2, llama, bitnet, gemma3, smollm3)")
     g = lambda k, d=None: meta.get(f"{arch}.{k}", d)
     tensors, rope = {}, None
     for name, dims, typ, off in infos:

@@ -7,6 +7,7 @@
 // file's own F16 bytes. Errors are rethrown as std::runtime_error("cuda: ...") like the reference's backends.
 #pragma once
 
+#include <algorithm>
 #include <stdexcept>
 #include <string>
 #include <string_view>
@@ -29,11 +30,13 @@ public:
         int arch;
         switch (c.architecture) {
             case Architecture::Qwen3: arch = BRISK_ARCH_QWEN3; break;
+            case Architecture::Qwen2: arch = BRISK_ARCH_QWEN3; break;  // the same layer without Q/K norms (NULL) and with q/k/v biases
+            case Architecture::Phi3: arch = BRISK_ARCH_QWEN3; break;   // ... with partial rotary; the loader has split its fused tensors
             case Architecture::Llama: arch = BRISK_ARCH_LLAMA; break;
             case Architecture::BitNet: arch = BRISK_ARCH_BITNET; break;
             case Architecture::Gemma3: arch = BRISK_ARCH_GEMMA3; break;
             case Architecture::SmolLM3: arch = BRISK_ARCH_LLAMA; break;  // llama-shaped; its layers without RoPE are flagged below
-            default: throw std::runtime_error("cuda: this architecture is not supported by the CUDA backend (qwen3, llama, bitnet, gemma3, smollm3 are)");
+            default: throw std::runtime_error("cuda: this architecture is not supported by the CUDA backend (qwen3, qwen2, llama, bitnet, gemma3, smollm3, phi3 are)");
         }
         std::vector<brisk_cuda_layer> layers(c.layer_count);
         for (std::size_t i = 0; i < layers.size(); ++i) {
@@ -75,8 +78,14 @@ public:
         d.rope_base = c.rope_base;
         d.rms_epsilon = c.rms_epsilon;
         d.rope_neox = c.rope_neox ? 1 : 0;
-        d.rope_factor_count = static_cast<std::uint32_t>(c.rope_factors.size());
-        d.rope_factors = c.rope_factors.empty() ? nullptr : c.rope_factors.data();
+        // LongRoPE: a session whose context exceeds the original one takes the long divisors (src/model.cpp:691-694).
+        const std::size_t context = max_context == 0 ? c.context_length : std::min<std::size_t>(max_context, c.context_length);
+        const std::vector<float>& factors =
+            !c.rope_factors_long.empty() && c.rope_original_context != 0 && context > c.rope_original_context ? c.rope_factors_long : c.rope_factors;
+        d.rope_factor_count = static_cast<std::uint32_t>(factors.size());
+        d.rope_factors = factors.empty() ? nullptr : factors.data();
+        d.rope_dim = c.rope_dim;
+        d.rope_attn_factor = c.rope_attn_factor;
         d.token_embd = describe(model.token_embedding(), file, "token_embd.weight");
         if (file.tensor("output.weight") != nullptr) d.output = describe(model.output_projection(), file, "output.weight");
         d.output_norm = model.output_norm().data();

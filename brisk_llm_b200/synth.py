@@ -20,7 +20,7 @@ from . import abi, formats as F
 @dataclass(frozen=True)
 class ModelSpec:
     name: str
-    arch: str  # "qwen3" | "llama" | "bitnet" | "gemma3" | "smollm3"
+    arch: str  # "qwen3" | "qwen2" | "llama" | "bitnet" | "gemma3" | "smollm3" | "phi3"
     layers: int
     hidden: int
     heads: int
@@ -43,6 +43,11 @@ class ModelSpec:
     rope_base_local: float = 10000.0
     rope_scaling_factor: float = 1.0
     final_softcap: float = 0.0
+    # Phi-3 / Phi-4-mini (src/model.cpp:177-188): values of a head that rotate (0: all), the factor on cos and sin, and the
+    # context up to which the short LongRoPE divisors apply (0: no divisors)
+    rope_dim: int = 0
+    rope_attn_factor: float = 1.0
+    rope_original_context: int = 0
 
     def layer_has_rope(self, layer: int) -> bool:
         """SmolLM3: every fourth layer attends without positional rotation (src/model.cpp:168, src/model.h:97-110)."""
@@ -155,6 +160,11 @@ class HostModel:
         m.context_length = s.context
         m.rope_base, m.rms_epsilon = s.rope_base, s.eps
         m.rope_neox = 0 if s.arch in ("llama", "smollm3") else 1  # brisk-llm src/model.cpp:167
+        if s.arch == "phi3":
+            m.rope_dim, m.rope_attn_factor = s.rope_dim, s.rope_attn_factor
+            if "rope_factors_short.weight" in self.tensors:  # a session picks by its context (src/model.cpp:691-694)
+                which = "rope_factors_long.weight" if s.context > s.rope_original_context else "rope_factors_short.weight"
+                self.rope_factors = self.tensors[which][2]
         if self.rope_factors is not None:
             m.rope_factor_count = len(self.rope_factors)
             m.rope_factors = self.rope_factors.ctypes.data_as(C.POINTER(C.c_float))
@@ -207,6 +217,10 @@ def generate(spec: ModelSpec, seed: int = 0, share_layers: bool = False) -> Host
     if not spec.tied:
         matrix("output.weight", "output", spec.vocab, spec.hidden)
     ones("output_norm.weight", spec.hidden)
+    if spec.arch == "phi3" and spec.rope_original_context:
+        half = (spec.rope_dim or spec.head_dim) // 2
+        t["rope_factors_short.weight"] = (F.F32, (1, half), (1.0 + 0.05 * rng.random(half)).astype(np.float32))
+        t["rope_factors_long.weight"] = (F.F32, (1, half), (1.0 + 3.0 * rng.random(half)).astype(np.float32))
     for i in range(spec.layers):
         p = f"blk.{i}."
         if share_layers and i > 0:

@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define BRISK_CUDA_ABI_VERSION 3u
+#define BRISK_CUDA_ABI_VERSION 4u
 
 /* Tensor storage types, numbered as in ggml / the reference's TensorType (src/gguf.h:22-27).
  * Quantised data is passed exactly as it lies in a GGUF file: row after row of blocks
@@ -108,7 +108,7 @@ typedef struct brisk_cuda_model {
     float rope_base;
     float rms_epsilon;
     int32_t rope_neox;           /* 1: pair (i, i+head_dim/2); 0: pair (2i, 2i+1)          */
-    uint32_t rope_factor_count;  /* 0 or head_dim/2                                        */
+    uint32_t rope_factor_count;  /* 0 or (rope_dim ? rope_dim : head_dim) / 2              */
     const float* rope_factors;   /* per-frequency divisors of the angle (src/model.cpp:886) */
     brisk_cuda_matrix token_embd; /* vocab x hidden                                        */
     brisk_cuda_matrix output;     /* vocab x hidden; data == NULL: tied to token_embd       */
@@ -122,6 +122,12 @@ typedef struct brisk_cuda_model {
     float embedding_scale;   /* embedding rows are multiplied by this (sqrt(hidden), src/model.cpp:899-901); 0 means 1 */
     float final_softcap;     /* logits = c * tanh(logits / c) when non-zero (src/model.cpp:1206-1209)                */
     int32_t gelu;            /* 1: gate with tanh-GELU instead of SiLU (src/model.cpp:1139-1140)                     */
+    /* Phi-3 / Phi-4-mini (src/model.cpp:177-188, src/model.h:54-62). */
+    uint32_t rope_dim;       /* leading values of a head that rotate (partial rotary); 0: all head_dim of them. The angles
+                                are built for this width (src/model.cpp:893) and rope_factor_count is then rope_dim / 2     */
+    float rope_attn_factor;  /* cos and sin are multiplied by this (src/model.cpp:887-888); 0 means 1. rope_factors are the
+                                short or the long LongRoPE divisors, whichever the session's context selects
+                                (src/model.cpp:691-694)                                                                 */
 } brisk_cuda_model;
 
 typedef struct brisk_cuda_options {

@@ -704,15 +704,18 @@ static void eval_batch(oracle_session* s, const int32_t* tokens, size_t n, int a
     const int bitnet = c->arch == BRISK_ARCH_BITNET;
 
     /* cos/sin by repeated multiplication from pos (src/model.cpp:880-892). */
-    const float theta_scale = powf(c->rope_base, -2.0f / (float)D);
+    /* Phi rotates only the first rope_dim values of a head; the angles are built for that width (:893, :1024). */
+    const size_t RD = c->rope_dim != 0 && c->rope_dim < D ? c->rope_dim : D;
+    const float attn_factor = c->rope_attn_factor != 0.0f ? c->rope_attn_factor : 1.0f;
+    const float theta_scale = powf(c->rope_base, -2.0f / (float)RD);
     const float rope_scale = c->rope_scale != 0.0f ? c->rope_scale : 1.0f;
     for (size_t t = 0; t < n; ++t) {
         float theta = (float)(s->position + t) * rope_scale;
         float* rope = s->rope + t * D;
-        for (size_t i = 0; i < D / 2; ++i) {
+        for (size_t i = 0; i < RD / 2; ++i) {
             const float angle = c->rope_factor_count ? theta / c->rope_factors[i] : theta;
-            rope[2 * i] = cosf(angle) * 1.0f;
-            rope[2 * i + 1] = sinf(angle) * 1.0f;
+            rope[2 * i] = cosf(angle) * attn_factor;
+            rope[2 * i + 1] = sinf(angle) * attn_factor;
             theta *= theta_scale;
         }
     }
@@ -742,7 +745,9 @@ static void eval_batch(oracle_session* s, const int32_t* tokens, size_t n, int a
         mm(&L->k, s->normed, n, s->newk);
         mm(&L->v, s->normed, n, s->newv);
         for (size_t t = 0; t < n; ++t) { /* :1022-1046 */
-            const float* rope = (L->slides && c->sliding_window != 0 ? s->rope_local : s->rope) + t * D; /* :1024 */
+            const int local = L->slides && c->sliding_window != 0;
+            const float* rope = (local ? s->rope_local : s->rope) + t * D; /* :1024-1025 */
+            const size_t W = local ? D : RD; /* rotated width */
             if (L->q_bias) { /* add_bias, :1026-1030 (src/model.cpp:117-119) */
                 for (size_t i = 0; i < Q; ++i) s->query[t * Q + i] += L->q_bias[i];
                 for (size_t i = 0; i < KV; ++i) s->newk[t * KV + i] += L->k_bias[i];
@@ -751,13 +756,13 @@ static void eval_batch(oracle_session* s, const int32_t* tokens, size_t n, int a
             for (size_t h = 0; h < c->head_count; ++h) {
                 float* q = s->query + t * Q + h * D;
                 if (L->q_norm) rms_norm(q, L->q_norm, eps, q, D);
-                if (!L->no_rope) apply_rope(q, rope, D, c->rope_neox); /* rope_dim 0 on SmolLM3's NoPE layers, :1024 */
+                if (!L->no_rope) apply_rope(q, rope, W, c->rope_neox); /* rope_dim 0 on SmolLM3's NoPE layers, :1024 */
             }
             for (size_t h = 0; h < c->kv_head_count; ++h) {
                 float* k = s->newk + t * KV + h * D;
                 float* v = s->newv + t * KV + h * D;
                 if (L->k_norm) rms_norm(k, L->k_norm, eps, k, D);
-                if (!L->no_rope) apply_rope(k, rope, D, c->rope_neox);
+                if (!L->no_rope) apply_rope(k, rope, W, c->rope_neox);
                 uint16_t* kc = s->keys[l] + (h * s->max_context + s->position + t) * D;
                 uint16_t* vc = s->values[l] + (h * s->max_context + s->position + t) * D;
                 for (size_t i = 0; i < D; ++i) {

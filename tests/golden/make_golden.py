@@ -32,6 +32,11 @@ MORE_FAMILIES = {
     "biased": synth.tiny(synth.MISTRAL_7B, hidden=256, heads=4, kv_heads=2, ffn=512, vocab=256, qkv_bias=True, fmt=F.Q8_0),
     "mixed": synth.tiny(synth.QWEN3_0_6B, hidden=256, heads=4, kv_heads=2, ffn=512, vocab=256, tied=False, fmt=F.Q5_K,
                         fmt_overrides={"v": F.Q4_1, "down": F.Q5_0, "embd": F.Q4_1, "output": F.BF16}),
+    # Phi-4-mini's layer: partial rotary (96 of 128), scaled cos/sin, short LongRoPE divisors, fused tensors in the file
+    "phi3": synth.tiny(synth.MISTRAL_7B, arch="phi3", hidden=384, heads=3, kv_heads=1, head_dim=128, ffn=768, vocab=256,
+                       rope_dim=96, rope_attn_factor=1.19, rope_original_context=1024),
+    # Qwen2.5's layer: the qwen2 architecture id, biases, 6 query heads per K/V head
+    "qwen2": synth.tiny(synth.MISTRAL_7B, arch="qwen2", hidden=384, heads=6, kv_heads=1, head_dim=64, ffn=768, vocab=256, qkv_bias=True),
     # SmolLM3: llama-shaped, the fourth layer attends without RoPE
     "smollm3": synth.tiny(synth.LLAMA_3_2_1B, arch="smollm3", layers=4, hidden=256, heads=8, kv_heads=2, ffn=512, vocab=256),
     # Gemma 3 layers: six sliding layers (window 16) around one global layer, soft-capped logits

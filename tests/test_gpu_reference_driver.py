@@ -19,6 +19,9 @@ DRIVER = os.path.join(H.ORACLE_DIR, "_ref", "ref_driver")
     ("qwen3", synth.tiny(synth.QWEN3_0_6B, layers=3, vocab=1024, hidden=512, heads=8, kv_heads=4, ffn=1024)),
     ("llama", synth.tiny(synth.LLAMA_3_2_1B, layers=2, vocab=1024, hidden=512, heads=8, kv_heads=2, ffn=1024)),
     ("bitnet", synth.tiny(synth.BITNET_2B, layers=2, vocab=1024, hidden=512, heads=4, kv_heads=1, ffn=768)),
+    ("phi3", synth.tiny(synth.MISTRAL_7B, arch="phi3", layers=2, vocab=1024, hidden=384, heads=3, kv_heads=1, head_dim=128, ffn=768,
+                        rope_dim=96, rope_attn_factor=1.19, rope_original_context=128)),
+    ("qwen2", synth.tiny(synth.MISTRAL_7B, arch="qwen2", layers=2, vocab=1024, hidden=384, heads=6, kv_heads=1, head_dim=64, ffn=768, qkv_bias=True)),
     ("gemma3", synth.tiny(synth.QWEN3_0_6B, arch="gemma3", layers=7, vocab=1024, hidden=512, heads=8, kv_heads=4, ffn=1024,
                           sliding_window=16, rope_scaling_factor=8.0, final_softcap=30.0)),
 ])

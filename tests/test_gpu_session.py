@@ -139,6 +139,12 @@ def test_sliding_window_layers_are_bit_exact_without_a_tanh():
     # the formats beyond the benchmark configurations (Q5_K, Q4_1, Q5_0, a BF16 head), mixed as stock downloads mix them
     ("mixed", synth.tiny(synth.QWEN3_0_6B, layers=2, vocab=1024, context=1024, tied=False, fmt=formats.Q5_K,
                          fmt_overrides={"v": formats.Q4_1, "down": formats.Q5_0, "embd": formats.Q4_1, "output": formats.BF16})),
+    # Phi-4-mini's layer at its own widths: 24 query heads on 8 K/V heads, the first 96 of 128 values rotate, scaled cos/sin,
+    # the long LongRoPE divisors
+    ("phi3", synth.tiny(synth.MISTRAL_7B, arch="phi3", layers=2, vocab=1024, context=1024, hidden=3072, heads=24, kv_heads=8, head_dim=128,
+                        ffn=8192, rope_dim=96, rope_attn_factor=1.19, rope_original_context=512)),
+    # the qwen2 architecture id: NeoX rotation, biases, no Q/K norms
+    ("qwen2", synth.tiny(synth.MISTRAL_7B, arch="qwen2", layers=2, vocab=1024, context=1024, hidden=1536, heads=12, kv_heads=2, head_dim=128, ffn=2048, qkv_bias=True)),
     # 5 and 6 query heads per K/V head (Qwen2.5-14B, Qwen2.5-1.5B)
     ("group5", synth.tiny(synth.QWEN3_0_6B, layers=2, vocab=1024, context=1024, hidden=640, heads=5, kv_heads=1, ffn=1280)),
     ("group6", synth.tiny(synth.MISTRAL_7B, layers=2, vocab=1024, context=1024, hidden=768, heads=12, kv_heads=2, head_dim=64, ffn=1536, qkv_bias=True)),

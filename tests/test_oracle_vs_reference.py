@@ -54,6 +54,14 @@ def test_f16_head_bit_exact():
     # layer 5 is global with a scaled position, soft-capped logits (src/model.cpp:169-176, :1084-1085, :1116-1119, :1206-1209)
     ("gemma3", synth.tiny(synth.QWEN3_0_6B, arch="gemma3", layers=7, hidden=256, heads=4, kv_heads=2, ffn=512, context=512,
                           sliding_window=64, rope_scaling_factor=8.0, final_softcap=30.0)),
+    # Qwen2.5-1.5B's geometry: 6 query heads per K/V head, q/k/v biases, NeoX rotation, no Q/K norms
+    ("qwen2", synth.tiny(synth.MISTRAL_7B, arch="qwen2", hidden=384, heads=6, kv_heads=1, head_dim=64, ffn=768, context=512, qkv_bias=True)),
+    # Phi-4-mini's layer: fused QKV and gate/up tensors in the file, 3 query heads per K/V head, the first 96 of 128 values
+    # rotate, cos/sin scaled, LongRoPE divisors - the long ones (context past the original one) and the short ones
+    ("phi3-long", synth.tiny(synth.MISTRAL_7B, arch="phi3", hidden=384, heads=3, kv_heads=1, head_dim=128, ffn=768, context=512,
+                             rope_dim=96, rope_attn_factor=1.19, rope_original_context=256)),
+    ("phi3-short", synth.tiny(synth.MISTRAL_7B, arch="phi3", hidden=384, heads=3, kv_heads=1, head_dim=128, ffn=768, context=512,
+                              rope_dim=96, rope_attn_factor=1.19, rope_original_context=1024)),
     # SmolLM3: llama-shaped, the fourth layer attends without RoPE (src/model.cpp:168, :1024)
     ("smollm3", synth.tiny(synth.LLAMA_3_2_1B, arch="smollm3", layers=5, hidden=512, heads=8, kv_heads=2, ffn=1024, context=512)),
     # Gemma 3's head geometry: 256-wide heads, one K/V head for four query heads
