@@ -128,9 +128,9 @@ def read_gguf(path: str) -> HostModel:
     align = meta.get("general.alignment", ALIGN)
     base = (r.p + align - 1) // align * align
     arch = meta["general.architecture"]
-    fam = {"qwen3": "qwen3", "llama": "llama", "bitnet": "bitnet", "bitnet-b1.58": "bitnet", "gemma3": "gemma3", "smollm3": "smollm3", "qwen2": "qwen2"}.get(arch)
+    fam = {"qwen3": "qwen3", "llama": "llama", "bitnet": "bitnet", "bitnet-b1.58": "bitnet", "gemma3": "gemma3", "smollm3": "smollm3", "qwen2": "qwen2", "phi3": "phi3"}.get(arch)
     if fam is None:
-        raise ValueError(f"gguf: architecture '{arch}' is not one this backend runs (qwen3, qwen2, llama, bitnet, gemma3, smollm3)")
+        raise ValueError(f"gguf: architecture '{arch}' is not one this backend runs (qwen3, qwen2, llama, bitnet, gemma3, smollm3, phi3)")
     g = lambda k, d=None: meta.get(f"{arch}.{k}", d)
     tensors, rope = {}, None
     for name, dims, typ, off in infos:
@@ -148,11 +148,30 @@ def read_gguf(path: str) -> HostModel:
         else:
             tensors[name] = (typ, (rows, cols), raw)
     hidden, heads = g("embedding_length"), g("attention.head_count")
+    if fam == "phi3":  # split the fused tensors by rows, as the reference's loader does (src/model.cpp:370-382)
+        kv_heads = g("attention.head_count_kv")
+        head_dim = g("attention.key_length", hidden // heads)
+        for name in [n for n in tensors if n.endswith("attn_qkv.weight") or n.endswith("ffn_up.weight")]:
+            typ, (rows, cols), raw = tensors.pop(name)
+            rb = F.row_bytes(typ, cols)
+            p = name.rsplit(".", 2)[0] + "."
+            if name.endswith("attn_qkv.weight"):
+                parts = [("attn_q.weight", heads * head_dim), ("attn_k.weight", kv_heads * head_dim), ("attn_v.weight", kv_heads * head_dim)]
+            else:
+                parts = [("ffn_gate.weight", rows // 2), ("ffn_up.weight", rows // 2)]
+            at = 0
+            for part, n_rows in parts:
+                tensors[p + part] = (typ, (n_rows, cols), raw[at * rb:(at + n_rows) * rb])
+                at += n_rows
     emb = tensors["token_embd.weight"]
     spec = ModelSpec(meta.get("general.name", "gguf"), fam, g("block_count"), hidden, heads, g("attention.head_count_kv"),
                      g("attention.key_length", hidden // heads), g("feed_forward_length"), emb[1][0], g("context_length"),
                      g("rope.freq_base"), g("attention.layer_norm_rms_epsilon"), "output.weight" not in tensors,
                      tensors["blk.0.attn_q.weight"][0])
+    if fam == "phi3":
+        from dataclasses import replace
+        spec = replace(spec, rope_dim=g("rope.dimension_count", 0), rope_attn_factor=g("rope.scaling.attn_factor", 1.0),
+                       rope_original_context=g("rope.scaling.original_context_length", 0))
     if fam == "gemma3":
         from dataclasses import replace
         spec = replace(spec, sliding_window=g("attention.sliding_window", 0), rope_base_local=g("rope.freq_base_swa", 10000.0),

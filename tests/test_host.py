@@ -110,6 +110,38 @@ def test_device_memory_estimate_needs_no_gpu():
     assert tp2["cache"] * 2 == e["cache"] and tp2["weights"] < e["weights"]
 
 
+@pytest.mark.parametrize("spec", [
+    synth.tiny(synth.MISTRAL_7B, arch="phi3", hidden=384, heads=3, kv_heads=1, head_dim=128, ffn=768, vocab=256, rope_dim=96,
+               rope_attn_factor=1.19, rope_original_context=128),
+    synth.tiny(synth.QWEN3_0_6B, arch="gemma3", layers=7, hidden=256, heads=4, kv_heads=2, ffn=512, vocab=256, sliding_window=16,
+               rope_scaling_factor=8.0, final_softcap=30.0),
+    synth.tiny(synth.LLAMA_3_2_1B, arch="smollm3", layers=4, hidden=256, heads=8, kv_heads=2, ffn=512, vocab=256),
+    synth.tiny(synth.MISTRAL_7B, arch="qwen2", hidden=384, heads=6, kv_heads=1, head_dim=64, ffn=768, vocab=256, qkv_bias=True),
+], ids=lambda s: s.arch)
+def test_gguf_round_trip_of_the_layer_variants(spec, tmp_path):
+    """What write_gguf puts into a file (Phi's fused QKV and gate/up tensors, Gemma's and Phi's metadata) comes back from
+    read_gguf as the same tensors and the same model description."""
+    from brisk_llm_b200 import gguf_io
+    m = synth.perturb_norms(synth.generate(spec, seed=4))
+    path = str(tmp_path / "m.gguf")
+    gguf_io.write_gguf(m, path)
+    back = gguf_io.read_gguf(path)
+    assert set(back.tensors) >= {n for n in m.tensors}
+    for name, (fmt, shape, data) in m.tensors.items():
+        bf, bs, bd = back.tensors[name]
+        assert (bf, tuple(bs)) == (fmt, tuple(shape)), name
+        assert np.array_equal(np.asarray(bd).view(np.uint8).reshape(-1), np.ascontiguousarray(data).view(np.uint8).reshape(-1)), name
+    a, b = m.c_model, back.c_model
+    for field in ("arch", "vocab_size", "hidden", "layer_count", "head_count", "kv_head_count", "head_dim", "ffn", "context_length", "rope_neox",
+                  "rope_factor_count", "sliding_window", "gelu", "rope_dim"):
+        assert getattr(a, field) == getattr(b, field), field
+    for field in ("rope_base", "rms_epsilon", "rope_scale", "rope_base_local", "embedding_scale", "final_softcap", "rope_attn_factor"):
+        assert getattr(a, field) == pytest.approx(getattr(b, field)), field
+    for i in range(spec.layers):
+        assert (a.layers[i].slides, a.layers[i].no_rope) == (b.layers[i].slides, b.layers[i].no_rope)
+        assert bool(a.layers[i].attn_post_norm) == bool(b.layers[i].attn_post_norm) and bool(a.layers[i].q_bias) == bool(b.layers[i].q_bias)
+
+
 def test_memory_estimate_counts_the_gemma_tables():
     """A model whose GELU or soft cap needs the tanh correction table (one 4-bit entry per float of [2^-25, 22)) and a
     second RoPE table for its sliding layers is estimated with them."""
