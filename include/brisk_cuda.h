@@ -40,7 +40,9 @@ enum brisk_cuda_type {
     BRISK_TYPE_TQ2_0 = 35
 };
 
-/* Model families of the configured workloads (subset of brisk::Architecture, src/model.h:20-31). */
+/* Layer families (subset of brisk::Architecture, src/model.h:20-31). The id selects the gate activation and little
+ * else; what a family needs beyond it travels in the fields below (absent norms are NULL, biases, no_rope, rope_dim ...).
+ * Qwen2 and Phi3 files are described as BRISK_ARCH_QWEN3, SmolLM3 as BRISK_ARCH_LLAMA. */
 enum brisk_cuda_arch {
     BRISK_ARCH_QWEN3 = 0,  /* per-head RMS norm on Q and K, SiLU-gated FFN, NeoX RoPE            */
     BRISK_ARCH_LLAMA = 1,  /* adjacent-pair RoPE, optional per-frequency divisors (rope_freqs)  */
