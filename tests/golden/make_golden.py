@@ -1,6 +1,8 @@
 """Generates tests/golden/*.npz from the UNMODIFIED reference CPU engine (oracle/_ref/libbrisk_ref.so).
 
 Run where a reference checkout is present:  make -C oracle ref && python tests/golden/make_golden.py
+(`--family NAME` writes model_NAME.npz of one of MORE_FAMILIES and leaves every other file untouched; so do
+`--more-families-only` and `--more-formats-only` for their groups.)
 The fixtures pin the C oracle (and through it the CUDA library) on machines that have no reference:
   primitives.npz  f16 conversions, quantize_q8_0 / quantize_q8_k bytes, dequantised rows and matvec/matmul
                   outputs of every format on seeded inputs (the shapes of the reference's kernels_test:
