@@ -26,7 +26,11 @@ WORKER = textwrap.dedent(r'''
     rank, local, world = parallel.env_rank()
     torch.cuda.set_device(local)
     dist.init_process_group("gloo")
-    spec = synth.tiny(synth.MISTRAL_7B, layers=2, vocab=1024, hidden=1024, heads=8, kv_heads=4, ffn=2048, context=512)
+    if sys.argv[3] == "gemma3":  # post-norms read the gathered projection, the GELU runs on this rank's slice, soft-capped logits
+        spec = synth.tiny(synth.QWEN3_0_6B, arch="gemma3", layers=7, vocab=1024, hidden=1024, heads=8, kv_heads=4, ffn=2048, context=512,
+                          sliding_window=16, rope_scaling_factor=8.0, final_softcap=30.0)
+    else:
+        spec = synth.tiny(synth.MISTRAL_7B, layers=2, vocab=1024, hidden=1024, heads=8, kv_heads=4, ffn=2048, context=512)
     model = synth.perturb_norms(synth.generate(spec, seed=4))
     toks = synth.random_tokens(spec, 80, seed=5)
     mark("model ready")
@@ -59,16 +63,17 @@ WORKER = textwrap.dedent(r'''
 ''')
 
 
-def test_two_rank_tensor_parallel_matches_the_oracle(tmp_path):
+@pytest.mark.parametrize("family", ["llama", "gemma3"])
+def test_two_rank_tensor_parallel_matches_the_oracle(family, tmp_path):
     from brisk_llm_b200 import engine
     if engine.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     script = tmp_path / "tp_worker.py"
     script.write_text(WORKER)
-    port = 29700 + os.getpid() % 200
+    port = 29700 + os.getpid() % 200 + (0 if family == "llama" else 211)
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", NCCL_IB_DISABLE="1", NCCL_SOCKET_IFNAME="lo", NCCL_DEBUG="WARN")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", str(port), str(script), H.ROOT, str(tmp_path)]
+           "--master-port", str(port), str(script), H.ROOT, str(tmp_path), family]
     try:
         r = subprocess.run(cmd, capture_output=True, text=True, timeout=200, env=env)
     except subprocess.TimeoutExpired as e:
