@@ -88,6 +88,21 @@ void build_tanh_table(uint8_t* table, unsigned threads, cudaStream_t s) {
     std::vector<uint8_t> packed(tanh_table_bytes());
     std::string failure;
     std::mutex failure_lock;
+    // Outside the table both sides must agree by themselves: tanhf(x) == x below 2^-25 and == 1 from 22 on (the device's
+    // base function returns exactly that). Sampled, every 65537th float, so that a C library for which this does not hold
+    // is refused instead of silently disagreeing.
+    auto outside = [&](uint32_t first, uint32_t last, bool small) {
+        for (uint32_t u = first; u < last; u += 65537u) {
+            float x;
+            std::memcpy(&x, &u, sizeof x);
+            const float want = small ? x : 1.0f, got = ::tanhf(x);
+            if (std::memcmp(&want, &got, sizeof want) != 0) {
+                throw CudaError("cuda: the host library's tanhf leaves the range the correction table covers (set BRISK_CUDA_TANH_TABLE=0 to run without it)");
+            }
+        }
+    };
+    outside(1u, kTanhTableLo, true);
+    outside(kTanhTableHi, 0x7f800000u, false);
     auto request = [&](uint32_t c0, int slot) {
         const uint32_t n = std::min(kChunk, total - c0);
         tanh_base_kernel<<<(n + 255) / 256, 256, 0, s>>>(kTanhTableLo + c0, n, buf.dev[slot]);
