@@ -39,11 +39,8 @@ __global__ void __launch_bounds__(256) norm_quant_kernel(const float* __restrict
 void launch_norm_quant(const float* x, uint32_t ldx, const float* weight, float eps, uint32_t n, uint32_t cols,
                        const DevActMut& act, bool want0, bool wantk, cudaStream_t s) {
     const size_t smem = size_t(cols) * sizeof(float);
-    static bool raised = false;
-    if (smem > 48 * 1024 && !raised) {
-        BK_CUDA(cudaFuncSetAttribute(norm_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        raised = true;
-    }
+    static DeviceOnce once;
+    if (smem > 48 * 1024 && once.first()) BK_CUDA(cudaFuncSetAttribute(norm_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     norm_quant_kernel<<<n, 256, smem, s>>>(x, ldx, weight, eps, cols, act, want0 ? 1 : 0, wantk ? 1 : 0);
     BK_CUDA(cudaGetLastError());
 }

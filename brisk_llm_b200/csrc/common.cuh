@@ -7,6 +7,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstddef>
 #include <cstdint>
 #include <stdexcept>
@@ -30,6 +31,17 @@ inline void check(cudaError_t e, const char* what, const char* file, int line) {
     }
 }
 #define BK_CUDA(expr) ::bk::check((expr), #expr, __FILE__, __LINE__)
+
+// A kernel's function attributes (its opt-in to more than 48 KB of dynamic shared memory) belong to one device's
+// context, and one process may hold sessions on several GPUs: first() is true once per device, for the current device.
+struct DeviceOnce {
+    std::atomic<bool> done[64] = {};
+    bool first() {
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return true;
+        return !done[device].exchange(true);
+    }
+};
 
 // A weight matrix in HBM after the load-time repack. File blocks (18/34/66/144/210 bytes) cannot be
 // read with aligned vector loads, so every format is split into planes whose elements are 16-byte

@@ -253,6 +253,10 @@ void launch_dec_multiply(const MatTarget* targets, int count, const float* x, co
     }
 }
 
+bool dec_attention_fits(uint32_t max_context, uint32_t heads, uint32_t dim, uint32_t sms) {
+    return dec_attn_out_smem(max_context, dec_attn_slice_width(heads, dim, sms)) <= 200 * 1024;
+}
+
 void launch_dec_attention(const RopeArgs& r, const AttnArgs& at, uint32_t sms, cudaStream_t s) {
     DecAttnParams a{};
     a.q = r.q; a.k = r.k; a.v = r.v; a.q_norm = r.q_norm; a.k_norm = r.k_norm; a.rope = r.rope;
@@ -283,11 +287,8 @@ void launch_dec_attention(const RopeArgs& r, const AttnArgs& at, uint32_t sms, c
 #undef BK_SCORES
     a.slice_width = dec_attn_slice_width(a.heads, a.dim, sms);
     const size_t smem2 = dec_attn_out_smem(a.max_context, a.slice_width);
-    static bool raised = false;
-    if (smem2 > 40 * 1024 && !raised) {
-        BK_CUDA(cudaFuncSetAttribute(dec_attn_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        raised = true;
-    }
+    static DeviceOnce once;
+    if (smem2 > 40 * 1024 && once.first()) BK_CUDA(cudaFuncSetAttribute(dec_attn_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     if (smem2 > 200 * 1024) throw CudaError("cuda: context too long for the single-token attention kernel");
     launch_pdl(dec_attn_out_kernel, dim3(a.heads, a.dim / a.slice_width), dim3(256), smem2, s, a);
 }

@@ -84,25 +84,34 @@ struct TaggedIo {
 };
 constexpr uint32_t kPollLimit = 1u << 20;  // re-reads of one batch before giving up (a fraction of a second)
 
+// A pair travels as ONE 64-bit scalar (value in the low word, tag in the high word): a naturally aligned 64-bit access is
+// single-copy atomic in the PTX memory model, so a reader sees the value and the tag of the same store. (A .v2.u32 access
+// is modelled as two separate 32-bit accesses.) Two pairs at once: .v2.b64, each half atomic on its own.
 __device__ __forceinline__ uint4 ld_pairs2(const void* p) {  // two {value, tag} pairs, from L2
-    uint4 v;
-    asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-    return v;
+    unsigned long long a, b;
+    asm volatile("ld.relaxed.gpu.global.v2.b64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+    return make_uint4(uint32_t(a), uint32_t(a >> 32), uint32_t(b), uint32_t(b >> 32));
 }
 __device__ __forceinline__ uint2 ld_pair(const void* p) {
-    uint2 v;
-    asm volatile("ld.relaxed.gpu.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-    return v;
+    unsigned long long a;
+    asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(a) : "l"(p) : "memory");
+    return make_uint2(uint32_t(a), uint32_t(a >> 32));
 }
 __device__ __forceinline__ void st_pair(void* p, float value, uint32_t tag) {
-    asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(__float_as_uint(value)), "r"(tag) : "memory");
+    const unsigned long long a = (static_cast<unsigned long long>(tag) << 32) | __float_as_uint(value);
+    asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(p), "l"(a) : "memory");
 }
 __device__ __forceinline__ void poll_failed(unsigned int* error) { atomicExch(error, 1u); }
+// Once any wait of the launch has run out, every later wait gives up after a few re-reads instead of running its own full
+// limit: a stalled producer then costs one limit, not one per dependent operation.
+__device__ __forceinline__ bool poll_abandoned(uint32_t spin, const unsigned int* error) {
+    return (spin & 1023u) == 1023u && *reinterpret_cast<const volatile unsigned int*>(error) != 0u;
+}
 // One tagged value; bounded.
 __device__ __forceinline__ float poll_pair(const void* p, uint32_t tag, unsigned int* error) {
     uint2 v = ld_pair(p);
     for (uint32_t spin = 0; v.y != tag; ++spin) {
-        if (spin == kPollLimit) {
+        if (spin == kPollLimit || poll_abandoned(spin, error)) {
             poll_failed(error);
             break;
         }
@@ -225,7 +234,7 @@ __device__ __forceinline__ void dec_multiply_body(const DecMatParams& p, const u
 #pragma unroll
                 for (int k = 0; k < K; ++k) complete = complete && a[k].y == io.tag_x && a[k].w == io.tag_x && b[k].y == io.tag_x && b[k].w == io.tag_x;
                 if (complete) break;
-                if (spin == kPollLimit) {
+                if (spin == kPollLimit || poll_abandoned(spin, io.error)) {
                     poll_failed(io.error);
                     break;
                 }

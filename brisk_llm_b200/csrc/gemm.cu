@@ -217,11 +217,10 @@ template <int WBYTES, int MI>
 static void launch_gemm_tile(const GemmParams& p, cudaStream_t s) {
     constexpr int GM = 64 * MI;
     constexpr size_t smem = 2 * Stage<WBYTES, GM>::kBytes;
-    static bool raised = false;
-    if (!raised) {
+    static DeviceOnce once;
+    if (once.first()) {
         BK_CUDA(cudaFuncSetAttribute(gemm_q8_kernel<WBYTES, MI>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
         BK_CUDA(cudaFuncSetAttribute(gemm_q8_kernel<WBYTES, MI>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
-        raised = true;
     }
     const dim3 grid((p.m.rows + GM - 1) / GM, (p.n + GN - 1) / GN);
     gemm_q8_kernel<WBYTES, MI><<<grid, GWARPS * 32, smem, s>>>(p);

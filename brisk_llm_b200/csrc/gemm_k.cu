@@ -340,11 +340,8 @@ __global__ void __launch_bounds__(KWARPS * 32, 1) gemm_k_kernel(const KParams p)
 template <int TYPE>
 void launch_one(const KParams& p, cudaStream_t s) {
     constexpr size_t smem = 2 * KStage<TYPE>::kBytes;
-    static bool raised = false;
-    if (!raised) {
-        BK_CUDA(cudaFuncSetAttribute(gemm_k_kernel<TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-        raised = true;
-    }
+    static DeviceOnce once;
+    if (once.first()) BK_CUDA(cudaFuncSetAttribute(gemm_k_kernel<TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
     const dim3 grid((p.m.rows + KM - 1) / KM, (p.n + KN - 1) / KN);
     gemm_k_kernel<TYPE><<<grid, KWARPS * 32, smem, s>>>(p);
     BK_CUDA(cudaGetLastError());

@@ -130,6 +130,8 @@ void launch_dec_multiply(const MatTarget* targets, int count, const float* x, co
 // Attention of the single new token: scores kernel (per-head norm + RoPE of q and the new k, f16 K/V store in its
 // prologue) and softmax + weighted-sum kernel. Takes the same argument structs as the batched kernels (n is 1).
 void launch_dec_attention(const RopeArgs& r, const AttnArgs& at, uint32_t sms, cudaStream_t s);
+// Whether a context of max_context positions fits the shared memory of that attention's weighted-sum kernel.
+bool dec_attention_fits(uint32_t max_context, uint32_t heads, uint32_t dim, uint32_t sms);
 
 // ---- the single-token step of all layers as one persistent kernel (step.cu) -------------------------------------
 struct StepLayerArgs {
@@ -176,6 +178,9 @@ public:
     StepPlan& operator=(const StepPlan&) = delete;
     bool build(const std::vector<StepLayerArgs>& layers, const StepShared& shared, uint32_t sms, cudaStream_t s, std::string& why_not);
     bool ready() const { return impl_ != nullptr; }
+    // False when the launch parameters must differ from token to token (the tagged exchange): such a launch cannot be
+    // replayed from a captured graph.
+    bool graph_safe() const;
     void launch(cudaStream_t s);
     const unsigned int* error_word() const;
     // Development aid: 4 words per phase (6 per layer) written by CTA 0 - entry, barrier passed, finished (ns), polls.

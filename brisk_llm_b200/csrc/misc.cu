@@ -1,6 +1,7 @@
 // Per-token vector kernels of the token loop: embedding lookup, per-head norm + RoPE + K/V cache write,
 // split-position attention with a combine pass, and the greedy arg-max that keeps decoding on the device.
 #include <cstdio>
+#include <mutex>
 #include <string>
 #include <utility>
 
@@ -33,7 +34,8 @@ void launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, c
 __global__ void embed_kernel(const DevMatrix m, const int32_t* tokens, float* __restrict__ hidden) {
     pdl_wait();
     const uint32_t t = blockIdx.x;
-    const uint32_t row = uint32_t(tokens[t]);
+    uint32_t row = uint32_t(tokens[t]);
+    if (row >= m.rows) row = 0;  // the host checks ids it is given; an id chosen on the device is checked where it is chosen, this is the last guard
     float* out = hidden + size_t(t) * m.cols;
     for (uint32_t u = threadIdx.x; u < m.units; u += blockDim.x) {
         const size_t i = size_t(row) * m.units + u;
@@ -450,8 +452,12 @@ __global__ void __launch_bounds__(256) argmax_stage1(const float* logits, uint32
     }
 }
 
-__global__ void __launch_bounds__(256) argmax_stage2(const float* pv, const int32_t* pi, int32_t* out, int32_t* token_slot, uint32_t* position,
-                                                     int32_t* history, uint32_t* history_len) {
+// `logits`/`vocab` restate what std::max_element (src/sampler.cpp:11-13) does with NaN: a comparison with NaN is false, so
+// a NaN is never chosen over the running maximum - and never displaced when it IS the running maximum, which only
+// element 0 can be. A row that starts with NaN, and a row of nothing but NaN, therefore answer 0; the result is always
+// an id inside the vocabulary, whatever the logits hold.
+__global__ void __launch_bounds__(256) argmax_stage2(const float* pv, const int32_t* pi, const float* logits, uint32_t vocab, int32_t* out,
+                                                     int32_t* token_slot, uint32_t* position, int32_t* history, uint32_t* history_len) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t row = blockIdx.x;
     float v = -INFINITY;
@@ -471,6 +477,8 @@ __global__ void __launch_bounds__(256) argmax_stage2(const float* pv, const int3
     __syncthreads();
     if (threadIdx.x == 0) {
         for (int w = 1; w < 8; ++w) better(v, idx, sv[w], si[w]);
+        const float first = logits[size_t(row) * vocab];
+        if (first != first || uint32_t(idx) >= vocab) idx = 0;
         out[row] = idx;
         if (token_slot != nullptr) {  // feed the decode loop: next input token, next position, history
             *token_slot = idx;
@@ -574,15 +582,15 @@ void launch_argmax(const float* logits, uint32_t vocab, uint32_t n, int32_t* out
                    cudaStream_t s) {
     argmax_stage1<<<dim3(kArgmaxBlocks, n), 256, 0, s>>>(logits, vocab, scratch_val, scratch_idx);
     BK_CUDA(cudaGetLastError());
-    argmax_stage2<<<n, 256, 0, s>>>(scratch_val, scratch_idx, out_token, nullptr, nullptr, nullptr, nullptr);
+    argmax_stage2<<<n, 256, 0, s>>>(scratch_val, scratch_idx, logits, vocab, out_token, nullptr, nullptr, nullptr, nullptr);
     BK_CUDA(cudaGetLastError());
 }
 
 void launch_argmax_advance(const float* logits, uint32_t vocab, int32_t* out_token, float* scratch_val, int32_t* scratch_idx,
                            int32_t* token_slot, uint32_t* position, int32_t* history, uint32_t* history_len, cudaStream_t s) {
     launch_pdl(argmax_stage1, dim3(kArgmaxBlocks, 1), dim3(256), 0, s, logits, vocab, scratch_val, scratch_idx);
-    launch_pdl(argmax_stage2, dim3(1), dim3(256), 0, s, (const float*)scratch_val, (const int32_t*)scratch_idx, out_token, token_slot, position,
-               history, history_len);
+    launch_pdl(argmax_stage2, dim3(1), dim3(256), 0, s, (const float*)scratch_val, (const int32_t*)scratch_idx, logits, vocab, out_token, token_slot,
+               position, history, history_len);
 }
 
 }  // namespace bk
@@ -596,6 +604,8 @@ constexpr uint32_t kStaticArgmaxRows = 64;  // rows one call may reduce (the mos
 static __device__ __align__(256) unsigned char g_static_argmax_scratch[kStaticArgmaxRows * bk::kArgmaxBlocks * 8];
 constexpr int kMaxDevices = 64;
 void* g_static_argmax_address[kMaxDevices] = {};  // device address of the array, per device, filled on first use
+std::once_flag g_static_argmax_once[kMaxDevices];  // host threads may make their first call on a device at the same time
+cudaError_t g_static_argmax_status[kMaxDevices] = {};
 }  // namespace
 
 extern "C" int brisk_cuda_argmax_static(const float* logits, uint32_t vocab, uint32_t rows, int32_t* out_tokens, void* stream, char* err,
@@ -614,12 +624,14 @@ extern "C" int brisk_cuda_argmax_static(const float* logits, uint32_t vocab, uin
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) return fail(std::string("cuda: cudaGetDevice failed: ") + cudaGetErrorString(e));
     if (device < 0 || device >= kMaxDevices) return fail("cuda: device ordinal out of range");
-    if (g_static_argmax_address[device] == nullptr) {
-        // In host code the array's name is only a handle; the kernels need the address it has on the current device.
+    // In host code the array's name is only a handle; the kernels need the address it has on the current device.
+    std::call_once(g_static_argmax_once[device], [device] {
         void* address = nullptr;
-        e = cudaGetSymbolAddress(&address, g_static_argmax_scratch);
-        if (e != cudaSuccess || address == nullptr) return fail(std::string("cuda: cudaGetSymbolAddress failed: ") + cudaGetErrorString(e));
+        g_static_argmax_status[device] = cudaGetSymbolAddress(&address, g_static_argmax_scratch);
         g_static_argmax_address[device] = address;
+    });
+    if (g_static_argmax_status[device] != cudaSuccess || g_static_argmax_address[device] == nullptr) {
+        return fail(std::string("cuda: cudaGetSymbolAddress failed: ") + cudaGetErrorString(g_static_argmax_status[device]));
     }
     unsigned char* base = static_cast<unsigned char*>(g_static_argmax_address[device]);
     float* partial_value = reinterpret_cast<float*>(base);
@@ -627,7 +639,7 @@ extern "C" int brisk_cuda_argmax_static(const float* logits, uint32_t vocab, uin
     // Stage 1 writes every pair stage 2 reads for these rows, so nothing of the previous call has to be cleared.
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     bk::argmax_stage1<<<dim3(bk::kArgmaxBlocks, rows), 256, 0, s>>>(logits, vocab, partial_value, partial_index);
-    bk::argmax_stage2<<<rows, 256, 0, s>>>(partial_value, partial_index, out_tokens, nullptr, nullptr, nullptr, nullptr);
+    bk::argmax_stage2<<<rows, 256, 0, s>>>(partial_value, partial_index, logits, vocab, out_tokens, nullptr, nullptr, nullptr, nullptr);
     e = cudaGetLastError();
     if (e != cudaSuccess) return fail(std::string("cuda: arg-max launch failed: ") + cudaGetErrorString(e));
     return 0;

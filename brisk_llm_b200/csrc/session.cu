@@ -812,13 +812,15 @@ struct Session {
         }
     }
 
-    // Three launches per token gain little from a graph; BRISK_CUDA_STEP_GRAPH=1 captures them all the same.
-    static bool step_in_graph() {
+    // Three launches per token gain little from a graph; BRISK_CUDA_STEP_GRAPH=1 captures them all the same - unless the
+    // kernel exchanges tagged pairs: its tags are a launch parameter that must change with every token, and a replayed
+    // graph would launch with the tags of the token it was captured for.
+    bool step_in_graph() const {
         static const bool on = [] {
             const char* env = std::getenv("BRISK_CUDA_STEP_GRAPH");
             return env != nullptr && std::atoi(env) != 0;
         }();
-        return on;
+        return on && step_plan.graph_safe();
     }
 
     void build_step_graph() {
@@ -845,7 +847,11 @@ struct Session {
     }
 
     void step_on_device() {  // one token whose id is tokens_dev[0] at *d_position()
-        if (flags & BRISK_CUDA_FLAG_NO_MEGAKERNEL) {
+        // The fused weighted sum keeps a head's probabilities of the whole context in shared memory; past that the batched
+        // kernels, which have no such limit, take single tokens too.
+        const bool too_long = !step_active() && !variant_layers &&
+                              !dec_attention_fits(uint32_t(max_context), heads_l, head_dim, sms);
+        if ((flags & BRISK_CUDA_FLAG_NO_MEGAKERNEL) || too_long) {
             forward(1, false, uint32_t(max_context));  // the batched kernels, one token
         } else if ((flags & BRISK_CUDA_FLAG_NO_GRAPH) || profiling || (step_active() && !step_in_graph())) {
             forward_decode();
@@ -904,7 +910,12 @@ struct Session {
         float ms = 0;
         BK_CUDA(cudaEventElapsedTime(&ms, ev0, ev1));
         end_call(ms);
-        finish_step_check();
+        try {
+            finish_step_check();
+        } catch (...) {
+            position -= n;  // nothing of this call can be trusted: the cache rows it wrote are overwritten by the next call
+            throw;
+        }
         return logits_host;
     }
 
@@ -951,9 +962,9 @@ struct Session {
         BK_CUDA(cudaStreamSynchronize(stream));
         float ms = 0;
         BK_CUDA(cudaEventElapsedTime(&ms, ev0, ev1));
-        position += steps;
         end_call(ms);
-        finish_step_check();
+        finish_step_check();  // throws: the position stays where it was
+        position += steps;
     }
 };
 

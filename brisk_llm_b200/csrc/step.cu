@@ -85,7 +85,7 @@ __device__ __forceinline__ void warp_fetch_tagged(const uint2* src, float* dst, 
 #pragma unroll
             for (int k = 0; k < 4; ++k) complete = complete && v[k].y == tag && v[k].w == tag;
             if (complete) break;
-            if (spin == kPollLimit) {
+            if (spin == kPollLimit || poll_abandoned(spin, error)) {
                 poll_failed(error);
                 break;
             }
@@ -799,6 +799,8 @@ void StepPlan::launch(cudaStream_t s) {
     cfg.numAttrs = 1;
     BK_CUDA(cudaLaunchKernelEx(&cfg, impl_->kernel, P));
 }
+
+bool StepPlan::graph_safe() const { return impl_ == nullptr || !impl_->tagged; }
 
 void StepPlan::set_trace(unsigned long long* words) { impl_->trace = words; }
 

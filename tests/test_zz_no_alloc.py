@@ -71,3 +71,38 @@ def test_static_argmax_ties_and_limits():
     out65 = torch.zeros((65,), dtype=torch.int32, device=dev)
     rc, msg = static_argmax(lib, too_many, out65, 65, 8, stream)
     assert rc != 0 and "at most 64 rows" in msg
+
+
+def test_static_argmax_follows_max_element_on_nan():
+    """std::max_element (brisk-llm src/sampler.cpp:11-13) never prefers a NaN and never leaves one that sits at index 0:
+    the pick stays inside the vocabulary whatever the row holds. The call only reads the caller's buffer."""
+    import torch
+    lib = abi.load_library()
+    dev = torch.device("cuda", 0)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    nan = float("nan")
+    rows = torch.zeros((5, 3000), dtype=torch.float32, device=dev)
+    rows[0, :] = nan                      # nothing but NaN: the first element stays
+    rows[1, 100] = nan                    # NaN among numbers is skipped ...
+    rows[1, 2500] = 2.0                   # ... the first maximum of the rest wins
+    rows[1, 2900] = 2.0
+    rows[2, 0] = nan                      # a NaN in front is never displaced
+    rows[2, 7] = 9.0
+    rows[3, :] = -float("inf")            # equal values: the first
+    rows[4, :] = -float("inf")
+    rows[4, 1234] = nan
+    rows[4, 2000] = -1.0
+    out = torch.full((5,), -1, dtype=torch.int32, device=dev)
+    rc, msg = static_argmax(lib, rows, out, 5, 3000, stream)
+    assert rc == 0, msg
+    torch.cuda.synchronize()
+    host = rows.cpu().numpy()
+    want = []
+    for r in host:  # the loop of std::max_element
+        best = 0
+        for i in range(1, len(r)):
+            if r[best] < r[i]:
+                best = i
+        want.append(best)
+    assert want == [0, 2500, 0, 0, 2000]
+    assert out.cpu().tolist() == want
