@@ -13,7 +13,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 OUT = os.path.join(PKG, "libbrisk_cuda.so")
 OBJ = os.path.join(PKG, "build")
-SOURCES = ["repack.cu", "activations.cu", "matvec.cu", "gemm.cu", "gemm_k.cu", "misc.cu", "gemma.cu", "decode.cu", "step.cu", "session.cu", "hooks.cu"]
+SOURCES = ["repack.cu", "activations.cu", "matvec.cu", "gemm.cu", "gemm_k.cu", "misc.cu", "gemma.cu", "decode.cu", "step.cu", "token.cu", "session.cu", "hooks.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-std=c++20", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-fmad=false",
          "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v"]

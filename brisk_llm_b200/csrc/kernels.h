@@ -194,6 +194,45 @@ private:
     std::string description_;
 };
 
+// ---- one decoded token as one launch (token.cu) -------------------------------------------------------------------
+// Embedding row, every layer, output head and arg-max of one token in a single cooperative kernel, for models whose layer
+// matrices and head are Q4_0 and whose per-SM share of one layer fits shared memory. With advance the kernel also feeds
+// the next step (*token = choice, *position += 1, history) exactly as launch_argmax_advance does.
+struct TokenEnds {
+    DevMatrix embd, head;
+    const float* output_norm = nullptr;
+    float* logits = nullptr;        // [vocab]
+    uint32_t vocab = 0;
+    int32_t* token = nullptr;       // device: the token to evaluate (and, advancing, the next one)
+    int32_t* chosen = nullptr;      // device: arg-max of the logits
+    int32_t* history = nullptr;
+    uint32_t* history_len = nullptr;
+};
+class TokenPlan {
+public:
+    TokenPlan();
+    ~TokenPlan();
+    TokenPlan(const TokenPlan&) = delete;
+    TokenPlan& operator=(const TokenPlan&) = delete;
+    // false, with the reason, when the model is outside what the kernel covers
+    bool build(const std::vector<StepLayerArgs>& layers, const StepShared& shared, const TokenEnds& ends, uint32_t sms, cudaStream_t s, std::string& why_not);
+    bool ready() const { return impl_ != nullptr; }
+    // The token's embedding row is read from the Q4_0 embedding inside the kernel; for any other embedding type the caller
+    // writes it to shared.hidden first (embeds_itself() is false).
+    bool embeds_itself() const { return embd_q4_0_; }
+    void launch(cudaStream_t s, bool advance);
+    const unsigned int* error_word() const;
+    void set_trace(unsigned long long* words);  // development aid: CTA 0 stamps the end of every phase
+    void rearm(cudaStream_t s);
+    const std::string& description() const { return description_; }
+
+private:
+    struct Impl;
+    Impl* impl_ = nullptr;
+    bool embd_q4_0_ = false;
+    std::string description_;
+};
+
 // Tensor parallel re-layout: gathered[rank][t][rows_l] -> dst[t][rank*rows_l + r] (add: dst += ...), tp ranks.
 void launch_tp_unpack(const float* gathered, float* dst, uint32_t n, uint32_t rows_l, uint32_t tp, bool add, cudaStream_t s);
 

@@ -189,6 +189,10 @@ struct Session {
     // The persistent all-layer kernel of the single-token step (step.cu), when the model is within what it covers.
     StepPlan step_plan;
     bool step_enabled = false;
+    // One launch per token (token.cu): embedding, layers, head and arg-max in one kernel, where the model allows it.
+    TokenPlan token_plan;
+    bool token_enabled = false;
+    bool advance_on_device = false;  // the device greedy loop: the token kernel also feeds the next step
     std::string step_note;                 // how it was configured, or why it is not used
     unsigned int* step_error_host = nullptr;  // pinned copy of the kernel's barrier-timeout word
     uint64_t persistent_steps = 0;
@@ -556,13 +560,27 @@ struct Session {
         sh.act_epi = arch == BRISK_ARCH_BITNET ? EPI_RELU2_MUL : EPI_SILU_MUL;
         const bool tracing = std::getenv("BRISK_CUDA_STEP_TRACE") != nullptr;
         if (tracing) {  // per-phase stamps of every layer, then the stamps inside one layer's multiplies
-            trace.alloc((size_t(n_layers) * 6 * 4 + 48) * sizeof(unsigned long long));
+            trace.alloc((size_t(n_layers) * 6 * 4 + 64) * sizeof(unsigned long long));
             BK_CUDA(cudaMemset(trace.p, 0, trace.bytes));
             sh.body_trace = trace.as<unsigned long long>() + size_t(n_layers) * 6 * 4;
         }
         std::string why;
+        const char* tok_env = std::getenv("BRISK_CUDA_TOKEN");
+        if (!(tok_env != nullptr && std::strcmp(tok_env, "0") == 0)) {
+            TokenEnds ends;
+            ends.embd = embd; ends.head = head; ends.output_norm = output_norm; ends.logits = logits_b.as<float>(); ends.vocab = vocab;
+            ends.token = tokens_dev.as<int32_t>(); ends.chosen = d_chosen(); ends.history = history.as<int32_t>(); ends.history_len = d_history_len();
+            token_enabled = token_plan.build(args, sh, ends, sms, stream, why);
+            if (token_enabled) {
+                step_note = "on: " + token_plan.description();
+                if (tracing) token_plan.set_trace(trace.as<unsigned long long>());
+                return;
+            }
+        }
+        const std::string token_why = why;
         step_enabled = step_plan.build(args, sh, sms, stream, why);
         step_note = step_enabled ? "on: " + step_plan.description() : "off: " + why;
+        if (!token_why.empty()) step_note += " (one launch per token: " + token_why + ")";
         if (step_enabled && tracing) step_plan.set_trace(trace.as<unsigned long long>());
     }
 
@@ -784,10 +802,21 @@ struct Session {
     }
 
     void forward(uint32_t n, bool all_logits, uint32_t max_visible) { run_layers(n, all_logits, max_visible, false); }
-    bool step_active() const { return step_enabled && !profiling; }
+    bool step_active() const { return (step_enabled || token_enabled) && !profiling; }
+    bool token_active() const { return token_enabled && !profiling; }
     void forward_decode() {
         if (!step_active()) {
             run_layers(1, false, uint32_t(max_context), true);
+            return;
+        }
+        if (token_enabled) {
+            if (!token_plan.embeds_itself()) {
+                launch_embed(embd, tokens_dev.as<int32_t>(), 1, hidden_b.as<float>(), stream);
+                ++launches;
+            }
+            token_plan.launch(stream, advance_on_device);
+            ++launches;
+            ++persistent_steps;
             return;
         }
         // embedding | all layers in one persistent kernel | output head
@@ -800,13 +829,15 @@ struct Session {
     }
     // After the call's final synchronisation: did a barrier wait of the persistent kernel run out?
     void queue_step_check() {
-        if (step_enabled) BK_CUDA(cudaMemcpyAsync(step_error_host, step_plan.error_word(), sizeof(unsigned int), cudaMemcpyDeviceToHost, stream));
+        if (token_enabled) BK_CUDA(cudaMemcpyAsync(step_error_host, token_plan.error_word(), sizeof(unsigned int), cudaMemcpyDeviceToHost, stream));
+        else if (step_enabled) BK_CUDA(cudaMemcpyAsync(step_error_host, step_plan.error_word(), sizeof(unsigned int), cudaMemcpyDeviceToHost, stream));
     }
     void finish_step_check() {
-        if (step_enabled && *step_error_host != 0) {
+        if ((step_enabled || token_enabled) && *step_error_host != 0) {
             *step_error_host = 0;
-            step_plan.rearm(stream);
-            step_enabled = false;  // later steps take the per-operation kernels
+            if (token_enabled) token_plan.rearm(stream);
+            else step_plan.rearm(stream);
+            step_enabled = token_enabled = false;  // later steps take the per-operation kernels
             step_note = "off: a grid barrier timed out";
             throw CudaError("cuda: a grid barrier of the single-token kernel timed out; the results of this call are invalid");
         }
@@ -820,7 +851,7 @@ struct Session {
             const char* env = std::getenv("BRISK_CUDA_STEP_GRAPH");
             return env != nullptr && std::atoi(env) != 0;
         }();
-        return on && step_plan.graph_safe();
+        return on && !token_enabled && step_plan.graph_safe();
     }
 
     void build_step_graph() {
@@ -939,12 +970,15 @@ struct Session {
         stats.h2d_bytes += 4 * sizeof(int32_t);
         build_step_graph();
         BK_CUDA(cudaEventRecord(ev0, stream));
+        const bool fused_pick = token_active() && !(flags & BRISK_CUDA_FLAG_NO_MEGAKERNEL);
         for (uint64_t i = 0; i < steps; ++i) {
+            advance_on_device = fused_pick;
             step_on_device();
+            advance_on_device = false;
             if (out_logits != nullptr) {
                 BK_CUDA(cudaMemcpyAsync(logit_history.as<float>() + i * vocab, logits_b.p, size_t(vocab) * sizeof(float), cudaMemcpyDeviceToDevice, stream));
             }
-            {
+            if (!fused_pick) {
                 Scope sc(this, PH_SAMPLE);
                 launch_argmax_advance(logits_b.as<float>(), vocab, d_chosen(), am_val.as<float>(), am_idx.as<int32_t>(), tokens_dev.as<int32_t>(),
                                       d_position(), history.as<int32_t>(), d_history_len(), stream);

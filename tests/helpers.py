@@ -210,3 +210,73 @@ def rel_l2(a, b):
     a = np.asarray(a, np.float64).ravel()
     b = np.asarray(b, np.float64).ravel()
     return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))
+
+
+class RefSession:
+    """The unmodified reference engine (oracle/_ref/libbrisk_ref.so) behind the same calls as OracleSession. The model
+    goes through a GGUF file the reference's own loader parses."""
+
+    def __init__(self, host_model, max_context=0, threads=0):
+        import tempfile
+        from brisk_llm_b200 import gguf_io
+        self.lib = ref()
+        self.vocab = host_model.spec.vocab
+        fd, self.path = tempfile.mkstemp(suffix=".gguf", prefix="brisk_ref_")
+        os.close(fd)
+        gguf_io.write_gguf(host_model, self.path)
+        self.h = self.lib.ref_session_create(self.path.encode(), threads or (os.cpu_count() or 1), max_context or host_model.spec.context)
+        if not self.h:
+            os.remove(self.path)
+            raise RuntimeError(self.lib.ref_last_error().decode())
+
+    def close(self):
+        if self.h:
+            self.lib.ref_session_destroy(self.h)
+            self.h = None
+            os.remove(self.path)
+
+    def __del__(self):
+        self.close()
+
+    def _eval(self, tokens, all_logits):
+        tokens = np.ascontiguousarray(tokens, np.int32)
+        out = np.empty((len(tokens) if all_logits else 1, self.vocab), np.float32)
+        if self.lib.ref_session_eval(self.h, iptr(tokens), len(tokens), int(all_logits), fptr(out)) != 0:
+            raise RuntimeError(self.lib.ref_last_error().decode())
+        return out if all_logits else out[0]
+
+    def eval(self, tokens):
+        return self._eval(np.atleast_1d(tokens), False)
+
+    def eval_all(self, tokens):
+        return self._eval(tokens, True)
+
+    def rollback(self, position):
+        if self.lib.ref_session_rollback(self.h, position) != 0:
+            raise RuntimeError(self.lib.ref_last_error().decode())
+
+    def log_likelihood(self, tokens):
+        tokens = np.ascontiguousarray(tokens, np.int32)
+        out = C.c_double()
+        if self.lib.ref_session_log_likelihood(self.h, iptr(tokens), len(tokens), C.byref(out)) != 0:
+            raise RuntimeError(self.lib.ref_last_error().decode())
+        return out.value
+
+    def generate_greedy(self, prompt, steps, want_logits=True):
+        """eval(prompt), then `steps` greedy picks; logits[i] is the row pick i was made from."""
+        prompt = np.ascontiguousarray(prompt, np.int32)
+        toks = np.empty(steps, np.int32)
+        logits = np.empty((steps, self.vocab), np.float32) if want_logits else None
+        rc = self.lib.ref_session_generate_greedy(self.h, iptr(prompt), len(prompt), steps, iptr(toks),
+                                                  fptr(logits) if want_logits else None, None, None)
+        if rc != 0:
+            raise RuntimeError(self.lib.ref_last_error().decode())
+        return toks, logits
+
+
+def cpu_checker(host_model, max_context=0):
+    """The reference engine itself where it was built (oracle/_ref), else the C restatement on all cores: (session, kind)."""
+    if have_ref():
+        return RefSession(host_model, max_context), "reference"
+    os.environ.setdefault("BRISK_ORACLE_THREADS", str(os.cpu_count() or 1))
+    return OracleSession(host_model, max_context), "port"

@@ -293,20 +293,26 @@ def test_memory_preflight_refuses_what_cannot_fit(monkeypatch):
     ("group7", synth.tiny(synth.MISTRAL_7B, layers=2, vocab=1024, context=2048, hidden=896, heads=14, kv_heads=2, head_dim=64, ffn=1792, qkv_bias=True)),
 ])
 def test_the_three_single_token_paths_agree_bit_for_bit(family, spec, monkeypatch):
-    """A single-token step can run as one persistent kernel for all layers (the default where the model allows it), as
-    one fused kernel per operation, or through the batched kernels. All three repeat the same float operations in the
-    same order: their logits must be identical bits, at several context lengths (one that crosses the 512-position
-    chunks of the attention phases included)."""
+    """A single-token step can run as one launch for the whole token (embedding to arg-max; Q4_0 models of the 0.6B class),
+    as one persistent kernel for all layers, as one fused kernel per operation, or through the batched kernels. All of
+    them repeat the same float operations in the same order: their logits must be identical bits, at several context
+    lengths (one that crosses the 512-position chunks of the attention phases included)."""
     from brisk_llm_b200 import abi
     # the persistent kernel is off by default for models with wide rows (slower there); force it, to test its variants
     monkeypatch.setenv("BRISK_CUDA_STEP", "force")
     m = synth.perturb_norms(synth.generate(spec, seed=11))
     toks = synth.random_tokens(spec, 1200, seed=12)
     results = {}
-    for name, flags in (("persistent", 0), ("per_operation", abi.FLAG_NO_PERSISTENT), ("batched", abi.FLAG_NO_MEGAKERNEL)):
+    for name, flags in (("token", 0), ("persistent", 0), ("per_operation", abi.FLAG_NO_PERSISTENT), ("batched", abi.FLAG_NO_MEGAKERNEL)):
+        monkeypatch.setenv("BRISK_CUDA_TOKEN", "1" if name == "token" else "0")
         with engine.CudaSession(m, flags=flags) as s:
             uniform = len({f for n, (f, sh, d) in m.tensors.items() if n.startswith("blk.") and n.endswith(".weight") and not n.endswith("norm.weight")}) == 1
-            persistent = name == "persistent" and uniform  # mixed weight types in the layers keep the per-operation kernels
+            if name == "token":
+                if "one launch per token:" not in s.step_path().split("(")[0]:
+                    assert family in ("llama", "bitnet", "mistral", "group7"), s.step_path()  # not Q4_0, or rows the kernel does not take
+                    continue
+                assert family in ("qwen3", "biased", "group3")
+            persistent = name in ("token", "persistent") and uniform  # mixed weight types in the layers keep the per-operation kernels
             assert ("kernel on" in s.step_path()) == persistent, s.step_path()
             out = []
             at = 0
@@ -326,24 +332,56 @@ def test_the_three_single_token_paths_agree_bit_for_bit(family, spec, monkeypatc
             out.append(logits)
             out.append(np.asarray(ids, np.float32))
             results[name] = out
-    for other in ("per_operation", "batched"):
+    base = "token" if "token" in results else "persistent"
+    for other in ("persistent", "per_operation", "batched"):
+        if other == base:
+            continue
         # the ternary family's F16 head sums lane partials; the batched head kernel may group them differently
         exact = family != "bitnet" or other == "per_operation"
-        for a, b in zip(results["persistent"], results[other]):
+        for a, b in zip(results[base], results[other]):
             if exact:
                 assert np.array_equal(a, b), (other, float(np.abs(a - b).max()))
             else:
                 assert np.abs(a - b).max() <= 1e-5, (other, float(np.abs(a - b).max()))
 
 
-def test_default_choice_of_the_single_token_path():
-    """Where the persistent kernel is measured to be slower (rows wider than 4096 values) or does not apply (layer
-    matrices of several types), sessions use one kernel per operation by default; step_path() says which and why."""
-    for spec, expect in ((synth.tiny(synth.QWEN3_0_6B, layers=1, vocab=512), "kernel on: tagged exchange"),
+def test_one_launch_per_token_at_long_contexts(monkeypatch):
+    """The one-launch token kernel past the 1536 positions its value ring holds at once (chunks are refilled behind the
+    products) and across further 512-position boundaries, against the per-operation kernels: identical bits, logits and ids."""
+    from brisk_llm_b200 import abi
+    spec = synth.tiny(synth.QWEN3_0_6B, layers=2, vocab=1024, context=4096)
+    m = synth.perturb_norms(synth.generate(spec, seed=21))
+    toks = synth.random_tokens(spec, 3700, seed=22)
+    results = {}
+    for name, flags in (("token", 0), ("per_operation", abi.FLAG_NO_PERSISTENT)):
+        with engine.CudaSession(m, flags=flags) as s:
+            assert ("one launch per token" in s.step_path()) == (name == "token"), s.step_path()
+            out, at = [], 0
+            for prompt in (1534, 510, 512, 1100):  # decode at 1534.., 2047.., 2562.., 3665..
+                s.eval(toks[at:at + prompt])
+                at += prompt
+                for _ in range(3):
+                    out.append(s.eval(toks[at:at + 1]))
+                    at += 1
+            ids, logits = s.generate_greedy(int(toks[at]), 4, want_logits=True)
+            out += [logits, np.asarray(ids, np.float32)]
+            results[name] = out
+    for a, b in zip(results["token"], results["per_operation"]):
+        assert np.array_equal(a, b), float(np.abs(a - b).max())
+
+
+def test_default_choice_of_the_single_token_path(monkeypatch):
+    """Q4_0 models of the 0.6B class run a token as one launch. Where that kernel does not apply the persistent all-layer
+    kernel is next, and where that is measured to be slower (rows wider than 4096 values) or does not apply (layer
+    matrices of several types) sessions use one kernel per operation; step_path() says which and why."""
+    for spec, expect in ((synth.tiny(synth.QWEN3_0_6B, layers=1, vocab=512), "kernel on: one launch per token"),
                          (synth.tiny(synth.MISTRAL_7B, layers=1, vocab=512), "off: activation rows wider than 4096"),
                          (synth.tiny(synth.LLAMA_3_2_1B, layers=1, vocab=512), "off: ")):
         with engine.CudaSession(synth.generate(spec, seed=1)) as s:
             assert expect in s.step_path(), s.step_path()
+    monkeypatch.setenv("BRISK_CUDA_TOKEN", "0")
+    with engine.CudaSession(synth.generate(synth.tiny(synth.QWEN3_0_6B, layers=1, vocab=512), seed=1)) as s:
+        assert "kernel on: tagged exchange" in s.step_path(), s.step_path()
 
 
 @pytest.mark.parametrize("family,spec", [
