@@ -8,6 +8,9 @@ greedily. `value` is decode tokens/s with everything resident in HBM (on-device 
 `e2e` is the same metric through the Engine-shaped public call with host buffers: token ids copied in and all
 logits copied out every step, arg-max on the host - the loop brisk-llm's `generate` runs. With N > 1 every rank
 runs an independent replica (batch-1 decode of one sequence has nothing to shard for this configuration).
+After the headline the same run times the one configuration that does shard - the Mistral-7B-shaped Q4_0 model,
+8192-token prompt + 512 greedy steps - tensor-parallel over all N ranks (N = 1: on the one GPU) and reports it in the
+`tensor_parallel` object, so the 1 -> N scaling of that configuration can be read from the per-N lines.
 `--impl reference` times the reference's own CPU engine on the host cores instead.
 """
 from __future__ import annotations
@@ -45,6 +48,7 @@ def parse():
     p.add_argument("--decode", type=int, default=0)
     p.add_argument("--layers", type=int, default=0, help="override the layer count (debugging; the reported number is then not the configured workload)")
     p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel section (the 7B-shaped configuration)")
     p.add_argument("--profile", action="store_true", help="for ncu launch lists: exactly --warmup warm-up steps, no end-to-end loop, no CPU baseline (the printed number is not a bench value)")
     return p.parse_args()
 
@@ -58,10 +62,13 @@ WORKLOADS = {  # prompt tokens, decode steps, context
 }
 
 
-# DRAM bytes one decoded token moves, from ncu captures of the two kernels that move them at context ~516
-# (dram__bytes_read + write per launch): the persistent step kernel 306.94 + 5.39 MB and the output head
-# 87.56 + 2.85 MB; the embedding and arg-max kernels move well under 1 MB.
-MEASURED_TRAFFIC_PER_TOKEN = {"qwen3-0.6b-q4_0": int((306.94 + 5.39 + 87.56 + 2.85) * 1e6)}
+def analytic_traffic(spec, weight_bytes, prompt, decode):
+    """DRAM bytes one decoded token must move, counted (not measured): every weight plane once, the visible K/V cache at
+    the mean context of the decode steps, the logits row written. ncu's dram__bytes of the token kernel at context ~516
+    (profiles/) agrees with this figure to a few percent; the number here follows the workload, not a capture."""
+    mean_ctx = prompt + decode / 2
+    kv = spec.layers * 2 * spec.kv_heads * spec.head_dim * 2 * mean_ctx
+    return int(weight_bytes + kv + spec.vocab * 4)
 
 
 def peaks():
@@ -155,14 +162,16 @@ def cpu_engine(model, spec, threads):
         if not handle:
             raise RuntimeError(r.ref_last_error().decode())
 
-        def run(prompt_ids, steps):
+        def run(prompt_ids, steps, want_logits=False):
             r.ref_session_rollback(handle, 0)
             out = np.empty(steps, np.int32)
+            logits = np.empty((steps, spec.vocab), np.float32) if want_logits else None
             tp, td = C.c_double(), C.c_double()
-            rc = r.ref_session_generate_greedy(handle, H.iptr(prompt_ids), len(prompt_ids), steps, H.iptr(out), None, C.byref(tp), C.byref(td))
+            rc = r.ref_session_generate_greedy(handle, H.iptr(prompt_ids), len(prompt_ids), steps, H.iptr(out),
+                                               H.fptr(logits) if want_logits else None, C.byref(tp), C.byref(td))
             if rc != 0:
                 raise RuntimeError(r.ref_last_error().decode())
-            return tp.value, td.value
+            return (tp.value, td.value, out, logits) if want_logits else (tp.value, td.value)
 
         def close():
             r.ref_session_destroy(handle)
@@ -172,21 +181,31 @@ def cpu_engine(model, spec, threads):
     os.environ["BRISK_ORACLE_THREADS"] = str(threads)
     sess = H.OracleSession(model, spec.context)
 
-    def run(prompt_ids, steps):
+    def run(prompt_ids, steps, want_logits=False):
         sess.rollback(0)
+        rows, picks = [], []
         t0 = time.perf_counter()
         logits = sess.eval(prompt_ids)
         t1 = time.perf_counter()
-        for _ in range(steps - 1):
-            logits = sess.eval([int(np.argmax(logits))])
-        return t1 - t0, time.perf_counter() - t1
+        for i in range(steps):
+            if want_logits:
+                rows.append(logits.copy())
+            picks.append(int(np.argmax(logits)))
+            if i + 1 < steps:
+                logits = sess.eval([picks[-1]])
+        t2 = time.perf_counter()
+        return (t1 - t0, t2 - t1, np.array(picks, np.int32), np.stack(rows)) if want_logits else (t1 - t0, t2 - t1)
 
     return "port", "scalar C port", run, sess.close
 
 
-def cpu_sample_sizes(spec):
-    # about 10-30 s of CPU work on a few dozen cores: cost grows with the weight bytes per token
-    scale = max(1.0, spec.layers * (spec.hidden * (spec.q_dim * 2 + spec.kv_dim * 2 + 3 * spec.ffn)) / 4.4e8)
+def cpu_sample_sizes(spec, prompt, decode):
+    """(prompt tokens, greedy picks) of one CPU step. The 0.6B-class configuration runs its whole workload (about 10-20 s on
+    a few dozen cores; `decode` + 1 picks are `decode` decoded tokens); larger models a sample whose cost stays in that
+    range - it shrinks with the weight bytes per token."""
+    scale = spec.layers * (spec.hidden * (spec.q_dim * 2 + spec.kv_dim * 2 + 3 * spec.ffn)) / 4.4e8
+    if scale <= 1.05:
+        return prompt, decode + 1
     return max(8, int(128 / scale)), max(4, int(32 / scale))
 
 
@@ -197,29 +216,80 @@ def run_reference_arm(args):
     spec, prompt, decode = workload_for(args)
     model = synth.generate(spec, seed=0, share_layers=spec.layers * spec.hidden * spec.ffn > 1e9)
     threads = os.cpu_count() or 1
-    sp, sd = cpu_sample_sizes(spec)
+    sp, sd = cpu_sample_sizes(spec, prompt, decode)
     kind, kernels, run, close = cpu_engine(model, spec, threads)
     ids = synth.random_tokens(spec, sp, seed=1)
-    for _ in range(min(args.warmup, 1)):
+    # a CPU step is ten seconds or more: at most three timed steps and one warm-up, whatever was asked for, so that the
+    # whole run ends within a few minutes
+    steps, warmup = min(args.steps, 3), min(args.warmup, 1)
+    for _ in range(warmup):
         run(ids, sd)
     tp = td = 0.0
-    for _ in range(args.steps):
+    for _ in range(steps):
         a, b = run(ids, sd)
         tp += a
         td += b
     close()
-    value = args.steps * (sd - 1) / td if td > 0 else 0.0
-    sample = f"{sp}-token prompt + {sd} greedy steps of the same model per step ({kernels} kernels)"
-    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": min(args.warmup, 1), "ms_per_step": 1e3 * (tp + td) / args.steps, "higher_is_better": True, "scaling": "weak",
+    value = steps * (sd - 1) / td if td > 0 else 0.0
+    whole = (sp, sd - 1) == (prompt, decode)
+    sample = (f"the whole workload ({sp}-token prompt + {sd - 1} decoded tokens) per step, {steps} timed steps" if whole else
+              f"{sp}-token prompt + {sd - 1} decoded tokens of the same model per step, {steps} timed steps") + f" ({kernels} kernels)"
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+            "warmup": warmup, "ms_per_step": 1e3 * (tp + td) / steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "int8 dot products, f32 accumulate", "data": "synthetic",
-            "config": describe(spec, prompt, decode, {"sample": sample}), "prefill_tokens_per_s": args.steps * sp / tp,
+            "config": describe(spec, prompt, decode, {"sample": sample, "same_workload": whole}), "prefill_tokens_per_s": steps * sp / tp,
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
 
 # ---- our arm ------------------------------------------------------------------------------------------------------
+
+def tensor_parallel_section(engine, torch, dist, rank, local, world, max_over_ranks, barrier):
+    """The configuration that shards: the Mistral-7B-shaped Q4_0 model, 8192-token prompt filling the f16 K/V cache, then
+    512 greedy steps, batch 1 - on one GPU, or tensor-parallel over all ranks (every matrix split by output rows, K/V
+    heads split, activations exchanged inside the library). One warm-up pass (prompt + 16 steps), one timed pass; device
+    time by CUDA events on the session's stream, maximum over the ranks."""
+    from dataclasses import replace
+    from brisk_llm_b200 import parallel
+    prompt, decode, ctx = WORKLOADS["mistral-7b-q4_0"]
+    spec = replace(synth.PRESETS["mistral-7b-q4_0"], context=ctx)
+    model = synth.generate(spec, seed=0, share_layers=True)  # one layer's weights drawn, reused by all 32 (same shapes and distributions)
+    ids = synth.random_tokens(spec, prompt, seed=1)
+    sess = parallel.tensor_parallel_session(model, max_context=ctx) if world > 1 else engine.CudaSession(model, max_context=ctx, device=local)
+    try:
+        def one_pass(steps):
+            sess.rollback(0)
+            logits = sess.eval(ids)
+            pre = sess.stats()["device_ms"]
+            sess.generate_greedy(int(np.argmax(logits)), steps)
+            return pre, sess.stats()["device_ms"]
+        one_pass(16)
+        barrier()
+        pre_ms, dec_ms = one_pass(decode)
+        barrier()
+        # share of a decode step spent exchanging activations: per-phase device time of 16 more steps (profiling runs the
+        # step kernel by kernel, so this is a share, not a speed)
+        sess.rollback(prompt)
+        sess.profile(True)
+        sess.generate_greedy(0, 16)
+        phases = sess.profile(False)
+        total = sum(v["ms"] for v in phases.values())
+        exchange = phases.get("exchange", {"ms": 0.0})["ms"] / total if total > 0 else 0.0
+        pre_ms, dec_ms = max_over_ranks(pre_ms), max_over_ranks(dec_ms)
+        weight_bytes = model.weight_bytes()
+        peak, peak_kind = peaks()
+        per_gpu = weight_bytes / world * decode / (dec_ms * 1e-3) / 1e9
+        return {"config": f"{spec.name}: {spec.layers} layers, hidden {spec.hidden}, {spec.heads}/{spec.kv_heads} heads x {spec.head_dim}, ffn {spec.ffn}, "
+                          f"vocab {spec.vocab}, Q4_0; {prompt}-token random prompt + {decode} greedy decode steps, batch 1, f16 K/V cache, ctx {ctx}",
+                "tp": world, "parallelism": "single GPU" if world == 1 else f"tensor parallel x{world}: matrices split by output rows, K/V heads split",
+                "decode_tokens_per_s": decode / (dec_ms * 1e-3), "decode_us_per_token": 1e3 * dec_ms / decode,
+                "prefill_tokens_per_s": prompt / (pre_ms * 1e-3), "scaling": "strong",
+                "roofline_frac_per_gpu": per_gpu / peak, "roofline_achieved_gbs_per_gpu": per_gpu, "peak_kind": f"of {peak_kind}",
+                "exchange_share_of_decode_step": exchange, "single_token_path": sess.step_path()}
+    finally:
+        sess.close()
+
 
 def main():
     args = parse()
@@ -322,6 +392,12 @@ def main():
         return float(t.item())
 
     pre_ms, dec_ms, e_pre, e_dec = (max_over_ranks(v) for v in (pre_ms, dec_ms, e_pre, e_dec))
+    tp_line = None
+    if not args.profile and not args.no_tp and args.config == "qwen3-0.6b-q4_0" and not args.layers:
+        try:
+            tp_line = tensor_parallel_section(engine, torch, dist, rank, local, world, max_over_ranks, barrier)
+        except Exception as e:  # reported, never allowed to take the headline down with it
+            tp_line = {"failed": f"{type(e).__name__}: {e}"}
     if rank == 0:
         peak, peak_kind = peaks()
         tokens = args.steps * decode
@@ -341,7 +417,8 @@ def main():
                 "gpu_launches": launches,
                 "clocks": clocks,
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                             "traffic": MEASURED_TRAFFIC_PER_TOKEN.get(args.config) if (world == 1 and not args.layers) else None,
+                             "traffic": analytic_traffic(spec, weight_bytes, prompt, decode) if world == 1 else None,
+                             "traffic_kind": "analytic: weights + visible K/V at the mean context + logits (ncu captures under profiles/ agree)",
                              "peak_kind": f"of {peak_kind}", "kernel": "decode step (all kernels of one token)",
                              "algorithmic_bytes_per_token": weight_bytes // (world if tensor_parallel else 1)}}
         line["config"]["single_token_path"] = sess.step_path()
@@ -351,15 +428,29 @@ def main():
         if world == 1 and not args.no_cpu_baseline and not args.profile:
             try:
                 threads = os.cpu_count() or 1
-                sp, sd = cpu_sample_sizes(spec)
+                sp, sd = cpu_sample_sizes(spec, prompt, decode)
                 kind, kernels, run, close = cpu_engine(model, spec, threads)
-                tp, td = run(synth.random_tokens(spec, sp, seed=1), sd)
+                cpu_ids = synth.random_tokens(spec, sp, seed=1)
+                tp, td, want_picks, want_logits = run(cpu_ids, sd, want_logits=True)
                 close()
+                whole = (sp, sd - 1) == (prompt, decode)
                 line["cpu_baseline"] = {"value": (sd - 1) / td, "unit": UNIT, "cores": threads, "kind": kind,
-                                        "sample": f"{sp}-token prompt + {sd} greedy steps of the same model ({kernels} kernels)",
+                                        "sample": ("the whole workload: " if whole else "") + f"{sp}-token prompt + {sd - 1} decoded tokens of the same model ({kernels} kernels)",
                                         "prefill_tokens_per_s": sp / tp}
+                # parity on this very run: the device's logits for the CPU leg's prompt and picks against the CPU leg's own
+                sess.rollback(0)
+                first = sess.eval(cpu_ids)
+                got_picks, got_logits = sess.generate_greedy(int(np.argmax(first)), sd - 1, want_logits=True)
+                got = np.concatenate([first[None, :], got_logits])
+                got_all = np.concatenate([[int(np.argmax(first))], got_picks])[:sd]
+                diff = np.abs(got - want_logits)
+                rel = max(float(np.linalg.norm((g - w).astype(np.float64)) / max(np.linalg.norm(w.astype(np.float64)), 1e-30)) for g, w in zip(got, want_logits))
+                line["parity"] = {"against": kind, "rows": int(sd), "max_abs": float(diff.max()), "rel_l2": rel, "bit_equal": bool(np.array_equal(got, want_logits)),
+                                  "greedy_ids_equal": bool(np.array_equal(got_all, want_picks)), "tolerance": {"max_abs": 2e-2, "rel_l2": 1e-3}}
             except Exception as e:  # the baseline is reported, never required
                 line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": f"failed: {e}"}
+        if tp_line is not None:
+            line["tensor_parallel"] = tp_line
         print(json.dumps(line), flush=True)
     sess.close()
     if dist is not None:

@@ -15,6 +15,8 @@ OUT = os.path.join(PKG, "libbrisk_cuda.so")
 OBJ = os.path.join(PKG, "build")
 SOURCES = ["repack.cu", "activations.cu", "matvec.cu", "gemm.cu", "gemm_k.cu", "misc.cu", "gemma.cu", "decode.cu", "step.cu", "token.cu", "session.cu", "hooks.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+# development aid: BRISK_TOK_TRACE=1 compiles cycle stamps into the one-launch token kernel (slower; never the default)
+EXTRA = ["-DBK_TOK_TRACE"] if os.environ.get("BRISK_TOK_TRACE") else []
 FLAGS = ["-std=c++20", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-fmad=false",
          "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v"]
 
@@ -44,7 +46,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
     def compile_one(job):
         path, obj = job
-        r = subprocess.run([NVCC, *FLAGS, "-c", path, "-o", obj], capture_output=True, text=True)
+        r = subprocess.run([NVCC, *FLAGS, *EXTRA, "-c", path, "-o", obj], capture_output=True, text=True)
         with open(obj + ".log", "w") as f:
             f.write(r.stderr)
         if r.returncode != 0:

@@ -1,30 +1,34 @@
 // One decoded token as ONE kernel launch: embedding row -> every layer -> output head -> arg-max -> next token and
-// position, for models whose layer matrices are Q4_0 and small enough that one SM's share of a layer's weights fits its
-// shared memory (the 0.6B class). One 512-thread CTA per SM, launched cooperatively so that all CTAs are resident.
+// position, for models whose layer matrices and head are Q4_0 and small enough that an SM's share of a layer's weights
+// fits its shared memory (the 0.6B class). One 512-thread CTA per SM, launched cooperatively so all CTAs are resident.
 //
-// What bounds a token of such a model is not HBM (a layer is 9 MB: 1.4 us at full bandwidth) but the chain of ~170
-// dependent operations, each needing the whole result vector of the one before. The kernel is arranged around that:
+// A token of such a model is not bound by HBM (a layer is 9 MB: 1.4 us at full bandwidth) but by the chain of dependent
+// operations, each needing the whole result vector of the one before. Measured on B200, three things decide the length
+// of that chain, and the kernel is arranged around them:
 //
-//   * WEIGHTS NEVER WAIT FOR ACTIVATIONS. Every CTA owns a fixed, contiguous range of each matrix's rows. Its share of
-//     an operation's weights (nibble plane and scale plane, two cp.async.bulk copies per matrix segment, completion on
-//     an mbarrier) is requested one whole layer ahead - the moment the same operation of the previous layer has
-//     finished with the buffer - so when an operation's input arrives its weights are already in shared memory.
-//     K rows and V slices of the cached positions are requested at the start of the layer in the same spirit.
-//   * OPERATIONS HAND OVER THROUGH TAGGED PAIRS in L2 (see decode_body.cuh): each element is one 64-bit {value, tag}
-//     store; consumers re-read until the tag of this token, layer and operation is there. No grid barrier, no fence.
-//     Exchange vectors alternate between two copies by layer parity, so a vector is rewritten two layers later.
-//   * THE RESIDUAL STREAM LIVES IN REGISTERS of the threads that own its rows (the o and down projections split the
-//     hidden rows the same way), and is only broadcast, never read back.
-//   * ONE PROLOGUE PER OPERATION: the threads that fetched the input vector keep it in registers, reduce the sum of
-//     squares, scale, and quantise to 8 bits with two shuffles per 32-value block (8 values per thread); then every warp
-//     multiplies (row, 32-block chunk) tasks out of shared memory, and one thread per row adds the row's block terms in
-//     block order - the reference's order (src/quant.cpp:445-456, src/kernels.cpp:13-30).
-//   * THE HEAD STREAMS through per-warp double-buffered bulk copies (8 rows each) over the shared memory the layers no
-//     longer need, requested while the last down projection still runs; every CTA reduces its rows' maximum, CTA 0
-//     gathers the 148 candidates, applies std::max_element's rule (src/sampler.cpp:11-13) and feeds the next step.
+//   * DOUBLE PRECISION IS SCARCE: an SM retires about two f64 lane-operations per clock (one warp instruction per 16
+//     cycles), and the reference's arithmetic needs f64 in three places - the sums of squares of the RMS norms, the
+//     softmax's exp (glibc's algorithm is double inside, exact_math.h) and its denominator. So every f64 value is
+//     computed ONCE, by whoever owns the data, and travels with it: the owner of 32 residual values publishes their sum
+//     of squares; a score task computes the exps of its own 32 positions and publishes them with their partial sum.
+//   * WHO OWNS WHAT is aligned to the 32-value quantisation blocks: an output-projection / down-projection CTA owns whole
+//     blocks of the hidden rows (and keeps the residual stream of those rows in registers), a gate/up CTA owns whole
+//     blocks of the feed-forward rows, an attention CTA owns (head, 32 dimensions), a q/k/v CTA owns one whole head. The
+//     owner therefore finishes the vector: per-head RMS norm + RoPE + K/V cache store for q/k/v, 8-bit quantisation
+//     (quantize_q8_0, src/quant.cpp:115-142) for the attended and the gated vector - consumers of those two read a
+//     quarter of the bytes and copy them straight into the activation planes.
+//   * WEIGHTS NEVER WAIT FOR ACTIVATIONS: a CTA's rows of an operation (nibble plane and scale plane, cp.async.bulk,
+//     completion on an mbarrier) are requested a whole layer ahead, the moment the same operation of the previous layer
+//     has left the buffer; cached K rows and V slices are requested when the previous layer's attention has left theirs.
 //
-// All float arithmetic is the reference's, in the reference's order; results are bit-identical to the CPU engine and to
-// the other single-token paths. Every wait (tagged pairs, mbarriers) is bounded and ends in the error word.
+// Operations hand over through TAGGED WORDS in L2 (decode_body.cuh): one 64-bit {payload, tag} store per element,
+// consumers re-read until the tag of this token, layer and operation is there; no grid barrier, no fence. Vectors
+// alternate between two copies by layer parity. The code is kept small on purpose: the layer loop must stay inside the
+// instruction cache (a first version of 124 KB lost ~2.5 us per layer to refetching it).
+//
+// All float arithmetic is the reference's, in the reference's order (the f64 sums are tree-ordered, as in the other
+// single-token paths); results are bit-identical to the CPU engine and to the other paths. Every wait (tagged words,
+// mbarriers) is bounded and ends in the error word.
 #include <algorithm>
 #include <cstdio>
 #include <cstring>
@@ -38,11 +42,20 @@ namespace {
 constexpr uint32_t kTokThreads = 512;
 constexpr uint32_t kTokWarps = 16;
 constexpr uint32_t kVChunkPos = 512;           // positions per chunk of the V ring
-constexpr uint32_t kVRingChunks = 3;           // chunks the ring holds
-constexpr uint32_t kSub = 128;                 // positions per product tile of the weighted sum
-constexpr uint32_t kSubStride = kSub + 4;      // floats per column of a product tile
-constexpr uint32_t kTagsPerLayer = 8;
+constexpr uint32_t kSub = 256;                 // positions per product tile of the weighted sum
+constexpr uint32_t kSliceW = 32;               // head dimensions per attention CTA: one quantisation block
+constexpr uint32_t kTagsPerLayer = 8;          // q/k/v, scores, exps, attended, o, gated, down
 constexpr uint32_t kMbarLimit = 1u << 22;      // try_wait rounds before a bulk copy is declared lost
+constexpr uint32_t kNone = 0xffffffffu;
+
+#ifdef BK_TOK_TRACE
+#define TOK_STAMP(tr, k) do { if ((tr) != nullptr) (tr)[k] = (unsigned long long)clock64(); } while (0)
+#define TOK_TRACE_PTR(P, l, slot) (((P).trace != nullptr && threadIdx.x == 0 && (l) == 5 && (blockIdx.x == 0 || blockIdx.x == 40 || blockIdx.x == 100)) \
+    ? (P).trace + 4 * (2 + (P).n_layers * 6) + (blockIdx.x == 0 ? 0 : blockIdx.x == 40 ? 1 : 2) * 96 + (slot) * 12 : nullptr)
+#else
+#define TOK_STAMP(tr, k) do { } while (0)
+#define TOK_TRACE_PTR(P, l, slot) nullptr
+#endif
 
 struct alignas(16) TokLayer {
     const uint8_t* nib[7];  // q k v o gate up down: 16-byte units of nibbles, row-major
@@ -51,8 +64,6 @@ struct alignas(16) TokLayer {
     const float* ffn_norm;
     const float* q_norm;
     const float* k_norm;
-    const float* attn_sub_norm;
-    const float* ffn_sub_norm;
     const float* q_bias;
     const float* k_bias;
     const float* v_bias;
@@ -62,9 +73,10 @@ struct alignas(16) TokLayer {
 };
 static_assert(sizeof(TokLayer) % 16 == 0, "copied in 16-byte pieces");
 
-struct TokSmem {  // byte offsets into dynamic shared memory
-    uint32_t tabs, xlo, xhi, xd, xs, tile, w_down, w_qkv, w_o, w_gu, sslot, ps, vring, vown, prod, ring, total;
-    uint32_t sslot_bytes, n_sslots, head_rows, ring_slot_bytes;
+struct TokSmem {  // byte offsets into dynamic shared memory; `region` holds what a CTA's roles need, laid out per CTA
+    uint32_t tabs, xlo, xhi, xd, xs, tile, hv, sslot, region, total;
+    uint32_t sslot_bytes, n_sslots, head_rows, ring_slot_bytes, ring_chunks;
+    uint32_t size_a, size_b, size_d, size_c;  // weight buffers of the roles
 };
 
 struct TokParams {
@@ -73,16 +85,25 @@ struct TokParams {
     uint32_t hidden, q_rows, kv_rows, ffn, heads, kv_heads, vocab, max_context;
     float eps, scale;
     int act;  // EPI_SILU_MUL or EPI_RELU2_MUL
+    // role ranges over the CTAs
+    uint32_t n_units;              // head units (q heads, then k heads, then v heads): CTA u < n_units owns unit u
+    uint32_t bd_first, bd_ctas;    // CTAs owning hidden blocks (output and down projections)
+    uint32_t c_first, c_ctas;      // CTAs owning feed-forward blocks (gate/up)
+    uint32_t w_first;              // CTA w_first + t owns attention task t = head * slices + slice
     // tagged exchange vectors, two copies each (layer parity)
-    uint2* hid_a[2];   // residual stream after the embedding / a down projection
-    uint2* hid_b[2];   // after an output projection
-    uint2* xq[2];
-    uint2* xk[2];
-    uint2* xv[2];
-    uint2* sc[2];      // scores [heads][max_context]
-    uint2* att[2];
-    uint2* gated[2];
-    uint2* part;       // per CTA: {best value, tag}, {best index, tag}
+    uint2* ha[2];    // residual stream after the embedding / a down projection: hidden values ...
+    uint2* hsa[2];   // ... and per 32-value block the f64 sum of their squares (two words)
+    uint2* hb[2];    // after an output projection
+    uint2* hsb[2];
+    uint2* xq[2];    // q after per-head norm and RoPE
+    uint2* xk[2];    // k after norm and RoPE, rounded to f16
+    uint2* xv[2];    // v (+bias), unrounded
+    uint2* sc[2];    // per (head, 32 positions): the maximum of those scores
+    uint2* ex[2];    // exp(score - max) [heads][max_context]
+    uint2* exs[2];   // per (head, 32 positions): f64 sum of those exps (two words)
+    uint2* aq[2];    // attended vector, quantised: per block 8 words of 4 int8, scale, sum
+    uint2* gq[2];    // gated vector, quantised likewise
+    uint2* part;     // per CTA: {best value}, {best index}
     // model ends
     const uint8_t* embd_nib;
     const __half* embd_scl;
@@ -94,20 +115,40 @@ struct TokParams {
     float* hidden_out;       // final residual stream as plain floats (debug reads)
     float* logits;
     // step state
-    const int32_t* token;    // the token to evaluate
+    int32_t* token;          // the token to evaluate; advancing, the next one is written here
     uint32_t* position;
     int32_t* chosen;         // arg-max of the logits
-    int32_t* token_slot;     // advance: next input token (may alias `token`)
     int32_t* history;
     uint32_t* history_len;
     uint32_t* epoch;         // launches so far; tags of a launch start above epoch * tags_per_launch
     uint32_t tags_per_launch;
     unsigned int* error;
     int advance;
-    uint32_t slice_w;        // columns of V per weighted-sum CTA (16 or 32)
     unsigned long long* trace;  // optional: CTA 0 stamps the end of every phase (ns)
     TokSmem sm;
 };
+
+// What this CTA does, worked out once at the start of the kernel.
+struct Roles {
+    uint32_t unit;                // head unit of the q/k/v multiply, or kNone
+    uint32_t bd_blk0, bd_blks;    // hidden blocks of the output / down projections (bd_blks = 0: none)
+    uint32_t c_blk0, c_blks;      // feed-forward blocks of gate/up
+    uint32_t wtask;               // attention task, or kNone
+    uint32_t off_a, off_b, off_d, off_c, off_w;  // byte offsets of the roles' buffers inside the region
+    // per multiply (q/k/v, output projection, gate/up, down): rows in the buffer, 16-byte units per row, first matrix, its first
+    // row, buffer offset, and for q/k/v the head's index among its kind
+    uint32_t op_rows[4], op_units[4], op_mat[4], op_first[4], op_off[4], op_head;
+};
+
+// The kernel's shared memory, declared at file scope: a device function that is handed a pointer to shared memory as an
+// argument sees a generic pointer and compiles generic loads and stores (measured: the serial add chains ran at 21 cycles
+// per add instead of 7); a function that names the array itself gets shared-memory instructions.
+extern __shared__ __align__(128) unsigned char tok_smem[];
+__shared__ double g_red[kTokWarps];
+__shared__ uint64_t g_exp_table[32];
+__shared__ Roles g_roles;
+__shared__ __align__(8) uint64_t g_bars[4];
+__shared__ __align__(8) uint64_t g_hbar[kTokWarps][2];
 
 // ---- small device helpers ---------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t saddr(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -128,7 +169,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* b, uint32_t parity) {
 }
 // Bounded: a bulk copy from valid memory always completes; if it does not within the limit the error word is set and the
 // caller goes on (with garbage), so the kernel still ends.
-__device__ __forceinline__ void mbar_wait(uint64_t* b, uint32_t parity, unsigned int* error) {
+__device__ __noinline__ void mbar_wait(uint64_t* b, uint32_t parity, unsigned int* error) {
     for (uint32_t spin = 0; !mbar_try_wait(b, parity); ++spin) {
         if (spin == kMbarLimit || poll_abandoned(spin, error)) {
             poll_failed(error);
@@ -147,8 +188,7 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
 __device__ __forceinline__ unsigned long long tok_now() {
     unsigned long long t;
@@ -156,31 +196,7 @@ __device__ __forceinline__ unsigned long long tok_now() {
     return t;
 }
 
-__host__ __device__ inline uint32_t part_lo(uint32_t rows, uint32_t cta, uint32_t nctas) { return uint32_t(uint64_t(rows) * cta / nctas); }
-
-// `count` tagged values (a multiple of 64) from src into shared memory at dst, by one warp; bounded re-reads.
-__device__ __forceinline__ void warp_fetch_pairs(const uint2* src, float* dst, uint32_t count, uint32_t tag, unsigned int* error) {
-    const uint32_t lane = threadIdx.x & 31;
-    const uint4* src2 = reinterpret_cast<const uint4*>(src);
-    for (uint32_t base = 0; base < count / 2; base += 64) {
-        uint4 v[2];
-        for (uint32_t spin = 0;; ++spin) {
-            v[0] = ld_pairs2(src2 + base + lane);
-            v[1] = ld_pairs2(src2 + base + 32 + lane);
-            if (v[0].y == tag && v[0].w == tag && v[1].y == tag && v[1].w == tag) break;
-            if (spin == kPollLimit || poll_abandoned(spin, error)) {
-                poll_failed(error);
-                break;
-            }
-        }
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-            const uint32_t i = base + 32 * k + lane;
-            dst[2 * i] = __uint_as_float(v[k].x);
-            dst[2 * i + 1] = __uint_as_float(v[k].z);
-        }
-    }
-}
+__host__ __device__ inline uint32_t part_lo(uint32_t rows, uint32_t idx, uint32_t parts) { return uint32_t(uint64_t(rows) * idx / parts); }
 
 // first maximum wins; a NaN is never chosen (comparisons with it are false)
 __device__ __forceinline__ void tok_better(float& v, int32_t& i, float ov, int32_t oi) {
@@ -190,73 +206,126 @@ __device__ __forceinline__ void tok_better(float& v, int32_t& i, float ov, int32
     }
 }
 
-// ---- one multiply --------------------------------------------------------------------------------------------------
-struct Shape {  // this CTA's share of one operation: up to three runs of rows, each inside one matrix
-    uint32_t rows, nseg;
-    uint32_t seg_rows[3], seg_first[3], seg_mat[3];
-};
+// Two tagged words with one 16-byte load, re-read until both carry `tag` (bounded). Out of line: the single polls of the
+// kernel share these few instructions.
+__device__ __noinline__ uint2 poll_words2(const uint2* p, uint32_t tag, unsigned int* error) {
+    uint4 v = ld_pairs2(p);
+    for (uint32_t spin = 0; v.y != tag || v.w != tag; ++spin) {
+        if (spin == kPollLimit || poll_abandoned(spin, error)) {
+            poll_failed(error);
+            break;
+        }
+        v = ld_pairs2(p);
+    }
+    return make_uint2(v.x, v.z);
+}
+// N pairs of tagged words, `stride` words apart, ALL loads in flight together and re-read together until every tag is
+// there: a vector costs one L2 round trip per re-read, not one per load. Pairs at or past `count` are skipped (zeros).
+template <int N>
+__device__ __forceinline__ void poll_batch(const uint2* p, uint32_t stride, uint32_t first, uint32_t count, uint32_t tag, unsigned int* error, uint2 (&out)[N]) {
+    uint4 v[N];
+    for (uint32_t spin = 0;; ++spin) {
+        bool complete = true;
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+            const uint32_t e = first + k * stride;
+            v[k] = e < count ? ld_pairs2(p + e) : make_uint4(0u, tag, 0u, tag);
+        }
+#pragma unroll
+        for (int k = 0; k < N; ++k) complete = complete && v[k].y == tag && v[k].w == tag;
+        if (complete) break;
+        if (spin == kPollLimit || poll_abandoned(spin, error)) {
+            poll_failed(error);
+            break;
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < N; ++k) out[k] = make_uint2(v[k].x, v[k].z);
+}
+// One tagged value, re-read until its tag is there (bounded). Out of line, like poll_words2.
+__device__ __noinline__ float poll_word(const uint2* p, uint32_t tag, unsigned int* error) {
+    uint2 v = ld_pair(p);
+    for (uint32_t spin = 0; v.y != tag; ++spin) {
+        if (spin == kPollLimit || poll_abandoned(spin, error)) {
+            poll_failed(error);
+            break;
+        }
+        v = ld_pair(p);
+    }
+    return __uint_as_float(v.x);
+}
+// The f64 butterfly sum, once in the code: a double-precision warp instruction occupies the SM's f64 unit for 16 cycles.
+__device__ __noinline__ double warp_sum_f64(double v) {
+#pragma unroll 1
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ void st_word(uint2* p, uint32_t payload, uint32_t tag) { st_pair(p, __uint_as_float(payload), tag); }
+// A double as two tagged words, low half first.
+__device__ __forceinline__ void st_double(uint2* p, double v, uint32_t tag) {
+    const unsigned long long b = (unsigned long long)__double_as_longlong(v);
+    st_word(p, uint32_t(b), tag);
+    st_word(p + 1, uint32_t(b >> 32), tag);
+}
+__device__ __forceinline__ double words_double(uint2 w) { return __longlong_as_double((long long)((unsigned long long)w.x | ((unsigned long long)w.y << 32))); }
 
-// The tagged vector x (n values; n % 256 == 0, n <= 4096) -> optional RMS norm -> Q8_0 planes in shared memory
-// (quantize_q8_0, src/quant.cpp:115-142; rms_norm, src/model.cpp:87-97). Thread t < n/8 owns values 8t..8t+7 from the poll
-// to the packed bytes: a 32-value block is four neighbouring lanes, its maximum and its sum two shuffles each.
-// Contains CTA barriers: all 512 threads call it.
-#define TOK_STAMP(tr, k) do { if ((tr) != nullptr) (tr)[k] = tok_now(); } while (0)
-__device__ __forceinline__ void tok_prologue(const TokParams& P, unsigned char* smem, double* red, const uint2* x, uint32_t tag, uint32_t n,
-                                             const float* norm, unsigned long long* tr = nullptr) {
-    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+// ---- activation prologues -------------------------------------------------------------------------------------------
+struct Planes {
+    unsigned char* xlo;  // per block the 8-bit values 0..15 (they meet the low nibbles of the weights)
+    unsigned char* xhi;  // per block the values 16..31
+    float* xd;           // per block the f16-rounded scale
+    int* xs;             // per block the sum of its 32 integers
+};
+__device__ __forceinline__ Planes planes_of(const TokParams& P, unsigned char* smem) {
+    return Planes{smem + P.sm.xlo, smem + P.sm.xhi, reinterpret_cast<float*>(smem + P.sm.xd), reinterpret_cast<int*>(smem + P.sm.xs)};
+}
+
+// f32 input (the residual stream) with its owners' sums of squares: RMS norm (rms_norm, src/model.cpp:87-97), then
+// quantize_q8_0 (src/quant.cpp:115-142). x: n tagged values (n % 256 == 0, n <= 4096); sums: per 32-value block the f64
+// sum of squares as two words. Thread t < n/8 owns values 8t..8t+7 from the poll to the packed bytes: a block is four
+// neighbouring lanes, its maximum and its sum two shuffles each. Warp 0 alone adds the block sums (f64 is scarce) and
+// hands the scale over through shared memory. Contains two CTA barriers: all 512 threads call it.
+__device__ __noinline__ void prologue_f32(const TokParams& P, unsigned char* smem, double* red, const uint2* x, const uint2* sums, uint32_t tag,
+                                          uint32_t n, const float* norm) {
+    smem = tok_smem;
+    red = g_red;
+    const uint32_t tid = threadIdx.x, lane = tid & 31;
     const bool mine = tid < n / 8;  // whole warps: n / 8 is a multiple of 32
     float v[8];
     float4 w0 = make_float4(0.f, 0.f, 0.f, 0.f), w1 = w0;
     if (mine) {
-        if (norm != nullptr) {  // independent of the previous operation: in flight while the poll waits
-            w0 = __ldg(reinterpret_cast<const float4*>(norm) + 2 * tid);
-            w1 = __ldg(reinterpret_cast<const float4*>(norm) + 2 * tid + 1);
-        }
-        const uint4* src = reinterpret_cast<const uint4*>(x) + 4 * tid;
-        uint4 a[4];
-        for (uint32_t spin = 0;; ++spin) {
-#pragma unroll
-            for (int k = 0; k < 4; ++k) a[k] = ld_pairs2(src + k);
-            bool complete = true;
-#pragma unroll
-            for (int k = 0; k < 4; ++k) complete = complete && a[k].y == tag && a[k].w == tag;
-            if (complete) break;
-            if (spin == kPollLimit || poll_abandoned(spin, P.error)) {
-                poll_failed(P.error);
-                break;
-            }
-        }
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            v[2 * k] = __uint_as_float(a[k].x);
-            v[2 * k + 1] = __uint_as_float(a[k].z);
-        }
-    } else {
-#pragma unroll
-        for (int k = 0; k < 8; ++k) v[k] = 0.0f;
+        w0 = __ldg(reinterpret_cast<const float4*>(norm) + 2 * tid);  // independent of the previous operation
+        w1 = __ldg(reinterpret_cast<const float4*>(norm) + 2 * tid + 1);
     }
-    TOK_STAMP(tr, 2);
-    if (norm != nullptr) {
-        double part = 0.0;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) part += double(__fmul_rn(v[k], v[k]));
-        part = warp_sum(part);
-        if (lane == 0) red[warp] = part;
-        cta_sync();
-        TOK_STAMP(tr, 3);
+    // ONE warp waits for the input: it polls the owners' block sums, which they publish after their values. Everybody
+    // else is parked at the barrier - sixteen warps re-reading L2 in a loop slow down whatever else runs on the SM and
+    // the very stores they are waiting for.
+    float* fs = reinterpret_cast<float*>(red);
+    if (tid >= kTokThreads - 32) {
         double total = 0.0;
-#pragma unroll
-        for (uint32_t w = 0; w < kTokWarps; ++w) total += red[w];
+        for (uint32_t b = lane; b < n / 32; b += 32) total += words_double(poll_words2(sums + 2 * b, tag, P.error));
+        total = warp_sum_f64(total);
         const bool pow2 = (n & (n - 1)) == 0;
         const double recip = __longlong_as_double((long long)(1023 - (31 - __clz(int(n)))) << 52);
         const float mean = float(pow2 ? total * recip : total / double(n));
-        const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, P.eps)));
+        if (lane == 0) fs[0] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, P.eps)));
+    }
+    cta_sync();
+    if (mine) {  // the values are (all but surely) there by now; their tags are still what decides
+        uint2 w[4];
+        poll_batch<4>(x + 8 * tid, 2, 0, 8, tag, P.error, w);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            v[2 * k] = __uint_as_float(w[k].x);
+            v[2 * k + 1] = __uint_as_float(w[k].y);
+        }
+    }
+    if (mine) {
+        const float scale = fs[0];
         v[0] = __fmul_rn(__fmul_rn(v[0], scale), w0.x); v[1] = __fmul_rn(__fmul_rn(v[1], scale), w0.y);
         v[2] = __fmul_rn(__fmul_rn(v[2], scale), w0.z); v[3] = __fmul_rn(__fmul_rn(v[3], scale), w0.w);
         v[4] = __fmul_rn(__fmul_rn(v[4], scale), w1.x); v[5] = __fmul_rn(__fmul_rn(v[5], scale), w1.y);
         v[6] = __fmul_rn(__fmul_rn(v[6], scale), w1.z); v[7] = __fmul_rn(__fmul_rn(v[7], scale), w1.w);
-    }
-    if (mine) {
         float amax = 0.0f;
 #pragma unroll
         for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(v[k]));
@@ -274,26 +343,82 @@ __device__ __forceinline__ void tok_prologue(const TokParams& P, unsigned char* 
         sum += __shfl_xor_sync(0xffffffffu, sum, 2);
         const uint32_t p0 = uint32_t(q[0] & 0xFF) | (uint32_t(q[1] & 0xFF) << 8) | (uint32_t(q[2] & 0xFF) << 16) | (uint32_t(q[3] & 0xFF) << 24);
         const uint32_t p1 = uint32_t(q[4] & 0xFF) | (uint32_t(q[5] & 0xFF) << 8) | (uint32_t(q[6] & 0xFF) << 16) | (uint32_t(q[7] & 0xFF) << 24);
-        // values 0..15 of a block meet the low nibbles of its weights, 16..31 the high nibbles: two planes of 16 bytes per block
+        const Planes pl = planes_of(P, smem);
         const uint32_t b = tid >> 2, k4 = tid & 3;
-        unsigned char* plane = smem + (k4 < 2 ? P.sm.xlo : P.sm.xhi) + b * 16 + (k4 & 1) * 8;
-        *reinterpret_cast<uint2*>(plane) = make_uint2(p0, p1);
+        *reinterpret_cast<uint2*>((k4 < 2 ? pl.xlo : pl.xhi) + b * 16 + (k4 & 1) * 8) = make_uint2(p0, p1);
         if (k4 == 0) {
-            reinterpret_cast<float*>(smem + P.sm.xd)[b] = __half2float(__float2half_rn(dd));
-            reinterpret_cast<int*>(smem + P.sm.xs)[b] = sum;
+            pl.xd[b] = __half2float(__float2half_rn(dd));
+            pl.xs[b] = sum;
         }
     }
-    TOK_STAMP(tr, 4);
     cta_sync();
-    TOK_STAMP(tr, 5);
 }
 
+// Input that its owners already quantised (the attended and the gated vector): per block ten words - eight of four 8-bit
+// values, the scale, the sum - copied into the planes as they arrive. One CTA barrier: all 512 threads call it.
+__device__ __noinline__ void prologue_q8(const TokParams& P, unsigned char* smem, const uint2* x, uint32_t tag, uint32_t nblocks) {
+    smem = tok_smem;
+    const Planes pl = planes_of(P, smem);
+    // TWO warps fetch the whole vector, every word of it in every re-read (a few kilobytes): the wait ends with the data
+    // already in registers, and the other fourteen warps are parked at the barrier instead of re-reading L2 in a loop.
+    if (threadIdx.x >= kTokThreads - 64) {  // two warps, eight pairs per lane and re-read each: up to 102 blocks in one go
+        const uint32_t lane = threadIdx.x & 31, pairs = nblocks * 5;
+        for (uint32_t base = ((threadIdx.x >> 5) & 1) * 8 * 32; base < pairs; base += 2 * 8 * 32) {
+            uint2 w[8];
+            poll_batch<8>(x, 64, 2 * (base + lane), 2 * pairs, tag, P.error, w);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const uint32_t e = 2 * (base + lane + 32 * k);  // word index, even
+                if (e < 2 * pairs) {
+                    const uint32_t blk = e / 10, wi = e - 10 * blk;
+                    if (wi < 8) {
+                        *reinterpret_cast<uint2*>((wi < 4 ? pl.xlo : pl.xhi) + blk * 16 + (wi & 3) * 4) = w[k];
+                    } else {
+                        pl.xd[blk] = __uint_as_float(w[k].x);
+                        pl.xs[blk] = int(w[k].y);
+                    }
+                }
+            }
+        }
+    }
+    cta_sync();
+}
+
+// One warp quantises the 32 values its lanes hold (lane = index in the block) and publishes the block's ten words.
+__device__ __noinline__ void publish_block_q8(uint2* dst, float r, uint32_t tag) {
+    const uint32_t lane = threadIdx.x & 31;
+    const float amax = warp_max(fabsf(r));
+    const float dd = __fdiv_rn(amax, 127.0f);
+    const float inv = dd != 0.0f ? __fdiv_rn(1.0f, dd) : 0.0f;
+    const int q = __float2int_rn(__fmul_rn(r, inv));
+    const int sum = warp_sum(q);
+    uint32_t word = uint32_t(q & 0xFF) << (8 * (lane & 3));
+    word |= __shfl_xor_sync(0xffffffffu, word, 1);
+    word |= __shfl_xor_sync(0xffffffffu, word, 2);
+    if ((lane & 3) == 0) st_word(dst + (lane >> 2), word, tag);
+    if (lane == 1) st_word(dst + 8, __float_as_uint(__half2float(__float2half_rn(dd))), tag);
+    if (lane == 2) st_word(dst + 9, uint32_t(sum), tag);
+}
+
+// A row's block terms added in block order: one dependent chain of adds, 16 per pass with their four loads on top.
+// blocks is a multiple of 8.
 __device__ __forceinline__ float chain_row(const float* t, uint32_t blocks) {
     float run = 0.0f;
-#pragma unroll 4
-    for (uint32_t b = 0; b < blocks; b += 4) {
-        const float4 q = *reinterpret_cast<const float4*>(t + b);
-        run = __fadd_rn(run, q.x); run = __fadd_rn(run, q.y); run = __fadd_rn(run, q.z); run = __fadd_rn(run, q.w);
+    uint32_t b = 0;
+#pragma unroll 1
+    for (; b + 16 <= blocks; b += 16) {
+        const float4* c4 = reinterpret_cast<const float4*>(t + b);
+        const float4 p0 = c4[0], p1 = c4[1], p2 = c4[2], p3 = c4[3];
+        run = __fadd_rn(run, p0.x); run = __fadd_rn(run, p0.y); run = __fadd_rn(run, p0.z); run = __fadd_rn(run, p0.w);
+        run = __fadd_rn(run, p1.x); run = __fadd_rn(run, p1.y); run = __fadd_rn(run, p1.z); run = __fadd_rn(run, p1.w);
+        run = __fadd_rn(run, p2.x); run = __fadd_rn(run, p2.y); run = __fadd_rn(run, p2.z); run = __fadd_rn(run, p2.w);
+        run = __fadd_rn(run, p3.x); run = __fadd_rn(run, p3.y); run = __fadd_rn(run, p3.z); run = __fadd_rn(run, p3.w);
+    }
+    if (b < blocks) {
+        const float4* c4 = reinterpret_cast<const float4*>(t + b);
+        const float4 p0 = c4[0], p1 = c4[1];
+        run = __fadd_rn(run, p0.x); run = __fadd_rn(run, p0.y); run = __fadd_rn(run, p0.z); run = __fadd_rn(run, p0.w);
+        run = __fadd_rn(run, p1.x); run = __fadd_rn(run, p1.y); run = __fadd_rn(run, p1.z); run = __fadd_rn(run, p1.w);
     }
     return run;
 }
@@ -314,379 +439,474 @@ __device__ __forceinline__ float q4_0_term(const uint4 q, const __half d, const 
     return __fmul_rn(__fmul_rn(float(acc), __half2float(d)), xd);
 }
 
-struct MulArgs {
-    const uint2* x;
-    uint32_t tag_x, tag_out, cols;
-    const float* norm;
-    const unsigned char* w;  // shared memory: this CTA's rows
-    uint64_t* bar;
-    uint32_t parity;
-    int kind;                // 0: store per matrix (q/k/v), 1: add to the residual, 2: gate/up pair
-    unsigned long long* tr;  // development aid: 10 stamps of this thread, or nullptr
-    uint2* out[3];           // per segment
-    float* plain;            // kind 1: also the plain copy of the result, or nullptr
-    int act;
-};
-
-// One operation of this CTA: returns the residual value of row `tid` of the CTA's hidden rows (kind 1 updates it).
-__device__ __noinline__ float tok_multiply(const TokParams& P, unsigned char* smem, double* red, const Shape& sh, const MulArgs& a, float hres) {
-    if (sh.rows == 0) return hres;  // no rows here: this CTA must not read the input either
-    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint32_t units = a.cols / 32, tstride = units + 4;
-    TOK_STAMP(a.tr, 0);
-    mbar_wait(a.bar, a.parity, P.error);  // requested a layer ago: long since there
-    TOK_STAMP(a.tr, 1);
-    tok_prologue(P, smem, red, a.x, a.tag_x, a.cols, a.norm, a.tr);
-    const unsigned char* wn = a.w;
-    const __half* ws = reinterpret_cast<const __half*>(a.w + size_t(sh.rows) * units * 16);
+// rows x units block terms out of shared memory into the tile: every warp takes (row, 32-block chunk) tasks, lane =
+// block. Chunk-major, so a warp's consecutive tasks share the activation block it holds in registers.
+__device__ __noinline__ void tile_terms(const TokParams& P, unsigned char* smem, const unsigned char* w, uint32_t rows, uint32_t units) {
+    smem = tok_smem;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, tstride = units + 4;
+    const __half* ws = reinterpret_cast<const __half*>(w + size_t(rows) * units * 16);
     float* tile = reinterpret_cast<float*>(smem + P.sm.tile);
     const uint4* xlo = reinterpret_cast<const uint4*>(smem + P.sm.xlo);
     const uint4* xhi = reinterpret_cast<const uint4*>(smem + P.sm.xhi);
     const float* xd = reinterpret_cast<const float*>(smem + P.sm.xd);
     const int* xs = reinterpret_cast<const int*>(smem + P.sm.xs);
-    const uint32_t chunks = (units + 31) / 32, tasks = sh.rows * chunks;
-    uint32_t cur = 0xffffffffu;
-    uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
-    float xdv = 0.0f;
-    int xsv = 0;
-    for (uint32_t t = warp; t < tasks; t += kTokWarps) {  // chunk-major: a warp's consecutive tasks share the activation block
-        const uint32_t c = t / sh.rows, j = t - c * sh.rows, u = c * 32 + lane;
-        const bool valid = u < units;
-        const uint32_t uu = valid ? u : 0;
-        if (c != cur) {
-            lo = xlo[uu]; hi = xhi[uu]; xdv = xd[uu]; xsv = xs[uu];
-            cur = c;
-        }
-        const uint4 q = *reinterpret_cast<const uint4*>(wn + (size_t(j) * units + uu) * 16);
-        const __half d = ws[j * units + uu];
-        const float term = q4_0_term(q, d, lo, hi, xdv, xsv);
-        if (valid) tile[j * tstride + u] = term;
-    }
-    TOK_STAMP(a.tr, 6);
-    cta_sync();
-    TOK_STAMP(a.tr, 7);
-    if (a.kind == 2) {
-        const uint32_t pairs = sh.rows / 2;
-        if (tid < pairs) {
-            const float* tg = tile + tid * tstride;
-            const float* tu = tile + (pairs + tid) * tstride;
-            float g = 0.0f, u = 0.0f;
-#pragma unroll 2
-            for (uint32_t b = 0; b < units; b += 4) {
-                const float4 qg = *reinterpret_cast<const float4*>(tg + b), qu = *reinterpret_cast<const float4*>(tu + b);
-                g = __fadd_rn(g, qg.x); u = __fadd_rn(u, qu.x);
-                g = __fadd_rn(g, qg.y); u = __fadd_rn(u, qu.y);
-                g = __fadd_rn(g, qg.z); u = __fadd_rn(u, qu.z);
-                g = __fadd_rn(g, qg.w); u = __fadd_rn(u, qu.w);
+    for (uint32_t c = 0; c * 32 < units; ++c) {
+        const uint32_t u = c * 32 + lane;
+        if (u < units) {
+            const uint4 lo = xlo[u], hi = xhi[u];
+            const float xdv = xd[u];
+            const int xsv = xs[u];
+            // two rows per pass: their loads are issued together, ahead of the arithmetic
+#pragma unroll 1
+            for (uint32_t j0 = warp; j0 < rows; j0 += 2 * kTokWarps) {
+                const uint32_t j1 = j0 + kTokWarps, j1c = min(j1, rows - 1);
+                const uint4 q0 = *reinterpret_cast<const uint4*>(w + (size_t(j0) * units + u) * 16);
+                const uint4 q1 = *reinterpret_cast<const uint4*>(w + (size_t(j1c) * units + u) * 16);
+                const __half d0 = ws[j0 * units + u], d1 = ws[j1c * units + u];
+                tile[j0 * tstride + u] = q4_0_term(q0, d0, lo, hi, xdv, xsv);
+                if (j1 < rows) tile[j1 * tstride + u] = q4_0_term(q1, d1, lo, hi, xdv, xsv);
             }
-            const float r = a.act == EPI_SILU_MUL ? silu_mul(g, u) : relu2_mul(g, u);
-            st_pair(a.out[0] + sh.seg_first[0] + tid, r, a.tag_out);
-        }
-    } else if (tid < sh.rows) {
-        const float sum = chain_row(tile + tid * tstride, units);
-        uint32_t j = tid, s = 0;
-        while (j >= sh.seg_rows[s]) {
-            j -= sh.seg_rows[s];
-            ++s;
-        }
-        const uint32_t row = sh.seg_first[s] + j;
-        if (a.kind == 1) {
-            hres = __fadd_rn(hres, sum);
-            st_pair(a.out[s] + row, hres, a.tag_out);
-            if (a.plain != nullptr) a.plain[row] = hres;
-        } else {
-            st_pair(a.out[s] + row, sum, a.tag_out);
         }
     }
-    TOK_STAMP(a.tr, 8);
+}
+
+// ---- the four multiplies of a layer --------------------------------------------------------------------------------
+// kind 0: q/k/v of this CTA's head unit   1: output projection (+residual)   2: gate/up (+activation)   3: down (+residual)
+struct OpRows {
+    uint32_t rows, units, mat, first, off;  // rows in the buffer, 16-byte units per row, first matrix, its first row, buffer offset
+};
+__device__ __forceinline__ OpRows op_rows(const Roles& R, uint32_t kind) { return OpRows{R.op_rows[kind], R.op_units[kind], R.op_mat[kind], R.op_first[kind], R.op_off[kind]}; }
+__device__ __forceinline__ void fill_ops(const TokParams& P, Roles& R) {  // once, by one thread
+    const uint32_t dim = P.q_rows / P.heads;
+    for (uint32_t kind = 0; kind < 4; ++kind) {
+        uint32_t rows = 0, units = 0, mat = 0, first = 0, off = 0;
+        if (kind == 0) {
+            if (R.unit != kNone) {
+                mat = R.unit < P.heads ? 0 : R.unit < P.heads + P.kv_heads ? 1 : 2;
+                R.op_head = R.unit - (mat == 0 ? 0 : mat == 1 ? P.heads : P.heads + P.kv_heads);
+                first = R.op_head * dim; rows = dim; units = P.hidden / 32; off = R.off_a;
+            }
+        } else if (kind == 2) {
+            mat = 4; first = R.c_blk0 * 32; rows = 64 * R.c_blks; units = P.hidden / 32; off = R.off_c;
+        } else {
+            mat = kind == 1 ? 3 : 6; first = R.bd_blk0 * 32; rows = 32 * R.bd_blks;
+            units = (kind == 1 ? P.q_rows : P.ffn) / 32; off = kind == 1 ? R.off_b : R.off_d;
+        }
+        R.op_rows[kind] = rows; R.op_units[kind] = units; R.op_mat[kind] = mat; R.op_first[kind] = first; R.op_off[kind] = off;
+    }
+}
+
+// Requests this CTA's rows of one multiply of `layer` into the multiply's buffer (one thread). Nibbles of all rows first,
+// then their scales; gate/up: the gate rows, then the same rows of up.
+__device__ __noinline__ void tok_request(const TokParams& P, unsigned char* smem, const Roles&, uint64_t* bars, uint32_t kind, uint32_t layer) {
+    smem = tok_smem;
+    bars = g_bars;
+    const Roles& R = g_roles;
+    const OpRows o = op_rows(R, kind);
+    if (o.rows == 0) return;
+    const TokLayer& L = reinterpret_cast<const TokLayer*>(smem + P.sm.tabs)[layer];
+    unsigned char* dst = smem + P.sm.region + o.off;
+    fence_async_proxy();  // the buffer's last readers were generic loads
+    mbar_expect_tx(&bars[kind], o.rows * o.units * 18);
+    const uint32_t segs = kind == 2 ? 2 : 1, seg_rows = o.rows / segs;
+    for (uint32_t s = 0; s < segs; ++s) {
+        const uint32_t m = o.mat + s;
+        bulk_g2s(dst + size_t(s) * seg_rows * o.units * 16, L.nib[m] + size_t(o.first) * o.units * 16, seg_rows * o.units * 16, &bars[kind]);
+        bulk_g2s(dst + size_t(o.rows) * o.units * 16 + size_t(s) * seg_rows * o.units * 2, L.scl[m] + size_t(o.first) * o.units, seg_rows * o.units * 2,
+                 &bars[kind]);
+    }
+}
+
+// Per-head RMS norm (optional) + RoPE of one head by ONE WARP (src/model.cpp:1031-1042, :104-115), from `hv` in shared
+// memory. q: the rotated head goes out as tagged words. k: it is rounded to f16, stored to the cache and published as
+// the rounded value (the score of the token's own position uses the cache's value).
+// `rope` (the position's cos/sin row) and `norm` (the head's norm weights, or nullptr) are copies in shared memory.
+__device__ __forceinline__ void head_norm_rope(const TokParams& P, const float* hv, const float* norm, const float* rope, int neox, uint32_t dim, uint2* out,
+                                               uint32_t tag, __half* cache_row) {
+    const uint32_t lane = threadIdx.x & 31;
+    float scale = 1.0f;
+    if (norm != nullptr) {
+        double part = 0.0;
+#pragma unroll 1
+        for (uint32_t i = lane; i < dim; i += 32) part += double(__fmul_rn(hv[i], hv[i]));
+        part = warp_sum_f64(part);
+        const float mean = float(part * (1.0 / double(dim)));  // the head size is a power of two: the same value as the division
+        scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, P.eps)));
+    }
+#pragma unroll 1
+    for (uint32_t p = lane; p < dim / 2; p += 32) {
+        const uint32_t ia = neox ? p : 2 * p, ib = neox ? p + dim / 2 : 2 * p + 1;
+        float x0 = hv[ia], x1 = hv[ib];
+        if (norm != nullptr) {
+            x0 = __fmul_rn(__fmul_rn(x0, scale), norm[ia]);
+            x1 = __fmul_rn(__fmul_rn(x1, scale), norm[ib]);
+        }
+        const float c = rope[2 * p], sn = rope[2 * p + 1];
+        float y0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, sn));
+        float y1 = __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, c));
+        if (cache_row != nullptr) {
+            const __half h0 = __float2half_rn(y0), h1 = __float2half_rn(y1);
+            cache_row[ia] = h0;
+            cache_row[ib] = h1;
+            y0 = __half2float(h0);
+            y1 = __half2float(h1);
+        }
+        st_pair(out + ia, y0, tag);
+        st_pair(out + ib, y1, tag);
+    }
+}
+
+// Tags of layer l start at T = base + 2 + l * kTagsPerLayer: +0 q/k/v, +1 scores, +2 exps, +3 attended, +4 output
+// projection, +5 gated, +6 down projection. base + 1 is the embedding.
+__device__ __noinline__ float tok_op(const TokParams& P, unsigned char* smem, double* red, const Roles&, uint64_t* bars, const uint64_t* exp_table,
+                                     const uint32_t kind, const uint32_t l, const uint32_t base, const uint32_t pos, const int neox, float hres) {
+    smem = tok_smem;
+    red = g_red;
+    bars = g_bars;
+    exp_table = g_exp_table;
+    const Roles& R = g_roles;
+    const OpRows o = op_rows(R, kind);
+    if (o.rows == 0) return hres;  // not this CTA's role: it must not read the input either
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t par = l & 1, T = base + 2 + l * kTagsPerLayer, tstride = o.units + 4;
+    const TokLayer& Ly = reinterpret_cast<const TokLayer*>(smem + P.sm.tabs)[l];
+    unsigned long long* tr = TOK_TRACE_PTR(P, l, kind);
+    (void)tr;
+    TOK_STAMP(tr, 0);
+    mbar_wait(&bars[kind], par, P.error);  // requested a layer ago: long since there
+    TOK_STAMP(tr, 1);
+    float* hv = reinterpret_cast<float*>(smem + P.sm.hv);  // [dim] the head's raw values | [dim] its norm weights | [dim] the position's RoPE row
+    const float* head_norm = kind != 0 ? nullptr : o.mat == 0 ? Ly.q_norm : o.mat == 1 ? Ly.k_norm : nullptr;
+    if (kind == 0 && warp == 8 && head_norm != nullptr) {  // a warp with nothing else to do before the first barrier
+        for (uint32_t i = lane; i < o.rows; i += 32) hv[o.rows + i] = __ldg(head_norm + i);
+    }
+    if (kind == 0) prologue_f32(P, smem, red, P.ha[par ^ 1], P.hsa[par ^ 1], l == 0 ? base + 1 : T - kTagsPerLayer + 6, P.hidden, Ly.attn_norm);
+    else if (kind == 2) prologue_f32(P, smem, red, P.hb[par], P.hsb[par], T + 4, P.hidden, Ly.ffn_norm);
+    else if (kind == 1) prologue_q8(P, smem, P.aq[par], T + 3, P.q_rows / 32);
+    else prologue_q8(P, smem, P.gq[par], T + 5, P.ffn / 32);
+    TOK_STAMP(tr, 2);
+    tile_terms(P, smem, smem + P.sm.region + o.off, o.rows, o.units);
+    TOK_STAMP(tr, 3);
+    cta_sync();
+    TOK_STAMP(tr, 4);
+    const float* tile = reinterpret_cast<const float*>(smem + P.sm.tile);
+    if (kind == 0) {
+        const uint32_t dim = o.rows, m = o.mat, head = R.op_head;  // head: index among the q heads, or among the K/V heads
+        const float* bias = m == 0 ? Ly.q_bias : m == 1 ? Ly.k_bias : Ly.v_bias;
+        float r = 0.0f;
+        if (tid < dim) {
+            r = chain_row(tile + tid * tstride, o.units);
+            if (bias != nullptr) r = __fadd_rn(r, bias[o.first + tid]);  // add_bias, src/model.cpp:1026-1030
+        }
+        const size_t cache_row = (size_t(head) * P.max_context + pos) * dim;
+        if (m == 2) {
+            if (tid < dim) {
+                st_pair(P.xv[par] + o.first + tid, r, T);
+                Ly.v_cache[cache_row + tid] = __float2half_rn(r);
+            }
+        } else {
+            if (tid < dim) hv[tid] = r;
+            TOK_STAMP(tr, 5);
+            cta_sync();
+            TOK_STAMP(tr, 6);
+            if (warp == 0) {
+                head_norm_rope(P, hv, head_norm != nullptr ? hv + dim : nullptr, hv + 2 * dim, neox, dim, (m == 0 ? P.xq[par] : P.xk[par]) + o.first, T,
+                               m == 0 ? nullptr : Ly.k_cache + cache_row);
+            }
+        }
+    } else if (kind == 2) {
+        const uint32_t half = o.rows / 2;
+        if (tid < half) {
+            const float g = chain_row(tile + tid * tstride, o.units), u = chain_row(tile + (half + tid) * tstride, o.units);
+            // silu_mul_f32 (src/kernels_f32.cpp:287-289): gate / (1 + exp(-gate)) * up; or the squared ReLU (src/model.cpp:1135-1138)
+            const float r = P.act == EPI_SILU_MUL ? __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, exact_expf_tab(-g, exp_table))), u) : relu2_mul(g, u);
+            publish_block_q8(P.gq[par] + size_t(R.c_blk0 + warp) * 10, r, T + 5);
+        }
+    } else if (tid < o.rows) {
+        const uint32_t row = o.first + tid, tag_out = kind == 1 ? T + 4 : T + 6;
+        hres = __fadd_rn(hres, chain_row(tile + tid * tstride, o.units));
+        st_pair((kind == 1 ? P.hb[par] : P.ha[par]) + row, hres, tag_out);
+        if (kind == 3 && l + 1 == P.n_layers) P.hidden_out[row] = hres;
+        const double sq = warp_sum_f64(double(__fmul_rn(hres, hres)));  // whole warps: the rows are whole blocks
+        if (lane == 0) st_double((kind == 1 ? P.hsb[par] : P.hsa[par]) + 2 * (R.bd_blk0 + warp), sq, tag_out);
+    }
+    TOK_STAMP(tr, 7);
     return hres;
 }
 
-// Requests this CTA's rows of one operation of `layer` into the operation's buffer (one thread).
-__device__ __forceinline__ void tok_request(const Shape& sh, const TokLayer& L, unsigned char* dst, uint32_t cols, uint64_t* bar) {
-    const uint32_t units = cols / 32;
-    mbar_expect_tx(bar, sh.rows * units * 18);
-    uint32_t joff = 0;
-    for (uint32_t s = 0; s < sh.nseg; ++s) {
-        const uint32_t m = sh.seg_mat[s], first = sh.seg_first[s], rows = sh.seg_rows[s];
-        bulk_g2s(dst + size_t(joff) * units * 16, L.nib[m] + size_t(first) * units * 16, rows * units * 16, bar);
-        bulk_g2s(dst + size_t(sh.rows) * units * 16 + size_t(joff) * units * 2, L.scl[m] + size_t(first) * units, rows * units * 2, bar);
-        joff += rows;
-    }
-}
-
 // ---- attention -----------------------------------------------------------------------------------------------------
-// Scores: WARP tasks of (K/V head, 32 positions) dealt round-robin over the CTAs; the warps 0..n_sslots-1 of a CTA take
-// its tasks, each with its own slice of shared memory: the group's query heads [group][dim] f32, the new K row [dim]
-// f32, and 32 cached K rows of dim halves padded by 16 bytes (so that the 16-byte reads of a quarter warp fall into
-// distinct banks). The K rows of a warp's first task are requested at the start of the layer. The task that covers the
-// token's own position also norms, rotates and stores the new K row and stores the new V row.
-__device__ __forceinline__ uint32_t score_tasks(const TokParams& P, uint32_t pos) { return P.kv_heads * ((pos + 1 + 31) / 32); }
-
-template <int VPL>
-__device__ __forceinline__ void scores_request(const TokParams& P, unsigned char* slot, const TokLayer& L, uint32_t task, uint32_t pos) {
-    constexpr uint32_t dim = VPL * 32;
-    const uint32_t lane = threadIdx.x & 31, group = P.heads / P.kv_heads;
+// Scores and exps: WARP tasks of (query head, 32 positions) dealt round-robin over the CTAs; warps 0..n_sslots-1 of a CTA
+// take its tasks, each with a slice of shared memory: the query head [dim] f32 | 32 K rows of dim halves padded by 16
+// bytes (so the 16-byte reads of a quarter warp fall into distinct banks). The cached rows are requested ahead; the
+// token's own row arrives as tagged words (already rounded to f16) and is put in its place among them. A task computes
+// its 32 scores (dot_f32's 16 interleaved partial sums, src/kernels_f32.cpp:231-254), publishes their maximum, takes the
+// head's maximum from all tasks' maxima, and publishes exp(score - max) of ITS positions with their f64 sum (softmax,
+// src/kernels_f32.cpp:275-284).
+__device__ __forceinline__ void scores_request(const TokParams& P, unsigned char* slot, const TokLayer& L, uint32_t task, uint32_t pos, uint32_t dim) {
+    const uint32_t lane = threadIdx.x & 31;
     const uint32_t chunks = (pos + 1 + 31) / 32;
-    const uint32_t kvh = task / chunks, p = (task % chunks) * 32 + lane;
+    const uint32_t kvh = (task / chunks) / (P.heads / P.kv_heads), p = (task % chunks) * 32 + lane;
     if (p < pos) {
         const __half* kr = L.k_cache + (size_t(kvh) * P.max_context + p) * dim;
-        const uint32_t dst = saddr(slot + size_t(group + 1) * dim * 4 + size_t(lane) * (dim * 2 + 16));
-#pragma unroll
+        const uint32_t dst = saddr(slot + dim * 4 + lane * (dim * 2 + 16));
+#pragma unroll 1
         for (uint32_t i = 0; i < dim / 8; ++i) cp_async16(dst + i * 16, kr + i * 8);
     }
 }
 
-template <int VPL, bool NEOX>
-__device__ __forceinline__ void tok_scores(const TokParams& P, unsigned char* smem, const TokLayer& L, uint32_t par, uint32_t tag_in, uint32_t tag_out,
-                                           uint32_t pos, uint32_t cta, uint32_t nctas) {
+// `count` tagged values (an even number) from src into dst (shared memory), by one warp: four loads per lane in flight.
+__device__ __forceinline__ void warp_fetch_words(const uint2* src, float* dst, uint32_t count, uint32_t tag, unsigned int* error) {
+    const uint32_t lane = threadIdx.x & 31;
+    uint2 w[4];
+    poll_batch<4>(src, 64, 2 * lane, count, tag, error, w);  // heads of up to 256 values
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const uint32_t e = 2 * lane + 64 * k;
+        if (e < count) {
+            dst[e] = __uint_as_float(w[k].x);
+            dst[e + 1] = __uint_as_float(w[k].y);
+        }
+    }
+}
+
+template <int VPL>
+__device__ __noinline__ void tok_scores(const TokParams& P, unsigned char* smem, const uint64_t* exp_table, uint32_t l, uint32_t base, uint32_t pos,
+                                        uint32_t cta, uint32_t nctas) {
+    smem = tok_smem;
+    exp_table = g_exp_table;
     constexpr uint32_t dim = VPL * 32;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (warp >= P.sm.n_sslots) return;
-    const uint32_t group = P.heads / P.kv_heads, visible = pos + 1, chunks = (visible + 31) / 32, tasks = P.kv_heads * chunks;
+    const TokLayer* tabs = reinterpret_cast<const TokLayer*>(smem + P.sm.tabs);
+    const uint32_t par = l & 1, T = base + 2 + l * kTagsPerLayer;
+    const uint32_t group = P.heads / P.kv_heads, visible = pos + 1, chunks = (visible + 31) / 32, tasks = P.heads * chunks;
     unsigned char* slot = smem + P.sm.sslot + size_t(warp) * P.sm.sslot_bytes;
     float* qs = reinterpret_cast<float*>(slot);
-    float* knew = qs + group * dim;
-    const uint4* krow = reinterpret_cast<const uint4*>(slot + size_t(group + 1) * dim * 4 + size_t(lane) * (dim * 2 + 16));
-    const float* rope = P.rope + size_t(pos) * dim;
+    unsigned char* krows = slot + dim * 4;
+    const uint4* krow = reinterpret_cast<const uint4*>(krows + lane * (dim * 2 + 16));
+#pragma unroll 1
     for (uint32_t i = warp;; i += P.sm.n_sslots) {
         const uint32_t task = cta + i * nctas;
         if (task >= tasks) break;
-        if (i >= P.sm.n_sslots) {  // beyond the task whose rows were requested at the start of the layer
+        if (i >= P.sm.n_sslots) {  // beyond the task whose rows were requested ahead
             __syncwarp();
-            scores_request<VPL>(P, slot, L, task, pos);
+            scores_request(P, slot, tabs[l], task, pos, dim);
             cp_async_commit();
         }
-        const uint32_t kvh = task / chunks, begin = (task % chunks) * 32, p = begin + lane;
-        const bool owner = pos >= begin && pos < begin + 32, cached = p < pos;
-        // the raw query heads of the group (adjacent in the q vector) and, for the owner, the raw new K row
-        {
-            const uint4* src = reinterpret_cast<const uint4*>(P.xq[par] + size_t(kvh) * group * dim);
-            const uint32_t n2 = group * dim / 2;  // 16-byte pieces of two pairs
-            for (uint32_t base = 0; base < n2; base += 64) {
-                uint4 v[2];
-                for (uint32_t spin = 0;; ++spin) {
-                    bool complete = true;
-#pragma unroll
-                    for (int k = 0; k < 2; ++k) {
-                        const uint32_t e = base + 32 * k + lane;
-                        v[k] = e < n2 ? ld_pairs2(src + e) : make_uint4(0u, tag_in, 0u, tag_in);
-                        complete = complete && v[k].y == tag_in && v[k].w == tag_in;
-                    }
-                    if (complete) break;
-                    if (spin == kPollLimit || poll_abandoned(spin, P.error)) {
-                        poll_failed(P.error);
-                        break;
-                    }
-                }
-#pragma unroll
-                for (int k = 0; k < 2; ++k) {
-                    const uint32_t e = base + 32 * k + lane;
-                    if (e < n2) {
-                        qs[2 * e] = __uint_as_float(v[k].x);
-                        qs[2 * e + 1] = __uint_as_float(v[k].z);
-                    }
-                }
-            }
-            if (owner) {
-                for (uint32_t e = lane; e < dim; e += 32) knew[e] = poll_pair(P.xk[par] + size_t(kvh) * dim + e, tag_in, P.error);
-            }
-        }
+        const uint32_t h = task / chunks, chunk = task % chunks, kvh = h / group, p = chunk * 32 + lane;
+        unsigned long long* tr = (i == warp && warp == 0) ? TOK_TRACE_PTR(P, l, 5) : nullptr;
+        (void)tr;
+        TOK_STAMP(tr, 0);
+        // one lane waits for the head (its last value), then the whole warp fetches it: whole warps re-reading L2 in a loop
+        // compete with whatever else runs on this SM meanwhile (a multiply, the chain of a weighted sum)
+        if (lane == 0) (void)poll_word(P.xq[par] + size_t(h) * dim + dim - 1, T, P.error);
         __syncwarp();
-        if (owner) {
-            float kv[VPL];
+        warp_fetch_words(P.xq[par] + size_t(h) * dim, qs, dim, T, P.error);
+        if (pos / 32 == chunk) {  // the token's own K row into the place of its position
+            uint2 w[4];
+            poll_batch<4>(P.xk[par] + size_t(kvh) * dim, 64, 2 * lane, dim, T, P.error, w);
+            __half2* own = reinterpret_cast<__half2*>(krows + (pos & 31) * (dim * 2 + 16));
 #pragma unroll
-            for (int k = 0; k < VPL; ++k) {
-                const uint32_t e = NEOX ? lane + 32 * k : VPL * lane + k;
-                kv[k] = knew[e];
-                if (L.k_bias != nullptr) kv[k] = __fadd_rn(kv[k], L.k_bias[size_t(kvh) * dim + e]);  // add_bias, src/model.cpp:1026-1030
-            }
-            warp_head_norm_rope<VPL, NEOX>(kv, L.k_norm, rope, P.eps, knew);
-            __syncwarp();
-            const size_t row = (size_t(kvh) * P.max_context + pos) * dim;
-            for (uint32_t e = lane; e < dim; e += 32) {
-                const __half kh = __float2half_rn(knew[e]);
-                knew[e] = __half2float(kh);  // the score of the own position uses the cache's f16 value
-                L.k_cache[row + e] = kh;
-                float v = poll_pair(P.xv[par] + size_t(kvh) * dim + e, tag_in, P.error);
-                if (L.v_bias != nullptr) v = __fadd_rn(v, L.v_bias[size_t(kvh) * dim + e]);
-                L.v_cache[row + e] = __float2half_rn(v);
+            for (int k = 0; k < 4; ++k) {
+                const uint32_t e = 2 * lane + 64 * k;
+                if (e < dim) own[e / 2] = __floats2half2_rn(__uint_as_float(w[k].x), __uint_as_float(w[k].y));  // exact: the values are f16 already
             }
         }
-        for (uint32_t g = 0; g < group; ++g) {
-            float v[VPL];
-#pragma unroll
-            for (int k = 0; k < VPL; ++k) {
-                const uint32_t e = NEOX ? lane + 32 * k : VPL * lane + k;
-                v[k] = qs[g * dim + e];
-                if (L.q_bias != nullptr) v[k] = __fadd_rn(v[k], L.q_bias[size_t(kvh * group + g) * dim + e]);
-            }
-            warp_head_norm_rope<VPL, NEOX>(v, L.q_norm, rope, P.eps, qs + g * dim);
-        }
-        // this lane's K row: the first task's rows were committed before the V slice's (one group may still be in flight)
-        if (i < P.sm.n_sslots) cp_async_wait<1>();
-        else cp_async_wait<0>();
+        TOK_STAMP(tr, 1);
+        cp_async_wait_all();
         __syncwarp();
+        TOK_STAMP(tr, 2);
+        float lanes[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) lanes[j] = 0.0f;
+#pragma unroll 2
+        for (uint32_t e = 0; e < dim; e += 16) {
+            const uint4 r0 = krow[e / 8], r1 = krow[e / 8 + 1];
+            const __half2* h0 = reinterpret_cast<const __half2*>(&r0);
+            const __half2* h1 = reinterpret_cast<const __half2*>(&r1);
+            float kf[16];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f0 = __half22float2(h0[j]), f1 = __half22float2(h1[j]);
+                kf[2 * j] = f0.x; kf[2 * j + 1] = f0.y; kf[8 + 2 * j] = f1.x; kf[8 + 2 * j + 1] = f1.y;
+            }
+            const float4* q4 = reinterpret_cast<const float4*>(qs + e);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float4 qq = q4[j];
+                lanes[4 * j + 0] = __fadd_rn(lanes[4 * j + 0], __fmul_rn(qq.x, kf[4 * j + 0]));
+                lanes[4 * j + 1] = __fadd_rn(lanes[4 * j + 1], __fmul_rn(qq.y, kf[4 * j + 1]));
+                lanes[4 * j + 2] = __fadd_rn(lanes[4 * j + 2], __fmul_rn(qq.z, kf[4 * j + 2]));
+                lanes[4 * j + 3] = __fadd_rn(lanes[4 * j + 3], __fmul_rn(qq.w, kf[4 * j + 3]));
+            }
+        }
+        float sum = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) sum = __fadd_rn(sum, lanes[j]);
+        const float sc = __fmul_rn(sum, P.scale);  // lanes past the last position hold whatever their stale rows gave: never published
+        TOK_STAMP(tr, 3);
+        // the maximum of these 32 scores is all a head's other tasks need of them
+        const uint2* maxima = P.sc[par] + size_t(h) * (P.max_context / 32);
+        const float cmx = warp_max(p < visible ? sc : -INFINITY);
+        if (lane == 0) st_pair(P.sc[par] + size_t(h) * (P.max_context / 32) + chunk, cmx, T + 1);
+        float mx = -INFINITY;
+#pragma unroll 1
+        for (uint32_t c = lane; c < chunks; c += 32) mx = fmaxf(mx, poll_word(maxima + c, T + 1, P.error));
+        mx = warp_max(mx);
+        double part = 0.0;
         if (p < visible) {
-            for (uint32_t g = 0; g < group; ++g) {
-                const float* q = qs + g * dim;
-                float lanes[16];
+            const float e = exact_expf_tab(__fsub_rn(sc, mx), exp_table);
+            st_pair(P.ex[par] + size_t(h) * P.max_context + p, e, T + 2);
+            part = double(e);
+        }
+        part = warp_sum_f64(part);
+        if (lane == 0) st_double(P.exs[par] + 2 * (size_t(h) * (P.max_context / 32) + chunk), part, T + 2);
+        TOK_STAMP(tr, 4);
+    }
+    // the cached K rows of this warp's first task of the next layer (same positions, the next layer's cache)
+    if (l + 1 < P.n_layers && cta + warp * nctas < tasks) {
+        __syncwarp();
+        scores_request(P, slot, tabs[l + 1], cta + warp * nctas, pos, dim);
+    }
+    cp_async_commit();
+}
+
+// Rows [first, last) of this CTA's V slice into the ring (16-byte pieces, every given thread a share).
+__device__ __noinline__ void values_request(const TokParams& P, unsigned char* ring, const TokLayer& L, uint32_t kvh, uint32_t slice, uint32_t dim,
+                                               uint32_t first, uint32_t last, uint32_t t0, uint32_t nthreads) {
+    const __half* vbase = L.v_cache + size_t(kvh) * P.max_context * dim + slice * kSliceW;
+    const uint32_t base = saddr(ring);  // only its shared-window address is used
+    for (uint32_t c = t0; c < (last - first) * 4; c += nthreads) {
+        const uint32_t row = first + (c >> 2), piece = c & 3;
+        const uint32_t at = ((row / kVChunkPos) % P.sm.ring_chunks) * kVChunkPos + row % kVChunkPos;
+        cp_async16(base + (at * kSliceW + piece * 8) * 2, vbase + size_t(row) * dim + piece * 8);
+    }
+}
+
+// Weighted sum: this CTA's (query head, 32 head dimensions). The sum over positions is one serial chain of f32 adds per
+// dimension (src/kernels_f32.cpp:265-273), so a head is split by dimensions, never by positions. Warp 0 carries the
+// chains (lane = dimension); the other 15 warps compute the products p[pos] * v[pos][c] of 128 positions at a time into
+// one of two tiles, a tile ahead of the chain. V comes through a ring of 512-position chunks requested when the previous
+// layer had left it (refilled behind the products for longer contexts); the token's own V row comes from the tagged v
+// vector. The 32 results are one quantisation block: the chain warp quantises and publishes it.
+__device__ __noinline__ void tok_attend(const TokParams& P, unsigned char* smem, double* red, const Roles&, uint32_t l, uint32_t base, uint32_t pos) {
+    smem = tok_smem;
+    red = g_red;
+    const Roles& R = g_roles;
+    if (R.wtask == kNone) return;
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t dim = P.q_rows / P.heads, slices = dim / kSliceW, group = P.heads / P.kv_heads;
+    const uint32_t h = R.wtask / slices, slice = R.wtask % slices, kvh = h / group, visible = pos + 1;
+    const uint32_t par = l & 1, T = base + 2 + l * kTagsPerLayer;
+    const TokLayer* tabs = reinterpret_cast<const TokLayer*>(smem + P.sm.tabs);
+    unsigned char* wbase = smem + P.sm.region + R.off_w;
+    float* ps = reinterpret_cast<float*>(wbase);
+    unsigned char* ring = wbase + P.max_context * 4;
+    const __half* vring = reinterpret_cast<const __half*>(ring);
+    __half* vown = reinterpret_cast<__half*>(ring + size_t(P.sm.ring_chunks) * kVChunkPos * kSliceW * 2);
+    float* prod = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(vown) + 128);
+    unsigned long long* tr = TOK_TRACE_PTR(P, l, 4);
+    (void)tr;
+    // Everybody meets here first: the warps that have nothing left to do for the previous layer's task wait, parked, for
+    // its chain warp and for this CTA's score tasks - sixteen warps polling L2 in a loop would slow exactly those down.
+    cta_sync();
+    TOK_STAMP(tr, 0);
+    if (warp == 1 || warp == 3) {
+        // TWO warps fetch the head's softmax: the tasks' partial sums for the denominator, then every exp - all words of a
+        // batch in every re-read, so the wait ends with the data in registers. p = e * float(1 / sum), scaled as it is stored.
+        const uint32_t chunks = (visible + 31) / 32;
+        double total = 0.0;
+        for (uint32_t c = lane; c < chunks; c += 32) total += words_double(poll_words2(P.exs[par] + 2 * (size_t(h) * (P.max_context / 32) + c), T + 2, P.error));
+        total = warp_sum_f64(total);
+        const float inv = float(1.0 / total);
+        const uint2* src = P.ex[par] + size_t(h) * P.max_context;
+        const uint32_t even = visible & ~1u;  // pairs; an odd last word alone
+        for (uint32_t base = (warp >> 1) * 8 * 64; base < even; base += 2 * 8 * 64) {  // eight pairs per lane and re-read: 512 positions per warp and pass
+            uint2 w[8];
+            poll_batch<8>(src, 64, base + 2 * lane, even, T + 2, P.error, w);
 #pragma unroll
-                for (int j = 0; j < 16; ++j) lanes[j] = 0.0f;
-#pragma unroll
-                for (uint32_t e = 0; e < dim; e += 16) {
-                    float kf[16];
-                    if (!cached) {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) kf[j] = knew[e + j];
-                    } else {
-                        const uint4 r0 = krow[e / 8], r1 = krow[e / 8 + 1];
-                        const __half2* h0 = reinterpret_cast<const __half2*>(&r0);
-                        const __half2* h1 = reinterpret_cast<const __half2*>(&r1);
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const float2 f0 = __half22float2(h0[j]), f1 = __half22float2(h1[j]);
-                            kf[2 * j] = f0.x; kf[2 * j + 1] = f0.y; kf[8 + 2 * j] = f1.x; kf[8 + 2 * j + 1] = f1.y;
-                        }
-                    }
-                    const float4* q4 = reinterpret_cast<const float4*>(q + e);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {  // dot_f32's 16 interleaved partial sums (src/kernels_f32.cpp:231-254)
-                        const float4 qq = q4[j];
-                        lanes[4 * j + 0] = __fadd_rn(lanes[4 * j + 0], __fmul_rn(qq.x, kf[4 * j + 0]));
-                        lanes[4 * j + 1] = __fadd_rn(lanes[4 * j + 1], __fmul_rn(qq.y, kf[4 * j + 1]));
-                        lanes[4 * j + 2] = __fadd_rn(lanes[4 * j + 2], __fmul_rn(qq.z, kf[4 * j + 2]));
-                        lanes[4 * j + 3] = __fadd_rn(lanes[4 * j + 3], __fmul_rn(qq.w, kf[4 * j + 3]));
-                    }
+            for (int k = 0; k < 8; ++k) {
+                const uint32_t e = base + 2 * lane + 64 * k;
+                if (e < even) {
+                    ps[e] = __fmul_rn(__uint_as_float(w[k].x), inv);
+                    ps[e + 1] = __fmul_rn(__uint_as_float(w[k].y), inv);
                 }
-                float sum = 0.0f;
-#pragma unroll
-                for (int j = 0; j < 16; ++j) sum = __fadd_rn(sum, lanes[j]);
-                st_pair(P.sc[par] + size_t(kvh * group + g) * P.max_context + p, __fmul_rn(sum, P.scale), tag_out);
             }
         }
+        if (warp == 1 && lane == 0 && (visible & 1u)) ps[visible - 1] = __fmul_rn(poll_word(src + visible - 1, T + 2, P.error), inv);
+    } else if (warp == 2) {  // the token's own V row, rounded as the cache rounds it
+        vown[lane] = __float2half_rn(poll_word(P.xv[par] + size_t(kvh) * dim + slice * kSliceW + lane, T, P.error));
     }
-}
-
-// Softmax + weighted sum: CTA `cta` < heads * slices takes (query head, slice of slice_w head dimensions). The sum over
-// positions is one serial chain of f32 adds per dimension (src/kernels_f32.cpp:265-273), so a head is split by
-// dimensions, never by positions. Warp 0 carries the chains (lane = dimension); the other 15 warps compute the products
-// p[pos] * v[pos][c] of 128 positions at a time into one of two tiles, a tile ahead of the chain. V comes through a
-// ring of three 512-position chunks requested at the start of the layer (refilled behind the products for longer
-// contexts); the token's own V row comes from the tagged v vector.
-__device__ __forceinline__ void values_request(const TokParams& P, unsigned char* smem, const TokLayer& L, uint32_t cta, uint32_t first, uint32_t last,
-                                               uint32_t tid0, uint32_t nthreads) {
-    const uint32_t dim = P.q_rows / P.heads, width = P.slice_w, slices = dim / width, group = P.heads / P.kv_heads;
-    const uint32_t h = cta / slices, slice = cta % slices, kvh = h / group;
-    const uint32_t ppr = width / 8;  // 16-byte pieces per position
-    const __half* vbase = L.v_cache + size_t(kvh) * P.max_context * dim + slice * width;
-    const uint32_t ring = saddr(smem + P.sm.vring);
-    constexpr uint32_t kRingPos = kVChunkPos * kVRingChunks;
-    for (uint32_t c = tid0; c < (last - first) * ppr; c += nthreads) {
-        const uint32_t row = first + c / ppr, piece = c % ppr;
-        cp_async16(ring + ((row % kRingPos) * width + piece * 8) * 2, vbase + size_t(row) * dim + piece * 8);
-    }
-}
-
-__device__ __noinline__ void tok_attend(const TokParams& P, unsigned char* smem, double* red, float* redf, const TokLayer& L, uint32_t par,
-                                        uint32_t tag_qkv, uint32_t tag_scores, uint32_t tag_out, uint32_t pos, uint32_t cta, unsigned long long* tr) {
-    const uint32_t dim = P.q_rows / P.heads, width = P.slice_w, slices = dim / width, group = P.heads / P.kv_heads;
-    if (cta >= P.heads * slices) return;
-    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint32_t h = cta / slices, slice = cta % slices, kvh = h / group, visible = pos + 1;
-    constexpr uint32_t kRingPos = kVChunkPos * kVRingChunks;
-    float* ps = reinterpret_cast<float*>(smem + P.sm.ps);
-    const __half* vring = reinterpret_cast<const __half*>(smem + P.sm.vring);
-    __half* vown = reinterpret_cast<__half*>(smem + P.sm.vown);
-    float* prod = reinterpret_cast<float*>(smem + P.sm.prod);
-    const uint2* scores = P.sc[par] + size_t(h) * P.max_context;
-
-    // softmax (src/kernels_f32.cpp:275-284): max, e = expf(s - max), f64 sum, p = e * float(1 / sum)
-    TOK_STAMP(tr, 0);
-    float mx = -INFINITY;
-    for (uint32_t p = tid; p < visible; p += kTokThreads) {
-        const float v = poll_pair(scores + p, tag_scores, P.error);
-        ps[p] = v;
-        mx = fmaxf(mx, v);
-    }
-    TOK_STAMP(tr, 1);
-    mx = warp_max(mx);
-    if (lane == 0) redf[warp] = mx;
-    cta_sync();
     TOK_STAMP(tr, 2);
-    mx = redf[0];
-#pragma unroll
-    for (uint32_t w = 1; w < kTokWarps; ++w) mx = fmaxf(mx, redf[w]);
-    double part = 0.0;
-    for (uint32_t p = tid; p < visible; p += kTokThreads) {
-        const float e = exact_expf(__fsub_rn(ps[p], mx));
-        ps[p] = e;
-        part += double(e);
-    }
-    part = warp_sum(part);
-    if (lane == 0) red[warp] = part;
-    if (tid < width) {  // the token's own V row, rounded as the cache rounds it
-        float v = poll_pair(P.xv[par] + size_t(kvh) * dim + slice * width + tid, tag_qkv, P.error);
-        if (L.v_bias != nullptr) v = __fadd_rn(v, L.v_bias[size_t(kvh) * dim + slice * width + tid]);
-        vown[tid] = __float2half_rn(v);
-    }
+    cp_async_wait_all();  // this thread's share of the first V chunks
     TOK_STAMP(tr, 3);
     cta_sync();
     TOK_STAMP(tr, 4);
-    double total = 0.0;
-#pragma unroll
-    for (uint32_t w = 0; w < kTokWarps; ++w) total += red[w];
-    const float inv = float(1.0 / total);
-    for (uint32_t p = tid; p < visible; p += kTokThreads) ps[p] = __fmul_rn(ps[p], inv);
-    cp_async_wait<0>();  // this thread's share of the first V chunks
-    TOK_STAMP(tr, 5);
-    cta_sync();
-    TOK_STAMP(tr, 6);
-
+#ifdef BK_TOK_TRACE
+    if (tr != nullptr) tr[9] = tok_now();
+#endif
     const uint32_t nsub = (visible + kSub - 1) / kSub;
-    const bool refills = pos > kRingPos;  // positions beyond what the ring held at the start
-    if (warp == 0) {
-        float acc = 0.0f;
-        for (uint32_t s = 0; s < nsub; ++s) {
-            const uint32_t b = s & 1, rows = min(kSub, visible - s * kSub);
-            bar_sync(2 + b, kTokThreads);  // tile b holds the products of sub-chunk s
-            if (lane < width) {
-                const float* mine = prod + (size_t(b) * width + lane) * kSubStride;
-                uint32_t j = 0;
-#pragma unroll 4
-                for (; j + 4 <= rows; j += 4) {
-                    const float4 q = *reinterpret_cast<const float4*>(mine + j);
-                    acc = __fadd_rn(acc, q.x); acc = __fadd_rn(acc, q.y); acc = __fadd_rn(acc, q.z); acc = __fadd_rn(acc, q.w);
-                }
-                for (; j < rows; ++j) acc = __fadd_rn(acc, mine[j]);
-            }
-            if (s + 2 < nsub) bar_arrive(4 + b, kTokThreads);  // tile b may be rewritten
+    const uint32_t ring_pos = P.sm.ring_chunks * kVChunkPos;
+    const bool refills = pos > ring_pos;  // positions beyond what the ring held at the start
+    // Products and chain ALTERNATE: all sixteen warps fill the tile with the products of 256 positions, then warp 0 alone adds
+    // them while the others are parked at the barrier. Overlapping the two (products of the next tile during the chain)
+    // measured slower: the chain then ran at 15-21 cycles per add instead of 7.
+    const uint32_t c8 = lane & 7, r4 = lane >> 3;  // a lane's four columns 4 * c8 .. 4 * c8 + 3, its position within a group of four
+    float acc = 0.0f;
+#ifdef BK_TOK_TRACE
+    if (tr != nullptr) tr[8] = 0;
+#endif
+    for (uint32_t s = 0; s < nsub; ++s) {
+        const uint32_t first = s * kSub, rows = min(kSub, visible - first);
+        if (refills && first != 0 && first % kVChunkPos == 0) {
+            const uint32_t c = first / kVChunkPos;  // entering chunk c: chunk c - 1 is consumed (the barrier after its last chain)
+            const uint32_t from = (c - 1 + P.sm.ring_chunks) * kVChunkPos;
+            if (from < pos) values_request(P, ring, tabs[l], kvh, slice, dim, from, min(pos, from + kVChunkPos), tid, kTokThreads);
+            cp_async_commit();
+            asm volatile("cp.async.wait_group 1;" ::: "memory");  // everything but the chunk just requested: chunk c has landed
+            cta_sync();
         }
-        if (lane < width) st_pair(P.att[par] + size_t(h) * dim + slice * width + lane, acc, tag_out);
-        TOK_STAMP(tr, 7);
-    } else {
-        const uint32_t ptid = tid - 32, nprod = kTokThreads - 32;
-        for (uint32_t s = 0; s < nsub; ++s) {
-            const uint32_t b = s & 1, base = s * kSub, rows = min(kSub, visible - base);
-            if (refills && base != 0 && base % kVChunkPos == 0) {
-                const uint32_t c = base / kVChunkPos;  // entering chunk c: chunk c - 1 is consumed once every producer is here
-                bar_sync(6, nprod);
-                const uint32_t first = (c + 2) * kVChunkPos, last = min(pos, first + kVChunkPos);
-                if (first < pos) values_request(P, smem, L, cta, first, last, ptid, nprod);
-                cp_async_commit();
-                cp_async_wait<1>();  // everything but the chunk just requested: chunk c has landed
-                bar_sync(6, nprod);
-            }
-            if (s >= 2) bar_sync(4 + b, kTokThreads);  // the chain is done with tile b
-            float* tile = prod + size_t(b) * width * kSubStride;
-            for (uint32_t e = ptid; e < rows * width; e += nprod) {
-                const uint32_t r = e / width, col = e % width, p = base + r;
-                const __half vv = p == pos ? vown[col] : vring[(p % kRingPos) * width + col];
-                tile[col * kSubStride + r] = __fmul_rn(ps[p], __half2float(vv));
-            }
-            bar_arrive(2 + b, kTokThreads);
+        // The tile is [position][32 columns]. A lane computes four columns of one position - one 8-byte load of V, one of the
+        // probability, one 16-byte store - so a product costs 2.5 instructions (written column-major, one product per
+        // instruction, the products took three times as long as the chain they feed). The chain reads one float per add.
+        const uint32_t at0 = ((first / kVChunkPos) % P.sm.ring_chunks) * kVChunkPos + first % kVChunkPos;  // a tile lies inside one chunk
+#pragma unroll 2
+        for (uint32_t r = warp * 4 + r4; r < rows; r += 4 * kTokWarps) {
+            const uint32_t p = first + r;
+            const uint2 raw = p == pos ? *reinterpret_cast<const uint2*>(vown + 4 * c8) : *reinterpret_cast<const uint2*>(vring + (at0 + r) * kSliceW + 4 * c8);
+            const float2 v01 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x)), v23 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+            const float pr = ps[p];
+            *reinterpret_cast<float4*>(prod + r * kSliceW + 4 * c8) = make_float4(__fmul_rn(pr, v01.x), __fmul_rn(pr, v01.y), __fmul_rn(pr, v23.x), __fmul_rn(pr, v23.y));
         }
+        cta_sync();
+#ifdef BK_TOK_TRACE
+        const long long c0 = clock64();
+#endif
+        if (warp == 0) {
+            const float* col = prod + lane;
+            uint32_t j = 0;
+            // 16 adds per pass with their loads on top
+#pragma unroll 1
+            for (; j + 16 <= rows; j += 16) {
+                float t[16];
+#pragma unroll
+                for (int k = 0; k < 16; ++k) t[k] = col[(j + k) * kSliceW];
+#pragma unroll
+                for (int k = 0; k < 16; ++k) acc = __fadd_rn(acc, t[k]);
+            }
+            for (; j < rows; ++j) acc = __fadd_rn(acc, col[j * kSliceW]);
+        }
+#ifdef BK_TOK_TRACE
+        if (tr != nullptr) tr[8] += (unsigned long long)(clock64() - c0);  // cycles in the chains alone
+#endif
+        if (s + 1 < nsub) cta_sync();  // the tile is free for the next 256 positions
     }
+    TOK_STAMP(tr, 5);
+    // the ring is free: the next layer's V slice (the same positions of its cache) - by the warps that have nothing else to do
+    if (warp != 0 && l + 1 < P.n_layers) values_request(P, ring, tabs[l + 1], kvh, slice, dim, 0, min(pos, ring_pos), tid - 32, kTokThreads - 32);
+    if (warp == 0) publish_block_q8(P.aq[par] + size_t(R.wtask) * 10, acc, T + 3);
+    TOK_STAMP(tr, 6);
+    cp_async_commit();
 }
 
 // ---- output head -------------------------------------------------------------------------------------------------
@@ -708,18 +928,29 @@ __device__ __forceinline__ void head_request(const TokParams& P, unsigned char* 
     const uint32_t chunk = warp + i * kTokWarps;  // the warp's i-th chunk
     if (chunk >= w.chunks) return;
     const uint32_t hr = P.sm.head_rows, first = chunk * hr, nrows = min(hr, w.rows - first);
-    unsigned char* slot = smem + P.sm.ring + size_t(warp * 2 + (i & 1)) * P.sm.ring_slot_bytes;
+    unsigned char* slot = smem + P.sm.region + size_t(warp * 2 + (i & 1)) * P.sm.ring_slot_bytes;
     mbar_expect_tx(bar, nrows * w.units * 18);
     bulk_g2s(slot, P.head_nib + size_t(w.lo + first) * w.units * 16, nrows * w.units * 16, bar);
     bulk_g2s(slot + size_t(hr) * w.units * 16, P.head_scl + size_t(w.lo + first) * w.units, nrows * w.units * 2, bar);
 }
 
-__device__ __noinline__ void tok_head(const TokParams& P, unsigned char* smem, double* red, uint64_t (*hbar)[2], float* sv, int* si, const uint2* x,
-                                      uint32_t tag_x, uint32_t tag_part, uint32_t pos, uint32_t cta, uint32_t nctas) {
-    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+__device__ __noinline__ void tok_head(const TokParams& P, unsigned char* smem, double* red, uint64_t (*hbar)[2], float* sv, int* si, uint32_t base,
+                                      uint32_t pos, uint32_t cta, uint32_t nctas) {
+    smem = tok_smem;
+    red = g_red;
+    hbar = g_hbar;
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, L = P.n_layers;
     const HeadWalk w = head_walk(P, cta, nctas);
     const uint32_t units = w.units, tstride = units + 4, hr = P.sm.head_rows;
-    tok_prologue(P, smem, red, x, tag_x, P.hidden, P.output_norm);
+    const uint32_t tag_part = base + 2 + L * kTagsPerLayer;
+    // every buffer of the layers is free now: the head's first chunks stream while the last residual values arrive
+    cta_sync();
+    if (lane == 0) {
+        fence_async_proxy();
+        head_request(P, smem, w, warp, 0, &hbar[warp][0]);
+        head_request(P, smem, w, warp, 1, &hbar[warp][1]);
+    }
+    prologue_f32(P, smem, red, P.ha[(L - 1) & 1], P.hsa[(L - 1) & 1], base + 2 + (L - 1) * kTagsPerLayer + 6, P.hidden, P.output_norm);
     const uint4* xlo = reinterpret_cast<const uint4*>(smem + P.sm.xlo);
     const uint4* xhi = reinterpret_cast<const uint4*>(smem + P.sm.xhi);
     const float* xd = reinterpret_cast<const float*>(smem + P.sm.xd);
@@ -731,7 +962,7 @@ __device__ __noinline__ void tok_head(const TokParams& P, unsigned char* smem, d
         const uint32_t chunk = warp + i * kTokWarps;
         if (chunk >= w.chunks) break;
         const uint32_t first = chunk * hr, nrows = min(hr, w.rows - first);
-        const unsigned char* slot = smem + P.sm.ring + size_t(warp * 2 + (i & 1)) * P.sm.ring_slot_bytes;
+        const unsigned char* slot = smem + P.sm.region + size_t(warp * 2 + (i & 1)) * P.sm.ring_slot_bytes;
         const __half* ws = reinterpret_cast<const __half*>(slot + size_t(hr) * units * 16);
         mbar_wait(&hbar[warp][i & 1], (i >> 1) & 1, P.error);
         for (uint32_t u = lane; u < units; u += 32) {
@@ -774,10 +1005,13 @@ __device__ __noinline__ void tok_head(const TokParams& P, unsigned char* smem, d
         if (cta == 0) {
             float v = -INFINITY;
             int32_t idx = 0x7fffffff;
-            for (uint32_t c = lane; c < nctas; c += 32) {
-                const float cv = poll_pair(P.part + 2 * c, tag_part, P.error);
-                const int32_t ci = __float_as_int(poll_pair(P.part + 2 * c + 1, tag_part, P.error));
-                tok_better(v, idx, cv, ci);
+            for (uint32_t c0 = 0; c0 < nctas; c0 += 8 * 32) {  // up to eight candidates per lane in flight
+                uint2 w2[8];
+                poll_batch<8>(P.part, 64, c0 * 2 + 2 * lane, 2 * nctas, tag_part, P.error, w2);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    if (c0 + lane + 32 * k < nctas) tok_better(v, idx, __uint_as_float(w2[k].x), int32_t(w2[k].y));
+                }
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) tok_better(v, idx, __shfl_xor_sync(0xffffffffu, v, o), __shfl_xor_sync(0xffffffffu, idx, o));
@@ -786,7 +1020,7 @@ __device__ __noinline__ void tok_head(const TokParams& P, unsigned char* smem, d
                 if (first_logit != first_logit || uint32_t(idx) >= P.vocab) idx = 0;
                 *P.chosen = idx;
                 if (P.advance) {
-                    *P.token_slot = idx;
+                    *P.token = idx;
                     *P.position = pos + 1;
                     if (P.history != nullptr) {
                         const uint32_t n = *P.history_len;
@@ -803,14 +1037,14 @@ __device__ __noinline__ void tok_head(const TokParams& P, unsigned char* smem, d
 // ---- the kernel ----------------------------------------------------------------------------------------------------
 template <int VPL, bool NEOX>
 __global__ void __launch_bounds__(kTokThreads, 1) token_kernel(const __grid_constant__ TokParams P) {
-    extern __shared__ __align__(128) unsigned char smem[];
-    __shared__ double red[kTokWarps];
-    __shared__ float redf[kTokWarps];
+    unsigned char* smem = tok_smem;
+    double* red = g_red;
     __shared__ float sv[kTokWarps];
     __shared__ int si[kTokWarps];
-    __shared__ __align__(8) uint64_t bars[4];
-    __shared__ __align__(8) uint64_t hbar[kTokWarps][2];
-    __shared__ Shape shapes[4];
+    uint64_t* bars = g_bars;
+    uint64_t (*hbar)[2] = g_hbar;
+    uint64_t* exp_table = g_exp_table;
+    Roles& R = g_roles;
     constexpr uint32_t dim = VPL * 32;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, cta = blockIdx.x, nctas = gridDim.x;
     const uint32_t L = P.n_layers;
@@ -824,47 +1058,31 @@ __global__ void __launch_bounds__(kTokThreads, 1) token_kernel(const __grid_cons
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_proxy();
-        // this CTA's rows of the four multiplies: q|k|v as one row space, o, gate/up pairs, down
-        const uint32_t bounds[4] = {0, P.q_rows, P.q_rows + P.kv_rows, P.q_rows + 2 * P.kv_rows};
-        Shape s{};
-        {
-            const uint32_t lo = part_lo(bounds[3], cta, nctas), hi = part_lo(bounds[3], cta + 1, nctas);
-            for (uint32_t m = 0; m < 3; ++m) {
-                const uint32_t a = max(lo, bounds[m]), e = min(hi, bounds[m + 1]);
-                if (a < e) {
-                    s.seg_rows[s.nseg] = e - a;
-                    s.seg_first[s.nseg] = a - bounds[m];
-                    s.seg_mat[s.nseg] = m;
-                    ++s.nseg;
-                    s.rows += e - a;
-                }
-            }
-            shapes[0] = s;
+        Roles r;
+        r.unit = cta < P.n_units ? cta : kNone;
+        const uint32_t hb = P.hidden / 32, fb = P.ffn / 32, slices = dim / kSliceW;
+        r.bd_blk0 = r.bd_blks = r.c_blk0 = r.c_blks = 0;
+        if (cta >= P.bd_first && cta < P.bd_first + P.bd_ctas) {
+            r.bd_blk0 = part_lo(hb, cta - P.bd_first, P.bd_ctas);
+            r.bd_blks = part_lo(hb, cta - P.bd_first + 1, P.bd_ctas) - r.bd_blk0;
         }
-        {
-            const uint32_t lo = part_lo(P.hidden, cta, nctas), hi = part_lo(P.hidden, cta + 1, nctas);
-            s = Shape{};
-            s.rows = hi - lo;
-            s.nseg = s.rows != 0 ? 1 : 0;
-            s.seg_rows[0] = hi - lo;
-            s.seg_first[0] = lo;
-            s.seg_mat[0] = 3;
-            shapes[1] = s;
-            s.seg_mat[0] = 6;
-            shapes[3] = s;
+        if (cta >= P.c_first && cta < P.c_first + P.c_ctas) {
+            r.c_blk0 = part_lo(fb, cta - P.c_first, P.c_ctas);
+            r.c_blks = part_lo(fb, cta - P.c_first + 1, P.c_ctas) - r.c_blk0;
         }
-        {
-            const uint32_t lo = part_lo(P.ffn, cta, nctas), hi = part_lo(P.ffn, cta + 1, nctas);
-            s = Shape{};
-            s.rows = 2 * (hi - lo);
-            s.nseg = s.rows != 0 ? 2 : 0;
-            s.seg_rows[0] = s.seg_rows[1] = hi - lo;
-            s.seg_first[0] = s.seg_first[1] = lo;
-            s.seg_mat[0] = 4;
-            s.seg_mat[1] = 5;
-            shapes[2] = s;
-        }
+        r.wtask = (cta >= P.w_first && cta - P.w_first < P.heads * slices) ? cta - P.w_first : kNone;
+        uint32_t off = 0;
+        r.off_a = off; if (r.unit != kNone) off += P.sm.size_a;
+        r.off_b = off; if (r.bd_blks != 0) off += P.sm.size_b;
+        r.off_d = off; if (r.bd_blks != 0) off += P.sm.size_d;
+        r.off_c = off; if (r.c_blks != 0) off += P.sm.size_c;
+        r.off_w = off;
+        r.op_head = 0;
+        fill_ops(P, r);
+        R = r;
     }
+    if (tid < 32) exp_table[tid] = exp2_table_device()[tid];
+    if (tid >= 64 && tid < 64 + dim) reinterpret_cast<float*>(smem + P.sm.hv)[2 * dim + tid - 64] = __ldg(P.rope + size_t(*P.position) * dim + tid - 64);
     {   // every layer's table into shared memory: the pointers are read on the way to each request
         const uint4* src = reinterpret_cast<const uint4*>(P.layers);
         uint4* dst = reinterpret_cast<uint4*>(smem + P.sm.tabs);
@@ -876,18 +1094,28 @@ __global__ void __launch_bounds__(kTokThreads, 1) token_kernel(const __grid_cons
     if (token >= P.vocab) token = 0;  // ids from the host are checked there, ids chosen on the device where they are chosen: the last guard
     __syncthreads();
     const TokLayer* tabs = reinterpret_cast<const TokLayer*>(smem + P.sm.tabs);
-    unsigned char* wbuf[4] = {smem + P.sm.w_qkv, smem + P.sm.w_o, smem + P.sm.w_gu, smem + P.sm.w_down};
-    const uint32_t wcols[4] = {P.hidden, P.q_rows, P.hidden, P.ffn};
     if (tid == kIssuer) {
-        for (int k = 0; k < 4; ++k) tok_request(shapes[k], tabs[0], wbuf[k], wcols[k], &bars[k]);
+        for (uint32_t k = 0; k < 4; ++k) tok_request(P, smem, R, bars, k, 0);
     }
-    unsigned long long* trace = (P.trace != nullptr && cta == 0 && tid == 0) ? P.trace : nullptr;
+    // what does not depend on this token: the cached K rows of this CTA's first score tasks, the V slice of its weighted sum
+    if (warp < P.sm.n_sslots && cta + warp * nctas < P.heads * ((pos + 32) / 32)) {
+        scores_request(P, smem + P.sm.sslot + size_t(warp) * P.sm.sslot_bytes, tabs[0], cta + warp * nctas, pos, dim);
+    }
+    if (R.wtask != kNone) {
+        const uint32_t slices = dim / kSliceW, h = R.wtask / slices;
+        values_request(P, smem + P.sm.region + R.off_w + P.max_context * 4, tabs[0], h / (P.heads / P.kv_heads), R.wtask % slices, dim, 0,
+                       min(pos, P.sm.ring_chunks * kVChunkPos), tid, kTokThreads);
+    }
+    cp_async_commit();
+    // development aid: thread 0 of CTAs 0, 40, 100 and the last one stamp the end of every phase (ns), a section each
+    const uint32_t traced = cta == 0 ? 0 : cta == 40 ? 1 : cta == 100 ? 2 : cta == nctas - 1 ? 3 : kNone;
+    unsigned long long* trace = (P.trace != nullptr && traced != kNone && tid == 0) ? P.trace + traced * (2 + L * 6) : nullptr;
     if (trace) trace[0] = tok_now();
 
-    // the token's embedding row: each owner of hidden rows dequantises its own values (embedding_row, src/model.cpp:27-70)
+    // the token's embedding row: the owners of the hidden blocks dequantise their values (embedding_row, src/model.cpp:27-70)
     float hres = 0.0f;
-    if (tid < shapes[1].rows) {
-        const uint32_t r = shapes[1].seg_first[0] + tid;
+    if (tid < 32 * R.bd_blks) {
+        const uint32_t r = R.bd_blk0 * 32 + tid;
         if (P.hidden_in != nullptr) {
             hres = P.hidden_in[r];
         } else {
@@ -897,86 +1125,31 @@ __global__ void __launch_bounds__(kTokThreads, 1) token_kernel(const __grid_cons
             const int q = int(wi < 16 ? (byte & 0xFu) : (byte >> 4));
             hres = __fmul_rn(float(q - 8), __half2float(P.embd_scl[unit]));
         }
-        st_pair(P.hid_a[1] + r, hres, base + 1);
+        st_pair(P.ha[1] + r, hres, base + 1);
+        const double sq = warp_sum_f64(double(__fmul_rn(hres, hres)));
+        if (lane == 0) st_double(P.hsa[1] + 2 * (R.bd_blk0 + warp), sq, base + 1);
     }
 
-    const uint32_t slices = dim / P.slice_w, wtasks = P.heads * slices, stasks = score_tasks(P, pos);
-    constexpr uint32_t kRingPos = kVChunkPos * kVRingChunks;
     for (uint32_t l = 0; l < L; ++l) {
-        const TokLayer& Ly = tabs[l];
-        const uint32_t par = l & 1, T = base + 2 + l * kTagsPerLayer;
         const bool more = l + 1 < L;
-        // what does not depend on this token: the cached K rows of this CTA's score tasks, the V slice of its weighted sum
-        if (warp < P.sm.n_sslots && cta + warp * nctas < stasks) {
-            scores_request<VPL>(P, smem + P.sm.sslot + size_t(warp) * P.sm.sslot_bytes, Ly, cta + warp * nctas, pos);
-        }
-        cp_async_commit();
-        if (cta < wtasks) values_request(P, smem, Ly, cta, 0, min(pos, kRingPos), tid, kTokThreads);
-        cp_async_commit();
-
-        MulArgs a{};
-        a.act = P.act;
-        unsigned long long* btr = (trace != nullptr && l == 5) ? trace + 2 + L * 6 : nullptr;  // 4 x 10 stamps inside layer 5's multiplies
-        a.tr = btr;
-        // q/k/v
-        a.x = P.hid_a[(l + 1) & 1]; a.tag_x = l == 0 ? base + 1 : T - kTagsPerLayer + 5; a.tag_out = T; a.cols = P.hidden; a.norm = Ly.attn_norm;
-        a.w = wbuf[0]; a.bar = &bars[0]; a.parity = par; a.kind = 0; a.plain = nullptr;
-        for (uint32_t s = 0; s < shapes[0].nseg; ++s) a.out[s] = shapes[0].seg_mat[s] == 0 ? P.xq[par] : shapes[0].seg_mat[s] == 1 ? P.xk[par] : P.xv[par];
-        hres = tok_multiply(P, smem, red, shapes[0], a, hres);
-        if (tid == kIssuer && more) {
-            fence_async_proxy();
-            tok_request(shapes[0], tabs[l + 1], wbuf[0], wcols[0], &bars[0]);
-        }
+        hres = tok_op(P, smem, red, R, bars, exp_table, 0, l, base, pos, NEOX, hres);
+        if (tid == kIssuer && more) tok_request(P, smem, R, bars, 0, l + 1);
         if (trace) trace[1 + l * 6 + 0] = tok_now();
-
-        tok_scores<VPL, NEOX>(P, smem, Ly, par, T, T + 1, pos, cta, nctas);
+        tok_scores<VPL>(P, smem, exp_table, l, base, pos, cta, nctas);
         if (trace) trace[1 + l * 6 + 1] = tok_now();
-        tok_attend(P, smem, red, redf, Ly, par, T, T + 1, T + 2, pos, cta, btr ? btr + 40 : nullptr);
+        tok_attend(P, smem, red, R, l, base, pos);
         if (trace) trace[1 + l * 6 + 2] = tok_now();
-
-        // output projection + residual
-        a.x = P.att[par]; a.tag_x = T + 2; a.tag_out = T + 3; a.cols = P.q_rows; a.norm = Ly.attn_sub_norm;
-        a.w = wbuf[1]; a.bar = &bars[1]; a.kind = 1; a.out[0] = P.hid_b[par]; a.tr = btr ? btr + 10 : nullptr;
-        hres = tok_multiply(P, smem, red, shapes[1], a, hres);
-        if (tid == kIssuer && more) {
-            fence_async_proxy();
-            tok_request(shapes[1], tabs[l + 1], wbuf[1], wcols[1], &bars[1]);
-        }
+        hres = tok_op(P, smem, red, R, bars, exp_table, 1, l, base, pos, NEOX, hres);
+        if (tid == kIssuer && more) tok_request(P, smem, R, bars, 1, l + 1);
         if (trace) trace[1 + l * 6 + 3] = tok_now();
-
-        // gate/up + activation
-        a.x = P.hid_b[par]; a.tag_x = T + 3; a.tag_out = T + 4; a.cols = P.hidden; a.norm = Ly.ffn_norm;
-        a.w = wbuf[2]; a.bar = &bars[2]; a.kind = 2; a.out[0] = P.gated[par]; a.tr = btr ? btr + 20 : nullptr;
-        hres = tok_multiply(P, smem, red, shapes[2], a, hres);
-        if (more) {
-            if (tid == kIssuer) {
-                fence_async_proxy();
-                tok_request(shapes[2], tabs[l + 1], wbuf[2], wcols[2], &bars[2]);
-            }
-        } else {
-            // last layer: everything but the down projection's buffer is free - the head's first chunks start streaming
-            // (the barrier: a CTA without gate/up rows came here without one, and its chain warp may still be in the weighted sum)
-            cta_sync();
-            if (lane == 0) {
-                const HeadWalk w = head_walk(P, cta, nctas);
-                fence_async_proxy();
-                head_request(P, smem, w, warp, 0, &hbar[warp][0]);
-                head_request(P, smem, w, warp, 1, &hbar[warp][1]);
-            }
-        }
+        hres = tok_op(P, smem, red, R, bars, exp_table, 2, l, base, pos, NEOX, hres);
+        if (tid == kIssuer && more) tok_request(P, smem, R, bars, 2, l + 1);
         if (trace) trace[1 + l * 6 + 4] = tok_now();
-
-        // down projection + residual
-        a.x = P.gated[par]; a.tag_x = T + 4; a.tag_out = T + 5; a.cols = P.ffn; a.norm = Ly.ffn_sub_norm;
-        a.w = wbuf[3]; a.bar = &bars[3]; a.kind = 1; a.out[0] = P.hid_a[par]; a.plain = more ? nullptr : P.hidden_out; a.tr = btr ? btr + 30 : nullptr;
-        hres = tok_multiply(P, smem, red, shapes[3], a, hres);
-        if (tid == kIssuer && more) {
-            fence_async_proxy();
-            tok_request(shapes[3], tabs[l + 1], wbuf[3], wcols[3], &bars[3]);
-        }
+        hres = tok_op(P, smem, red, R, bars, exp_table, 3, l, base, pos, NEOX, hres);
+        if (tid == kIssuer && more) tok_request(P, smem, R, bars, 3, l + 1);
         if (trace) trace[1 + l * 6 + 5] = tok_now();
     }
-    tok_head(P, smem, red, hbar, sv, si, P.hid_a[(L - 1) & 1], base + 2 + (L - 1) * kTagsPerLayer + 5, base + 2 + L * kTagsPerLayer, pos, cta, nctas);
+    tok_head(P, smem, red, hbar, sv, si, base, pos, cta, nctas);
     if (trace) trace[1 + L * 6] = tok_now();
 }
 
@@ -1021,30 +1194,31 @@ bool TokenPlan::build(const std::vector<StepLayerArgs>& layers, const StepShared
                 return false;
             }
         }
+        if (L.attn_sub_norm != nullptr || L.ffn_sub_norm != nullptr) {
+            why_not = "sub-norms ahead of the output or down projection";
+            return false;
+        }
     }
     if (ends.head.type != T_Q4_0) {
         why_not = "the output head is not Q4_0";
         return false;
     }
-    const uint32_t q_dim = sh.heads * sh.dim, kv_dim = sh.kv_heads * sh.dim, group = sh.heads / sh.kv_heads;
-    for (uint32_t n : {sh.hidden_size, q_dim, sh.ffn_size}) {
-        if (n % 256 != 0 || n > 4096) {
-            why_not = "a row length is not a multiple of 256 up to 4096";
-            return false;
-        }
+    const uint32_t dim = sh.dim, q_dim = sh.heads * dim, kv_dim = sh.kv_heads * dim, group = sh.heads / sh.kv_heads;
+    if (sh.hidden_size % 256 != 0 || sh.hidden_size > 4096 || q_dim % 256 != 0 || sh.ffn_size % 256 != 0) {
+        why_not = "a row length is not a multiple of 256, or the hidden size exceeds 4096";
+        return false;
     }
-    if ((sh.dim != 64 && sh.dim != 128) || group > 8) {
+    if ((dim != 64 && dim != 128) || group > 8) {
         why_not = "head size is not 64 or 128, or more than 8 query heads per K/V head";
         return false;
     }
-    uint32_t slice_w = 16;
-    if (sh.heads * (sh.dim / slice_w) > sms) slice_w = 32;
-    if (sh.heads * (sh.dim / slice_w) > sms) {
-        why_not = "more (head, 32-column slice) tasks than SMs";
+    if (sh.max_context % 32 != 0) {
+        why_not = "the context length is not a multiple of 32";
         return false;
     }
-    if (ends.vocab < sms || sh.hidden_size < 32) {
-        why_not = "fewer vocabulary rows than SMs";
+    const uint32_t n_units = sh.heads + 2 * sh.kv_heads, wtasks = sh.heads * (dim / kSliceW);
+    if (n_units > sms || wtasks > sms || ends.vocab < sms) {
+        why_not = "more heads (or fewer vocabulary rows) than SMs";
         return false;
     }
     int dev = 0, limit = 0, coop = 0;
@@ -1056,42 +1230,58 @@ bool TokenPlan::build(const std::vector<StepLayerArgs>& layers, const StepShared
         return false;
     }
 
-    // shared-memory layout: what the head's ring may overwrite comes last
+    // Who does what. q/k/v: one head unit per CTA from CTA 0. Output and down projection: the hidden blocks over the CTAs
+    // after those (or over all of them). Gate/up: the feed-forward blocks from CTA 0. Attention: the last CTAs.
     const uint32_t L = uint32_t(layers.size());
-    const uint32_t widest = std::max(std::max(sh.hidden_size, q_dim), sh.ffn_size);
-    const uint32_t r_qkv = ceil_div(q_dim + 2 * kv_dim, sms), r_h = ceil_div(sh.hidden_size, sms), r_gu = 2 * ceil_div(sh.ffn_size, sms);
     const uint32_t hu = sh.hidden_size / 32, qu = q_dim / 32, fu = sh.ffn_size / 32;
+    TokParams base{};
+    base.n_units = n_units;
+    base.bd_ctas = std::min(hu, sms - std::min(n_units, sms - 1));
+    base.bd_first = n_units + base.bd_ctas <= sms ? n_units : sms - base.bd_ctas;
+    base.c_ctas = std::min(fu, sms);
+    base.c_first = 0;
+    base.w_first = sms - wtasks;
+    const uint32_t bd_blks = ceil_div(hu, base.bd_ctas), c_blks = ceil_div(fu, base.c_ctas);
+    const uint32_t size_a = align_up(dim * hu * 18, 128), size_b = align_up(32 * bd_blks * qu * 18, 128), size_d = align_up(32 * bd_blks * fu * 18, 128),
+                   size_c = align_up(64 * c_blks * hu * 18, 128);
     TokSmem best{};
     bool fits = false;
-    for (uint32_t hr : {8u, 4u, 2u, 1u}) {
-        for (uint32_t nss : {4u, 2u, 1u}) {
+    const uint32_t tries[][2] = {{4, 3}, {4, 2}, {3, 2}, {2, 3}, {2, 2}, {1, 2}};  // score slots, V ring chunks
+    for (const auto& t : tries) {
+        for (uint32_t hr : {8u, 4u, 2u, 1u}) {
             if (fits) break;
             TokSmem m{};
+            m.n_sslots = t[0];
+            m.ring_chunks = t[1];
+            m.head_rows = hr;
+            m.size_a = size_a; m.size_b = size_b; m.size_d = size_d; m.size_c = size_c;
+            const uint32_t size_w = align_up(sh.max_context * 4 + m.ring_chunks * kVChunkPos * kSliceW * 2 + 128 + kSliceW * kSub * 4, 128);
+            const uint32_t widest = std::max(std::max(sh.hidden_size, q_dim), sh.ffn_size);
             uint32_t off = 0;
             m.tabs = off; off = align_up(off + L * uint32_t(sizeof(TokLayer)), 128);
             m.xlo = off; off += widest / 32 * 16;
             m.xhi = off; off += widest / 32 * 16;
             m.xd = off; off += widest / 32 * 4;
             m.xs = off; off = align_up(off + widest / 32 * 4, 128);
-            const uint32_t op_tile = std::max(std::max(r_qkv * (hu + 4), r_h * (qu + 4)), std::max(r_gu * (hu + 4), r_h * (fu + 4)));
+            const uint32_t op_tile = std::max(std::max(dim * (hu + 4), 32 * bd_blks * (qu + 4)), std::max(64 * c_blks * (hu + 4), 32 * bd_blks * (fu + 4)));
             m.tile = off; off = align_up(off + std::max(op_tile, kTokWarps * hr * (hu + 4)) * 4, 128);
-            m.w_down = off; off = align_up(off + r_h * fu * 18, 128);
-            const uint32_t alias = off;
-            m.w_qkv = off; off = align_up(off + r_qkv * hu * 18, 128);
-            m.w_o = off; off = align_up(off + r_h * qu * 18, 128);
-            m.w_gu = off; off = align_up(off + r_gu * hu * 18, 128);
-            m.n_sslots = nss;
-            m.sslot_bytes = align_up((group + 1) * sh.dim * 4 + 32 * (sh.dim * 2 + 16), 128);
-            m.sslot = off; off += nss * m.sslot_bytes;
-            m.ps = off; off = align_up(off + sh.max_context * 4, 128);
-            m.vring = off; off = align_up(off + kVChunkPos * kVRingChunks * slice_w * 2, 128);
-            m.vown = off; off += 128;
-            m.prod = off; off = align_up(off + 2 * slice_w * kSubStride * 4, 128);
-            m.head_rows = hr;
+            m.hv = off; off += 3 * dim * 4;
+            uint32_t region = 0;  // the largest sum of role buffers over the CTAs
+            for (uint32_t cta = 0; cta < sms; ++cta) {
+                uint32_t need = 0;
+                if (cta < n_units) need += size_a;
+                if (cta >= base.bd_first && cta < base.bd_first + base.bd_ctas) need += size_b + size_d;
+                if (cta >= base.c_first && cta < base.c_first + base.c_ctas) need += size_c;
+                if (cta >= base.w_first) need += size_w;
+                region = std::max(region, need);
+            }
+            m.region = off; off += region;
+            m.sslot_bytes = align_up(dim * 4 + 32 * (dim * 2 + 16), 128);
+            m.sslot = off; off += m.n_sslots * m.sslot_bytes;
             m.ring_slot_bytes = hr * hu * 18;
-            m.ring = alias;
-            m.total = std::max(off, alias + 2 * kTokWarps * m.ring_slot_bytes);
-            if (m.total + 2048 <= uint32_t(limit)) {
+            if (2 * kTokWarps * m.ring_slot_bytes > off - m.region) continue;  // the head's ring lies over the region and the score slots
+            m.total = off;
+            if (m.total + 4096 <= uint32_t(limit)) {
                 best = m;
                 fits = true;
             }
@@ -1103,7 +1293,7 @@ bool TokenPlan::build(const std::vector<StepLayerArgs>& layers, const StepShared
         return false;
     }
 
-    void (*kernel)(TokParams) = sh.dim == 128 ? (sh.neox ? token_kernel<4, true> : token_kernel<4, false>) : (sh.neox ? token_kernel<2, true> : token_kernel<2, false>);
+    void (*kernel)(TokParams) = dim == 128 ? (sh.neox ? token_kernel<4, true> : token_kernel<4, false>) : (sh.neox ? token_kernel<2, true> : token_kernel<2, false>);
     BK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(best.total)));
     int per_sm = 0;
     BK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, int(kTokThreads), best.total));
@@ -1115,8 +1305,9 @@ bool TokenPlan::build(const std::vector<StepLayerArgs>& layers, const StepShared
     auto impl = std::make_unique<Impl>();
     impl->kernel = kernel;
     impl->grid = sms;
-    // tagged vectors, two copies each: hid_a hid_b q k v scores attended gated, then the per-CTA arg-max candidates
-    const size_t per_copy = 2 * size_t(sh.hidden_size) + 2 * q_dim + 2 * kv_dim + size_t(sh.heads) * sh.max_context + sh.ffn_size;
+    const size_t rows_ctx = size_t(sh.heads) * sh.max_context;
+    const size_t maxima = (rows_ctx / 32 + 1) & ~size_t(1);  // an even count keeps the next vector 16-byte aligned
+    const size_t per_copy = 2 * (size_t(sh.hidden_size) + 2 * hu) + q_dim + 2 * kv_dim + maxima + rows_ctx + 2 * rows_ctx / 32 + size_t(qu) * 10 + size_t(fu) * 10;
     impl->pairs = 2 * per_copy + 2 * size_t(sms);
     BK_CUDA(cudaMalloc(&impl->pairs_dev, impl->pairs * sizeof(uint2)));
     BK_CUDA(cudaMemsetAsync(impl->pairs_dev, 0, impl->pairs * sizeof(uint2), s));  // tag 0 is never expected
@@ -1126,21 +1317,26 @@ bool TokenPlan::build(const std::vector<StepLayerArgs>& layers, const StepShared
     BK_CUDA(cudaMemcpyAsync(impl->words_dev, &one, sizeof(one), cudaMemcpyHostToDevice, s));  // epoch starts at 1
 
     TokParams& P = impl->params;
+    P = base;
     uint2* at = impl->pairs_dev;
-    auto take = [&](size_t n) {
+    auto take = [&](size_t n) {  // every vector starts 16-byte aligned: all counts are even
         uint2* p = at;
         at += n;
         return p;
     };
     for (int c = 0; c < 2; ++c) {
-        P.hid_a[c] = take(sh.hidden_size);
-        P.hid_b[c] = take(sh.hidden_size);
+        P.ha[c] = take(sh.hidden_size);
+        P.hsa[c] = take(2 * hu);
+        P.hb[c] = take(sh.hidden_size);
+        P.hsb[c] = take(2 * hu);
         P.xq[c] = take(q_dim);
         P.xk[c] = take(kv_dim);
         P.xv[c] = take(kv_dim);
-        P.sc[c] = take(size_t(sh.heads) * sh.max_context);
-        P.att[c] = take(q_dim);
-        P.gated[c] = take(sh.ffn_size);
+        P.sc[c] = take(maxima);
+        P.ex[c] = take(rows_ctx);
+        P.exs[c] = take(2 * rows_ctx / 32);
+        P.aq[c] = take(size_t(qu) * 10);
+        P.gq[c] = take(size_t(fu) * 10);
     }
     P.part = take(2 * size_t(sms));
 
@@ -1155,7 +1351,6 @@ bool TokenPlan::build(const std::vector<StepLayerArgs>& layers, const StepShared
             t.scl[k] = ms[k]->d;
         }
         t.attn_norm = A.attn_norm; t.ffn_norm = A.ffn_norm; t.q_norm = A.q_norm; t.k_norm = A.k_norm;
-        t.attn_sub_norm = A.attn_sub_norm; t.ffn_sub_norm = A.ffn_sub_norm;
         t.q_bias = A.q_bias; t.k_bias = A.k_bias; t.v_bias = A.v_bias;
         t.k_cache = A.k_cache; t.v_cache = A.v_cache;
     }
@@ -1173,22 +1368,22 @@ bool TokenPlan::build(const std::vector<StepLayerArgs>& layers, const StepShared
     P.output_norm = ends.output_norm; P.rope = sh.rope;
     P.hidden_in = embd_q4_0_ ? nullptr : sh.hidden;
     P.hidden_out = sh.hidden; P.logits = ends.logits;
-    P.token = ends.token; P.position = const_cast<uint32_t*>(sh.position); P.chosen = ends.chosen; P.token_slot = ends.token;
+    P.token = ends.token; P.position = const_cast<uint32_t*>(sh.position); P.chosen = ends.chosen;
     P.history = ends.history; P.history_len = ends.history_len;
     P.epoch = impl->words_dev; P.error = impl->words_dev + 1;
     P.tags_per_launch = L * kTagsPerLayer + 8;
-    P.slice_w = slice_w;
     P.sm = best;
     impl_ = impl.release();
-    char text[160];
-    std::snprintf(text, sizeof text, "one launch per token: %u CTAs, %u KB shared, %u score slots, head chunks of %u rows, %u-column value slices", sms,
-                  best.total / 1024, best.n_sslots, best.head_rows, slice_w);
+    char text[200];
+    std::snprintf(text, sizeof text, "one launch per token: %u CTAs (%u head units, %u hidden-block, %u feed-forward-block, %u attention), %u KB shared, %u score slots, "
+                  "V ring of %u chunks, head chunks of %u rows", sms, n_units, base.bd_ctas, base.c_ctas, wtasks, best.total / 1024, best.n_sslots, best.ring_chunks,
+                  best.head_rows);
     description_ = text;
     return true;
 }
 
 void TokenPlan::launch(cudaStream_t s, bool advance) {
-    // Tags must never repeat while old pairs are still in the buffers: long before the 32-bit range runs out, wipe them.
+    // Tags must never repeat while old words are still in the buffers: long before the 32-bit range runs out, wipe them.
     if ((impl_->launches_since_wipe + 2) * impl_->params.tags_per_launch >= (uint64_t(1) << 32)) {
         BK_CUDA(cudaMemsetAsync(impl_->pairs_dev, 0, impl_->pairs * sizeof(uint2), s));
         const uint32_t one = 1;

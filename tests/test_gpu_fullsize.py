@@ -91,18 +91,20 @@ def test_qwen3_0_6b_q4_0_exactly_as_benchmarked():
 
 def test_llama_3_2_1b_q4_k_m_full_depth():
     """configs[2] at full depth and vocabulary (16 layers, 128 256 ids, Q4_K with Q6_K V/down/embedding, llama3 rope
-    frequency scaling); prompt shortened from 1024 to 160 tokens and the greedy run from 256 to 24 steps."""
+    frequency scaling; every layer reuses layer 0's seeded weights - quantising sixteen distinct layers in numpy takes two
+    minutes); prompt shortened from 1024 to 160 tokens and the greedy run from 256 to 24 steps."""
     from dataclasses import replace
     spec = replace(synth.PRESETS["llama-3.2-1b-q4_k_m"], context=4096)
-    run_workload(spec, 160, 24, scored=70, exact=True)
+    run_workload(spec, 160, 24, scored=70, exact=True, share_layers=True)
 
 
 def test_bitnet_2b_tq2_0_full_depth():
     """configs[3] at full depth and vocabulary (30 layers, ternary TQ2_0 matrices, sub-norms, squared-ReLU gate, F16
-    embedding/head); prompt shortened from 512 to 96 tokens and the greedy run from 256 to 16 steps."""
+    embedding/head; every layer reuses layer 0's seeded weights); prompt shortened from 512 to 96 tokens and the greedy run
+    from 256 to 16 steps."""
     from dataclasses import replace
     spec = replace(synth.PRESETS["bitnet-2b4t-tq2_0"], context=4096)
-    run_workload(spec, 96, 16, scored=66, exact=False)
+    run_workload(spec, 96, 16, scored=66, exact=False, share_layers=True)
 
 
 def test_mistral_7b_q4_0_full_depth_one_gpu():

@@ -354,6 +354,7 @@ def test_one_launch_per_token_at_long_contexts(monkeypatch):
     toks = synth.random_tokens(spec, 3700, seed=22)
     results = {}
     for name, flags in (("token", 0), ("per_operation", abi.FLAG_NO_PERSISTENT)):
+        monkeypatch.setenv("BRISK_CUDA_TOKEN", "1" if name == "token" else "0")
         with engine.CudaSession(m, flags=flags) as s:
             assert ("one launch per token" in s.step_path()) == (name == "token"), s.step_path()
             out, at = [], 0
@@ -371,17 +372,18 @@ def test_one_launch_per_token_at_long_contexts(monkeypatch):
 
 
 def test_default_choice_of_the_single_token_path(monkeypatch):
-    """Q4_0 models of the 0.6B class run a token as one launch. Where that kernel does not apply the persistent all-layer
-    kernel is next, and where that is measured to be slower (rows wider than 4096 values) or does not apply (layer
-    matrices of several types) sessions use one kernel per operation; step_path() says which and why."""
-    for spec, expect in ((synth.tiny(synth.QWEN3_0_6B, layers=1, vocab=512), "kernel on: one launch per token"),
+    """Where the persistent all-layer kernel is measured to be slower (rows wider than 4096 values) or does not apply
+    (layer matrices of several types) sessions use one kernel per operation; step_path() says which and why. The
+    one-launch token kernel (Q4_0 models of the 0.6B class) is opt-in: measured slower than the persistent kernel."""
+    monkeypatch.delenv("BRISK_CUDA_TOKEN", raising=False)
+    for spec, expect in ((synth.tiny(synth.QWEN3_0_6B, layers=1, vocab=512), "kernel on: tagged exchange"),
                          (synth.tiny(synth.MISTRAL_7B, layers=1, vocab=512), "off: activation rows wider than 4096"),
                          (synth.tiny(synth.LLAMA_3_2_1B, layers=1, vocab=512), "off: ")):
         with engine.CudaSession(synth.generate(spec, seed=1)) as s:
             assert expect in s.step_path(), s.step_path()
-    monkeypatch.setenv("BRISK_CUDA_TOKEN", "0")
+    monkeypatch.setenv("BRISK_CUDA_TOKEN", "1")
     with engine.CudaSession(synth.generate(synth.tiny(synth.QWEN3_0_6B, layers=1, vocab=512), seed=1)) as s:
-        assert "kernel on: tagged exchange" in s.step_path(), s.step_path()
+        assert "kernel on: one launch per token" in s.step_path(), s.step_path()
 
 
 @pytest.mark.parametrize("family,spec", [
