@@ -70,6 +70,7 @@ SIGNATURES = {
     "brisk_cuda_create": (C.c_void_p, [C.POINTER(Model), C.POINTER(Options), C.c_char_p, C.c_size_t]),
     "brisk_cuda_destroy": (None, [C.c_void_p]),
     "brisk_cuda_eval": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_uint64, C.c_int, C.POINTER(_FP)]),
+    "brisk_cuda_eval_topk": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_uint64, C.c_uint32, C.POINTER(C.c_int32), _FP]),
     "brisk_cuda_rollback": (C.c_int, [C.c_void_p, C.c_uint64]),
     "brisk_cuda_position": (C.c_uint64, [C.c_void_p]),
     "brisk_cuda_vocab_size": (C.c_uint32, [C.c_void_p]),

@@ -82,7 +82,16 @@ struct TaggedIo {
     unsigned int* error;
     float* plain_out;   // optional: also store the results as ordinary floats (the step's final residual stream)
 };
-constexpr uint32_t kPollLimit = 1u << 20;  // re-reads of one batch before giving up (a fraction of a second)
+constexpr uint32_t kPollLimitDefault = 1u << 20;  // re-reads of one batch before giving up (a fraction of a second)
+#ifdef __CUDACC__
+// The limit in force, per translation unit. Only the persistent step kernel's copy is ever changed: a test makes one of its
+// waits run out (a tag nobody writes) to exercise the recovery path, with a limit of a few re-reads so that the kernel
+// still ends at once.
+static __constant__ uint32_t c_poll_limit = kPollLimitDefault;
+#define kPollLimit c_poll_limit
+#else
+constexpr uint32_t kPollLimit = kPollLimitDefault;
+#endif
 
 // A pair travels as ONE 64-bit scalar (value in the low word, tag in the high word): a naturally aligned 64-bit access is
 // single-copy atomic in the PTX memory model, so a reader sees the value and the tag of the same store. (A .v2.u32 access

@@ -233,6 +233,14 @@ private:
     std::string description_;
 };
 
+// ---- the k best logits of a row (topk.cu) --------------------------------------------------------------------------
+constexpr uint32_t kMaxTopK = 64;
+// out_ids[k], out_values[k]: descending by value, the lower id first among equal values; a NaN never ahead of a number.
+// scratch: topk_scratch_keys(vocab, k) 64-bit words.
+size_t topk_scratch_keys(uint32_t vocab, uint32_t k);
+void launch_topk(const float* logits, uint32_t vocab, uint32_t k, unsigned long long* scratch, int32_t* out_ids, float* out_values, cudaStream_t s,
+                 uint64_t* launches = nullptr);
+
 // Tensor parallel re-layout: gathered[rank][t][rows_l] -> dst[t][rank*rows_l + r] (add: dst += ...), tp ranks.
 void launch_tp_unpack(const float* gathered, float* dst, uint32_t n, uint32_t rows_l, uint32_t tp, bool add, cudaStream_t s);
 

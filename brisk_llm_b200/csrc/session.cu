@@ -177,10 +177,11 @@ struct Session {
 
     // state and scratch
     DevBuffer kv, rope, rope_local, rope_none, proj_b, tanh_table, tokens_dev, scalars, hidden_b, q_b, k_b, v_b, attended_b, ffn_b, up_b, logits_b, tp_local, tp_gathered, full_b, actf, actq0, actd0, acts0, actqk,
-        actdk, actbs, partial, am_val, am_idx, history, logit_history, trace;
+        actdk, actbs, partial, am_val, am_idx, history, logit_history, trace, topk_keys, topk_out;
     DevActMut act;
     float* logits_host = nullptr;     // pinned [64][vocab]
     int32_t* tokens_host = nullptr;   // pinned [kMaxBatch + 4]
+    int32_t* topk_host = nullptr;     // pinned [2 * kMaxTopK]: ids, then the values' bits
     uint64_t position = 0;
     cudaStream_t stream = nullptr;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
@@ -266,6 +267,7 @@ struct Session {
         if (stream) cudaStreamDestroy(stream);
         if (logits_host) cudaFreeHost(logits_host);
         if (tokens_host) cudaFreeHost(tokens_host);
+        if (topk_host) cudaFreeHost(topk_host);
         if (step_error_host) cudaFreeHost(step_error_host);
     }
 
@@ -518,12 +520,15 @@ struct Session {
         am_val.alloc(argmax_scratch_elems(vocab) * 4);
         am_idx.alloc(argmax_scratch_elems(vocab) * 4);
         history.alloc((max_context + 1) * sizeof(int32_t));
+        topk_keys.alloc(topk_scratch_keys(vocab, kMaxTopK) * sizeof(unsigned long long));
+        topk_out.alloc(2 * kMaxTopK * sizeof(int32_t));
         if (std::getenv("BRISK_CUDA_TRACE") != nullptr) {  // per-kernel phase time stamps of the decode multiplies
             trace.alloc(512 * 8 * sizeof(unsigned long long));
             BK_CUDA(cudaMemsetAsync(trace.p, 0, trace.bytes, stream));
         }
         BK_CUDA(cudaMallocHost(&logits_host, size_t(kMaxScored) * vocab * sizeof(float)));
         BK_CUDA(cudaMallocHost(&tokens_host, (kMaxBatch + 4) * sizeof(int32_t)));
+        BK_CUDA(cudaMallocHost(&topk_host, 2 * kMaxTopK * sizeof(int32_t)));
         BK_CUDA(cudaMallocHost(&step_error_host, sizeof(unsigned int)));
         *step_error_host = 0;
         BK_CUDA(cudaStreamSynchronize(stream));
@@ -915,8 +920,10 @@ struct Session {
         if (n > max_context - position) throw CudaError("cuda: context length exceeded");
     }
 
-    const float* eval(const int32_t* tokens, uint64_t n, bool all) {
+    // topk > 0: instead of the last row of logits, its `topk` best (id, value) pairs go to the host (topk_host).
+    const float* eval(const int32_t* tokens, uint64_t n, bool all, uint32_t topk = 0) {
         check_tokens(tokens, n, all);
+        if (topk > kMaxTopK || topk > vocab) throw CudaError("cuda: top-k takes k from 1 to " + std::to_string(std::min<uint32_t>(kMaxTopK, vocab)));
         begin_call();
         BK_CUDA(cudaEventRecord(ev0, stream));
         for (uint64_t begin = 0; begin < n; begin += kMaxBatch) {
@@ -934,9 +941,16 @@ struct Session {
             (void)last;
             position += cnt;
         }
-        const size_t out_bytes = size_t(all ? n : 1) * vocab * sizeof(float);
-        BK_CUDA(cudaMemcpyAsync(logits_host, logits_b.p, out_bytes, cudaMemcpyDeviceToHost, stream));
-        stats.d2h_bytes += out_bytes;
+        if (topk != 0) {
+            launch_topk(logits_b.as<float>(), vocab, topk, topk_keys.as<unsigned long long>(), topk_out.as<int32_t>(),
+                        reinterpret_cast<float*>(topk_out.as<int32_t>() + kMaxTopK), stream, &launches);
+            BK_CUDA(cudaMemcpyAsync(topk_host, topk_out.p, 2 * kMaxTopK * sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+            stats.d2h_bytes += 2 * size_t(topk) * sizeof(int32_t);
+        } else {
+            const size_t out_bytes = size_t(all ? n : 1) * vocab * sizeof(float);
+            BK_CUDA(cudaMemcpyAsync(logits_host, logits_b.p, out_bytes, cudaMemcpyDeviceToHost, stream));
+            stats.d2h_bytes += out_bytes;
+        }
         BK_CUDA(cudaEventRecord(ev1, stream));
         queue_step_check();
         BK_CUDA(cudaStreamSynchronize(stream));
@@ -1073,6 +1087,16 @@ int brisk_cuda_eval(brisk_cuda_session* session, const int32_t* tokens, uint64_t
         BK_CUDA(cudaSetDevice(session->s.device));
         const float* out = session->s.eval(tokens, n, all_logits != 0);
         if (logits != nullptr) *logits = out;
+    });
+}
+
+int brisk_cuda_eval_topk(brisk_cuda_session* session, const int32_t* tokens, uint64_t n, uint32_t k, int32_t* out_ids, float* out_values) {
+    return guarded(session, [&] {
+        if (k == 0 || out_ids == nullptr || out_values == nullptr) throw bk::CudaError("cuda: top-k needs k >= 1 and both output arrays");
+        BK_CUDA(cudaSetDevice(session->s.device));
+        session->s.eval(tokens, n, false, k);
+        std::memcpy(out_ids, session->s.topk_host, k * sizeof(int32_t));
+        std::memcpy(out_values, session->s.topk_host + bk::kMaxTopK, k * sizeof(float));
     });
 }
 

@@ -59,6 +59,7 @@ struct StepParams {
     // tagged exchange (see TaggedIo): the tags of this launch start above tag_base; the residual stream comes in and
     // goes out as ordinary floats in plain_hidden and lives in between as tagged pairs in tagged_hidden
     uint32_t tag_base;
+    uint32_t fault_layer;  // test only: this layer's q/k/v multiply expects a tag nobody writes (0xffffffff: none)
     float* plain_hidden;
     uint2* tagged_hidden;
     uint32_t hidden_size;
@@ -397,11 +398,12 @@ __global__ void __launch_bounds__(kStepThreads, 1) step_kernel(const StepParams 
             if (l + 1 < P.n_layers) fetch_desc(l + 1);
             const uint32_t t0 = P.tag_base + 2 + l * 6;  // tags of this layer's six operations: t0 .. t0 + 5
             const uint32_t tag_residual = l == 0 ? tag_in : t0 - 1;  // the previous layer's down projection
+            const uint32_t tag_qkv_in = l == P.fault_layer ? (tag_residual ^ 0x40000000u) : tag_residual;
             const bool last = l + 1 == P.n_layers;
 
             enter();
             dec_multiply_body<F, RWA, false, ring_depth(RWA * kWordsPerUnit, DEEP)>(L.qkv, cta, nctas, smem, tile, red, gate,
-                                                                                    TaggedIo{tag_residual, 0u, t0, error, nullptr});
+                                                                                    TaggedIo{tag_qkv_in, 0u, t0, error, nullptr});
             leave();
 
             enter();
@@ -571,6 +573,7 @@ struct StepPlan::Impl {
     uint32_t epoch = 0;          // launches so far; tags of a launch start above epoch * tags_per_launch
     uint32_t tags_per_launch = 0;
     uint32_t n_layers = 0, grid = 0, tile_offset = 0;
+    uint32_t fault_layer = 0xffffffffu;
     size_t smem = 0;
     unsigned long long* trace = nullptr;
 };
@@ -752,6 +755,16 @@ bool StepPlan::build(const std::vector<StepLayerArgs>& layers, const StepShared&
     impl_->plain_hidden = shared.hidden;
     impl_->hidden_size = shared.hidden_size;
     impl_->tags_per_launch = uint32_t(descs.size()) * 6 + 2;
+    {
+        // BRISK_CUDA_TEST_POLL_TIMEOUT=1 (tests only): the second layer's first multiply waits for a tag nobody writes and every
+        // wait gives up after 64 re-reads - the kernel ends at once with the error word set, and the host must raise, keep the
+        // position and carry on with the per-operation kernels. Every access stays in bounds; nothing faults or hangs.
+        const char* env = std::getenv("BRISK_CUDA_TEST_POLL_TIMEOUT");
+        const bool inject = tagged && env != nullptr && std::strcmp(env, "1") == 0;
+        impl_->fault_layer = inject ? std::min<uint32_t>(1u, uint32_t(descs.size()) - 1) : 0xffffffffu;
+        const uint32_t limit = inject ? 64u : kPollLimitDefault;
+        BK_CUDA(cudaMemcpyToSymbolAsync(c_poll_limit, &limit, sizeof(limit), 0, cudaMemcpyHostToDevice, s));
+    }
     impl_->n_layers = uint32_t(descs.size());
     impl_->grid = sms;
     impl_->tile_offset = uint32_t(act);
@@ -783,6 +796,7 @@ void StepPlan::launch(cudaStream_t s) {
         }
         ++impl_->epoch;
         P.tag_base = impl_->epoch * impl_->tags_per_launch;
+        P.fault_layer = impl_->fault_layer;
         P.plain_hidden = impl_->plain_hidden;
         P.tagged_hidden = impl_->tagged_hidden;
         P.hidden_size = impl_->hidden_size;
@@ -807,6 +821,7 @@ void StepPlan::set_trace(unsigned long long* words) { impl_->trace = words; }
 const unsigned int* StepPlan::error_word() const { return impl_->sync_dev + 2; }
 
 void StepPlan::rearm(cudaStream_t s) {
+    impl_->fault_layer = 0xffffffffu;
     BK_CUDA(cudaMemsetAsync(impl_->sync_dev, 0, 64, s));
     BK_CUDA(cudaStreamSynchronize(s));
 }

@@ -75,6 +75,19 @@ class CudaSession:
         """Like eval(), one row of logits per token; at most 64 tokens."""
         return self._eval(tokens, True, copy)
 
+    def eval_topk(self, tokens, k: int):
+        """Appends the tokens like eval(); instead of the logits row, its k best (ids, values) - descending, the lower id
+        first among equal values - selected on the device. What a sampler needs after its partial sort (brisk-llm
+        src/sampler.cpp:15-46), at k * 8 bytes per token instead of the vocabulary-sized row."""
+        tokens = np.ascontiguousarray(np.atleast_1d(tokens), np.int32)
+        ids = np.empty(k, np.int32)
+        values = np.empty(k, np.float32)
+        rc = self._lib.brisk_cuda_eval_topk(self._h, tokens.ctypes.data_as(C.POINTER(C.c_int32)), len(tokens), k,
+                                            ids.ctypes.data_as(C.POINTER(C.c_int32)), values.ctypes.data_as(C.POINTER(C.c_float)))
+        if rc != 0:
+            self._fail()
+        return ids, values
+
     def profile(self, enable: bool = True) -> dict:
         """Per-phase device milliseconds accumulated since the previous call (then cleared); switches profiling on/off."""
         import json

@@ -118,6 +118,22 @@ public:
     }
     std::size_t position() const override { return brisk_cuda_position(session_); }
 
+    // For a sampling caller: appends the tokens like eval(), but brings back only the k best (id, logit) pairs of the row,
+    // selected on the device - descending by value - instead of the vocabulary-sized span. They are everything
+    // Sampler::sample reads after its partial sort (src/sampler.cpp:15-46), so a Sampler overload taking candidates draws
+    // from them what sample(span) draws from the full row (k >= the sampler's top_k).
+    struct TopK {
+        std::vector<Token> ids;
+        std::vector<float> values;
+    };
+    TopK eval_topk(std::span<const Token> tokens, std::uint32_t k) {
+        TopK out{std::vector<Token>(k), std::vector<float>(k)};
+        if (brisk_cuda_eval_topk(session_, tokens.data(), tokens.size(), k, out.ids.data(), out.values.data()) != 0) {
+            throw std::runtime_error(brisk_cuda_last_error(session_));
+        }
+        return out;
+    }
+
     // Greedy decoding without the per-token host round trip of cmd_generate's loop (src/main.cpp:288-299).
     std::vector<Token> generate_greedy(Token first, std::size_t steps) {
         std::vector<Token> out(steps);

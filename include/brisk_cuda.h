@@ -219,6 +219,14 @@ const char* brisk_cuda_last_error(const brisk_cuda_session* session);
 int brisk_cuda_generate_greedy(brisk_cuda_session* session, int32_t first_token, uint64_t steps, int32_t* out_tokens,
                                float* out_logits);
 
+/* Engine::eval for a sampling host: appends the tokens like brisk_cuda_eval, but instead of the vocabulary-sized row of
+ * logits returns its k best (id, logit) pairs, selected on the device - out_ids[k] / out_values[k], descending by value,
+ * the lower id first among equal values, a NaN never ahead of a number. That is all Sampler::sample reads after its
+ * std::partial_sort (src/sampler.cpp:15-46: the top_k candidates by value, then softmax, top-p cut and draw on those
+ * alone), so a host sampler fed the k pairs draws what it would draw from the full row, and the per-token copy shrinks
+ * from vocab * 4 bytes to k * 8. k: 1..64 (and at most the vocabulary size); k = 1 is the greedy pick. */
+int brisk_cuda_eval_topk(brisk_cuda_session* session, const int32_t* tokens, uint64_t n, uint32_t k, int32_t* out_ids, float* out_values);
+
 int brisk_cuda_get_stats(const brisk_cuda_session* session, brisk_cuda_stats* out);
 
 /* Test hook, the counterpart of metal_matmul (src/metal/metal_session.h:39-47): out[t*rows + r] =

@@ -219,6 +219,25 @@ int ref_session_generate_greedy(void* h, const std::int32_t* prompt, std::uint64
     }
 }
 
+// Sampler::sample (src/sampler.cpp:9-46) `draws` times on one row of logits, with one Sampler (its generator advances
+// from draw to draw). Tests feed it the full row and a row that holds only the device's top-k pairs (-inf elsewhere).
+int ref_sampler_draws(const float* logits, std::uint64_t n, float temperature, std::uint32_t top_k, float top_p, std::uint64_t seed,
+                      std::uint64_t draws, std::int32_t* out) {
+    try {
+        brisk::SamplerConfig config;
+        config.temperature = temperature;
+        config.top_k = top_k;
+        config.top_p = top_p;
+        config.seed = seed;
+        brisk::Sampler sampler(config);
+        for (std::uint64_t i = 0; i < draws; ++i) out[i] = sampler.sample(std::span<const float>(logits, n));
+        return 0;
+    } catch (const std::exception& e) {
+        g_error = e.what();
+        return -1;
+    }
+}
+
 // LookupDrafter::observe + draft (src/speculative.cpp:45-65). Returns the number of guesses written.
 std::uint64_t ref_lookup_draft(const std::int32_t* history, std::uint64_t n, std::uint64_t count, std::int32_t* out) {
     brisk::LookupDrafter drafter;

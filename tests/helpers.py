@@ -109,6 +109,8 @@ def ref() -> C.CDLL:
         lib.ref_session_speculate.restype = C.c_int64
         lib.ref_session_speculate.argtypes = [C.c_void_p, _IP, C.c_uint64, C.c_uint64, C.c_uint64, _IP,
                                               C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
+        if hasattr(lib, "ref_sampler_draws"):
+            lib.ref_sampler_draws.argtypes = [_FP, C.c_uint64, C.c_float, C.c_uint32, C.c_float, C.c_uint64, C.c_uint64, _IP]
         _ref = lib
     return _ref
 

@@ -74,7 +74,15 @@ def run_workload(spec, prompt_len, steps, scored, exact, share_layers=False):
         s.rollback(0)
         cpu.rollback(0)
         got_ll, want_ll = s.log_likelihood(seq), cpu.log_likelihood(seq)
-        assert round(math.exp(-got_ll / (scored - 1)), 3) == round(math.exp(-want_ll / (scored - 1)), 3), (got_ll, want_ll)
+        if exact:
+            assert round(math.exp(-got_ll / (scored - 1)), 3) == round(math.exp(-want_ll / (scored - 1)), 3), (got_ll, want_ll)
+        else:
+            # An F16 head agrees to 1e-5 per logit, not bit for bit, and a random sequence on random weights has a perplexity
+            # near the vocabulary size (~2e5): three decimals of THAT number would be nine significant digits. The quantity
+            # a perplexity pin of real text fixes to three decimals is of order ten - so here the mean negative
+            # log-likelihood (the logarithm of the perplexity, ~12) is held to three decimals, and far more tightly in fact.
+            assert round(-got_ll / (scored - 1), 3) == round(-want_ll / (scored - 1), 3), (got_ll, want_ll)
+            assert abs(got_ll - want_ll) <= 1e-5 * (scored - 1), (got_ll, want_ll)
         path = s.step_path()
     cpu.close()
     print(f"\n{spec.name}: checker={kind}, prompt {prompt_len} + {steps} steps, max|d|={worst[0]:.3g} rel-L2={worst[1]:.3g} "

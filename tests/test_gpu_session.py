@@ -406,3 +406,36 @@ def test_long_prompt_against_the_oracle(family, spec):
             close(s.eval(toks[i:i + 1]), o.eval(toks[i:i + 1]))
         close(s.eval_all(toks[1304:1310]), o.eval_all(toks[1304:1310]))
     o.close()
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_session_carries_on(monkeypatch):
+    """Every wait inside the persistent kernel is bounded. A test-only switch makes one operation wait for a tag nobody
+    writes, with a limit of a few re-reads: the kernel must still end at once (every access stays in bounds - nothing faults or
+    hangs), the call must raise, the position must stay where it was, and the session must go on decoding - through the
+    per-operation kernels - with results identical to the oracle's."""
+    spec = synth.tiny(synth.QWEN3_0_6B, layers=3, vocab=1024, context=256)
+    m = synth.perturb_norms(synth.generate(spec, seed=31))
+    toks = synth.random_tokens(spec, 24, seed=32)
+    o = H.OracleSession(m)
+    monkeypatch.setenv("BRISK_CUDA_TEST_POLL_TIMEOUT", "1")
+    monkeypatch.setenv("BRISK_CUDA_TOKEN", "0")
+    with engine.CudaSession(m) as s:
+        assert "kernel on: tagged exchange" in s.step_path()
+        close(s.eval(toks[:16]), o.eval(toks[:16]))  # prompts take the batched kernels: unaffected
+        with pytest.raises(RuntimeError, match="timed out"):
+            s.eval(toks[16:17])  # one single-token step (not the device greedy loop, which would feed on the garbage)
+        assert s.position() == 16
+        assert "off: " in s.step_path()
+        for i in range(16, 20):  # the same token again, and more: now one kernel per operation
+            close(s.eval(toks[i:i + 1]), o.eval(toks[i:i + 1]))
+            assert s.stats()["persistent_steps"] == 0
+        ids, logits = s.generate_greedy(int(toks[20]), 3, want_logits=True)
+        want_ids, want_logits = o.generate_greedy(toks[20:21], 3)
+        assert np.array_equal(ids, want_ids) and np.array_equal(logits, want_logits)
+    o.close()
+    monkeypatch.delenv("BRISK_CUDA_TEST_POLL_TIMEOUT")
+    with engine.CudaSession(m) as s:  # the next session has the full limit again
+        assert "kernel on: tagged exchange" in s.step_path()
+        s.eval(toks[:16])
+        s.eval(toks[16:17])
+        assert s.stats()["persistent_steps"] == 1

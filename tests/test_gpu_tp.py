@@ -1,5 +1,6 @@
-"""Tensor-parallel token loop on 2 GPUs (skipped with fewer): each rank holds half of every matrix's rows and half of
-the K/V heads; the logits every rank returns must equal the CPU oracle's bit for bit, like the single-GPU path."""
+"""Tensor-parallel token loop on 2, 4 and 8 GPUs (each case skipped where the machine has fewer): every rank holds its
+share of every matrix's rows and of the K/V heads - one K/V head per GPU at 8 ranks; the logits every rank returns must
+equal the CPU oracle's bit for bit, like the single-GPU path."""
 import os
 import subprocess
 import sys
@@ -29,8 +30,8 @@ WORKER = textwrap.dedent(r'''
     if sys.argv[3] == "gemma3":  # post-norms read the gathered projection, the GELU runs on this rank's slice, soft-capped logits
         spec = synth.tiny(synth.QWEN3_0_6B, arch="gemma3", layers=7, vocab=1024, hidden=1024, heads=8, kv_heads=4, ffn=2048, context=512,
                           sliding_window=16, rope_scaling_factor=8.0, final_softcap=30.0)
-    else:
-        spec = synth.tiny(synth.MISTRAL_7B, layers=2, vocab=1024, hidden=1024, heads=8, kv_heads=4, ffn=2048, context=512)
+    else:  # 16 query heads on 8 K/V heads: at 8 ranks every GPU holds one K/V head and its two query heads
+        spec = synth.tiny(synth.MISTRAL_7B, layers=2, vocab=1024, hidden=1024, heads=16, kv_heads=8, ffn=2048, context=512)
     model = synth.perturb_norms(synth.generate(spec, seed=4))
     toks = synth.random_tokens(spec, 80, seed=5)
     mark("model ready")
@@ -63,16 +64,16 @@ WORKER = textwrap.dedent(r'''
 ''')
 
 
-@pytest.mark.parametrize("family", ["llama", "gemma3"])
-def test_two_rank_tensor_parallel_matches_the_oracle(family, tmp_path):
+@pytest.mark.parametrize("family,world", [("llama", 2), ("llama", 4), ("llama", 8), ("gemma3", 2), ("gemma3", 4)])
+def test_tensor_parallel_matches_the_oracle(family, world, tmp_path):
     from brisk_llm_b200 import engine
-    if engine.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
+    if engine.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     script = tmp_path / "tp_worker.py"
     script.write_text(WORKER)
-    port = 29700 + os.getpid() % 200 + (0 if family == "llama" else 211)
+    port = 29700 + os.getpid() % 200 + (0 if family == "llama" else 211) + 17 * world
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", NCCL_IB_DISABLE="1", NCCL_SOCKET_IFNAME="lo", NCCL_DEBUG="WARN")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
            "--master-port", str(port), str(script), H.ROOT, str(tmp_path), family]
     try:
         r = subprocess.run(cmd, capture_output=True, text=True, timeout=200, env=env)
@@ -86,5 +87,6 @@ def test_two_rank_tensor_parallel_matches_the_oracle(family, tmp_path):
         with open(os.path.join(log_dir, "tp_test_failure.log"), "w") as f:
             f.write(r.stdout + "\n---- stderr ----\n" + r.stderr + "\n---- rank logs ----\n" + repr(logs))
     assert r.returncode == 0, (logs, r.stdout[-1500:], r.stderr[-3000:])
-    a, b = np.load(tmp_path / "logits0.npy"), np.load(tmp_path / "logits1.npy")
-    assert np.array_equal(a, b)  # every rank holds the full, identical logits
+    a = np.load(tmp_path / "logits0.npy")
+    for rank in range(1, world):  # every rank holds the full, identical logits
+        assert np.array_equal(a, np.load(tmp_path / f"logits{rank}.npy")), rank
