@@ -49,6 +49,8 @@ def parse():
     p.add_argument("--layers", type=int, default=0, help="override the layer count (debugging; the reported number is then not the configured workload)")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel section (the 7B-shaped configuration)")
+    p.add_argument("--spec", type=int, default=0, metavar="D", help="instead of the headline: the speculative-verify variant of the 7B-shaped configuration - "
+                   "4 sequences, D drafted tokens per verify step (n-gram lookup drafts), on one GPU")
     p.add_argument("--profile", action="store_true", help="for ncu launch lists: exactly --warmup warm-up steps, no end-to-end loop, no CPU baseline (the printed number is not a bench value)")
     return p.parse_args()
 
@@ -291,10 +293,72 @@ def tensor_parallel_section(engine, torch, dist, rank, local, world, max_over_ra
         sess.close()
 
 
+def run_speculative(args):
+    """configs[4]'s second workload: 4 sequences of the Mistral-7B-shaped model, each an 8192-token prompt, then 512 tokens
+    settled by lookup-draft speculative decoding with D drafted tokens per verify step (Speculator + LookupDrafter,
+    brisk-llm src/speculative.cpp:45-118: a verify step is eval_all(1 + drafts) and a rollback). The four sessions are
+    stepped round-robin from one host thread, every call with host buffers (the logits of all 1 + D rows come back)."""
+    import torch  # noqa: F401  (device initialisation order as in the main arm)
+    from dataclasses import replace
+    from brisk_llm_b200 import engine, speculative
+    prompt_len, decode, ctx = WORKLOADS["mistral-7b-q4_0"]
+    prompt_len, decode = args.prompt or prompt_len, args.decode or decode
+    spec = replace(synth.PRESETS["mistral-7b-q4_0"], context=ctx)
+    model = synth.generate(spec, seed=0, share_layers=True)
+    sequences = 4
+    sessions = [engine.CudaSession(model, max_context=ctx) for _ in range(sequences)]
+    try:
+        # text that repeats itself, so that the drafter has something to propose: a 64-token motif with seeded variations
+        rng = np.random.default_rng(1)
+        prompts = []
+        for i in range(sequences):
+            motif = rng.integers(0, spec.vocab, size=64, dtype=np.int32)
+            prompts.append(np.tile(motif, prompt_len // 64 + 1)[:prompt_len].copy())
+        t0 = time.perf_counter()
+        specs = []
+        for sess, prm in zip(sessions, prompts):
+            drafter = speculative.LookupDrafter()
+            drafter.observe(prm)
+            sess.eval(prm[:-1])
+            specs.append(speculative.Speculator(sess, drafter, int(prm[-1]), args.spec))
+        t_prefill = time.perf_counter() - t0
+        settled = [0] * sequences
+        verify_ms, plain_ms, verify_n, plain_n = 0.0, 0.0, 0, 0
+        t0 = time.perf_counter()
+        while min(settled) < decode:
+            for i, sp in enumerate(specs):
+                if settled[i] >= decode:
+                    continue
+                was_plain = sp.backoff > 0
+                settled[i] += len(sp.step())
+                ms = sessions[i].stats()["device_ms"]
+                if was_plain:
+                    plain_ms, plain_n = plain_ms + ms, plain_n + 1
+                else:
+                    verify_ms, verify_n = verify_ms + ms, verify_n + 1
+        wall = time.perf_counter() - t0
+        stats = {k: sum(sp.stats[k] for sp in specs) for k in specs[0].stats}
+        line = {"metric": "speculative_settled_tokens_per_s", "value": sum(settled) / wall, "unit": "tok/s", "n_gpus": 1, "higher_is_better": True,
+                "data": "synthetic", "config": {"workload": f"{spec.name}: {sequences} sequences x ({prompt_len}-token repeating prompt + {decode} settled tokens), "
+                                                            f"{args.spec} drafted tokens per verify step (n-gram lookup), ctx {ctx}, one GPU, host buffers"},
+                "verify_steps": verify_n, "ms_per_verify_step_device": verify_ms / max(verify_n, 1), "plain_steps": plain_n,
+                "ms_per_plain_step_device": plain_ms / max(plain_n, 1) if plain_n else None,
+                "verify_step_over_plain_step": (verify_ms / max(verify_n, 1)) / (plain_ms / plain_n) if plain_n else None,
+                "drafted": stats["drafted"], "accepted": stats["accepted"], "prefill_tokens_per_s": sequences * (prompt_len - 1) / t_prefill,
+                "wall_s": wall}
+        print(json.dumps(line), flush=True)
+    finally:
+        for sess in sessions:
+            sess.close()
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.spec:
+        run_speculative(args)
         return
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -357,6 +421,18 @@ def main():
         t2 = time.perf_counter()
         return t1 - t0, t2 - t1, h2d, d2h
 
+    def topk_step(k=20):
+        """Decode through eval_topk: per token 4 bytes of token id in, k (id, logit) pairs out - what a sampling host needs
+        (here it takes the first pair, so the sequence is the greedy one)."""
+        sess.rollback(0)
+        logits = sess.eval(ids)
+        nxt = int(np.argmax(logits))
+        t1 = time.perf_counter()
+        for _ in range(decode):
+            top_ids, _ = sess.eval_topk([nxt], k)
+            nxt = int(top_ids[0])
+        return time.perf_counter() - t1
+
     warmups = args.warmup if args.profile else max(args.warmup, 3)
     for _ in range(warmups):
         device_step()
@@ -383,6 +459,9 @@ def main():
             a, b, c, d = e2e_step()
             e_pre, e_dec, h2d, d2h = e_pre + a, e_dec + b, c, d
         barrier()
+        topk_step()
+        k_dec = sum(topk_step() for _ in range(args.steps))
+        barrier()
 
     def max_over_ranks(v):
         if dist is None:
@@ -392,6 +471,7 @@ def main():
         return float(t.item())
 
     pre_ms, dec_ms, e_pre, e_dec = (max_over_ranks(v) for v in (pre_ms, dec_ms, e_pre, e_dec))
+    k_dec = max_over_ranks(k_dec) if not args.profile else 0.0
     tp_line = None
     if not args.profile and not args.no_tp and args.config == "qwen3-0.6b-q4_0" and not args.layers:
         try:
@@ -414,6 +494,8 @@ def main():
                 "wall_s_timed_region": t_wall,
                 "e2e": {"value": jobs * tokens / e_dec, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                         "prefill_tokens_per_s": jobs * args.steps * prompt / e_pre},
+                "e2e_topk": None if args.profile else {"value": jobs * args.steps * decode / k_dec, "unit": UNIT, "k": 20, "h2d_bytes_per_token": 8, "d2h_bytes_per_token": 160,
+                                                       "note": "eval_topk per token: the host gets the 20 best (id, logit) pairs instead of the whole row"},
                 "gpu_launches": launches,
                 "clocks": clocks,
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
