@@ -303,6 +303,7 @@ def run_speculative(args):
     from brisk_llm_b200 import engine, speculative
     prompt_len, decode, ctx = WORKLOADS["mistral-7b-q4_0"]
     prompt_len, decode = args.prompt or prompt_len, args.decode or decode
+    ctx += 64  # a verify step evaluates up to D tokens past the last settled one: room for it at the end of the run
     spec = replace(synth.PRESETS["mistral-7b-q4_0"], context=ctx)
     model = synth.generate(spec, seed=0, share_layers=True)
     sequences = 4

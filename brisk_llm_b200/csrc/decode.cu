@@ -10,6 +10,7 @@
 // norm, 8-bit quantisation) is recomputed by every CTA in shared memory instead of by a separate one-CTA kernel. All arithmetic is the reference's, in the
 // reference's order (see formats.cuh, rowops.cuh, exact_math.h), so the step stays bit-identical to the CPU engine.
 #include <cstdlib>
+#include <cstring>
 #include <type_traits>
 
 #include "decode_body.cuh"
@@ -65,13 +66,22 @@ struct PdlGate {  // the gate of the one-kernel-per-operation path: programmatic
     }
 };
 
-template <class F, int RW, bool PAIR, int kDepth>
+template <class F, int RW, bool PAIR, int kDepth, bool RELAX = false>
 __global__ void __launch_bounds__(kDecWarps * 32) dec_matvec_kernel(const DecMatParams p) {
     constexpr int CHAINS = (PAIR ? 2 : 1) * RW;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    __shared__ __align__(16) float tile[F::kExact ? dec_tile_floats(CHAINS) : 1];
+    __shared__ __align__(16) float tile[F::kExact && !RELAX ? dec_tile_floats(CHAINS) : 1];
     __shared__ double red[32];
-    dec_multiply_body<F, RW, PAIR, kDepth>(p, blockIdx.x, gridDim.x, smem_raw, tile, red, PdlGate{p.pdl});
+    dec_multiply_body<F, RW, PAIR, kDepth, PdlGate, PlainIo, RELAX>(p, blockIdx.x, gridDim.x, smem_raw, tile, red, PdlGate{p.pdl});
+}
+
+// BRISK_CUDA_RELAXED: a comma-separated list of the orders to relax in the one-kernel-per-operation single-token path -
+// "rowsum" (butterfly row sums in the multiplies), "attention" (split-position softmax and weighted sum combined afterwards,
+// with the fast exp). Off by default and never used by a parity test: the exact order is what makes the results the
+// reference's; these switches exist so that the cost of giving it up can be measured (tests/test_gpu_relaxed.py).
+bool relaxed(const char* what) {
+    const char* env = std::getenv("BRISK_CUDA_RELAXED");
+    return env != nullptr && (std::strstr(env, what) != nullptr || std::strstr(env, "all") != nullptr);
 }
 
 template <class F, int RW, bool PAIR>
@@ -88,6 +98,12 @@ void launch_dec_one(DecMatParams& p, uint32_t sms, cudaStream_t s) {
         if (smem > 40 * 1024) BK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
         launch_pdl(kernel, dim3(grid), dim3(kDecWarps * 32), smem, s, p);
     };
+    if constexpr (F::kExact && RW <= 2) {  // the relaxed variants, for the measurement only (fewer shapes: compile time)
+        if (relaxed("rowsum")) {
+            go(dec_matvec_kernel<F, RW, PAIR, 1, true>);
+            return;
+        }
+    }
     if (iters > 2 && kDeep > 1) go(dec_matvec_kernel<F, RW, PAIR, kDeep>);
     else go(dec_matvec_kernel<F, RW, PAIR, 1>);
 }
@@ -106,6 +122,7 @@ void dispatch_dec(DecMatParams& p, bool pair, uint32_t sms, cudaStream_t s) {
     const uint32_t enough = sms * kDecWarps / 2;
     constexpr bool heavy = sizeof(typename F::W) > 32;  // K-quants: many registers per row, cap the rows per warp
     int rw = 1;
+    if (relaxed("rowsum")) div4 = false;
     if (div4 && !heavy && rows / 4 >= enough) rw = 4;
     else if (div2 && (!heavy || !pair) && rows / 2 >= enough) rw = 2;
     if (pair) {
@@ -215,6 +232,56 @@ __global__ void __launch_bounds__(256) dec_attn_out_kernel(const DecAttnParams a
     dec_attn_out_body<256>(a, blockIdx.x, blockIdx.y, raw, redf, redd, PdlGateEarly{a.pdl});
 }
 
+// ---- relaxed order, for the measurement only (BRISK_CUDA_RELAXED=attention) -------------------------------------------
+// The usual GPU formulation of single-token attention: the positions are split into eight ranges, each range reduces its own
+// maximum, its sum of (fast) exps and its weighted sum of V, and a second kernel combines the eight with the usual rescaling.
+// Every sum is in another order than the reference's (position after position over the whole context, glibc's expf).
+constexpr uint32_t kFlashSplits = 8;
+constexpr uint32_t kFlashHeads = 64;
+// the ranges' partial results [head][range][dim + 2]; in the library image because the step is captured into a graph, where
+// nothing may be allocated (270 KB; only ever touched when the measurement switch is on)
+__device__ float g_flash_partial[kFlashHeads * kFlashSplits * 130];
+__global__ void __launch_bounds__(128) dec_attn_flash_kernel(const DecAttnParams a, float* partial) {
+    const uint32_t h = blockIdx.x, split = blockIdx.y, dim = a.dim, tid = threadIdx.x;
+    const uint32_t visible = *a.position + 1, kvh = h / (a.heads / a.kv_heads);
+    const uint32_t per = (visible + kFlashSplits - 1) / kFlashSplits, begin = split * per, end = min(visible, begin + per);
+    const float* s = a.scores + size_t(h) * a.max_context;
+    __shared__ float red[4];
+    float m = -INFINITY;
+    for (uint32_t p = begin + tid; p < end; p += 128) m = fmaxf(m, s[p]);
+    m = warp_max(m);
+    if ((tid & 31) == 0) red[tid >> 5] = m;
+    __syncthreads();
+    m = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    float l = 0.0f, acc = 0.0f;
+    for (uint32_t p = begin; p < end; ++p) {
+        const float e = __expf(s[p] - m);
+        l += e;
+        if (tid < dim) acc = fmaf(e, __half2float(a.v_cache[(size_t(kvh) * a.max_context + p) * dim + tid]), acc);
+    }
+    float* out = partial + (size_t(h) * kFlashSplits + split) * (dim + 2);
+    if (tid < dim) out[tid] = acc;
+    if (tid == 0) {
+        out[dim] = m;
+        out[dim + 1] = l;
+    }
+}
+__global__ void __launch_bounds__(128) dec_attn_combine_kernel(const DecAttnParams a, const float* partial) {
+    const uint32_t h = blockIdx.x, dim = a.dim, tid = threadIdx.x;
+    const float* in = partial + size_t(h) * kFlashSplits * (dim + 2);
+    float m = -INFINITY;
+    for (uint32_t i = 0; i < kFlashSplits; ++i) m = fmaxf(m, in[i * (dim + 2) + dim]);
+    float l = 0.0f, acc = 0.0f;
+    for (uint32_t i = 0; i < kFlashSplits; ++i) {
+        const float li = in[i * (dim + 2) + dim + 1];
+        if (li == 0.0f) continue;  // an empty range
+        const float w = __expf(in[i * (dim + 2) + dim] - m);
+        l = fmaf(li, w, l);
+        if (tid < dim) acc = fmaf(in[i * (dim + 2) + tid], w, acc);
+    }
+    if (tid < dim) a.out[size_t(h) * dim + tid] = acc / l;
+}
+
 }  // namespace
 
 // The launchers below are declared in kernels.h.
@@ -285,6 +352,15 @@ void launch_dec_attention(const RopeArgs& r, const AttnArgs& at, uint32_t sms, c
         default: throw CudaError("cuda: query heads per K/V head must be 1 to 8");
     }
 #undef BK_SCORES
+    if (relaxed("attention")) {  // measurement only: split-position softmax and weighted sum
+        float* partial = nullptr;
+        BK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&partial), g_flash_partial));
+        if (a.heads > kFlashHeads || a.dim > 128) throw CudaError("cuda: the relaxed attention measurement takes up to 64 heads of up to 128 values");
+        dec_attn_flash_kernel<<<dim3(a.heads, kFlashSplits), 128, 0, s>>>(a, partial);
+        dec_attn_combine_kernel<<<a.heads, 128, 0, s>>>(a, partial);
+        BK_CUDA(cudaGetLastError());
+        return;
+    }
     a.slice_width = dec_attn_slice_width(a.heads, a.dim, sms);
     const size_t smem2 = dec_attn_out_smem(a.max_context, a.slice_width);
     static DeviceOnce once;

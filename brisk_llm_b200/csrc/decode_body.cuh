@@ -135,10 +135,15 @@ __device__ __forceinline__ float poll_pair(const void* p, uint32_t tag, unsigned
 //   red: 32 doubles.
 // Ends with every thread past its last shared-memory access except the epilogue stores; callers that reuse the shared
 // memory must put a barrier after it.
-template <class F, int RW, bool PAIR, int kDepth, class Gate, class Io = PlainIo>
+// RELAX (never the default, never in a parity test): a row's block terms are added as a butterfly over the lanes instead of
+// in block order - the order a GPU kernel would naturally use. It exists to put a number on what that costs in agreement
+// with the reference (BRISK_CUDA_RELAXED, see launch_dec_multiply).
+template <class F, int RW, bool PAIR, int kDepth, class Gate, class Io = PlainIo, bool RELAX = false>
 __device__ __forceinline__ void dec_multiply_body(const DecMatParams& p, const uint32_t cta, const uint32_t nctas, unsigned char* act_smem, float* tile,
                                                   double* red, Gate&& gate, const Io& io = Io{}) {
     static_assert(!Io::kTagged || F::kExact, "tagged exchange is implemented for the exact (quantised) formats");
+    static_assert(!(RELAX && Io::kTagged), "the relaxed sum exists for the one-kernel-per-operation path only");
+    constexpr bool kOrdered = F::kExact && !RELAX;  // block-order row sums through the shared-memory transpose
     constexpr int MATS = PAIR ? 2 : 1;
     constexpr int CHAINS = MATS * RW;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -351,7 +356,7 @@ __device__ __forceinline__ void dec_multiply_body(const DecMatParams& p, const u
         for (int d = 0; d < kDepth; ++d) {
             const uint32_t it = it0 + d;
             if (it >= my_iters) break;
-            if (F::kExact && !PAIR && step == 0 && p.epi == EPI_ADD && lane < RW) {
+            if (kOrdered && !PAIR && step == 0 && p.epi == EPI_ADD && lane < RW) {
                 int target;
                 uint32_t row0;
                 locate(group, target, row0);
@@ -376,10 +381,10 @@ __device__ __forceinline__ void dec_multiply_body(const DecMatParams& p, const u
 #pragma unroll
                 for (int r = 0; r < RW; ++r) {
                     const float term = F::term(w[a][r], x, valid, uu);
-                    if constexpr (F::kExact) tile[(warp * CHAINS + a * RW + r) * 36 + lane] = term;
+                    if constexpr (kOrdered) tile[(warp * CHAINS + a * RW + r) * 36 + lane] = term;
                     else acc[a][r] = __fadd_rn(acc[a][r], term);
                 }
-            if constexpr (F::kExact) {
+            if constexpr (kOrdered) {
                 __syncwarp();
                 if (lane < CHAINS) {
                     const int cnt = int(min(32u, units - step * 32));
@@ -406,7 +411,7 @@ __device__ __forceinline__ void dec_multiply_body(const DecMatParams& p, const u
                 locate(group, target, row0);
                 const DevMatrix& m = p.m[target];
                 float* outp = p.out[PAIR ? 0 : target];
-                if constexpr (F::kExact) {
+                if constexpr (kOrdered) {
                     const float other = PAIR ? __shfl_down_sync(0xffffffffu, run, RW) : 0.0f;
                     if (lane < RW && row0 + lane < m.rows) {
                         float result;

@@ -646,9 +646,23 @@ struct Session {
     void exchange(const float* local, float* dst, uint32_t n, uint32_t rows_l, bool add) {
         Scope sc(this, PH_EXCHANGE);
         const Nccl& nccl = Nccl::get();
+        if (n == 1 && !add) {  // one token: the gathered order [rank][rows_l] IS the row order - no re-layout kernel
+            nccl.check(nccl.AllGather(local, dst, rows_l, kNcclFloat, comm, stream), "ncclAllGather");
+            ++launches;
+            return;
+        }
         nccl.check(nccl.AllGather(local, tp_gathered.p, size_t(n) * rows_l, kNcclFloat, comm, stream), "ncclAllGather");
         launch_tp_unpack(tp_gathered.as<float>(), dst, n, rows_l, uint32_t(tp_size), add, stream);
         launches += 2;
+    }
+
+    // One token, a projection that joins the residual stream: every rank has added its rows into its own slice of the (everywhere
+    // identical) stream; the slices are gathered in place.
+    void gather_in_place(float* full, uint32_t rows_l) {
+        Scope sc(this, PH_EXCHANGE);
+        const Nccl& nccl = Nccl::get();
+        nccl.check(nccl.AllGather(full + size_t(tp_rank) * rows_l, full, rows_l, kNcclFloat, comm, stream), "ncclAllGather");
+        ++launches;
     }
 
     // The layers of one batch. n tokens are in tokens_dev, their first position in d_position(); max_visible bounds
@@ -739,12 +753,20 @@ struct Session {
             if (tp) {
                 exchange(attended_b.as<float>(), full_b.as<float>(), n, q_dim_l, false);
                 attended = full_b.as<float>();
-                {
-                    Scope sc(this, PH_ATTN_OUT);
-                    apply({{L.o, tp_local.as<float>(), hidden_l}}, attended, q_dim, L.attn_sub_norm, q_dim, EPI_STORE);
+                if (n == 1 && L.attn_post_norm == nullptr) {
+                    {
+                        Scope sc(this, PH_ATTN_OUT);
+                        apply({{L.o, hid + size_t(tp_rank) * hidden_l, hidden_l}}, attended, q_dim, L.attn_sub_norm, q_dim, EPI_ADD);
+                    }
+                    gather_in_place(hid, hidden_l);
+                } else {
+                    {
+                        Scope sc(this, PH_ATTN_OUT);
+                        apply({{L.o, tp_local.as<float>(), hidden_l}}, attended, q_dim, L.attn_sub_norm, q_dim, EPI_STORE);
+                    }
+                    exchange(tp_local.as<float>(), L.attn_post_norm ? proj_b.as<float>() : hid, n, hidden_l, L.attn_post_norm == nullptr);
+                    if (L.attn_post_norm) post_norm_add(L.attn_post_norm);
                 }
-                exchange(tp_local.as<float>(), L.attn_post_norm ? proj_b.as<float>() : hid, n, hidden_l, L.attn_post_norm == nullptr);
-                if (L.attn_post_norm) post_norm_add(L.attn_post_norm);
             } else {
                 Scope sc(this, PH_ATTN_OUT);
                 if (L.attn_post_norm) {
@@ -773,12 +795,20 @@ struct Session {
             if (tp) {
                 gate_up(tp_local.as<float>(), ffn_l);
                 exchange(tp_local.as<float>(), ffn_b.as<float>(), n, ffn_l, false);
-                {
-                    Scope sc(this, PH_DOWN);
-                    apply({{L.down, tp_local.as<float>(), hidden_l}}, gated, ffn, L.ffn_sub_norm, ffn, EPI_STORE);
+                if (n == 1 && L.ffn_post_norm == nullptr) {
+                    {
+                        Scope sc(this, PH_DOWN);
+                        apply({{L.down, hid + size_t(tp_rank) * hidden_l, hidden_l}}, gated, ffn, L.ffn_sub_norm, ffn, EPI_ADD);
+                    }
+                    gather_in_place(hid, hidden_l);
+                } else {
+                    {
+                        Scope sc(this, PH_DOWN);
+                        apply({{L.down, tp_local.as<float>(), hidden_l}}, gated, ffn, L.ffn_sub_norm, ffn, EPI_STORE);
+                    }
+                    exchange(tp_local.as<float>(), L.ffn_post_norm ? proj_b.as<float>() : hid, n, hidden_l, L.ffn_post_norm == nullptr);
+                    if (L.ffn_post_norm) post_norm_add(L.ffn_post_norm);
                 }
-                exchange(tp_local.as<float>(), L.ffn_post_norm ? proj_b.as<float>() : hid, n, hidden_l, L.ffn_post_norm == nullptr);
-                if (L.ffn_post_norm) post_norm_add(L.ffn_post_norm);
             } else {
                 gate_up(ffn_b.as<float>(), ffn);
                 Scope sc(this, PH_DOWN);
@@ -936,7 +966,7 @@ struct Session {
             BK_CUDA(cudaMemcpyAsync(d_position(), tokens_host + kMaxBatch, sizeof(uint32_t), cudaMemcpyHostToDevice, stream));
             stats.h2d_bytes += cnt * sizeof(int32_t) + sizeof(uint32_t);
             const bool last = begin + cnt == n;
-            if (cnt == 1 && !all) step_on_device();
+            if (cnt == 1 && (!all || n == 1)) step_on_device();  // one token: its one row of logits is all there is, with or without `all`
             else forward(cnt, all, uint32_t(position + cnt));
             (void)last;
             position += cnt;
