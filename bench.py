@@ -325,26 +325,46 @@ def run_speculative(args):
         t_prefill = time.perf_counter() - t0
         settled = [0] * sequences
         verify_ms, plain_ms, verify_n, plain_n = 0.0, 0.0, 0, 0
+        by_tokens = {}  # tokens in the verify step (1 + its drafts) -> [steps, device ms]
         t0 = time.perf_counter()
         while min(settled) < decode:
             for i, sp in enumerate(specs):
                 if settled[i] >= decode:
                     continue
                 was_plain = sp.backoff > 0
+                drafted_before = sp.stats["drafted"]
                 settled[i] += len(sp.step())
                 ms = sessions[i].stats()["device_ms"]
                 if was_plain:
                     plain_ms, plain_n = plain_ms + ms, plain_n + 1
                 else:
                     verify_ms, verify_n = verify_ms + ms, verify_n + 1
+                    slot = by_tokens.setdefault(1 + sp.stats["drafted"] - drafted_before, [0, 0.0])
+                    slot[0], slot[1] = slot[0] + 1, slot[1] + ms
         wall = time.perf_counter() - t0
         stats = {k: sum(sp.stats[k] for sp in specs) for k in specs[0].stats}
+        # the verify step by itself, at the context the run ended on: eval_all of 1 + D tokens and the rollback, against one token
+        sess, pos = sessions[0], sessions[0].position()
+        probe = rng.integers(0, spec.vocab, size=1 + args.spec, dtype=np.int32)
+        full_ms = one_ms = 0.0
+        reps = 10
+        for r in range(reps + 2):
+            sess.eval_all(probe)
+            a = sess.stats()["device_ms"]
+            sess.rollback(pos)
+            sess.eval(probe[:1])
+            b = sess.stats()["device_ms"]
+            sess.rollback(pos)
+            if r >= 2:
+                full_ms, one_ms = full_ms + a / reps, one_ms + b / reps
         line = {"metric": "speculative_settled_tokens_per_s", "value": sum(settled) / wall, "unit": "tok/s", "n_gpus": 1, "higher_is_better": True,
                 "data": "synthetic", "config": {"workload": f"{spec.name}: {sequences} sequences x ({prompt_len}-token repeating prompt + {decode} settled tokens), "
                                                             f"{args.spec} drafted tokens per verify step (n-gram lookup), ctx {ctx}, one GPU, host buffers"},
                 "verify_steps": verify_n, "ms_per_verify_step_device": verify_ms / max(verify_n, 1), "plain_steps": plain_n,
                 "ms_per_plain_step_device": plain_ms / max(plain_n, 1) if plain_n else None,
                 "verify_step_over_plain_step": (verify_ms / max(verify_n, 1)) / (plain_ms / plain_n) if plain_n else None,
+                "verify_steps_by_tokens": {str(k): {"steps": v[0], "ms_device": v[1] / v[0]} for k, v in sorted(by_tokens.items())},
+                "probe": {"context": pos, "tokens": 1 + args.spec, "eval_all_ms_device": full_ms, "eval_one_ms_device": one_ms, "ratio": full_ms / one_ms},
                 "drafted": stats["drafted"], "accepted": stats["accepted"], "prefill_tokens_per_s": sequences * (prompt_len - 1) / t_prefill,
                 "wall_s": wall}
         print(json.dumps(line), flush=True)

@@ -229,7 +229,9 @@ __global__ void __launch_bounds__(256) dec_attn_out_kernel(const DecAttnParams a
     extern __shared__ __align__(16) unsigned char raw[];
     __shared__ float redf[8];
     __shared__ double redd[8];
-    dec_attn_out_body<256>(a, blockIdx.x, blockIdx.y, raw, redf, redd, PdlGateEarly{a.pdl});
+    __shared__ uint64_t table[32];
+    if (threadIdx.x < 32) table[threadIdx.x] = exp2_table_device()[threadIdx.x];  // ordered before its use by the body's first barrier
+    dec_attn_out_body<256>(a, blockIdx.x, blockIdx.y, raw, redf, redd, PdlGateEarly{a.pdl}, PlainIo{}, table);
 }
 
 // ---- relaxed order, for the measurement only (BRISK_CUDA_RELAXED=attention) -------------------------------------------
@@ -360,6 +362,17 @@ void launch_dec_attention(const RopeArgs& r, const AttnArgs& at, uint32_t sms, c
         dec_attn_combine_kernel<<<a.heads, 128, 0, s>>>(a, partial);
         BK_CUDA(cudaGetLastError());
         return;
+    }
+    {
+        // on request (BRISK_CUDA_CHAIN=1) the chained kernel of attn_chain.cu instead of the fused one below: same results
+        if (chain_mode() == 1 && attn_chain_fits(1, a.heads, a.kv_heads, a.dim, a.max_context, sms)) {
+            AttnArgs one = at;
+            one.n = 1;
+            one.max_visible = a.max_context;
+            one.window = 0;
+            launch_attn_chain(one, sms, s);
+            return;
+        }
     }
     a.slice_width = dec_attn_slice_width(a.heads, a.dim, sms);
     const size_t smem2 = dec_attn_out_smem(a.max_context, a.slice_width);

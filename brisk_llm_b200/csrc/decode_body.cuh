@@ -578,7 +578,7 @@ struct TaggedAttnIo {
 // before gate.wait(); the row of the position written by this step only after it (or, tagged, taken from the v vector).
 template <int NT, class Gate, class Io = PlainIo>
 __device__ __forceinline__ void dec_attn_out_body(const DecAttnParams& a, const uint32_t h, const uint32_t slice, unsigned char* raw, float* redf,
-                                                  double* redd, Gate&& gate, const Io& io = Io{}) {
+                                                  double* redd, Gate&& gate, const Io& io = Io{}, const uint64_t* exp_table = nullptr) {
     constexpr int kWarps = NT / 32;
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, dim = a.dim, width = a.slice_width;
     const uint32_t visible = *a.position + 1, pos = visible - 1;
@@ -614,12 +614,27 @@ __device__ __forceinline__ void dec_attn_out_body(const DecAttnParams& a, const 
     // shared memory; the loops have run-time trip counts (one or two rounds at short contexts) - an unrolled,
     // predicated form issues its exp code eight times whether or not a thread has a score.
     float mx = -INFINITY;
-    for (uint32_t p = tid; p < visible; p += NT) {
-        float v;
-        if constexpr (Io::kTagged) v = poll_pair(reinterpret_cast<const uint2*>(a.scores) + size_t(h) * a.max_context + p, io.tag_scores, io.error);
-        else v = __ldcg(s + p);
-        ps[p] = v;
-        mx = fmaxf(mx, v);
+    {
+        uint32_t p = tid;
+        if constexpr (!Io::kTagged) {
+            for (; p + 3 * NT < visible; p += 4 * NT) {  // four loads in flight: one after the other each costs an L2 round trip
+                float v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) v[u] = __ldcg(s + p + u * NT);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    ps[p + u * NT] = v[u];
+                    mx = fmaxf(mx, v[u]);
+                }
+            }
+        }
+        for (; p < visible; p += NT) {
+            float v;
+            if constexpr (Io::kTagged) v = poll_pair(reinterpret_cast<const uint2*>(a.scores) + size_t(h) * a.max_context + p, io.tag_scores, io.error);
+            else v = __ldcg(s + p);
+            ps[p] = v;
+            mx = fmaxf(mx, v);
+        }
     }
     mx = warp_max(mx);
     if (lane == 0) redf[warp] = mx;
@@ -628,11 +643,24 @@ __device__ __forceinline__ void dec_attn_out_body(const DecAttnParams& a, const 
 #pragma unroll
     for (int w = 1; w < kWarps; ++w) mx = fmaxf(mx, redf[w]);
     dec_stamp(trace, 0, 2);
+    // the exps without a branch in them and, where the caller has one, with the 2^(i/32) table in shared memory; two at a time,
+    // added in the same order as one at a time
+    const uint64_t* table = exp_table != nullptr ? exp_table : exp2_table_device();
     double part = 0.0;
-    for (uint32_t p = tid; p < visible; p += NT) {
-        const float e = exact_expf(__fsub_rn(ps[p], mx));
-        ps[p] = e;
-        part += double(e);
+    {
+        uint32_t p = tid;
+        for (; p + NT < visible; p += 2 * NT) {
+            const float e0 = exact_expf_flat(__fsub_rn(ps[p], mx), table), e1 = exact_expf_flat(__fsub_rn(ps[p + NT], mx), table);
+            ps[p] = e0;
+            ps[p + NT] = e1;
+            part += double(e0);
+            part += double(e1);
+        }
+        if (p < visible) {
+            const float e = exact_expf_flat(__fsub_rn(ps[p], mx), table);
+            ps[p] = e;
+            part += double(e);
+        }
     }
     dec_stamp(trace, 0, 3);
     part = warp_sum(part);

@@ -104,6 +104,28 @@ __device__ __forceinline__ float exact_expf_tab(float x, const uint64_t* table) 
     return __double2float_rn(__dmul_rn(y, s));
 }
 __device__ __forceinline__ const uint64_t* exp2_table_device() { return kExp2TableDev; }
+// The same value again without a branch in it (the three special cases are selected at the end), so that a caller's
+// unrolled loop overlaps several of them: the double-precision operations of one exp form a single dependent chain.
+__device__ __forceinline__ float exact_expf_flat(float x, const uint64_t* table) {
+    const double n = 32.0;
+    const double inv_ln2_n = 0x1.71547652b82fep+0 * n;
+    const double shift = 0x1.8p52;
+    const double c0 = 0x1.c6af84b912394p-5 / n / n / n, c1 = 0x1.ebfce50fac4f3p-3 / n / n, c2 = 0x1.62e42ff0c52d6p-1 / n;
+    const bool special = !(x <= 0x1.62e42ep6f && x >= -0x1.9fe368p6f);  // NaN, overflow or underflow
+    const float xs = special ? 0.0f : x;                               // keeps the table index and the shifts in range
+    const double z = __dmul_rn(inv_ln2_n, double(xs));
+    double kd = __dadd_rn(z, shift);
+    const uint64_t ki = uint64_t(__double_as_longlong(kd));
+    kd = __dsub_rn(kd, shift);
+    const double r = __dsub_rn(z, kd);
+    const double s = __longlong_as_double((long long)(table[ki & 31] + (ki << 47)));
+    const double p = __dadd_rn(__dmul_rn(c0, r), c1);
+    const double r2 = __dmul_rn(r, r);
+    double y = __dadd_rn(__dmul_rn(c2, r), 1.0);
+    y = __dadd_rn(__dmul_rn(p, r2), y);
+    const float main_path = __double2float_rn(__dmul_rn(y, s));
+    return x != x ? x + x : x > 0x1.62e42ep6f ? __builtin_huge_valf() : x < -0x1.9fe368p6f ? 0.0f : main_path;
+}
 #endif
 
 }  // namespace bk

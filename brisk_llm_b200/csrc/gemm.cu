@@ -7,7 +7,10 @@
 // alone owns, walking the blocks in order - the same sequence of roundings as the CPU, so results are bit-identical
 // and the next 8-bit re-quantisation sees the same values. K is never split across threads. Q4_0's nibbles are
 // widened in registers (the low nibbles of a 4-byte word are exactly the MMA fragment for k = 4t..4t+3, the high
-// nibbles the fragment for k = 16+4t..), and its -8 offset is folded in as -8 * sum(x) per block.
+// nibbles the fragment for k = 16+4t..) and its -8 offset is taken off the fragment once, four bytes at a time, so the
+// integer block dot comes out of the MMA complete. The MMA's C operand is the constant 0x4B400000 - the bit pattern of
+// the float 1.5 * 2^23 - so that each result, read as a float, is exactly 1.5 * 2^23 + dot (|dot| <= 32 * 127 * 127 <
+// 2^22): one exact f32 subtraction stands in for the integer-to-float conversion and nothing is zeroed between MMAs.
 //
 // Tiling: CTA = 128 rows x 64 tokens, 8 warps of 32 x 32 - or, for matrices with so few rows that such tiles would leave
 // half of the SMs idle, 64 rows x 64 tokens with warps of 16 x 32; weights, activations and their scales are staged through
@@ -29,8 +32,7 @@ struct Stage {
     static constexpr int kAd = GM * KB * 2;       // weight scales (f16)
     static constexpr int kB = GN * kBRow;         // activation quants
     static constexpr int kBd = GN * KB * 4;       // activation scales (f32)
-    static constexpr int kBs = GN * KB * 4;       // activation block sums (i32)
-    static constexpr int kBytes = kA + kAd + kB + kBd + kBs;
+    static constexpr int kBytes = kA + kAd + kB + kBd;
 };
 
 __device__ __forceinline__ void cp_async8(void* smem, const void* gmem) {
@@ -43,10 +45,19 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(a), "l"(gmem) : "memory");
 }
 
-__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+constexpr int kMagicBits = 0x4B400000;     // 1.5 * 2^23 as a float
+constexpr float kMagic = 12582912.0f;
+
+// d = a x b + kMagicBits in every element
+__device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(kMagicBits));
+}
+
+// one block's term added to a running sum in the reference's order: (float(dot) * d_w) * d_x
+__device__ __forceinline__ float add_term(float acc, int biased, float dw, float dx) {
+    return __fadd_rn(acc, __fmul_rn(__fmul_rn(__fsub_rn(__int_as_float(biased), kMagic), dw), dx));
 }
 
 struct GemmParams {
@@ -105,13 +116,11 @@ __global__ void __launch_bounds__(GWARPS * 32, 2) gemm_q8_kernel(const GemmParam
             cp_async16(bq + r * S::kBRow + piece * 16, p.act.q0 + size_t(tok) * p.act.cols + b0 * 32 + piece * 16);
         }
         unsigned char* bd = bq + S::kB;
-        unsigned char* bs = bd + S::kBd;
         for (uint32_t i = tid; i < GN * 2; i += GWARPS * 32) {
             const uint32_t r = i >> 1, piece = i & 1;
             if (piece * 4 >= valid) continue;
             const uint32_t tok = min(tok_base + r, p.n - 1);
             cp_async16(bd + r * KB * 4 + piece * 16, p.act.d0 + size_t(tok) * nb + b0 + piece * 4);
-            cp_async16(bs + r * KB * 4 + piece * 16, p.act.s0 + size_t(tok) * nb + b0 + piece * 4);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -138,7 +147,6 @@ __global__ void __launch_bounds__(GWARPS * 32, 2) gemm_q8_kernel(const GemmParam
         const __half* ad = reinterpret_cast<const __half*>(base + S::kA);
         const unsigned char* bq = base + S::kA + S::kAd;
         const float* bd = reinterpret_cast<const float*>(bq + S::kB);
-        const int* bs = reinterpret_cast<const int*>(bq + S::kB + S::kBd);
         const int valid = int(min(uint32_t(KB), nb - chunk * KB));
 #pragma unroll
         for (int b = 0; b < KB; ++b) {
@@ -151,10 +159,10 @@ __global__ void __launch_bounds__(GWARPS * 32, 2) gemm_q8_kernel(const GemmParam
                 if (WBYTES == 16) {
                     const uint32_t w0 = *reinterpret_cast<const uint32_t*>(aq + r0 * S::kARow + b * 16 + 4 * t);
                     const uint32_t w1 = *reinterpret_cast<const uint32_t*>(aq + r1 * S::kARow + b * 16 + 4 * t);
-                    a[mi][0] = w0 & 0x0F0F0F0Fu;
-                    a[mi][1] = w1 & 0x0F0F0F0Fu;
-                    a[mi][2] = (w0 >> 4) & 0x0F0F0F0Fu;
-                    a[mi][3] = (w1 >> 4) & 0x0F0F0F0Fu;
+                    a[mi][0] = __vsub4(w0 & 0x0F0F0F0Fu, 0x08080808u);
+                    a[mi][1] = __vsub4(w1 & 0x0F0F0F0Fu, 0x08080808u);
+                    a[mi][2] = __vsub4((w0 >> 4) & 0x0F0F0F0Fu, 0x08080808u);
+                    a[mi][3] = __vsub4((w1 >> 4) & 0x0F0F0F0Fu, 0x08080808u);
                 } else {
                     a[mi][0] = *reinterpret_cast<const uint32_t*>(aq + r0 * S::kARow + b * 32 + 4 * t);
                     a[mi][1] = *reinterpret_cast<const uint32_t*>(aq + r1 * S::kARow + b * 32 + 4 * t);
@@ -171,16 +179,15 @@ __global__ void __launch_bounds__(GWARPS * 32, 2) gemm_q8_kernel(const GemmParam
                 const uint32_t b1 = *reinterpret_cast<const uint32_t*>(bq + (tb + g) * S::kBRow + b * 32 + 16 + 4 * t);
                 const uint32_t c0 = tb + 2 * t, c1 = c0 + 1;  // the two token columns this thread's results belong to
                 const float dx0 = bd[c0 * KB + b], dx1 = bd[c1 * KB + b];
-                const int off0 = WBYTES == 16 ? 8 * bs[c0 * KB + b] : 0, off1 = WBYTES == 16 ? 8 * bs[c1 * KB + b] : 0;
 #pragma unroll
                 for (int mi = 0; mi < MI; ++mi) {
-                    int c[4] = {0, 0, 0, 0};
+                    int c[4];
                     mma_s8(c, a[mi][0], a[mi][1], a[mi][2], a[mi][3], b0, b1);
                     // (row g, col 2t) (row g, col 2t+1) (row g+8, col 2t) (row g+8, col 2t+1)
-                    acc[mi][ni][0] = __fadd_rn(acc[mi][ni][0], __fmul_rn(__fmul_rn(float(c[0] - off0), dw[mi][0]), dx0));
-                    acc[mi][ni][1] = __fadd_rn(acc[mi][ni][1], __fmul_rn(__fmul_rn(float(c[1] - off1), dw[mi][0]), dx1));
-                    acc[mi][ni][2] = __fadd_rn(acc[mi][ni][2], __fmul_rn(__fmul_rn(float(c[2] - off0), dw[mi][1]), dx0));
-                    acc[mi][ni][3] = __fadd_rn(acc[mi][ni][3], __fmul_rn(__fmul_rn(float(c[3] - off1), dw[mi][1]), dx1));
+                    acc[mi][ni][0] = add_term(acc[mi][ni][0], c[0], dw[mi][0], dx0);
+                    acc[mi][ni][1] = add_term(acc[mi][ni][1], c[1], dw[mi][0], dx1);
+                    acc[mi][ni][2] = add_term(acc[mi][ni][2], c[2], dw[mi][1], dx0);
+                    acc[mi][ni][3] = add_term(acc[mi][ni][3], c[3], dw[mi][1], dx1);
                 }
             }
         }

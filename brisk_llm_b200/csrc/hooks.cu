@@ -39,11 +39,13 @@ struct ActBuffers {
 };
 
 // The multiply the session would run for n tokens: the fused single-token kernel (which quantises x itself), the
-// streaming kernel for small batches, the tensor-core kernel for prompt batches.
+// few-token kernel or the streaming kernel for small batches, the tensor-core kernel for prompt batches.
 void multiply(const bk::DevMatrix& m, float* out, const float* x, const bk::DevAct& a, uint32_t n, uint32_t sms, cudaStream_t s) {
     bk::MatTarget t{m, out, m.rows};
     if (n == 1) {
         bk::launch_dec_multiply(&t, 1, x, nullptr, 0.0f, m.cols, bk::EPI_STORE, sms, s);
+    } else if (bk::launch_smallbatch(&t, 1, a, n, bk::EPI_STORE, s)) {
+        // 2..16 tokens of a Q4_0 / Q8_0 matrix
     } else if (!(n >= 16 && bk::launch_gemm(&t, 1, a, n, bk::EPI_STORE, s))) {
         bk::launch_matvec(&t, 1, a, n, bk::EPI_STORE, s);
     }

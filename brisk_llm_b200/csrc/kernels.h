@@ -58,6 +58,12 @@ struct MatTarget {
 // goes to targets[0].out. n may exceed 8: the launcher walks token tiles.
 void launch_matvec(const MatTarget* targets, int count, const DevAct& act, uint32_t n, Epilogue epi, cudaStream_t s);
 
+// ---- 2..16 tokens on the int8 tensor path, weights streamed once (smallbatch.cu) ---------------------
+// Same contract as launch_matvec; returns false (nothing launched) unless the targets are Q4_0 / Q8_0 with rows of a
+// multiple of 8 blocks and 2 <= n <= kSmallBatchMax.
+constexpr uint32_t kSmallBatchMax = 16;
+bool launch_smallbatch(const MatTarget* targets, int count, const DevAct& act, uint32_t n, Epilogue epi, cudaStream_t s);
+
 // ---- batched multiply on the int8 tensor path (gemm.cu) ----------------------------------------
 // Same contract as launch_matvec for n >= 16 tokens; returns false when this type/shape has no tensor kernel
 // (the caller then uses launch_matvec).
@@ -120,6 +126,16 @@ struct AttnArgs {
 };
 size_t attn_scratch_floats(uint32_t n, uint32_t heads, uint32_t max_context);
 void launch_attention(const AttnArgs& a, cudaStream_t s);
+// Softmax + weighted sum for a few tokens (attn_chain.cu): a.scores holds their scaled scores. One CTA per (token, one or
+// two query heads, slice of the head), chain warps and product warps; same results as the kernels above.
+bool attn_chain_fits(uint32_t n, uint32_t heads, uint32_t kv_heads, uint32_t dim, uint32_t max_visible, uint32_t sms);
+void launch_attn_chain(const AttnArgs& a, uint32_t sms, cudaStream_t s);
+constexpr uint32_t kChainMaxTokens = 24;      // more tokens than this share V rows through the tiled kernel instead
+// BRISK_CUDA_CHAIN: 0 never, 1 wherever it fits (single tokens too), unset: 2..kChainMaxTokens tokens. A single token keeps
+// the fused kernel of decode.cu by default: at 8192 positions that one measures ~75 us per layer, this one 99 us (the f16 ->
+// f32 widening, which the fused kernel spreads over all its threads, costs a chain lane ~4 cycles per position here).
+int chain_mode();
+unsigned int* attn_chain_error_word();        // non-zero on the device after a launch whose wait for a bulk copy ran out
 
 // ---- fused single-token step (decode.cu) -------------------------------------------------------------------------
 // One multiply of the decode step: every CTA rebuilds the activation row in shared memory (x, optionally RMS-normed with

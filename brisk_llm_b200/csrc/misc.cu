@@ -6,6 +6,8 @@
 #include <utility>
 
 #include "exact_math.h"
+#include <cstdlib>
+
 #include "kernels.h"
 
 namespace bk {
@@ -522,6 +524,11 @@ void launch_qk_norm_rope_store(const RopeArgs& a, cudaStream_t s) {
     BK_CUDA(cudaGetLastError());
 }
 
+int chain_mode() {  // read at every call: the tests switch it between sessions of one process
+    const char* env = std::getenv("BRISK_CUDA_CHAIN");
+    return env == nullptr ? -1 : std::atoi(env) != 0 ? 1 : 0;
+}
+
 size_t attn_scratch_floats(uint32_t n, uint32_t heads, uint32_t max_context) { return size_t(n) * heads * max_context; }
 
 void launch_attention(const AttnArgs& a, cudaStream_t s) {
@@ -561,6 +568,18 @@ void launch_attention(const AttnArgs& a, cudaStream_t s) {
 #undef BK_SCORES
 #undef BK_SCORES_T
     BK_CUDA(cudaGetLastError());
+    {
+        static const int sms = [] {
+            int dev = 0, count = 148;
+            if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev);
+            return count;
+        }();
+        const int mode = chain_mode();
+        if (mode != 0 && (a.n <= kChainMaxTokens || mode == 1) && attn_chain_fits(a.n, a.heads, a.kv_heads, a.dim, a.max_visible, uint32_t(sms))) {
+            launch_attn_chain(a, uint32_t(sms), s);
+            return;
+        }
+    }
     attn_softmax_kernel<<<dim3(a.heads, a.n), 256, 0, s>>>(a);
     BK_CUDA(cudaGetLastError());
     const uint32_t parts = (a.dim + 127) / 128;

@@ -195,6 +195,7 @@ struct Session {
     bool token_enabled = false;
     bool advance_on_device = false;  // the device greedy loop: the token kernel also feeds the next step
     std::string step_note;                 // how it was configured, or why it is not used
+    unsigned int* chain_error_dev = nullptr;  // the few-token attention kernel's error word (a device symbol)
     unsigned int* step_error_host = nullptr;  // pinned copy of the kernel's barrier-timeout word
     uint64_t persistent_steps = 0;
     uint64_t launches = 0;  // kernels launched by the current call
@@ -529,8 +530,9 @@ struct Session {
         BK_CUDA(cudaMallocHost(&logits_host, size_t(kMaxScored) * vocab * sizeof(float)));
         BK_CUDA(cudaMallocHost(&tokens_host, (kMaxBatch + 4) * sizeof(int32_t)));
         BK_CUDA(cudaMallocHost(&topk_host, 2 * kMaxTopK * sizeof(int32_t)));
-        BK_CUDA(cudaMallocHost(&step_error_host, sizeof(unsigned int)));
-        *step_error_host = 0;
+        BK_CUDA(cudaMallocHost(&step_error_host, 3 * sizeof(unsigned int)));  // [0] the persistent kernel's word, [2] the few-token attention's
+        step_error_host[0] = step_error_host[1] = step_error_host[2] = 0;
+        chain_error_dev = attn_chain_error_word();
         BK_CUDA(cudaStreamSynchronize(stream));
         plan_step();
         stats.weight_bytes = weight_bytes;
@@ -615,6 +617,10 @@ struct Session {
     void multiply(std::vector<MatTarget> targets, const DevAct& a, uint32_t n, Epilogue epi) {
         const bool pair = epi == EPI_SILU_MUL || epi == EPI_RELU2_MUL;
         if (pair) {
+            if (small_batch_on() && launch_smallbatch(targets.data(), int(targets.size()), a, n, epi, stream)) {  // 2..16 tokens
+                ++launches;
+                return;
+            }
             if (n >= 16 && gemm_supports(targets[0].m.type, targets[0].m.cols)) {
                 // prompt batches: gate and up as two tensor-core multiplies, then the activation elementwise
                 MatTarget gate{targets[0].m, targets[0].out, targets[0].ldo}, up{targets[1].m, up_b.as<float>(), targets[0].ldo};
@@ -631,7 +637,9 @@ struct Session {
         while (!targets.empty()) {
             std::vector<MatTarget> same, rest;
             for (const MatTarget& t : targets) (t.m.type == targets[0].m.type ? same : rest).push_back(t);
-            if (!(n >= 16 && launch_gemm(same.data(), int(same.size()), a, n, epi, stream))) {
+            if (small_batch_on() && launch_smallbatch(same.data(), int(same.size()), a, n, epi, stream)) {  // 2..16 tokens
+                ++launches;
+            } else if (!(n >= 16 && launch_gemm(same.data(), int(same.size()), a, n, epi, stream))) {
                 launch_matvec(same.data(), int(same.size()), a, n, epi, stream);
                 launches += (n + kMaxSmallBatch - 1) / kMaxSmallBatch;
             } else {
@@ -865,11 +873,23 @@ struct Session {
         ++persistent_steps;
     }
     // After the call's final synchronisation: did a barrier wait of the persistent kernel run out?
+    // BRISK_CUDA_SMALLBATCH=0 keeps the streaming kernel for 2..16 tokens (a comparison aid); read at every call
+    static bool small_batch_on() {
+        const char* env = std::getenv("BRISK_CUDA_SMALLBATCH");
+        return env == nullptr || std::atoi(env) != 0;
+    }
     void queue_step_check() {
+        // the few-token attention kernel waits for bulk copies (every wait bounded): its error word, read with the call's results
+        BK_CUDA(cudaMemcpyAsync(step_error_host + 2, chain_error_dev, sizeof(unsigned int), cudaMemcpyDeviceToHost, stream));
         if (token_enabled) BK_CUDA(cudaMemcpyAsync(step_error_host, token_plan.error_word(), sizeof(unsigned int), cudaMemcpyDeviceToHost, stream));
         else if (step_enabled) BK_CUDA(cudaMemcpyAsync(step_error_host, step_plan.error_word(), sizeof(unsigned int), cudaMemcpyDeviceToHost, stream));
     }
     void finish_step_check() {
+        if (step_error_host[2] != 0) {
+            step_error_host[2] = 0;
+            BK_CUDA(cudaMemsetAsync(chain_error_dev, 0, sizeof(unsigned int), stream));
+            throw CudaError("cuda: a bulk copy of the few-token attention kernel did not complete in time; the results of this call are invalid");
+        }
         if ((step_enabled || token_enabled) && *step_error_host != 0) {
             *step_error_host = 0;
             if (token_enabled) token_plan.rearm(stream);

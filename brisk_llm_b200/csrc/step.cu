@@ -354,6 +354,8 @@ __global__ void __launch_bounds__(kStepThreads, 1) step_kernel(const StepParams 
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ double red[32];
     __shared__ float redf[kDecWarps];
+    __shared__ uint64_t exp_table[32];  // 2^(i/32) for the softmax's exps: the kernel keeps almost no L1, a global table means an L2 trip per exp
+    if (threadIdx.x < 32) exp_table[threadIdx.x] = exp2_table_device()[threadIdx.x];  // ordered before its first use by the barriers of the first phases
     constexpr int kWordsPerUnit = F::kRegs;
     float* tile = reinterpret_cast<float*>(smem + P.tile_offset);
     const uint32_t cta = blockIdx.x, nctas = gridDim.x;
@@ -423,7 +425,7 @@ __global__ void __launch_bounds__(kStepThreads, 1) step_kernel(const StepParams 
             {
                 const uint32_t slices = L.attn.dim / L.attn.slice_width;
                 for (uint32_t task = cta; task < L.attn.heads * slices; task += nctas) {
-                    dec_attn_out_body<kStepThreads>(L.attn, task / slices, task % slices, smem, redf, red, gate, TaggedAttnIo{t0 + 1, t0, t0 + 2, error});
+                    dec_attn_out_body<kStepThreads>(L.attn, task / slices, task % slices, smem, redf, red, gate, TaggedAttnIo{t0 + 1, t0, t0 + 2, error}, exp_table);
                     __syncthreads();
                 }
             }
@@ -471,7 +473,7 @@ __global__ void __launch_bounds__(kStepThreads, 1) step_kernel(const StepParams 
             {
                 const uint32_t slices = L.attn.dim / L.attn.slice_width;
                 for (uint32_t task = cta; task < L.attn.heads * slices; task += nctas) {
-                    dec_attn_out_body<kStepThreads>(L.attn, task / slices, task % slices, smem, redf, red, gate);
+                    dec_attn_out_body<kStepThreads>(L.attn, task / slices, task % slices, smem, redf, red, gate, PlainIo{}, exp_table);
                     __syncthreads();  // the shared-memory row of probabilities is rewritten for the CTA's next task
                 }
             }

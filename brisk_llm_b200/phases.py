@@ -20,6 +20,7 @@ def main():
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--decode", type=int, default=16)
+    ap.add_argument("--verify", type=int, default=0, help="also break down an eval_all of this many tokens (a speculative verify step)")
     a = ap.parse_args()
     spec = replace(synth.PRESETS[a.config], context=a.context)
     model = synth.generate(spec, seed=0, share_layers=spec.layers * spec.hidden * spec.ffn > 1e9)
@@ -44,6 +45,22 @@ def main():
                 print(f"  {k:10s} {1000 * v['ms'] / a.decode:9.1f} us  {100 * v['ms'] / total:5.1f}%")
         s.generate_greedy(5, a.decode)
         print(f"  graph-replayed step, unprofiled: {1000 * s.stats()['device_ms'] / a.decode:.1f} us per token")
+        if a.verify:
+            pos = s.position()
+            probe = synth.random_tokens(spec, a.verify, seed=3)
+            s.eval_all(probe)
+            s.rollback(pos)
+            s.profile(True)
+            s.eval_all(probe)
+            p = s.profile(False)
+            s.rollback(pos)
+            total = sum(v["ms"] for v in p.values())
+            print(f"eval_all of {a.verify} tokens at context {pos}: {1000 * total:.1f} us in phases")
+            for k, v in p.items():
+                if v["calls"]:
+                    print(f"  {k:10s} {1000 * v['ms']:9.1f} us  {100 * v['ms'] / total:5.1f}%")
+            s.eval_all(probe)
+            print(f"  unprofiled: {1000 * s.stats()['device_ms']:.1f} us")
 
 
 if __name__ == "__main__":

@@ -1,4 +1,4 @@
-"""Kernel sweep: the quantised multiply on its own, every format x the sweep shapes x 1, 4 and 512 tokens.
+"""Kernel sweep: the quantised multiply on its own, every format x the sweep shapes x 1, 4, 9 and 512 tokens.
 
     python -m brisk_llm_b200.sweep [--formats Q4_0,Q8_0,...] [--quick]
 
@@ -18,7 +18,7 @@ import numpy as np
 from . import engine, formats as F
 
 SHAPES = [(1024, 3072), (2048, 8192), (4096, 14336), (14336, 4096)]  # rows x cols
-TOKENS = [1, 4, 512]
+TOKENS = [1, 4, 9, 512]
 
 
 def peak_gbs() -> float:

@@ -26,7 +26,7 @@ def check(fmt, rows, cols, n, seed=0, scale=1.0):
 
 
 @pytest.mark.parametrize("fmt", FORMATS, ids=lambda f: F.NAMES[f])
-@pytest.mark.parametrize("n", [1, 2, 4, 7, 8, 9, 20, 64])
+@pytest.mark.parametrize("n", [1, 2, 4, 7, 8, 9, 13, 16, 20, 64])
 def test_reference_test_shape(fmt, n):
     # the reference's kernel test shape: 1024 columns, 37 rows (a row count no row group divides)
     check(fmt, 37, 1024, n, seed=n)
