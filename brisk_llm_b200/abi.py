@@ -85,6 +85,8 @@ SIGNATURES = {
     "brisk_cuda_profile": (C.c_int, [C.c_void_p, C.c_int, C.c_char_p, C.c_size_t]),
     "brisk_cuda_debug_buffer": (C.c_int, [C.c_void_p, C.c_char_p, _FP, C.c_uint64]),
     "brisk_cuda_tp_unique_id": (C.c_int, [C.c_void_p, C.c_char_p, C.c_size_t]),
+    "brisk_cuda_tp_peer_handle": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "brisk_cuda_tp_peer_attach": (C.c_int, [C.c_void_p, C.c_void_p]),
 }
 
 _lib = None

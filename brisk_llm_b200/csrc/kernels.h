@@ -64,6 +64,13 @@ void launch_matvec(const MatTarget* targets, int count, const DevAct& act, uint3
 constexpr uint32_t kSmallBatchMax = 16;
 bool launch_smallbatch(const MatTarget* targets, int count, const DevAct& act, uint32_t n, Epilogue epi, cudaStream_t s);
 
+// ---- tensor-parallel exchange of one token by peer stores (tp_peer.cu) ---------------------------------
+// bufs_dev: device array of the tp ranks' exchange buffers (2 slots of slot_pairs tagged pairs each) as mapped here;
+// this rank's [rows_l] slice goes to every rank, dst receives (or is added) the whole [rows_l * tp] vector.
+constexpr uint32_t kPeerSlotPairs = 65536;
+void launch_tp_peer_exchange(uint2* const* bufs_dev, uint32_t* epoch, unsigned int* error, uint32_t tp, uint32_t rank, uint32_t slot_pairs,
+                             const float* local, float* dst, uint32_t rows_l, bool add, cudaStream_t s);
+
 // ---- batched multiply on the int8 tensor path (gemm.cu) ----------------------------------------
 // Same contract as launch_matvec for n >= 16 tokens; returns false when this type/shape has no tensor kernel
 // (the caller then uses launch_matvec).

@@ -195,6 +195,10 @@ struct Session {
     bool token_enabled = false;
     bool advance_on_device = false;  // the device greedy loop: the token kernel also feeds the next step
     std::string step_note;                 // how it was configured, or why it is not used
+    // Peer-store exchange of single tokens (tp_peer.cu): this rank's buffer of tagged pairs, the peers' buffers as mapped here.
+    DevBuffer peer_buf, peer_table, peer_state;  // peer_state: [0] the next tag, [1] the error word
+    std::vector<void*> peer_mapped;              // what cudaIpcOpenMemHandle returned (closed with the session)
+    bool peer_on = false;
     unsigned int* chain_error_dev = nullptr;  // the few-token attention kernel's error word (a device symbol)
     unsigned int* step_error_host = nullptr;  // pinned copy of the kernel's barrier-timeout word
     uint64_t persistent_steps = 0;
@@ -262,6 +266,7 @@ struct Session {
         if (step_graph) cudaGraphExecDestroy(step_graph);
         step_graph = nullptr;
         if (comm != nullptr && Nccl::get().ok()) Nccl::get().CommDestroy(comm);
+        for (void* m : peer_mapped) cudaIpcCloseMemHandle(m);
         for (cudaEvent_t e : event_pool) cudaEventDestroy(e);
         if (ev0) cudaEventDestroy(ev0);
         if (ev1) cudaEventDestroy(ev1);
@@ -530,7 +535,7 @@ struct Session {
         BK_CUDA(cudaMallocHost(&logits_host, size_t(kMaxScored) * vocab * sizeof(float)));
         BK_CUDA(cudaMallocHost(&tokens_host, (kMaxBatch + 4) * sizeof(int32_t)));
         BK_CUDA(cudaMallocHost(&topk_host, 2 * kMaxTopK * sizeof(int32_t)));
-        BK_CUDA(cudaMallocHost(&step_error_host, 3 * sizeof(unsigned int)));  // [0] the persistent kernel's word, [2] the few-token attention's
+        BK_CUDA(cudaMallocHost(&step_error_host, 3 * sizeof(unsigned int)));  // [0] the persistent kernel's word, [1] the peer exchange's, [2] the few-token attention's
         step_error_host[0] = step_error_host[1] = step_error_host[2] = 0;
         chain_error_dev = attn_chain_error_word();
         BK_CUDA(cudaStreamSynchronize(stream));
@@ -654,6 +659,10 @@ struct Session {
     void exchange(const float* local, float* dst, uint32_t n, uint32_t rows_l, bool add) {
         Scope sc(this, PH_EXCHANGE);
         const Nccl& nccl = Nccl::get();
+        if (n == 1 && peer_fits(rows_l)) {  // one token, peers mapped: stores into every rank's buffer, no collective
+            peer_exchange(local, dst, rows_l, add);
+            return;
+        }
         if (n == 1 && !add) {  // one token: the gathered order [rank][rows_l] IS the row order - no re-layout kernel
             nccl.check(nccl.AllGather(local, dst, rows_l, kNcclFloat, comm, stream), "ncclAllGather");
             ++launches;
@@ -668,9 +677,60 @@ struct Session {
     // identical) stream; the slices are gathered in place.
     void gather_in_place(float* full, uint32_t rows_l) {
         Scope sc(this, PH_EXCHANGE);
+        if (peer_fits(rows_l)) {
+            peer_exchange(full + size_t(tp_rank) * rows_l, full, rows_l, false);
+            return;
+        }
         const Nccl& nccl = Nccl::get();
         nccl.check(nccl.AllGather(full + size_t(tp_rank) * rows_l, full, rows_l, kNcclFloat, comm, stream), "ncclAllGather");
         ++launches;
+    }
+
+    bool peer_fits(uint32_t rows_l) const { return peer_on && size_t(rows_l) * size_t(tp_size) <= kPeerSlotPairs; }
+    void peer_exchange(const float* local, float* dst, uint32_t rows_l, bool add) {
+        launch_tp_peer_exchange(peer_table.as<uint2*>(), peer_state.as<uint32_t>(), peer_state.as<unsigned int>() + 1, uint32_t(tp_size), uint32_t(tp_rank),
+                                kPeerSlotPairs, local, dst, rows_l, add, stream);
+        ++launches;
+    }
+    // The 64 bytes a peer needs to map this rank's exchange buffer (allocated on the first call).
+    void peer_handle(void* out64) {
+        if (tp_size <= 1) throw CudaError("cuda: peer exchange buffers belong to tensor-parallel sessions");
+        if (peer_buf.p == nullptr) {
+            peer_buf.alloc(size_t(2) * kPeerSlotPairs * sizeof(uint2));
+            BK_CUDA(cudaMemset(peer_buf.p, 0, peer_buf.bytes));  // tag 0 is never used
+            peer_state.alloc(2 * sizeof(uint32_t));
+            const uint32_t init[2] = {1, 0};
+            BK_CUDA(cudaMemcpy(peer_state.p, init, sizeof init, cudaMemcpyHostToDevice));
+        }
+        cudaIpcMemHandle_t h;
+        BK_CUDA(cudaIpcGetMemHandle(&h, peer_buf.p));
+        static_assert(sizeof(h) == 64, "the ABI hands 64 bytes around");
+        std::memcpy(out64, &h, sizeof h);
+    }
+    // handles: tp_size x 64 bytes in rank order (this rank's own entry is ignored). Every rank must have called
+    // peer_handle() before any rank attaches, and all ranks attach before the next single-token step.
+    void peer_attach(const void* handles) {
+        if (peer_buf.p == nullptr) throw CudaError("cuda: brisk_cuda_tp_peer_handle first");
+        std::vector<uint2*> table(size_t(tp_size), nullptr);
+        for (int r = 0; r < tp_size; ++r) {
+            if (r == tp_rank) {
+                table[size_t(r)] = peer_buf.as<uint2>();
+                continue;
+            }
+            cudaIpcMemHandle_t h;
+            std::memcpy(&h, static_cast<const unsigned char*>(handles) + size_t(r) * sizeof h, sizeof h);
+            void* mapped = nullptr;
+            BK_CUDA(cudaIpcOpenMemHandle(&mapped, h, cudaIpcMemLazyEnablePeerAccess));
+            peer_mapped.push_back(mapped);
+            table[size_t(r)] = static_cast<uint2*>(mapped);
+        }
+        peer_table.alloc(table.size() * sizeof(uint2*));
+        BK_CUDA(cudaMemcpy(peer_table.p, table.data(), table.size() * sizeof(uint2*), cudaMemcpyHostToDevice));
+        if (step_graph) {  // a captured step holds all-gathers: capture again with the peer exchange
+            cudaGraphExecDestroy(step_graph);
+            step_graph = nullptr;
+        }
+        peer_on = true;
     }
 
     // The layers of one batch. n tokens are in tokens_dev, their first position in d_position(); max_visible bounds
@@ -881,10 +941,16 @@ struct Session {
     void queue_step_check() {
         // the few-token attention kernel waits for bulk copies (every wait bounded): its error word, read with the call's results
         BK_CUDA(cudaMemcpyAsync(step_error_host + 2, chain_error_dev, sizeof(unsigned int), cudaMemcpyDeviceToHost, stream));
+        if (peer_on) BK_CUDA(cudaMemcpyAsync(step_error_host + 1, peer_state.as<unsigned int>() + 1, sizeof(unsigned int), cudaMemcpyDeviceToHost, stream));
         if (token_enabled) BK_CUDA(cudaMemcpyAsync(step_error_host, token_plan.error_word(), sizeof(unsigned int), cudaMemcpyDeviceToHost, stream));
         else if (step_enabled) BK_CUDA(cudaMemcpyAsync(step_error_host, step_plan.error_word(), sizeof(unsigned int), cudaMemcpyDeviceToHost, stream));
     }
     void finish_step_check() {
+        if (step_error_host[1] != 0) {
+            step_error_host[1] = 0;
+            BK_CUDA(cudaMemsetAsync(peer_state.as<unsigned int>() + 1, 0, sizeof(unsigned int), stream));
+            throw CudaError("cuda: a tensor-parallel peer did not deliver its share of an exchange in time; the results of this call are invalid");
+        }
         if (step_error_host[2] != 0) {
             step_error_host[2] = 0;
             BK_CUDA(cudaMemsetAsync(chain_error_dev, 0, sizeof(unsigned int), stream));
@@ -1246,6 +1312,20 @@ int brisk_cuda_tp_unique_id(void* out128, char* err, size_t errlen) {
         put_error(err, errlen, e.what());
         return -1;
     }
+}
+
+int brisk_cuda_tp_peer_handle(brisk_cuda_session* session, void* out64) {
+    return guarded(session, [&] {
+        BK_CUDA(cudaSetDevice(session->s.device));
+        session->s.peer_handle(out64);
+    });
+}
+
+int brisk_cuda_tp_peer_attach(brisk_cuda_session* session, const void* handles) {
+    return guarded(session, [&] {
+        BK_CUDA(cudaSetDevice(session->s.device));
+        session->s.peer_attach(handles);
+    });
 }
 
 }  // extern "C"

@@ -1,0 +1,82 @@
+// Tensor-parallel exchange of one token's activations by peer stores, in place of an NCCL all-gather.
+//
+// Every rank owns an exchange buffer of tagged pairs {value, tag} (two slots, used alternately) that its peers have
+// mapped (CUDA IPC). One kernel per exchange and rank, a single CTA: it stores its own slice of the vector - value and
+// tag in ONE 8-byte store each - straight into every rank's buffer over NVLink, then reads its own buffer until every
+// pair carries the exchange's tag, and writes the plain vector for the kernels that follow. A pair is either the old one
+// or the new one, never half of each, so no flag, fence or second round trip is needed; the tag is a counter in device
+// memory that every rank advances once per exchange (so a replayed CUDA graph keeps counting), and since a rank can
+// finish exchange k only after every peer has at least started pushing k, ranks are never more than one exchange apart:
+// two slots are enough. Every wait is bounded: a rank whose peer never writes gives up, sets the error word the session
+// reads after the call, and ends.
+//
+// Kernels of different ranks wait for one another here, which is only sound because every rank has its own GPU.
+#include "kernels.h"
+
+namespace bk {
+namespace {
+
+constexpr uint32_t kPeerThreads = 1024;
+constexpr uint32_t kPeerPollLimit = 1u << 22;  // re-reads of one pair (~a second) before giving up
+
+struct PeerParams {
+    uint2* const* bufs;  // device array [tp]: every rank's exchange buffer, as mapped into this process
+    uint32_t* epoch;     // the next exchange's tag
+    unsigned int* error;
+    const float* local;  // this rank's slice [rows_l]
+    float* dst;          // the whole vector [rows_l * tp]
+    uint32_t tp, rank, rows_l, slot_pairs;
+    int add;
+};
+
+__device__ __forceinline__ void st_pair_sys(uint2* p, float v, uint32_t tag) {
+    asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint2 ld_pair_sys(const uint2* p) {
+    uint2 w;
+    asm volatile("ld.relaxed.sys.global.v2.b32 {%0, %1}, [%2];" : "=r"(w.x), "=r"(w.y) : "l"(p) : "memory");
+    return w;
+}
+
+__global__ void __launch_bounds__(kPeerThreads) tp_peer_exchange_kernel(const PeerParams p) {
+    const uint32_t tid = threadIdx.x;
+    // After a wait has run out the call is lost anyway (the host raises when it ends): the exchanges still queued behind it
+    // return at once instead of each waiting out its own limit.
+    if (*reinterpret_cast<volatile unsigned int*>(p.error) != 0) return;
+    const uint32_t tag = *reinterpret_cast<volatile uint32_t*>(p.epoch);
+    const uint32_t slot = (tag & 1u) * p.slot_pairs;
+    for (uint32_t i = tid; i < p.rows_l; i += kPeerThreads) {
+        const float v = p.local[i];
+        for (uint32_t r = 0; r < p.tp; ++r) st_pair_sys(p.bufs[r] + slot + p.rank * p.rows_l + i, v, tag);
+    }
+    const uint2* mine = p.bufs[p.rank] + slot;
+    bool dead = false;
+    for (uint32_t j = tid; j < p.rows_l * p.tp; j += kPeerThreads) {
+        uint2 w = ld_pair_sys(mine + j);
+        for (uint32_t spin = 0; w.y != tag && !dead; ++spin) {
+            if (spin == kPeerPollLimit) {
+                atomicOr(p.error, 1u);
+                dead = true;
+                break;
+            }
+            w = ld_pair_sys(mine + j);
+        }
+        if (w.y == tag) {
+            const float v = __uint_as_float(w.x);
+            p.dst[j] = p.add ? __fadd_rn(p.dst[j], v) : v;
+        }
+    }
+    __syncthreads();  // every thread has read the tag
+    if (tid == 0) *p.epoch = tag + 1;
+}
+
+}  // namespace
+
+void launch_tp_peer_exchange(uint2* const* bufs_dev, uint32_t* epoch, unsigned int* error, uint32_t tp, uint32_t rank, uint32_t slot_pairs,
+                             const float* local, float* dst, uint32_t rows_l, bool add, cudaStream_t s) {
+    PeerParams p{bufs_dev, epoch, error, local, dst, tp, rank, rows_l, slot_pairs, add ? 1 : 0};
+    tp_peer_exchange_kernel<<<1, kPeerThreads, 0, s>>>(p);
+    BK_CUDA(cudaGetLastError());
+}
+
+}  // namespace bk

@@ -109,6 +109,18 @@ class CudaSession:
     def position(self) -> int:
         return self._lib.brisk_cuda_position(self._h)
 
+    def tp_peer_handle(self) -> bytes:
+        """64 bytes with which the other ranks of a tensor-parallel group map this rank's exchange buffer."""
+        buf = C.create_string_buffer(64)
+        if self._lib.brisk_cuda_tp_peer_handle(self._h, buf) != 0:
+            self._fail()
+        return buf.raw
+
+    def tp_peer_attach(self, handles: bytes) -> None:
+        """handles: every rank's tp_peer_handle() in rank order. Single-token steps then exchange by peer stores."""
+        if self._lib.brisk_cuda_tp_peer_attach(self._h, handles) != 0:
+            self._fail()
+
     def log_likelihood(self, tokens, chunk: int = MAX_SCORED_TOKENS) -> float:
         """Sum over i >= 1 of log p(tokens[i] | tokens[..i]) (Engine::log_likelihood, src/engine.cpp:10-33)."""
         tokens = np.ascontiguousarray(tokens, np.int32)

@@ -59,4 +59,11 @@ def tensor_parallel_session(host_model, max_context: int = 0, flags: int = 0):
     check_tp_shape(host_model.spec, world)
     uid = engine.tp_unique_id() if rank == 0 else None
     uid = broadcast_bytes(uid, 128, 0) if world > 1 else uid
-    return engine.CudaSession(host_model, max_context=max_context, device=local, flags=flags, tp_rank=rank, tp_size=world, tp_unique_id=uid)
+    sess = engine.CudaSession(host_model, max_context=max_context, device=local, flags=flags, tp_rank=rank, tp_size=world, tp_unique_id=uid)
+    if world > 1 and os.environ.get("BRISK_CUDA_TP_PEER", "1") != "0":
+        # single-token steps exchange by stores into the peers' buffers: every rank publishes a handle of its buffer, all map all
+        handles = [None] * world
+        dist.all_gather_object(handles, sess.tp_peer_handle())
+        sess.tp_peer_attach(b"".join(handles))
+        dist.barrier()  # nobody steps before everybody has attached
+    return sess

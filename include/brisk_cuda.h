@@ -279,6 +279,15 @@ int brisk_cuda_debug_buffer(brisk_cuda_session* session, const char* name, float
  * and hands the 128 bytes to every rank's brisk_cuda_options.tp_unique_id. */
 int brisk_cuda_tp_unique_id(void* out128, char* err, size_t errlen);
 
+/* Optional, after every rank's session exists: single-token steps then exchange activations by stores into the peers'
+ * buffers (one small kernel per exchange) instead of NCCL all-gathers; prompts keep the all-gathers. Same results.
+ * Every rank calls brisk_cuda_tp_peer_handle (64 bytes out: a CUDA IPC handle of its exchange buffer), the host program
+ * gathers the handles in rank order (tp_size x 64 bytes), and every rank calls brisk_cuda_tp_peer_attach with them. All
+ * ranks must have attached before any rank runs its next single-token step. One rank per GPU, all on one node. No
+ * counterpart in the reference. */
+int brisk_cuda_tp_peer_handle(brisk_cuda_session* session, void* out64);
+int brisk_cuda_tp_peer_attach(brisk_cuda_session* session, const void* handles);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,6 +1,7 @@
 """Tensor-parallel token loop on 2, 4 and 8 GPUs (each case skipped where the machine has fewer): every rank holds its
 share of every matrix's rows and of the K/V heads - one K/V head per GPU at 8 ranks; the logits every rank returns must
-equal the CPU oracle's bit for bit, like the single-GPU path."""
+equal the CPU oracle's bit for bit, like the single-GPU path. Single-token steps exchange activations by stores into the
+peers' buffers (csrc/tp_peer.cu) or, for comparison, by NCCL all-gathers."""
 import os
 import subprocess
 import sys
@@ -64,15 +65,18 @@ WORKER = textwrap.dedent(r'''
 ''')
 
 
-@pytest.mark.parametrize("family,world", [("llama", 2), ("llama", 4), ("llama", 8), ("gemma3", 2), ("gemma3", 4)])
-def test_tensor_parallel_matches_the_oracle(family, world, tmp_path):
+# exchange of single tokens: "peer" = stores into the peers' buffers (the default), "nccl" = all-gathers as for prompts
+@pytest.mark.parametrize("family,world,exchange", [("llama", 2, "peer"), ("llama", 2, "nccl"), ("llama", 4, "peer"), ("llama", 8, "peer"),
+                                                   ("gemma3", 2, "peer"), ("gemma3", 4, "peer")])
+def test_tensor_parallel_matches_the_oracle(family, world, exchange, tmp_path):
     from brisk_llm_b200 import engine
     if engine.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     script = tmp_path / "tp_worker.py"
     script.write_text(WORKER)
-    port = 29700 + os.getpid() % 200 + (0 if family == "llama" else 211) + 17 * world
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", NCCL_IB_DISABLE="1", NCCL_SOCKET_IFNAME="lo", NCCL_DEBUG="WARN")
+    port = 29700 + os.getpid() % 200 + (0 if family == "llama" else 211) + 17 * world + (0 if exchange == "peer" else 7)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", NCCL_IB_DISABLE="1", NCCL_SOCKET_IFNAME="lo", NCCL_DEBUG="WARN",
+               BRISK_CUDA_TP_PEER="1" if exchange == "peer" else "0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
            "--master-port", str(port), str(script), H.ROOT, str(tmp_path), family]
     try:
