@@ -13,7 +13,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 OUT = os.path.join(PKG, "libbrisk_cuda.so")
 OBJ = os.path.join(PKG, "build")
-SOURCES = ["repack.cu", "activations.cu", "matvec.cu", "gemm.cu", "gemm_k.cu", "misc.cu", "gemma.cu", "decode.cu", "step.cu", "token.cu", "topk.cu", "attn_chain.cu", "smallbatch.cu", "tp_peer.cu", "session.cu", "hooks.cu"]
+SOURCES = ["repack.cu", "activations.cu", "matvec.cu", "gemm.cu", "gemm_tc.cu", "gemm_k.cu", "misc.cu", "gemma.cu", "decode.cu", "step.cu", "token.cu", "topk.cu", "attn_chain.cu", "smallbatch.cu", "tp_peer.cu", "session.cu", "hooks.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 # development aid: BRISK_TOK_TRACE=1 compiles cycle stamps into the one-launch token kernel (slower; never the default)
 EXTRA = ["-DBK_TOK_TRACE"] if os.environ.get("BRISK_TOK_TRACE") else []

@@ -17,6 +17,9 @@
 // shared memory with cp.async, two stages of 8 blocks (256 columns). Padding of 16 bytes per row keeps the fragment
 // reads bank-conflict free. The per-block rescale (5 ALU instructions per output and block) bounds the kernel, not the
 // tensor pipe: that is the price of integer-exact semantics.
+#include <cstdlib>
+#include <cstring>
+
 #include "kernels.h"
 
 namespace bk {
@@ -55,9 +58,23 @@ __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, ui
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(kMagicBits));
 }
 
-// one block's term added to a running sum in the reference's order: (float(dot) * d_w) * d_x
-__device__ __forceinline__ float add_term(float acc, int biased, float dw, float dx) {
-    return __fadd_rn(acc, __fmul_rn(__fmul_rn(__fsub_rn(__int_as_float(biased), kMagic), dw), dx));
+// Two f32 operations per instruction (packed f32x2, IEEE round-to-nearest in each half: the same results as two scalar
+// instructions). Not used for the final addition: a mul.rn.f32x2 whose only use is an add.rn.f32x2 is contracted into a
+// fused multiply-add by the assembler (measured), and the reference does not fuse.
+using f32x2 = unsigned long long;
+__device__ __forceinline__ f32x2 pack2(float a, float b) { f32x2 r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b)); return r; }
+__device__ __forceinline__ f32x2 pack2(int a, int b) { f32x2 r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(a), "r"(b)); return r; }
+__device__ __forceinline__ void unpack2(f32x2 v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b) { f32x2 r; asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) { f32x2 r; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
+
+// Two outputs of one row (token columns 2t and 2t + 1): each block's term added to its running sum in the reference's order,
+// (float(dot) * d_w) * d_x, then the add.
+__device__ __forceinline__ void add_terms(float& acc0, float& acc1, int biased0, int biased1, f32x2 dw2, f32x2 dx2) {
+    float t0, t1;
+    unpack2(mul2(mul2(sub2(pack2(biased0, biased1), pack2(kMagic, kMagic)), dw2), dx2), t0, t1);
+    acc0 = __fadd_rn(acc0, t0);
+    acc1 = __fadd_rn(acc1, t1);
 }
 
 struct GemmParams {
@@ -152,7 +169,7 @@ __global__ void __launch_bounds__(GWARPS * 32, 2) gemm_q8_kernel(const GemmParam
         for (int b = 0; b < KB; ++b) {
             if (b >= 4 && valid <= 4) continue;  // the short last chunk of a row of 8k + 4 blocks
             uint32_t a[MI][4];
-            float dw[MI][2];
+            f32x2 dw2[MI][2];  // each row's weight scale, twice (for the row's two token columns)
 #pragma unroll
             for (int mi = 0; mi < MI; ++mi) {
                 const uint32_t r0 = wr + mi * 16 + g, r1 = r0 + 8;
@@ -169,8 +186,9 @@ __global__ void __launch_bounds__(GWARPS * 32, 2) gemm_q8_kernel(const GemmParam
                     a[mi][2] = *reinterpret_cast<const uint32_t*>(aq + r0 * S::kARow + b * 32 + 16 + 4 * t);
                     a[mi][3] = *reinterpret_cast<const uint32_t*>(aq + r1 * S::kARow + b * 32 + 16 + 4 * t);
                 }
-                dw[mi][0] = __half2float(ad[r0 * KB + b]);
-                dw[mi][1] = __half2float(ad[r1 * KB + b]);
+                const float d0 = __half2float(ad[r0 * KB + b]), d1 = __half2float(ad[r1 * KB + b]);
+                dw2[mi][0] = pack2(d0, d0);
+                dw2[mi][1] = pack2(d1, d1);
             }
 #pragma unroll
             for (int ni = 0; ni < 4; ++ni) {
@@ -178,16 +196,14 @@ __global__ void __launch_bounds__(GWARPS * 32, 2) gemm_q8_kernel(const GemmParam
                 const uint32_t b0 = *reinterpret_cast<const uint32_t*>(bq + (tb + g) * S::kBRow + b * 32 + 4 * t);
                 const uint32_t b1 = *reinterpret_cast<const uint32_t*>(bq + (tb + g) * S::kBRow + b * 32 + 16 + 4 * t);
                 const uint32_t c0 = tb + 2 * t, c1 = c0 + 1;  // the two token columns this thread's results belong to
-                const float dx0 = bd[c0 * KB + b], dx1 = bd[c1 * KB + b];
+                const f32x2 dx2 = pack2(bd[c0 * KB + b], bd[c1 * KB + b]);
 #pragma unroll
                 for (int mi = 0; mi < MI; ++mi) {
                     int c[4];
                     mma_s8(c, a[mi][0], a[mi][1], a[mi][2], a[mi][3], b0, b1);
                     // (row g, col 2t) (row g, col 2t+1) (row g+8, col 2t) (row g+8, col 2t+1)
-                    acc[mi][ni][0] = add_term(acc[mi][ni][0], c[0], dw[mi][0], dx0);
-                    acc[mi][ni][1] = add_term(acc[mi][ni][1], c[1], dw[mi][0], dx1);
-                    acc[mi][ni][2] = add_term(acc[mi][ni][2], c[2], dw[mi][1], dx0);
-                    acc[mi][ni][3] = add_term(acc[mi][ni][3], c[3], dw[mi][1], dx1);
+                    add_terms(acc[mi][ni][0], acc[mi][ni][1], c[0], c[1], dw2[mi][0], dx2);
+                    add_terms(acc[mi][ni][2], acc[mi][ni][3], c[2], c[3], dw2[mi][1], dx2);
                 }
             }
         }
@@ -213,6 +229,14 @@ __global__ void __launch_bounds__(GWARPS * 32, 2) gemm_q8_kernel(const GemmParam
 
 }  // namespace
 
+bool gemm_tc_supports(int type, uint32_t cols);  // gemm_tc.cu: the same arithmetic on tcgen05 / tensor memory
+void launch_gemm_tc(const MatTarget& tg, const DevAct& act, uint32_t n, Epilogue epi, cudaStream_t s);
+// BRISK_CUDA_GEMM=tc / mma picks the prompt GEMM of Q4_0 / Q8_0 matrices (read at every call); unset: kGemmTcDefault
+constexpr bool kGemmTcDefault = false;
+static bool gemm_tc_on() {
+    const char* env = std::getenv("BRISK_CUDA_GEMM");
+    return env == nullptr ? kGemmTcDefault : std::strcmp(env, "tc") == 0;
+}
 bool gemm_k_supports(int type);  // gemm_k.cu: the 256-value super-block formats
 void launch_gemm_k(const MatTarget& tg, const DevAct& act, uint32_t n, Epilogue epi, cudaStream_t s);
 
@@ -235,6 +259,10 @@ static void launch_gemm_tile(const GemmParams& p, cudaStream_t s) {
 }
 
 static void launch_gemm_one(const MatTarget& tg, const DevAct& act, uint32_t n, Epilogue epi, cudaStream_t s) {
+    if (n >= 32 && gemm_tc_on() && gemm_tc_supports(tg.m.type, tg.m.cols)) {
+        launch_gemm_tc(tg, act, n, epi, s);
+        return;
+    }
     const GemmParams p{tg.m, act, tg.out, tg.ldo, n, int(epi)};
     static const int sms = [] {
         int dev = 0, count = 148;

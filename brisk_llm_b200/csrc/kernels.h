@@ -75,6 +75,9 @@ void launch_tp_peer_exchange(uint2* const* bufs_dev, uint32_t* epoch, unsigned i
 // Same contract as launch_matvec for n >= 16 tokens; returns false when this type/shape has no tensor kernel
 // (the caller then uses launch_matvec).
 bool launch_gemm(const MatTarget* targets, int count, const DevAct& act, uint32_t n, Epilogue epi, cudaStream_t s);
+// The Q4_0 / Q8_0 prompt multiply on tcgen05 / tensor memory (gemm_tc.cu; BRISK_CUDA_GEMM=tc): its waits are bounded, and this
+// word is non-zero on the device after a launch whose wait ran out.
+unsigned int* gemm_tc_error_word();
 bool gemm_supports(int type, uint32_t cols);
 // The activation after separate gate and up multiplies. mode 0: gate[i] = silu(gate[i]) * up[i]; 1: max(gate[i],0)^2 * up[i];
 // 2: tanh-GELU(gate[i]) * up[i] (gelu_mul_f32, src/kernels_f32.cpp:291-296), its tanh corrected by tanh_table (see

@@ -199,6 +199,7 @@ struct Session {
     DevBuffer peer_buf, peer_table, peer_state;  // peer_state: [0] the next tag, [1] the error word
     std::vector<void*> peer_mapped;              // what cudaIpcOpenMemHandle returned (closed with the session)
     bool peer_on = false;
+    unsigned int* gemm_tc_error_dev = nullptr;
     unsigned int* chain_error_dev = nullptr;  // the few-token attention kernel's error word (a device symbol)
     unsigned int* step_error_host = nullptr;  // pinned copy of the kernel's barrier-timeout word
     uint64_t persistent_steps = 0;
@@ -535,9 +536,10 @@ struct Session {
         BK_CUDA(cudaMallocHost(&logits_host, size_t(kMaxScored) * vocab * sizeof(float)));
         BK_CUDA(cudaMallocHost(&tokens_host, (kMaxBatch + 4) * sizeof(int32_t)));
         BK_CUDA(cudaMallocHost(&topk_host, 2 * kMaxTopK * sizeof(int32_t)));
-        BK_CUDA(cudaMallocHost(&step_error_host, 3 * sizeof(unsigned int)));  // [0] the persistent kernel's word, [1] the peer exchange's, [2] the few-token attention's
-        step_error_host[0] = step_error_host[1] = step_error_host[2] = 0;
+        BK_CUDA(cudaMallocHost(&step_error_host, 4 * sizeof(unsigned int)));  // [0] the persistent kernel's word, [1] the peer exchange's, [2] the few-token attention's
+        step_error_host[0] = step_error_host[1] = step_error_host[2] = step_error_host[3] = 0;  // [3]: the tcgen05 prompt multiply's
         chain_error_dev = attn_chain_error_word();
+        gemm_tc_error_dev = gemm_tc_error_word();
         BK_CUDA(cudaStreamSynchronize(stream));
         plan_step();
         stats.weight_bytes = weight_bytes;
@@ -941,11 +943,17 @@ struct Session {
     void queue_step_check() {
         // the few-token attention kernel waits for bulk copies (every wait bounded): its error word, read with the call's results
         BK_CUDA(cudaMemcpyAsync(step_error_host + 2, chain_error_dev, sizeof(unsigned int), cudaMemcpyDeviceToHost, stream));
+        BK_CUDA(cudaMemcpyAsync(step_error_host + 3, gemm_tc_error_dev, sizeof(unsigned int), cudaMemcpyDeviceToHost, stream));
         if (peer_on) BK_CUDA(cudaMemcpyAsync(step_error_host + 1, peer_state.as<unsigned int>() + 1, sizeof(unsigned int), cudaMemcpyDeviceToHost, stream));
         if (token_enabled) BK_CUDA(cudaMemcpyAsync(step_error_host, token_plan.error_word(), sizeof(unsigned int), cudaMemcpyDeviceToHost, stream));
         else if (step_enabled) BK_CUDA(cudaMemcpyAsync(step_error_host, step_plan.error_word(), sizeof(unsigned int), cudaMemcpyDeviceToHost, stream));
     }
     void finish_step_check() {
+        if (step_error_host[3] != 0) {
+            step_error_host[3] = 0;
+            BK_CUDA(cudaMemsetAsync(gemm_tc_error_dev, 0, sizeof(unsigned int), stream));
+            throw CudaError("cuda: a wait inside the tcgen05 prompt multiply ran out; the results of this call are invalid");
+        }
         if (step_error_host[1] != 0) {
             step_error_host[1] = 0;
             BK_CUDA(cudaMemsetAsync(peer_state.as<unsigned int>() + 1, 0, sizeof(unsigned int), stream));

@@ -30,9 +30,15 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--formats", default="Q4_0,Q8_0,Q4_K,Q6_K,TQ2_0")
     ap.add_argument("--quick", action="store_true", help="first and last shape only")
+    ap.add_argument("--shapes", default="", help="rows x cols pairs instead of the grid's, e.g. 4096x14336,14336x4096")
+    ap.add_argument("--tokens", default="", help="token counts instead of 1,4,9,512")
+    ap.add_argument("--iterations", type=int, default=0, help="timed multiplies per case (default 200 up to 8 tokens, 20 beyond)")
     args = ap.parse_args()
     peak = peak_gbs()
     shapes = [SHAPES[0], SHAPES[-1]] if args.quick else SHAPES
+    if args.shapes:
+        shapes = [tuple(int(v) for v in pair.split("x")) for pair in args.shapes.split(",")]
+    tokens = [int(v) for v in args.tokens.split(",")] if args.tokens else TOKENS
     rng = np.random.default_rng(0)
     print(f"{'format':6s} {'rows':>6s} {'cols':>6s} {'n':>4s} {'us':>9s} {'GB/s':>8s} {'of peak':>8s} {'GMAC/s':>9s}")
     for name in args.formats.split(","):
@@ -45,8 +51,8 @@ def main():
             wb = F.quantize(fmt, w)
             nbytes = wb.nbytes
             copies = max(2, int(300e6 // nbytes) + 1)
-            for n in TOKENS:
-                iters = 200 if n <= 8 else 20
+            for n in tokens:
+                iters = args.iterations or (200 if n <= 8 else 20)
                 sec = engine.matmul_seconds(fmt, wb, rows, cols, n, copies, iters)
                 gbs = nbytes / sec / 1e9
                 gmacs = rows * cols * n / sec / 1e9

@@ -62,6 +62,18 @@ def test_zero_and_extreme_activations(fmt):
     assert np.all(got[0] == 0.0)
 
 
+@pytest.mark.parametrize("fmt", (F.Q4_0, F.Q8_0), ids=lambda f: F.NAMES[f])
+def test_prompt_multiply_on_tcgen05_matches_the_oracle(fmt, monkeypatch):
+    """BRISK_CUDA_GEMM=tc: the prompt multiply through tcgen05.mma.kind::i8 and tensor memory (csrc/gemm_tc.cu) instead of
+    mma.sync fragments - same integers, same f32 roundings, so the oracle's bits. Ragged rows and token counts (tiles of 128
+    rows x 64 tokens), a single K chunk, and the sweep's smallest shape at 512 tokens."""
+    monkeypatch.setenv("BRISK_CUDA_GEMM", "tc")
+    check(fmt, 37, 1024, 64, seed=1)
+    check(fmt, 130, 128, 33, seed=2)
+    check(fmt, 300, 3072, 200, seed=3)
+    check(fmt, 1024, 3072, 512, seed=4)
+
+
 @pytest.mark.parametrize("fmt", (F.F16, F.BF16, F.F32), ids=lambda f: F.NAMES[f])
 def test_float_head(fmt):
     rng = np.random.default_rng(3)
