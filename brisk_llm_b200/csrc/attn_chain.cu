@@ -260,6 +260,200 @@ __global__ void __launch_bounds__(256) attn_chain_kernel(const ChainParams a) {
     for (int k = 0; k < C; ++k) o[k] = acc[k];
 }
 
+// ---- one token ------------------------------------------------------------------------------------------------------
+// With a single token there are only `heads` chains of work per value and nothing to share V rows with, and the f16 -> f32
+// widening that a chain lane does in the kernel above costs it ~3 cycles per position. So the single-token form separates
+// the roles: a CTA takes 32 values of one head; warp 0 runs the 32 chains (one per lane: a shared load and a dependent add
+// per position, two register sets), warps 1-7 produce the products p[pos] * v[pos][i] into a pair of 32 KB tiles of 256
+// positions - each product lane asks for its own 8 bytes of V three tiles ahead with cp.async into a slot only it reads
+// (a prefetch queue that costs no registers and no barrier), then loads them back, widens, multiplies and stores four
+// products with one 16-byte store. Chain and producers meet at named barriers (bar.sync / bar.arrive: nothing spins).
+// Shared-memory traffic is 8 bytes per product, which is why this form is for one token (32 products per position and CTA)
+// and the form above for several.
+constexpr uint32_t kOneThreads = 256, kOneW = 32, kOnePC = 256, kOneProducers = 7, kOneItems = 10, kOneDepth = 4;
+constexpr uint32_t kOneTileFloats = kOnePC * kOneW;                                 // 32 KB
+constexpr uint32_t kOneRingBytes = kOneDepth * kOneItems * kOneProducers * 32 * 8;  // 70 KB
+
+__device__ __forceinline__ void bar_sync_one(int id) { asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(kOneThreads) : "memory"); }
+__device__ __forceinline__ void bar_arrive_one(int id) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "n"(kOneThreads) : "memory"); }
+
+__global__ void __launch_bounds__(kOneThreads) attn_chain_one_kernel(const ChainParams a) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ float redf[8];
+    __shared__ double redd[8];
+    __shared__ uint64_t tab[32];
+    float* ps = reinterpret_cast<float*>(smem);                    // [ps_stride]
+    float* tiles = ps + a.ps_stride;                               // [2][kOnePC][kOneW]
+    unsigned char* ring = reinterpret_cast<unsigned char*>(tiles + 2 * kOneTileFloats);
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t slices = a.dim / kOneW, slice = blockIdx.x % slices, h = blockIdx.x / slices;
+    const uint32_t kvh = h / (a.heads / a.kv_heads);
+    const uint32_t visible = *a.position + 1;
+    const uint32_t start = a.window != 0 && visible > a.window ? visible - a.window : 0;
+    const uint32_t cnt = visible - start;
+    const __half* vbase = a.v_cache + (size_t(kvh) * a.max_context + start) * a.dim + slice * kOneW;
+
+    // ---- softmax (the same operations and the same split of the f64 sum as everywhere else) ----
+    if (tid < 32) tab[tid] = exp2_table_device()[tid];
+    const float* s = a.scores + size_t(h) * a.max_context + start;
+    float m = -INFINITY;
+    {
+        uint32_t p = tid;
+        for (; p + 7 * kOneThreads < cnt; p += 8 * kOneThreads) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = __ldcg(s + p + u * kOneThreads);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                ps[p + u * kOneThreads] = v[u];
+                m = fmaxf(m, v[u]);
+            }
+        }
+        for (; p < cnt; p += kOneThreads) {
+            const float v = __ldcg(s + p);
+            ps[p] = v;
+            m = fmaxf(m, v);
+        }
+    }
+    m = warp_max(m);
+    if (lane == 0) redf[warp] = m;
+    __syncthreads();
+    m = redf[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) m = fmaxf(m, redf[w]);
+    double part = 0.0;
+    {
+        uint32_t p = tid;
+        for (; p + 3 * kOneThreads < cnt; p += 4 * kOneThreads) {
+            const float e0 = exact_expf_flat(__fsub_rn(ps[p], m), tab), e1 = exact_expf_flat(__fsub_rn(ps[p + kOneThreads], m), tab);
+            const float e2 = exact_expf_flat(__fsub_rn(ps[p + 2 * kOneThreads], m), tab), e3 = exact_expf_flat(__fsub_rn(ps[p + 3 * kOneThreads], m), tab);
+            ps[p] = e0; ps[p + kOneThreads] = e1; ps[p + 2 * kOneThreads] = e2; ps[p + 3 * kOneThreads] = e3;
+            part += double(e0); part += double(e1); part += double(e2); part += double(e3);
+        }
+        for (; p < cnt; p += kOneThreads) {
+            const float e = exact_expf_flat(__fsub_rn(ps[p], m), tab);
+            ps[p] = e;
+            part += double(e);
+        }
+    }
+    part = warp_sum(part);
+    if (lane == 0) redd[warp] = part;
+    __syncthreads();
+    double total = 0.0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) total += redd[w];
+    const float inv = float(1.0 / total);
+    for (uint32_t p = tid; p < cnt; p += kOneThreads) ps[p] = __fmul_rn(ps[p], inv);
+    __syncthreads();
+
+    // ---- products and chains ----
+    const uint32_t chunks = (cnt + kOnePC - 1) / kOnePC;
+    if (warp >= 1) {
+        const uint32_t pw = warp - 1, sub = lane >> 3, lg = lane & 7;  // 8 lanes per position (4 values each), 4 positions per item
+        const uint32_t my_slot = (pw * 32 + lane) * 8;
+        constexpr uint32_t kItemStride = kOneProducers * 32 * 8;
+        auto request = [&](uint32_t chunk) {
+            if (chunk < chunks) {
+                const uint32_t rows = min(kOnePC, cnt - chunk * kOnePC);
+                unsigned char* base = ring + size_t(chunk % kOneDepth) * kOneItems * kItemStride + my_slot;
+#pragma unroll
+                for (uint32_t i = 0; i < kOneItems; ++i) {
+                    const uint32_t r = (i * kOneProducers + pw) * 4 + sub;
+                    if (r < rows) {
+                        const uint32_t dst = uint32_t(__cvta_generic_to_shared(base + i * kItemStride));
+                        asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(vbase + size_t(chunk * kOnePC + r) * a.dim + 4 * lg) : "memory");
+                    }
+                }
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");  // one group per chunk, empty or not
+        };
+#pragma unroll 1
+        for (uint32_t d = 0; d + 1 < kOneDepth; ++d) request(d);
+#pragma unroll 1
+        for (uint32_t c = 0; c < chunks; ++c) {
+            const uint32_t b = c & 1, rows = min(kOnePC, cnt - c * kOnePC);
+            request(c + kOneDepth - 1);
+            asm volatile("cp.async.wait_group %0;" ::"n"(kOneDepth - 1) : "memory");  // chunk c's values are in this lane's slots
+            if (c >= 2) bar_sync_one(3 + b);  // the chain warp is done with this buffer's previous tile
+            float* tile = tiles + size_t(b) * kOneTileFloats;
+            const unsigned char* base = ring + size_t(c % kOneDepth) * kOneItems * kItemStride + my_slot;
+            // all of the chunk's loads first, then the arithmetic
+            uint2 raw[kOneItems];
+            float pr[kOneItems];
+#pragma unroll
+            for (uint32_t i = 0; i < kOneItems; ++i) {
+                const uint32_t r = min((i * kOneProducers + pw) * 4 + sub, rows - 1);
+                raw[i] = *reinterpret_cast<const uint2*>(base + i * kItemStride);
+                pr[i] = ps[c * kOnePC + r];
+            }
+#pragma unroll
+            for (uint32_t i = 0; i < kOneItems; ++i) {
+                const uint32_t r = (i * kOneProducers + pw) * 4 + sub;
+                if (r < rows) {
+                    const __half2* hv = reinterpret_cast<const __half2*>(&raw[i]);
+                    const float2 v01 = __half22float2(hv[0]), v23 = __half22float2(hv[1]);
+                    float4 prod;
+                    prod.x = __fmul_rn(pr[i], v01.x); prod.y = __fmul_rn(pr[i], v01.y); prod.z = __fmul_rn(pr[i], v23.x); prod.w = __fmul_rn(pr[i], v23.y);
+                    *reinterpret_cast<float4*>(tile + r * kOneW + 4 * lg) = prod;
+                }
+            }
+            bar_arrive_one(1 + b);
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+    } else {
+        float acc = 0.0f;
+        const float* tile0 = tiles + lane;
+        auto load_batch = [&](const float* src, float (&dst)[8]) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) dst[u] = src[u * kOneW];
+        };
+        auto add_batch = [&](const float (&src)[8]) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) acc = __fadd_rn(acc, src[u]);
+        };
+        float s0[8], s1[8];
+        uint32_t waited = 0;  // tiles 0 .. waited - 1 have been waited for
+        if (cnt >= 16) {
+            bar_sync_one(1);
+            waited = 1;
+            load_batch(tile0, s0);
+        }
+        uint32_t pos = 0;
+#pragma unroll 1
+        for (uint32_t c = 0; c < chunks; ++c) {
+            const uint32_t rows = min(kOnePC, cnt - c * kOnePC), pairs = rows / 16;
+            if (pairs == 0) break;  // a last tile of fewer than 16 positions: below
+            const float* mine = tile0 + (c & 1) * kOneTileFloats;  // s0 holds its first 8 positions
+#pragma unroll 1
+            for (uint32_t i = 0; i + 1 < pairs; ++i) {
+                load_batch(mine + (16 * i + 8) * kOneW, s1);
+                add_batch(s0);
+                load_batch(mine + (16 * i + 16) * kOneW, s0);
+                add_batch(s1);
+            }
+            load_batch(mine + (16 * pairs - 8) * kOneW, s1);
+            add_batch(s0);
+            if (c + 1 < chunks && min(kOnePC, cnt - (c + 1) * kOnePC) >= 16) {  // the next tile's first batch, before this tile's last additions
+                bar_sync_one(1 + ((c + 1) & 1));
+                waited = c + 2;
+                load_batch(tile0 + ((c + 1) & 1) * kOneTileFloats, s0);
+            }
+            add_batch(s1);
+            pos = c * kOnePC + 16 * pairs;
+            if (rows == kOnePC && c + 2 < chunks) bar_arrive_one(3 + (c & 1));  // a product warp waits for exactly these
+        }
+        if (pos < cnt) {  // what is left of the last tile: fewer than 16 positions
+            const uint32_t c = pos / kOnePC;
+            if (waited <= c) bar_sync_one(1 + (c & 1));
+            const float* mine = tile0 + (c & 1) * kOneTileFloats;
+            for (; pos < cnt; ++pos) acc = __fadd_rn(acc, mine[(pos % kOnePC) * kOneW]);
+        }
+        a.out[size_t(h) * a.dim + slice * kOneW + lane] = acc;
+    }
+}
+
+size_t one_smem(uint32_t max_visible) { return size_t((max_visible + 3) & ~3u) * sizeof(float) + 2 * size_t(kOneTileFloats) * sizeof(float) + kOneRingBytes; }
+
 struct Choice {
     int c = 0, hq = 0;
 };
@@ -301,6 +495,20 @@ unsigned int* attn_chain_error_word() {
     unsigned int* p = nullptr;
     BK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_chain_error));
     return p;
+}
+
+bool attn_chain_one_fits(uint32_t dim, uint32_t max_visible) { return dim % kOneW == 0 && one_smem(max_visible) <= 200 * 1024; }
+
+// One token: a.scores holds its scaled scores [heads][max_context]; a.out receives the attended row.
+void launch_attn_chain_one(const AttnArgs& a, cudaStream_t s) {
+    ChainParams p{};
+    p.scores = a.scores; p.v_cache = a.v_cache; p.out = a.out; p.position = a.position;
+    p.n = 1; p.heads = a.heads; p.kv_heads = a.kv_heads; p.dim = a.dim; p.max_context = a.max_context; p.window = a.window;
+    p.ps_stride = (a.max_visible + 3) & ~3u;
+    static DeviceOnce once;
+    if (once.first()) BK_CUDA(cudaFuncSetAttribute(attn_chain_one_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attn_chain_one_kernel<<<a.heads * (a.dim / kOneW), kOneThreads, one_smem(a.max_visible), s>>>(p);
+    BK_CUDA(cudaGetLastError());
 }
 
 bool attn_chain_fits(uint32_t n, uint32_t heads, uint32_t kv_heads, uint32_t dim, uint32_t max_visible, uint32_t sms) {

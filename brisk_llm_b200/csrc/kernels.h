@@ -140,6 +140,10 @@ void launch_attention(const AttnArgs& a, cudaStream_t s);
 // two query heads, slice of the head), chain warps and product warps; same results as the kernels above.
 bool attn_chain_fits(uint32_t n, uint32_t heads, uint32_t kv_heads, uint32_t dim, uint32_t max_visible, uint32_t sms);
 void launch_attn_chain(const AttnArgs& a, uint32_t sms, cudaStream_t s);
+// The single-token form (product warps and a chain warp; same file): a.n is taken as 1.
+bool attn_chain_one_fits(uint32_t dim, uint32_t max_visible);
+void launch_attn_chain_one(const AttnArgs& a, cudaStream_t s);
+constexpr uint32_t kChainOneMinContext = 2048;  // single tokens of sessions with at least this context take it
 constexpr uint32_t kChainMaxTokens = 24;      // more tokens than this share V rows through the tiled kernel instead
 // BRISK_CUDA_CHAIN: 0 never, 1 wherever it fits (single tokens too), unset: 2..kChainMaxTokens tokens. A single token keeps
 // the fused kernel of decode.cu by default: at 8192 positions that one measures ~75 us per layer, this one 99 us (the f16 ->
