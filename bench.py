@@ -88,7 +88,12 @@ class ClockSampler:
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        self.index, self.proc, self.lines = index, None, []
+        self.index, self.proc, self.lines, self.t0 = index, None, [], None
+
+    def mark(self):
+        """The timed region starts now: samples from here on are the ones reported (the sampler itself is started a warm-up
+        step earlier - with eight ranks starting nvidia-smi at once its first line can take longer than a short timed region)."""
+        self.t0 = time.perf_counter()
 
     def start(self):
         try:
@@ -100,7 +105,7 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.perf_counter(), line.strip()))
 
     def stop(self) -> dict:
         if self.proc is None:
@@ -109,7 +114,11 @@ class ClockSampler:
         self.proc.terminate()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        inside = [line for t, line in self.lines if self.t0 is None or t >= self.t0]
+        window = "timed region"
+        if not inside:  # a timed region shorter than the sampling period: the warm-up step before it ran the same load
+            inside, window = [line for _, line in self.lines], "last warm-up step and timed region"
+        for line in inside:
             parts = [x.strip() for x in line.split(",")]
             if len(parts) < 7:
                 continue
@@ -122,7 +131,7 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "window": window}
 
 
 def workload_for(args):
@@ -455,11 +464,15 @@ def main():
         return time.perf_counter() - t1
 
     warmups = args.warmup if args.profile else max(args.warmup, 3)
-    for _ in range(warmups):
-        device_step()
     sampler = ClockSampler(local)
+    for i in range(warmups):
+        if i == warmups - 1:
+            sampler.start()
+        device_step()
+    if sampler.proc is None:
+        sampler.start()
     barrier()
-    sampler.start()
+    sampler.mark()
     pre_ms = dec_ms = 0.0
     launches = 0
     t_wall = time.perf_counter()

@@ -145,9 +145,8 @@ bool attn_chain_one_fits(uint32_t dim, uint32_t max_visible);
 void launch_attn_chain_one(const AttnArgs& a, cudaStream_t s);
 constexpr uint32_t kChainOneMinContext = 2048;  // single tokens of sessions with at least this context take it
 constexpr uint32_t kChainMaxTokens = 24;      // more tokens than this share V rows through the tiled kernel instead
-// BRISK_CUDA_CHAIN: 0 never, 1 wherever it fits (single tokens too), unset: 2..kChainMaxTokens tokens. A single token keeps
-// the fused kernel of decode.cu by default: at 8192 positions that one measures ~75 us per layer, this one 99 us (the f16 ->
-// f32 widening, which the fused kernel spreads over all its threads, costs a chain lane ~4 cycles per position here).
+// BRISK_CUDA_CHAIN: 0 never, 1 wherever it fits, unset: 2..kChainMaxTokens tokens, and single tokens (their own form of the
+// kernel, below) in sessions whose context is at least kChainOneMinContext.
 int chain_mode();
 unsigned int* attn_chain_error_word();        // non-zero on the device after a launch whose wait for a bulk copy ran out
 

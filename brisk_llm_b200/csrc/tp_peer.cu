@@ -29,13 +29,16 @@ struct PeerParams {
     int add;
 };
 
+// One 64-bit scalar access per pair: single-copy atomic in the memory model (a two-element vector access is not), so a
+// reader sees the old pair or the new one, never the new tag with the old value.
 __device__ __forceinline__ void st_pair_sys(uint2* p, float v, uint32_t tag) {
-    asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+    const unsigned long long w = (static_cast<unsigned long long>(tag) << 32) | __float_as_uint(v);
+    asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
 }
 __device__ __forceinline__ uint2 ld_pair_sys(const uint2* p) {
-    uint2 w;
-    asm volatile("ld.relaxed.sys.global.v2.b32 {%0, %1}, [%2];" : "=r"(w.x), "=r"(w.y) : "l"(p) : "memory");
-    return w;
+    unsigned long long w;
+    asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return make_uint2(static_cast<uint32_t>(w), static_cast<uint32_t>(w >> 32));
 }
 
 __global__ void __launch_bounds__(kPeerThreads) tp_peer_exchange_kernel(const PeerParams p) {
