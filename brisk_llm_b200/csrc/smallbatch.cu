@@ -8,7 +8,8 @@
 // still fills the GPU:
 //
 //   CTA            32 weight rows (two MMA row tiles; for a gate/up pair 16 rows of each, so the activation is applied in
-//                  the epilogue) x all tokens. 4096 rows give 128 CTAs.
+//                  the epilogue) x all tokens. 4096 rows give 128 CTAs (16 rows per CTA, 256 CTAs, measured slower: the
+//                  activation traffic doubles).
 //   stages         the CTA's next 8 blocks of every row - quants, f16 scales - and the tokens' quantised activations and
 //                  scales go into a ring of 5 (Q8_0: 4) stages with cp.async, 16 bytes a piece and about two pieces per
 //                  thread and chunk, four chunks ahead of the arithmetic. The rows go to padded pitches: fragment reads
@@ -27,11 +28,12 @@
 namespace bk {
 namespace {
 
-constexpr int kRows = 32, kChunk = 8, kConsumers = 256;
+constexpr int kChunk = 8, kConsumers = 256;  // a CTA takes RT (1 or 2) tiles of 16 weight rows
 
-template <int WBYTES, int NT>
+template <int WBYTES, int NT, int RT>
 struct Stage {
-    static constexpr int kStages = WBYTES == 16 ? 5 : 4;  // two CTAs per SM either way
+    static constexpr int kRows = 16 * RT;
+    static constexpr int kStages = WBYTES == 16 ? 5 : 4;  // two CTAs per SM with two row tiles; more with one
     static constexpr int kWPitch = kChunk * WBYTES + 16;
     static constexpr int kW = kRows * kWPitch;
     static constexpr int kD = kRows * kChunk * 2;   // f16 scales [row][8]
@@ -39,7 +41,7 @@ struct Stage {
     static constexpr int kX = 8 * NT * kXPitch;
     static constexpr int kDx = 8 * NT * kChunk * 4; // f32 scales [token][8]
     static constexpr int kBytes = kW + kD + kX + kDx;
-    static constexpr int kTerms = kChunk * 2 * 128 * NT * 4;  // one buffer of terms: [block][row tile][128 NT outputs]
+    static constexpr int kTerms = kChunk * RT * 128 * NT * 4;  // one buffer of terms: [block][row tile][128 NT outputs]
     static constexpr int kTotal = kStages * kBytes + 2 * kTerms;
 };
 
@@ -85,9 +87,11 @@ struct TileRef {
     uint32_t row0;
 };
 
-template <int WBYTES, int NT, bool PAIR>
+template <int WBYTES, int NT, bool PAIR, int RT>
 __global__ void __launch_bounds__(kConsumers) smallbatch_kernel(const SbParams p) {
-    using S = Stage<WBYTES, NT>;
+    static_assert(RT == 2 || !PAIR, "a gate/up pair is one row tile of each");
+    using S = Stage<WBYTES, NT, RT>;
+    constexpr int kRows = S::kRows;
     extern __shared__ __align__(128) unsigned char smem[];
     constexpr int kStages = S::kStages;
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -101,7 +105,7 @@ __global__ void __launch_bounds__(kConsumers) smallbatch_kernel(const SbParams p
         while (target + 1 < p.count && blockIdx.x >= p.first_cta[target + 1]) ++target;
         const uint32_t row0 = (blockIdx.x - p.first_cta[target]) * kRows;
         tile[0] = {target, row0};
-        tile[1] = {target, row0 + 16};
+        tile[1] = {target, row0 + 16};  // unused with one row tile
     }
     const uint32_t nb = p.m[0].blocks, chunks = nb / kChunk;
 
@@ -110,29 +114,54 @@ __global__ void __launch_bounds__(kConsumers) smallbatch_kernel(const SbParams p
     // tried first: the copy engine takes them one after the other, ~60 cycles each, and the chunk took 5000 cycles.)
     constexpr uint32_t kWPieces = kChunk * WBYTES / 16;  // 16-byte pieces of a row's quants
     const uint32_t pieces = kRows * kWPieces + kRows + p.n * (kChunk * 2) + p.n * 2;
+    // Which pieces a thread copies does not change from chunk to chunk: their sources, destinations and per-chunk strides
+    // are worked out once (the matrix descriptors sit in the kernel's parameters, and indexing those per piece and chunk
+    // cost ~500 cycles of every chunk), so that a chunk's loads are an add and a cp.async each.
+    constexpr int kMaxPieces = (kRows * kWPieces + kRows + kSmallBatchMax * (kChunk * 2) + kSmallBatchMax * 2 + kConsumers - 1) / kConsumers;
+    const unsigned char* src[kMaxPieces];
+    uint32_t dst[kMaxPieces], step[kMaxPieces];
+#pragma unroll
+    for (int k = 0; k < kMaxPieces; ++k) {
+        const uint32_t i = tid + k * kConsumers;
+        src[k] = nullptr;
+        dst[k] = step[k] = 0;
+        if (i >= pieces) continue;
+        if (i < kRows * kWPieces + kRows) {
+            const bool scales = i >= kRows * kWPieces;
+            const uint32_t r = scales ? i - kRows * kWPieces : i / kWPieces, piece = scales ? 0 : i % kWPieces;
+            const int target = r < 16 ? tile[0].target : tile[1].target;  // selects, not an indexed array: that would live in local memory
+            const DevMatrix& m = p.m[target];
+            const uint32_t row = min((r < 16 ? tile[0].row0 : tile[1].row0) + (r % 16), m.rows - 1);
+            if (scales) {
+                src[k] = reinterpret_cast<const unsigned char*>(m.d + size_t(row) * nb);
+                dst[k] = S::kW + r * (kChunk * 2);
+                step[k] = kChunk * 2;
+            } else {
+                src[k] = m.qa + size_t(row) * nb * WBYTES + piece * 16;
+                dst[k] = r * S::kWPitch + piece * 16;
+                step[k] = kChunk * WBYTES;
+            }
+        } else {
+            const uint32_t j = i - (kRows * kWPieces + kRows);
+            if (j < p.n * (kChunk * 2)) {
+                const uint32_t t = j / (kChunk * 2), piece = j % (kChunk * 2);
+                src[k] = reinterpret_cast<const unsigned char*>(p.act.q0 + size_t(t) * p.act.cols) + piece * 16;
+                dst[k] = S::kW + S::kD + t * S::kXPitch + piece * 16;
+                step[k] = kChunk * 32;
+            } else {
+                const uint32_t q = j - p.n * (kChunk * 2), t = q / 2, piece = q % 2;
+                src[k] = reinterpret_cast<const unsigned char*>(p.act.d0 + size_t(t) * nb + piece * 4);
+                dst[k] = S::kW + S::kD + S::kX + t * (kChunk * 4) + piece * 16;
+                step[k] = kChunk * 4;
+            }
+        }
+    }
     auto load_stage = [&](uint32_t c) {
         if (c < chunks) {
             unsigned char* st = smem + size_t(c % kStages) * S::kBytes;
-            const uint32_t b0 = c * kChunk;
-            for (uint32_t i = tid; i < pieces; i += kConsumers) {
-                if (i < kRows * kWPieces + kRows) {
-                    const bool scales = i >= kRows * kWPieces;
-                    const uint32_t r = scales ? i - kRows * kWPieces : i / kWPieces, piece = scales ? 0 : i % kWPieces;
-                    const int target = r < 16 ? tile[0].target : tile[1].target;  // selects, not an indexed array: that would live in local memory
-                    const DevMatrix& m = p.m[target];
-                    const uint32_t row = min((r < 16 ? tile[0].row0 : tile[1].row0) + (r % 16), m.rows - 1);
-                    if (scales) cp_async16(st + S::kW + r * (kChunk * 2), m.d + size_t(row) * nb + b0);
-                    else cp_async16(st + r * S::kWPitch + piece * 16, m.qa + (size_t(row) * nb + b0) * WBYTES + piece * 16);
-                } else {
-                    const uint32_t j = i - (kRows * kWPieces + kRows);
-                    if (j < p.n * (kChunk * 2)) {
-                        const uint32_t t = j / (kChunk * 2), piece = j % (kChunk * 2);
-                        cp_async16(st + S::kW + S::kD + t * S::kXPitch + piece * 16, p.act.q0 + size_t(t) * p.act.cols + size_t(b0) * 32 + piece * 16);
-                    } else {
-                        const uint32_t k = j - p.n * (kChunk * 2), t = k / 2, piece = k % 2;
-                        cp_async16(st + S::kW + S::kD + S::kX + t * (kChunk * 4) + piece * 16, p.act.d0 + size_t(t) * nb + b0 + piece * 4);
-                    }
-                }
+#pragma unroll
+            for (int k = 0; k < kMaxPieces; ++k) {
+                if (src[k] != nullptr) cp_async16(st + dst[k], src[k] + size_t(c) * step[k]);
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");  // one group per chunk, empty or not
@@ -147,7 +176,7 @@ __global__ void __launch_bounds__(kConsumers) smallbatch_kernel(const SbParams p
     const uint32_t g = lane >> 2, t = lane & 3;
     float* terms = reinterpret_cast<float*>(smem + size_t(kStages) * S::kBytes);
     constexpr uint32_t kOut = 128 * NT;  // outputs per row tile
-    float acc[2] = {0.0f, 0.0f};
+    float acc[2] = {0.0f, 0.0f};  // [1] unused with one row tile
     for (uint32_t c = 0; c < chunks; ++c) {
         const long long t_l = SB_CLOCK();
         load_stage(c + kStages - 1);  // into the stage of chunk c - 1: everybody left it before the barrier that ended the last iteration
@@ -156,11 +185,11 @@ __global__ void __launch_bounds__(kConsumers) smallbatch_kernel(const SbParams p
         const unsigned char* st = smem + size_t(c % kStages) * S::kBytes;
         const unsigned char* xs = st + S::kW + S::kD;
         const float* dxs = reinterpret_cast<const float*>(xs + S::kX);
-        float* tb = terms + size_t(c & 1) * (S::kTerms / 4) + size_t(warp) * 2 * kOut;  // this warp's block of the chunk
+        float* tb = terms + size_t(c & 1) * (S::kTerms / 4) + size_t(warp) * RT * kOut;  // this warp's block of the chunk
         uint32_t a[2][4];
         float dw[2][2];
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
+        for (int j = 0; j < RT; ++j) {
             const uint32_t r0 = j * 16 + g, r1 = r0 + 8;
             if (WBYTES == 16) {
                 const uint32_t w0 = *reinterpret_cast<const uint32_t*>(st + r0 * S::kWPitch + warp * 16 + 4 * t);
@@ -185,7 +214,7 @@ __global__ void __launch_bounds__(kConsumers) smallbatch_kernel(const SbParams p
             const uint32_t b1 = *reinterpret_cast<const uint32_t*>(xs + (ni * 8 + g) * S::kXPitch + warp * 32 + 16 + 4 * t);
             const float dx0 = dxs[(ni * 8 + 2 * t) * kChunk + warp], dx1 = dxs[(ni * 8 + 2 * t + 1) * kChunk + warp];
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
+            for (int j = 0; j < RT; ++j) {
                 int d[4];
                 mma_s8(d, a[j], b0, b1);
                 // outputs of a row tile are numbered  o = ((ni * 2 + half) * 4 + t) * 16 + g * 2 + (column & 1)
@@ -206,8 +235,8 @@ __global__ void __launch_bounds__(kConsumers) smallbatch_kernel(const SbParams p
             const float* tc = terms + size_t(c & 1) * (S::kTerms / 4) + tid;
 #pragma unroll
             for (int b = 0; b < kChunk; ++b) {
-                acc[0] = __fadd_rn(acc[0], tc[(b * 2 + 0) * kOut]);
-                acc[1] = __fadd_rn(acc[1], tc[(b * 2 + 1) * kOut]);
+                acc[0] = __fadd_rn(acc[0], tc[(b * RT + 0) * kOut]);
+                if (RT == 2) acc[1] = __fadd_rn(acc[1], tc[(b * RT + 1) * kOut]);
             }
         }
         SB_ADD(5, t_c);
@@ -225,7 +254,7 @@ __global__ void __launch_bounds__(kConsumers) smallbatch_kernel(const SbParams p
                 }
             } else {
 #pragma unroll
-                for (int j = 0; j < 2; ++j) {
+                for (int j = 0; j < RT; ++j) {
                     const uint32_t row = tile[j].row0 + r;
                     if (row < p.m[tile[j].target].rows) {
                         float* o = p.out[tile[j].target] + size_t(tok) * p.ldo[tile[j].target] + row;
@@ -237,23 +266,25 @@ __global__ void __launch_bounds__(kConsumers) smallbatch_kernel(const SbParams p
     }
 }
 
-template <int WBYTES, int NT, bool PAIR>
+template <int WBYTES, int NT, bool PAIR, int RT>
 void launch_variant(const SbParams& p, uint32_t ctas, cudaStream_t s) {
-    using S = Stage<WBYTES, NT>;
+    using S = Stage<WBYTES, NT, RT>;
     static DeviceOnce once;
-    if (once.first()) BK_CUDA(cudaFuncSetAttribute(smallbatch_kernel<WBYTES, NT, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
-    smallbatch_kernel<WBYTES, NT, PAIR><<<ctas, kConsumers, S::kTotal, s>>>(p);
+    if (once.first()) BK_CUDA(cudaFuncSetAttribute(smallbatch_kernel<WBYTES, NT, PAIR, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
+    smallbatch_kernel<WBYTES, NT, PAIR, RT><<<ctas, kConsumers, S::kTotal, s>>>(p);
     BK_CUDA(cudaGetLastError());
 }
 
 template <int WBYTES>
-void launch_type(const SbParams& p, uint32_t ctas, bool pair, cudaStream_t s) {
+void launch_type(const SbParams& p, uint32_t ctas, bool pair, int row_tiles, cudaStream_t s) {
     if (p.n <= 8) {
-        if (pair) launch_variant<WBYTES, 1, true>(p, ctas, s);
-        else launch_variant<WBYTES, 1, false>(p, ctas, s);
+        if (pair) launch_variant<WBYTES, 1, true, 2>(p, ctas, s);
+        else if (row_tiles == 2) launch_variant<WBYTES, 1, false, 2>(p, ctas, s);
+        else launch_variant<WBYTES, 1, false, 1>(p, ctas, s);
     } else {
-        if (pair) launch_variant<WBYTES, 2, true>(p, ctas, s);
-        else launch_variant<WBYTES, 2, false>(p, ctas, s);
+        if (pair) launch_variant<WBYTES, 2, true, 2>(p, ctas, s);
+        else if (row_tiles == 2) launch_variant<WBYTES, 2, false, 2>(p, ctas, s);
+        else launch_variant<WBYTES, 2, false, 1>(p, ctas, s);
     }
 }
 
@@ -278,6 +309,17 @@ bool launch_smallbatch(const MatTarget* targets, int count, const DevAct& act, u
     p.epi = epi;
     p.act = act;
     p.n = n;
+    static const uint32_t sms = [] {
+        int dev = 0, count = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev);
+        return uint32_t(count);
+    }();
+    // Two row tiles (32 rows) per CTA share the activation loads. One tile per CTA (16 rows, twice the CTAs) for matrices of
+    // few rows was measured and is slower - 4096 x 14336 at 9 tokens 49.2 us against 44.0, 4096 x 4096 19.7 against 18.4 - so
+    // it stays a compile-time option of the kernel that nothing selects.
+    (void)sms;
+    const int row_tiles = 2;
+    const uint32_t rows_per_cta = 16u * uint32_t(row_tiles);
     uint32_t ctas = 0;
     for (int i = 0; i < count; ++i) {
         p.m[i] = targets[i].m;
@@ -285,13 +327,13 @@ bool launch_smallbatch(const MatTarget* targets, int count, const DevAct& act, u
         p.ldo[i] = targets[i].ldo;
         if (!pair) {
             p.first_cta[i] = ctas;
-            ctas += (targets[i].m.rows + kRows - 1) / kRows;
+            ctas += (targets[i].m.rows + rows_per_cta - 1) / rows_per_cta;
         }
     }
     if (pair) ctas = (targets[0].m.rows + 15) / 16;
     else p.first_cta[count] = ctas;
-    if (targets[0].m.type == T_Q4_0) launch_type<16>(p, ctas, pair, s);
-    else launch_type<32>(p, ctas, pair, s);
+    if (targets[0].m.type == T_Q4_0) launch_type<16>(p, ctas, pair, row_tiles, s);
+    else launch_type<32>(p, ctas, pair, row_tiles, s);
     return true;
 }
 
