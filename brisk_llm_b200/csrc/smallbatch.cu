@@ -75,8 +75,16 @@ __device__ __forceinline__ void mma_s8(int (&d)[4], const uint32_t (&a)[4], uint
         : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(kMagicBits));
 }
-__device__ __forceinline__ float term_of(int biased, float dw, float dx) {
-    return __fmul_rn(__fmul_rn(__fsub_rn(__int_as_float(biased), kMagic), dw), dx);
+// Two terms per instruction: packed f32x2 subtract and multiplies round each half exactly as the scalar instructions do
+// (there is no add here for the assembler to fuse them with: the terms go to shared memory).
+using f32x2 = unsigned long long;
+__device__ __forceinline__ f32x2 pack2(float a, float b) { f32x2 r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b)); return r; }
+__device__ __forceinline__ f32x2 pack2(int a, int b) { f32x2 r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(a), "r"(b)); return r; }
+__device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b) { f32x2 r; asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) { f32x2 r; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
+// ((float(dot0), float(dot1)) * d_w) * (d_x0, d_x1)
+__device__ __forceinline__ f32x2 terms_of(int biased0, int biased1, f32x2 dw2, f32x2 dx2) {
+    return mul2(mul2(sub2(pack2(biased0, biased1), pack2(kMagic, kMagic)), dw2), dx2);
 }
 // four nibbles 0..15, one per byte -> four signed bytes (nibble - 8): no borrow can cross a byte once bit 7 is set
 __device__ __forceinline__ uint32_t recentre(uint32_t nibbles) { return ((nibbles | 0x80808080u) - 0x08080808u) ^ 0x80808080u; }
@@ -212,15 +220,15 @@ __global__ void __launch_bounds__(kConsumers) smallbatch_kernel(const SbParams p
         for (int ni = 0; ni < NT; ++ni) {
             const uint32_t b0 = *reinterpret_cast<const uint32_t*>(xs + (ni * 8 + g) * S::kXPitch + warp * 32 + 4 * t);
             const uint32_t b1 = *reinterpret_cast<const uint32_t*>(xs + (ni * 8 + g) * S::kXPitch + warp * 32 + 16 + 4 * t);
-            const float dx0 = dxs[(ni * 8 + 2 * t) * kChunk + warp], dx1 = dxs[(ni * 8 + 2 * t + 1) * kChunk + warp];
+            const f32x2 dx2 = pack2(dxs[(ni * 8 + 2 * t) * kChunk + warp], dxs[(ni * 8 + 2 * t + 1) * kChunk + warp]);
 #pragma unroll
             for (int j = 0; j < RT; ++j) {
                 int d[4];
                 mma_s8(d, a[j], b0, b1);
                 // outputs of a row tile are numbered  o = ((ni * 2 + half) * 4 + t) * 16 + g * 2 + (column & 1)
                 float2* dst = reinterpret_cast<float2*>(tb + j * kOut + ((ni * 2) * 4 + t) * 16 + g * 2);
-                dst[0] = make_float2(term_of(d[0], dw[j][0], dx0), term_of(d[1], dw[j][0], dx1));   // rows g
-                dst[32] = make_float2(term_of(d[2], dw[j][1], dx0), term_of(d[3], dw[j][1], dx1));  // rows g + 8: half 1, 64 floats on
+                *reinterpret_cast<f32x2*>(dst) = terms_of(d[0], d[1], pack2(dw[j][0], dw[j][0]), dx2);       // rows g
+                *reinterpret_cast<f32x2*>(dst + 32) = terms_of(d[2], d[3], pack2(dw[j][1], dw[j][1]), dx2);  // rows g + 8: half 1, 64 floats on
             }
         }
         SB_ADD(2, t_m);
