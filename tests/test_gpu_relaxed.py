@@ -5,9 +5,10 @@ steps, decoded with the order of two kinds of sums relaxed the way a GPU kernel 
   attention  softmax and weighted sum over eight ranges of positions, combined afterwards, with the fast exp
 
 - against the exact path (which is the reference's result bit for bit, tests/test_gpu_fullsize.py). The stated tolerance is
-max-abs 2e-2 and relative L2 1e-3 per step. This test asserts nothing about the relaxed numbers; it PRINTS them (pytest -s),
-and the table it printed on a B200 is in DESIGN.md. The relaxations are switched by BRISK_CUDA_RELAXED, exist in the
-one-kernel-per-operation path only and are never on by default."""
+max-abs 2e-2 and relative L2 1e-3 per step. This test asserts nothing about the relaxed numbers; it PRINTS them (pytest -s).
+On a B200 every one of the 128 steps left the tolerance with either relaxation (worst step: max-abs 4.4e-2 to 4.7e-2, relative L2
+1.4e-2) while the greedy ids and the mean negative log-likelihood to three decimals stayed. The relaxations are switched by
+BRISK_CUDA_RELAXED, exist in the one-kernel-per-operation path only and are never on by default."""
 import numpy as np
 import pytest
 
