@@ -697,6 +697,7 @@ struct Session {
     // The 64 bytes a peer needs to map this rank's exchange buffer (allocated on the first call).
     void peer_handle(void* out64) {
         if (tp_size <= 1) throw CudaError("cuda: peer exchange buffers belong to tensor-parallel sessions");
+        if (tp_size > 8) throw CudaError("cuda: the peer exchange takes up to 8 ranks");
         if (peer_buf.p == nullptr) {
             peer_buf.alloc(size_t(2) * kPeerSlotPairs * sizeof(uint2));
             BK_CUDA(cudaMemset(peer_buf.p, 0, peer_buf.bytes));  // tag 0 is never used

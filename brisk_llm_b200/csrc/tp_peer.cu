@@ -48,25 +48,57 @@ __global__ void __launch_bounds__(kPeerThreads) tp_peer_exchange_kernel(const Pe
     if (*reinterpret_cast<volatile unsigned int*>(p.error) != 0) return;
     const uint32_t tag = *reinterpret_cast<volatile uint32_t*>(p.epoch);
     const uint32_t slot = (tag & 1u) * p.slot_pairs;
+    uint2* peer[8];  // the ranks' buffers, read from the table once (tensor parallelism goes up to 8 ranks)
+#pragma unroll
+    for (uint32_t r = 0; r < 8; ++r) peer[r] = r < p.tp ? p.bufs[r] + slot + p.rank * p.rows_l : nullptr;
     for (uint32_t i = tid; i < p.rows_l; i += kPeerThreads) {
         const float v = p.local[i];
-        for (uint32_t r = 0; r < p.tp; ++r) st_pair_sys(p.bufs[r] + slot + p.rank * p.rows_l + i, v, tag);
+#pragma unroll
+        for (uint32_t r = 0; r < 8; ++r) {
+            if (r < p.tp) st_pair_sys(peer[r] + i, v, tag);
+        }
     }
     const uint2* mine = p.bufs[p.rank] + slot;
+    // Read back in batches of independent loads: one L2 round trip fetches a thread's whole share when it is already there
+    // (one pair after the other, each round trip waited for the one before: 14 of them for the widest vector), and only
+    // what has not arrived yet is read again.
+    constexpr uint32_t kBatch = 8;
+    const uint32_t total = p.rows_l * p.tp;
     bool dead = false;
-    for (uint32_t j = tid; j < p.rows_l * p.tp; j += kPeerThreads) {
-        uint2 w = ld_pair_sys(mine + j);
-        for (uint32_t spin = 0; w.y != tag && !dead; ++spin) {
+    for (uint32_t j0 = tid; j0 < total; j0 += kBatch * kPeerThreads) {
+        uint2 w[kBatch];
+        uint32_t pending = 0;
+#pragma unroll
+        for (uint32_t k = 0; k < kBatch; ++k) {
+            const uint32_t j = j0 + k * kPeerThreads;
+            if (j < total) {
+                w[k] = ld_pair_sys(mine + j);
+                pending |= (w[k].y != tag) << k;
+            } else {
+                w[k] = make_uint2(0, tag);
+            }
+        }
+        for (uint32_t spin = 0; pending != 0 && !dead; ++spin) {
             if (spin == kPeerPollLimit) {
                 atomicOr(p.error, 1u);
                 dead = true;
                 break;
             }
-            w = ld_pair_sys(mine + j);
+#pragma unroll
+            for (uint32_t k = 0; k < kBatch; ++k) {
+                if (pending & (1u << k)) {
+                    w[k] = ld_pair_sys(mine + j0 + k * kPeerThreads);
+                    if (w[k].y == tag) pending &= ~(1u << k);
+                }
+            }
         }
-        if (w.y == tag) {
-            const float v = __uint_as_float(w.x);
-            p.dst[j] = p.add ? __fadd_rn(p.dst[j], v) : v;
+#pragma unroll
+        for (uint32_t k = 0; k < kBatch; ++k) {
+            const uint32_t j = j0 + k * kPeerThreads;
+            if (j < total && !(pending & (1u << k))) {
+                const float v = __uint_as_float(w[k].x);
+                p.dst[j] = p.add ? __fadd_rn(p.dst[j], v) : v;
+            }
         }
     }
     __syncthreads();  // every thread has read the tag
