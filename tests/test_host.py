@@ -181,3 +181,33 @@ def test_ctypes_mirror_has_the_layout_of_the_c_header(tmp_path):
     assert int(out["layer.slides"]) == abi.Layer.slides.offset
     assert int(out["model.gelu"]) == abi.Model.gelu.offset
     assert int(out["abi"]) == abi.ABI_VERSION
+
+
+def test_bench_helpers_follow_the_workload():
+    """The figures bench.py derives without a GPU: counted DRAM traffic of a token, the CPU arm's sample, the clock
+    sampler's window."""
+    import importlib.util
+    import time
+    spec_ = importlib.util.spec_from_file_location("bench_module", os.path.join(H.ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec_)
+    spec_.loader.exec_module(bench)
+    spec = synth.PRESETS["qwen3-0.6b-q4_0"]
+    # weights once + K and V rows of all layers at the mean context of the decode steps (f16) + one row of logits (f32)
+    traffic = bench.analytic_traffic(spec, 1000, 512, 128)
+    assert traffic == 1000 + spec.layers * 2 * spec.kv_heads * spec.head_dim * 2 * (512 + 64) + spec.vocab * 4
+    # the 0.6B-class model runs its whole workload on the CPU, the 7B-class one a sample
+    assert bench.cpu_sample_sizes(spec, 512, 128) == (512, 129)
+    big = bench.cpu_sample_sizes(synth.PRESETS["mistral-7b-q4_0"], 8192, 512)
+    assert 8 <= big[0] < 64 and 4 <= big[1] < 16
+    # clock samples: only lines from the timed region count; a region shorter than the sampling period falls back to all lines
+    s = bench.ClockSampler(0)
+    s.proc = type("P", (), {"terminate": lambda self: None})()
+    now = time.perf_counter()
+    s.lines = [(now - 1.0, "1200, 1965, 300.0, Not Active, Not Active, Not Active, Active"),
+               (now + 0.5, "1965, 1965, 900.0, Not Active, Not Active, Not Active, Not Active")]
+    s.t0 = now
+    inside = s.stop()
+    assert inside["sm_mhz"] == 1965.0 and inside["reasons"] == [] and inside["samples"] == 1 and inside["window"] == "timed region"
+    s.t0 = now + 2.0
+    fallback = s.stop()
+    assert fallback["samples"] == 2 and fallback["reasons"] == ["sw_power_cap"] and "warm-up" in fallback["window"]
