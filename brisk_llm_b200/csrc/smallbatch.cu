@@ -14,7 +14,8 @@
 //                  scales go into a ring of 5 (Q8_0: 4) stages with cp.async, 16 bytes a piece and about two pieces per
 //                  thread and chunk, four chunks ahead of the arithmetic. The rows go to padded pitches: fragment reads
 //                  are conflict-free.
-//   8 MMA warps    split a stage's 8 blocks, one each: fragments straight from the stage (Q4_0 nibbles are widened and
+//   8 MMA warps    split a stage's 8 blocks, one each (16-block stages with two blocks per warp were measured: the same
+//                  time for a whole verify step): fragments straight from the stage (Q4_0 nibbles are widened and
 //                  re-centred in registers), one MMA per (row tile, 8 tokens), and each integer dot becomes its block's
 //                  term (float(dot) * d_w) * d_x. The MMA's C operand is the bit pattern of 1.5 * 2^23, so the integer comes
 //                  out as a float with one exact subtraction.
